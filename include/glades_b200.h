@@ -1,0 +1,207 @@
+/*
+ * glades_b200.h -- C ABI of the B200-native deep feed-forward train/infer path.
+ *
+ * The reference library (Gattic/glades-ml) has no FFI: its feed-forward path is the C++ member
+ * function NNetwork::run (Backend/Machine Learning/Networks/network.cpp:114-397) and the
+ * per-node / per-edge heap objects below it (State/LayerBuilder.cpp, State/node.cpp,
+ * State/edge.cpp, GMath/gmath.cpp, GMath/cmatrix.cpp).  This header is the boundary a maintainer
+ * binds instead: plain pointers and sizes, no C++ or torch types.  Each entry point names the
+ * reference code it replaces.  All entry points return 0 on success or a negative gl_status;
+ * gl_last_error() gives the text of the last failure on the calling thread.
+ *
+ * Layout conventions (all fp32, row-major):
+ *   layers 0..H+1 (0 = input, H+1 = output), n_l nodes each;
+ *   W_l is [n_{l+1}][n_l] (node-major, edge-minor, the order of LayerBuilder::getWeights,
+ *   State/LayerBuilder.cpp:390-410); the flat weight vector is W_0 | W_1 | ... | W_H;
+ *   one scalar bias per hidden layer l = 1..H (State/layer.h:35), used when computing layer l+1;
+ *   X is [rows][n_0], Y (expected) is [rows][n_{H+1}].
+ *
+ * The library needs a CUDA device of compute capability 10.0 (B200); there is no CPU path.
+ */
+#ifndef GLADES_B200_H
+#define GLADES_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define GL_MAX_WEIGHT_LAYERS 16
+
+/* activation ids: GMath::TANH..STEP, GMath/gmath.h:43-50; GL_ACT_SOFTMAX is an extension that
+ * the reference does not have (it is only legal on the last layer of a batched-mode network). */
+enum { GL_ACT_TANH = 0, GL_ACT_TANHP = 1, GL_ACT_SIGMOID = 2, GL_ACT_SIGMOIDP = 3, GL_ACT_LINEAR = 4,
+       GL_ACT_RELU = 5, GL_ACT_LEAKY = 6, GL_ACT_STEP = 7, GL_ACT_SOFTMAX = 8 };
+/* cost ids: GMath::REGRESSION / CLASSIFICATION / KL, GMath/gmath.h:38-40 */
+enum { GL_OUT_REGRESSION = 0, GL_OUT_CLASSIFICATION = 1, GL_OUT_KL = 2 };
+
+/* Arithmetic mode.
+ * GL_MODE_REFERENCE reproduces NNetwork::SGDHelper exactly, sample after sample: the online scalar
+ * bias update (network.cpp:653-656), the doubling error accumulation (network.cpp:660-662 with
+ * State/node.cpp:173-176), the {0},{1..mb},{mb+1..2mb} apply rows (network.cpp:646-651) and the
+ * intra-window momentum history (node.cpp:278-307).  It is sequential by construction.
+ * GL_MODE_BATCHED is the data-parallel mode: aligned windows of batch_size rows, weights and
+ * biases frozen inside a window, plain error sum, bias delta summed per window, optional
+ * softmax + cross-entropy head.  It is the only mode that shards over GPUs. */
+enum { GL_MODE_REFERENCE = 0, GL_MODE_BATCHED = 1 };
+
+/* Batched-mode scalar-bias step: GL_BIAS_MEAN b_l -= lr_l*sum(D)/mb; GL_BIAS_REFERENCE keeps the
+ * reference's magnitude b_l -= n_l*lr_l*sum(D) (the update runs once per (input, output) pair
+ * per sample, network.cpp:585-587,653-656). */
+enum { GL_BIAS_MEAN = 0, GL_BIAS_REFERENCE = 1 };
+
+/* Matrix-product engine for batched mode: GL_GEMM_AUTO picks by shape; GL_GEMM_FFMA forces the
+ * exact-fp32 FFMA tile kernel; GL_GEMM_TCGEN05 forces the TMA + tcgen05 3xTF32 kernel (shapes
+ * must then be multiples of its tile). */
+enum { GL_GEMM_AUTO = 0, GL_GEMM_FFMA = 1, GL_GEMM_TCGEN05 = 2 };
+
+typedef enum gl_status {
+	GL_OK = 0,
+	GL_ERR_INVALID = -1,    /* bad argument / descriptor */
+	GL_ERR_CUDA = -2,       /* a CUDA call failed; text in gl_last_error() */
+	GL_ERR_NO_DEVICE = -3,  /* no sm_100 device: there is no CPU fallback */
+	GL_ERR_STATE = -4,      /* call order (no data, no weights, wrong mode) */
+	GL_ERR_NONFINITE = -5,  /* reserved: weights went inf/NaN (reported in gl_metrics, not fatal) */
+	GL_ERR_TIMEOUT = -6,    /* a bounded device-side wait ran out */
+	GL_ERR_COMM = -7,       /* NCCL failure */
+	GL_ERR_TOO_LARGE = -8   /* size beyond a stated maximum */
+} gl_status;
+
+/* Hyper-parameters of one network, as NNInfo hands them to the loop.  Index l of the per-layer
+ * arrays is NNInfo's index l (Structure/nninfo.cpp:240-373): l = 0 the InputLayerInfo, l >= 1
+ * hidden layer l-1; entry l governs W_l and the activation that produces layer l+1
+ * (network.cpp:505-506,635-638).  The caller resolves NNInfo's quirks when filling it, e.g.
+ * getWeightDecay2(0) returning weightDecay1 (nninfo.cpp:305-306). */
+typedef struct gl_net_desc {
+	int32_t n_layers;                          /* node layers incl. input and output = H + 2 */
+	int32_t sizes[GL_MAX_WEIGHT_LAYERS + 1];   /* n_0 .. n_{H+1} */
+	float lr[GL_MAX_WEIGHT_LAYERS];
+	float momentum[GL_MAX_WEIGHT_LAYERS];
+	float wd1[GL_MAX_WEIGHT_LAYERS];
+	float wd2[GL_MAX_WEIGHT_LAYERS];
+	float p_dropout[GL_MAX_WEIGHT_LAYERS];     /* must be 0: dropout is not on this path yet */
+	int32_t activation[GL_MAX_WEIGHT_LAYERS];
+	float act_param[GL_MAX_WEIGHT_LAYERS];
+	int32_t output_type;                       /* GL_OUT_* (NNInfo::getOutputType) */
+	int32_t batch_size;                        /* NNInfo::getBatchSize, nninfo.cpp:154-160 */
+	int32_t mode;                              /* GL_MODE_* */
+	int32_t bias_rule;                         /* GL_BIAS_*, batched mode only */
+	int32_t gemm;                              /* GL_GEMM_* */
+	int32_t device;                            /* CUDA device ordinal */
+} gl_net_desc;
+
+/* Per-epoch (or per-call) statistics: the members NNetwork::run leaves behind
+ * (network.cpp:179-224): overallTotalError, overallTotalAccuracy (already divided by
+ * rows*n_out) and the five confusion-matrix figures in percent. */
+typedef struct gl_metrics {
+	float total_error;
+	float total_accuracy;
+	float class_accuracy;
+	float class_precision;
+	float class_recall;
+	float class_specificity;
+	float class_f1;
+	int32_t epochs;          /* epochs completed by this handle so far */
+	int32_t nonfinite;       /* 1 if a weight or bias is inf/NaN after the call */
+	int64_t rows;            /* rows the figures cover (all ranks) */
+	double device_ms;        /* device time of the call, CUDA events on the library's stream */
+	int64_t kernel_launches; /* kernels of this library launched by the call */
+} gl_metrics;
+
+typedef struct gl_net gl_net;
+
+const char* gl_last_error(void);
+/* Number of usable sm_100 devices (0 when there is none or no driver). */
+int gl_device_count(void);
+
+/* Replaces LayerBuilder::build (State/LayerBuilder.cpp:54-98) minus the weight draw: allocates
+ * the per-layer device matrices.  Weights start at 0 until gl_set_weights. */
+int gl_create(const gl_net_desc* desc, gl_net** out);
+/* Replaces LayerBuilder::clean / NNetwork::~NNetwork. */
+int gl_destroy(gl_net* net);
+
+/* Replaces Node::setEdgeWeight / Layer::setBiasWeight (State/node.cpp:142-148,
+ * State/layer.cpp:70-73) for the whole network.  bias has H entries (hidden layers 1..H) and
+ * may be NULL (= zeros).  Also clears pending deltas and error accumulators. */
+int gl_set_weights(gl_net* net, const float* w_flat, const float* bias);
+/* Replaces LayerBuilder::getWeights (State/LayerBuilder.cpp:390-410) + Layer::getBiasWeight. */
+int gl_get_weights(gl_net* net, float* w_flat, float* bias);
+/* Total number of weights, sum of n_{l+1}*n_l. */
+int64_t gl_weight_count(const gl_net* net);
+
+/* Replaces LayerBuilder::buildInputLayers (State/LayerBuilder.cpp:101-189) and the
+ * DataInput::getTrainRow / getTrainExpectedRow reads of the loop (network.cpp:523,605): the rows
+ * are packed once.  Host pointers are copied (through pinned staging) before the call returns. */
+int gl_set_data(gl_net* net, const float* x, const float* y, int64_t rows);
+/* Same, for rows that already live in device memory; the buffers are borrowed, not copied, and
+ * must outlive the handle's use of them. */
+int gl_set_data_device(gl_net* net, const float* d_x, const float* d_y, int64_t rows);
+
+/* Replaces n iterations of the epoch loop of NNetwork::run with RUN_TRAIN
+ * (network.cpp:173-256): every row through SGDHelper (forward, metrics, confusion counts,
+ * backward, update).  out (may be NULL) receives the last epoch's figures. */
+int gl_train_epochs(gl_net* net, int32_t n_epochs, gl_metrics* out);
+/* Batched mode: one window step (forward, backward, update) over rows
+ * [first_row, first_row+rows) of the resident data.  Under data parallelism each rank passes its
+ * own shard of the global window and the gradient is all-reduced before the update. */
+int gl_train_window(gl_net* net, int64_t first_row, int32_t rows, gl_metrics* out);
+/* Batched mode: the same step with the window's rows in host memory (copied in by the call). */
+int gl_train_window_host(gl_net* net, const float* x, const float* y, int32_t rows, gl_metrics* out);
+
+/* Replaces NNetwork::run with RUN_TEST (network.cpp:109-112,428): forward only over rows
+ * [first_row, first_row+rows) of the resident data.  outputs ([rows][n_out], host) and argmax
+ * ([rows], host; -1 when no output exceeds 0, GMath::naiveVectorDecomp gmath.cpp:435-455) may
+ * each be NULL.  Metrics and confusion counts are accumulated exactly as the train pass does. */
+int gl_forward(gl_net* net, int64_t first_row, int64_t rows, float* outputs, int32_t* argmax, gl_metrics* out);
+/* Forward over rows in host memory (copied in by the call), results to host memory. */
+int gl_forward_host(gl_net* net, const float* x, const float* y, int64_t rows, float* outputs, int32_t* argmax,
+                    gl_metrics* out);
+
+/* Activations of every non-input layer for one resident row, concatenated n_1 | ... | n_{H+1}
+ * (what Node::getWeight holds after ForwardPass, network.cpp:517). */
+int gl_get_activations(gl_net* net, int64_t row, float* out);
+/* Reference mode: the k-th pending delta of every edge (Edge::prevDelta[k], State/edge.cpp:54-60;
+ * 0 where the history is shorter), flat like the weights. */
+int gl_get_pending_delta(gl_net* net, int32_t k, float* out);
+/* Confusion counts of the last epoch / forward call, [expected][predicted], n_out*n_out ints
+ * (CMatrix::addResult, GMath/cmatrix.cpp:57-98). */
+int gl_get_confusion(gl_net* net, int32_t* out);
+/* Epoch counter, NNetwork::getEpochs. */
+int gl_get_epochs(const gl_net* net);
+
+/* Replaces NNetwork::stop (network.cpp:99-102): async-signal-safe; the flag is looked at between
+ * epochs of gl_train_epochs. */
+void gl_stop(gl_net* net);
+
+/* ---- data parallelism (batched mode) --------------------------------------------------- */
+/* Contiguous shard of `rows` for `rank` of `world` (remainder rows go to the lowest ranks). */
+void gl_shard_range(int64_t rows, int32_t rank, int32_t world, int64_t* first, int64_t* count);
+/* Fills 128 bytes with an NCCL unique id (rank 0 calls it and hands the bytes to the others). */
+int gl_dp_unique_id(void* id128);
+/* Joins this handle to a data-parallel group; gradients, bias sums and metric sums of every
+ * gl_train_window call are then all-reduced (sum) over the group before the update. */
+int gl_dp_init(gl_net* net, int32_t rank, int32_t world, const void* id128);
+/* Position of this rank's shard inside the global window (used for the momentum weights) and
+ * the global window length. */
+int gl_dp_set_window(gl_net* net, int32_t global_rows, int32_t first_global_pos);
+
+/* ---- synthetic inputs (counter-based, identical on CPU and GPU) ------------------------- */
+/* Philox4x32-10 stream: element i of stream `stream` under `seed`.  dist 0: U[0,1) with 24 bits;
+ * dist 1: N(0,1) by Box-Muller on elements (2i, 2i+1); out = offset + scale*value.
+ * d_out is a device pointer. */
+int gl_synth_fill(float* d_out, int64_t n, uint64_t seed, uint32_t stream, int32_t dist, float scale, float offset,
+                  int32_t device);
+
+/* ---- raw device helpers for callers that keep data resident ---------------------------- */
+int gl_device_alloc(void** d_ptr, int64_t bytes, int32_t device);
+int gl_device_free(void* d_ptr, int32_t device);
+int gl_memcpy_h2d(void* d_dst, const void* h_src, int64_t bytes, int32_t device);
+int gl_memcpy_d2h(void* h_dst, const void* d_src, int64_t bytes, int32_t device);
+int gl_host_alloc_pinned(void** h_ptr, int64_t bytes);
+int gl_host_free_pinned(void* h_ptr);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GLADES_B200_H */

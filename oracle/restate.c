@@ -1,0 +1,657 @@
+/*
+ * TEST INFRASTRUCTURE ONLY -- the checker, never the thing shipped or measured as the product.
+ * Only tests/, the smoke check and the CPU-baseline leg of bench.py may load this library.
+ *
+ * CPU restatement, on dense row-major matrices, of the reference's deep feed-forward path:
+ *   NNetwork::run / SGDHelper / ForwardPass / BackPropagation   Networks/network.cpp:114-668
+ *   Node::getActivation / getDelta / applyDeltas                State/node.cpp:82-93,278-307
+ *   Edge history                                                State/edge.cpp:54-60,87-107
+ *   GMath::squash / activationErrDer / costs / naiveVectorDecomp GMath/gmath.cpp:22-101,182-353,435-455
+ *   CMatrix::addResult / updateResultParams / getters           GMath/cmatrix.cpp:57-266
+ *
+ * Reference mode (rs_epoch, rs_train_row, rs_forward_row) keeps the reference's operation order
+ * in fp32 -- product rounded, then sum rounded, i ascending; glibc expf/tanhf/logf -- and is
+ * checked bit-for-bit against the compiled reference (oracle/_ref) by tests/test_oracle_pin.py.
+ * Batched mode (rs_window_*) is the same arithmetic with the documented switches flipped
+ * (aligned windows, frozen weights, plain error sum, summed bias delta, optional softmax head);
+ * its sums are accumulated in double so that a comparison against it measures only the rounding
+ * of the kernel under test.
+ *
+ * Build: gcc -std=c11 -O2 -ffp-contract=off -fopenmp (see Makefile); no FMA contraction.
+ */
+#include <math.h>
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include "glades_b200.h"
+
+#define OUTLIER 0.046f /* GMath/gmath.h:35 */
+
+typedef struct rs_net {
+	gl_net_desc d;
+	int H;             /* hidden layers */
+	int64_t rows;
+	const float* x;    /* borrowed */
+	const float* y;
+	float* w[GL_MAX_WEIGHT_LAYERS];     /* W_l [n_{l+1}][n_l] */
+	float bias[GL_MAX_WEIGHT_LAYERS];   /* bias[l], l = 1..H (index 0 unused) */
+	float* hist[GL_MAX_WEIGHT_LAYERS];  /* pending deltas [mb][n_{l+1}*n_l] */
+	int hist_len;
+	float* act[GL_MAX_WEIGHT_LAYERS + 1]; /* a_l, l = 0..H+1 (one row) */
+	float* err[GL_MAX_WEIGHT_LAYERS + 1]; /* E_l accumulators */
+	int32_t* cm;       /* confusion [n_out][n_out] */
+	float tot_err, tot_acc;
+	int epochs;
+	int math_mode;     /* 0 glibc single precision (reference); 1 double then round (kernel) */
+} rs_net;
+
+static int g_math_mode = 0;
+void rs_set_math_mode(int m) { g_math_mode = m; }
+
+static float f_exp(float v) { return g_math_mode ? (float)exp((double)v) : expf(v); }
+static float f_tanh(float v) { return g_math_mode ? (float)tanh((double)v) : tanhf(v); }
+static float f_log(float v) { return g_math_mode ? (float)log((double)v) : logf(v); }
+
+/* GMath::squash, gmath.cpp:22-101 */
+float rs_squash(float z, int act, float p)
+{
+	switch (act)
+	{
+	case GL_ACT_TANH: return f_tanh(z);
+	case GL_ACT_TANHP:
+		if (z > 1.0f - p) return 1.0f;
+		if (z < p - 1.0f) return -1.0f;
+		return f_tanh(z);
+	case GL_ACT_SIGMOID: return 1.0f / (1.0f + f_exp(-z));
+	case GL_ACT_SIGMOIDP:
+		if (z < p) return 0.01f;
+		if (z > 1.0f - p) return 0.99f;
+		return 1.0f / (1.0f + f_exp(-z));
+	case GL_ACT_RELU: return z < OUTLIER ? 0.0f : z;
+	case GL_ACT_LEAKY: return z < OUTLIER ? p * z : z;
+	case GL_ACT_LINEAR: return p * z;
+	case GL_ACT_STEP: return z < p ? 0.0f : 1.0f;
+	}
+	return 0.0f;
+}
+
+/* GMath::activationErrDer, gmath.cpp:182-245 (argument is the node's OUTPUT value) */
+float rs_act_der(float a, int act, float p)
+{
+	switch (act)
+	{
+	case GL_ACT_TANH:
+	case GL_ACT_TANHP: return 1.0f - (a * a);
+	case GL_ACT_SIGMOID:
+	case GL_ACT_SIGMOIDP: return a * (1.0f - a);
+	case GL_ACT_RELU: return a > 0.0f ? 1.0f : 0.0f;
+	case GL_ACT_LEAKY: return a > 0.0f ? 1.0f : (p < 0 ? p : -p);
+	case GL_ACT_LINEAR: return p;
+	case GL_ACT_STEP: return 0.0f;
+	}
+	return 1.0f;
+}
+
+/* GMath::outputNodeCost, gmath.cpp:288-321 */
+float rs_cost(float e, float p, float n, int fx)
+{
+	float c = 0.0f;
+	switch (fx)
+	{
+	case GL_OUT_REGRESSION: { float t = e - p; c = t * t; c /= n; break; }
+	case GL_OUT_CLASSIFICATION: c = -((e * f_log(p)) + ((1.0f - e) * f_log(1.0f - p))); c /= n; break;
+	case GL_OUT_KL: c = f_log(e / p); c /= n; break;
+	}
+	return c;
+}
+
+/* GMath::costErrDer, gmath.cpp:323-353 */
+float rs_cost_der(float e, float p, int fx)
+{
+	switch (fx)
+	{
+	case GL_OUT_REGRESSION: return 2.0f * (p - e);
+	case GL_OUT_CLASSIFICATION: return (p - e) / ((1.0f - p) * p);
+	case GL_OUT_KL: return -(e / p);
+	}
+	return 1.0f;
+}
+
+/* GMath::naiveVectorDecomp, gmath.cpp:435-455: strict > starting from 0, first maximum wins,
+ * -1 when nothing exceeds 0. */
+static int rs_argmax(const float* v, int n, int stride)
+{
+	float mx = 0.0f;
+	int idx = -1;
+	for (int i = 0; i < n; ++i)
+		if (v[(size_t)i * stride] > mx)
+		{
+			mx = v[(size_t)i * stride];
+			idx = i;
+		}
+	return idx;
+}
+
+static size_t wcount(const rs_net* n, int l) { return (size_t)n->d.sizes[l + 1] * n->d.sizes[l]; }
+
+rs_net* rs_create(const gl_net_desc* d, const float* x, const float* y, int64_t rows)
+{
+	rs_net* n = (rs_net*)calloc(1, sizeof *n);
+	n->d = *d;
+	n->H = d->n_layers - 2;
+	n->rows = rows;
+	n->x = x;
+	n->y = y;
+	int mb = d->batch_size > 0 ? d->batch_size : 1;
+	for (int l = 0; l <= n->H; ++l)
+	{
+		n->w[l] = (float*)calloc(wcount(n, l), sizeof(float));
+		if (d->mode == GL_MODE_REFERENCE)
+			n->hist[l] = (float*)calloc(wcount(n, l) * mb, sizeof(float));
+	}
+	for (int l = 0; l <= n->H + 1; ++l)
+	{
+		n->act[l] = (float*)calloc(d->sizes[l], sizeof(float));
+		n->err[l] = (float*)calloc(d->sizes[l], sizeof(float));
+	}
+	int no = d->sizes[n->H + 1];
+	n->cm = (int32_t*)calloc((size_t)no * no, sizeof(int32_t));
+	return n;
+}
+
+void rs_destroy(rs_net* n)
+{
+	if (!n) return;
+	for (int l = 0; l <= n->H; ++l) { free(n->w[l]); free(n->hist[l]); }
+	for (int l = 0; l <= n->H + 1; ++l) { free(n->act[l]); free(n->err[l]); }
+	free(n->cm);
+	free(n);
+}
+
+void rs_set_data(rs_net* n, const float* x, const float* y, int64_t rows) { n->x = x; n->y = y; n->rows = rows; }
+
+void rs_set_weights(rs_net* n, const float* w, const float* bias)
+{
+	size_t k = 0;
+	for (int l = 0; l <= n->H; ++l)
+	{
+		memcpy(n->w[l], w + k, wcount(n, l) * sizeof(float));
+		k += wcount(n, l);
+		if (l >= 1) n->bias[l] = bias ? bias[l - 1] : 0.0f;
+	}
+	n->hist_len = 0;
+	for (int l = 0; l <= n->H + 1; ++l) memset(n->err[l], 0, n->d.sizes[l] * sizeof(float));
+}
+
+void rs_get_weights(const rs_net* n, float* w, float* bias)
+{
+	size_t k = 0;
+	for (int l = 0; l <= n->H; ++l)
+	{
+		memcpy(w + k, n->w[l], wcount(n, l) * sizeof(float));
+		k += wcount(n, l);
+		if (l >= 1 && bias) bias[l - 1] = n->bias[l];
+	}
+}
+
+void rs_get_pending_delta(const rs_net* n, int k, float* out)
+{
+	size_t j = 0;
+	for (int l = 0; l <= n->H; ++l)
+	{
+		size_t c = wcount(n, l);
+		for (size_t e = 0; e < c; ++e)
+			out[j++] = (k < n->hist_len) ? n->hist[l][(size_t)k * c + e] : 0.0f;
+	}
+}
+
+/* ForwardPass for one row, network.cpp:457-575 (metrics excluded). */
+static void forward_row(rs_net* n, int64_t r)
+{
+	const gl_net_desc* d = &n->d;
+	memcpy(n->act[0], n->x + (size_t)r * d->sizes[0], d->sizes[0] * sizeof(float));
+	for (int l = 0; l <= n->H; ++l)
+	{
+		const int ni = d->sizes[l], no = d->sizes[l + 1];
+		const float* W = n->w[l];
+		const float* a = n->act[l];
+		for (int o = 0; o < no; ++o)
+		{
+			float z = 0.0f;
+			for (int i = 0; i < ni; ++i)
+			{
+				float prod = W[(size_t)o * ni + i] * a[i]; /* Edge::activation, a float member */
+				z = z + prod;                               /* Node::getActivation, node.cpp:82-93 */
+			}
+			if (l >= 1) z = z + n->bias[l];               /* network.cpp:501-502 */
+			n->act[l + 1][o] = rs_squash(z, d->activation[l], d->act_param[l]);
+		}
+	}
+}
+
+/* Output-layer metrics of one row, network.cpp:519-547, and CMatrix::addResult. */
+static void metrics_row(rs_net* n, int64_t r)
+{
+	const gl_net_desc* d = &n->d;
+	const int no = d->sizes[n->H + 1];
+	const float* p = n->act[n->H + 1];
+	const float* e = n->y + (size_t)r * no;
+	const float dataSize = (float)(n->rows * no);
+	for (int o = 0; o < no; ++o)
+	{
+		float cost = rs_cost(e[o], p[o], dataSize, d->output_type);
+		n->tot_err += cost;
+		float pe = p[o] - e[o];
+		if (pe < 0.0f) pe = -pe;
+		if (pe > 1.0f) pe = 1.0f;
+		float acc = (1.0f - pe) * 100.0f;
+		if (acc < 0.0f) acc = 0.0f;
+		n->tot_acc += acc;
+	}
+	if (d->output_type != GL_OUT_REGRESSION)
+	{
+		int ie = rs_argmax(e, no, 1), ip = rs_argmax(p, no, 1);
+		if (ie >= 0 && ip >= 0) n->cm[ie * no + ip] += 1;
+	}
+}
+
+/* BackPropagation for one row, network.cpp:577-668: layer from the top, input node OUTER,
+ * output node INNER. */
+static void backward_row(rs_net* n, int64_t r)
+{
+	const gl_net_desc* d = &n->d;
+	const int mb = d->batch_size;
+	const int apply = (r % mb) == 0;                     /* network.cpp:647 */
+	const float* e = n->y + (size_t)r * d->sizes[n->H + 1];
+	const int k = n->hist_len;                           /* slot this row's deltas go to */
+	for (int L = n->H + 1; L >= 1; --L)
+	{
+		const int l = L - 1;
+		const int ni = d->sizes[l], no = d->sizes[L];
+		float* W = n->w[l];
+		float* hist = n->hist[l];
+		const size_t cnt = (size_t)ni * no;
+		const float lr = d->lr[l], m = d->momentum[l], wd1 = d->wd1[l], wd2 = d->wd2[l];
+		float* EL = n->err[L];
+		float* El = n->err[l];
+		for (int i = 0; i < ni; ++i)
+		{
+			const float ai = n->act[l][i];
+			for (int o = 0; o < no; ++o)
+			{
+				float der = 1.0f;
+				if (L == n->H + 1)
+				{
+					/* clearErrDer + adjustErrDer: 0 + cost' */
+					EL[o] = 0.0f + rs_cost_der(e[o], n->act[L][o], d->output_type);
+				}
+				else
+					der = rs_act_der(n->act[L][o], d->activation[l], 0.01f); /* network.cpp:618 */
+				float dd = EL[o] * der;
+				if (i == ni - 1) EL[o] = 0.0f;
+				float base = lr * dd;
+				/* Node::getDelta, node.cpp:278-292 */
+				size_t eidx = (size_t)o * ni + i;
+				float last = (k > 0) ? hist[(size_t)(k - 1) * cnt + eidx] : 0.0f;
+				float absa = ai < 0.0f ? -ai : ai;
+				float delta = (((base * ai) + (m * last)) + (wd1 * lr * absa)) + (wd2 * lr * ai);
+				hist[(size_t)k * cnt + eidx] = delta;
+				if (apply)
+				{
+					/* Node::applyDeltas, node.cpp:294-307 */
+					float s = 0.0f;
+					for (int t = 0; t < mb; ++t)
+						s += (t <= k) ? hist[(size_t)t * cnt + eidx] : 0.0f;
+					s /= (float)mb;
+					W[eidx] = W[eidx] - s;
+				}
+				if (l >= 1) n->bias[l] = n->bias[l] - base;      /* network.cpp:654-656 */
+				if (l >= 1)
+				{
+					float t = El[i] + (dd * W[eidx]);              /* network.cpp:660-661 */
+					El[i] += t;                                    /* Node::adjustErrDer */
+				}
+			}
+		}
+	}
+	n->hist_len = apply ? 0 : k + 1;
+}
+
+static void finish_class_metrics(const rs_net* n, gl_metrics* m)
+{
+	/* CMatrix::updateResultParams + getters, cmatrix.cpp:100-266 */
+	const int c = n->d.sizes[n->H + 1];
+	float acc = 0, prec = 0, rec = 0, spec = 0, f1 = 0;
+	for (int k = 0; k < c; ++k)
+	{
+		int tp = n->cm[k * c + k], tn = 0, fp = 0, fn = 0;
+		for (int j = 0; j < c; ++j)
+		{
+			if (j != k) { tn += n->cm[j * c + j]; fp += n->cm[j * c + k]; fn += n->cm[k * c + j]; }
+		}
+		float truth = (float)(tp + tn), untruth = (float)(fp + fn);
+		acc += truth / (truth + untruth);
+		float p = ((float)tp) / ((float)(tp + fp));
+		float r = ((float)tp) / ((float)(tp + fn));
+		prec += p;
+		rec += r;
+		spec += ((float)tn) / ((float)(tn + fp));
+		f1 += (2.0f * r * p) / (r + p);
+	}
+	m->class_accuracy = (acc / (float)c) * 100.0f;
+	m->class_precision = (prec / (float)c) * 100.0f;
+	m->class_recall = (rec / (float)c) * 100.0f;
+	m->class_specificity = (spec / (float)c) * 100.0f;
+	m->class_f1 = (f1 / (float)c) * 100.0f;
+}
+
+static void fill_metrics(const rs_net* n, gl_metrics* m)
+{
+	if (!m) return;
+	memset(m, 0, sizeof *m);
+	const int no = n->d.sizes[n->H + 1];
+	m->total_error = n->tot_err;
+	m->total_accuracy = n->tot_acc / (((float)n->rows) * ((float)no));  /* network.cpp:194-195 */
+	m->epochs = n->epochs;
+	m->rows = n->rows;
+	if (n->d.output_type != GL_OUT_REGRESSION) finish_class_metrics(n, m);
+	size_t k = 0;
+	for (int l = 0; l <= n->H; ++l)
+		for (size_t e = 0; e < wcount(n, l); ++e, ++k)
+			if (!isfinite(n->w[l][e])) m->nonfinite = 1;
+}
+
+/* One epoch of NNetwork::run (network.cpp:179-195), reference mode.  run_type 0 train, 1 test. */
+int rs_epoch(rs_net* n, int run_type, gl_metrics* m, int32_t* confusion, float* outputs)
+{
+	const int no = n->d.sizes[n->H + 1];
+	n->tot_err = 0.0f;
+	n->tot_acc = 0.0f;
+	memset(n->cm, 0, (size_t)no * no * sizeof(int32_t));
+	for (int64_t r = 0; r < n->rows; ++r)
+	{
+		forward_row(n, r);
+		metrics_row(n, r);
+		if (outputs) memcpy(outputs + (size_t)r * no, n->act[n->H + 1], no * sizeof(float));
+		if (run_type == 0) backward_row(n, r);
+	}
+	if (run_type == 0) n->epochs += 1;
+	fill_metrics(n, m);
+	if (confusion) memcpy(confusion, n->cm, (size_t)no * no * sizeof(int32_t));
+	return 0;
+}
+
+int rs_forward_row(rs_net* n, int64_t row, float* acts)
+{
+	forward_row(n, row);
+	size_t k = 0;
+	for (int l = 1; l <= n->H + 1; ++l)
+	{
+		memcpy(acts + k, n->act[l], n->d.sizes[l] * sizeof(float));
+		k += n->d.sizes[l];
+	}
+	return 0;
+}
+
+int rs_train_row(rs_net* n, int64_t row)
+{
+	forward_row(n, row);
+	backward_row(n, row);
+	return 0;
+}
+
+/* ------------------------------------------------------------------------------------------
+ * Batched mode.  One window = rows [first, first+cnt) which sit at positions
+ * [first_pos, first_pos+cnt) of a global window of global_rows rows.  rs_window_grad computes this
+ * shard's contribution
+ *     grad = [ G_0 | ... | G_H | bias sums (H) | cost sum | accuracy sum ]   (doubles)
+ * and rs_window_apply applies a (summed) contribution.  With one shard, grad then apply is the
+ * whole step.  Softmax head: activation GL_ACT_SOFTMAX on the last weight layer.
+ * ------------------------------------------------------------------------------------------ */
+int64_t rs_grad_len(const rs_net* n)
+{
+	int64_t k = 0;
+	for (int l = 0; l <= n->H; ++l) k += (int64_t)wcount(n, l);
+	return k + n->H + 2;
+}
+
+/* Forward of a block of rows in batched arithmetic (double accumulation, fp32 storage).
+ * acts[l] : [cnt][n_l] for l = 0..H+1 (caller-allocated). */
+static void forward_block(const rs_net* n, int64_t first, int cnt, float** acts)
+{
+	const gl_net_desc* d = &n->d;
+	memcpy(acts[0], n->x + (size_t)first * d->sizes[0], (size_t)cnt * d->sizes[0] * sizeof(float));
+	for (int l = 0; l <= n->H; ++l)
+	{
+		const int ni = d->sizes[l], no = d->sizes[l + 1];
+		const float* W = n->w[l];
+#pragma omp parallel for schedule(static)
+		for (int j = 0; j < cnt; ++j)
+		{
+			const float* a = acts[l] + (size_t)j * ni;
+			float* out = acts[l + 1] + (size_t)j * no;
+			if (d->activation[l] == GL_ACT_SOFTMAX)
+			{
+				double* z = (double*)malloc(no * sizeof(double));
+				double mx = -INFINITY;
+				for (int o = 0; o < no; ++o)
+				{
+					double s = 0.0;
+					for (int i = 0; i < ni; ++i) s += (double)W[(size_t)o * ni + i] * (double)a[i];
+					if (l >= 1) s += (double)n->bias[l];
+					z[o] = (double)(float)s;
+					if (z[o] > mx) mx = z[o];
+				}
+				double den = 0.0;
+				for (int o = 0; o < no; ++o) den += exp(z[o] - mx);
+				for (int o = 0; o < no; ++o) out[o] = (float)(exp(z[o] - mx) / den);
+				free(z);
+			}
+			else
+				for (int o = 0; o < no; ++o)
+				{
+					double s = 0.0;
+					for (int i = 0; i < ni; ++i) s += (double)W[(size_t)o * ni + i] * (double)a[i];
+					if (l >= 1) s += (double)n->bias[l];
+					out[o] = rs_squash((float)s, d->activation[l], d->act_param[l]);
+				}
+		}
+	}
+}
+
+/* Batched forward for inference checks: outputs [cnt][n_out], argmax [cnt] (either may be NULL);
+ * also the pre-activation-free per-layer activations of the LAST row into acts_last if given. */
+int rs_forward_block(rs_net* n, int64_t first, int cnt, float* outputs, int32_t* argmax)
+{
+	float* acts[GL_MAX_WEIGHT_LAYERS + 1];
+	for (int l = 0; l <= n->H + 1; ++l) acts[l] = (float*)malloc((size_t)cnt * n->d.sizes[l] * sizeof(float));
+	forward_block(n, first, cnt, acts);
+	const int no = n->d.sizes[n->H + 1];
+	if (outputs) memcpy(outputs, acts[n->H + 1], (size_t)cnt * no * sizeof(float));
+	if (argmax)
+		for (int j = 0; j < cnt; ++j) argmax[j] = rs_argmax(acts[n->H + 1] + (size_t)j * no, no, 1);
+	for (int l = 0; l <= n->H + 1; ++l) free(acts[l]);
+	return 0;
+}
+
+int rs_window_grad(rs_net* n, int64_t first, int cnt, int global_rows, int first_pos, double* grad,
+                   int32_t* confusion_add, int64_t metric_rows)
+{
+	const gl_net_desc* d = &n->d;
+	const int H = n->H;
+	const int no_out = d->sizes[H + 1];
+	float* acts[GL_MAX_WEIGHT_LAYERS + 1];
+	float* D[GL_MAX_WEIGHT_LAYERS + 1];
+	for (int l = 0; l <= H + 1; ++l)
+	{
+		acts[l] = (float*)malloc((size_t)cnt * d->sizes[l] * sizeof(float));
+		D[l] = (float*)calloc((size_t)cnt * d->sizes[l], sizeof(float));
+	}
+	forward_block(n, first, cnt, acts);
+	memset(grad, 0, rs_grad_len(n) * sizeof(double));
+	int64_t off[GL_MAX_WEIGHT_LAYERS + 1];
+	off[0] = 0;
+	for (int l = 0; l <= H; ++l) off[l + 1] = off[l] + (int64_t)wcount(n, l);
+	double* gb = grad + off[H + 1];      /* H bias sums: gb[l-1] for l = 1..H */
+	double* gm = gb + H;                  /* cost sum, accuracy sum */
+	const int softmax = d->activation[H] == GL_ACT_SOFTMAX;
+	const float dataSize = (float)(metric_rows * no_out);
+
+	/* metrics + output delta */
+	for (int j = 0; j < cnt; ++j)
+	{
+		const float* p = acts[H + 1] + (size_t)j * no_out;
+		const float* e = n->y + (size_t)(first + j) * no_out;
+		for (int o = 0; o < no_out; ++o)
+		{
+			float cost;
+			if (softmax)
+				cost = (e[o] != 0.0f) ? (-(e[o] * (float)log((double)p[o]))) / dataSize : 0.0f;
+			else
+				cost = rs_cost(e[o], p[o], dataSize, d->output_type);
+			gm[0] += (double)cost;
+			float pe = p[o] - e[o];
+			if (pe < 0.0f) pe = -pe;
+			if (pe > 1.0f) pe = 1.0f;
+			float acc = (1.0f - pe) * 100.0f;
+			if (acc < 0.0f) acc = 0.0f;
+			gm[1] += (double)acc;
+			D[H + 1][(size_t)j * no_out + o] = softmax ? (p[o] - e[o]) : rs_cost_der(e[o], p[o], d->output_type);
+		}
+		if (confusion_add && d->output_type != GL_OUT_REGRESSION)
+		{
+			int ie = rs_argmax(e, no_out, 1), ip = rs_argmax(p, no_out, 1);
+			if (ie >= 0 && ip >= 0) confusion_add[ie * no_out + ip] += 1;
+		}
+	}
+	/* layers from the top */
+	for (int L = H + 1; L >= 1; --L)
+	{
+		const int l = L - 1;
+		const int ni = d->sizes[l], no = d->sizes[L];
+		const float lr = d->lr[l], wd1 = d->wd1[l], wd2 = d->wd2[l];
+		const double m = (double)d->momentum[l];
+		const float* W = n->w[l];
+		/* momentum weights c_j = sum_{t=0}^{mb-1-pos} m^t, closed form of the reference's
+		 * intra-window history (node.cpp:278-292) */
+		double* c = (double*)malloc(cnt * sizeof(double));
+		for (int j = 0; j < cnt; ++j)
+		{
+			int terms = global_rows - (first_pos + j);
+			double s = 0.0, pw = 1.0;
+			for (int t = 0; t < terms; ++t) { s += pw; pw *= m; }
+			c[j] = s;
+		}
+		/* propagate the error first (plain sum), needed only for l >= 1 */
+		if (l >= 1)
+		{
+#pragma omp parallel for schedule(static)
+			for (int j = 0; j < cnt; ++j)
+				for (int i = 0; i < ni; ++i)
+				{
+					double s = 0.0;
+					for (int o = 0; o < no; ++o)
+						s += (double)D[L][(size_t)j * no + o] * (double)W[(size_t)o * ni + i];
+					/* D_l = E_l * act'(A_l), derivative of the activation that produced layer l */
+					float der = rs_act_der(acts[l][(size_t)j * ni + i], d->activation[l - 1], 0.01f);
+					D[l][(size_t)j * ni + i] = (float)s * der;
+				}
+		}
+		/* weight gradient G_l = lr * D_L^T diag(c) A_l + decay terms */
+		double* G = grad + off[l];
+#pragma omp parallel for schedule(static)
+		for (int o = 0; o < no; ++o)
+			for (int i = 0; i < ni; ++i)
+			{
+				double s = 0.0;
+				for (int j = 0; j < cnt; ++j)
+				{
+					double a = (double)acts[l][(size_t)j * ni + i];
+					double g = (double)lr * (double)D[L][(size_t)j * no + o] * a +
+					           (double)wd1 * (double)lr * fabs(a) + (double)wd2 * (double)lr * a;
+					s += c[j] * g;
+				}
+				G[(size_t)o * ni + i] = s;
+			}
+		if (l >= 1)
+		{
+			double s = 0.0;
+			for (int j = 0; j < cnt; ++j)
+				for (int o = 0; o < no; ++o) s += (double)lr * (double)D[L][(size_t)j * no + o];
+			gb[l - 1] = s;
+		}
+		free(c);
+	}
+	for (int l = 0; l <= H + 1; ++l) { free(acts[l]); free(D[l]); }
+	return 0;
+}
+
+int rs_window_apply(rs_net* n, const double* grad, int global_rows)
+{
+	const int H = n->H;
+	int64_t k = 0;
+	for (int l = 0; l <= H; ++l)
+	{
+		size_t c = wcount(n, l);
+		for (size_t e = 0; e < c; ++e, ++k)
+			n->w[l][e] = n->w[l][e] - (float)(grad[k] / (double)global_rows);
+	}
+	for (int l = 1; l <= H; ++l)
+	{
+		double s = grad[k + l - 1];
+		if (n->d.bias_rule == GL_BIAS_REFERENCE)
+			n->bias[l] = n->bias[l] - (float)((double)n->d.sizes[l] * s);
+		else
+			n->bias[l] = n->bias[l] - (float)(s / (double)global_rows);
+	}
+	return 0;
+}
+
+/* ------------------------------------------------------------------------------------------
+ * Counter-based synthetic inputs: Philox4x32-10 (Salmon et al., SC'11), key = (seed lo, seed hi),
+ * counter = (index lo, index hi, stream, 0); element i uses word 0 of block i.
+ * dist 0: U = (u32 >> 8) * 2^-24.  dist 1: N(0,1) by Box-Muller on the uniforms of elements
+ * 2*(i/2) and 2*(i/2)+1 (cos for even i, sin for odd i), with U1 nudged away from 0.
+ * ------------------------------------------------------------------------------------------ */
+static inline void philox_round(uint32_t* c, uint32_t* k)
+{
+	const uint64_t p0 = (uint64_t)0xD2511F53u * c[0];
+	const uint64_t p1 = (uint64_t)0xCD9E8D57u * c[2];
+	uint32_t n0 = (uint32_t)(p1 >> 32) ^ c[1] ^ k[0];
+	uint32_t n1 = (uint32_t)p1;
+	uint32_t n2 = (uint32_t)(p0 >> 32) ^ c[3] ^ k[1];
+	uint32_t n3 = (uint32_t)p0;
+	c[0] = n0; c[1] = n1; c[2] = n2; c[3] = n3;
+	k[0] += 0x9E3779B9u;
+	k[1] += 0xBB67AE85u;
+}
+
+uint32_t rs_philox_u32(uint64_t seed, uint32_t stream, uint64_t index)
+{
+	uint32_t c[4] = { (uint32_t)index, (uint32_t)(index >> 32), stream, 0u };
+	uint32_t k[2] = { (uint32_t)seed, (uint32_t)(seed >> 32) };
+	for (int r = 0; r < 10; ++r) philox_round(c, k);
+	return c[0];
+}
+
+void rs_synth_fill(float* out, int64_t n, uint64_t seed, uint32_t stream, int dist, float scale, float offset)
+{
+#pragma omp parallel for schedule(static)
+	for (int64_t i = 0; i < n; ++i)
+	{
+		float v;
+		if (dist == 0)
+			v = (float)(rs_philox_u32(seed, stream, (uint64_t)i) >> 8) * (1.0f / 16777216.0f);
+		else
+		{
+			uint64_t b = (uint64_t)i & ~(uint64_t)1;
+			float u1 = ((float)(rs_philox_u32(seed, stream, b) >> 8) + 0.5f) * (1.0f / 16777216.0f);
+			float u2 = (float)(rs_philox_u32(seed, stream, b + 1) >> 8) * (1.0f / 16777216.0f);
+			double rad = sqrt(-2.0 * log((double)u1));
+			double ang = 6.283185307179586 * (double)u2;
+			v = (float)(rad * ((i & 1) ? sin(ang) : cos(ang)));
+		}
+		out[i] = offset + scale * v;
+	}
+}
