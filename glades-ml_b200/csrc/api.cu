@@ -1,0 +1,1060 @@
+// extern "C" layer of the B200-native glades feed-forward path (declared in include/glades_b200.h).
+// It owns the device memory of one network, packs rows and weights into contiguous row-major
+// device matrices, and drives the kernels of ref_mode.cu (reference arithmetic), batched.cu /
+// gemm_tcgen05.cu (batched arithmetic) and synth.cu.  There is no CPU compute path: every compute
+// entry point fails with GL_ERR_NO_DEVICE when no sm_100 device is present.
+#include <dlfcn.h>
+#include <math.h>
+#include <stdarg.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include <string>
+#include <vector>
+
+#include "internal.h"
+#include "tc_gemm.h"
+
+using namespace glb;
+
+// ------------------------------------------------------------------------------------------------
+static thread_local std::string g_err;
+
+static int fail(int code, const char* fmt, ...)
+{
+	char buf[512];
+	va_list ap;
+	va_start(ap, fmt);
+	vsnprintf(buf, sizeof buf, fmt, ap);
+	va_end(ap);
+	g_err = buf;
+	return code;
+}
+
+#define CU(call)                                                                                     \
+	do                                                                                               \
+	{                                                                                                \
+		cudaError_t e__ = (call);                                                                    \
+		if (e__ != cudaSuccess)                                                                      \
+			return fail(GL_ERR_CUDA, "%s failed: %s (%s:%d)", #call, cudaGetErrorString(e__), __FILE__, __LINE__); \
+	} while (0)
+
+extern "C" const char* gl_last_error(void) { return g_err.c_str(); }
+
+extern "C" int gl_device_count(void)
+{
+	int n = 0;
+	if (cudaGetDeviceCount(&n) != cudaSuccess)
+	{
+		cudaGetLastError();
+		return 0;
+	}
+	int ok = 0;
+	for (int i = 0; i < n; ++i)
+	{
+		int major = 0;
+		if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, i) == cudaSuccess && major == 10) ++ok;
+	}
+	return ok;
+}
+
+// ---- NCCL, bound at run time so that single-GPU users need no NCCL at all ----------------------
+namespace {
+typedef struct { char internal[128]; } nccl_uid;
+typedef void* nccl_comm;
+struct NcclApi
+{
+	void* so = nullptr;
+	int (*GetUniqueId)(nccl_uid*) = nullptr;
+	int (*CommInitRank)(nccl_comm*, int, nccl_uid, int) = nullptr;
+	int (*CommDestroy)(nccl_comm) = nullptr;
+	int (*AllReduce)(const void*, void*, size_t, int, int, nccl_comm, cudaStream_t) = nullptr;
+	int (*GroupStart)() = nullptr;
+	int (*GroupEnd)() = nullptr;
+	const char* (*GetErrorString)(int) = nullptr;
+};
+NcclApi g_nccl;
+enum { NCCL_INT32 = 2, NCCL_FLOAT32 = 7, NCCL_FLOAT64 = 8, NCCL_SUM = 0 };
+
+int nccl_load()
+{
+	if (g_nccl.so) return 0;
+	const char* names[] = {"libnccl.so.2", "libnccl.so"};
+	void* so = nullptr;
+	for (const char* nm : names)
+	{
+		so = dlopen(nm, RTLD_NOW | RTLD_GLOBAL);
+		if (so) break;
+	}
+	if (!so) return fail(GL_ERR_COMM, "cannot load libnccl.so.2: %s", dlerror());
+	g_nccl.GetUniqueId = (int (*)(nccl_uid*))dlsym(so, "ncclGetUniqueId");
+	g_nccl.CommInitRank = (int (*)(nccl_comm*, int, nccl_uid, int))dlsym(so, "ncclCommInitRank");
+	g_nccl.CommDestroy = (int (*)(nccl_comm))dlsym(so, "ncclCommDestroy");
+	g_nccl.AllReduce =
+	    (int (*)(const void*, void*, size_t, int, int, nccl_comm, cudaStream_t))dlsym(so, "ncclAllReduce");
+	g_nccl.GroupStart = (int (*)())dlsym(so, "ncclGroupStart");
+	g_nccl.GroupEnd = (int (*)())dlsym(so, "ncclGroupEnd");
+	g_nccl.GetErrorString = (const char* (*)(int))dlsym(so, "ncclGetErrorString");
+	if (!g_nccl.GetUniqueId || !g_nccl.CommInitRank || !g_nccl.AllReduce || !g_nccl.GroupStart || !g_nccl.GroupEnd)
+		return fail(GL_ERR_COMM, "libnccl lacks a required symbol");
+	g_nccl.so = so;
+	return 0;
+}
+}  // namespace
+
+#define NC(call)                                                                                 \
+	do                                                                                           \
+	{                                                                                            \
+		int r__ = (call);                                                                        \
+		if (r__ != 0)                                                                            \
+			return fail(GL_ERR_COMM, "%s failed: %s", #call,                                     \
+			            g_nccl.GetErrorString ? g_nccl.GetErrorString(r__) : "nccl error");     \
+	} while (0)
+
+// ------------------------------------------------------------------------------------------------
+struct gl_net
+{
+	gl_net_desc d;
+	int H = 0;
+	int64_t nw = 0;
+	int64_t woff[GL_MAX_WEIGHT_LAYERS + 1];
+	int n_out = 0;
+	int total_nodes = 0;
+	int softmax = 0;
+	cudaStream_t stream = nullptr;
+	cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+
+	float* dW = nullptr;      // flat weights
+	float* dBias = nullptr;   // [GL_MAX_WEIGHT_LAYERS]
+	float* dG = nullptr;      // flat gradient | per-layer bias sums (GL_MAX_WEIGHT_LAYERS floats)
+	float* dBscale = nullptr; // [GL_MAX_WEIGHT_LAYERS]
+	int* dFlags = nullptr;
+	double* dSums = nullptr;  // [2] cost, accuracy (batched)
+	float* dSumsF = nullptr;  // reference mode: [n_epochs][2]
+	int sumsFCap = 0;
+	int* dConf = nullptr;     // [n_out][n_out]
+	// reference mode
+	float* dHist = nullptr;
+	int* dHistLen = nullptr;
+	float* dScratch = nullptr;
+	// data
+	const float* dX = nullptr;
+	const float* dY = nullptr;
+	float* ownX = nullptr;
+	float* ownY = nullptr;
+	int64_t rows = 0;
+	// batched work buffers
+	int64_t capRows = 0;
+	float* dA[GL_MAX_WEIGHT_LAYERS + 2] = {};
+	float* dD[GL_MAX_WEIGHT_LAYERS + 2] = {};
+	float* dC[GL_MAX_WEIGHT_LAYERS] = {};  // momentum weights per layer (NULL when momentum is 0)
+	float* dColterm = nullptr;
+	int cRows = -1, cGlobal = -1, cFirst = -1;
+	int* dArgmax = nullptr;
+	// host-window staging
+	float* dXwin = nullptr;
+	float* dYwin = nullptr;
+	int64_t winCap = 0;
+	float* hPinned = nullptr;
+	size_t pinnedBytes = 0;
+	// tensor-core path state (operand splits, transposes); opaque to this file
+	TcState* tc = nullptr;
+
+	int epochs = 0;
+	volatile int stop = 0;
+	int64_t launches = 0;
+	// data parallel
+	int rank = 0, world = 1;
+	nccl_comm comm = nullptr;
+	int globalRows = 0, firstPos = 0;
+};
+
+static NetView make_view(const gl_net* n)
+{
+	NetView v;
+	memset(&v, 0, sizeof v);
+	v.H = n->H;
+	for (int l = 0; l <= n->H + 1; ++l) v.sizes[l] = n->d.sizes[l];
+	for (int l = 0; l <= n->H; ++l)
+	{
+		v.lr[l] = n->d.lr[l];
+		v.mom[l] = n->d.momentum[l];
+		v.wd1[l] = n->d.wd1[l];
+		v.wd2[l] = n->d.wd2[l];
+		v.act[l] = n->d.activation[l];
+		v.par[l] = n->d.act_param[l];
+		v.W[l] = n->dW + n->woff[l];
+	}
+	v.out_type = n->d.output_type;
+	v.mb = n->d.batch_size;
+	v.bias = n->dBias;
+	return v;
+}
+
+static int use_device(const gl_net* n)
+{
+	CU(cudaSetDevice(n->d.device));
+	return 0;
+}
+
+extern "C" int gl_create(const gl_net_desc* d, gl_net** out)
+{
+	if (!d || !out) return fail(GL_ERR_INVALID, "gl_create: null argument");
+	*out = nullptr;
+	const int H = d->n_layers - 2;
+	if (H < 1 || H + 1 > GL_MAX_WEIGHT_LAYERS) return fail(GL_ERR_INVALID, "gl_create: n_layers %d out of range", d->n_layers);
+	for (int l = 0; l <= H + 1; ++l)
+		if (d->sizes[l] < 1) return fail(GL_ERR_INVALID, "gl_create: layer %d has size %d", l, d->sizes[l]);
+	if (d->batch_size < 1) return fail(GL_ERR_INVALID, "gl_create: batch_size must be >= 1");
+	if (d->mode != GL_MODE_REFERENCE && d->mode != GL_MODE_BATCHED) return fail(GL_ERR_INVALID, "gl_create: bad mode");
+	for (int l = 0; l <= H; ++l)
+	{
+		if (d->p_dropout[l] != 0.0f) return fail(GL_ERR_INVALID, "gl_create: dropout is not supported on this path");
+		const int a = d->activation[l];
+		if (a < 0 || a > GL_ACT_SOFTMAX) return fail(GL_ERR_INVALID, "gl_create: bad activation id %d", a);
+		if (a == GL_ACT_SOFTMAX && (l != H || d->mode != GL_MODE_BATCHED))
+			return fail(GL_ERR_INVALID, "gl_create: softmax is only legal on the last layer of a batched-mode net");
+	}
+	if (gl_device_count() < 1) return fail(GL_ERR_NO_DEVICE, "no sm_100 CUDA device: this library has no CPU path");
+	int major = 0;
+	if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, d->device) != cudaSuccess || major != 10)
+		return fail(GL_ERR_NO_DEVICE, "device %d is not an sm_100 device", d->device);
+
+	gl_net* n = new gl_net();
+	n->d = *d;
+	n->H = H;
+	n->n_out = d->sizes[H + 1];
+	n->softmax = d->activation[H] == GL_ACT_SOFTMAX;
+	n->woff[0] = 0;
+	for (int l = 0; l <= H; ++l) n->woff[l + 1] = n->woff[l] + (int64_t)d->sizes[l] * d->sizes[l + 1];
+	n->nw = n->woff[H + 1];
+	for (int l = 0; l <= H + 1; ++l) n->total_nodes += d->sizes[l];
+	n->globalRows = 0;
+
+	CU(cudaSetDevice(d->device));
+	CU(cudaStreamCreateWithFlags(&n->stream, cudaStreamNonBlocking));
+	CU(cudaEventCreate(&n->ev0));
+	CU(cudaEventCreate(&n->ev1));
+	CU(cudaMalloc(&n->dW, (n->nw + 4) * sizeof(float)));
+	CU(cudaMemset(n->dW, 0, (n->nw + 4) * sizeof(float)));
+	CU(cudaMalloc(&n->dBias, GL_MAX_WEIGHT_LAYERS * sizeof(float)));
+	CU(cudaMemset(n->dBias, 0, GL_MAX_WEIGHT_LAYERS * sizeof(float)));
+	CU(cudaMalloc(&n->dBscale, GL_MAX_WEIGHT_LAYERS * sizeof(float)));
+	CU(cudaMalloc(&n->dFlags, 4 * sizeof(int)));
+	CU(cudaMemset(n->dFlags, 0, 4 * sizeof(int)));
+	CU(cudaMalloc(&n->dSums, 2 * sizeof(double)));
+	CU(cudaMemset(n->dSums, 0, 2 * sizeof(double)));
+	CU(cudaMalloc(&n->dConf, (size_t)n->n_out * n->n_out * sizeof(int)));
+	CU(cudaMemset(n->dConf, 0, (size_t)n->n_out * n->n_out * sizeof(int)));
+	if (d->mode == GL_MODE_REFERENCE)
+	{
+		CU(cudaMalloc(&n->dHist, (size_t)n->nw * d->batch_size * sizeof(float)));
+		CU(cudaMemset(n->dHist, 0, (size_t)n->nw * d->batch_size * sizeof(float)));
+		CU(cudaMalloc(&n->dHistLen, sizeof(int)));
+		CU(cudaMemset(n->dHistLen, 0, sizeof(int)));
+	}
+	else
+	{
+		CU(cudaMalloc(&n->dG, (n->nw + GL_MAX_WEIGHT_LAYERS + 4) * sizeof(float)));
+		CU(cudaMemset(n->dG, 0, (n->nw + GL_MAX_WEIGHT_LAYERS + 4) * sizeof(float)));
+		int maxn = 1;
+		for (int l = 0; l <= H + 1; ++l) maxn = d->sizes[l] > maxn ? d->sizes[l] : maxn;
+		CU(cudaMalloc(&n->dColterm, maxn * sizeof(float)));
+	}
+	*out = n;
+	return GL_OK;
+}
+
+static void free_work(gl_net* n)
+{
+	for (int l = 0; l <= GL_MAX_WEIGHT_LAYERS + 1; ++l)
+	{
+		if (n->dA[l]) cudaFree(n->dA[l]);
+		if (n->dD[l]) cudaFree(n->dD[l]);
+		n->dA[l] = n->dD[l] = nullptr;
+	}
+	for (int l = 0; l < GL_MAX_WEIGHT_LAYERS; ++l)
+	{
+		if (n->dC[l]) cudaFree(n->dC[l]);
+		n->dC[l] = nullptr;
+	}
+	if (n->dArgmax) cudaFree(n->dArgmax);
+	n->dArgmax = nullptr;
+	n->capRows = 0;
+	n->cRows = -1;
+}
+
+extern "C" int gl_destroy(gl_net* n)
+{
+	if (!n) return GL_OK;
+	cudaSetDevice(n->d.device);
+	if (n->stream) cudaStreamSynchronize(n->stream);
+	if (n->comm && g_nccl.CommDestroy) g_nccl.CommDestroy(n->comm);
+	tc_destroy(n->tc);
+	free_work(n);
+	cudaFree(n->dW); cudaFree(n->dBias); cudaFree(n->dG); cudaFree(n->dBscale); cudaFree(n->dFlags);
+	cudaFree(n->dSums); cudaFree(n->dSumsF); cudaFree(n->dConf); cudaFree(n->dHist); cudaFree(n->dHistLen);
+	cudaFree(n->dScratch); cudaFree(n->ownX); cudaFree(n->ownY); cudaFree(n->dColterm);
+	cudaFree(n->dXwin); cudaFree(n->dYwin);
+	if (n->hPinned) cudaFreeHost(n->hPinned);
+	if (n->ev0) cudaEventDestroy(n->ev0);
+	if (n->ev1) cudaEventDestroy(n->ev1);
+	if (n->stream) cudaStreamDestroy(n->stream);
+	delete n;
+	return GL_OK;
+}
+
+extern "C" int64_t gl_weight_count(const gl_net* n) { return n ? n->nw : 0; }
+extern "C" int gl_get_epochs(const gl_net* n) { return n ? n->epochs : 0; }
+extern "C" void gl_stop(gl_net* n) { if (n) n->stop = 1; }
+
+static int ensure_pinned(gl_net* n, size_t bytes)
+{
+	if (n->pinnedBytes >= bytes) return 0;
+	if (n->hPinned) cudaFreeHost(n->hPinned);
+	n->hPinned = nullptr;
+	n->pinnedBytes = 0;
+	CU(cudaMallocHost(&n->hPinned, bytes));
+	n->pinnedBytes = bytes;
+	return 0;
+}
+
+// Host -> device through the pinned staging buffer, in chunks.
+static int upload(gl_net* n, float* dst, const float* src, size_t count)
+{
+	const size_t chunk = (size_t)16 << 20;  // floats per chunk (64 MB)
+	if (int r = ensure_pinned(n, (count < chunk ? count : chunk) * sizeof(float))) return r;
+	for (size_t off = 0; off < count; off += chunk)
+	{
+		const size_t c = count - off < chunk ? count - off : chunk;
+		memcpy(n->hPinned, src + off, c * sizeof(float));
+		CU(cudaMemcpyAsync(dst + off, n->hPinned, c * sizeof(float), cudaMemcpyHostToDevice, n->stream));
+		CU(cudaStreamSynchronize(n->stream));
+	}
+	return 0;
+}
+
+extern "C" int gl_set_weights(gl_net* n, const float* w, const float* bias)
+{
+	if (!n || !w) return fail(GL_ERR_INVALID, "gl_set_weights: null argument");
+	if (int r = use_device(n)) return r;
+	if (int r = upload(n, n->dW, w, (size_t)n->nw)) return r;
+	float b[GL_MAX_WEIGHT_LAYERS] = {0};
+	for (int l = 1; l <= n->H; ++l) b[l] = bias ? bias[l - 1] : 0.0f;
+	CU(cudaMemcpyAsync(n->dBias, b, sizeof b, cudaMemcpyHostToDevice, n->stream));
+	if (n->dHist)
+	{
+		CU(cudaMemsetAsync(n->dHist, 0, (size_t)n->nw * n->d.batch_size * sizeof(float), n->stream));
+		CU(cudaMemsetAsync(n->dHistLen, 0, sizeof(int), n->stream));
+	}
+	CU(cudaMemsetAsync(n->dFlags, 0, 4 * sizeof(int), n->stream));
+	CU(cudaStreamSynchronize(n->stream));
+	if (n->tc) tc_weights_changed(n->tc);
+	return GL_OK;
+}
+
+extern "C" int gl_get_weights(gl_net* n, float* w, float* bias)
+{
+	if (!n || !w) return fail(GL_ERR_INVALID, "gl_get_weights: null argument");
+	if (int r = use_device(n)) return r;
+	CU(cudaStreamSynchronize(n->stream));
+	CU(cudaMemcpy(w, n->dW, (size_t)n->nw * sizeof(float), cudaMemcpyDeviceToHost));
+	if (bias)
+	{
+		float b[GL_MAX_WEIGHT_LAYERS];
+		CU(cudaMemcpy(b, n->dBias, sizeof b, cudaMemcpyDeviceToHost));
+		for (int l = 1; l <= n->H; ++l) bias[l - 1] = b[l];
+	}
+	return GL_OK;
+}
+
+extern "C" int gl_set_data(gl_net* n, const float* x, const float* y, int64_t rows)
+{
+	if (!n || !x || !y || rows < 1) return fail(GL_ERR_INVALID, "gl_set_data: bad argument");
+	if (int r = use_device(n)) return r;
+	cudaFree(n->ownX);
+	cudaFree(n->ownY);
+	n->ownX = n->ownY = nullptr;
+	const size_t cx = (size_t)rows * n->d.sizes[0], cy = (size_t)rows * n->n_out;
+	CU(cudaMalloc(&n->ownX, cx * sizeof(float)));
+	CU(cudaMalloc(&n->ownY, cy * sizeof(float)));
+	if (int r = upload(n, n->ownX, x, cx)) return r;
+	if (int r = upload(n, n->ownY, y, cy)) return r;
+	n->dX = n->ownX;
+	n->dY = n->ownY;
+	n->rows = rows;
+	return GL_OK;
+}
+
+extern "C" int gl_set_data_device(gl_net* n, const float* dx, const float* dy, int64_t rows)
+{
+	if (!n || !dx || !dy || rows < 1) return fail(GL_ERR_INVALID, "gl_set_data_device: bad argument");
+	n->dX = dx;
+	n->dY = dy;
+	n->rows = rows;
+	return GL_OK;
+}
+
+// ---- confusion-matrix figures, CMatrix::updateResultParams + getters (GMath/cmatrix.cpp:100-266)
+static void class_metrics(const int* cm, int c, gl_metrics* m)
+{
+	float acc = 0, prec = 0, rec = 0, spec = 0, f1 = 0;
+	for (int k = 0; k < c; ++k)
+	{
+		long long tp = cm[k * c + k], tn = 0, fp = 0, fn = 0;
+		for (int j = 0; j < c; ++j)
+			if (j != k)
+			{
+				tn += cm[j * c + j];
+				fp += cm[j * c + k];
+				fn += cm[k * c + j];
+			}
+		const float truth = (float)(int)(tp + tn), untruth = (float)(int)(fp + fn);
+		acc += truth / (truth + untruth);
+		const float p = ((float)(int)tp) / ((float)(int)(tp + fp));
+		const float r = ((float)(int)tp) / ((float)(int)(tp + fn));
+		prec += p;
+		rec += r;
+		spec += ((float)(int)tn) / ((float)(int)(tn + fp));
+		f1 += (2.0f * r * p) / (r + p);
+	}
+	m->class_accuracy = (acc / (float)c) * 100.0f;
+	m->class_precision = (prec / (float)c) * 100.0f;
+	m->class_recall = (rec / (float)c) * 100.0f;
+	m->class_specificity = (spec / (float)c) * 100.0f;
+	m->class_f1 = (f1 / (float)c) * 100.0f;
+}
+
+static int finish_metrics(gl_net* n, gl_metrics* out, float tot_err, float tot_acc_raw, int64_t rows, float ms,
+                          int64_t launches, bool with_class)
+{
+	if (!out) return 0;
+	memset(out, 0, sizeof *out);
+	out->total_error = tot_err;
+	out->total_accuracy = tot_acc_raw / (((float)rows) * ((float)n->n_out));  // network.cpp:194-195
+	out->epochs = n->epochs;
+	out->rows = rows;
+	out->device_ms = ms;
+	out->kernel_launches = launches;
+	int flags[4];
+	CU(cudaMemcpy(flags, n->dFlags, sizeof flags, cudaMemcpyDeviceToHost));
+	out->nonfinite = flags[0] & 1;
+	if (with_class && n->d.output_type != GL_OUT_REGRESSION && n->n_out <= 4096)
+	{
+		std::vector<int> cm((size_t)n->n_out * n->n_out);
+		CU(cudaMemcpy(cm.data(), n->dConf, cm.size() * sizeof(int), cudaMemcpyDeviceToHost));
+		class_metrics(cm.data(), n->n_out, out);
+	}
+	return 0;
+}
+
+// ------------------------------------------------------------------------------------------------
+// reference mode
+static int ref_train(gl_net* n, int n_epochs, gl_metrics* out)
+{
+	if (n->sumsFCap < n_epochs)
+	{
+		cudaFree(n->dSumsF);
+		n->dSumsF = nullptr;
+		CU(cudaMalloc(&n->dSumsF, (size_t)2 * n_epochs * sizeof(float)));
+		n->sumsFCap = n_epochs;
+	}
+	RefTrainArgs a;
+	memset(&a, 0, sizeof a);
+	a.net = make_view(n);
+	for (int l = 0; l <= n->H; ++l) a.hist[l] = n->dHist + n->woff[l] * n->d.batch_size;
+	a.hist_len = n->dHistLen;
+	a.X = n->dX;
+	a.Y = n->dY;
+	a.rows = n->rows;
+	a.n_epochs = n_epochs;
+	a.epoch_sums = n->dSumsF;
+	a.confusion = n->dConf;
+	a.outputs = nullptr;
+	a.flags = n->dFlags;
+	a.weights_in_smem = ref_train_smem_bytes(a.net, true) <= (size_t)227 * 1024;
+	if (!a.weights_in_smem && ref_train_smem_bytes(a.net, false) > (size_t)227 * 1024)
+		return fail(GL_ERR_TOO_LARGE, "reference mode: %d nodes do not fit the per-sample shared-memory vectors", n->total_nodes);
+	CU(cudaEventRecord(n->ev0, n->stream));
+	CU(launch_ref_train(a, n->stream));
+	CU(cudaEventRecord(n->ev1, n->stream));
+	CU(cudaStreamSynchronize(n->stream));
+	n->launches += 1;
+	n->epochs += n_epochs;
+	float ms = 0;
+	CU(cudaEventElapsedTime(&ms, n->ev0, n->ev1));
+	float sums[2];
+	CU(cudaMemcpy(sums, n->dSumsF + 2 * (n_epochs - 1), sizeof sums, cudaMemcpyDeviceToHost));
+	return finish_metrics(n, out, sums[0], sums[1], n->rows, ms, 1, true);
+}
+
+static int ensure_work(gl_net* n, int64_t rows)
+{
+	if (rows <= n->capRows) return 0;
+	free_work(n);
+	for (int l = 1; l <= n->H + 1; ++l)
+	{
+		CU(cudaMalloc(&n->dA[l], (size_t)rows * n->d.sizes[l] * sizeof(float)));
+		if (n->d.mode == GL_MODE_BATCHED) CU(cudaMalloc(&n->dD[l], (size_t)rows * n->d.sizes[l] * sizeof(float)));
+	}
+	CU(cudaMalloc(&n->dArgmax, (size_t)rows * sizeof(int)));
+	n->capRows = rows;
+	return 0;
+}
+
+// ------------------------------------------------------------------------------------------------
+// batched mode
+static int set_momentum_weights(gl_net* n, int rows, int global_rows, int first_pos)
+{
+	if (n->cRows == rows && n->cGlobal == global_rows && n->cFirst == first_pos) return 0;
+	std::vector<float> c(rows);
+	for (int l = 0; l <= n->H; ++l)
+	{
+		const double m = (double)n->d.momentum[l];
+		if (m == 0.0)
+		{
+			if (n->dC[l]) cudaFree(n->dC[l]);
+			n->dC[l] = nullptr;
+			continue;
+		}
+		// c_j = sum_{t=0}^{global_rows-1-pos} m^t: the closed form of the reference's intra-window
+		// momentum history (State/node.cpp:278-292), which restarts at every apply.
+		for (int j = 0; j < rows; ++j)
+		{
+			const int terms = global_rows - (first_pos + j);
+			double s = 0.0, pw = 1.0;
+			for (int t = 0; t < terms; ++t) { s += pw; pw *= m; if (pw < 1e-30) break; }
+			c[j] = (float)s;
+		}
+		if (n->dC[l]) cudaFree(n->dC[l]);
+		CU(cudaMalloc(&n->dC[l], (size_t)n->capRows * sizeof(float)));
+		CU(cudaMemcpyAsync(n->dC[l], c.data(), rows * sizeof(float), cudaMemcpyHostToDevice, n->stream));
+		CU(cudaStreamSynchronize(n->stream));
+	}
+	n->cRows = rows;
+	n->cGlobal = global_rows;
+	n->cFirst = first_pos;
+	return 0;
+}
+
+static bool want_tc(const gl_net* n, int rows)
+{
+	if (n->d.gemm == GL_GEMM_FFMA) return false;
+	return tc_shapes_ok(n->d, rows, n->d.gemm == GL_GEMM_TCGEN05);
+}
+
+// Forward of `rows` rows starting at device pointer X; activations land in dA[1..H+1].
+static int batched_forward(gl_net* n, const float* X, int rows, int64_t* launches)
+{
+	if (want_tc(n, rows))
+	{
+		if (!n->tc) n->tc = tc_create(n->d, n->dW, n->dBias, n->stream);
+		cudaError_t e = tc_forward(n->tc, X, rows, n->dA, launches);
+		if (e != cudaSuccess) return fail(GL_ERR_CUDA, "tensor-core forward failed: %s", cudaGetErrorString(e));
+		return 0;
+	}
+	const float* in = X;
+	for (int l = 0; l <= n->H; ++l)
+	{
+		GemmArgs g;
+		memset(&g, 0, sizeof g);
+		g.A = in;
+		g.B = n->dW + n->woff[l];
+		g.C = n->dA[l + 1];
+		g.M = rows;
+		g.N = n->d.sizes[l + 1];
+		g.K = n->d.sizes[l];
+		g.a_sm = g.K; g.a_sk = 1;
+		g.b_sn = g.K; g.b_sk = 1;
+		g.ldc = g.N;
+		g.epi = EPI_FORWARD;
+		g.bias_ptr = (l >= 1) ? n->dBias + l : nullptr;
+		g.act = n->d.activation[l];
+		g.par = n->d.act_param[l];
+		CU(launch_gemm_ffma(g, n->stream));
+		++*launches;
+		in = n->dA[l + 1];
+	}
+	return 0;
+}
+
+static int batched_window(gl_net* n, const float* X, const float* Y, int rows, int64_t metric_rows, gl_metrics* out)
+{
+	if (int r = ensure_work(n, rows)) return r;
+	const int global_rows = (n->world > 1 && n->globalRows > 0) ? n->globalRows : rows;
+	const int first_pos = (n->world > 1) ? n->firstPos : 0;
+	if (int r = set_momentum_weights(n, rows, global_rows, first_pos)) return r;
+	int64_t launches = 0;
+	const bool tc = want_tc(n, rows);
+	CU(cudaEventRecord(n->ev0, n->stream));
+	CU(cudaMemsetAsync(n->dSums, 0, 2 * sizeof(double), n->stream));
+	CU(cudaMemsetAsync(n->dG + n->nw, 0, GL_MAX_WEIGHT_LAYERS * sizeof(float), n->stream));
+	if (int r = batched_forward(n, X, rows, &launches)) return r;
+
+	HeadArgs h;
+	memset(&h, 0, sizeof h);
+	h.P = n->dA[n->H + 1];
+	h.Y = Y;
+	h.D = n->dD[n->H + 1];
+	h.rows = rows;
+	h.n = n->n_out;
+	h.out_type = n->d.output_type;
+	h.softmax = n->softmax;
+	h.data_size = (float)(metric_rows * (int64_t)n->n_out);
+	h.sums2 = n->dSums;
+	h.confusion = (n->d.output_type != GL_OUT_REGRESSION) ? n->dConf : nullptr;
+	CU(launch_head(h, n->stream));
+	++launches;
+
+	if (tc)
+	{
+		cudaError_t e = tc_backward(n->tc, X, rows, n->dA, n->dD, n->dC, n->dG, &launches);
+		if (e != cudaSuccess) return fail(GL_ERR_CUDA, "tensor-core backward failed: %s", cudaGetErrorString(e));
+	}
+	for (int L = n->H + 1; L >= 1; --L)
+	{
+		const int l = L - 1;
+		const int ni = n->d.sizes[l], no = n->d.sizes[L];
+		const float* Al = (l == 0) ? X : n->dA[l];
+		if (!tc)
+		{
+			if (l >= 1)
+			{
+				GemmArgs g;
+				memset(&g, 0, sizeof g);
+				g.A = n->dD[L]; g.a_sm = no; g.a_sk = 1;
+				g.B = n->dW + n->woff[l]; g.b_sn = 1; g.b_sk = ni;
+				g.C = n->dD[l]; g.ldc = ni;
+				g.M = rows; g.N = ni; g.K = no;
+				g.epi = EPI_ERRPROP;
+				g.aux = n->dA[l]; g.ld_aux = ni;
+				g.act = n->d.activation[l - 1];
+				g.par = 0.01f;  // the reference passes a fixed 0.01, network.cpp:618
+				CU(launch_gemm_ffma(g, n->stream));
+				++launches;
+			}
+		}
+		const float* colterm = nullptr;
+		if (n->d.wd1[l] != 0.0f || n->d.wd2[l] != 0.0f)
+		{
+			CU(launch_decay_colterm(Al, rows, ni, n->dC[l], n->d.lr[l], n->d.wd1[l], n->d.wd2[l], n->dColterm, n->stream));
+			++launches;
+			colterm = n->dColterm;
+			if (tc) return fail(GL_ERR_STATE, "weight decay is not wired into the tensor-core gradient epilogue");
+		}
+		if (!tc)
+		{
+			GemmArgs g;
+			memset(&g, 0, sizeof g);
+			g.A = n->dD[L]; g.a_sm = 1; g.a_sk = no;
+			g.B = Al; g.b_sn = 1; g.b_sk = ni;
+			g.C = n->dG + n->woff[l]; g.ldc = ni;
+			g.M = no; g.N = ni; g.K = rows;
+			g.kscale = n->dC[l];
+			g.epi = EPI_GRAD;
+			g.alpha = n->d.lr[l];
+			g.colterm = colterm;
+			CU(launch_gemm_ffma(g, n->stream));
+			++launches;
+		}
+		if (l >= 1)
+		{
+			CU(launch_sum_scaled(n->dD[L], (int64_t)rows * no, n->d.lr[l], n->dG + n->nw + l, n->stream));
+			++launches;
+		}
+	}
+	if (n->world > 1)
+	{
+		NC(g_nccl.GroupStart());
+		NC(g_nccl.AllReduce(n->dG, n->dG, (size_t)(n->nw + GL_MAX_WEIGHT_LAYERS), NCCL_FLOAT32, NCCL_SUM, n->comm, n->stream));
+		NC(g_nccl.AllReduce(n->dSums, n->dSums, 2, NCCL_FLOAT64, NCCL_SUM, n->comm, n->stream));
+		NC(g_nccl.GroupEnd());
+	}
+	float bscale[GL_MAX_WEIGHT_LAYERS] = {0};
+	for (int l = 1; l <= n->H; ++l)
+		bscale[l] = (n->d.bias_rule == GL_BIAS_REFERENCE) ? (float)n->d.sizes[l] : 1.0f / (float)global_rows;
+	CU(cudaMemcpyAsync(n->dBscale, bscale, sizeof bscale, cudaMemcpyHostToDevice, n->stream));
+	CU(launch_update(n->dW, n->dG, n->nw, 1.0f / (float)global_rows, n->dBias, n->dG + n->nw, n->dBscale, n->H,
+	                 n->dFlags, n->stream));
+	++launches;
+	if (tc)
+	{
+		cudaError_t e = tc_after_update(n->tc, &launches);
+		if (e != cudaSuccess) return fail(GL_ERR_CUDA, "tensor-core operand refresh failed: %s", cudaGetErrorString(e));
+	}
+	CU(cudaEventRecord(n->ev1, n->stream));
+	n->launches += launches;
+	if (out)
+	{
+		CU(cudaStreamSynchronize(n->stream));
+		float ms = 0;
+		CU(cudaEventElapsedTime(&ms, n->ev0, n->ev1));
+		double sums[2];
+		CU(cudaMemcpy(sums, n->dSums, sizeof sums, cudaMemcpyDeviceToHost));
+		memset(out, 0, sizeof *out);
+		out->total_error = (float)sums[0];
+		out->total_accuracy = (float)(sums[1] / ((double)global_rows * (double)n->n_out));
+		out->epochs = n->epochs;
+		out->rows = global_rows;
+		out->device_ms = ms;
+		out->kernel_launches = launches;
+		int flags[4];
+		CU(cudaMemcpy(flags, n->dFlags, sizeof flags, cudaMemcpyDeviceToHost));
+		out->nonfinite = flags[0] & 1;
+	}
+	return GL_OK;
+}
+
+extern "C" int gl_train_window(gl_net* n, int64_t first_row, int32_t rows, gl_metrics* out)
+{
+	if (!n) return fail(GL_ERR_INVALID, "gl_train_window: null handle");
+	if (n->d.mode != GL_MODE_BATCHED) return fail(GL_ERR_STATE, "gl_train_window needs a batched-mode network");
+	if (!n->dX) return fail(GL_ERR_STATE, "gl_train_window: no data set");
+	if (first_row < 0 || rows < 1 || first_row + rows > n->rows) return fail(GL_ERR_INVALID, "gl_train_window: row range");
+	if (int r = use_device(n)) return r;
+	return batched_window(n, n->dX + first_row * n->d.sizes[0], n->dY + first_row * n->n_out, rows, n->rows, out);
+}
+
+static int ensure_window_staging(gl_net* n, int64_t rows)
+{
+	if (rows <= n->winCap) return 0;
+	cudaFree(n->dXwin);
+	cudaFree(n->dYwin);
+	n->dXwin = n->dYwin = nullptr;
+	CU(cudaMalloc(&n->dXwin, (size_t)rows * n->d.sizes[0] * sizeof(float)));
+	CU(cudaMalloc(&n->dYwin, (size_t)rows * n->n_out * sizeof(float)));
+	n->winCap = rows;
+	return 0;
+}
+
+extern "C" int gl_train_window_host(gl_net* n, const float* x, const float* y, int32_t rows, gl_metrics* out)
+{
+	if (!n || !x || !y || rows < 1) return fail(GL_ERR_INVALID, "gl_train_window_host: bad argument");
+	if (n->d.mode != GL_MODE_BATCHED) return fail(GL_ERR_STATE, "gl_train_window_host needs a batched-mode network");
+	if (int r = use_device(n)) return r;
+	if (int r = ensure_window_staging(n, rows)) return r;
+	// the caller's buffers are read directly by the copy engine (fast when they are pinned)
+	CU(cudaMemcpyAsync(n->dXwin, x, (size_t)rows * n->d.sizes[0] * sizeof(float), cudaMemcpyHostToDevice, n->stream));
+	CU(cudaMemcpyAsync(n->dYwin, y, (size_t)rows * n->n_out * sizeof(float), cudaMemcpyHostToDevice, n->stream));
+	return batched_window(n, n->dXwin, n->dYwin, rows, rows, out);
+}
+
+extern "C" int gl_train_epochs(gl_net* n, int32_t n_epochs, gl_metrics* out)
+{
+	if (!n || n_epochs < 1) return fail(GL_ERR_INVALID, "gl_train_epochs: bad argument");
+	if (!n->dX) return fail(GL_ERR_STATE, "gl_train_epochs: no data set");
+	if (int r = use_device(n)) return r;
+	n->stop = 0;
+	if (n->d.mode == GL_MODE_REFERENCE) return ref_train(n, n_epochs, out);
+	// batched mode: aligned windows of batch_size rows; epoch figures are sums over the windows
+	const int mb = n->d.batch_size;
+	gl_metrics last;
+	memset(&last, 0, sizeof last);
+	for (int ep = 0; ep < n_epochs && !n->stop; ++ep)
+	{
+		double cost = 0.0, acc = 0.0, ms = 0.0;
+		int64_t launches = 0;
+		int nonfinite = 0;
+		CU(cudaMemsetAsync(n->dConf, 0, (size_t)n->n_out * n->n_out * sizeof(int), n->stream));
+		for (int64_t r0 = 0; r0 < n->rows; r0 += mb)
+		{
+			const int cnt = (int)((n->rows - r0) < mb ? (n->rows - r0) : mb);
+			gl_metrics m;
+			if (int r = batched_window(n, n->dX + r0 * n->d.sizes[0], n->dY + r0 * n->n_out, cnt, n->rows, &m)) return r;
+			cost += (double)m.total_error;
+			acc += (double)m.total_accuracy * (double)m.rows * (double)n->n_out;
+			ms += m.device_ms;
+			launches += m.kernel_launches;
+			nonfinite |= m.nonfinite;
+		}
+		n->epochs += 1;
+		if (int r = finish_metrics(n, &last, (float)cost, (float)acc, n->rows, (float)ms, launches, true)) return r;
+		last.nonfinite = nonfinite;
+	}
+	if (out) *out = last;
+	return GL_OK;
+}
+
+// ------------------------------------------------------------------------------------------------
+static int forward_rows(gl_net* n, const float* X, const float* Y, int64_t rows, int64_t metric_rows, float* outputs,
+                        int32_t* argmax, gl_metrics* out)
+{
+	const int64_t chunk_max = (n->d.mode == GL_MODE_REFERENCE) ? 65536 : (rows < 65536 ? rows : 65536);
+	if (int r = ensure_work(n, chunk_max < rows ? chunk_max : rows)) return r;
+	int64_t launches = 0;
+	CU(cudaEventRecord(n->ev0, n->stream));
+	CU(cudaMemsetAsync(n->dSums, 0, 2 * sizeof(double), n->stream));
+	CU(cudaMemsetAsync(n->dConf, 0, (size_t)n->n_out * n->n_out * sizeof(int), n->stream));
+	float* dSumsRef = nullptr;
+	if (n->d.mode == GL_MODE_REFERENCE)
+	{
+		if (n->sumsFCap < 1)
+		{
+			CU(cudaMalloc(&n->dSumsF, 2 * sizeof(float)));
+			n->sumsFCap = 1;
+		}
+		dSumsRef = n->dSumsF;
+		CU(cudaMemsetAsync(dSumsRef, 0, 2 * sizeof(float), n->stream));
+	}
+	const NetView v = make_view(n);
+	for (int64_t r0 = 0; r0 < rows; r0 += n->capRows)
+	{
+		const int cnt = (int)((rows - r0) < n->capRows ? (rows - r0) : n->capRows);
+		const float* Xc = X + r0 * n->d.sizes[0];
+		const float* Yc = Y ? Y + r0 * n->n_out : nullptr;
+		if (n->d.mode == GL_MODE_REFERENCE)
+		{
+			CU(launch_ref_forward(v, Xc, cnt, n->dA, n->stream));
+			launches += n->H + 1;
+			if (Yc && out)
+			{
+				CU(launch_ref_metrics(v, n->dA[n->H + 1], Yc, cnt, metric_rows, dSumsRef, n->dConf, n->stream));
+				++launches;
+			}
+		}
+		else
+		{
+			if (int r = batched_forward(n, Xc, cnt, &launches)) return r;
+		}
+		if (n->d.mode == GL_MODE_BATCHED || argmax)
+		{
+			// batched head: softmax normalisation, argmax, and (with targets) the metric sums
+			HeadArgs h;
+			memset(&h, 0, sizeof h);
+			h.P = n->dA[n->H + 1];
+			h.Y = Yc ? Yc : n->dA[n->H + 1];
+			h.rows = cnt;
+			h.n = n->n_out;
+			h.out_type = n->d.output_type;
+			h.softmax = n->softmax;
+			h.data_size = (float)(metric_rows * (int64_t)n->n_out);
+			h.sums2 = (Yc && n->d.mode == GL_MODE_BATCHED) ? n->dSums : nullptr;
+			h.confusion = (Yc && n->d.mode == GL_MODE_BATCHED && n->d.output_type != GL_OUT_REGRESSION) ? n->dConf : nullptr;
+			h.argmax = n->dArgmax;
+			CU(launch_head(h, n->stream));
+			++launches;
+		}
+		if (outputs)
+			CU(cudaMemcpyAsync(outputs + r0 * n->n_out, n->dA[n->H + 1], (size_t)cnt * n->n_out * sizeof(float),
+			                   cudaMemcpyDeviceToHost, n->stream));
+		if (argmax)
+			CU(cudaMemcpyAsync(argmax + r0, n->dArgmax, (size_t)cnt * sizeof(int), cudaMemcpyDeviceToHost, n->stream));
+		if (outputs || argmax) CU(cudaStreamSynchronize(n->stream));  // the work buffers are reused by the next chunk
+	}
+	CU(cudaEventRecord(n->ev1, n->stream));
+	CU(cudaStreamSynchronize(n->stream));
+	n->launches += launches;
+	if (out)
+	{
+		float ms = 0;
+		CU(cudaEventElapsedTime(&ms, n->ev0, n->ev1));
+		float te = 0, ta = 0;
+		if (Y)
+		{
+			if (n->d.mode == GL_MODE_REFERENCE)
+			{
+				float s[2];
+				CU(cudaMemcpy(s, dSumsRef, sizeof s, cudaMemcpyDeviceToHost));
+				te = s[0];
+				ta = s[1];
+			}
+			else
+			{
+				double s[2];
+				CU(cudaMemcpy(s, n->dSums, sizeof s, cudaMemcpyDeviceToHost));
+				te = (float)s[0];
+				ta = (float)s[1];
+			}
+		}
+		return finish_metrics(n, out, te, ta, rows, ms, launches, Y != nullptr);
+	}
+	return GL_OK;
+}
+
+extern "C" int gl_forward(gl_net* n, int64_t first_row, int64_t rows, float* outputs, int32_t* argmax, gl_metrics* out)
+{
+	if (!n) return fail(GL_ERR_INVALID, "gl_forward: null handle");
+	if (!n->dX) return fail(GL_ERR_STATE, "gl_forward: no data set");
+	if (first_row < 0 || rows < 1 || first_row + rows > n->rows) return fail(GL_ERR_INVALID, "gl_forward: row range");
+	if (int r = use_device(n)) return r;
+	return forward_rows(n, n->dX + first_row * n->d.sizes[0], n->dY ? n->dY + first_row * n->n_out : nullptr, rows,
+	                    n->rows, outputs, argmax, out);
+}
+
+extern "C" int gl_forward_host(gl_net* n, const float* x, const float* y, int64_t rows, float* outputs, int32_t* argmax,
+                               gl_metrics* out)
+{
+	if (!n || !x || rows < 1) return fail(GL_ERR_INVALID, "gl_forward_host: bad argument");
+	if (int r = use_device(n)) return r;
+	if (int r = ensure_window_staging(n, rows)) return r;
+	CU(cudaMemcpyAsync(n->dXwin, x, (size_t)rows * n->d.sizes[0] * sizeof(float), cudaMemcpyHostToDevice, n->stream));
+	if (y) CU(cudaMemcpyAsync(n->dYwin, y, (size_t)rows * n->n_out * sizeof(float), cudaMemcpyHostToDevice, n->stream));
+	return forward_rows(n, n->dXwin, y ? n->dYwin : nullptr, rows, rows, outputs, argmax, out);
+}
+
+extern "C" int gl_get_activations(gl_net* n, int64_t row, float* out)
+{
+	if (!n || !out) return fail(GL_ERR_INVALID, "gl_get_activations: null argument");
+	if (!n->dX || row < 0 || row >= n->rows) return fail(GL_ERR_STATE, "gl_get_activations: no such row");
+	if (int r = use_device(n)) return r;
+	if (int r = ensure_work(n, 1)) return r;
+	int64_t launches = 0;
+	const float* X = n->dX + row * n->d.sizes[0];
+	if (n->d.mode == GL_MODE_REFERENCE)
+	{
+		const NetView v = make_view(n);
+		CU(launch_ref_forward(v, X, 1, n->dA, n->stream));
+		launches = n->H + 1;
+	}
+	else
+	{
+		if (int r = batched_forward(n, X, 1, &launches)) return r;
+		if (n->softmax)
+		{
+			HeadArgs h;
+			memset(&h, 0, sizeof h);
+			h.P = n->dA[n->H + 1];
+			h.Y = n->dA[n->H + 1];
+			h.rows = 1;
+			h.n = n->n_out;
+			h.out_type = n->d.output_type;
+			h.softmax = 1;
+			h.data_size = 1.0f;
+			CU(launch_head(h, n->stream));
+			++launches;
+		}
+	}
+	n->launches += launches;
+	size_t k = 0;
+	for (int l = 1; l <= n->H + 1; ++l)
+	{
+		CU(cudaMemcpyAsync(out + k, n->dA[l], n->d.sizes[l] * sizeof(float), cudaMemcpyDeviceToHost, n->stream));
+		k += n->d.sizes[l];
+	}
+	CU(cudaStreamSynchronize(n->stream));
+	return GL_OK;
+}
+
+extern "C" int gl_get_pending_delta(gl_net* n, int32_t k, float* out)
+{
+	if (!n || !out) return fail(GL_ERR_INVALID, "gl_get_pending_delta: null argument");
+	if (n->d.mode != GL_MODE_REFERENCE) return fail(GL_ERR_STATE, "pending deltas exist in reference mode only");
+	if (int r = use_device(n)) return r;
+	int len = 0;
+	CU(cudaMemcpy(&len, n->dHistLen, sizeof len, cudaMemcpyDeviceToHost));
+	if (k < 0 || k >= len || k >= n->d.batch_size)
+	{
+		memset(out, 0, (size_t)n->nw * sizeof(float));
+		return GL_OK;
+	}
+	for (int l = 0; l <= n->H; ++l)
+	{
+		const int64_t cnt = n->woff[l + 1] - n->woff[l];
+		CU(cudaMemcpy(out + n->woff[l], n->dHist + n->woff[l] * n->d.batch_size + (int64_t)k * cnt, cnt * sizeof(float),
+		              cudaMemcpyDeviceToHost));
+	}
+	return GL_OK;
+}
+
+extern "C" int gl_get_confusion(gl_net* n, int32_t* out)
+{
+	if (!n || !out) return fail(GL_ERR_INVALID, "gl_get_confusion: null argument");
+	if (int r = use_device(n)) return r;
+	CU(cudaStreamSynchronize(n->stream));
+	CU(cudaMemcpy(out, n->dConf, (size_t)n->n_out * n->n_out * sizeof(int), cudaMemcpyDeviceToHost));
+	return GL_OK;
+}
+
+// ------------------------------------------------------------------------------------------------
+extern "C" void gl_shard_range(int64_t rows, int32_t rank, int32_t world, int64_t* first, int64_t* count)
+{
+	if (world < 1) world = 1;
+	const int64_t base = rows / world, rem = rows % world;
+	const int64_t f = (int64_t)rank * base + (rank < rem ? rank : rem);
+	if (first) *first = f;
+	if (count) *count = base + (rank < rem ? 1 : 0);
+}
+
+extern "C" int gl_dp_unique_id(void* id128)
+{
+	if (!id128) return fail(GL_ERR_INVALID, "gl_dp_unique_id: null argument");
+	if (int r = nccl_load()) return r;
+	nccl_uid id;
+	NC(g_nccl.GetUniqueId(&id));
+	memcpy(id128, &id, sizeof id);
+	return GL_OK;
+}
+
+extern "C" int gl_dp_init(gl_net* n, int32_t rank, int32_t world, const void* id128)
+{
+	if (!n || !id128 || world < 1 || rank < 0 || rank >= world) return fail(GL_ERR_INVALID, "gl_dp_init: bad argument");
+	if (n->d.mode != GL_MODE_BATCHED) return fail(GL_ERR_STATE, "data parallelism needs a batched-mode network");
+	if (int r = use_device(n)) return r;
+	n->rank = rank;
+	n->world = world;
+	if (world == 1) return GL_OK;
+	if (int r = nccl_load()) return r;
+	nccl_uid id;
+	memcpy(&id, id128, sizeof id);
+	NC(g_nccl.CommInitRank(&n->comm, world, id, rank));
+	return GL_OK;
+}
+
+extern "C" int gl_dp_set_window(gl_net* n, int32_t global_rows, int32_t first_global_pos)
+{
+	if (!n || global_rows < 1 || first_global_pos < 0) return fail(GL_ERR_INVALID, "gl_dp_set_window: bad argument");
+	n->globalRows = global_rows;
+	n->firstPos = first_global_pos;
+	return GL_OK;
+}
+
+// ------------------------------------------------------------------------------------------------
+extern "C" int gl_synth_fill(float* d_out, int64_t count, uint64_t seed, uint32_t stream_id, int32_t dist, float scale,
+                             float offset, int32_t device)
+{
+	if (!d_out || count < 0) return fail(GL_ERR_INVALID, "gl_synth_fill: bad argument");
+	if (gl_device_count() < 1) return fail(GL_ERR_NO_DEVICE, "no sm_100 CUDA device");
+	CU(cudaSetDevice(device));
+	CU(launch_synth_fill(d_out, count, seed, stream_id, dist, scale, offset, 0));
+	CU(cudaDeviceSynchronize());
+	return GL_OK;
+}
+
+extern "C" int gl_device_alloc(void** p, int64_t bytes, int32_t device)
+{
+	if (!p || bytes < 0) return fail(GL_ERR_INVALID, "gl_device_alloc: bad argument");
+	if (gl_device_count() < 1) return fail(GL_ERR_NO_DEVICE, "no sm_100 CUDA device");
+	CU(cudaSetDevice(device));
+	CU(cudaMalloc(p, (size_t)bytes));
+	return GL_OK;
+}
+extern "C" int gl_device_free(void* p, int32_t device)
+{
+	CU(cudaSetDevice(device));
+	CU(cudaFree(p));
+	return GL_OK;
+}
+extern "C" int gl_memcpy_h2d(void* d, const void* h, int64_t bytes, int32_t device)
+{
+	CU(cudaSetDevice(device));
+	CU(cudaMemcpy(d, h, (size_t)bytes, cudaMemcpyHostToDevice));
+	return GL_OK;
+}
+extern "C" int gl_memcpy_d2h(void* h, const void* d, int64_t bytes, int32_t device)
+{
+	CU(cudaSetDevice(device));
+	CU(cudaMemcpy(h, d, (size_t)bytes, cudaMemcpyDeviceToHost));
+	return GL_OK;
+}
+extern "C" int gl_host_alloc_pinned(void** p, int64_t bytes)
+{
+	if (!p || bytes < 0) return fail(GL_ERR_INVALID, "gl_host_alloc_pinned: bad argument");
+	CU(cudaMallocHost(p, (size_t)bytes));
+	return GL_OK;
+}
+extern "C" int gl_host_free_pinned(void* p)
+{
+	CU(cudaFreeHost(p));
+	return GL_OK;
+}

@@ -1,0 +1,105 @@
+// Internal declarations shared by the C-ABI layer (api.cu) and the kernel files.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "glades_b200.h"
+
+namespace glb {
+
+// Device-side view of one network, passed by value to the kernels.
+struct NetView
+{
+	int H;                                   // hidden layers; weight layers are 0..H
+	int sizes[GL_MAX_WEIGHT_LAYERS + 1];
+	float lr[GL_MAX_WEIGHT_LAYERS], mom[GL_MAX_WEIGHT_LAYERS], wd1[GL_MAX_WEIGHT_LAYERS], wd2[GL_MAX_WEIGHT_LAYERS];
+	int act[GL_MAX_WEIGHT_LAYERS];
+	float par[GL_MAX_WEIGHT_LAYERS];
+	int out_type;
+	int mb;
+	float* W[GL_MAX_WEIGHT_LAYERS];          // W_l [n_{l+1}][n_l], slices of one flat allocation
+	float* bias;                             // [GL_MAX_WEIGHT_LAYERS], entry l used for l = 1..H
+};
+
+// ---- reference mode (ref_mode.cu) ----------------------------------------------------------
+struct RefTrainArgs
+{
+	NetView net;
+	float* hist[GL_MAX_WEIGHT_LAYERS];  // pending deltas [mb][n_{l+1}*n_l]
+	int* hist_len;                      // device scalar
+	const float* X;
+	const float* Y;
+	long long rows;
+	int n_epochs;
+	float* scratch;                     // 3 * total_nodes floats: activations, error accumulators, d / base
+	float* epoch_sums;                  // [n_epochs][2]: raw cost sum, raw accuracy sum
+	int* confusion;                     // [n_out][n_out], counts of the LAST epoch
+	float* outputs;                     // optional [rows][n_out], predictions of the last epoch
+	int* flags;                         // [0] non-finite weight seen after the call
+	int weights_in_smem;                // stage W and hist in shared memory for the whole launch
+};
+size_t ref_train_smem_bytes(const NetView& n, bool weights_in_smem);
+cudaError_t launch_ref_train(const RefTrainArgs& a, cudaStream_t s);
+
+// Exact-order forward of rows [first, first+rows): one thread per (row, output node), k ascending.
+// acts: per-layer activation buffers [rows][n_l] for l = 1..H+1 (device).
+cudaError_t launch_ref_forward(const NetView& n, const float* X, long long rows, float* const* acts, cudaStream_t s);
+// Sequential (row-major) metric accumulation over predictions P [rows][n_out] against Y.
+cudaError_t launch_ref_metrics(const NetView& n, const float* P, const float* Y, long long rows, long long data_rows,
+                               float* sums2, int* confusion, cudaStream_t s);
+
+// ---- batched mode (batched.cu) ---------------------------------------------------------------
+enum { EPI_NONE = 0, EPI_FORWARD = 1, EPI_ERRPROP = 2, EPI_GRAD = 3 };
+struct GemmArgs
+{
+	// C[M][N] (ldc) = sum_k A(m,k) * B(n,k);  A(m,k) = A[m*a_sm + k*a_sk], B(n,k) = B[n*b_sn + k*b_sk]
+	const float* A;
+	const float* B;
+	float* C;
+	int M, N, K;
+	long long a_sm, a_sk, b_sn, b_sk, ldc;
+	const float* kscale;   // optional per-k factor (momentum weights c_j), applied to A(m,k)
+	int epi;
+	// EPI_FORWARD: C = squash(acc + bias, act, par).  EPI_ERRPROP: C = acc * act'(aux[m][n]).
+	// EPI_GRAD: C = alpha * acc + colterm[n]
+	const float* bias_ptr;  // device scalar added before the activation, or NULL
+	int act;
+	float par;
+	const float* aux;
+	long long ld_aux;
+	float alpha;
+	const float* colterm;
+};
+cudaError_t launch_gemm_ffma(const GemmArgs& g, cudaStream_t s);
+
+struct HeadArgs
+{
+	// Output layer: predictions P [rows][n] (for softmax: logits in, probabilities out), targets Y,
+	// writes D = delta of the output layer and accumulates metrics.
+	float* P;
+	const float* Y;
+	float* D;          // may be NULL (inference)
+	int rows, n;
+	int out_type;
+	int softmax;
+	float data_size;   // rows_of_epoch * n_out, the cost divisor
+	double* sums2;     // [0] cost sum, [1] accuracy sum (atomic)
+	int* confusion;    // [n][n] or NULL
+	int* argmax;       // optional [rows]
+};
+cudaError_t launch_head(const HeadArgs& h, cudaStream_t s);
+
+// sum over all elements of D [rows*n] times alpha, atomically added to *out
+cudaError_t launch_sum_scaled(const float* D, long long count, float alpha, float* out, cudaStream_t s);
+// colterm[i] = lr * sum_j c_j * (wd1*|A[j][i]| + wd2*A[j][i])
+cudaError_t launch_decay_colterm(const float* A, int rows, int n, const float* c, float lr, float wd1, float wd2,
+                                 float* colterm, cudaStream_t s);
+// W -= G * inv_mb for the flat weight vector; biases b_l -= gb_l * bscale_l; sets flags[0] on non-finite
+cudaError_t launch_update(float* W, const float* G, long long count, float inv_mb, float* bias, const float* gb,
+                          const float* bscale, int H, int* flags, cudaStream_t s);
+
+// ---- synthetic inputs (synth.cu) ---------------------------------------------------------------
+cudaError_t launch_synth_fill(float* out, long long n, unsigned long long seed, unsigned stream_id, int dist,
+                              float scale, float offset, cudaStream_t s);
+
+}  // namespace glb

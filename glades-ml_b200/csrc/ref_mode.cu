@@ -1,0 +1,377 @@
+// Reference-mode kernels: the reference's per-sample SGD, sample after sample, in its exact fp32
+// operation order.
+//
+// ref_train_kernel is one persistent CTA that runs n_epochs * rows samples in a single launch.  A
+// sample of NNetwork::SGDHelper (Networks/network.cpp:399-455) is restated on dense matrices:
+//   forward   (network.cpp:457-575)  one thread per output node, k ascending, product rounded then
+//             sum rounded (Node::getActivation, State/node.cpp:82-93), scalar layer bias added
+//             after the sum, then GMath::squash;
+//   metrics   (network.cpp:519-547)  one thread, row-major (row, output) order, because the
+//             reference's epoch sums are sequential fp32 accumulations;
+//   backward  (network.cpp:577-668)  per weight layer from the top: first the node deltas
+//             d_o = E_o * act'(a_o); then one thread per INPUT node i walks o = 0..n-1 (the
+//             reference's inner loop): pending delta (Node::getDelta, node.cpp:278-292), apply on
+//             rows with r % mb == 0 (node.cpp:294-307), and the doubling error accumulation
+//             E_i += E_i + d_o*W_oi with the already-updated weight (network.cpp:660-662); the
+//             scalar bias recurrence b -= lr*d_o, executed n_in*n_out times per sample
+//             (network.cpp:653-656), is a strictly sequential fp32 chain and runs on one thread
+//             beside the column threads.
+// Weights, pending deltas and all per-sample vectors live in shared memory when they fit
+// (up to 227 KB); otherwise in global memory (L1-resident for one CTA).
+#include "common.cuh"
+#include "internal.h"
+
+namespace glb {
+
+__device__ __forceinline__ int argmax_ref(const float* v, int n)
+{
+	// GMath::naiveVectorDecomp (GMath/gmath.cpp:435-455): strict > from 0, first maximum wins.
+	float mx = 0.0f;
+	int idx = -1;
+	for (int i = 0; i < n; ++i)
+		if (v[i] > mx)
+		{
+			mx = v[i];
+			idx = i;
+		}
+	return idx;
+}
+
+__global__ void __launch_bounds__(1024, 1) ref_train_kernel(const __grid_constant__ RefTrainArgs a)
+{
+	extern __shared__ __align__(16) float smem[];
+	const NetView& n = a.net;
+	const int H = n.H;
+	const int T = blockDim.x;
+	const int t = threadIdx.x;
+	const int n_out = n.sizes[H + 1];
+
+	int total_nodes = 0;
+	for (int l = 0; l <= H + 1; ++l) total_nodes += n.sizes[l];
+
+	// per-sample vectors: activations | error accumulators | d | base
+	float* act_base = smem;
+	float* err_base = act_base + total_nodes;
+	float* dvec = err_base + total_nodes;
+	float* basev = dvec + total_nodes;
+	float* sbias = basev + total_nodes;  // GL_MAX_WEIGHT_LAYERS floats
+	float* wcur = sbias + GL_MAX_WEIGHT_LAYERS;
+
+	float* actp[GL_MAX_WEIGHT_LAYERS + 1];
+	float* errp[GL_MAX_WEIGHT_LAYERS + 1];
+	float* Wp[GL_MAX_WEIGHT_LAYERS];
+	float* Hp[GL_MAX_WEIGHT_LAYERS];
+	{
+		int off = 0;
+		for (int l = 0; l <= H + 1; ++l)
+		{
+			actp[l] = act_base + off;
+			errp[l] = err_base + off;
+			off += n.sizes[l];
+		}
+	}
+	for (int l = 0; l <= H; ++l)
+	{
+		const int cnt = n.sizes[l] * n.sizes[l + 1];
+		if (a.weights_in_smem)
+		{
+			Wp[l] = wcur;
+			wcur += cnt;
+			Hp[l] = wcur;
+			wcur += (size_t)cnt * n.mb;
+			for (int e = t; e < cnt; e += T) Wp[l][e] = n.W[l][e];
+			for (int e = t; e < cnt * n.mb; e += T) Hp[l][e] = a.hist[l][e];
+		}
+		else
+		{
+			Wp[l] = n.W[l];
+			Hp[l] = a.hist[l];
+		}
+	}
+	for (int e = t; e < total_nodes; e += T) err_base[e] = 0.0f;
+	if (t < GL_MAX_WEIGHT_LAYERS) sbias[t] = n.bias[t];
+	__shared__ int s_hist_len;
+	__shared__ float s_tot_err, s_tot_acc;
+	if (t == 0) s_hist_len = *a.hist_len;
+	__syncthreads();
+
+	const float data_size = (float)(a.rows * (long long)n_out);
+	const bool classify = n.out_type != GL_OUT_REGRESSION;
+
+	for (int ep = 0; ep < a.n_epochs; ++ep)
+	{
+		const bool last_epoch = (ep == a.n_epochs - 1);
+		if (t == 0)
+		{
+			s_tot_err = 0.0f;
+			s_tot_acc = 0.0f;
+		}
+		if (classify)
+			for (int e = t; e < n_out * n_out; e += T) a.confusion[e] = 0;
+		__syncthreads();
+
+		for (long long r = 0; r < a.rows; ++r)
+		{
+			// ---------------- forward
+			for (int i = t; i < n.sizes[0]; i += T) actp[0][i] = a.X[r * n.sizes[0] + i];
+			__syncthreads();
+			for (int l = 0; l <= H; ++l)
+			{
+				const int ni = n.sizes[l], no = n.sizes[l + 1];
+				const float* W = Wp[l];
+				const float* ain = actp[l];
+				for (int o = t; o < no; o += T)
+				{
+					float z = 0.0f;
+					const float* wr = W + (size_t)o * ni;
+					for (int i = 0; i < ni; ++i) z = __fadd_rn(z, __fmul_rn(wr[i], ain[i]));
+					if (l >= 1) z = __fadd_rn(z, sbias[l]);
+					actp[l + 1][o] = squash_x(z, n.act[l], n.par[l]);
+				}
+				__syncthreads();
+			}
+			// ---------------- metrics: sequential fp32 sums in (row, output) order
+			const float* yr = a.Y + r * n_out;
+			if (t == 0)
+			{
+				const float* p = actp[H + 1];
+				float te = s_tot_err, ta = s_tot_acc;
+				for (int o = 0; o < n_out; ++o)
+				{
+					te = __fadd_rn(te, cost_x(yr[o], p[o], data_size, n.out_type));
+					ta = __fadd_rn(ta, node_accuracy_x(yr[o], p[o]));
+				}
+				s_tot_err = te;
+				s_tot_acc = ta;
+				if (classify)
+				{
+					int ie = argmax_ref(yr, n_out), ip = argmax_ref(p, n_out);
+					if (ie >= 0 && ip >= 0) a.confusion[ie * n_out + ip] += 1;
+				}
+			}
+			if (a.outputs && last_epoch)
+				for (int o = t; o < n_out; o += T) a.outputs[r * n_out + o] = actp[H + 1][o];
+
+			// ---------------- backward
+			const int k = s_hist_len;
+			const bool apply = (r % n.mb) == 0;
+			for (int L = H + 1; L >= 1; --L)
+			{
+				const int l = L - 1;
+				const int ni = n.sizes[l], no = n.sizes[L];
+				const float lr = n.lr[l], mom = n.mom[l];
+				// node deltas of layer L
+				for (int o = t; o < no; o += T)
+				{
+					float E, der = 1.0f;
+					if (L == H + 1)
+						E = __fadd_rn(0.0f, cost_der_x(yr[o], actp[L][o], n.out_type));
+					else
+					{
+						E = errp[L][o];
+						der = act_der_x(actp[L][o], n.act[l], 0.01f);  // parameter fixed by the caller, network.cpp:618
+						errp[L][o] = 0.0f;
+					}
+					const float d = __fmul_rn(E, der);
+					dvec[o] = d;
+					basev[o] = __fmul_rn(lr, d);
+				}
+				__syncthreads();
+				float* W = Wp[l];
+				float* hist = Hp[l];
+				const size_t cnt = (size_t)ni * no;
+				const float wl1 = __fmul_rn(n.wd1[l], lr), wl2 = __fmul_rn(n.wd2[l], lr);
+				const float fmb = (float)n.mb;
+				for (int i = t; i < ni; i += T)
+				{
+					const float ai = actp[l][i];
+					const float c3 = __fmul_rn(wl1, fabsf(ai));
+					const float c4 = __fmul_rn(wl2, ai);
+					float E = (l >= 1) ? errp[l][i] : 0.0f;
+					for (int o = 0; o < no; ++o)
+					{
+						const size_t e = (size_t)o * ni + i;
+						const float last = (k > 0) ? hist[(size_t)(k - 1) * cnt + e] : 0.0f;
+						const float delta = __fadd_rn(
+						    __fadd_rn(__fadd_rn(__fmul_rn(basev[o], ai), __fmul_rn(mom, last)), c3), c4);
+						hist[(size_t)k * cnt + e] = delta;
+						float w = W[e];
+						if (apply)
+						{
+							float s = 0.0f;
+							for (int q = 0; q < k; ++q) s = __fadd_rn(s, hist[(size_t)q * cnt + e]);
+							s = __fadd_rn(s, delta);
+							s = __fdiv_rn(s, fmb);
+							w = __fsub_rn(w, s);
+							W[e] = w;
+						}
+						if (l >= 1)
+						{
+							const float tt = __fadd_rn(E, __fmul_rn(dvec[o], w));
+							E = __fadd_rn(E, tt);
+						}
+					}
+					if (l >= 1) errp[l][i] = E;
+				}
+				// scalar bias recurrence of the input-side hidden layer: one sequential chain
+				if (l >= 1 && t == T - 1)
+				{
+					float b = sbias[l];
+					for (int i = 0; i < ni; ++i)
+						for (int o = 0; o < no; ++o) b = __fsub_rn(b, basev[o]);
+					sbias[l] = b;
+				}
+				__syncthreads();
+			}
+			if (t == 0) s_hist_len = apply ? 0 : k + 1;
+			__syncthreads();
+		}
+		if (t == 0)
+		{
+			a.epoch_sums[2 * ep + 0] = s_tot_err;
+			a.epoch_sums[2 * ep + 1] = s_tot_acc;
+		}
+		__syncthreads();
+	}
+
+	// write back state and look for non-finite weights
+	int bad = 0;
+	for (int l = 0; l <= H; ++l)
+	{
+		const int cnt = n.sizes[l] * n.sizes[l + 1];
+		if (a.weights_in_smem)
+		{
+			for (int e = t; e < cnt; e += T) n.W[l][e] = Wp[l][e];
+			for (int e = t; e < cnt * n.mb; e += T) a.hist[l][e] = Hp[l][e];
+		}
+		for (int e = t; e < cnt; e += T)
+			if (!isfinite(Wp[l][e])) bad = 1;
+	}
+	if (t < GL_MAX_WEIGHT_LAYERS)
+	{
+		n.bias[t] = sbias[t];
+		if (t >= 1 && t <= H && !isfinite(sbias[t])) bad = 1;
+	}
+	if (t == 0) *a.hist_len = s_hist_len;
+	if (bad) atomicOr(a.flags, 1);
+}
+
+static int total_nodes_of(const NetView& n)
+{
+	int s = 0;
+	for (int l = 0; l <= n.H + 1; ++l) s += n.sizes[l];
+	return s;
+}
+
+size_t ref_train_smem_bytes(const NetView& n, bool weights_in_smem)
+{
+	size_t f = 4 * (size_t)total_nodes_of(n) + GL_MAX_WEIGHT_LAYERS;
+	if (weights_in_smem)
+		for (int l = 0; l <= n.H; ++l) f += (size_t)n.sizes[l] * n.sizes[l + 1] * (1 + (size_t)n.mb);
+	return f * sizeof(float);
+}
+
+cudaError_t launch_ref_train(const RefTrainArgs& a, cudaStream_t s)
+{
+	int maxw = 1;
+	for (int l = 0; l <= a.net.H + 1; ++l) maxw = a.net.sizes[l] > maxw ? a.net.sizes[l] : maxw;
+	int T = ((maxw + 1 + 31) / 32) * 32;  // one spare thread for the bias chain
+	if (T > 1024) T = 1024;
+	const size_t bytes = ref_train_smem_bytes(a.net, a.weights_in_smem != 0);
+	cudaError_t e = cudaFuncSetAttribute(ref_train_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+	if (e != cudaSuccess) return e;
+	ref_train_kernel<<<1, T, bytes, s>>>(a);
+	return cudaGetLastError();
+}
+
+// ---------------------------------------------------------------------------------------------
+// Exact-order forward for inference / read-back: rows are independent, so the grid runs over
+// (row, output node); each thread still sums k ascending with separately rounded products.
+struct FwdLayerArgs
+{
+	const float* in;   // [rows][ni]
+	float* out;        // [rows][no]
+	const float* W;
+	const float* bias; // device array, entry l
+	int ni, no, l, act;
+	float par;
+	long long rows;
+};
+
+__global__ void ref_forward_layer_kernel(const FwdLayerArgs f)
+{
+	const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+	const long long total = f.rows * f.no;
+	if (idx >= total) return;
+	const long long r = idx / f.no;
+	const int o = (int)(idx - r * f.no);
+	const float* x = f.in + r * f.ni;
+	const float* w = f.W + (size_t)o * f.ni;
+	float z = 0.0f;
+	for (int i = 0; i < f.ni; ++i) z = __fadd_rn(z, __fmul_rn(w[i], x[i]));
+	if (f.l >= 1) z = __fadd_rn(z, f.bias[f.l]);
+	f.out[idx] = squash_x(z, f.act, f.par);
+}
+
+cudaError_t launch_ref_forward(const NetView& n, const float* X, long long rows, float* const* acts, cudaStream_t s)
+{
+	const float* in = X;
+	for (int l = 0; l <= n.H; ++l)
+	{
+		FwdLayerArgs f;
+		f.in = in;
+		f.out = acts[l + 1];
+		f.W = n.W[l];
+		f.bias = n.bias;
+		f.ni = n.sizes[l];
+		f.no = n.sizes[l + 1];
+		f.l = l;
+		f.act = n.act[l];
+		f.par = n.par[l];
+		f.rows = rows;
+		const long long total = rows * f.no;
+		const int T = 128;
+		ref_forward_layer_kernel<<<(unsigned)((total + T - 1) / T), T, 0, s>>>(f);
+		cudaError_t e = cudaGetLastError();
+		if (e != cudaSuccess) return e;
+		in = f.out;
+	}
+	return cudaSuccess;
+}
+
+// Sequential metric accumulation in the reference's (row, output) order -- one thread, because
+// fp32 addition is not associative and the epoch figures are compared bit for bit.
+__global__ void ref_metrics_kernel(NetView n, const float* P, const float* Y, long long rows, long long data_rows,
+                                   float* sums2, int* confusion)
+{
+	if (threadIdx.x != 0 || blockIdx.x != 0) return;
+	const int no = n.sizes[n.H + 1];
+	const float data_size = (float)(data_rows * (long long)no);
+	float te = sums2[0], ta = sums2[1];
+	for (long long r = 0; r < rows; ++r)
+	{
+		const float* p = P + r * no;
+		const float* y = Y + r * no;
+		for (int o = 0; o < no; ++o)
+		{
+			te = __fadd_rn(te, cost_x(y[o], p[o], data_size, n.out_type));
+			ta = __fadd_rn(ta, node_accuracy_x(y[o], p[o]));
+		}
+		if (n.out_type != GL_OUT_REGRESSION && confusion)
+		{
+			int ie = argmax_ref(y, no), ip = argmax_ref(p, no);
+			if (ie >= 0 && ip >= 0) confusion[ie * no + ip] += 1;
+		}
+	}
+	sums2[0] = te;
+	sums2[1] = ta;
+}
+
+cudaError_t launch_ref_metrics(const NetView& n, const float* P, const float* Y, long long rows, long long data_rows,
+                               float* sums2, int* confusion, cudaStream_t s)
+{
+	ref_metrics_kernel<<<1, 32, 0, s>>>(n, P, Y, rows, data_rows, sums2, confusion);
+	return cudaGetLastError();
+}
+
+}  // namespace glb

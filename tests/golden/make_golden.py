@@ -1,0 +1,233 @@
+"""Generates the golden fixtures in this directory from the COMPILED REFERENCE.
+
+Run once, where a reference checkout exists (it cannot run on the GPU box):
+
+    make -C oracle ref restate && python tests/golden/make_golden.py
+
+Every array below is produced by the reference's own code (oracle/_ref/libglades_ref.so: the
+unmodified Backend/Machine Learning sources behind oracle/ref_harness.cpp) on seeded synthetic
+inputs; nothing is taken from the reference's data files.  Large weight sets are not stored: they
+are regenerated from (seed, stream) by the counter-based uniform generator, which is exact on CPU
+and GPU alike.
+"""
+import json
+import os
+import sys
+import time
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(os.path.dirname(HERE))
+sys.path.insert(0, ROOT)
+import __graft_entry__ as ge  # noqa: E402
+
+import importlib.util  # noqa: E402
+
+_spec = importlib.util.spec_from_file_location("capi", os.path.join(ROOT, "glades-ml_b200", "capi.py"))
+capi = importlib.util.module_from_spec(_spec)
+_spec.loader.exec_module(capi)
+o = ge.import_oracle()
+
+SEED = 0x474C4144  # "GLAD"
+
+
+def gaussian_classes(rng, rows, n_in, n_cls, interleaved=True):
+    means = rng.uniform(-2, 2, (n_cls, n_in))
+    cls = (np.arange(rows) % n_cls) if interleaved else (np.arange(rows) // (rows // n_cls))
+    x = (means[cls] + 0.5 * rng.standard_normal((rows, n_in))).astype(np.float32)
+    y = np.full((rows, n_cls), 0.01, np.float32)
+    y[np.arange(rows), cls] = 0.99
+    return x, y
+
+
+def save(name, meta, **arrays):
+    path = os.path.join(HERE, name + ".npz")
+    np.savez_compressed(path, meta=np.array(json.dumps(meta)), **arrays)
+    print("wrote %s (%.1f KB)" % (name, os.path.getsize(path) / 1024.0))
+
+
+def trajectory(name, sizes, acts, out, x, y, mb, lr, mom, epochs, snapshots, w_range, seed, params=None, wd1=0.0,
+               wd2=0.0):
+    rng = np.random.default_rng(seed)
+    d = capi.make_desc(sizes, acts, out, batch=mb, lr=lr, momentum=mom, wd1=wd1, wd2=wd2, params=params)
+    nw = capi.weight_count(d)
+    w0 = rng.uniform(-w_range, w_range, nw).astype(np.float32)
+    b0 = rng.uniform(-0.1, 0.1, len(sizes) - 2).astype(np.float32)
+    R = o.Reference(d, x, y, capi.Metrics)
+    R.set_weights(w0, b0)
+    mets, cms, ws, bs, outs = [], [], [], [], []
+    for e in range(1, epochs + 1):
+        m, cm, outp = R.epoch(0, True)
+        if e in snapshots:
+            w, b = R.get_weights()
+            mets.append([m.total_error, m.total_accuracy, m.class_accuracy, m.class_precision, m.class_recall,
+                         m.class_specificity, m.class_f1])
+            cms.append(cm)
+            ws.append(w)
+            bs.append(b)
+            outs.append(outp)
+    pend = np.stack([R.pending_delta(k) for k in range(mb)])
+    # cross-check the public path: a second reference object trained with NNetwork::train()
+    R2 = o.Reference(d, x, y, capi.Metrics)
+    R2.set_weights(w0, b0)
+    R2.train_public(epochs)
+    w2, b2 = R2.get_weights()
+    assert np.array_equal(w2.view(np.uint32), ws[-1].view(np.uint32)), "public train() differs from row-driven epochs"
+    assert np.array_equal(b2.view(np.uint32), bs[-1].view(np.uint32))
+    meta = dict(kind="trajectory", sizes=sizes, acts=acts, out=out, batch=mb, lr=lr, momentum=mom, wd1=wd1, wd2=wd2,
+                params=params, epochs=epochs, snapshots=sorted(snapshots))
+    save(name, meta, x=x, y=y, w0=w0, b0=b0, metrics=np.array(mets, np.float32), confusion=np.array(cms, np.int32),
+         w=np.array(ws), b=np.array(bs), outputs=np.array(outs), pending=pend)
+
+
+def main():
+    t0 = time.time()
+    L = o.reference_lib()
+
+    # ---- A. scalar known answers of GMath (gmath.cpp:22-101,182-353)
+    zs = np.concatenate([np.linspace(-12, 12, 193), [0.0, 0.046, 0.0459, 0.0461, 1e-8, -1e-8, 88.0, -88.0, 0.9, 0.1]]
+                        ).astype(np.float32)
+    squash = np.array([[L.ref_squash(float(z), a, p) for z in zs] for a in range(8) for p in (0.0, 0.1, 1.0)],
+                      np.float32)
+    der = np.array([[L.ref_act_der(float(z), a, p) for z in zs] for a in range(8) for p in (0.01, -0.02)], np.float32)
+    ps = np.linspace(0.001, 0.999, 97).astype(np.float32)
+    es = np.array([0.01, 0.99, 0.0, 1.0, 0.5], np.float32)
+    with np.errstate(all="ignore"):
+        cost = np.array([[[L.ref_cost(float(e), float(p), 450.0, fx) for p in ps] for e in es] for fx in range(3)],
+                        np.float32)
+        cder = np.array([[[L.ref_cost_der(float(e), float(p), fx) for p in ps] for e in es] for fx in range(3)],
+                        np.float32)
+    save("kat_scalar", dict(kind="scalar", squash_params=[0.0, 0.1, 1.0], der_params=[0.01, -0.02], data_size=450.0),
+         zs=zs, squash=squash, der=der, ps=ps, es=es, cost=cost, cost_der=cder)
+
+    # ---- B. trajectories
+    rng = np.random.default_rng(11)
+    # the reference's own toy shape: 2-2-1 tanh regression, lr 0.003, online
+    xx = np.array([[0, 0], [0, 1], [1, 0], [1, 1]], np.float32)
+    xy = np.array([[0], [1], [1], [0]], np.float32)
+    trajectory("traj_xor_2_2_1", [2, 2, 1], ["tanh", "tanh"], "regression", xx, xy, 1, 0.003, 0.0, 100, {1, 10, 100},
+               0.5, 21)
+    x, y = gaussian_classes(rng, 150, 4, 3)
+    trajectory("traj_cls_4_5_3", [4, 5, 3], ["sigmoid", "sigmoid"], "classification", x, y, 1, 0.01, 0.0, 20,
+               {1, 5, 20}, 0.5, 22)
+    # config 1 at the only learning rate where the reference stays finite (0.01, interleaved rows)
+    x1, y1 = gaussian_classes(rng, 150, 4, 3)
+    trajectory("traj_cfg1_lr001", [4, 16, 3], ["sigmoid", "sigmoid"], "classification", x1, y1, 1, 0.01, 0.9, 200,
+               {1, 2, 5, 20, 200}, 0.5, 23)
+    trajectory("traj_cfg1_mb4", [4, 16, 3], ["sigmoid", "sigmoid"], "classification", x1, y1, 4, 0.01, 0.9, 7,
+               {1, 2, 7}, 0.5, 24)
+    xr = rng.uniform(0, 1, (64, 10)).astype(np.float32)
+    yr = rng.uniform(0, 1, (64, 1)).astype(np.float32)
+    trajectory("traj_reg_10_8_8_1_mb32", [10, 8, 8, 1], ["tanh", "tanh", "sigmoid"], "regression", xr, yr, 32, 0.05,
+               0.9, 5, {1, 5}, 0.5, 25)
+    xr = rng.uniform(-1, 1, (100, 6)).astype(np.float32)
+    yr = rng.uniform(0, 1, (100, 2)).astype(np.float32)
+    trajectory("traj_relu_6_5_4_2_mb7", [6, 5, 4, 2], ["relu", "relu", "linear"], "regression", xr, yr, 7, 0.01, 0.5,
+               3, {1, 3}, 0.5, 26, params=[0.0, 0.0, 1.0], wd1=0.001, wd2=[0.001, 0.002, 0.003])
+    xc, yc = gaussian_classes(rng, 40, 5, 3)
+    trajectory("traj_cls_5_6_7_3_mb3", [5, 6, 7, 3], ["tanh", "sigmoid", "sigmoid"], "classification", xc, yc, 3,
+               0.01, 0.3, 4, {1, 4}, 0.5, 27)
+    xm = rng.uniform(-1, 1, (20, 3)).astype(np.float32)
+    ym = rng.uniform(0, 1, (20, 2)).astype(np.float32)
+    trajectory("traj_mixed_acts_mb5", [3, 4, 4, 4, 2], ["leaky", "tanhp", "sigmoidp", "linear"], "regression", xm, ym,
+               5, 0.01, 0.2, 3, {1, 3}, 0.5, 28, params=[0.05, 0.1, 0.1, 0.7])
+
+    # ---- config 1 as written (lr 0.1): the reference goes non-finite; record the first such row
+    d = capi.make_desc([4, 16, 3], ["sigmoid", "sigmoid"], "classification", batch=1, lr=0.1, momentum=0.9)
+    rngw = np.random.default_rng(23)
+    w0 = rngw.uniform(-0.5, 0.5, 112).astype(np.float32)
+    b0 = rngw.uniform(-0.1, 0.1, 1).astype(np.float32)
+    R = o.Reference(d, x1, y1, capi.Metrics)
+    R.set_weights(w0, b0)
+    first_bad, last_good = -1, None
+    for step in range(150 * 3):
+        R.train_row(step % 150)
+        w, b = R.get_weights()
+        if not (np.isfinite(w).all() and np.isfinite(b).all()):
+            first_bad = step
+            break
+        last_good = (w.copy(), b.copy())
+    save("cfg1_lr01_nonfinite", dict(kind="nonfinite", sizes=[4, 16, 3], acts=["sigmoid", "sigmoid"],
+                                     out="classification", batch=1, lr=0.1, momentum=0.9, first_bad_step=first_bad),
+         x=x1, y=y1, w0=w0, b0=b0, w_last_good=last_good[0] if last_good else w0,
+         b_last_good=last_good[1] if last_good else b0)
+    print("cfg1 lr 0.1: first non-finite after training step", first_bad)
+
+    # ---- config 2, step level: rows 0..32 (windows {0} and {1..32}) from identical state, then the
+    # whole first epoch's metrics.  All 2^10 binary vectors in counting order, target = parity.
+    idx = np.arange(1024)
+    x2 = ((idx[:, None] >> np.arange(9, -1, -1)) & 1).astype(np.float32)
+    y2 = (x2.sum(1) % 2).astype(np.float32)[:, None]
+    d2 = capi.make_desc([10, 32, 32, 1], ["tanh", "tanh", "sigmoid"], "regression", batch=32, lr=0.05, momentum=0.0)
+    w0 = o.synth_fill(capi.weight_count(d2), SEED + 2, 2, 0, 2.0, -1.0)
+    R = o.Reference(d2, x2, y2, capi.Metrics)
+    R.set_weights(w0, None)
+    snaps_w, snaps_b = [], []
+    for r in range(33):
+        R.train_row(r)
+        if r in (0, 16, 32):
+            w, b = R.get_weights()
+            snaps_w.append(w)
+            snaps_b.append(b)
+    pend16 = None
+    R = o.Reference(d2, x2, y2, capi.Metrics)
+    R.set_weights(w0, None)
+    m, _, outp = R.epoch(0, True)
+    w_e1, b_e1 = R.get_weights()
+    save("cfg2_step", dict(kind="cfg2", sizes=[10, 32, 32, 1], acts=["tanh", "tanh", "sigmoid"], out="regression",
+                           batch=32, lr=0.05, momentum=0.0, seed=SEED + 2, stream=2, scale=2.0, offset=-1.0,
+                           snapshot_rows=[0, 16, 32]),
+         w_rows=np.array(snaps_w), b_rows=np.array(snaps_b), w_epoch1=w_e1, b_epoch1=b_e1,
+         metrics_epoch1=np.array([m.total_error, m.total_accuracy], np.float32), outputs_epoch1=outp)
+
+    # ---- C. forward-only parity on the wide shapes (sampled rows; weights from seed)
+    def forward_case(name, sizes, acts_native, n_rows, a_range, cfg, x_gen, params=None):
+        d = capi.make_desc(sizes, acts_native, "classification" if sizes[-1] > 1 else "regression", batch=1, lr=0.0,
+                           params=params)
+        nw = capi.weight_count(d)
+        w = o.synth_fill(nw, SEED + cfg, 2, 0, 2.0 * a_range, -a_range)
+        b = np.array([0.01 * (l + 1) for l in range(len(sizes) - 2)], np.float32)
+        x = x_gen(n_rows, sizes[0])
+        y = np.full((n_rows, sizes[-1]), 0.01, np.float32)
+        t = time.time()
+        R = o.Reference(d, x, y, capi.Metrics)
+        R.set_weights(w, b)
+        acts = np.stack([R.forward_row(r) for r in range(n_rows)])
+        R.close()
+        # the same net with a LINEAR (param 1.0) last layer exposes the last pre-activation z
+        acts_lin = list(acts_native[:-1]) + ["linear"]
+        p_lin = list(params) if params else [0.0] * (len(sizes) - 1)
+        p_lin[-1] = 1.0
+        dl = capi.make_desc(sizes, acts_lin, "regression", batch=1, lr=0.0, params=p_lin)
+        R = o.Reference(dl, x, y, capi.Metrics)
+        R.set_weights(w, b)
+        z_last = np.stack([R.forward_row(r)[-sizes[-1]:] for r in range(n_rows)])
+        R.close()
+        print("  %s: %d rows in %.1fs" % (name, n_rows, time.time() - t))
+        save(name, dict(kind="forward", sizes=sizes, acts=acts_native, params=params, seed=SEED + cfg, stream=2,
+                        scale=2.0 * a_range, offset=-a_range, bias=[float(v) for v in b]),
+             x=x, acts=acts, z_last=z_last)
+
+    rngx = np.random.default_rng(33)
+
+    def walk_windows(n, k):
+        steps = rngx.standard_normal(n + k + 1)
+        walk = np.cumsum(steps)
+        wins = np.stack([walk[i:i + k] for i in range(n)])
+        mu = wins.mean(1, keepdims=True)
+        sd = wins.std(1, keepdims=True)
+        return ((wins - mu) / sd).astype(np.float32)
+
+    forward_case("fwd_cfg3_32_256_256_1", [32, 256, 256, 1], ["relu", "relu", "linear"], 8, 1.0 / np.sqrt(32.0), 3,
+                 walk_windows, params=[0.0, 0.0, 1.0])
+    forward_case("fwd_cfg5_784_2048_2048_10", [784, 2048, 2048, 10], ["relu", "relu", "sigmoid"], 3, 0.05, 5,
+                 lambda n, k: rngx.uniform(0, 1, (n, k)).astype(np.float32))
+    if os.environ.get("GOLDEN_SKIP_CFG4") != "1":
+        forward_case("fwd_cfg4_1024_4096_4096_1024", [1024, 4096, 4096, 1024], ["relu", "relu", "sigmoid"], 2,
+                     1.0 / 32.0, 4, lambda n, k: rngx.standard_normal((n, k)).astype(np.float32))
+    print("done in %.1fs" % (time.time() - t0))
+
+
+if __name__ == "__main__":
+    main()
