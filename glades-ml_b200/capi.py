@@ -140,6 +140,10 @@ def lib():
         "gl_get_confusion": (C.c_int, [vp, vp]),
         "gl_get_epochs": (C.c_int, [vp]),
         "gl_stop": (None, [vp]),
+        "gl_sync": (C.c_int, [vp]),
+        "gl_kernel_launches": (i64, [vp]),
+        "gl_tensor_core_launches": (i64, [vp]),
+        "gl_matmul": (C.c_int, [vp, i64, i64, vp, i64, i64, vp, i64, i32, i32, i32, i32, i32]),
         "gl_shard_range": (None, [i64, i32, i32, C.POINTER(i64), C.POINTER(i64)]),
         "gl_dp_unique_id": (C.c_int, [vp]),
         "gl_dp_init": (C.c_int, [vp, i32, i32, vp]),
@@ -282,6 +286,15 @@ class Net:
 
     def stop(self):
         lib().gl_stop(self.h)
+
+    def sync(self):
+        _check(lib().gl_sync(self.h))
+
+    def kernel_launches(self):
+        return lib().gl_kernel_launches(self.h)
+
+    def tensor_core_launches(self):
+        return lib().gl_tensor_core_launches(self.h)
 
     def dp_init(self, rank, world, id_bytes):
         buf = (C.c_char * 128).from_buffer_copy(id_bytes)

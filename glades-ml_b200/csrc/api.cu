@@ -158,8 +158,17 @@ struct gl_net
 	int64_t winCap = 0;
 	float* hPinned = nullptr;
 	size_t pinnedBytes = 0;
-	// tensor-core path state (operand splits, transposes); opaque to this file
-	TcState* tc = nullptr;
+	// low TF32 parts of the tensor-core operands (X_lo = X - trunc_tf32(X)), made on demand
+	float* dXlo = nullptr;
+	float* dWlo = nullptr;
+	float* dAlo[GL_MAX_WEIGHT_LAYERS + 2] = {};
+	float* dDlo[GL_MAX_WEIGHT_LAYERS + 2] = {};
+	float* dDc = nullptr;     // momentum-weighted copy of one delta matrix and its low part
+	float* dDclo = nullptr;
+	bool loX = false, loW = false, loDc = false;
+	bool loA[GL_MAX_WEIGHT_LAYERS + 2] = {};
+	bool loD[GL_MAX_WEIGHT_LAYERS + 2] = {};
+	int64_t tcLaunches = 0;
 
 	int epochs = 0;
 	volatile int stop = 0;
@@ -168,6 +177,7 @@ struct gl_net
 	int rank = 0, world = 1;
 	nccl_comm comm = nullptr;
 	int globalRows = 0, firstPos = 0;
+	int bscaleRows = -1;
 };
 
 static NetView make_view(const gl_net* n)
@@ -279,6 +289,16 @@ static void free_work(gl_net* n)
 		if (n->dC[l]) cudaFree(n->dC[l]);
 		n->dC[l] = nullptr;
 	}
+	for (int l = 0; l <= GL_MAX_WEIGHT_LAYERS + 1; ++l)
+	{
+		if (n->dAlo[l]) cudaFree(n->dAlo[l]);
+		if (n->dDlo[l]) cudaFree(n->dDlo[l]);
+		n->dAlo[l] = n->dDlo[l] = nullptr;
+	}
+	if (n->dXlo) cudaFree(n->dXlo);
+	if (n->dDc) cudaFree(n->dDc);
+	if (n->dDclo) cudaFree(n->dDclo);
+	n->dXlo = n->dDc = n->dDclo = nullptr;
 	if (n->dArgmax) cudaFree(n->dArgmax);
 	n->dArgmax = nullptr;
 	n->capRows = 0;
@@ -291,8 +311,8 @@ extern "C" int gl_destroy(gl_net* n)
 	cudaSetDevice(n->d.device);
 	if (n->stream) cudaStreamSynchronize(n->stream);
 	if (n->comm && g_nccl.CommDestroy) g_nccl.CommDestroy(n->comm);
-	tc_destroy(n->tc);
 	free_work(n);
+	cudaFree(n->dWlo);
 	cudaFree(n->dW); cudaFree(n->dBias); cudaFree(n->dG); cudaFree(n->dBscale); cudaFree(n->dFlags);
 	cudaFree(n->dSums); cudaFree(n->dSumsF); cudaFree(n->dConf); cudaFree(n->dHist); cudaFree(n->dHistLen);
 	cudaFree(n->dScratch); cudaFree(n->ownX); cudaFree(n->ownY); cudaFree(n->dColterm);
@@ -350,7 +370,7 @@ extern "C" int gl_set_weights(gl_net* n, const float* w, const float* bias)
 	}
 	CU(cudaMemsetAsync(n->dFlags, 0, 4 * sizeof(int), n->stream));
 	CU(cudaStreamSynchronize(n->stream));
-	if (n->tc) tc_weights_changed(n->tc);
+	n->loW = false;
 	return GL_OK;
 }
 
@@ -499,6 +519,20 @@ static int ensure_work(gl_net* n, int64_t rows)
 		if (n->d.mode == GL_MODE_BATCHED) CU(cudaMalloc(&n->dD[l], (size_t)rows * n->d.sizes[l] * sizeof(float)));
 	}
 	CU(cudaMalloc(&n->dArgmax, (size_t)rows * sizeof(int)));
+	if (n->d.mode == GL_MODE_BATCHED && n->d.gemm != GL_GEMM_FFMA)
+	{
+		int maxn = 1;
+		for (int l = 0; l <= n->H + 1; ++l) maxn = n->d.sizes[l] > maxn ? n->d.sizes[l] : maxn;
+		CU(cudaMalloc(&n->dXlo, (size_t)rows * n->d.sizes[0] * sizeof(float)));
+		for (int l = 1; l <= n->H + 1; ++l)
+		{
+			CU(cudaMalloc(&n->dAlo[l], (size_t)rows * n->d.sizes[l] * sizeof(float)));
+			CU(cudaMalloc(&n->dDlo[l], (size_t)rows * n->d.sizes[l] * sizeof(float)));
+		}
+		CU(cudaMalloc(&n->dDc, (size_t)rows * maxn * sizeof(float)));
+		CU(cudaMalloc(&n->dDclo, (size_t)rows * maxn * sizeof(float)));
+		if (!n->dWlo) CU(cudaMalloc(&n->dWlo, (size_t)(n->nw + 4) * sizeof(float)));
+	}
 	n->capRows = rows;
 	return 0;
 }
@@ -538,23 +572,89 @@ static int set_momentum_weights(gl_net* n, int rows, int global_rows, int first_
 	return 0;
 }
 
-static bool want_tc(const gl_net* n, int rows)
+// One operand of a layer product: the fp32 matrix it is a slice of, the buffer for that matrix's low
+// TF32 part with the flag that says whether it is current, and the slice of the low part to use.
+struct Operand
 {
-	if (n->d.gemm == GL_GEMM_FFMA) return false;
-	return tc_shapes_ok(n->d, rows, n->d.gemm == GL_GEMM_TCGEN05);
+	const float* src_all;
+	float* lo_all;
+	bool* valid;
+	long long count_all;
+	const float* lo_use;
+};
+
+// Runs one layer product on the tensor-core kernel when its shape fits (and the network allows it),
+// else on the exact-fp32 FFMA kernel.
+static int run_gemm(gl_net* n, GemmArgs g, Operand a, Operand b, int64_t* launches)
+{
+	bool tc = false;
+	if (n->d.gemm != GL_GEMM_FFMA && a.lo_all && b.lo_all)
+	{
+		GemmArgs probe = g;
+		probe.kscale = nullptr;  // a per-k scale is folded into a scaled operand copy below
+		tc = tc_gemm_supported(probe) &&
+		     (n->d.gemm == GL_GEMM_TCGEN05 || (long long)g.M * g.N * g.K >= (1ll << 24));
+	}
+	if (!tc)
+	{
+		CU(launch_gemm_ffma(g, n->stream));
+		++*launches;
+		return 0;
+	}
+	if (g.kscale)
+	{
+		// momentum weights: A(m,k) * c_k becomes a scaled copy of the delta matrix (rows = k)
+		CU(launch_scale_split_lo(g.A, g.kscale, (int)g.a_sk, n->dDc, n->dDclo, (long long)g.M * g.K, n->stream));
+		++*launches;
+		g.A = n->dDc;
+		a.lo_use = n->dDclo;
+		g.kscale = nullptr;
+	}
+	else if (!*a.valid)
+	{
+		CU(launch_split_lo(a.src_all, a.lo_all, a.count_all, n->stream));
+		++*launches;
+		*a.valid = true;
+	}
+	if (!*b.valid)
+	{
+		CU(launch_split_lo(b.src_all, b.lo_all, b.count_all, n->stream));
+		++*launches;
+		*b.valid = true;
+	}
+	CU(launch_gemm_tc(g, a.lo_use, b.lo_use, n->dFlags + 1, n->stream));
+	++*launches;
+	++n->tcLaunches;
+	return 0;
+}
+
+// all weight layers share one flat low-part buffer and one flag: it is refreshed as a whole
+static Operand op_w(gl_net* n, int l)
+{
+	Operand o = {n->dW, n->dWlo, &n->loW, ((n->nw + 3) / 4) * 4, n->dWlo ? n->dWlo + n->woff[l] : nullptr};
+	return o;
+}
+static Operand op_act(gl_net* n, int l, const float* X, int rows)
+{
+	if (l == 0)
+	{
+		Operand o = {X, n->dXlo, &n->loX, (long long)rows * n->d.sizes[0], n->dXlo};
+		return o;
+	}
+	Operand o = {n->dA[l], n->dAlo[l], &n->loA[l], (long long)rows * n->d.sizes[l], n->dAlo[l]};
+	return o;
+}
+static Operand op_delta(gl_net* n, int L, int rows)
+{
+	Operand o = {n->dD[L], n->dDlo[L], &n->loD[L], (long long)rows * n->d.sizes[L], n->dDlo[L]};
+	return o;
 }
 
 // Forward of `rows` rows starting at device pointer X; activations land in dA[1..H+1].
 static int batched_forward(gl_net* n, const float* X, int rows, int64_t* launches)
 {
-	if (want_tc(n, rows))
-	{
-		if (!n->tc) n->tc = tc_create(n->d, n->dW, n->dBias, n->stream);
-		cudaError_t e = tc_forward(n->tc, X, rows, n->dA, launches);
-		if (e != cudaSuccess) return fail(GL_ERR_CUDA, "tensor-core forward failed: %s", cudaGetErrorString(e));
-		return 0;
-	}
 	const float* in = X;
+	n->loX = false;
 	for (int l = 0; l <= n->H; ++l)
 	{
 		GemmArgs g;
@@ -572,8 +672,8 @@ static int batched_forward(gl_net* n, const float* X, int rows, int64_t* launche
 		g.bias_ptr = (l >= 1) ? n->dBias + l : nullptr;
 		g.act = n->d.activation[l];
 		g.par = n->d.act_param[l];
-		CU(launch_gemm_ffma(g, n->stream));
-		++*launches;
+		n->loA[l + 1] = false;
+		if (int r = run_gemm(n, g, op_act(n, l, X, rows), op_w(n, l), launches)) return r;
 		in = n->dA[l + 1];
 	}
 	return 0;
@@ -586,7 +686,6 @@ static int batched_window(gl_net* n, const float* X, const float* Y, int rows, i
 	const int first_pos = (n->world > 1) ? n->firstPos : 0;
 	if (int r = set_momentum_weights(n, rows, global_rows, first_pos)) return r;
 	int64_t launches = 0;
-	const bool tc = want_tc(n, rows);
 	CU(cudaEventRecord(n->ev0, n->stream));
 	CU(cudaMemsetAsync(n->dSums, 0, 2 * sizeof(double), n->stream));
 	CU(cudaMemsetAsync(n->dG + n->nw, 0, GL_MAX_WEIGHT_LAYERS * sizeof(float), n->stream));
@@ -606,34 +705,29 @@ static int batched_window(gl_net* n, const float* X, const float* Y, int rows, i
 	h.confusion = (n->d.output_type != GL_OUT_REGRESSION) ? n->dConf : nullptr;
 	CU(launch_head(h, n->stream));
 	++launches;
+	n->loD[n->H + 1] = false;
+	n->loA[n->H + 1] = false;  // the softmax head rewrote the last activations in place
 
-	if (tc)
-	{
-		cudaError_t e = tc_backward(n->tc, X, rows, n->dA, n->dD, n->dC, n->dG, &launches);
-		if (e != cudaSuccess) return fail(GL_ERR_CUDA, "tensor-core backward failed: %s", cudaGetErrorString(e));
-	}
 	for (int L = n->H + 1; L >= 1; --L)
 	{
 		const int l = L - 1;
 		const int ni = n->d.sizes[l], no = n->d.sizes[L];
 		const float* Al = (l == 0) ? X : n->dA[l];
-		if (!tc)
+		const Operand opD = op_delta(n, L, rows);
+		if (l >= 1)
 		{
-			if (l >= 1)
-			{
-				GemmArgs g;
-				memset(&g, 0, sizeof g);
-				g.A = n->dD[L]; g.a_sm = no; g.a_sk = 1;
-				g.B = n->dW + n->woff[l]; g.b_sn = 1; g.b_sk = ni;
-				g.C = n->dD[l]; g.ldc = ni;
-				g.M = rows; g.N = ni; g.K = no;
-				g.epi = EPI_ERRPROP;
-				g.aux = n->dA[l]; g.ld_aux = ni;
-				g.act = n->d.activation[l - 1];
-				g.par = 0.01f;  // the reference passes a fixed 0.01, network.cpp:618
-				CU(launch_gemm_ffma(g, n->stream));
-				++launches;
-			}
+			GemmArgs g;
+			memset(&g, 0, sizeof g);
+			g.A = n->dD[L]; g.a_sm = no; g.a_sk = 1;
+			g.B = n->dW + n->woff[l]; g.b_sn = 1; g.b_sk = ni;
+			g.C = n->dD[l]; g.ldc = ni;
+			g.M = rows; g.N = ni; g.K = no;
+			g.epi = EPI_ERRPROP;
+			g.aux = n->dA[l]; g.ld_aux = ni;
+			g.act = n->d.activation[l - 1];
+			g.par = 0.01f;  // the reference passes a fixed 0.01, network.cpp:618
+			n->loD[l] = false;
+			if (int r = run_gemm(n, g, opD, op_w(n, l), &launches)) return r;
 		}
 		const float* colterm = nullptr;
 		if (n->d.wd1[l] != 0.0f || n->d.wd2[l] != 0.0f)
@@ -641,9 +735,7 @@ static int batched_window(gl_net* n, const float* X, const float* Y, int rows, i
 			CU(launch_decay_colterm(Al, rows, ni, n->dC[l], n->d.lr[l], n->d.wd1[l], n->d.wd2[l], n->dColterm, n->stream));
 			++launches;
 			colterm = n->dColterm;
-			if (tc) return fail(GL_ERR_STATE, "weight decay is not wired into the tensor-core gradient epilogue");
 		}
-		if (!tc)
 		{
 			GemmArgs g;
 			memset(&g, 0, sizeof g);
@@ -655,8 +747,7 @@ static int batched_window(gl_net* n, const float* X, const float* Y, int rows, i
 			g.epi = EPI_GRAD;
 			g.alpha = n->d.lr[l];
 			g.colterm = colterm;
-			CU(launch_gemm_ffma(g, n->stream));
-			++launches;
+			if (int r = run_gemm(n, g, opD, op_act(n, l, X, rows), &launches)) return r;
 		}
 		if (l >= 1)
 		{
@@ -671,18 +762,19 @@ static int batched_window(gl_net* n, const float* X, const float* Y, int rows, i
 		NC(g_nccl.AllReduce(n->dSums, n->dSums, 2, NCCL_FLOAT64, NCCL_SUM, n->comm, n->stream));
 		NC(g_nccl.GroupEnd());
 	}
-	float bscale[GL_MAX_WEIGHT_LAYERS] = {0};
-	for (int l = 1; l <= n->H; ++l)
-		bscale[l] = (n->d.bias_rule == GL_BIAS_REFERENCE) ? (float)n->d.sizes[l] : 1.0f / (float)global_rows;
-	CU(cudaMemcpyAsync(n->dBscale, bscale, sizeof bscale, cudaMemcpyHostToDevice, n->stream));
+	if (n->bscaleRows != global_rows)
+	{
+		float bscale[GL_MAX_WEIGHT_LAYERS] = {0};
+		for (int l = 1; l <= n->H; ++l)
+			bscale[l] = (n->d.bias_rule == GL_BIAS_REFERENCE) ? (float)n->d.sizes[l] : 1.0f / (float)global_rows;
+		CU(cudaMemcpyAsync(n->dBscale, bscale, sizeof bscale, cudaMemcpyHostToDevice, n->stream));
+		CU(cudaStreamSynchronize(n->stream));
+		n->bscaleRows = global_rows;
+	}
 	CU(launch_update(n->dW, n->dG, n->nw, 1.0f / (float)global_rows, n->dBias, n->dG + n->nw, n->dBscale, n->H,
 	                 n->dFlags, n->stream));
 	++launches;
-	if (tc)
-	{
-		cudaError_t e = tc_after_update(n->tc, &launches);
-		if (e != cudaSuccess) return fail(GL_ERR_CUDA, "tensor-core operand refresh failed: %s", cudaGetErrorString(e));
-	}
+	n->loW = false;
 	CU(cudaEventRecord(n->ev1, n->stream));
 	n->launches += launches;
 	if (out)
@@ -702,6 +794,7 @@ static int batched_window(gl_net* n, const float* X, const float* Y, int rows, i
 		int flags[4];
 		CU(cudaMemcpy(flags, n->dFlags, sizeof flags, cudaMemcpyDeviceToHost));
 		out->nonfinite = flags[0] & 1;
+		if (flags[1]) return fail(GL_ERR_TIMEOUT, "a bounded wait inside the tensor-core kernel ran out (role %d)", flags[1]);
 	}
 	return GL_OK;
 }
@@ -1006,6 +1099,63 @@ extern "C" int gl_dp_set_window(gl_net* n, int32_t global_rows, int32_t first_gl
 	if (!n || global_rows < 1 || first_global_pos < 0) return fail(GL_ERR_INVALID, "gl_dp_set_window: bad argument");
 	n->globalRows = global_rows;
 	n->firstPos = first_global_pos;
+	return GL_OK;
+}
+
+extern "C" int64_t gl_tensor_core_launches(const gl_net* n) { return n ? n->tcLaunches : 0; }
+extern "C" int64_t gl_kernel_launches(const gl_net* n) { return n ? n->launches : 0; }
+
+extern "C" int gl_sync(gl_net* n)
+{
+	if (!n) return fail(GL_ERR_INVALID, "gl_sync: null handle");
+	if (int r = use_device(n)) return r;
+	CU(cudaStreamSynchronize(n->stream));
+	int flags[4];
+	CU(cudaMemcpy(flags, n->dFlags, sizeof flags, cudaMemcpyDeviceToHost));
+	if (flags[1]) return fail(GL_ERR_TIMEOUT, "a bounded wait inside the tensor-core kernel ran out (role %d)", flags[1]);
+	return GL_OK;
+}
+
+// Diagnostic matrix product on device buffers: C[m][n] = sum_k A(m,k) * B(n,k) with
+// A(m,k) = dA[m*a_sm + k*a_sk], B(n,k) = dB[n*b_sn + k*b_sk].
+extern "C" int gl_matmul(const float* dA, int64_t a_sm, int64_t a_sk, const float* dB, int64_t b_sn, int64_t b_sk, float* dC,
+                         int64_t ldc, int32_t M, int32_t N, int32_t K, int32_t engine, int32_t device)
+{
+	if (!dA || !dB || !dC || M < 1 || N < 1 || K < 1) return fail(GL_ERR_INVALID, "gl_matmul: bad argument");
+	if (gl_device_count() < 1) return fail(GL_ERR_NO_DEVICE, "no sm_100 CUDA device");
+	CU(cudaSetDevice(device));
+	GemmArgs g;
+	memset(&g, 0, sizeof g);
+	g.A = dA; g.a_sm = a_sm; g.a_sk = a_sk;
+	g.B = dB; g.b_sn = b_sn; g.b_sk = b_sk;
+	g.C = dC; g.ldc = ldc;
+	g.M = M; g.N = N; g.K = K;
+	g.epi = EPI_NONE;
+	if (engine == GL_GEMM_FFMA)
+	{
+		CU(launch_gemm_ffma(g, 0));
+		CU(cudaDeviceSynchronize());
+		return GL_OK;
+	}
+	if (!tc_gemm_supported(g)) return fail(GL_ERR_INVALID, "gl_matmul: shape or strides do not fit the tensor-core tiles");
+	// extents of the two operand allocations, from their strides
+	const long long ca = (a_sk == 1) ? (long long)(M - 1) * a_sm + K : (long long)(K - 1) * a_sk + M;
+	const long long cb = (b_sk == 1) ? (long long)(N - 1) * b_sn + K : (long long)(K - 1) * b_sk + N;
+	float *alo = nullptr, *blo = nullptr;
+	int* flag = nullptr;
+	CU(cudaMalloc(&alo, (size_t)(ca + 4) * sizeof(float)));
+	CU(cudaMalloc(&blo, (size_t)(cb + 4) * sizeof(float)));
+	CU(cudaMalloc(&flag, sizeof(int)));
+	CU(cudaMemset(flag, 0, sizeof(int)));
+	cudaError_t e = launch_split_lo(dA, alo, (ca / 4) * 4, 0);
+	if (e == cudaSuccess) e = launch_split_lo(dB, blo, (cb / 4) * 4, 0);
+	if (e == cudaSuccess) e = launch_gemm_tc(g, alo, blo, flag, 0);
+	if (e == cudaSuccess) e = cudaDeviceSynchronize();
+	int hflag = 0;
+	if (e == cudaSuccess) e = cudaMemcpy(&hflag, flag, sizeof hflag, cudaMemcpyDeviceToHost);
+	cudaFree(alo); cudaFree(blo); cudaFree(flag);
+	if (e != cudaSuccess) return fail(GL_ERR_CUDA, "gl_matmul: %s", cudaGetErrorString(e));
+	if (hflag) return fail(GL_ERR_TIMEOUT, "gl_matmul: a bounded wait inside the tensor-core kernel ran out (role %d)", hflag);
 	return GL_OK;
 }
 

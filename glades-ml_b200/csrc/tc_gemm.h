@@ -1,27 +1,27 @@
-// Interface between the C-ABI layer and the tensor-core (TMA + tcgen05, 3xTF32) batched path.
+// Tensor-core matrix product of batched mode: TMA-fed tcgen05.mma (kind::tf32) with the operands
+// split into a high and a low TF32 part ("3xTF32"), fp32 accumulation in tensor memory.
 #pragma once
 #include <cuda_runtime.h>
 #include <stdint.h>
 
-#include "glades_b200.h"
+#include "internal.h"
 
 namespace glb {
 
-struct TcState;
+// Tile constraints of the kernel: M % 128 == 0, N % 128 == 0, K % 32 == 0, every operand either
+// K-contiguous or M/N-contiguous with 16-byte aligned rows, no per-k scale vector.
+bool tc_gemm_supported(const GemmArgs& g);
 
-// True when every matrix product of a `rows`-row window of this network fits the tensor-core
-// kernel's tiles (and, unless forced, is large enough to be worth it).
-bool tc_shapes_ok(const gl_net_desc& d, int rows, bool forced);
-TcState* tc_create(const gl_net_desc& d, float* dW, float* dBias, cudaStream_t s);
-void tc_destroy(TcState* t);
-// The fp32 master weights were overwritten from outside: the split operand copies are stale.
-void tc_weights_changed(TcState* t);
-// A_{l+1} = squash(A_l W_l^T + b_l) for l = 0..H; fp32 activations land in dA[1..H+1].
-cudaError_t tc_forward(TcState* t, const float* X, int rows, float* const* dA, int64_t* launches);
-// Given the output delta dD[H+1]: D_l for l = H..1 and the flat gradient dG (already scaled by lr).
-cudaError_t tc_backward(TcState* t, const float* X, int rows, float* const* dA, float* const* dD, float* const* dC,
-                        float* dG, int64_t* launches);
-// Re-derive the split / transposed operand copies from the updated fp32 weights.
-cudaError_t tc_after_update(TcState* t, int64_t* launches);
+// C = epilogue(A * B^T) with A ~ A + A_lo and B ~ B + B_lo, where X_lo = X - trunc_tf32(X) (see
+// launch_split_lo).  Three tensor-core products per k-step: A*B_lo, A_lo*B, A*B; the tensor core
+// reads only the upper 19 bits of each fp32 operand word, so passing X itself supplies trunc_tf32(X).
+// err_flag: device int, set non-zero if a bounded wait inside the kernel ran out.
+cudaError_t launch_gemm_tc(const GemmArgs& g, const float* A_lo, const float* B_lo, int* err_flag, cudaStream_t s);
+
+// lo[i] = tf32_round(src[i] - trunc_tf32(src[i])); with rowscale: first dst_scaled[i] = src[i] *
+// rowscale[i / ld] is formed (and stored), and lo is taken from that.
+cudaError_t launch_split_lo(const float* src, float* lo, long long count, cudaStream_t s);
+cudaError_t launch_scale_split_lo(const float* src, const float* rowscale, int ld, float* dst_scaled, float* lo,
+                                  long long count, cudaStream_t s);
 
 }  // namespace glb

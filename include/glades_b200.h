@@ -52,8 +52,8 @@ enum { GL_MODE_REFERENCE = 0, GL_MODE_BATCHED = 1 };
 enum { GL_BIAS_MEAN = 0, GL_BIAS_REFERENCE = 1 };
 
 /* Matrix-product engine for batched mode: GL_GEMM_AUTO picks by shape; GL_GEMM_FFMA forces the
- * exact-fp32 FFMA tile kernel; GL_GEMM_TCGEN05 forces the TMA + tcgen05 3xTF32 kernel (shapes
- * must then be multiples of its tile). */
+ * exact-fp32 FFMA tile kernel; GL_GEMM_TCGEN05 uses the TMA + tcgen05 3xTF32 kernel for every
+ * product whose shape fits its tiles, however small (AUTO leaves small products on FFMA). */
 enum { GL_GEMM_AUTO = 0, GL_GEMM_FFMA = 1, GL_GEMM_TCGEN05 = 2 };
 
 typedef enum gl_status {
@@ -169,6 +169,21 @@ int gl_get_pending_delta(gl_net* net, int32_t k, float* out);
 int gl_get_confusion(gl_net* net, int32_t* out);
 /* Epoch counter, NNetwork::getEpochs. */
 int gl_get_epochs(const gl_net* net);
+
+/* Waits for the handle's queued device work (gl_train_window with out == NULL returns before the
+ * device has finished) and reports a tensor-core kernel whose bounded wait ran out. */
+int gl_sync(gl_net* net);
+/* Diagnostics: kernels launched by this handle so far, and how many of them were tensor-core
+ * (tcgen05) products.  No counterpart in the reference. */
+int64_t gl_kernel_launches(const gl_net* net);
+int64_t gl_tensor_core_launches(const gl_net* net);
+/* Diagnostic matrix product on device buffers, C[m][n] = sum_k A(m,k)*B(n,k) with
+ * A(m,k) = d_a[m*a_sm + k*a_sk] and B(n,k) = d_b[n*b_sn + k*b_sk]; engine GL_GEMM_FFMA or
+ * GL_GEMM_TCGEN05 (M % 128 == 0, N % 128 == 0, K % 32 == 0, each operand contiguous in k or in
+ * m/n).  It exposes the layer-product kernels of the path for numerical tests; the reference has
+ * no matrix product (it walks edges, network.cpp:461-508). */
+int gl_matmul(const float* d_a, int64_t a_sm, int64_t a_sk, const float* d_b, int64_t b_sn, int64_t b_sk, float* d_c,
+              int64_t ldc, int32_t m, int32_t n, int32_t k, int32_t engine, int32_t device);
 
 /* Replaces NNetwork::stop (network.cpp:99-102): async-signal-safe; the flag is looked at between
  * epochs of gl_train_epochs. */

@@ -1,0 +1,100 @@
+"""GPU tests of the tensor-core (TMA + tcgen05, 3xTF32) layer product, through the C ABI.
+
+Tolerance: the 3xTF32 split keeps about 21 mantissa bits per operand and accumulates in fp32, so
+each output must agree with a float64 product within 4e-6 * sum_k |a_mk||b_nk| (the fp32 tolerance
+1e-5 of the task with margin; plain TF32 would be ~1e-3 and fail)."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+def _dev(L, a):
+    p = C.c_void_p()
+    assert L.gl_device_alloc(C.byref(p), a.nbytes + 64, 0) == 0
+    assert L.gl_memcpy_h2d(p, a.ctypes.data_as(C.c_void_p), a.nbytes, 0) == 0
+    return p
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(0, 0), (0, 1), (1, 1), (1, 0)])
+@pytest.mark.parametrize("M,N,K", [(128, 128, 32), (256, 256, 64), (128, 384, 96), (384, 256, 160), (256, 512, 1024)])
+def test_tc_matmul_all_layouts(g, a_mn, b_mn, M, N, K):
+    L = g.lib()
+    rng = np.random.default_rng(M + 3 * N + 7 * K + a_mn + 2 * b_mn)
+    A = rng.standard_normal((M, K)).astype(np.float32)   # logical A(m,k)
+    B = rng.standard_normal((N, K)).astype(np.float32)   # logical B(n,k)
+    A_mem = np.ascontiguousarray(A.T) if a_mn else A      # MN-major: stored [k][m]
+    B_mem = np.ascontiguousarray(B.T) if b_mn else B
+    a_sm, a_sk = (1, M) if a_mn else (K, 1)
+    b_sn, b_sk = (1, N) if b_mn else (K, 1)
+    dA, dB = _dev(L, A_mem), _dev(L, B_mem)
+    out = np.zeros((M, N), np.float32)
+    dC = _dev(L, out)
+    ref = A.astype(np.float64) @ B.astype(np.float64).T
+    bound = np.abs(A).astype(np.float64) @ np.abs(B).astype(np.float64).T
+    for engine in (g.GEMM_TCGEN05, g.GEMM_FFMA):
+        st = L.gl_matmul(dA, a_sm, a_sk, dB, b_sn, b_sk, dC, N, M, N, K, engine, 0)
+        assert st == 0, L.gl_last_error()
+        assert L.gl_memcpy_d2h(out.ctypes.data_as(C.c_void_p), dC, out.nbytes, 0) == 0
+        err = float(np.max(np.abs(out.astype(np.float64) - ref) / bound))
+        assert err <= 4e-6, "engine %d: error %.3g of sum|a||b|" % (engine, err)
+    for p in (dA, dB, dC):
+        L.gl_device_free(p, 0)
+
+
+def test_tc_matmul_rejects_odd_shapes(g):
+    L = g.lib()
+    a = np.zeros((100, 32), np.float32)
+    dA, dB, dC = _dev(L, a), _dev(L, a), _dev(L, np.zeros((100, 100), np.float32))
+    assert L.gl_matmul(dA, 32, 1, dB, 32, 1, dC, 100, 100, 100, 32, g.GEMM_TCGEN05, 0) != 0
+    assert L.gl_matmul(dA, 32, 1, dB, 32, 1, dC, 100, 100, 100, 32, g.GEMM_FFMA, 0) == 0
+    for p in (dA, dB, dC):
+        L.gl_device_free(p, 0)
+
+
+@pytest.mark.parametrize("momentum,head", [(0.0, "softmax"), (0.9, "sigmoid")])
+def test_batched_window_on_tensor_cores_vs_restatement(g, oracle, momentum, head):
+    """A whole window step (forward, error propagation, weight gradient, update) with every layer
+    product on the tcgen05 kernel, against the double-accumulating CPU restatement."""
+    rng = np.random.default_rng(17)
+    sizes = [128, 256, 384, 128]
+    rows = 256
+    out_type = "classification"
+    d = g.make_desc(sizes, ["relu", "tanh", head], out_type, batch=rows, lr=0.05, momentum=momentum,
+                    mode=g.MODE_BATCHED, gemm=g.GEMM_TCGEN05)
+    x = rng.standard_normal((rows, sizes[0])).astype(np.float32)
+    if head == "softmax":
+        y = np.zeros((rows, sizes[-1]), np.float32)
+        y[np.arange(rows), rng.integers(0, sizes[-1], rows)] = 1.0
+    else:
+        y = rng.uniform(0.05, 0.95, (rows, sizes[-1])).astype(np.float32)
+    nw = sum(sizes[i] * sizes[i + 1] for i in range(3))
+    w = (rng.standard_normal(nw) * 0.05).astype(np.float32)
+    b = np.array([0.02, -0.03], np.float32)
+    net = g.Net(d)
+    net.set_weights(w, b)
+    net.set_data(x, y)
+    S = oracle.Restate(d, x, y, g.Metrics)
+    S.set_weights(w, b)
+    for step in range(2):
+        m = net.train_window(0, rows)
+        gr = S.window_grad(0, rows)
+        S.window_apply(gr, rows)
+        wg, bg = net.get_weights()
+        ws, bs = S.get_weights()
+        err = float(np.max(np.abs(wg.astype(np.float64) - ws)) / np.max(np.abs(ws)))
+        assert err <= 1e-5, "step %d: weights rel err %g" % (step, err)
+        assert np.allclose(bg, bs, rtol=1e-4, atol=1e-6)
+        assert abs(m.total_error - gr[-2]) <= 1e-5 * max(1.0, abs(gr[-2]))
+    # 3 forward + 2 error-propagation + 3 gradient products per step, all on tensor cores
+    assert net.tensor_core_launches() == 16
+    # inference from identical weights (the two sides' weights differ by the step tolerance above)
+    wg, bg = net.get_weights()
+    S.set_weights(wg, bg)
+    out_g, am_g, _ = net.forward(0, rows)
+    out_s, am_s = S.forward_block(0, rows)
+    assert np.max(np.abs(out_g - out_s)) <= 1e-5 * max(1.0, float(np.max(np.abs(out_s))))
+    assert np.array_equal(am_g, am_s)
+    net.close()
