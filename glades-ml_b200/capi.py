@@ -149,6 +149,11 @@ def lib():
         "gl_dp_init": (C.c_int, [vp, i32, i32, vp]),
         "gl_dp_set_window": (C.c_int, [vp, i32, i32]),
         "gl_synth_fill": (C.c_int, [vp, i64, u64, u32, i32, f32, f32, i32]),
+        "gl_onehot_fill": (C.c_int, [vp, vp, i64, i32, f32, f32, i32]),
+        "gl_timer_start": (C.c_int, [vp]),
+        "gl_timer_stop": (C.c_int, [vp, C.POINTER(C.c_double)]),
+        "gl_profile_enable": (C.c_int, [vp, i32]),
+        "gl_profile_read": (C.c_int, [vp, C.POINTER(C.c_double)]),
         "gl_device_alloc": (C.c_int, [C.POINTER(vp), i64, i32]),
         "gl_device_free": (C.c_int, [vp, i32]),
         "gl_memcpy_h2d": (C.c_int, [vp, vp, i64, i32]),
@@ -230,14 +235,18 @@ class Net:
         _check(lib().gl_set_data(self.h, _ptr(x), _ptr(y), rows))
 
     def set_data_device(self, d_x, d_y, rows):
-        _check(lib().gl_set_data_device(self.h, C.c_void_p(d_x), C.c_void_p(d_y), rows))
+        _check(lib().gl_set_data_device(self.h, C.c_void_p(d_x), C.c_void_p(d_y) if d_y else None, rows))
 
     def train_epochs(self, n):
         m = Metrics()
         _check(lib().gl_train_epochs(self.h, n, C.byref(m)))
         return m
 
-    def train_window(self, first_row, rows):
+    def train_window(self, first_row, rows, want_metrics=True):
+        """One window step; with want_metrics=False the call only queues the work (see sync())."""
+        if not want_metrics:
+            _check(lib().gl_train_window(self.h, first_row, rows, None))
+            return None
         m = Metrics()
         _check(lib().gl_train_window(self.h, first_row, rows, C.byref(m)))
         return m
@@ -289,6 +298,23 @@ class Net:
 
     def sync(self):
         _check(lib().gl_sync(self.h))
+
+    def timer_start(self):
+        _check(lib().gl_timer_start(self.h))
+
+    def timer_stop(self):
+        ms = C.c_double()
+        _check(lib().gl_timer_stop(self.h, C.byref(ms)))
+        return ms.value
+
+    def profile_enable(self, on=True):
+        _check(lib().gl_profile_enable(self.h, 1 if on else 0))
+
+    def profile_read(self):
+        out = (C.c_double * 6)()
+        _check(lib().gl_profile_read(self.h, out))
+        return {"tc": {"launches": int(out[0]), "ms": out[1], "flop": out[2]},
+                "ffma": {"launches": int(out[3]), "ms": out[4], "flop": out[5]}}
 
     def kernel_launches(self):
         return lib().gl_kernel_launches(self.h)

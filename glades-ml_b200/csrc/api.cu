@@ -169,6 +169,13 @@ struct gl_net
 	bool loA[GL_MAX_WEIGHT_LAYERS + 2] = {};
 	bool loD[GL_MAX_WEIGHT_LAYERS + 2] = {};
 	int64_t tcLaunches = 0;
+	// optional per-launch timing of the layer products (gl_profile_enable)
+	bool profile = false;
+	std::vector<cudaEvent_t> profEv;   // pairs
+	std::vector<double> profFlops;
+	std::vector<int> profIsTc;
+	size_t profUsed = 0;
+	cudaEvent_t tim0 = nullptr, tim1 = nullptr;
 
 	int epochs = 0;
 	volatile int stop = 0;
@@ -318,6 +325,9 @@ extern "C" int gl_destroy(gl_net* n)
 	cudaFree(n->dScratch); cudaFree(n->ownX); cudaFree(n->ownY); cudaFree(n->dColterm);
 	cudaFree(n->dXwin); cudaFree(n->dYwin);
 	if (n->hPinned) cudaFreeHost(n->hPinned);
+	for (cudaEvent_t e : n->profEv) cudaEventDestroy(e);
+	if (n->tim0) cudaEventDestroy(n->tim0);
+	if (n->tim1) cudaEventDestroy(n->tim1);
 	if (n->ev0) cudaEventDestroy(n->ev0);
 	if (n->ev1) cudaEventDestroy(n->ev1);
 	if (n->stream) cudaStreamDestroy(n->stream);
@@ -409,7 +419,7 @@ extern "C" int gl_set_data(gl_net* n, const float* x, const float* y, int64_t ro
 
 extern "C" int gl_set_data_device(gl_net* n, const float* dx, const float* dy, int64_t rows)
 {
-	if (!n || !dx || !dy || rows < 1) return fail(GL_ERR_INVALID, "gl_set_data_device: bad argument");
+	if (!n || !dx || rows < 1) return fail(GL_ERR_INVALID, "gl_set_data_device: bad argument");
 	n->dX = dx;
 	n->dY = dy;
 	n->rows = rows;
@@ -595,9 +605,28 @@ static int run_gemm(gl_net* n, GemmArgs g, Operand a, Operand b, int64_t* launch
 		tc = tc_gemm_supported(probe) &&
 		     (n->d.gemm == GL_GEMM_TCGEN05 || (long long)g.M * g.N * g.K >= (1ll << 24));
 	}
+	cudaEvent_t pe0 = nullptr, pe1 = nullptr;
+	if (n->profile)
+	{
+		if (n->profUsed + 2 > n->profEv.size())
+		{
+			cudaEvent_t a, b;
+			CU(cudaEventCreate(&a));
+			CU(cudaEventCreate(&b));
+			n->profEv.push_back(a);
+			n->profEv.push_back(b);
+		}
+		pe0 = n->profEv[n->profUsed];
+		pe1 = n->profEv[n->profUsed + 1];
+		n->profUsed += 2;
+		n->profFlops.push_back(2.0 * (double)g.M * (double)g.N * (double)g.K);
+		n->profIsTc.push_back(tc ? 1 : 0);
+	}
 	if (!tc)
 	{
+		if (pe0) CU(cudaEventRecord(pe0, n->stream));
 		CU(launch_gemm_ffma(g, n->stream));
+		if (pe1) CU(cudaEventRecord(pe1, n->stream));
 		++*launches;
 		return 0;
 	}
@@ -622,7 +651,9 @@ static int run_gemm(gl_net* n, GemmArgs g, Operand a, Operand b, int64_t* launch
 		++*launches;
 		*b.valid = true;
 	}
+	if (pe0) CU(cudaEventRecord(pe0, n->stream));
 	CU(launch_gemm_tc(g, a.lo_use, b.lo_use, n->dFlags + 1, n->stream));
+	if (pe1) CU(cudaEventRecord(pe1, n->stream));
 	++*launches;
 	++n->tcLaunches;
 	return 0;
@@ -803,7 +834,7 @@ extern "C" int gl_train_window(gl_net* n, int64_t first_row, int32_t rows, gl_me
 {
 	if (!n) return fail(GL_ERR_INVALID, "gl_train_window: null handle");
 	if (n->d.mode != GL_MODE_BATCHED) return fail(GL_ERR_STATE, "gl_train_window needs a batched-mode network");
-	if (!n->dX) return fail(GL_ERR_STATE, "gl_train_window: no data set");
+	if (!n->dX || !n->dY) return fail(GL_ERR_STATE, "gl_train_window: no data (inputs and expected rows) set");
 	if (first_row < 0 || rows < 1 || first_row + rows > n->rows) return fail(GL_ERR_INVALID, "gl_train_window: row range");
 	if (int r = use_device(n)) return r;
 	return batched_window(n, n->dX + first_row * n->d.sizes[0], n->dY + first_row * n->n_out, rows, n->rows, out);
@@ -836,7 +867,7 @@ extern "C" int gl_train_window_host(gl_net* n, const float* x, const float* y, i
 extern "C" int gl_train_epochs(gl_net* n, int32_t n_epochs, gl_metrics* out)
 {
 	if (!n || n_epochs < 1) return fail(GL_ERR_INVALID, "gl_train_epochs: bad argument");
-	if (!n->dX) return fail(GL_ERR_STATE, "gl_train_epochs: no data set");
+	if (!n->dX || !n->dY) return fail(GL_ERR_STATE, "gl_train_epochs: no data (inputs and expected rows) set");
 	if (int r = use_device(n)) return r;
 	n->stop = 0;
 	if (n->d.mode == GL_MODE_REFERENCE) return ref_train(n, n_epochs, out);
@@ -1102,6 +1133,59 @@ extern "C" int gl_dp_set_window(gl_net* n, int32_t global_rows, int32_t first_gl
 	return GL_OK;
 }
 
+// ---- timing helpers: CUDA events on the handle's own stream ---------------------------------------
+extern "C" int gl_timer_start(gl_net* n)
+{
+	if (!n) return fail(GL_ERR_INVALID, "gl_timer_start: null handle");
+	if (int r = use_device(n)) return r;
+	if (!n->tim0)
+	{
+		CU(cudaEventCreate(&n->tim0));
+		CU(cudaEventCreate(&n->tim1));
+	}
+	CU(cudaEventRecord(n->tim0, n->stream));
+	return GL_OK;
+}
+extern "C" int gl_timer_stop(gl_net* n, double* ms)
+{
+	if (!n || !ms || !n->tim0) return fail(GL_ERR_INVALID, "gl_timer_stop: bad argument");
+	if (int r = use_device(n)) return r;
+	CU(cudaEventRecord(n->tim1, n->stream));
+	CU(cudaEventSynchronize(n->tim1));
+	float f = 0;
+	CU(cudaEventElapsedTime(&f, n->tim0, n->tim1));
+	*ms = f;
+	return GL_OK;
+}
+extern "C" int gl_profile_enable(gl_net* n, int32_t on)
+{
+	if (!n) return fail(GL_ERR_INVALID, "gl_profile_enable: null handle");
+	n->profile = on != 0;
+	n->profUsed = 0;
+	n->profFlops.clear();
+	n->profIsTc.clear();
+	return GL_OK;
+}
+// Sums the recorded layer-product launches since gl_profile_enable: out[0] launches, out[1] total ms,
+// out[2] total flop (2*M*N*K each), for the tensor-core kernel; out[3..5] the same for the FFMA kernel.
+extern "C" int gl_profile_read(gl_net* n, double* out6)
+{
+	if (!n || !out6) return fail(GL_ERR_INVALID, "gl_profile_read: bad argument");
+	if (int r = use_device(n)) return r;
+	CU(cudaStreamSynchronize(n->stream));
+	for (int i = 0; i < 6; ++i) out6[i] = 0.0;
+	for (size_t i = 0; i < n->profFlops.size(); ++i)
+	{
+		float f = 0;
+		CU(cudaEventElapsedTime(&f, n->profEv[2 * i], n->profEv[2 * i + 1]));
+		const int o = n->profIsTc[i] ? 0 : 3;
+		out6[o] += 1.0;
+		out6[o + 1] += f;
+		out6[o + 2] += n->profFlops[i];
+	}
+	return GL_OK;
+}
+
 extern "C" int64_t gl_tensor_core_launches(const gl_net* n) { return n ? n->tcLaunches : 0; }
 extern "C" int64_t gl_kernel_launches(const gl_net* n) { return n ? n->launches : 0; }
 
@@ -1168,6 +1252,21 @@ extern "C" int gl_synth_fill(float* d_out, int64_t count, uint64_t seed, uint32_
 	CU(cudaSetDevice(device));
 	CU(launch_synth_fill(d_out, count, seed, stream_id, dist, scale, offset, 0));
 	CU(cudaDeviceSynchronize());
+	return GL_OK;
+}
+
+extern "C" int gl_onehot_fill(float* d_y, const int32_t* labels, int64_t rows, int32_t n, float on, float off, int32_t device)
+{
+	if (!d_y || !labels || rows < 1 || n < 1) return fail(GL_ERR_INVALID, "gl_onehot_fill: bad argument");
+	if (gl_device_count() < 1) return fail(GL_ERR_NO_DEVICE, "no sm_100 CUDA device");
+	CU(cudaSetDevice(device));
+	int* dl = nullptr;
+	CU(cudaMalloc(&dl, (size_t)rows * sizeof(int)));
+	CU(cudaMemcpy(dl, labels, (size_t)rows * sizeof(int), cudaMemcpyHostToDevice));
+	cudaError_t e = launch_onehot_fill(d_y, dl, rows, n, on, off, 0);
+	if (e == cudaSuccess) e = cudaDeviceSynchronize();
+	cudaFree(dl);
+	if (e != cudaSuccess) return fail(GL_ERR_CUDA, "gl_onehot_fill: %s", cudaGetErrorString(e));
 	return GL_OK;
 }
 

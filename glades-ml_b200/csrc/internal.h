@@ -102,4 +102,7 @@ cudaError_t launch_update(float* W, const float* G, long long count, float inv_m
 cudaError_t launch_synth_fill(float* out, long long n, unsigned long long seed, unsigned stream_id, int dist,
                               float scale, float offset, cudaStream_t s);
 
+// y[r][c] = (c == labels[r]) ? on : off  (expected rows in the reference's one-hot convention)
+cudaError_t launch_onehot_fill(float* y, const int* labels, long long rows, int n, float on, float off, cudaStream_t s);
+
 }  // namespace glb

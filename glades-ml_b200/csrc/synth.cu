@@ -60,4 +60,24 @@ cudaError_t launch_synth_fill(float* out, long long n, unsigned long long seed, 
 	return cudaGetLastError();
 }
 
+__global__ void __launch_bounds__(256) onehot_fill_kernel(float* y, const int* labels, long long rows, int n, float on, float off)
+{
+	const long long total = rows * n;
+	const long long stride = (long long)gridDim.x * blockDim.x;
+	for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride)
+	{
+		const long long r = i / n;
+		y[i] = ((int)(i - r * n) == labels[r]) ? on : off;
+	}
+}
+
+cudaError_t launch_onehot_fill(float* y, const int* labels, long long rows, int n, float on, float off, cudaStream_t s)
+{
+	long long blocks = (rows * n + 255) / 256;
+	if (blocks > 148 * 16) blocks = 148 * 16;
+	if (blocks < 1) blocks = 1;
+	onehot_fill_kernel<<<(unsigned)blocks, 256, 0, s>>>(y, labels, rows, n, on, off);
+	return cudaGetLastError();
+}
+
 }  // namespace glb

@@ -135,7 +135,7 @@ int64_t gl_weight_count(const gl_net* net);
  * are packed once.  Host pointers are copied (through pinned staging) before the call returns. */
 int gl_set_data(gl_net* net, const float* x, const float* y, int64_t rows);
 /* Same, for rows that already live in device memory; the buffers are borrowed, not copied, and
- * must outlive the handle's use of them. */
+ * must outlive the handle's use of them.  d_y may be NULL for forward-only use without metrics. */
 int gl_set_data_device(gl_net* net, const float* d_x, const float* d_y, int64_t rows);
 
 /* Replaces n iterations of the epoch loop of NNetwork::run with RUN_TRAIN
@@ -207,6 +207,21 @@ int gl_dp_set_window(gl_net* net, int32_t global_rows, int32_t first_global_pos)
  * d_out is a device pointer. */
 int gl_synth_fill(float* d_out, int64_t n, uint64_t seed, uint32_t stream, int32_t dist, float scale, float offset,
                   int32_t device);
+
+/* Expected rows from class labels, on the device: d_y[r][c] = (c == labels[r]) ? on : off
+ * (the reference's one-hot encoder writes 0.99 / 0.01, GMath/OHE.cpp:159-198).  labels is a host
+ * array. */
+int gl_onehot_fill(float* d_y, const int32_t* labels, int64_t rows, int32_t n, float on, float off, int32_t device);
+
+/* ---- measurement helpers (no counterpart in the reference) ------------------------------ */
+/* CUDA events on the handle's own stream around whatever is queued between the two calls. */
+int gl_timer_start(gl_net* net);
+int gl_timer_stop(gl_net* net, double* ms);
+/* Per-launch event timing of the layer products.  gl_profile_read fills out6 with
+ * {launches, total ms, total flop (2*M*N*K each)} for the tensor-core kernel, then for the FFMA
+ * kernel, since gl_profile_enable(net, 1). */
+int gl_profile_enable(gl_net* net, int32_t on);
+int gl_profile_read(gl_net* net, double* out6);
 
 /* ---- raw device helpers for callers that keep data resident ---------------------------- */
 int gl_device_alloc(void** d_ptr, int64_t bytes, int32_t device);
