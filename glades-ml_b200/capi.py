@@ -149,6 +149,8 @@ def lib():
         "gl_dp_init": (C.c_int, [vp, i32, i32, vp]),
         "gl_dp_set_window": (C.c_int, [vp, i32, i32]),
         "gl_synth_fill": (C.c_int, [vp, i64, u64, u32, i32, f32, f32, i32]),
+        "gl_matmul_static": (C.c_int, [vp, i64, i64, vp, i64, i64, vp, i64, i32, i32, i32, i32]),
+        "gl_matmul_static_error": (C.c_char_p, []),
         "gl_onehot_fill": (C.c_int, [vp, vp, i64, i32, f32, f32, i32]),
         "gl_timer_start": (C.c_int, [vp]),
         "gl_timer_stop": (C.c_int, [vp, C.POINTER(C.c_double)]),

@@ -185,6 +185,20 @@ int64_t gl_tensor_core_launches(const gl_net* net);
 int gl_matmul(const float* d_a, int64_t a_sm, int64_t a_sk, const float* d_b, int64_t b_sn, int64_t b_sk, float* d_c,
               int64_t ldc, int32_t m, int32_t n, int32_t k, int32_t engine, int32_t device);
 
+/* The same tensor-core product for callers that cannot allocate device memory: hosts that gave the
+ * whole GPU to their own arena, or loops that must not hit cudaMalloc/cudaFree's device-wide
+ * synchronisation.  It has no counterpart in the reference.  Its scratch (the operands' low TF32
+ * parts and a status word) is a fixed 16 MiB + 256 B array inside the library image, held by every
+ * GPU that loads the library; the call allocates nothing.  Limits: tensor-core engine only (shape
+ * rules of gl_matmul), each operand at most 2 Mi floats as addressed by its strides (else
+ * GL_ERR_TOO_LARGE).  All calls share the array: do not let two calls overlap on the GPU.  The first
+ * call on a device looks the array's address up and should be made outside any stream capture.
+ * The call returns after the product has finished.  gl_matmul_static_error() gives the text of this
+ * entry point's last failure on the calling thread. */
+int gl_matmul_static(const float* d_a, int64_t a_sm, int64_t a_sk, const float* d_b, int64_t b_sn, int64_t b_sk,
+                     float* d_c, int64_t ldc, int32_t m, int32_t n, int32_t k, int32_t device);
+const char* gl_matmul_static_error(void);
+
 /* Replaces NNetwork::stop (network.cpp:99-102): async-signal-safe; the flag is looked at between
  * epochs of gl_train_epochs. */
 void gl_stop(gl_net* net);
