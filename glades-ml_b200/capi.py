@@ -138,6 +138,7 @@ def lib():
         "gl_get_activations": (C.c_int, [vp, i64, vp]),
         "gl_get_pending_delta": (C.c_int, [vp, i32, vp]),
         "gl_get_confusion": (C.c_int, [vp, vp]),
+        "gl_get_last_outputs": (C.c_int, [vp, vp]),
         "gl_get_epochs": (C.c_int, [vp]),
         "gl_stop": (None, [vp]),
         "gl_sync": (C.c_int, [vp]),
@@ -290,6 +291,11 @@ class Net:
     def confusion(self):
         a = np.zeros((self.n_out, self.n_out), np.int32)
         _check(lib().gl_get_confusion(self.h, _ptr(a)))
+        return a
+
+    def last_outputs(self):
+        a = np.empty(self.n_out, np.float32)
+        _check(lib().gl_get_last_outputs(self.h, _ptr(a)))
         return a
 
     def epochs(self):

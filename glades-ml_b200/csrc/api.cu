@@ -134,6 +134,7 @@ struct gl_net
 	float* dSumsF = nullptr;  // reference mode: [n_epochs][2]
 	int sumsFCap = 0;
 	int* dConf = nullptr;     // [n_out][n_out]
+	float* dLastOut = nullptr; // [n_out]: predictions of the last row the last call processed
 	// reference mode
 	float* dHist = nullptr;
 	int* dHistLen = nullptr;
@@ -262,6 +263,8 @@ extern "C" int gl_create(const gl_net_desc* d, gl_net** out)
 	CU(cudaMemset(n->dFlags, 0, 4 * sizeof(int)));
 	CU(cudaMalloc(&n->dSums, 2 * sizeof(double)));
 	CU(cudaMemset(n->dSums, 0, 2 * sizeof(double)));
+	CU(cudaMalloc(&n->dLastOut, (size_t)n->n_out * sizeof(float)));
+	CU(cudaMemset(n->dLastOut, 0, (size_t)n->n_out * sizeof(float)));
 	CU(cudaMalloc(&n->dConf, (size_t)n->n_out * n->n_out * sizeof(int)));
 	CU(cudaMemset(n->dConf, 0, (size_t)n->n_out * n->n_out * sizeof(int)));
 	if (d->mode == GL_MODE_REFERENCE)
@@ -322,6 +325,7 @@ extern "C" int gl_destroy(gl_net* n)
 	cudaFree(n->dWlo);
 	cudaFree(n->dW); cudaFree(n->dBias); cudaFree(n->dG); cudaFree(n->dBscale); cudaFree(n->dFlags);
 	cudaFree(n->dSums); cudaFree(n->dSumsF); cudaFree(n->dConf); cudaFree(n->dHist); cudaFree(n->dHistLen);
+	cudaFree(n->dLastOut);
 	cudaFree(n->dScratch); cudaFree(n->ownX); cudaFree(n->ownY); cudaFree(n->dColterm);
 	cudaFree(n->dXwin); cudaFree(n->dYwin);
 	if (n->hPinned) cudaFreeHost(n->hPinned);
@@ -502,6 +506,7 @@ static int ref_train(gl_net* n, int n_epochs, gl_metrics* out)
 	a.epoch_sums = n->dSumsF;
 	a.confusion = n->dConf;
 	a.outputs = nullptr;
+	a.last_out = n->dLastOut;
 	a.flags = n->dFlags;
 	a.weights_in_smem = ref_train_smem_bytes(a.net, true) <= (size_t)227 * 1024;
 	if (!a.weights_in_smem && ref_train_smem_bytes(a.net, false) > (size_t)227 * 1024)
@@ -738,6 +743,8 @@ static int batched_window(gl_net* n, const float* X, const float* Y, int rows, i
 	++launches;
 	n->loD[n->H + 1] = false;
 	n->loA[n->H + 1] = false;  // the softmax head rewrote the last activations in place
+	CU(cudaMemcpyAsync(n->dLastOut, n->dA[n->H + 1] + (size_t)(rows - 1) * n->n_out, (size_t)n->n_out * sizeof(float),
+	                   cudaMemcpyDeviceToDevice, n->stream));
 
 	for (int L = n->H + 1; L >= 1; --L)
 	{
@@ -959,6 +966,9 @@ static int forward_rows(gl_net* n, const float* X, const float* Y, int64_t rows,
 			CU(launch_head(h, n->stream));
 			++launches;
 		}
+		if (r0 + cnt == rows)
+			CU(cudaMemcpyAsync(n->dLastOut, n->dA[n->H + 1] + (size_t)(cnt - 1) * n->n_out, (size_t)n->n_out * sizeof(float),
+			                   cudaMemcpyDeviceToDevice, n->stream));
 		if (outputs)
 			CU(cudaMemcpyAsync(outputs + r0 * n->n_out, n->dA[n->H + 1], (size_t)cnt * n->n_out * sizeof(float),
 			                   cudaMemcpyDeviceToHost, n->stream));
@@ -1078,6 +1088,15 @@ extern "C" int gl_get_pending_delta(gl_net* n, int32_t k, float* out)
 		CU(cudaMemcpy(out + n->woff[l], n->dHist + n->woff[l] * n->d.batch_size + (int64_t)k * cnt, cnt * sizeof(float),
 		              cudaMemcpyDeviceToHost));
 	}
+	return GL_OK;
+}
+
+extern "C" int gl_get_last_outputs(gl_net* n, float* out)
+{
+	if (!n || !out) return fail(GL_ERR_INVALID, "gl_get_last_outputs: null argument");
+	if (int r = use_device(n)) return r;
+	CU(cudaStreamSynchronize(n->stream));
+	CU(cudaMemcpy(out, n->dLastOut, (size_t)n->n_out * sizeof(float), cudaMemcpyDeviceToHost));
 	return GL_OK;
 }
 

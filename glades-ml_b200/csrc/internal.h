@@ -35,6 +35,7 @@ struct RefTrainArgs
 	float* epoch_sums;                  // [n_epochs][2]: raw cost sum, raw accuracy sum
 	int* confusion;                     // [n_out][n_out], counts of the LAST epoch
 	float* outputs;                     // optional [rows][n_out], predictions of the last epoch
+	float* last_out;                    // [n_out]: predictions of the last row of the last epoch
 	int* flags;                         // [0] non-finite weight seen after the call
 	int weights_in_smem;                // stage W and hist in shared memory for the whole launch
 };

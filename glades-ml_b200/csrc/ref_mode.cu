@@ -151,6 +151,8 @@ __global__ void __launch_bounds__(1024, 1) ref_train_kernel(const __grid_constan
 			}
 			if (a.outputs && last_epoch)
 				for (int o = t; o < n_out; o += T) a.outputs[r * n_out + o] = actp[H + 1][o];
+			if (a.last_out && last_epoch && r == a.rows - 1)
+				for (int o = t; o < n_out; o += T) a.last_out[o] = actp[H + 1][o];
 
 			// ---------------- backward
 			const int k = s_hist_len;

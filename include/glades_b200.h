@@ -164,6 +164,10 @@ int gl_get_activations(gl_net* net, int64_t row, float* out);
 /* Reference mode: the k-th pending delta of every edge (Edge::prevDelta[k], State/edge.cpp:54-60;
  * 0 where the history is shorter), flat like the weights. */
 int gl_get_pending_delta(gl_net* net, int32_t k, float* out);
+/* Predictions of the last row the last train / forward call processed, n_out floats: the
+ * `predicted` half of NNetwork::getResults() (network.cpp:529-530; during training these are the
+ * outputs computed before that row's own update). */
+int gl_get_last_outputs(gl_net* net, float* out);
 /* Confusion counts of the last epoch / forward call, [expected][predicted], n_out*n_out ints
  * (CMatrix::addResult, GMath/cmatrix.cpp:57-98). */
 int gl_get_confusion(gl_net* net, int32_t* out);

@@ -163,7 +163,10 @@ int ref_set_weights(void* h, const float* w, const float* bias)
 		for (unsigned int o = 0; o < L->size(); ++o)
 		{
 			glades::Node* n = L->getNode(o);
-			for (unsigned int i = 0; i < n->numEdges(); ++i)
+			// A node can own more (or fewer) edges than its layer has inputs: when the weight builder
+			// restarts (State/LayerBuilder.cpp:212-221) it keeps the previous fan-in.  The dense view
+			// has exactly n_l weights per node; surplus edges are never read by the loop.
+			for (unsigned int i = 0; i < (unsigned int)r->desc.sizes[l]; ++i)
 			{
 				n->setEdgeWeight(i, w[k++]);
 				n->clearPrevDeltas(i);
@@ -187,8 +190,8 @@ int ref_get_weights(void* h, float* w, float* bias)
 		for (unsigned int o = 0; o < L->size(); ++o)
 		{
 			glades::Node* n = L->getNode(o);
-			for (unsigned int i = 0; i < n->numEdges(); ++i)
-				w[k++] = n->getEdgeWeight(i);
+			for (unsigned int i = 0; i < (unsigned int)r->desc.sizes[l]; ++i)
+				w[k++] = n->getEdgeWeight(i);  // 0 for an edge the node does not own
 		}
 		if (l < H && bias)
 			bias[l] = L->getBiasWeight();
@@ -208,7 +211,7 @@ int ref_get_pending_delta(void* h, int k, float* out)
 		for (unsigned int o = 0; o < L->size(); ++o)
 		{
 			glades::Node* n = L->getNode(o);
-			for (unsigned int i = 0; i < n->numEdges(); ++i)
+			for (unsigned int i = 0; i < (unsigned int)r->desc.sizes[l]; ++i)
 			{
 				std::vector<float> pd = n->getPrevDeltas(i);
 				out[j++] = (k < (int)pd.size()) ? pd[k] : 0.0f;

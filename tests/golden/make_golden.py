@@ -81,9 +81,33 @@ def trajectory(name, sizes, acts, out, x, y, mb, lr, mom, epochs, snapshots, w_r
          w=np.array(ws), b=np.array(bs), outputs=np.array(outs), pending=pend)
 
 
+def init_fixture():
+    """Weights the reference draws (Layer::initWeights, rand()-driven Ziggurat) after srand(seed)."""
+    import ctypes
+    libc = ctypes.CDLL(None)
+    cases = [dict(sizes=[4, 5, 3], acts=["sigmoid", "sigmoid"], out="classification", seed=1),
+             dict(sizes=[2, 2, 1], acts=["tanh", "tanh"], out="regression", seed=2),
+             dict(sizes=[6, 7, 5, 2], acts=["tanh", "relu", "linear"], out="regression", seed=3),
+             dict(sizes=[3, 4, 4, 2], acts=["relu", "tanh", "tanh"], out="regression", seed=4),
+             dict(sizes=[10, 32, 32, 1], acts=["tanh", "tanh", "sigmoid"], out="regression", seed=5)]
+    arrays = {}
+    for k, c in enumerate(cases):
+        d = capi.make_desc(c["sizes"], c["acts"], c["out"], batch=1, lr=0.01)
+        x = np.zeros((1, c["sizes"][0]), np.float32)
+        y = np.zeros((1, c["sizes"][-1]), np.float32)
+        libc.srand(c["seed"])
+        R = o.Reference(d, x, y, capi.Metrics)
+        arrays["w%d" % k] = R.get_weights()[0]
+    save("init_weights", dict(kind="init", cases=cases), **arrays)
+
+
 def main():
     t0 = time.time()
+    if "--only-init" in sys.argv:
+        init_fixture()
+        return
     L = o.reference_lib()
+    init_fixture()
 
     # ---- A. scalar known answers of GMath (gmath.cpp:22-101,182-353)
     zs = np.concatenate([np.linspace(-12, 12, 193), [0.0, 0.046, 0.0459, 0.0461, 1e-8, -1e-8, 88.0, -88.0, 0.9, 0.1]]

@@ -1,0 +1,195 @@
+// Test driver for the C++ host mirror (glades-ml_b200/host): reads like the reference's own
+// unit test (unit-tests/Backend/Machine Learning/nn-test.cpp:27-75: build the NNInfo, import the
+// data, set the terminator, check the accuracy before training, call train) but takes its case from
+// a file and writes what it ends with, so that the Python tests can compare it with the oracle.
+//
+//   host_tool unit                      host-only checks (no GPU needed); prints OK
+//   host_tool init  <case> <out>        draws initial weights after srand(seed) and writes them
+//   host_tool run   <case> <out>        trains / tests on the GPU through NNetwork and writes
+//                                       weights, biases, metrics, results, confusion counts
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include <string>
+#include <vector>
+
+#include "glades_b200.hpp"
+
+using namespace glades_b200;
+
+struct Case
+{
+	int nLayers;
+	std::vector<int> sizes;
+	std::vector<float> lr, mom, wd1, wd2, par;
+	std::vector<int> act;
+	int outType, batch, rows, epochs, runType, mode, haveWeights, seed;
+	std::vector<float> x, y, w, b;
+};
+
+static bool rd(FILE* f, void* p, size_t n) { return fread(p, 1, n, f) == n; }
+
+static bool loadCase(const char* path, Case& c)
+{
+	FILE* f = fopen(path, "rb");
+	if (!f) return false;
+	int hdr[9];
+	if (!rd(f, hdr, sizeof hdr)) return false;
+	c.nLayers = hdr[0]; c.outType = hdr[1]; c.batch = hdr[2]; c.rows = hdr[3]; c.epochs = hdr[4];
+	c.runType = hdr[5]; c.mode = hdr[6]; c.haveWeights = hdr[7]; c.seed = hdr[8];
+	const int L = c.nLayers - 1;
+	c.sizes.resize(c.nLayers); c.act.resize(L);
+	c.lr.resize(L); c.mom.resize(L); c.wd1.resize(L); c.wd2.resize(L); c.par.resize(L);
+	bool ok = rd(f, &c.sizes[0], 4 * c.nLayers) && rd(f, &c.act[0], 4 * L) && rd(f, &c.lr[0], 4 * L) &&
+	          rd(f, &c.mom[0], 4 * L) && rd(f, &c.wd1[0], 4 * L) && rd(f, &c.wd2[0], 4 * L) && rd(f, &c.par[0], 4 * L);
+	size_t nw = 0;
+	for (int l = 0; l < L; ++l) nw += (size_t)c.sizes[l] * c.sizes[l + 1];
+	c.x.resize((size_t)c.rows * c.sizes[0]); c.y.resize((size_t)c.rows * c.sizes[L]);
+	ok = ok && rd(f, &c.x[0], 4 * c.x.size()) && rd(f, &c.y[0], 4 * c.y.size());
+	if (c.haveWeights)
+	{
+		c.w.resize(nw); c.b.resize(c.nLayers - 2);
+		ok = ok && rd(f, &c.w[0], 4 * nw) && rd(f, &c.b[0], 4 * c.b.size());
+	}
+	fclose(f);
+	return ok;
+}
+
+static NNInfo* makeInfo(const Case& c)
+{
+	// the same three steps as a caller of the reference: input-layer info, hidden infos, output info
+	InputLayerInfo* in = new InputLayerInfo(c.batch, c.lr[0], c.mom[0], c.wd1[0], c.wd2[0], 0.0f, c.act[0], c.par[0]);
+	std::vector<HiddenLayerInfo*> hidden;
+	for (int l = 1; l <= c.nLayers - 2; ++l)
+		hidden.push_back(new HiddenLayerInfo(c.sizes[l], c.lr[l], c.mom[l], c.wd1[l], c.wd2[l], 0.0f, c.act[l], c.par[l]));
+	OutputLayerInfo* out = new OutputLayerInfo(c.sizes[c.nLayers - 1], c.outType);
+	return new NNInfo("case", in, hidden, out);
+}
+
+#define CHECK(expr)                                                       \
+	do                                                                    \
+	{                                                                     \
+		if (!(expr))                                                      \
+		{                                                                 \
+			printf("FAILED %s:%d: %s\n", __FILE__, __LINE__, #expr);    \
+			return 1;                                                     \
+		}                                                                 \
+	} while (0)
+
+static int unitChecks()
+{
+	// NNInfo getters: index 0 = input-layer info, index l = hidden l-1, defaults past the end
+	InputLayerInfo* in = new InputLayerInfo(4, 0.1f, 0.9f, 0.001f, 0.5f, 0.0f, GMath::SIGMOID, 0.3f);
+	std::vector<HiddenLayerInfo*> hidden;
+	hidden.push_back(new HiddenLayerInfo(16, 0.2f, 0.8f, 0.002f, 0.004f, 0.0f, GMath::TANH, 0.7f));
+	hidden.push_back(new HiddenLayerInfo(8, 0.3f, 0.7f, 0.003f, 0.006f, 0.0f, GMath::RELU, 0.9f));
+	NNInfo info("unit", in, hidden, new OutputLayerInfo(3, OutputLayerInfo::CLASSIFICATION));
+	CHECK(info.numHiddenLayers() == 2 && info.getBatchSize() == 4 && info.getOutputLayerSize() == 3);
+	CHECK(info.getLearningRate(0) == 0.1f && info.getLearningRate(1) == 0.2f && info.getLearningRate(2) == 0.3f);
+	CHECK(info.getLearningRate(3) == 0.01f);                  // past the end: the reference's default
+	CHECK(info.getWeightDecay2(0) == 0.001f);                 // quirk: index 0 returns weightDecay1
+	CHECK(info.getWeightDecay2(1) == 0.004f && info.getWeightDecay1(2) == 0.003f);
+	CHECK(info.getPDropout(3) == 1.0f && info.getMomentumFactor(7) == 0.0f);
+	CHECK(info.getActivationType(0) == GMath::SIGMOID && info.getActivationType(2) == GMath::RELU);
+	CHECK(info.getActivationParam(1) == 0.7f && info.getOutputType() == GMath::CLASSIFICATION);
+	gl_net_desc d;
+	CHECK(packDescriptor(info, 5, GL_MODE_REFERENCE, &d));
+	CHECK(d.n_layers == 4 && d.sizes[0] == 5 && d.sizes[1] == 16 && d.sizes[2] == 8 && d.sizes[3] == 3);
+	CHECK(d.wd2[0] == 0.001f && d.wd2[2] == 0.006f && d.batch_size == 4 && d.output_type == GL_OUT_CLASSIFICATION);
+	CHECK(d.activation[0] == GL_ACT_SIGMOID && d.activation[1] == GL_ACT_TANH && d.activation[2] == GL_ACT_RELU);
+	// Terminator::triggered (Terminator.cpp:63-78): modulo on time and epoch, threshold on accuracy
+	Terminator t;
+	CHECK(!t.triggered(100, 7, 99.0f));
+	t.setEpoch(5);
+	CHECK(t.triggered(1, 10, 0.0f) && !t.triggered(1, 11, 0.0f));
+	t.setEpoch(0);
+	t.setAccuracy(95.0f);
+	CHECK(t.triggered(1, 1, 95.0f) && !t.triggered(1, 1, 94.9f));
+	t.setAccuracy(0.0f);
+	t.setTimestamp(10);
+	CHECK(t.triggered(20, 1, 0.0f) && !t.triggered(21, 1, 0.0f));
+	// data interface
+	const float x[6] = {1, 2, 3, 4, 5, 6}, y[2] = {0.5f, 0.25f};
+	ArrayInput ai(x, y, 2, 3, 1);
+	CHECK(ai.getTrainSize() == 2 && ai.getFeatureCount() == 3 && ai.getTrainRow(1).getFloat(2) == 6.0f);
+	CHECK(ai.getTrainExpectedRow(1).getFloat(0) == 0.25f && ai.getTrainRow(5).size() == 0);
+	// error behaviour: NULL arguments return silently / NULL like the reference (main.cpp:84-85)
+	CHECK(train((NNetwork*)NULL, &ai) == NULL);
+	NNetwork none(NULL);
+	none.train(&ai);
+	CHECK(none.getEpochs() == 0 && !none.getRunning());
+	NNetwork net(&info);
+	net.setQuiet(true);
+	net.train(NULL);
+	CHECK(net.getEpochs() == 0);
+	// shard arithmetic of the C ABI
+	int64_t f = 0, c = 0;
+	gl_shard_range(10, 0, 3, &f, &c);
+	CHECK(f == 0 && c == 4);
+	gl_shard_range(10, 2, 3, &f, &c);
+	CHECK(f == 7 && c == 3);
+	// without a GPU a training call returns silently with the epoch counter untouched
+	if (gl_device_count() < 1)
+	{
+		const float xx[5] = {0, 0, 0, 0, 0}, yy[3] = {0.01f, 0.99f, 0.01f};
+		ArrayInput one(xx, yy, 1, 5, 3);
+		net.terminator.setEpoch(1);
+		net.train(&one);
+		CHECK(net.getEpochs() == 0 && net.getAccuracy() == 0.0f);
+	}
+	printf("OK\n");
+	return 0;
+}
+
+int main(int argc, char** argv)
+{
+	if (argc >= 2 && strcmp(argv[1], "unit") == 0) return unitChecks();
+	if (argc < 4) return 2;
+	Case c;
+	if (!loadCase(argv[2], c)) { fprintf(stderr, "cannot read case %s\n", argv[2]); return 2; }
+	NNInfo* info = makeInfo(c);
+	FILE* out = fopen(argv[3], "wb");
+	if (!out) return 2;
+	if (strcmp(argv[1], "init") == 0)
+	{
+		srand((unsigned)c.seed);
+		std::vector<float> w;
+		drawInitialWeights(*info, c.sizes[0], w);
+		fwrite(&w[0], 4, w.size(), out);
+		fclose(out);
+		return 0;
+	}
+	ArrayInput di(&c.x[0], &c.y[0], c.rows, c.sizes[0], c.sizes[c.nLayers - 1]);
+	NNetwork net(info);
+	net.setQuiet(true);
+	net.setMode(c.mode);
+	if (c.haveWeights) net.setWeights(c.w, c.b);
+	else srand((unsigned)c.seed);
+	// like nn-test.cpp:69-75: terminator on the epoch count, accuracy below the bar before training
+	net.terminator.setEpoch(c.epochs);
+	if (net.getAccuracy() >= 95.0f) return 3;
+	if (c.runType == NNetwork::RUN_TRAIN) train(&net, &di);
+	else test(&net, &di);
+	std::vector<float> w, b;
+	if (!net.getWeights(w, b)) { fclose(out); return 4; }
+	const int epochs = net.getEpochs();
+	float m[4] = {net.getError(), net.getAccuracy(), net.getClassAccuracy(), net.getClassF1()};
+	const shmea::GList res = net.getResults();
+	const int nres = (int)res.size();
+	const int ncm = (int)net.getConfusion().size();
+	fwrite(&epochs, 4, 1, out);
+	fwrite(m, 4, 4, out);
+	fwrite(&nres, 4, 1, out);
+	for (int i = 0; i < nres; ++i) { float v = res.getFloat(i); fwrite(&v, 4, 1, out); }
+	fwrite(&ncm, 4, 1, out);
+	if (ncm) fwrite(&net.getConfusion()[0], 4, ncm, out);
+	const int nw = (int)w.size(), nb = (int)b.size();
+	fwrite(&nw, 4, 1, out);
+	fwrite(&w[0], 4, nw, out);
+	fwrite(&nb, 4, 1, out);
+	if (nb) fwrite(&b[0], 4, nb, out);
+	fclose(out);
+	delete info;
+	return 0;
+}
