@@ -844,7 +844,9 @@ extern "C" int gl_train_window(gl_net* n, int64_t first_row, int32_t rows, gl_me
 	if (!n->dX || !n->dY) return fail(GL_ERR_STATE, "gl_train_window: no data (inputs and expected rows) set");
 	if (first_row < 0 || rows < 1 || first_row + rows > n->rows) return fail(GL_ERR_INVALID, "gl_train_window: row range");
 	if (int r = use_device(n)) return r;
-	return batched_window(n, n->dX + first_row * n->d.sizes[0], n->dY + first_row * n->n_out, rows, n->rows, out);
+	// the cost divisor of a single window call is that window's global row count
+	const int64_t win_rows = (n->world > 1 && n->globalRows > 0) ? n->globalRows : rows;
+	return batched_window(n, n->dX + first_row * n->d.sizes[0], n->dY + first_row * n->n_out, rows, win_rows, out);
 }
 
 static int ensure_window_staging(gl_net* n, int64_t rows)
@@ -868,7 +870,8 @@ extern "C" int gl_train_window_host(gl_net* n, const float* x, const float* y, i
 	// the caller's buffers are read directly by the copy engine (fast when they are pinned)
 	CU(cudaMemcpyAsync(n->dXwin, x, (size_t)rows * n->d.sizes[0] * sizeof(float), cudaMemcpyHostToDevice, n->stream));
 	CU(cudaMemcpyAsync(n->dYwin, y, (size_t)rows * n->n_out * sizeof(float), cudaMemcpyHostToDevice, n->stream));
-	return batched_window(n, n->dXwin, n->dYwin, rows, rows, out);
+	const int64_t win_rows = (n->world > 1 && n->globalRows > 0) ? n->globalRows : rows;
+	return batched_window(n, n->dXwin, n->dYwin, rows, win_rows, out);
 }
 
 extern "C" int gl_train_epochs(gl_net* n, int32_t n_epochs, gl_metrics* out)

@@ -144,7 +144,9 @@ int gl_set_data_device(gl_net* net, const float* d_x, const float* d_y, int64_t 
 int gl_train_epochs(gl_net* net, int32_t n_epochs, gl_metrics* out);
 /* Batched mode: one window step (forward, backward, update) over rows
  * [first_row, first_row+rows) of the resident data.  Under data parallelism each rank passes its
- * own shard of the global window and the gradient is all-reduced before the update. */
+ * own shard of the global window and the gradient is all-reduced before the update.  The cost in
+ * `out` is divided by (rows of the global window * n_out); gl_train_epochs divides by the data set's rows
+ * as the reference does. */
 int gl_train_window(gl_net* net, int64_t first_row, int32_t rows, gl_metrics* out);
 /* Batched mode: the same step with the window's rows in host memory (copied in by the call). */
 int gl_train_window_host(gl_net* net, const float* x, const float* y, int32_t rows, gl_metrics* out);

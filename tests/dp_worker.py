@@ -1,0 +1,107 @@
+"""Worker of the data-parallel tests: one process per rank (torchrun-style environment).
+
+mode `cpu`:  each rank computes the batched-mode gradient of ITS shard of one global window with the
+             CPU restatement, the contributions are summed with a gloo all-reduce, every rank
+             applies the same update; rank 0 checks the result against a one-rank run.
+mode `gpu`:  the same through the library on one GPU per rank (its own NCCL all-reduce), checked
+             against a one-GPU run of the whole window on rank 0.
+Exit code 0 = parity holds on every rank.
+"""
+import os
+import sys
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+import __graft_entry__ as ge  # noqa: E402
+
+
+def main():
+    mode = sys.argv[1]
+    import torch
+    import torch.distributed as td
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    td.init_process_group(backend="gloo")
+    rank, world = td.get_rank(), td.get_world_size()
+    g = ge.import_package()
+    o = ge.import_oracle()
+    rng = np.random.default_rng(123)  # same data on every rank
+    sizes = [128, 256, 128] if mode == "gpu" else [12, 20, 9, 4]
+    acts = ["relu", "softmax"] if mode == "gpu" else ["tanh", "relu", "sigmoid"]
+    rows = 512 if mode == "gpu" else 37   # 37 does not divide by 2: uneven shards
+    momentum = 0.6
+    d = g.make_desc(sizes, acts, "classification", batch=rows, lr=0.05, momentum=momentum, mode=g.MODE_BATCHED,
+                    device=int(os.environ.get("LOCAL_RANK", "0")) if mode == "gpu" else 0)
+    x = rng.standard_normal((rows, sizes[0])).astype(np.float32)
+    if acts[-1] == "softmax":
+        y = np.zeros((rows, sizes[-1]), np.float32)
+        y[np.arange(rows), rng.integers(0, sizes[-1], rows)] = 1.0
+    else:
+        y = rng.uniform(0.05, 0.95, (rows, sizes[-1])).astype(np.float32)
+    nw = g.weight_count(d)
+    w = rng.uniform(-0.2, 0.2, nw).astype(np.float32)
+    b = rng.uniform(-0.1, 0.1, len(sizes) - 2).astype(np.float32)
+    first, count = g.shard_range(rows, rank, world)
+    ok = True
+    if mode == "cpu":
+        S = o.Restate(d, x, y, g.Metrics)
+        S.set_weights(w, b)
+        for step in range(2):
+            part = S.window_grad(first, count, global_rows=rows, first_pos=first)
+            t = torch.from_numpy(part)
+            td.all_reduce(t)                      # the one exchange of the window
+            S.window_apply(t.numpy(), rows)
+        ws, bs = S.get_weights()
+        One = o.Restate(d, x, y, g.Metrics)
+        One.set_weights(w, b)
+        for step in range(2):
+            One.window_apply(One.window_grad(0, rows), rows)
+        w1, b1 = One.get_weights()
+        ok = np.allclose(ws, w1, rtol=1e-6, atol=1e-7) and np.allclose(bs, b1, rtol=1e-6, atol=1e-7)
+        # every replica holds the same weights bit for bit (same summed gradient, same update)
+        tw = torch.from_numpy(ws.copy())
+        td.broadcast(tw, 0)
+        ok = ok and np.array_equal(tw.numpy().view(np.uint32), ws.view(np.uint32))
+    else:
+        import ctypes as C
+        L = g.lib()
+        uid = (C.c_char * 128)()
+        if rank == 0:
+            assert L.gl_dp_unique_id(uid) == 0, L.gl_last_error()
+        lst = [bytes(uid.raw)]
+        td.broadcast_object_list(lst, src=0)
+        net = g.Net(d)
+        net.set_weights(w, b)
+        net.set_data(x[first:first + count], y[first:first + count])
+        net.dp_init(rank, world, lst[0])
+        net.dp_set_window(rows, first)
+        for step in range(2):
+            m = net.train_window(0, count)
+        wg, bg = net.get_weights()
+        tw = torch.from_numpy(wg.copy())
+        td.broadcast(tw, 0)
+        ok = np.array_equal(tw.numpy().view(np.uint32), wg.view(np.uint32))  # replicas identical
+        if rank == 0:
+            d1 = g.make_desc(sizes, acts, "classification", batch=rows, lr=0.05, momentum=momentum, mode=g.MODE_BATCHED)
+            one = g.Net(d1)
+            one.set_weights(w, b)
+            one.set_data(x, y)
+            for step in range(2):
+                m1 = one.train_window(0, rows)
+            w1, b1 = one.get_weights()
+            err = float(np.max(np.abs(wg - w1)) / np.max(np.abs(w1)))
+            ok = ok and err <= 1e-5 and np.allclose(bg, b1, rtol=1e-4, atol=1e-6)
+            ok = ok and abs(m.total_error - m1.total_error) <= 1e-5 * max(1.0, abs(m1.total_error)) and m.rows == rows
+            if not ok:
+                print("dp gpu mismatch: err %g loss %g vs %g" % (err, m.total_error, m1.total_error))
+            one.close()
+        net.close()
+    flag = torch.tensor([1 if ok else 0])
+    td.all_reduce(flag, op=td.ReduceOp.MIN)
+    td.destroy_process_group()
+    sys.exit(0 if int(flag[0]) == 1 else 1)
+
+
+if __name__ == "__main__":
+    main()
