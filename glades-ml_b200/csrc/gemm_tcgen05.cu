@@ -20,6 +20,7 @@
 // Every wait on an mbarrier is bounded: when it runs out the kernel raises *err_flag, leaves its
 // loops, waits (bounded) for the copies it still has in flight, frees its tensor memory and returns.
 #include <cuda.h>
+#include <stdlib.h>
 
 #include "common.cuh"
 #include "tc_gemm.h"
@@ -28,7 +29,8 @@ namespace glb {
 namespace {
 
 constexpr int TC_BM = 128;
-constexpr int TC_BK = 32;  // fp32 elements per k-block = one 128-byte swizzle row
+constexpr int TC_KALIGN = 32;  // K must be a multiple of the deepest k-block
+constexpr int TC_CHUNK_K = 128;  // k held by one tensor-memory accumulator before it is drained
 constexpr long long TC_WAIT_CYCLES = 2000000000ll;  // about a second
 
 struct TcParams
@@ -144,11 +146,14 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32])
 	    : "memory");
 }
 
-template <int BN, int STAGES>
+// BK = fp32 elements per k-block: 32 (128-byte rows, 128-byte swizzle) or 16 (64-byte rows, 64-byte
+// swizzle).  The shallower block with twice the stages keeps more bytes in flight for the same
+// shared memory, which is what bounds this kernel (operand bytes per flop are 4x those of a bf16 GEMM).
+template <int BN, int BK, int STAGES>
 struct TcSmem
 {
-	static constexpr int A_BYTES = TC_BM * TC_BK * 4;  // 16 KB per part
-	static constexpr int B_BYTES = BN * TC_BK * 4;
+	static constexpr int A_BYTES = TC_BM * BK * 4;
+	static constexpr int B_BYTES = BN * BK * 4;
 	static constexpr int STAGE_BYTES = 2 * A_BYTES + 2 * B_BYTES;
 	static constexpr int TILES_BYTES = STAGES * STAGE_BYTES;
 	static constexpr int TOTAL = TILES_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
@@ -159,17 +164,18 @@ struct TcSmem
 // The tensor core adds into its fp32 accumulator with truncation, not round-to-nearest: a chain of n
 // accumulations drifts by up to n * 2^-24 of the running sum, always towards zero (measured: -8e-5
 // relative at K = 4096 on all-positive operands).  So the accumulator in tensor memory only ever
-// holds TC_CHUNK_KB k-blocks (128 k = 48 accumulations); the epilogue warps drain each finished
+// holds TC_CHUNK_K = 128 k (48 accumulations); the epilogue warps drain each finished
 // chunk into fp32 registers with round-to-nearest adds while the MMA warp fills the other of two
 // tensor-memory accumulators.
-constexpr int TC_CHUNK_KB = 4;
 
-template <int BN, int STAGES>
-__global__ void __launch_bounds__(TcSmem<BN, STAGES>::THREADS, 1)
+template <int BN, int BK, int STAGES>
+__global__ void __launch_bounds__(TcSmem<BN, BK, STAGES>::THREADS, 1)
     gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapAlo,
                    const __grid_constant__ CUtensorMap mapB, const __grid_constant__ CUtensorMap mapBlo, const TcParams p)
 {
-	using S = TcSmem<BN, STAGES>;
+	using S = TcSmem<BN, BK, STAGES>;
+	constexpr int TC_BK = BK;
+	constexpr int TC_CHUNK_KB = TC_CHUNK_K / BK;
 	extern __shared__ uint8_t smem_raw[];
 	// the swizzled tiles need a 1024-byte aligned base
 	const uint32_t raw = smem_u32(smem_raw);
@@ -276,9 +282,12 @@ __global__ void __launch_bounds__(TcSmem<BN, STAGES>::THREADS, 1)
 		// MN-major: 32-element (128-byte) runs, one k per 128-byte row, swizzle atoms of 4 k-rows
 		// (512 bytes apart), so a k-step of 8 is 1024 bytes; the next 32-element chunk of M/N lies a
 		// whole 32x32 box (4096 bytes) further.
-		const uint32_t a_lbo = p.a_mn ? 4096u : 0u, a_sbo = p.a_mn ? 512u : 1024u, a_kstep = p.a_mn ? 1024u : 32u;
-		const uint32_t b_lbo = p.b_mn ? 4096u : 0u, b_sbo = p.b_mn ? 512u : 1024u, b_kstep = p.b_mn ? 1024u : 32u;
-		const uint32_t a_lt = p.a_mn ? 1u : 2u, b_lt = p.b_mn ? 1u : 2u;
+		// With 16-deep blocks the K-major rows are 64 bytes (64-byte swizzle, layout type 4, 8-row groups
+		// 512 bytes apart) and an MN-major 32-element chunk is a 32x16 box (2048 bytes).
+		constexpr uint32_t K_SBO = (BK == 32) ? 1024u : 512u, K_LT = (BK == 32) ? 2u : 4u, MN_LBO = 128u * BK;
+		const uint32_t a_lbo = p.a_mn ? MN_LBO : 0u, a_sbo = p.a_mn ? 512u : K_SBO, a_kstep = p.a_mn ? 1024u : 32u;
+		const uint32_t b_lbo = p.b_mn ? MN_LBO : 0u, b_sbo = p.b_mn ? 512u : K_SBO, b_kstep = p.b_mn ? 1024u : 32u;
+		const uint32_t a_lt = p.a_mn ? 1u : K_LT, b_lt = p.b_mn ? 1u : K_LT;
 		bool ok = true;
 		for (int kb = 0; kb < KB && ok; ++kb)
 		{
@@ -420,7 +429,7 @@ EncodeTiledFn encode_fn()
 
 // Operand X(r, k), r in [0, R): mn == 0: X[r*ld + k] (K-contiguous), box = 32 k x box_r rows;
 // mn == 1: X[k*ld + r] (row-contiguous in r), viewed as [r/32][k][r%32], box = 32 x 32 k x box_r/32.
-bool make_map(CUtensorMap* m, const float* ptr, int mn, long long R, long long K, long long ld, int box_r)
+bool make_map(CUtensorMap* m, const float* ptr, int mn, long long R, long long K, long long ld, int box_r, int bk)
 {
 	EncodeTiledFn fn = encode_fn();
 	if (!fn) return false;
@@ -429,16 +438,17 @@ bool make_map(CUtensorMap* m, const float* ptr, int mn, long long R, long long K
 	{
 		cuuint64_t dim[2] = {(cuuint64_t)K, (cuuint64_t)R};
 		cuuint64_t str[1] = {(cuuint64_t)ld * 4};
-		cuuint32_t box[2] = {(cuuint32_t)TC_BK, (cuuint32_t)box_r};
+		cuuint32_t box[2] = {(cuuint32_t)bk, (cuuint32_t)box_r};
 		cuuint32_t es[2] = {1, 1};
 		r = fn(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, (void*)ptr, dim, str, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
-		       CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+		       bk == 32 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+		       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
 	}
 	else
 	{
 		cuuint64_t dim[3] = {32, (cuuint64_t)K, (cuuint64_t)(R / 32)};
 		cuuint64_t str[2] = {(cuuint64_t)ld * 4, 128};
-		cuuint32_t box[3] = {32, (cuuint32_t)TC_BK, (cuuint32_t)(box_r / 32)};
+		cuuint32_t box[3] = {32, (cuuint32_t)bk, (cuuint32_t)(box_r / 32)};
 		cuuint32_t es[3] = {1, 1, 1};
 		r = fn(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, (void*)ptr, dim, str, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
 		       CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -446,20 +456,20 @@ bool make_map(CUtensorMap* m, const float* ptr, int mn, long long R, long long K
 	return r == CUDA_SUCCESS;
 }
 
-template <int BN, int STAGES>
+template <int BN, int BK, int STAGES>
 cudaError_t launch_cfg(const CUtensorMap& mA, const CUtensorMap& mAl, const CUtensorMap& mB, const CUtensorMap& mBl,
                        const TcParams& p, int M, int N, cudaStream_t s)
 {
-	using S = TcSmem<BN, STAGES>;
+	using S = TcSmem<BN, BK, STAGES>;
 	static bool attr_set = false;
 	if (!attr_set)
 	{
-		cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
+		cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, BK, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
 		if (e != cudaSuccess) return e;
 		attr_set = true;
 	}
 	dim3 grid(N / BN, M / TC_BM);
-	gemm_tc_kernel<BN, STAGES><<<grid, S::THREADS, S::TOTAL, s>>>(mA, mAl, mB, mBl, p);
+	gemm_tc_kernel<BN, BK, STAGES><<<grid, S::THREADS, S::TOTAL, s>>>(mA, mAl, mB, mBl, p);
 	return cudaGetLastError();
 }
 
@@ -503,8 +513,8 @@ __global__ void __launch_bounds__(256) scale_split_lo_kernel(const float* __rest
 
 bool tc_gemm_supported(const GemmArgs& g)
 {
-	if (g.M < TC_BM || g.N < 128 || g.K < TC_BK) return false;
-	if (g.M % TC_BM || g.N % 128 || g.K % TC_BK) return false;
+	if (g.M < TC_BM || g.N < 128 || g.K < TC_KALIGN) return false;
+	if (g.M % TC_BM || g.N % 128 || g.K % TC_KALIGN) return false;
 	if (g.kscale) return false;
 	const bool a_k = (g.a_sk == 1), a_mn = (g.a_sm == 1);
 	const bool b_k = (g.b_sk == 1), b_mn = (g.b_sn == 1);
@@ -524,9 +534,18 @@ cudaError_t launch_gemm_tc(const GemmArgs& g, const float* A_lo, const float* B_
 	const int b_mn = (g.b_sk == 1) ? 0 : 1;
 	const long long lda = a_mn ? g.a_sk : g.a_sm, ldb = b_mn ? g.b_sk : g.b_sn;
 	const int BN = (g.N % 256 == 0) ? 256 : 128;
+	// tile variant: 16-deep k-blocks with twice the stages by default; GLADES_TC_BK=32 selects the
+	// 32-deep blocks (kept for comparison runs)
+	static int bk_choice = 0;
+	if (!bk_choice)
+	{
+		const char* e = getenv("GLADES_TC_BK");
+		bk_choice = (e && atoi(e) == 32) ? 32 : 16;
+	}
+	const int bk = bk_choice;
 	CUtensorMap mA, mAl, mB, mBl;
-	if (!make_map(&mA, g.A, a_mn, g.M, g.K, lda, TC_BM) || !make_map(&mAl, A_lo, a_mn, g.M, g.K, lda, TC_BM) ||
-	    !make_map(&mB, g.B, b_mn, g.N, g.K, ldb, BN) || !make_map(&mBl, B_lo, b_mn, g.N, g.K, ldb, BN))
+	if (!make_map(&mA, g.A, a_mn, g.M, g.K, lda, TC_BM, bk) || !make_map(&mAl, A_lo, a_mn, g.M, g.K, lda, TC_BM, bk) ||
+	    !make_map(&mB, g.B, b_mn, g.N, g.K, ldb, BN, bk) || !make_map(&mBl, B_lo, b_mn, g.N, g.K, ldb, BN, bk))
 		return cudaErrorInvalidValue;
 	TcParams p;
 	p.C = g.C;
@@ -543,8 +562,13 @@ cudaError_t launch_gemm_tc(const GemmArgs& g, const float* A_lo, const float* B_
 	p.alpha = g.alpha;
 	p.colterm = g.colterm;
 	p.err_flag = err_flag;
-	if (BN == 256) return launch_cfg<256, 2>(mA, mAl, mB, mBl, p, g.M, g.N, s);
-	return launch_cfg<128, 3>(mA, mAl, mB, mBl, p, g.M, g.N, s);
+	if (bk == 32)
+	{
+		if (BN == 256) return launch_cfg<256, 32, 2>(mA, mAl, mB, mBl, p, g.M, g.N, s);
+		return launch_cfg<128, 32, 3>(mA, mAl, mB, mBl, p, g.M, g.N, s);
+	}
+	if (BN == 256) return launch_cfg<256, 16, 4>(mA, mAl, mB, mBl, p, g.M, g.N, s);
+	return launch_cfg<128, 16, 6>(mA, mAl, mB, mBl, p, g.M, g.N, s);
 }
 
 cudaError_t launch_split_lo(const float* src, float* lo, long long count, cudaStream_t s)
