@@ -48,6 +48,7 @@ struct TcParams
 	float alpha;
 	const float* colterm;
 	int* err_flag;
+	int tiles_m, tiles_n;  // the CTAs walk the tiles_m * tiles_n output tiles persistently
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -192,10 +193,25 @@ __global__ void __launch_bounds__(TcSmem<BN, BK, STAGES>::THREADS, 1)
 
 	const int warp = threadIdx.x >> 5;
 	const int lane = threadIdx.x & 31;
-	const int m0 = blockIdx.y * TC_BM;
-	const int n0 = blockIdx.x * BN;
 	const int KB = p.K / TC_BK;
 	const int NCHUNK = (KB + TC_CHUNK_KB - 1) / TC_CHUNK_KB;
+	// Persistent CTAs: tile t of this CTA is blockIdx.x + i * gridDim.x.  Tiles are numbered m-fastest
+	// inside bands of TC_BAND m-tiles, so that the CTAs running at one time share a band of A rows
+	// and a few B column blocks in L2.  All three roles walk the same sequence; the stage and
+	// accumulator barriers simply keep counting across tiles, which lets the producer and the MMA lane
+	// run ahead into the next tile while the epilogue warps still store the previous one.
+	const int total_tiles = p.tiles_m * p.tiles_n;
+	constexpr int TC_BAND = 16;
+	auto tile_origin = [&](int t, int& m0, int& n0) {
+		const int band_tiles = TC_BAND * p.tiles_n;
+		const int band = t / band_tiles;
+		const int in_band = t - band * band_tiles;
+		const int band_m = min(TC_BAND, p.tiles_m - band * TC_BAND);
+		const int mt = band * TC_BAND + in_band % band_m;
+		const int nt = in_band / band_m;
+		m0 = mt * TC_BM;
+		n0 = nt * BN;
+	};
 
 	if (threadIdx.x == 0)
 	{
@@ -228,11 +244,21 @@ __global__ void __launch_bounds__(TcSmem<BN, BK, STAGES>::THREADS, 1)
 	{
 		// ------------------------------------------------ TMA producer
 		int issued = 0;
-		for (int kb = 0; kb < KB; ++kb)
+		int it = 0;  // k-blocks issued so far, over all tiles
+		bool ok = true;
+		for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x)
 		{
-			const int s = kb % STAGES;
-			const uint32_t ph = (uint32_t)(kb / STAGES) & 1u;
-			if (!mbar_wait(bar0 + 8 * (STAGES + s), ph ^ 1u, abort_flag, p.err_flag, 1)) break;
+		int m0, n0;
+		tile_origin(t, m0, n0);
+		for (int kb = 0; kb < KB; ++kb, ++it)
+		{
+			const int s = it % STAGES;
+			const uint32_t ph = (uint32_t)(it / STAGES) & 1u;
+			if (!mbar_wait(bar0 + 8 * (STAGES + s), ph ^ 1u, abort_flag, p.err_flag, 1))
+			{
+				ok = false;
+				break;
+			}
 			const uint32_t full = bar0 + 8 * s;
 			mbar_expect_tx(full, S::STAGE_BYTES);
 			const uint32_t sa = base + s * S::STAGE_BYTES;
@@ -260,7 +286,8 @@ __global__ void __launch_bounds__(TcSmem<BN, BK, STAGES>::THREADS, 1)
 				tma_load_2d(sb, &mapB, full, k0, n0);
 				tma_load_2d(sbl, &mapBlo, full, k0, n0);
 			}
-			issued = kb + 1;
+			issued = it + 1;
+		}
 		}
 		if (*abort_flag)
 		{
@@ -289,12 +316,16 @@ __global__ void __launch_bounds__(TcSmem<BN, BK, STAGES>::THREADS, 1)
 		const uint32_t b_lbo = p.b_mn ? MN_LBO : 0u, b_sbo = p.b_mn ? 512u : K_SBO, b_kstep = p.b_mn ? 1024u : 32u;
 		const uint32_t a_lt = p.a_mn ? 1u : K_LT, b_lt = p.b_mn ? 1u : K_LT;
 		bool ok = true;
-		for (int kb = 0; kb < KB && ok; ++kb)
+		int it = 0;  // k-blocks consumed so far, over all tiles
+		int gc = 0;  // accumulator chunks started so far, over all tiles
+		for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x)
+		for (int kb = 0; kb < KB && ok; ++kb, ++it)
 		{
-			const int s = kb % STAGES;
-			const uint32_t ph = (uint32_t)(kb / STAGES) & 1u;
-			const int chunk = kb / TC_CHUNK_KB;
-			const int kin = kb - chunk * TC_CHUNK_KB;
+			const int s = it % STAGES;
+			const uint32_t ph = (uint32_t)(it / STAGES) & 1u;
+			const int kin = kb % TC_CHUNK_KB;
+			if (kin == 0 && kb != 0) ++gc;
+			const int chunk = gc;
 			const int buf = chunk & 1;
 			const uint32_t tmem_d = tmem_base + (uint32_t)(buf * BN);
 			if (kin == 0)
@@ -331,6 +362,7 @@ __global__ void __launch_bounds__(TcSmem<BN, BK, STAGES>::THREADS, 1)
 			}
 			umma_commit(bar0 + 8 * (STAGES + s));  // frees the stage once these MMAs have read it
 			if (kin == TC_CHUNK_KB - 1 || kb == KB - 1) umma_commit(bar_acc_full + 8 * buf);  // chunk complete
+			if (kb == KB - 1) ++gc;  // the next tile starts a new chunk
 		}
 	}
 	else if (warp >= 2)
@@ -338,14 +370,19 @@ __global__ void __launch_bounds__(TcSmem<BN, BK, STAGES>::THREADS, 1)
 		// ------------------------------------------------ epilogue: drain chunks, then the layer epilogue
 		const int q = warp & 3;          // the tensor-memory lane quarter this warp may read
 		const int half = (warp - 2) >> 2;  // which 128 columns of the tile
+		bool ok = true;
+		int gc = 0;  // accumulator chunks drained so far, over all tiles
+		for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x)
+		{
+		int m0, n0;
+		tile_origin(t, m0, n0);
 		float acc[128];
 #pragma unroll
 		for (int i = 0; i < 128; ++i) acc[i] = 0.0f;
-		bool ok = true;
-		for (int chunk = 0; chunk < NCHUNK && ok; ++chunk)
+		for (int c_in = 0; c_in < NCHUNK && ok; ++c_in, ++gc)
 		{
-			const int buf = chunk & 1;
-			const uint32_t use = (uint32_t)(chunk >> 1);
+			const int buf = gc & 1;
+			const uint32_t use = (uint32_t)(gc >> 1);
 			if (!mbar_wait(bar_acc_full + 8 * buf, use & 1u, abort_flag, p.err_flag, 3))
 			{
 				ok = false;
@@ -397,6 +434,7 @@ __global__ void __launch_bounds__(TcSmem<BN, BK, STAGES>::THREADS, 1)
 				}
 				*reinterpret_cast<float4*>(crow + v * 4) = make_float4(o[0], o[1], o[2], o[3]);
 			}
+		}
 		}
 	}
 	asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -468,8 +506,19 @@ cudaError_t launch_cfg(const CUtensorMap& mA, const CUtensorMap& mAl, const CUte
 		if (e != cudaSuccess) return e;
 		attr_set = true;
 	}
-	dim3 grid(N / BN, M / TC_BM);
-	gemm_tc_kernel<BN, BK, STAGES><<<grid, S::THREADS, S::TOTAL, s>>>(mA, mAl, mB, mBl, p);
+	TcParams q = p;
+	q.tiles_m = M / TC_BM;
+	q.tiles_n = N / BN;
+	static int sm_count = 0;
+	if (!sm_count)
+	{
+		int dev = 0;
+		cudaGetDevice(&dev);
+		if (cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm_count < 1) sm_count = 148;
+	}
+	const int total = q.tiles_m * q.tiles_n;
+	const int grid = total < sm_count ? total : sm_count;
+	gemm_tc_kernel<BN, BK, STAGES><<<grid, S::THREADS, S::TOTAL, s>>>(mA, mAl, mB, mBl, q);
 	return cudaGetLastError();
 }
 
