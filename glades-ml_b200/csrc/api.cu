@@ -186,6 +186,12 @@ struct gl_net
 	nccl_comm comm = nullptr;
 	int globalRows = 0, firstPos = 0;
 	int bscaleRows = -1;
+	// gradient all-reduce overlapped with the rest of the backward pass
+	cudaStream_t commStream = nullptr;
+	cudaEvent_t evGrad[GL_MAX_WEIGHT_LAYERS + 1] = {};
+	cudaEvent_t evComm = nullptr;
+	int dpOverlap = 1;
+	int dpReserveSms = 8;
 };
 
 static NetView make_view(const gl_net* n)
@@ -320,7 +326,11 @@ extern "C" int gl_destroy(gl_net* n)
 	if (!n) return GL_OK;
 	cudaSetDevice(n->d.device);
 	if (n->stream) cudaStreamSynchronize(n->stream);
+	if (n->commStream) cudaStreamSynchronize(n->commStream);
 	if (n->comm && g_nccl.CommDestroy) g_nccl.CommDestroy(n->comm);
+	if (n->commStream) cudaStreamDestroy(n->commStream);
+	for (int l = 0; l <= GL_MAX_WEIGHT_LAYERS; ++l) if (n->evGrad[l]) cudaEventDestroy(n->evGrad[l]);
+	if (n->evComm) cudaEventDestroy(n->evComm);
 	free_work(n);
 	cudaFree(n->dWlo);
 	cudaFree(n->dW); cudaFree(n->dBias); cudaFree(n->dG); cudaFree(n->dBscale); cudaFree(n->dFlags);
@@ -765,6 +775,7 @@ static int batched_window(gl_net* n, const float* X, const float* Y, int rows, i
 			g.act = n->d.activation[l - 1];
 			g.par = 0.01f;  // the reference passes a fixed 0.01, network.cpp:618
 			n->loD[l] = false;
+			g.sm_reserve = (n->world > 1 && n->dpOverlap) ? n->dpReserveSms : 0;
 			if (int r = run_gemm(n, g, opD, op_w(n, l), &launches)) return r;
 		}
 		const float* colterm = nullptr;
@@ -785,6 +796,7 @@ static int batched_window(gl_net* n, const float* X, const float* Y, int rows, i
 			g.epi = EPI_GRAD;
 			g.alpha = n->d.lr[l];
 			g.colterm = colterm;
+			g.sm_reserve = (n->world > 1 && n->dpOverlap && L <= n->H) ? n->dpReserveSms : 0;
 			if (int r = run_gemm(n, g, opD, op_act(n, l, X, rows), &launches)) return r;
 		}
 		if (l >= 1)
@@ -792,13 +804,36 @@ static int batched_window(gl_net* n, const float* X, const float* Y, int rows, i
 			CU(launch_sum_scaled(n->dD[L], (int64_t)rows * no, n->d.lr[l], n->dG + n->nw + l, n->stream));
 			++launches;
 		}
+		if (n->world > 1 && n->dpOverlap)
+		{
+			// this layer's gradient is complete: reduce it on the communication stream while the main
+			// stream goes on with the layers below
+			CU(cudaEventRecord(n->evGrad[l], n->stream));
+			CU(cudaStreamWaitEvent(n->commStream, n->evGrad[l], 0));
+			NC(g_nccl.AllReduce(n->dG + n->woff[l], n->dG + n->woff[l], (size_t)(n->woff[l + 1] - n->woff[l]), NCCL_FLOAT32,
+			                    NCCL_SUM, n->comm, n->commStream));
+		}
 	}
 	if (n->world > 1)
 	{
-		NC(g_nccl.GroupStart());
-		NC(g_nccl.AllReduce(n->dG, n->dG, (size_t)(n->nw + GL_MAX_WEIGHT_LAYERS), NCCL_FLOAT32, NCCL_SUM, n->comm, n->stream));
-		NC(g_nccl.AllReduce(n->dSums, n->dSums, 2, NCCL_FLOAT64, NCCL_SUM, n->comm, n->stream));
-		NC(g_nccl.GroupEnd());
+		if (n->dpOverlap)
+		{
+			CU(cudaEventRecord(n->evGrad[GL_MAX_WEIGHT_LAYERS], n->stream));
+			CU(cudaStreamWaitEvent(n->commStream, n->evGrad[GL_MAX_WEIGHT_LAYERS], 0));
+			NC(g_nccl.GroupStart());
+			NC(g_nccl.AllReduce(n->dG + n->nw, n->dG + n->nw, (size_t)GL_MAX_WEIGHT_LAYERS, NCCL_FLOAT32, NCCL_SUM, n->comm, n->commStream));
+			NC(g_nccl.AllReduce(n->dSums, n->dSums, 2, NCCL_FLOAT64, NCCL_SUM, n->comm, n->commStream));
+			NC(g_nccl.GroupEnd());
+			CU(cudaEventRecord(n->evComm, n->commStream));
+			CU(cudaStreamWaitEvent(n->stream, n->evComm, 0));
+		}
+		else
+		{
+			NC(g_nccl.GroupStart());
+			NC(g_nccl.AllReduce(n->dG, n->dG, (size_t)(n->nw + GL_MAX_WEIGHT_LAYERS), NCCL_FLOAT32, NCCL_SUM, n->comm, n->stream));
+			NC(g_nccl.AllReduce(n->dSums, n->dSums, 2, NCCL_FLOAT64, NCCL_SUM, n->comm, n->stream));
+			NC(g_nccl.GroupEnd());
+		}
 	}
 	if (n->bscaleRows != global_rows)
 	{
@@ -1144,6 +1179,11 @@ extern "C" int gl_dp_init(gl_net* n, int32_t rank, int32_t world, const void* id
 	nccl_uid id;
 	memcpy(&id, id128, sizeof id);
 	NC(g_nccl.CommInitRank(&n->comm, world, id, rank));
+	CU(cudaStreamCreateWithFlags(&n->commStream, cudaStreamNonBlocking));
+	for (int l = 0; l <= GL_MAX_WEIGHT_LAYERS; ++l) CU(cudaEventCreateWithFlags(&n->evGrad[l], cudaEventDisableTiming));
+	CU(cudaEventCreateWithFlags(&n->evComm, cudaEventDisableTiming));
+	if (const char* e = getenv("GLADES_DP_OVERLAP")) n->dpOverlap = atoi(e) != 0;
+	if (const char* e = getenv("GLADES_DP_RESERVE_SMS")) n->dpReserveSms = atoi(e);
 	return GL_OK;
 }
 

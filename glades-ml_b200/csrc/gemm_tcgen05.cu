@@ -496,7 +496,7 @@ bool make_map(CUtensorMap* m, const float* ptr, int mn, long long R, long long K
 
 template <int BN, int BK, int STAGES>
 cudaError_t launch_cfg(const CUtensorMap& mA, const CUtensorMap& mAl, const CUtensorMap& mB, const CUtensorMap& mBl,
-                       const TcParams& p, int M, int N, cudaStream_t s)
+                       const TcParams& p, int M, int N, int sm_reserve, cudaStream_t s)
 {
 	using S = TcSmem<BN, BK, STAGES>;
 	static bool attr_set = false;
@@ -517,7 +517,9 @@ cudaError_t launch_cfg(const CUtensorMap& mA, const CUtensorMap& mAl, const CUte
 		if (cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm_count < 1) sm_count = 148;
 	}
 	const int total = q.tiles_m * q.tiles_n;
-	const int grid = total < sm_count ? total : sm_count;
+	int avail = sm_count - sm_reserve;
+	if (avail < 1) avail = 1;
+	const int grid = total < avail ? total : avail;
 	gemm_tc_kernel<BN, BK, STAGES><<<grid, S::THREADS, S::TOTAL, s>>>(mA, mAl, mB, mBl, q);
 	return cudaGetLastError();
 }
@@ -613,11 +615,11 @@ cudaError_t launch_gemm_tc(const GemmArgs& g, const float* A_lo, const float* B_
 	p.err_flag = err_flag;
 	if (bk == 32)
 	{
-		if (BN == 256) return launch_cfg<256, 32, 2>(mA, mAl, mB, mBl, p, g.M, g.N, s);
-		return launch_cfg<128, 32, 3>(mA, mAl, mB, mBl, p, g.M, g.N, s);
+		if (BN == 256) return launch_cfg<256, 32, 2>(mA, mAl, mB, mBl, p, g.M, g.N, g.sm_reserve, s);
+		return launch_cfg<128, 32, 3>(mA, mAl, mB, mBl, p, g.M, g.N, g.sm_reserve, s);
 	}
-	if (BN == 256) return launch_cfg<256, 16, 4>(mA, mAl, mB, mBl, p, g.M, g.N, s);
-	return launch_cfg<128, 16, 6>(mA, mAl, mB, mBl, p, g.M, g.N, s);
+	if (BN == 256) return launch_cfg<256, 16, 4>(mA, mAl, mB, mBl, p, g.M, g.N, g.sm_reserve, s);
+	return launch_cfg<128, 16, 6>(mA, mAl, mB, mBl, p, g.M, g.N, g.sm_reserve, s);
 }
 
 cudaError_t launch_split_lo(const float* src, float* lo, long long count, cudaStream_t s)

@@ -70,6 +70,7 @@ struct GemmArgs
 	long long ld_aux;
 	float alpha;
 	const float* colterm;
+	int sm_reserve;        // tensor-core kernel: leave this many SMs without a CTA (for a concurrent collective)
 };
 cudaError_t launch_gemm_ffma(const GemmArgs& g, cudaStream_t s);
 
