@@ -909,6 +909,54 @@ extern "C" int gl_train_window_host(gl_net* n, const float* x, const float* y, i
 	return batched_window(n, n->dXwin, n->dYwin, rows, win_rows, out);
 }
 
+// Batched mode, small network: every weight fits in shared memory, so whole epochs run in one launch
+// of the fused kernel (GLADES_SMALL_FUSED=0 keeps the per-layer kernels instead).
+static bool small_fused_ok(const gl_net* n)
+{
+	if (n->world > 1 || n->d.gemm == GL_GEMM_TCGEN05) return false;
+	static int enabled = -1;
+	if (enabled < 0)
+	{
+		const char* e = getenv("GLADES_SMALL_FUSED");
+		enabled = (e && atoi(e) == 0) ? 0 : 1;
+	}
+	if (!enabled) return false;
+	const NetView v = make_view(n);
+	return small_fused_smem_bytes(v) <= (size_t)200 * 1024;
+}
+
+static int small_fused_train(gl_net* n, int n_epochs, gl_metrics* out)
+{
+	double* dEpoch = nullptr;
+	CU(cudaMalloc(&dEpoch, (size_t)2 * n_epochs * sizeof(double)));
+	SmallFusedArgs a;
+	memset(&a, 0, sizeof a);
+	a.net = make_view(n);
+	a.X = n->dX;
+	a.Y = n->dY;
+	a.rows = n->rows;
+	a.n_epochs = n_epochs;
+	a.bias_rule = n->d.bias_rule;
+	a.epoch_sums = dEpoch;
+	a.confusion = n->dConf;
+	a.last_out = n->dLastOut;
+	a.flags = n->dFlags;
+	CU(cudaEventRecord(n->ev0, n->stream));
+	cudaError_t e = launch_small_fused(a, n->stream);
+	if (e == cudaSuccess) e = cudaEventRecord(n->ev1, n->stream);
+	if (e == cudaSuccess) e = cudaStreamSynchronize(n->stream);
+	double sums[2] = {0, 0};
+	if (e == cudaSuccess) e = cudaMemcpy(sums, dEpoch + 2 * (n_epochs - 1), sizeof sums, cudaMemcpyDeviceToHost);
+	cudaFree(dEpoch);
+	if (e != cudaSuccess) return fail(GL_ERR_CUDA, "fused small-network kernel: %s", cudaGetErrorString(e));
+	n->launches += 1;
+	n->epochs += n_epochs;
+	n->loW = false;
+	float ms = 0;
+	CU(cudaEventElapsedTime(&ms, n->ev0, n->ev1));
+	return finish_metrics(n, out, (float)sums[0], (float)sums[1], n->rows, ms, 1, true);
+}
+
 extern "C" int gl_train_epochs(gl_net* n, int32_t n_epochs, gl_metrics* out)
 {
 	if (!n || n_epochs < 1) return fail(GL_ERR_INVALID, "gl_train_epochs: bad argument");
@@ -916,6 +964,7 @@ extern "C" int gl_train_epochs(gl_net* n, int32_t n_epochs, gl_metrics* out)
 	if (int r = use_device(n)) return r;
 	n->stop = 0;
 	if (n->d.mode == GL_MODE_REFERENCE) return ref_train(n, n_epochs, out);
+	if (small_fused_ok(n)) return small_fused_train(n, n_epochs, out);
 	// batched mode: aligned windows of batch_size rows; epoch figures are sums over the windows
 	const int mb = n->d.batch_size;
 	gl_metrics last;

@@ -100,6 +100,23 @@ cudaError_t launch_decay_colterm(const float* A, int rows, int n, const float* c
 cudaError_t launch_update(float* W, const float* G, long long count, float inv_mb, float* bias, const float* gb,
                           const float* bscale, int H, int* flags, cudaStream_t s);
 
+// ---- batched mode, whole small network in shared memory (small_fused.cu) -------------------------
+struct SmallFusedArgs
+{
+	NetView net;
+	const float* X;
+	const float* Y;
+	long long rows;
+	int n_epochs;
+	int bias_rule;
+	double* epoch_sums;  // [n_epochs][2]: cost sum, accuracy sum
+	int* confusion;      // [n_out][n_out], counts of the last epoch
+	float* last_out;     // [n_out]
+	int* flags;
+};
+size_t small_fused_smem_bytes(const NetView& n);
+cudaError_t launch_small_fused(const SmallFusedArgs& a, cudaStream_t s);
+
 // ---- synthetic inputs (synth.cu) ---------------------------------------------------------------
 cudaError_t launch_synth_fill(float* out, long long n, unsigned long long seed, unsigned stream_id, int dist,
                               float scale, float offset, cudaStream_t s);

@@ -402,3 +402,68 @@ def test_synth_fill_matches_cpu_generator(g, oracle):
     assert np.max(np.abs(host - cpu)) <= 1e-6  # normal stream: double libm on both sides, then one rounding
     assert abs(float(host.mean())) < 0.02 and abs(float(host.std()) - 1.0) < 0.02
     L.gl_device_free(p, 0)
+
+
+SMALL_FUSED_CASES = [
+    # sizes, acts, out, rows, mb, momentum, wd1, wd2, bias_rule, epochs
+    ([10, 32, 32, 1], ["tanh", "tanh", "sigmoid"], "regression", 1024, 32, 0.0, 0.0, 0.0, 0, 3),
+    ([4, 16, 3], ["sigmoid", "softmax"], "classification", 150, 1, 0.9, 0.0, 0.0, 0, 2),
+    ([7, 9, 5, 4], ["relu", "leaky", "sigmoid"], "regression", 77, 16, 0.7, 0.001, 0.002, 1, 3),
+    ([33, 40, 2], ["tanh", "linear"], "regression", 50, 64, 0.5, 0.0, 0.0, 0, 2),
+]
+
+
+@pytest.mark.parametrize("case", SMALL_FUSED_CASES, ids=lambda c: "-".join(map(str, c[0])) + "_mb%d" % c[4])
+def test_small_network_fused_epochs_vs_restatement(g, oracle, case):
+    """Batched-mode epochs of a network whose weights fit in shared memory run in the fused
+    whole-network kernel (one launch); checked window by window against the restatement."""
+    sizes, acts, out, rows, mb, mom, wd1, wd2, brule, epochs = case
+    rng = np.random.default_rng(len(sizes) * 1000 + rows)
+    params = [0.05 if a == "leaky" else 1.0 for a in acts]
+    d = g.make_desc(sizes, acts, out, batch=mb, lr=0.005 if brule else 0.05, momentum=mom, wd1=wd1, wd2=wd2,
+                    params=params, mode=g.MODE_BATCHED, bias_rule=brule)
+    if sizes == [10, 32, 32, 1]:
+        idx = np.arange(1024)
+        x = ((idx[:, None] >> np.arange(9, -1, -1)) & 1).astype(np.float32)
+        y = (x.sum(1) % 2).astype(np.float32)[:, None]
+    else:
+        x = rng.standard_normal((rows, sizes[0])).astype(np.float32)
+        if acts[-1] == "softmax":
+            y = np.zeros((rows, sizes[-1]), np.float32)
+            y[np.arange(rows), rng.integers(0, sizes[-1], rows)] = 1.0
+        elif out == "classification":
+            y = np.full((rows, sizes[-1]), 0.01, np.float32)
+            y[np.arange(rows), rng.integers(0, sizes[-1], rows)] = 0.99
+        else:
+            y = rng.uniform(0.05, 0.95, (rows, sizes[-1])).astype(np.float32)
+    w, b = _rand_net(rng, sizes)
+    net = g.Net(d)
+    net.set_weights(w, b)
+    net.set_data(x, y)
+    S = oracle.Restate(d, x, y, g.Metrics)
+    S.set_weights(w, b)
+    l0 = net.kernel_launches()
+    m = net.train_epochs(epochs)
+    assert net.kernel_launches() - l0 == 1, "the whole call must be one launch of the fused kernel"
+    for ep in range(epochs):
+        cm = np.zeros((sizes[-1], sizes[-1]), np.int32)
+        cost = acc = 0.0
+        for r0 in range(0, rows, mb):
+            cnt = min(mb, rows - r0)
+            gr = S.window_grad(r0, cnt, confusion=cm)
+            S.window_apply(gr, cnt)
+            cost += gr[-2]
+            acc += gr[-1]
+    wg, bg = net.get_weights()
+    ws, bs = S.get_weights()
+    assert np.isfinite(ws).all(), "the case itself must stay finite"
+    ok, err = tensor_close(wg, ws, 2e-5 if epochs * (rows // mb + 1) > 50 else RTOL)
+    assert ok, err
+    assert np.allclose(bg, bs, rtol=2e-4, atol=2e-6), (bg, bs)
+    assert abs(m.total_error - cost) <= 2e-5 * max(1.0, abs(cost))
+    assert abs(m.total_accuracy - acc / (rows * sizes[-1])) <= 2e-3
+    if out != "regression":
+        diff = int(np.abs(net.confusion() - cm).sum())
+        assert diff <= (2 if epochs * rows > 200 else 0), "confusion counts differ by %d" % diff
+    assert net.epochs() == epochs
+    net.close()
