@@ -270,13 +270,109 @@ def run_reference_arm(args, g, w, rank, world):
     print(json.dumps(line), flush=True)
 
 
+SMALL = {
+    # config 1 at the only learning rate where the reference stays finite (0.01, interleaved class rows)
+    "tiny_classifier": dict(sizes=[4, 16, 3], acts=["sigmoid", "sigmoid"], out="classification", batch=1, lr=0.01,
+                            momentum=0.9, rows=150, epochs=200, modes=["reference"]),
+    # config 2: all 2^10 binary vectors, parity target
+    "parity_net": dict(sizes=[10, 32, 32, 1], acts=["tanh", "tanh", "sigmoid"], out="regression", batch=32, lr=0.05,
+                       momentum=0.0, rows=1024, epochs=500, modes=["reference", "batched"]),
+}
+
+
+def small_data(name, w):
+    rng = np.random.default_rng(SEED + 1)
+    if name == "parity_net":
+        idx = np.arange(1024)
+        x = ((idx[:, None] >> np.arange(9, -1, -1)) & 1).astype(np.float32)
+        y = (x.sum(1) % 2).astype(np.float32)[:, None]
+        a = 1.0
+    else:
+        means = rng.uniform(-2, 2, (3, 4))
+        cls = np.arange(w["rows"]) % 3
+        x = (means[cls] + 0.5 * rng.standard_normal((w["rows"], 4))).astype(np.float32)
+        y = np.full((w["rows"], 3), 0.01, np.float32)
+        y[np.arange(w["rows"]), cls] = 0.99
+        a = 0.5
+    nw = sum(w["sizes"][i] * w["sizes"][i + 1] for i in range(len(w["sizes"]) - 1))
+    return x, y, rng.uniform(-a, a, nw).astype(np.float32)
+
+
+def run_small(args, g, name):
+    """The two small configs (sequential by construction, one GPU): whole training runs in one launch.
+    One step = `epochs` epochs over the data set; value = samples/s; the CPU figure beside it is the
+    reference's own compiled code (oracle/_ref) when it is present, else the CPU port."""
+    w = SMALL[name]
+    x, y, w0 = small_data(name, w)
+    peaks = measured_peaks()
+    o = ge.import_oracle()
+    for mode_name in w["modes"]:
+        mode = g.MODE_REFERENCE if mode_name == "reference" else g.MODE_BATCHED
+        d = g.make_desc(w["sizes"], w["acts"], w["out"], batch=w["batch"], lr=w["lr"], momentum=w["momentum"], mode=mode)
+        net = g.Net(d)
+        times, e2e = [], []
+        for i in range(args.warmup + args.steps):
+            t0 = time.perf_counter()
+            net.set_weights(w0, None)
+            net.set_data(x, y)                       # host rows in, every step
+            m = net.train_epochs(w["epochs"])        # metrics (loss) read back
+            dt = time.perf_counter() - t0
+            if i >= args.warmup:
+                times.append(m.device_ms / 1000.0)
+                e2e.append(dt)
+        samples = w["rows"] * w["epochs"]
+        value = samples / float(np.mean(times))
+        bytes_per_sample = 4 * (w["sizes"][0] + w["sizes"][-1])
+        t0 = time.perf_counter()
+        if mode_name == "reference" and o.have_reference():
+            R = o.Reference(d, x, y, g.Metrics)
+            R.set_weights(w0, None)
+            cpu_epochs = max(1, w["epochs"] // 10)
+            t0 = time.perf_counter()
+            R.train_public(cpu_epochs)
+            kind = "reference"
+        else:
+            S = o.Restate(d, x, y, g.Metrics)
+            S.set_weights(w0, None)
+            cpu_epochs = max(1, w["epochs"] // 10)
+            t0 = time.perf_counter()
+            for _ in range(cpu_epochs):
+                if mode_name == "reference":
+                    S.epoch(0)
+                else:
+                    for r0 in range(0, w["rows"], w["batch"]):
+                        S.train_window(r0, min(w["batch"], w["rows"] - r0))
+            kind = "port"
+        cpu_dt = time.perf_counter() - t0
+        line = {
+            "metric": "train_samples_per_s", "value": value, "unit": "samples/s", "n_gpus": 1, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": 1000.0 * float(np.mean(times)), "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": name, "sizes": w["sizes"], "mode": mode_name, "batch": w["batch"], "lr": w["lr"],
+                       "epochs_per_step": w["epochs"], "rows": w["rows"],
+                       "l2": "data set far smaller than L2: the run is a sequential dependent chain, not a bandwidth test"},
+            "e2e": {"value": samples / float(np.mean(e2e)), "unit": "samples/s",
+                    "h2d_bytes_per_step": int(x.nbytes + y.nbytes + w0.nbytes), "d2h_bytes_per_step": 32},
+            "gpu_launches": 1,
+            "roofline": {"bound": "hbm", "achieved": value * bytes_per_sample / 1e9, "peak": peaks["hbm"], "unit": "GB/s",
+                         "frac": value * bytes_per_sample / 1e9 / peaks["hbm"], "traffic": None,
+                         "note": "latency-bound: %s" % ("strictly sequential per-sample SGD" if mode_name == "reference"
+                                                        else "one window of %d rows at a time on one SM" % w["batch"])},
+            "cpu_baseline": {"value": w["rows"] * cpu_epochs / cpu_dt, "unit": "samples/s", "cores": 1, "kind": kind,
+                             "sample": "%d epochs (%.1f s)" % (cpu_epochs, cpu_dt)},
+            "final_accuracy": m.total_accuracy, "nonfinite": m.nonfinite,
+        }
+        print(json.dumps(line), flush=True)
+        net.close()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="wide_mlp", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="wide_mlp", choices=sorted(WORKLOADS) + sorted(SMALL))
     ap.add_argument("--windows", type=int, default=0, help="resident windows per GPU (default: steps+warmup, max 64)")
     ap.add_argument("--gemm", default="auto", choices=["auto", "ffma", "tcgen05"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -285,8 +381,12 @@ def main():
         args.warmup = 3
 
     rank, world, local = dist_env()
-    w = WORKLOADS[args.workload]
     g = ge.import_package()
+    if args.workload in SMALL:
+        if rank == 0 and args.impl == "ours":
+            run_small(args, g, args.workload)
+        return
+    w = WORKLOADS[args.workload]
     if args.impl == "reference":
         run_reference_arm(args, g, w, rank, world)
         return

@@ -610,7 +610,7 @@ struct Operand
 
 // Runs one layer product on the tensor-core kernel when its shape fits (and the network allows it),
 // else on the exact-fp32 FFMA kernel.
-static int run_gemm(gl_net* n, GemmArgs g, Operand a, Operand b, int64_t* launches)
+static int run_gemm(gl_net* n, GemmArgs g, Operand a, Operand b, int64_t* launches, bool* used_tc = nullptr)
 {
 	bool tc = false;
 	if (n->d.gemm != GL_GEMM_FFMA && a.lo_all && b.lo_all)
@@ -620,6 +620,8 @@ static int run_gemm(gl_net* n, GemmArgs g, Operand a, Operand b, int64_t* launch
 		tc = tc_gemm_supported(probe) &&
 		     (n->d.gemm == GL_GEMM_TCGEN05 || (long long)g.M * g.N * g.K >= (1ll << 24));
 	}
+	if (used_tc) *used_tc = tc;
+	if (!tc) g.C_lo = nullptr;
 	cudaEvent_t pe0 = nullptr, pe1 = nullptr;
 	if (n->profile)
 	{
@@ -674,6 +676,20 @@ static int run_gemm(gl_net* n, GemmArgs g, Operand a, Operand b, int64_t* launch
 	return 0;
 }
 
+// Writing the low TF32 part of a product's output from the tensor-core epilogue saves a split pass but
+// doubles the epilogue's store burst, which measured slower on the wide-MLP step (185.9 vs 197
+// TFLOP/s); it stays off unless GLADES_TC_FUSE_LO=1.  The head and update kernels always fuse theirs.
+static bool fuse_lo_in_epilogue()
+{
+	static int v = -1;
+	if (v < 0)
+	{
+		const char* e = getenv("GLADES_TC_FUSE_LO");
+		v = (e && atoi(e) == 1) ? 1 : 0;
+	}
+	return v == 1;
+}
+
 // all weight layers share one flat low-part buffer and one flag: it is refreshed as a whole
 static Operand op_w(gl_net* n, int l)
 {
@@ -718,8 +734,12 @@ static int batched_forward(gl_net* n, const float* X, int rows, int64_t* launche
 		g.bias_ptr = (l >= 1) ? n->dBias + l : nullptr;
 		g.act = n->d.activation[l];
 		g.par = n->d.act_param[l];
-		n->loA[l + 1] = false;
-		if (int r = run_gemm(n, g, op_act(n, l, X, rows), op_w(n, l), launches)) return r;
+		// the tensor-core epilogue also writes the low TF32 part of its output, so the next layer's
+		// products need no separate split pass (not for the last layer: the head rewrites it)
+		g.C_lo = (l < n->H && fuse_lo_in_epilogue()) ? n->dAlo[l + 1] : nullptr;
+		bool tc = false;
+		if (int r = run_gemm(n, g, op_act(n, l, X, rows), op_w(n, l), launches, &tc)) return r;
+		n->loA[l + 1] = tc && g.C_lo != nullptr;
 		in = n->dA[l + 1];
 	}
 	return 0;
@@ -742,6 +762,7 @@ static int batched_window(gl_net* n, const float* X, const float* Y, int rows, i
 	h.P = n->dA[n->H + 1];
 	h.Y = Y;
 	h.D = n->dD[n->H + 1];
+	h.D_lo = n->dDlo[n->H + 1];
 	h.rows = rows;
 	h.n = n->n_out;
 	h.out_type = n->d.output_type;
@@ -751,7 +772,7 @@ static int batched_window(gl_net* n, const float* X, const float* Y, int rows, i
 	h.confusion = (n->d.output_type != GL_OUT_REGRESSION) ? n->dConf : nullptr;
 	CU(launch_head(h, n->stream));
 	++launches;
-	n->loD[n->H + 1] = false;
+	n->loD[n->H + 1] = n->dDlo[n->H + 1] != nullptr;
 	n->loA[n->H + 1] = false;  // the softmax head rewrote the last activations in place
 	CU(cudaMemcpyAsync(n->dLastOut, n->dA[n->H + 1] + (size_t)(rows - 1) * n->n_out, (size_t)n->n_out * sizeof(float),
 	                   cudaMemcpyDeviceToDevice, n->stream));
@@ -774,9 +795,11 @@ static int batched_window(gl_net* n, const float* X, const float* Y, int rows, i
 			g.aux = n->dA[l]; g.ld_aux = ni;
 			g.act = n->d.activation[l - 1];
 			g.par = 0.01f;  // the reference passes a fixed 0.01, network.cpp:618
-			n->loD[l] = false;
+			g.C_lo = fuse_lo_in_epilogue() ? n->dDlo[l] : nullptr;
 			g.sm_reserve = (n->world > 1 && n->dpOverlap) ? n->dpReserveSms : 0;
-			if (int r = run_gemm(n, g, opD, op_w(n, l), &launches)) return r;
+			bool tc = false;
+			if (int r = run_gemm(n, g, opD, op_w(n, l), &launches, &tc)) return r;
+			n->loD[l] = tc && g.C_lo != nullptr;
 		}
 		const float* colterm = nullptr;
 		if (n->d.wd1[l] != 0.0f || n->d.wd2[l] != 0.0f)
@@ -844,10 +867,10 @@ static int batched_window(gl_net* n, const float* X, const float* Y, int rows, i
 		CU(cudaStreamSynchronize(n->stream));
 		n->bscaleRows = global_rows;
 	}
-	CU(launch_update(n->dW, n->dG, n->nw, 1.0f / (float)global_rows, n->dBias, n->dG + n->nw, n->dBscale, n->H,
+	CU(launch_update(n->dW, n->dWlo, n->dG, n->nw, 1.0f / (float)global_rows, n->dBias, n->dG + n->nw, n->dBscale, n->H,
 	                 n->dFlags, n->stream));
 	++launches;
-	n->loW = false;
+	n->loW = n->dWlo != nullptr;
 	CU(cudaEventRecord(n->ev1, n->stream));
 	n->launches += launches;
 	if (out)

@@ -153,6 +153,7 @@ __global__ void __launch_bounds__(256) head_kernel(const HeadArgs h)
 				p[o] = pv;
 				cost = (e != 0.0f) ? -(e * logf(pv)) / h.data_size : 0.0f;
 				if (h.D) h.D[r * h.n + o] = pv - e;
+				if (h.D_lo) h.D_lo[r * h.n + o] = tf32_lo(pv - e);
 			}
 			else
 			{
@@ -167,6 +168,7 @@ __global__ void __launch_bounds__(256) head_kernel(const HeadArgs h)
 					else if (h.out_type == GL_OUT_CLASSIFICATION) d = (pv - e) / ((1.0f - pv) * pv);
 					else d = -(e / pv);
 					h.D[r * h.n + o] = d;
+					if (h.D_lo) h.D_lo[r * h.n + o] = tf32_lo(d);
 				}
 			}
 			cost_acc += (double)cost;
@@ -271,8 +273,8 @@ cudaError_t launch_decay_colterm(const float* A, int rows, int n, const float* c
 
 // W -= G * inv_mb (Node::applyDeltas, State/node.cpp:294-307: the window sum is always divided by
 // the minibatch size); scalar biases; non-finite flag.
-__global__ void __launch_bounds__(256) update_kernel(float* W, const float* G, long long count, float inv_mb, float* bias,
-                                                      const float* gb, const float* bscale, int H, int* flags)
+__global__ void __launch_bounds__(256) update_kernel(float* W, float* W_lo, const float* G, long long count, float inv_mb,
+                                                      float* bias, const float* gb, const float* bscale, int H, int* flags)
 {
 	int bad = 0;
 	const long long stride = (long long)gridDim.x * blockDim.x;
@@ -287,12 +289,14 @@ __global__ void __launch_bounds__(256) update_kernel(float* W, const float* G, l
 		w.x -= g.x * inv_mb; w.y -= g.y * inv_mb; w.z -= g.z * inv_mb; w.w -= g.w * inv_mb;
 		if (!(isfinite(w.x) && isfinite(w.y) && isfinite(w.z) && isfinite(w.w))) bad = 1;
 		W4[i] = w;
+		if (W_lo) reinterpret_cast<float4*>(W_lo)[i] = make_float4(tf32_lo(w.x), tf32_lo(w.y), tf32_lo(w.z), tf32_lo(w.w));
 	}
 	for (long long i = n4 * 4 + i0; i < count; i += stride)
 	{
 		const float w = W[i] - G[i] * inv_mb;
 		if (!isfinite(w)) bad = 1;
 		W[i] = w;
+		if (W_lo) W_lo[i] = tf32_lo(w);
 	}
 	if (blockIdx.x == 0 && threadIdx.x >= 1 && threadIdx.x <= H)
 	{
@@ -303,13 +307,13 @@ __global__ void __launch_bounds__(256) update_kernel(float* W, const float* G, l
 	if (bad) atomicOr(flags, 1);
 }
 
-cudaError_t launch_update(float* W, const float* G, long long count, float inv_mb, float* bias, const float* gb,
+cudaError_t launch_update(float* W, float* W_lo, const float* G, long long count, float inv_mb, float* bias, const float* gb,
                           const float* bscale, int H, int* flags, cudaStream_t s)
 {
 	long long blocks = (count / 4 + 255) / 256;
 	if (blocks > 148 * 8) blocks = 148 * 8;
 	if (blocks < 1) blocks = 1;
-	update_kernel<<<(unsigned)blocks, 256, 0, s>>>(W, G, count, inv_mb, bias, gb, bscale, H, flags);
+	update_kernel<<<(unsigned)blocks, 256, 0, s>>>(W, W_lo, G, count, inv_mb, bias, gb, bscale, H, flags);
 	return cudaGetLastError();
 }
 

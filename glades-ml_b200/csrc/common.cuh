@@ -152,6 +152,16 @@ __device__ __forceinline__ float act_der_b(float a, int act, float p)
 	return 1.0f;
 }
 
+// Low TF32 part of an fp32 value for the 3xTF32 tensor-core products: v - trunc_tf32(v), rounded to
+// TF32 (the tensor core itself reads trunc_tf32(v) from the unmodified fp32 word).
+__device__ __forceinline__ float tf32_lo(float v)
+{
+	const float hi = __uint_as_float(__float_as_uint(v) & 0xFFFFE000u);
+	uint32_t t;
+	asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(t) : "f"(v - hi));
+	return __uint_as_float(t);
+}
+
 __device__ __forceinline__ float warp_sum(float v)
 {
 #pragma unroll

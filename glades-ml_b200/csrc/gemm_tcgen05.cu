@@ -29,13 +29,13 @@ namespace glb {
 namespace {
 
 constexpr int TC_BM = 128;
-constexpr int TC_KALIGN = 32;  // K must be a multiple of the deepest k-block
 constexpr int TC_CHUNK_K = 128;  // k held by one tensor-memory accumulator before it is drained
 constexpr long long TC_WAIT_CYCLES = 2000000000ll;  // about a second
 
 struct TcParams
 {
 	float* C;
+	float* C_lo;
 	long long ldc;
 	int K;
 	int a_mn, b_mn;  // 1: operand is M/N-contiguous (MN-major), 0: K-contiguous (K-major)
@@ -433,6 +433,9 @@ __global__ void __launch_bounds__(TcSmem<BN, BK, STAGES>::THREADS, 1)
 					for (int e = 0; e < 4; ++e) o[e] = p.alpha * o[e] + (p.colterm ? p.colterm[col0 + v * 4 + e] : 0.0f);
 				}
 				*reinterpret_cast<float4*>(crow + v * 4) = make_float4(o[0], o[1], o[2], o[3]);
+				if (p.C_lo)
+					*reinterpret_cast<float4*>(p.C_lo + (long long)row * p.ldc + col0 + v * 4) =
+					    make_float4(tf32_lo(o[0]), tf32_lo(o[1]), tf32_lo(o[2]), tf32_lo(o[3]));
 			}
 		}
 		}
@@ -531,15 +534,7 @@ __global__ void __launch_bounds__(256) split_lo_kernel(const float4* __restrict_
 	{
 		const float4 a = src[i];
 		const float v[4] = {a.x, a.y, a.z, a.w};
-		float o[4];
-#pragma unroll
-		for (int e = 0; e < 4; ++e)
-		{
-			const float hi = __uint_as_float(__float_as_uint(v[e]) & 0xFFFFE000u);
-			uint32_t t;
-			asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(t) : "f"(v[e] - hi));
-			o[e] = __uint_as_float(t);
-		}
+		const float o[4] = {tf32_lo(v[0]), tf32_lo(v[1]), tf32_lo(v[2]), tf32_lo(v[3])};
 		lo[i] = make_float4(o[0], o[1], o[2], o[3]);
 	}
 }
@@ -553,17 +548,27 @@ __global__ void __launch_bounds__(256) scale_split_lo_kernel(const float* __rest
 	{
 		const float v = src[i] * rowscale[i / ld];
 		dst[i] = v;
-		const float hi = __uint_as_float(__float_as_uint(v) & 0xFFFFE000u);
-		uint32_t t;
-		asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(t) : "f"(v - hi));
-		lo[i] = __uint_as_float(t);
+		lo[i] = tf32_lo(v);
 	}
 }
 
 }  // namespace
 
+// k-block depth of the tile variant in use: 16 (default) or 32 (GLADES_TC_BK=32, kept for comparison)
+static int tc_bk()
+{
+	static int bk_choice = 0;
+	if (!bk_choice)
+	{
+		const char* e = getenv("GLADES_TC_BK");
+		bk_choice = (e && atoi(e) == 32) ? 32 : 16;
+	}
+	return bk_choice;
+}
+
 bool tc_gemm_supported(const GemmArgs& g)
 {
+	const int TC_KALIGN = tc_bk();
 	if (g.M < TC_BM || g.N < 128 || g.K < TC_KALIGN) return false;
 	if (g.M % TC_BM || g.N % 128 || g.K % TC_KALIGN) return false;
 	if (g.kscale) return false;
@@ -587,19 +592,14 @@ cudaError_t launch_gemm_tc(const GemmArgs& g, const float* A_lo, const float* B_
 	const int BN = (g.N % 256 == 0) ? 256 : 128;
 	// tile variant: 16-deep k-blocks with twice the stages by default; GLADES_TC_BK=32 selects the
 	// 32-deep blocks (kept for comparison runs)
-	static int bk_choice = 0;
-	if (!bk_choice)
-	{
-		const char* e = getenv("GLADES_TC_BK");
-		bk_choice = (e && atoi(e) == 32) ? 32 : 16;
-	}
-	const int bk = bk_choice;
+	const int bk = tc_bk();
 	CUtensorMap mA, mAl, mB, mBl;
 	if (!make_map(&mA, g.A, a_mn, g.M, g.K, lda, TC_BM, bk) || !make_map(&mAl, A_lo, a_mn, g.M, g.K, lda, TC_BM, bk) ||
 	    !make_map(&mB, g.B, b_mn, g.N, g.K, ldb, BN, bk) || !make_map(&mBl, B_lo, b_mn, g.N, g.K, ldb, BN, bk))
 		return cudaErrorInvalidValue;
 	TcParams p;
 	p.C = g.C;
+	p.C_lo = g.C_lo;
 	p.ldc = g.ldc;
 	p.K = g.K;
 	p.a_mn = a_mn;

@@ -57,6 +57,7 @@ struct GemmArgs
 	const float* A;
 	const float* B;
 	float* C;
+	float* C_lo;           // tensor-core kernel only: also write the low TF32 part of C here (same layout), or NULL
 	int M, N, K;
 	long long a_sm, a_sk, b_sn, b_sk, ldc;
 	const float* kscale;   // optional per-k factor (momentum weights c_j), applied to A(m,k)
@@ -81,6 +82,7 @@ struct HeadArgs
 	float* P;
 	const float* Y;
 	float* D;          // may be NULL (inference)
+	float* D_lo;       // optional: low TF32 part of D for the tensor-core products
 	int rows, n;
 	int out_type;
 	int softmax;
@@ -97,7 +99,8 @@ cudaError_t launch_sum_scaled(const float* D, long long count, float alpha, floa
 cudaError_t launch_decay_colterm(const float* A, int rows, int n, const float* c, float lr, float wd1, float wd2,
                                  float* colterm, cudaStream_t s);
 // W -= G * inv_mb for the flat weight vector; biases b_l -= gb_l * bscale_l; sets flags[0] on non-finite
-cudaError_t launch_update(float* W, const float* G, long long count, float inv_mb, float* bias, const float* gb,
+// W_lo (optional): the low TF32 part of the updated weights, for the tensor-core products
+cudaError_t launch_update(float* W, float* W_lo, const float* G, long long count, float inv_mb, float* bias, const float* gb,
                           const float* bscale, int H, int* flags, cudaStream_t s);
 
 // ---- batched mode, whole small network in shared memory (small_fused.cu) -------------------------

@@ -79,7 +79,7 @@ extern "C" int gl_matmul_static(const float* d_a, int64_t a_sm, int64_t a_sk, co
 	{
 		snprintf(g_static_err, sizeof g_static_err,
 		         "gl_matmul_static: %dx%dx%d with these strides does not fit the tensor-core tiles "
-		         "(M %% 128, N %% 128, K %% 32, operands contiguous in k or in m/n, 16-byte aligned)", m, n, k);
+		         "(M %% 128, N %% 128, K %% 16, operands contiguous in k or in m/n, 16-byte aligned)", m, n, k);
 		return GL_ERR_INVALID;
 	}
 	// extents of the two operands as the product reads them

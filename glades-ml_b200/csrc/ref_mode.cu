@@ -55,7 +55,9 @@ __global__ void __launch_bounds__(1024, 1) ref_train_kernel(const __grid_constan
 	float* dvec = err_base + total_nodes;
 	float* basev = dvec + total_nodes;
 	float* sbias = basev + total_nodes;  // GL_MAX_WEIGHT_LAYERS floats
-	float* wcur = sbias + GL_MAX_WEIGHT_LAYERS;
+	float* mcost = sbias + GL_MAX_WEIGHT_LAYERS;  // per output node: cost and accuracy of this sample
+	float* macc = mcost + n_out;
+	float* wcur = macc + n_out;
 
 	float* actp[GL_MAX_WEIGHT_LAYERS + 1];
 	float* errp[GL_MAX_WEIGHT_LAYERS + 1];
@@ -132,14 +134,22 @@ __global__ void __launch_bounds__(1024, 1) ref_train_kernel(const __grid_constan
 			}
 			// ---------------- metrics: sequential fp32 sums in (row, output) order
 			const float* yr = a.Y + r * n_out;
+			// the per-node values are independent (computed in parallel); only their accumulation into the
+			// epoch sums is order-sensitive and stays on one thread
+			for (int o = t; o < n_out; o += T)
+			{
+				mcost[o] = cost_x(yr[o], actp[H + 1][o], data_size, n.out_type);
+				macc[o] = node_accuracy_x(yr[o], actp[H + 1][o]);
+			}
+			__syncthreads();
 			if (t == 0)
 			{
 				const float* p = actp[H + 1];
 				float te = s_tot_err, ta = s_tot_acc;
 				for (int o = 0; o < n_out; ++o)
 				{
-					te = __fadd_rn(te, cost_x(yr[o], p[o], data_size, n.out_type));
-					ta = __fadd_rn(ta, node_accuracy_x(yr[o], p[o]));
+					te = __fadd_rn(te, mcost[o]);
+					ta = __fadd_rn(ta, macc[o]);
 				}
 				s_tot_err = te;
 				s_tot_acc = ta;
@@ -267,7 +277,7 @@ static int total_nodes_of(const NetView& n)
 
 size_t ref_train_smem_bytes(const NetView& n, bool weights_in_smem)
 {
-	size_t f = 4 * (size_t)total_nodes_of(n) + GL_MAX_WEIGHT_LAYERS;
+	size_t f = 4 * (size_t)total_nodes_of(n) + GL_MAX_WEIGHT_LAYERS + 2 * (size_t)n.sizes[n.H + 1];
 	if (weights_in_smem)
 		for (int l = 0; l <= n.H; ++l) f += (size_t)n.sizes[l] * n.sizes[l + 1] * (1 + (size_t)n.mb);
 	return f * sizeof(float);

@@ -8,7 +8,7 @@
 
 namespace glb {
 
-// Tile constraints of the kernel: M % 128 == 0, N % 128 == 0, K % 32 == 0, every operand either
+// Tile constraints of the kernel: M % 128 == 0, N % 128 == 0, K % 16 == 0, every operand either
 // K-contiguous or M/N-contiguous with 16-byte aligned rows, no per-k scale vector.
 bool tc_gemm_supported(const GemmArgs& g);
 

@@ -185,7 +185,7 @@ int64_t gl_kernel_launches(const gl_net* net);
 int64_t gl_tensor_core_launches(const gl_net* net);
 /* Diagnostic matrix product on device buffers, C[m][n] = sum_k A(m,k)*B(n,k) with
  * A(m,k) = d_a[m*a_sm + k*a_sk] and B(n,k) = d_b[n*b_sn + k*b_sk]; engine GL_GEMM_FFMA or
- * GL_GEMM_TCGEN05 (M % 128 == 0, N % 128 == 0, K % 32 == 0, each operand contiguous in k or in
+ * GL_GEMM_TCGEN05 (M % 128 == 0, N % 128 == 0, K % 16 == 0, each operand contiguous in k or in
  * m/n).  It exposes the layer-product kernels of the path for numerical tests; the reference has
  * no matrix product (it walks edges, network.cpp:461-508). */
 int gl_matmul(const float* d_a, int64_t a_sm, int64_t a_sk, const float* d_b, int64_t b_sn, int64_t b_sk, float* d_c,

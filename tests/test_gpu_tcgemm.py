@@ -19,7 +19,8 @@ def _dev(L, a):
 
 
 @pytest.mark.parametrize("a_mn,b_mn", [(0, 0), (0, 1), (1, 1), (1, 0)])
-@pytest.mark.parametrize("M,N,K", [(128, 128, 32), (256, 256, 64), (128, 384, 96), (384, 256, 160), (256, 512, 1024)])
+@pytest.mark.parametrize("M,N,K", [(128, 128, 32), (256, 256, 64), (128, 384, 96), (384, 256, 160), (256, 512, 1024),
+                                   (128, 128, 48), (256, 256, 784)])
 def test_tc_matmul_all_layouts(g, a_mn, b_mn, M, N, K):
     L = g.lib()
     rng = np.random.default_rng(M + 3 * N + 7 * K + a_mn + 2 * b_mn)
