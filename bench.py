@@ -14,8 +14,9 @@ reference has; its own arithmetic is non-finite on this shape after the first sa
 
 `value`   train samples/s with the windows already resident in HBM (CUDA events on the library's
           stream, max over ranks).
-`e2e`     the same step through gl_train_window_host: the window's rows start in pinned HOST
-          memory, are copied in by the call, and the loss is read back every step.
+`e2e`     the same step through gl_train_window_host_submit / _result: every window's rows start in
+          pinned HOST memory and are copied in by the call, and every window's loss is read back; two
+          windows are in flight so the copy of one overlaps the compute of the other.
 `roofline` the tensor-core layer-product kernel: algorithmic flop of its launches / their summed
           CUDA-event durations, against the measured dense bf16 peak of MEASURED_PEAKS.json.
 `cpu_baseline` the CPU restatement of the same batched arithmetic (oracle port, all host cores)
@@ -475,23 +476,36 @@ def main():
     mm = g.Metrics()
     h_out = np.empty(8, np.float32)
 
-    def e2e_step(i):
+    def e2e_submit(i):
         px, py = pins[i % n_pin]
-        if train:
-            st = L.gl_train_window_host(net.h, px, py, lb, C.byref(mm))
-        else:
-            st = L.gl_forward_host(net.h, px, py, lb, None, None, C.byref(mm))
-        if st != 0:
+        if L.gl_train_window_host_submit(net.h, px, py, lb) != 0:
+            raise RuntimeError(L.gl_last_error().decode())
+
+    def e2e_result():
+        if L.gl_train_window_host_result(net.h, C.byref(mm)) != 0:
             raise RuntimeError(L.gl_last_error().decode())
         return mm.total_error
 
-    for i in range(3):
-        e2e_step(i)
+    def e2e_run(count):
+        """count steps, each with its own host->device copy and its own loss read-back; training keeps two
+        windows in flight so that the copy of one overlaps the compute of the other."""
+        if not train:
+            for i in range(count):
+                px, py = pins[i % n_pin]
+                if L.gl_forward_host(net.h, px, py, lb, None, None, C.byref(mm)) != 0:
+                    raise RuntimeError(L.gl_last_error().decode())
+            return
+        e2e_submit(0)
+        for i in range(1, count):
+            e2e_submit(i)
+            e2e_result()
+        e2e_result()
+
+    e2e_run(3)
     plumb.barrier()
-    e2e_steps = max(3, min(args.steps, 10))
+    e2e_steps = max(3, min(args.steps, 20))
     t0 = time.perf_counter()
-    for i in range(e2e_steps):
-        e2e_step(i)
+    e2e_run(e2e_steps)
     dt = time.perf_counter() - t0
     plumb.barrier()
     dt = plumb.max(dt)

@@ -133,6 +133,8 @@ def lib():
         "gl_train_epochs": (C.c_int, [vp, i32, mp]),
         "gl_train_window": (C.c_int, [vp, i64, i32, mp]),
         "gl_train_window_host": (C.c_int, [vp, vp, vp, i32, mp]),
+        "gl_train_window_host_submit": (C.c_int, [vp, vp, vp, i32]),
+        "gl_train_window_host_result": (C.c_int, [vp, mp]),
         "gl_forward": (C.c_int, [vp, i64, i64, vp, vp, mp]),
         "gl_forward_host": (C.c_int, [vp, vp, vp, i64, vp, vp, mp]),
         "gl_get_activations": (C.c_int, [vp, i64, vp]),
@@ -258,6 +260,15 @@ class Net:
         m = Metrics()
         rows = x.shape[0] if rows is None else rows
         _check(lib().gl_train_window_host(self.h, _ptr(x), _ptr(y), rows, C.byref(m)))
+        return m
+
+    def submit_window_host(self, x, y, rows=None):
+        rows = x.shape[0] if rows is None else rows
+        _check(lib().gl_train_window_host_submit(self.h, _ptr(x), _ptr(y), rows))
+
+    def window_result(self):
+        m = Metrics()
+        _check(lib().gl_train_window_host_result(self.h, C.byref(m)))
         return m
 
     def forward(self, first_row, rows, want_outputs=True, want_argmax=True):

@@ -131,6 +131,22 @@ struct gl_net
 	float* dBscale = nullptr; // [GL_MAX_WEIGHT_LAYERS]
 	int* dFlags = nullptr;
 	double* dSums = nullptr;  // [2] cost, accuracy (batched)
+	double* winSums = nullptr; // the sums the current window step accumulates into (dSums or a pipeline slot)
+	// two-deep pipeline of host-buffer windows (gl_train_window_host_submit / _result)
+	struct Slot
+	{
+		float* dX = nullptr;
+		float* dY = nullptr;
+		int64_t cap = 0;
+		double* dSums = nullptr;
+		double* hSums = nullptr;  // pinned: cost, accuracy, then the status words
+		cudaEvent_t copied = nullptr, done = nullptr, t0 = nullptr;
+		int rows = 0, globalRows = 0;
+		int64_t launches = 0;
+		bool pending = false;
+	} slot[2];
+	cudaStream_t copyStream = nullptr;
+	uint64_t submitted = 0, collected = 0;
 	float* dSumsF = nullptr;  // reference mode: [n_epochs][2]
 	int sumsFCap = 0;
 	int* dConf = nullptr;     // [n_out][n_out]
@@ -170,6 +186,7 @@ struct gl_net
 	bool loA[GL_MAX_WEIGHT_LAYERS + 2] = {};
 	bool loD[GL_MAX_WEIGHT_LAYERS + 2] = {};
 	int64_t tcLaunches = 0;
+	int64_t lastWindowLaunches = 0;
 	// optional per-launch timing of the layer products (gl_profile_enable)
 	bool profile = false;
 	std::vector<cudaEvent_t> profEv;   // pairs
@@ -338,6 +355,15 @@ extern "C" int gl_destroy(gl_net* n)
 	cudaFree(n->dLastOut);
 	cudaFree(n->dScratch); cudaFree(n->ownX); cudaFree(n->ownY); cudaFree(n->dColterm);
 	cudaFree(n->dXwin); cudaFree(n->dYwin);
+	for (int i = 0; i < 2; ++i)
+	{
+		cudaFree(n->slot[i].dX); cudaFree(n->slot[i].dY); cudaFree(n->slot[i].dSums);
+		if (n->slot[i].hSums) cudaFreeHost(n->slot[i].hSums);
+		if (n->slot[i].copied) cudaEventDestroy(n->slot[i].copied);
+		if (n->slot[i].done) cudaEventDestroy(n->slot[i].done);
+		if (n->slot[i].t0) cudaEventDestroy(n->slot[i].t0);
+	}
+	if (n->copyStream) cudaStreamDestroy(n->copyStream);
 	if (n->hPinned) cudaFreeHost(n->hPinned);
 	for (cudaEvent_t e : n->profEv) cudaEventDestroy(e);
 	if (n->tim0) cudaEventDestroy(n->tim0);
@@ -356,6 +382,15 @@ extern "C" void gl_stop(gl_net* n) { if (n) n->stop = 1; }
 static int ensure_pinned(gl_net* n, size_t bytes)
 {
 	if (n->pinnedBytes >= bytes) return 0;
+	for (int i = 0; i < 2; ++i)
+	{
+		cudaFree(n->slot[i].dX); cudaFree(n->slot[i].dY); cudaFree(n->slot[i].dSums);
+		if (n->slot[i].hSums) cudaFreeHost(n->slot[i].hSums);
+		if (n->slot[i].copied) cudaEventDestroy(n->slot[i].copied);
+		if (n->slot[i].done) cudaEventDestroy(n->slot[i].done);
+		if (n->slot[i].t0) cudaEventDestroy(n->slot[i].t0);
+	}
+	if (n->copyStream) cudaStreamDestroy(n->copyStream);
 	if (n->hPinned) cudaFreeHost(n->hPinned);
 	n->hPinned = nullptr;
 	n->pinnedBytes = 0;
@@ -752,8 +787,9 @@ static int batched_window(gl_net* n, const float* X, const float* Y, int rows, i
 	const int first_pos = (n->world > 1) ? n->firstPos : 0;
 	if (int r = set_momentum_weights(n, rows, global_rows, first_pos)) return r;
 	int64_t launches = 0;
+	double* const sums2 = n->winSums ? n->winSums : n->dSums;
 	CU(cudaEventRecord(n->ev0, n->stream));
-	CU(cudaMemsetAsync(n->dSums, 0, 2 * sizeof(double), n->stream));
+	CU(cudaMemsetAsync(sums2, 0, 2 * sizeof(double), n->stream));
 	CU(cudaMemsetAsync(n->dG + n->nw, 0, GL_MAX_WEIGHT_LAYERS * sizeof(float), n->stream));
 	if (int r = batched_forward(n, X, rows, &launches)) return r;
 
@@ -768,7 +804,7 @@ static int batched_window(gl_net* n, const float* X, const float* Y, int rows, i
 	h.out_type = n->d.output_type;
 	h.softmax = n->softmax;
 	h.data_size = (float)(metric_rows * (int64_t)n->n_out);
-	h.sums2 = n->dSums;
+	h.sums2 = sums2;
 	h.confusion = (n->d.output_type != GL_OUT_REGRESSION) ? n->dConf : nullptr;
 	CU(launch_head(h, n->stream));
 	++launches;
@@ -845,7 +881,7 @@ static int batched_window(gl_net* n, const float* X, const float* Y, int rows, i
 			CU(cudaStreamWaitEvent(n->commStream, n->evGrad[GL_MAX_WEIGHT_LAYERS], 0));
 			NC(g_nccl.GroupStart());
 			NC(g_nccl.AllReduce(n->dG + n->nw, n->dG + n->nw, (size_t)GL_MAX_WEIGHT_LAYERS, NCCL_FLOAT32, NCCL_SUM, n->comm, n->commStream));
-			NC(g_nccl.AllReduce(n->dSums, n->dSums, 2, NCCL_FLOAT64, NCCL_SUM, n->comm, n->commStream));
+			NC(g_nccl.AllReduce(sums2, sums2, 2, NCCL_FLOAT64, NCCL_SUM, n->comm, n->commStream));
 			NC(g_nccl.GroupEnd());
 			CU(cudaEventRecord(n->evComm, n->commStream));
 			CU(cudaStreamWaitEvent(n->stream, n->evComm, 0));
@@ -854,7 +890,7 @@ static int batched_window(gl_net* n, const float* X, const float* Y, int rows, i
 		{
 			NC(g_nccl.GroupStart());
 			NC(g_nccl.AllReduce(n->dG, n->dG, (size_t)(n->nw + GL_MAX_WEIGHT_LAYERS), NCCL_FLOAT32, NCCL_SUM, n->comm, n->stream));
-			NC(g_nccl.AllReduce(n->dSums, n->dSums, 2, NCCL_FLOAT64, NCCL_SUM, n->comm, n->stream));
+			NC(g_nccl.AllReduce(sums2, sums2, 2, NCCL_FLOAT64, NCCL_SUM, n->comm, n->stream));
 			NC(g_nccl.GroupEnd());
 		}
 	}
@@ -873,13 +909,14 @@ static int batched_window(gl_net* n, const float* X, const float* Y, int rows, i
 	n->loW = n->dWlo != nullptr;
 	CU(cudaEventRecord(n->ev1, n->stream));
 	n->launches += launches;
+	n->lastWindowLaunches = launches;
 	if (out)
 	{
 		CU(cudaStreamSynchronize(n->stream));
 		float ms = 0;
 		CU(cudaEventElapsedTime(&ms, n->ev0, n->ev1));
 		double sums[2];
-		CU(cudaMemcpy(sums, n->dSums, sizeof sums, cudaMemcpyDeviceToHost));
+		CU(cudaMemcpy(sums, sums2, sizeof sums, cudaMemcpyDeviceToHost));
 		memset(out, 0, sizeof *out);
 		out->total_error = (float)sums[0];
 		out->total_accuracy = (float)(sums[1] / ((double)global_rows * (double)n->n_out));
@@ -930,6 +967,93 @@ extern "C" int gl_train_window_host(gl_net* n, const float* x, const float* y, i
 	CU(cudaMemcpyAsync(n->dYwin, y, (size_t)rows * n->n_out * sizeof(float), cudaMemcpyHostToDevice, n->stream));
 	const int64_t win_rows = (n->world > 1 && n->globalRows > 0) ? n->globalRows : rows;
 	return batched_window(n, n->dXwin, n->dYwin, rows, win_rows, out);
+}
+
+// ---- pipelined host-buffer windows ------------------------------------------------------------------
+// submit() queues the copy of the window's rows on a copy stream and the step on the compute stream and
+// returns at once; result() waits for the oldest submitted window.  Two windows may be in flight, so the
+// copy of window i+1 overlaps the compute of window i.
+static int slot_prepare(gl_net* n, gl_net::Slot& sl, int64_t rows)
+{
+	if (!sl.copied)
+	{
+		CU(cudaEventCreateWithFlags(&sl.copied, cudaEventDisableTiming));
+		CU(cudaEventCreate(&sl.done));
+		CU(cudaEventCreate(&sl.t0));
+		CU(cudaMalloc(&sl.dSums, 2 * sizeof(double)));
+		CU(cudaMallocHost(&sl.hSums, 4 * sizeof(double)));
+	}
+	if (rows > sl.cap)
+	{
+		cudaFree(sl.dX);
+		cudaFree(sl.dY);
+		sl.dX = sl.dY = nullptr;
+		CU(cudaMalloc(&sl.dX, (size_t)rows * n->d.sizes[0] * sizeof(float)));
+		CU(cudaMalloc(&sl.dY, (size_t)rows * n->n_out * sizeof(float)));
+		sl.cap = rows;
+	}
+	return 0;
+}
+
+extern "C" int gl_train_window_host_submit(gl_net* n, const float* x, const float* y, int32_t rows)
+{
+	if (!n || !x || !y || rows < 1) return fail(GL_ERR_INVALID, "gl_train_window_host_submit: bad argument");
+	if (n->d.mode != GL_MODE_BATCHED) return fail(GL_ERR_STATE, "gl_train_window_host_submit needs a batched-mode network");
+	if (n->submitted - n->collected >= 2) return fail(GL_ERR_STATE, "two windows are already in flight: collect a result first");
+	if (int r = use_device(n)) return r;
+	if (!n->copyStream) CU(cudaStreamCreateWithFlags(&n->copyStream, cudaStreamNonBlocking));
+	gl_net::Slot& sl = n->slot[n->submitted & 1];
+	const bool used_before = sl.copied != nullptr;
+	if (int r = slot_prepare(n, sl, rows)) return r;
+	// the slot's buffers are free once the step that last read them has finished
+	if (used_before) CU(cudaStreamWaitEvent(n->copyStream, sl.done, 0));
+	CU(cudaMemcpyAsync(sl.dX, x, (size_t)rows * n->d.sizes[0] * sizeof(float), cudaMemcpyHostToDevice, n->copyStream));
+	CU(cudaMemcpyAsync(sl.dY, y, (size_t)rows * n->n_out * sizeof(float), cudaMemcpyHostToDevice, n->copyStream));
+	CU(cudaEventRecord(sl.copied, n->copyStream));
+	CU(cudaStreamWaitEvent(n->stream, sl.copied, 0));
+	CU(cudaEventRecord(sl.t0, n->stream));
+	const int64_t win_rows = (n->world > 1 && n->globalRows > 0) ? n->globalRows : rows;
+	n->winSums = sl.dSums;
+	const int st = batched_window(n, sl.dX, sl.dY, rows, win_rows, nullptr);
+	n->winSums = nullptr;
+	if (st != GL_OK) return st;
+	CU(cudaMemcpyAsync(sl.hSums, sl.dSums, 2 * sizeof(double), cudaMemcpyDeviceToHost, n->stream));
+	CU(cudaMemcpyAsync(sl.hSums + 2, n->dFlags, 4 * sizeof(int), cudaMemcpyDeviceToHost, n->stream));
+	CU(cudaEventRecord(sl.done, n->stream));
+	sl.rows = rows;
+	sl.globalRows = (int)win_rows;
+	sl.launches = n->lastWindowLaunches;
+	sl.pending = true;
+	++n->submitted;
+	return GL_OK;
+}
+
+extern "C" int gl_train_window_host_result(gl_net* n, gl_metrics* out)
+{
+	if (!n) return fail(GL_ERR_INVALID, "gl_train_window_host_result: null handle");
+	if (n->submitted == n->collected) return fail(GL_ERR_STATE, "no window in flight");
+	if (int r = use_device(n)) return r;
+	gl_net::Slot& sl = n->slot[n->collected & 1];
+	CU(cudaEventSynchronize(sl.done));
+	sl.pending = false;
+	++n->collected;
+	int flags[4];
+	memcpy(flags, sl.hSums + 2, sizeof flags);
+	if (out)
+	{
+		float ms = 0;
+		CU(cudaEventElapsedTime(&ms, sl.t0, sl.done));
+		memset(out, 0, sizeof *out);
+		out->total_error = (float)sl.hSums[0];
+		out->total_accuracy = (float)(sl.hSums[1] / ((double)sl.globalRows * (double)n->n_out));
+		out->epochs = n->epochs;
+		out->rows = sl.globalRows;
+		out->device_ms = ms;
+		out->kernel_launches = sl.launches;
+		out->nonfinite = flags[0] & 1;
+	}
+	if (flags[1]) return fail(GL_ERR_TIMEOUT, "a bounded wait inside the tensor-core kernel ran out (role %d)", flags[1]);
+	return GL_OK;
 }
 
 // Batched mode, small network: every weight fits in shared memory, so whole epochs run in one launch

@@ -138,6 +138,13 @@ int gl_set_data(gl_net* net, const float* x, const float* y, int64_t rows);
  * must outlive the handle's use of them.  d_y may be NULL for forward-only use without metrics. */
 int gl_set_data_device(gl_net* net, const float* d_x, const float* d_y, int64_t rows);
 
+/* The host-buffer window step as a two-deep pipeline: submit() queues the copy of the rows (x and y must
+ * stay valid, and should be pinned, until the matching result() returns) and the step, and returns at
+ * once; result() waits for the oldest submitted window and reports its figures.  At most two windows are
+ * in flight, so the copy of one overlaps the compute of the other.  No counterpart in the reference. */
+int gl_train_window_host_submit(gl_net* net, const float* x, const float* y, int32_t rows);
+int gl_train_window_host_result(gl_net* net, gl_metrics* out);
+
 /* Replaces n iterations of the epoch loop of NNetwork::run with RUN_TRAIN
  * (network.cpp:173-256): every row through SGDHelper (forward, metrics, confusion counts,
  * backward, update).  out (may be NULL) receives the last epoch's figures. */

@@ -467,3 +467,41 @@ def test_small_network_fused_epochs_vs_restatement(g, oracle, case):
         assert diff <= (2 if epochs * rows > 200 else 0), "confusion counts differ by %d" % diff
     assert net.epochs() == epochs
     net.close()
+
+
+def test_pipelined_host_windows_equal_synchronous_ones(g):
+    """submit/result keeps two host-buffer windows in flight; the weights and every window's loss
+    must equal those of the one-at-a-time entry point, and a third submit must be refused."""
+    rng = np.random.default_rng(77)
+    sizes = [12, 24, 5]
+    rows, steps = 40, 5
+    d = g.make_desc(sizes, ["tanh", "softmax"], "classification", batch=rows, lr=0.1, momentum=0.3, mode=g.MODE_BATCHED,
+                    gemm=g.GEMM_FFMA)
+    xs = [rng.standard_normal((rows, sizes[0])).astype(np.float32) for _ in range(steps)]
+    ys = []
+    for _ in range(steps):
+        y = np.zeros((rows, sizes[-1]), np.float32)
+        y[np.arange(rows), rng.integers(0, sizes[-1], rows)] = 1.0
+        ys.append(y)
+    w, b = _rand_net(rng, sizes)
+    a, c = g.Net(d), g.Net(d)
+    a.set_weights(w, b)
+    c.set_weights(w, b)
+    sync_losses = [a.train_window_host(xs[i], ys[i]).total_error for i in range(steps)]
+    pipe_losses = []
+    c.submit_window_host(xs[0], ys[0])
+    for i in range(1, steps):
+        c.submit_window_host(xs[i], ys[i])
+        if i == 1:
+            with pytest.raises(g.GladesError):
+                c.submit_window_host(xs[i], ys[i])  # two already in flight
+        pipe_losses.append(c.window_result().total_error)
+    pipe_losses.append(c.window_result().total_error)
+    with pytest.raises(g.GladesError):
+        c.window_result()  # nothing left in flight
+    assert pipe_losses == sync_losses
+    wa, ba = a.get_weights()
+    wc, bc = c.get_weights()
+    assert np.array_equal(bits(wa), bits(wc)) and np.array_equal(bits(ba), bits(bc))
+    a.close()
+    c.close()
