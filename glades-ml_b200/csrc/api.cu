@@ -180,6 +180,8 @@ struct gl_net
 	float* dWlo = nullptr;
 	float* dAlo[GL_MAX_WEIGHT_LAYERS + 2] = {};
 	float* dDlo[GL_MAX_WEIGHT_LAYERS + 2] = {};
+	unsigned* dMask[GL_MAX_WEIGHT_LAYERS + 2] = {};  // ReLU layers: (activation > 0) bits, [rows][n_l/32]
+	bool maskValid[GL_MAX_WEIGHT_LAYERS + 2] = {};
 	float* dDc = nullptr;     // momentum-weighted copy of one delta matrix and its low part
 	float* dDclo = nullptr;
 	bool loX = false, loW = false, loDc = false;
@@ -192,6 +194,7 @@ struct gl_net
 	std::vector<cudaEvent_t> profEv;   // pairs
 	std::vector<double> profFlops;
 	std::vector<int> profIsTc;
+	std::vector<int> profShape;  // M, N, K, epilogue per recorded launch
 	size_t profUsed = 0;
 	cudaEvent_t tim0 = nullptr, tim1 = nullptr;
 
@@ -327,6 +330,8 @@ static void free_work(gl_net* n)
 		if (n->dAlo[l]) cudaFree(n->dAlo[l]);
 		if (n->dDlo[l]) cudaFree(n->dDlo[l]);
 		n->dAlo[l] = n->dDlo[l] = nullptr;
+		if (n->dMask[l]) cudaFree(n->dMask[l]);
+		n->dMask[l] = nullptr;
 	}
 	if (n->dXlo) cudaFree(n->dXlo);
 	if (n->dDc) cudaFree(n->dDc);
@@ -588,6 +593,8 @@ static int ensure_work(gl_net* n, int64_t rows)
 		{
 			CU(cudaMalloc(&n->dAlo[l], (size_t)rows * n->d.sizes[l] * sizeof(float)));
 			CU(cudaMalloc(&n->dDlo[l], (size_t)rows * n->d.sizes[l] * sizeof(float)));
+			if (l <= n->H && n->d.sizes[l] % 128 == 0 && n->d.activation[l - 1] == GL_ACT_RELU)
+				CU(cudaMalloc(&n->dMask[l], (size_t)rows * (n->d.sizes[l] / 32) * sizeof(unsigned)));
 		}
 		CU(cudaMalloc(&n->dDc, (size_t)rows * maxn * sizeof(float)));
 		CU(cudaMalloc(&n->dDclo, (size_t)rows * maxn * sizeof(float)));
@@ -673,6 +680,7 @@ static int run_gemm(gl_net* n, GemmArgs g, Operand a, Operand b, int64_t* launch
 		n->profUsed += 2;
 		n->profFlops.push_back(2.0 * (double)g.M * (double)g.N * (double)g.K);
 		n->profIsTc.push_back(tc ? 1 : 0);
+		n->profShape.push_back(g.M); n->profShape.push_back(g.N); n->profShape.push_back(g.K); n->profShape.push_back(g.epi);
 	}
 	if (!tc)
 	{
@@ -772,9 +780,11 @@ static int batched_forward(gl_net* n, const float* X, int rows, int64_t* launche
 		// the tensor-core epilogue also writes the low TF32 part of its output, so the next layer's
 		// products need no separate split pass (not for the last layer: the head rewrites it)
 		g.C_lo = (l < n->H && fuse_lo_in_epilogue()) ? n->dAlo[l + 1] : nullptr;
+		g.relu_mask_out = (l < n->H) ? n->dMask[l + 1] : nullptr;
 		bool tc = false;
 		if (int r = run_gemm(n, g, op_act(n, l, X, rows), op_w(n, l), launches, &tc)) return r;
 		n->loA[l + 1] = tc && g.C_lo != nullptr;
+		n->maskValid[l + 1] = tc && g.relu_mask_out != nullptr;
 		in = n->dA[l + 1];
 	}
 	return 0;
@@ -832,6 +842,7 @@ static int batched_window(gl_net* n, const float* X, const float* Y, int rows, i
 			g.act = n->d.activation[l - 1];
 			g.par = 0.01f;  // the reference passes a fixed 0.01, network.cpp:618
 			g.C_lo = fuse_lo_in_epilogue() ? n->dDlo[l] : nullptr;
+			g.relu_mask_in = n->maskValid[l] ? n->dMask[l] : nullptr;
 			g.sm_reserve = (n->world > 1 && n->dpOverlap) ? n->dpReserveSms : 0;
 			bool tc = false;
 			if (int r = run_gemm(n, g, opD, op_w(n, l), &launches, &tc)) return r;
@@ -1422,6 +1433,7 @@ extern "C" int gl_profile_enable(gl_net* n, int32_t on)
 	n->profUsed = 0;
 	n->profFlops.clear();
 	n->profIsTc.clear();
+	n->profShape.clear();
 	return GL_OK;
 }
 // Sums the recorded layer-product launches since gl_profile_enable: out[0] launches, out[1] total ms,
@@ -1440,6 +1452,10 @@ extern "C" int gl_profile_read(gl_net* n, double* out6)
 		out6[o] += 1.0;
 		out6[o + 1] += f;
 		out6[o + 2] += n->profFlops[i];
+		if (getenv("GLADES_PROFILE_DUMP"))
+			fprintf(stderr, "[profile] %s M=%d N=%d K=%d epi=%d %.4f ms %.1f TFLOP/s\n", n->profIsTc[i] ? "tc" : "ffma",
+			        n->profShape[4 * i], n->profShape[4 * i + 1], n->profShape[4 * i + 2], n->profShape[4 * i + 3], f,
+			        n->profFlops[i] / (f * 1e-3) / 1e12);
 	}
 	return GL_OK;
 }

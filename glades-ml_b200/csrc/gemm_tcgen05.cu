@@ -48,6 +48,10 @@ struct TcParams
 	float alpha;
 	const float* colterm;
 	int* err_flag;
+	unsigned* relu_mask_out;
+	const unsigned* relu_mask_in;
+	int mask_ld;           // words per row of the ReLU masks (= N / 32)
+	int debug;             // experiments only: bit 0 skips the global stores of the epilogue
 	int tiles_m, tiles_n;  // the CTAs walk the tiles_m * tiles_n output tiles persistently
 };
 
@@ -168,6 +172,21 @@ struct TcSmem
 // holds TC_CHUNK_K = 128 k (48 accumulations); the epilogue warps drain each finished
 // chunk into fp32 registers with round-to-nearest adds while the MMA warp fills the other of two
 // tensor-memory accumulators.
+
+// One thread's 128 accumulators -> its row of C (and optionally the low TF32 parts), through the
+// element-wise function f(value, column).  Fully unrolled so that acc[] stays in registers.
+template <class F>
+__device__ __forceinline__ void store_row(const float (&acc)[128], float* crow, float* lorow, F f)
+{
+#pragma unroll
+	for (int v = 0; v < 32; ++v)
+	{
+		const float o0 = f(acc[v * 4 + 0], v * 4 + 0), o1 = f(acc[v * 4 + 1], v * 4 + 1);
+		const float o2 = f(acc[v * 4 + 2], v * 4 + 2), o3 = f(acc[v * 4 + 3], v * 4 + 3);
+		*reinterpret_cast<float4*>(crow + v * 4) = make_float4(o0, o1, o2, o3);
+		if (lorow) *reinterpret_cast<float4*>(lorow + v * 4) = make_float4(tf32_lo(o0), tf32_lo(o1), tf32_lo(o2), tf32_lo(o3));
+	}
+}
 
 template <int BN, int BK, int STAGES>
 __global__ void __launch_bounds__(TcSmem<BN, BK, STAGES>::THREADS, 1)
@@ -403,40 +422,101 @@ __global__ void __launch_bounds__(TcSmem<BN, BK, STAGES>::THREADS, 1)
 			__syncwarp();
 			if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar_acc_empty + 8 * buf) : "memory");
 		}
-		if (ok)
+		if (ok && !(p.debug & 1))
 		{
 			const int row = m0 + q * 32 + lane;
 			const int col0 = n0 + half * 128;
 			float* crow = p.C + (long long)row * p.ldc + col0;
-			const float* auxrow = p.aux ? p.aux + (long long)row * p.ld_aux + col0 : nullptr;
-			const float bias = (p.epi == EPI_FORWARD && p.bias_ptr) ? *p.bias_ptr : 0.0f;
-#pragma unroll
-			for (int v = 0; v < 32; ++v)
+			float* lorow = p.C_lo ? p.C_lo + (long long)row * p.ldc + col0 : nullptr;
+			// The element-wise part is chosen ONCE per tile: the store loop is fully unrolled (the
+			// accumulators must stay in registers), so a per-element switch over the activation ids would
+			// replicate the transcendental code 128 times and thrash the instruction cache.
+			if (p.epi == EPI_FORWARD)
 			{
-				float o[4] = {acc[v * 4 + 0], acc[v * 4 + 1], acc[v * 4 + 2], acc[v * 4 + 3]};
-				if (p.epi == EPI_FORWARD)
+				const float bias = p.bias_ptr ? *p.bias_ptr : 0.0f;
+				const float par = p.par;
+				switch (p.act)
 				{
+				case GL_ACT_RELU:
+					if (p.relu_mask_out)
+					{
+						// one bit per output: what the error propagation needs of this layer's activations
+						unsigned wds[4] = {0u, 0u, 0u, 0u};
 #pragma unroll
-					for (int e = 0; e < 4; ++e) o[e] = squash_b(o[e] + bias, p.act, p.par);
-				}
-				else if (p.epi == EPI_ERRPROP)
+						for (int c = 0; c < 128; ++c)
+							if (!(acc[c] + bias < GL_OUTLIER)) wds[c >> 5] |= 1u << (c & 31);
+						*reinterpret_cast<uint4*>(p.relu_mask_out + (long long)row * p.mask_ld + (col0 >> 5)) =
+						    make_uint4(wds[0], wds[1], wds[2], wds[3]);
+					}
+					store_row(acc, crow, lorow, [=](float z, int) { z += bias; return z < GL_OUTLIER ? 0.0f : z; });
+					break;
+				case GL_ACT_LEAKY:
+					store_row(acc, crow, lorow, [=](float z, int) { z += bias; return z < GL_OUTLIER ? par * z : z; });
+					break;
+				case GL_ACT_LINEAR:
+					store_row(acc, crow, lorow, [=](float z, int) { return par * (z + bias); });
+					break;
+				case GL_ACT_SOFTMAX:
+					store_row(acc, crow, lorow, [=](float z, int) { return z + bias; });
+					break;
+				case GL_ACT_TANH:
+					store_row(acc, crow, lorow, [=](float z, int) { return tanhf(z + bias); });
+					break;
+				case GL_ACT_SIGMOID:
+					store_row(acc, crow, lorow, [=](float z, int) { return 1.0f / (1.0f + expf(-(z + bias))); });
+					break;
+				default:
 				{
-					const float4 a4 = *reinterpret_cast<const float4*>(auxrow + v * 4);
-					o[0] *= act_der_b(a4.x, p.act, p.par);
-					o[1] *= act_der_b(a4.y, p.act, p.par);
-					o[2] *= act_der_b(a4.z, p.act, p.par);
-					o[3] *= act_der_b(a4.w, p.act, p.par);
+					const int act = p.act;
+					store_row(acc, crow, lorow, [=](float z, int) { return squash_b(z + bias, act, par); });
+					break;
 				}
-				else if (p.epi == EPI_GRAD)
-				{
-#pragma unroll
-					for (int e = 0; e < 4; ++e) o[e] = p.alpha * o[e] + (p.colterm ? p.colterm[col0 + v * 4 + e] : 0.0f);
 				}
-				*reinterpret_cast<float4*>(crow + v * 4) = make_float4(o[0], o[1], o[2], o[3]);
-				if (p.C_lo)
-					*reinterpret_cast<float4*>(p.C_lo + (long long)row * p.ldc + col0 + v * 4) =
-					    make_float4(tf32_lo(o[0]), tf32_lo(o[1]), tf32_lo(o[2]), tf32_lo(o[3]));
 			}
+			else if (p.epi == EPI_ERRPROP && p.act == GL_ACT_RELU && p.relu_mask_in)
+			{
+				const uint4 mk = *reinterpret_cast<const uint4*>(p.relu_mask_in + (long long)row * p.mask_ld + (col0 >> 5));
+				const unsigned wds[4] = {mk.x, mk.y, mk.z, mk.w};
+				store_row(acc, crow, lorow, [=](float e, int c) { return ((wds[c >> 5] >> (c & 31)) & 1u) ? e : 0.0f; });
+			}
+			else if (p.epi == EPI_ERRPROP)
+			{
+				const float* auxrow = p.aux + (long long)row * p.ld_aux + col0;
+				const float par = p.par;
+				switch (p.act)
+				{
+				case GL_ACT_RELU:
+					store_row(acc, crow, lorow, [=](float e, int c) { return auxrow[c] > 0.0f ? e : 0.0f; });
+					break;
+				case GL_ACT_TANH:
+				case GL_ACT_TANHP:
+					store_row(acc, crow, lorow, [=](float e, int c) { const float a = auxrow[c]; return e * (1.0f - a * a); });
+					break;
+				case GL_ACT_SIGMOID:
+				case GL_ACT_SIGMOIDP:
+					store_row(acc, crow, lorow, [=](float e, int c) { const float a = auxrow[c]; return e * (a * (1.0f - a)); });
+					break;
+				default:
+				{
+					const int act = p.act;
+					store_row(acc, crow, lorow, [=](float e, int c) { return e * act_der_b(auxrow[c], act, par); });
+					break;
+				}
+				}
+			}
+			else if (p.epi == EPI_GRAD)
+			{
+				const float alpha = p.alpha;
+				if (p.colterm)
+				{
+					const float* ct = p.colterm + col0;
+					store_row(acc, crow, lorow, [=](float g, int c) { return alpha * g + ct[c]; });
+				}
+				else
+					store_row(acc, crow, lorow, [=](float g, int) { return alpha * g; });
+			}
+			else
+				store_row(acc, crow, lorow, [](float v, int) { return v; });
 		}
 		}
 	}
@@ -612,7 +692,19 @@ cudaError_t launch_gemm_tc(const GemmArgs& g, const float* A_lo, const float* B_
 	p.ld_aux = g.ld_aux;
 	p.alpha = g.alpha;
 	p.colterm = g.colterm;
+	p.relu_mask_out = g.relu_mask_out;
+	p.relu_mask_in = g.relu_mask_in;
+	p.mask_ld = g.N / 32;
 	p.err_flag = err_flag;
+	{
+		static int dbg = -1;
+		if (dbg < 0)
+		{
+			const char* e = getenv("GLADES_TC_DEBUG");
+			dbg = e ? atoi(e) : 0;
+		}
+		p.debug = dbg;
+	}
 	if (bk == 32)
 	{
 		if (BN == 256) return launch_cfg<256, 32, 2>(mA, mAl, mB, mBl, p, g.M, g.N, g.sm_reserve, s);

@@ -71,6 +71,10 @@ struct GemmArgs
 	long long ld_aux;
 	float alpha;
 	const float* colterm;
+	// tensor-core kernel, ReLU layers: the forward epilogue can record (output > 0) as one bit per element
+	// ([M][N/32] words) and the error-propagation epilogue can read that instead of the fp32 activations
+	unsigned* relu_mask_out;
+	const unsigned* relu_mask_in;
 	int sm_reserve;        // tensor-core kernel: leave this many SMs without a CTA (for a concurrent collective)
 };
 cudaError_t launch_gemm_ffma(const GemmArgs& g, cudaStream_t s);
