@@ -161,8 +161,9 @@ struct TcSmem
 	static constexpr int B_BYTES = BN * BK * 4;
 	static constexpr int STAGE_BYTES = 2 * A_BYTES + 2 * B_BYTES;
 	static constexpr int TILES_BYTES = STAGES * STAGE_BYTES;
-	static constexpr int TOTAL = TILES_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
 	static constexpr int EPI_WARPS = 4 * (BN / 128);  // one warp per (lane quarter, 128-column half)
+	static constexpr int STAGING_BYTES = EPI_WARPS * 4096;  // per epilogue warp: 32 rows x 32 columns of C
+	static constexpr int TOTAL = TILES_BYTES + STAGING_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
 	static constexpr int THREADS = 64 + 32 * EPI_WARPS;
 };
 
@@ -173,25 +174,84 @@ struct TcSmem
 // chunk into fp32 registers with round-to-nearest adds while the MMA warp fills the other of two
 // tensor-memory accumulators.
 
+// Where one epilogue warp's 32 x 128 block of C goes.  Normal path: 32-column pieces are written
+// into the warp's 4 KB staging area in the 128-byte-swizzled order of the tensor map and leave as
+// one bulk tensor store each, so global memory sees whole 128-byte rows instead of 32 scattered
+// 16-byte pieces per instruction, and the warp does not wait for the stores.  direct = the plain
+// per-thread float4 stores (comparison runs only).
+struct RowSink
+{
+	float* crow;    // direct path: this thread's row of C, and of the low-part matrix (or NULL)
+	float* lorow;
+	uint32_t stage; // shared-memory address of the warp's staging area
+	const CUtensorMap* mapC;
+	const CUtensorMap* mapClo;  // or NULL
+	int col0, row0;  // first column of the warp's block, first row of the warp's 32 rows
+	int lane;
+	bool direct;
+};
+
+__device__ __forceinline__ void sink_piece(const RowSink& k, const CUtensorMap* map, int piece, const float (&o)[32])
+{
+	// the staging area may still be read by the previous piece's store
+	if (k.lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+	__syncwarp();
+	const uint32_t rowaddr = k.stage + (uint32_t)k.lane * 128u;
+#pragma unroll
+	for (int v = 0; v < 8; ++v)
+		asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(rowaddr + (uint32_t)((v ^ (k.lane & 7)) << 4)),
+		             "f"(o[v * 4 + 0]), "f"(o[v * 4 + 1]), "f"(o[v * 4 + 2]), "f"(o[v * 4 + 3])
+		             : "memory");
+	asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+	__syncwarp();
+	if (k.lane == 0)
+	{
+		asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map), "r"(k.stage),
+		             "r"(k.col0 + piece * 32), "r"(k.row0)
+		             : "memory");
+		asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+	}
+}
+
 // One thread's 128 accumulators -> its row of C (and optionally the low TF32 parts), through the
 // element-wise function f(value, column).  Fully unrolled so that acc[] stays in registers.
 template <class F>
-__device__ __forceinline__ void store_row(const float (&acc)[128], float* crow, float* lorow, F f)
+__device__ __forceinline__ void store_row(const float (&acc)[128], const RowSink& k, F f)
 {
-#pragma unroll
-	for (int v = 0; v < 32; ++v)
+	if (k.direct)
 	{
-		const float o0 = f(acc[v * 4 + 0], v * 4 + 0), o1 = f(acc[v * 4 + 1], v * 4 + 1);
-		const float o2 = f(acc[v * 4 + 2], v * 4 + 2), o3 = f(acc[v * 4 + 3], v * 4 + 3);
-		*reinterpret_cast<float4*>(crow + v * 4) = make_float4(o0, o1, o2, o3);
-		if (lorow) *reinterpret_cast<float4*>(lorow + v * 4) = make_float4(tf32_lo(o0), tf32_lo(o1), tf32_lo(o2), tf32_lo(o3));
+#pragma unroll
+		for (int v = 0; v < 32; ++v)
+		{
+			const float o0 = f(acc[v * 4 + 0], v * 4 + 0), o1 = f(acc[v * 4 + 1], v * 4 + 1);
+			const float o2 = f(acc[v * 4 + 2], v * 4 + 2), o3 = f(acc[v * 4 + 3], v * 4 + 3);
+			*reinterpret_cast<float4*>(k.crow + v * 4) = make_float4(o0, o1, o2, o3);
+			if (k.lorow)
+				*reinterpret_cast<float4*>(k.lorow + v * 4) = make_float4(tf32_lo(o0), tf32_lo(o1), tf32_lo(o2), tf32_lo(o3));
+		}
+		return;
+	}
+#pragma unroll
+	for (int piece = 0; piece < 4; ++piece)
+	{
+		float o[32];
+#pragma unroll
+		for (int e = 0; e < 32; ++e) o[e] = f(acc[piece * 32 + e], piece * 32 + e);
+		sink_piece(k, k.mapC, piece, o);
+		if (k.mapClo)
+		{
+#pragma unroll
+			for (int e = 0; e < 32; ++e) o[e] = tf32_lo(o[e]);
+			sink_piece(k, k.mapClo, piece, o);
+		}
 	}
 }
 
 template <int BN, int BK, int STAGES>
 __global__ void __launch_bounds__(TcSmem<BN, BK, STAGES>::THREADS, 1)
     gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapAlo,
-                   const __grid_constant__ CUtensorMap mapB, const __grid_constant__ CUtensorMap mapBlo, const TcParams p)
+                   const __grid_constant__ CUtensorMap mapB, const __grid_constant__ CUtensorMap mapBlo,
+                   const __grid_constant__ CUtensorMap mapC, const __grid_constant__ CUtensorMap mapClo, const TcParams p)
 {
 	using S = TcSmem<BN, BK, STAGES>;
 	constexpr int TC_BK = BK;
@@ -201,8 +261,9 @@ __global__ void __launch_bounds__(TcSmem<BN, BK, STAGES>::THREADS, 1)
 	const uint32_t raw = smem_u32(smem_raw);
 	const uint32_t base = (raw + 1023u) & ~1023u;
 	uint8_t* gen_base = smem_raw + (base - raw);
-	uint64_t* bars = reinterpret_cast<uint64_t*>(gen_base + S::TILES_BYTES);
-	const uint32_t bar0 = base + S::TILES_BYTES;
+	const uint32_t staging0 = base + S::TILES_BYTES;  // 1024-byte aligned, as the swizzled stores need
+	uint64_t* bars = reinterpret_cast<uint64_t*>(gen_base + S::TILES_BYTES + S::STAGING_BYTES);
+	const uint32_t bar0 = base + S::TILES_BYTES + S::STAGING_BYTES;
 	// barrier slots: full[s] = s, empty[s] = STAGES + s, acc_full[b] = 2*STAGES + b, acc_empty[b] = 2*STAGES + 2 + b
 	constexpr int NBARS = 2 * STAGES + 4;
 	const uint32_t bar_acc_full = bar0 + 8 * (2 * STAGES);
@@ -426,8 +487,16 @@ __global__ void __launch_bounds__(TcSmem<BN, BK, STAGES>::THREADS, 1)
 		{
 			const int row = m0 + q * 32 + lane;
 			const int col0 = n0 + half * 128;
-			float* crow = p.C + (long long)row * p.ldc + col0;
-			float* lorow = p.C_lo ? p.C_lo + (long long)row * p.ldc + col0 : nullptr;
+			RowSink out;
+			out.crow = p.C + (long long)row * p.ldc + col0;
+			out.lorow = p.C_lo ? p.C_lo + (long long)row * p.ldc + col0 : nullptr;
+			out.stage = staging0 + (uint32_t)(warp - 2) * 4096u;
+			out.mapC = &mapC;
+			out.mapClo = p.C_lo ? &mapClo : nullptr;
+			out.col0 = col0;
+			out.row0 = m0 + q * 32;
+			out.lane = lane;
+			out.direct = (p.debug & 2) != 0;
 			// The element-wise part is chosen ONCE per tile: the store loop is fully unrolled (the
 			// accumulators must stay in registers), so a per-element switch over the activation ids would
 			// replicate the transcendental code 128 times and thrash the instruction cache.
@@ -448,27 +517,27 @@ __global__ void __launch_bounds__(TcSmem<BN, BK, STAGES>::THREADS, 1)
 						*reinterpret_cast<uint4*>(p.relu_mask_out + (long long)row * p.mask_ld + (col0 >> 5)) =
 						    make_uint4(wds[0], wds[1], wds[2], wds[3]);
 					}
-					store_row(acc, crow, lorow, [=](float z, int) { z += bias; return z < GL_OUTLIER ? 0.0f : z; });
+					store_row(acc, out, [=](float z, int) { z += bias; return z < GL_OUTLIER ? 0.0f : z; });
 					break;
 				case GL_ACT_LEAKY:
-					store_row(acc, crow, lorow, [=](float z, int) { z += bias; return z < GL_OUTLIER ? par * z : z; });
+					store_row(acc, out, [=](float z, int) { z += bias; return z < GL_OUTLIER ? par * z : z; });
 					break;
 				case GL_ACT_LINEAR:
-					store_row(acc, crow, lorow, [=](float z, int) { return par * (z + bias); });
+					store_row(acc, out, [=](float z, int) { return par * (z + bias); });
 					break;
 				case GL_ACT_SOFTMAX:
-					store_row(acc, crow, lorow, [=](float z, int) { return z + bias; });
+					store_row(acc, out, [=](float z, int) { return z + bias; });
 					break;
 				case GL_ACT_TANH:
-					store_row(acc, crow, lorow, [=](float z, int) { return tanhf(z + bias); });
+					store_row(acc, out, [=](float z, int) { return tanhf(z + bias); });
 					break;
 				case GL_ACT_SIGMOID:
-					store_row(acc, crow, lorow, [=](float z, int) { return 1.0f / (1.0f + expf(-(z + bias))); });
+					store_row(acc, out, [=](float z, int) { return 1.0f / (1.0f + expf(-(z + bias))); });
 					break;
 				default:
 				{
 					const int act = p.act;
-					store_row(acc, crow, lorow, [=](float z, int) { return squash_b(z + bias, act, par); });
+					store_row(acc, out, [=](float z, int) { return squash_b(z + bias, act, par); });
 					break;
 				}
 				}
@@ -477,7 +546,7 @@ __global__ void __launch_bounds__(TcSmem<BN, BK, STAGES>::THREADS, 1)
 			{
 				const uint4 mk = *reinterpret_cast<const uint4*>(p.relu_mask_in + (long long)row * p.mask_ld + (col0 >> 5));
 				const unsigned wds[4] = {mk.x, mk.y, mk.z, mk.w};
-				store_row(acc, crow, lorow, [=](float e, int c) { return ((wds[c >> 5] >> (c & 31)) & 1u) ? e : 0.0f; });
+				store_row(acc, out, [=](float e, int c) { return ((wds[c >> 5] >> (c & 31)) & 1u) ? e : 0.0f; });
 			}
 			else if (p.epi == EPI_ERRPROP)
 			{
@@ -486,20 +555,20 @@ __global__ void __launch_bounds__(TcSmem<BN, BK, STAGES>::THREADS, 1)
 				switch (p.act)
 				{
 				case GL_ACT_RELU:
-					store_row(acc, crow, lorow, [=](float e, int c) { return auxrow[c] > 0.0f ? e : 0.0f; });
+					store_row(acc, out, [=](float e, int c) { return auxrow[c] > 0.0f ? e : 0.0f; });
 					break;
 				case GL_ACT_TANH:
 				case GL_ACT_TANHP:
-					store_row(acc, crow, lorow, [=](float e, int c) { const float a = auxrow[c]; return e * (1.0f - a * a); });
+					store_row(acc, out, [=](float e, int c) { const float a = auxrow[c]; return e * (1.0f - a * a); });
 					break;
 				case GL_ACT_SIGMOID:
 				case GL_ACT_SIGMOIDP:
-					store_row(acc, crow, lorow, [=](float e, int c) { const float a = auxrow[c]; return e * (a * (1.0f - a)); });
+					store_row(acc, out, [=](float e, int c) { const float a = auxrow[c]; return e * (a * (1.0f - a)); });
 					break;
 				default:
 				{
 					const int act = p.act;
-					store_row(acc, crow, lorow, [=](float e, int c) { return e * act_der_b(auxrow[c], act, par); });
+					store_row(acc, out, [=](float e, int c) { return e * act_der_b(auxrow[c], act, par); });
 					break;
 				}
 				}
@@ -510,15 +579,17 @@ __global__ void __launch_bounds__(TcSmem<BN, BK, STAGES>::THREADS, 1)
 				if (p.colterm)
 				{
 					const float* ct = p.colterm + col0;
-					store_row(acc, crow, lorow, [=](float g, int c) { return alpha * g + ct[c]; });
+					store_row(acc, out, [=](float g, int c) { return alpha * g + ct[c]; });
 				}
 				else
-					store_row(acc, crow, lorow, [=](float g, int) { return alpha * g; });
+					store_row(acc, out, [=](float g, int) { return alpha * g; });
 			}
 			else
-				store_row(acc, crow, lorow, [](float v, int) { return v; });
+				store_row(acc, out, [](float v, int) { return v; });
 		}
 		}
+		// every bulk store of this warp must have completed before the CTA may exit
+		if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
 	}
 	asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
 	__syncthreads();
@@ -579,7 +650,8 @@ bool make_map(CUtensorMap* m, const float* ptr, int mn, long long R, long long K
 
 template <int BN, int BK, int STAGES>
 cudaError_t launch_cfg(const CUtensorMap& mA, const CUtensorMap& mAl, const CUtensorMap& mB, const CUtensorMap& mBl,
-                       const TcParams& p, int M, int N, int sm_reserve, cudaStream_t s)
+                       const CUtensorMap& mC, const CUtensorMap& mCl, const TcParams& p, int M, int N, int sm_reserve,
+                       cudaStream_t s)
 {
 	using S = TcSmem<BN, BK, STAGES>;
 	static bool attr_set = false;
@@ -603,7 +675,7 @@ cudaError_t launch_cfg(const CUtensorMap& mA, const CUtensorMap& mAl, const CUte
 	int avail = sm_count - sm_reserve;
 	if (avail < 1) avail = 1;
 	const int grid = total < avail ? total : avail;
-	gemm_tc_kernel<BN, BK, STAGES><<<grid, S::THREADS, S::TOTAL, s>>>(mA, mAl, mB, mBl, q);
+	gemm_tc_kernel<BN, BK, STAGES><<<grid, S::THREADS, S::TOTAL, s>>>(mA, mAl, mB, mBl, mC, mCl, q);
 	return cudaGetLastError();
 }
 
@@ -677,6 +749,11 @@ cudaError_t launch_gemm_tc(const GemmArgs& g, const float* A_lo, const float* B_
 	if (!make_map(&mA, g.A, a_mn, g.M, g.K, lda, TC_BM, bk) || !make_map(&mAl, A_lo, a_mn, g.M, g.K, lda, TC_BM, bk) ||
 	    !make_map(&mB, g.B, b_mn, g.N, g.K, ldb, BN, bk) || !make_map(&mBl, B_lo, b_mn, g.N, g.K, ldb, BN, bk))
 		return cudaErrorInvalidValue;
+	// C (and its low-part matrix) as [M][N] row-major with 32 x 32 boxes for the epilogue's bulk stores
+	CUtensorMap mC, mCl;
+	if (!make_map(&mC, g.C, 0, g.M, g.N, g.ldc, 32, 32)) return cudaErrorInvalidValue;
+	mCl = mC;
+	if (g.C_lo && !make_map(&mCl, g.C_lo, 0, g.M, g.N, g.ldc, 32, 32)) return cudaErrorInvalidValue;
 	TcParams p;
 	p.C = g.C;
 	p.C_lo = g.C_lo;
@@ -707,11 +784,11 @@ cudaError_t launch_gemm_tc(const GemmArgs& g, const float* A_lo, const float* B_
 	}
 	if (bk == 32)
 	{
-		if (BN == 256) return launch_cfg<256, 32, 2>(mA, mAl, mB, mBl, p, g.M, g.N, g.sm_reserve, s);
-		return launch_cfg<128, 32, 3>(mA, mAl, mB, mBl, p, g.M, g.N, g.sm_reserve, s);
+		if (BN == 256) return launch_cfg<256, 32, 2>(mA, mAl, mB, mBl, mC, mCl, p, g.M, g.N, g.sm_reserve, s);
+		return launch_cfg<128, 32, 3>(mA, mAl, mB, mBl, mC, mCl, p, g.M, g.N, g.sm_reserve, s);
 	}
-	if (BN == 256) return launch_cfg<256, 16, 4>(mA, mAl, mB, mBl, p, g.M, g.N, g.sm_reserve, s);
-	return launch_cfg<128, 16, 6>(mA, mAl, mB, mBl, p, g.M, g.N, g.sm_reserve, s);
+	if (BN == 256) return launch_cfg<256, 16, 4>(mA, mAl, mB, mBl, mC, mCl, p, g.M, g.N, g.sm_reserve, s);
+	return launch_cfg<128, 16, 6>(mA, mAl, mB, mBl, mC, mCl, p, g.M, g.N, g.sm_reserve, s);
 }
 
 cudaError_t launch_split_lo(const float* src, float* lo, long long count, cudaStream_t s)
