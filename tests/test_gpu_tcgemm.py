@@ -99,3 +99,15 @@ def test_batched_window_on_tensor_cores_vs_restatement(g, oracle, momentum, head
     assert np.max(np.abs(out_g - out_s)) <= 1e-5 * max(1.0, float(np.max(np.abs(out_s))))
     assert np.array_equal(am_g, am_s)
     net.close()
+
+
+def test_cta_pair_variant_in_a_subprocess():
+    """The CTA-pair (cta_group::2) variant of the product is selected by an environment variable that
+    is read once per process, so it is exercised by re-running the layout tests in a child process."""
+    import os
+    import subprocess
+    import sys
+    env = dict(os.environ, GLADES_TC_PAIR="1")
+    r = subprocess.run([sys.executable, "-m", "pytest", os.path.abspath(__file__), "-x", "-q", "-m", "gpu", "-k",
+                        "all_layouts and 256"], capture_output=True, text=True, env=env, timeout=600)
+    assert r.returncode == 0, r.stdout[-1500:] + r.stderr[-500:]
