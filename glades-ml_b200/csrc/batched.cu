@@ -101,8 +101,84 @@ __global__ void __launch_bounds__(FB_T) gemm_ffma_kernel(const GemmArgs g)
 	}
 }
 
+// ---------------------------------------------------------------------------------------------
+// Skinny products (N <= 16 output nodes, e.g. a 10-class or single-node output layer): the whole B
+// operand sits in shared memory, one warp per row of A, lanes stride over k with 16-byte loads, the
+// N partial sums are combined by warp shuffles.  Bound by reading A once from HBM.
+constexpr int SK_NMAX = 16;
+
+template <int EPI>
+__global__ void __launch_bounds__(256) gemm_skinny_kernel(const GemmArgs g)
+{
+	extern __shared__ __align__(16) float sW[];  // [N][K]
+	const int K = g.K, N = g.N;
+	for (int e = threadIdx.x; e < N * K; e += blockDim.x) sW[e] = g.B[(long long)(e / K) * g.b_sn + (e % K)];
+	__syncthreads();
+	const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, wpb = blockDim.x >> 5;
+	const float bias = (EPI == EPI_FORWARD && g.bias_ptr) ? *g.bias_ptr : 0.0f;
+	const int K4 = K >> 2;
+	for (long long m = (long long)blockIdx.x * wpb + warp; m < g.M; m += (long long)gridDim.x * wpb)
+	{
+		const float4* arow = reinterpret_cast<const float4*>(g.A + m * g.a_sm);
+		float acc[SK_NMAX];
+#pragma unroll
+		for (int n = 0; n < SK_NMAX; ++n) acc[n] = 0.0f;
+		for (int k4 = lane; k4 < K4; k4 += 32)
+		{
+			const float4 a = arow[k4];
+#pragma unroll
+			for (int n = 0; n < SK_NMAX; ++n)
+				if (n < N)
+				{
+					const float4 w = reinterpret_cast<const float4*>(sW + n * K)[k4];
+					acc[n] = fmaf(a.x, w.x, fmaf(a.y, w.y, fmaf(a.z, w.z, fmaf(a.w, w.w, acc[n]))));
+				}
+		}
+#pragma unroll
+		for (int n = 0; n < SK_NMAX; ++n)
+			if (n < N) acc[n] = warp_sum(acc[n]);
+		if (lane == 0)
+		{
+#pragma unroll
+			for (int n = 0; n < SK_NMAX; ++n)
+				if (n < N)
+				{
+					float v = acc[n];
+					if (EPI == EPI_FORWARD) v = squash_b(v + bias, g.act, g.par);
+					g.C[m * g.ldc + n] = v;
+				}
+		}
+	}
+}
+
+static bool skinny_ok(const GemmArgs& g)
+{
+	return (g.epi == EPI_FORWARD || g.epi == EPI_NONE) && g.N <= SK_NMAX && g.a_sk == 1 && g.b_sk == 1 && !g.kscale &&
+	       g.K % 4 == 0 && g.a_sm % 4 == 0 && (((uintptr_t)g.A) & 15) == 0 && (size_t)g.N * g.K * 4 <= 160 * 1024 && g.M >= 64;
+}
+
 cudaError_t launch_gemm_ffma(const GemmArgs& g, cudaStream_t s)
 {
+	if (skinny_ok(g))
+	{
+		const size_t bytes = (size_t)g.N * g.K * sizeof(float);
+		long long blocks = (g.M + 7) / 8;
+		if (blocks > 148 * 4) blocks = 148 * 4;
+		cudaError_t e;
+		if (g.epi == EPI_FORWARD)
+		{
+			e = cudaFuncSetAttribute(gemm_skinny_kernel<EPI_FORWARD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+			if (e != cudaSuccess) return e;
+			gemm_skinny_kernel<EPI_FORWARD><<<(unsigned)blocks, 256, bytes, s>>>(g);
+		}
+		else
+		{
+			e = cudaFuncSetAttribute(gemm_skinny_kernel<EPI_NONE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+			if (e != cudaSuccess) return e;
+			gemm_skinny_kernel<EPI_NONE><<<(unsigned)blocks, 256, bytes, s>>>(g);
+		}
+		return cudaGetLastError();
+	}
 	dim3 grid((g.N + FB_N - 1) / FB_N, (g.M + FB_M - 1) / FB_M);
 	switch (g.epi)
 	{
