@@ -521,7 +521,10 @@ def main():
     achieved = dom["flop"] / (dom["ms"] / 1000.0) / 1e12 if dom["ms"] > 0 else 0.0
     roofline = {
         "bound": "tensor", "kernel": dom_name, "achieved": achieved, "peak": peaks["tensor"], "unit": "TFLOP/s",
-        "frac": achieved / peaks["tensor"], "traffic": None, "peak_source": peaks["source"] + " dense bf16 (sustained)",
+        "frac": achieved / peaks["tensor"],
+        # DRAM bytes per launch of this kernel from one ncu capture of this very workload
+        # (profiles/gemm_tc_kernel_wide_mlp.md: 5.81 GB over the 8 products of a step); null elsewhere
+        "traffic": 0.726e9 if (dom is tc and args.workload == "wide_mlp" and world == 1) else None, "peak_source": peaks["source"] + " dense bf16 (sustained)",
         "launches": dom["launches"], "avg_launch_ms": dom["ms"] / max(1, dom["launches"]),
         "algorithmic_flop_per_launch": dom["flop"] / max(1, dom["launches"]),
         "note": "achieved counts algorithmic fp32 flop (2*M*N*K per product); the 3xTF32 mode issues 3 TF32 MMAs per "
