@@ -429,6 +429,7 @@ def main():
         uid_bytes = plumb.bcast_bytes(bytes(uid.raw))
         net.dp_init(rank, world, uid_bytes)
         net.dp_set_window(gb, rank * lb)
+    dp_mode = net.dp_mode()
 
     def step(i, want_metrics=False):
         r0 = (i % nwin) * lb
@@ -552,7 +553,10 @@ def main():
                        "l2": "inputs larger than L2: every step streams a distinct %.0f MB window plus %.0f MB of "
                              "weights and ~1 GB of activations" % (lb * (sizes[0] + sizes[-1]) * 4 / 1e6,
                                                                     net.nw * 4 / 1e6),
-                       "parallelism": "dp%d" % world},
+                       "parallelism": "dp%d" % world,
+                       "gradient_exchange": {0: None, 1: "NCCL all-reduce per layer, overlapped with the backward pass",
+                                             2: "row bands stored into their owner's memory by the gradient product's "
+                                                "epilogue over NVLink; owner sums, updates, writes every replica"}[dp_mode]},
             "e2e": {"value": e2e_value, "unit": "samples/s" if train else "rows/s", "h2d_bytes_per_step": xb + yb,
                     "d2h_bytes_per_step": d2h_bytes, "steps": e2e_steps},
             "gpu_launches": int(launches),

@@ -151,6 +151,7 @@ def lib():
         "gl_dp_unique_id": (C.c_int, [vp]),
         "gl_dp_init": (C.c_int, [vp, i32, i32, vp]),
         "gl_dp_set_window": (C.c_int, [vp, i32, i32]),
+        "gl_dp_mode": (C.c_int, [vp]),
         "gl_synth_fill": (C.c_int, [vp, i64, u64, u32, i32, f32, f32, i32]),
         "gl_matmul_static": (C.c_int, [vp, i64, i64, vp, i64, i64, vp, i64, i32, i32, i32, i32]),
         "gl_matmul_static_error": (C.c_char_p, []),
@@ -344,6 +345,10 @@ class Net:
     def dp_init(self, rank, world, id_bytes):
         buf = (C.c_char * 128).from_buffer_copy(id_bytes)
         _check(lib().gl_dp_init(self.h, rank, world, buf))
+
+    def dp_mode(self):
+        """0: not data parallel, 1: NCCL all-reduce per layer, 2: exchange over peer memory."""
+        return int(lib().gl_dp_mode(self.h))
 
     def dp_set_window(self, global_rows, first_pos):
         _check(lib().gl_dp_set_window(self.h, global_rows, first_pos))

@@ -70,12 +70,13 @@ struct NcclApi
 	int (*CommInitRank)(nccl_comm*, int, nccl_uid, int) = nullptr;
 	int (*CommDestroy)(nccl_comm) = nullptr;
 	int (*AllReduce)(const void*, void*, size_t, int, int, nccl_comm, cudaStream_t) = nullptr;
+	int (*AllGather)(const void*, void*, size_t, int, nccl_comm, cudaStream_t) = nullptr;
 	int (*GroupStart)() = nullptr;
 	int (*GroupEnd)() = nullptr;
 	const char* (*GetErrorString)(int) = nullptr;
 };
 NcclApi g_nccl;
-enum { NCCL_INT32 = 2, NCCL_FLOAT32 = 7, NCCL_FLOAT64 = 8, NCCL_SUM = 0 };
+enum { NCCL_INT8 = 0, NCCL_INT32 = 2, NCCL_FLOAT32 = 7, NCCL_FLOAT64 = 8, NCCL_SUM = 0 };
 
 int nccl_load()
 {
@@ -93,6 +94,7 @@ int nccl_load()
 	g_nccl.CommDestroy = (int (*)(nccl_comm))dlsym(so, "ncclCommDestroy");
 	g_nccl.AllReduce =
 	    (int (*)(const void*, void*, size_t, int, int, nccl_comm, cudaStream_t))dlsym(so, "ncclAllReduce");
+	g_nccl.AllGather = (int (*)(const void*, void*, size_t, int, nccl_comm, cudaStream_t))dlsym(so, "ncclAllGather");
 	g_nccl.GroupStart = (int (*)())dlsym(so, "ncclGroupStart");
 	g_nccl.GroupEnd = (int (*)())dlsym(so, "ncclGroupEnd");
 	g_nccl.GetErrorString = (const char* (*)(int))dlsym(so, "ncclGetErrorString");
@@ -212,6 +214,18 @@ struct gl_net
 	cudaEvent_t evComm = nullptr;
 	int dpOverlap = 1;
 	int dpReserveSms = 8;
+	// gradient exchange over peer memory (dp_push.cu); dpPush == false: the NCCL all-reduce path
+	bool dpPush = false;
+	unsigned dpStep = 0;                 // window counter, the value the flags are raised to
+	char* dpArena = nullptr;             // this rank's arena: flag area, then one gradient slot per source rank
+	void* dpPeerArena[DP_MAX_WORLD] = {}; // every rank's arena as mapped here (own entry = dpArena)
+	void* dpPeerW[DP_MAX_WORLD] = {};     // every rank's weight vector as mapped here (own entry = dW)
+	int dpBand[GL_MAX_WEIGHT_LAYERS] = {};        // rows of layer l's gradient per owner (a multiple of 128)
+	int64_t dpSlotOff[GL_MAX_WEIGHT_LAYERS + 1] = {};  // float offset of layer l inside a slot; [H+1] = slot size
+	void* dpMaps = nullptr;              // device: [layer][owner] tensor maps of the owners' bands (this rank's slot)
+	float** dpBases = nullptr;           // device: [layer][owner] base pointers of the same
+	float* hostBases[GL_MAX_WEIGHT_LAYERS][DP_MAX_WORLD] = {};
+	int dpPushBlocks = 32;               // CTAs of an owner's update kernel while the backward pass still runs
 };
 
 static NetView make_view(const gl_net* n)
@@ -343,12 +357,27 @@ static void free_work(gl_net* n)
 	n->cRows = -1;
 }
 
+static void dp_push_release(gl_net* n);
+static void dp_barrier(gl_net* n)
+{
+	if (!n->comm || !n->dFlags) return;
+	if (g_nccl.AllReduce(n->dFlags + 2, n->dFlags + 2, 1, NCCL_INT32, NCCL_SUM, n->comm, n->stream) == 0) cudaStreamSynchronize(n->stream);
+}
+
 extern "C" int gl_destroy(gl_net* n)
 {
 	if (!n) return GL_OK;
 	cudaSetDevice(n->d.device);
 	if (n->stream) cudaStreamSynchronize(n->stream);
 	if (n->commStream) cudaStreamSynchronize(n->commStream);
+	if (n->dpArena)
+	{
+		// peers may still be writing into this rank's memory, and this rank maps theirs: meet once
+		// before unmapping and once before the memory goes away
+		dp_barrier(n);
+		dp_push_release(n);
+		dp_barrier(n);
+	}
 	if (n->comm && g_nccl.CommDestroy) g_nccl.CommDestroy(n->comm);
 	if (n->commStream) cudaStreamDestroy(n->commStream);
 	for (int l = 0; l <= GL_MAX_WEIGHT_LAYERS; ++l) if (n->evGrad[l]) cudaEventDestroy(n->evGrad[l]);
@@ -433,6 +462,8 @@ extern "C" int gl_set_weights(gl_net* n, const float* w, const float* bias)
 		CU(cudaMemsetAsync(n->dHistLen, 0, sizeof(int), n->stream));
 	}
 	CU(cudaMemsetAsync(n->dFlags, 0, 4 * sizeof(int), n->stream));
+	if (n->dpArena)  // the owners' sticky "non-finite weight" words belong to the old weights
+		CU(cudaMemsetAsync(n->dpArena + DP_WORD_BAD * sizeof(unsigned), 0, DP_MAX_WORLD * sizeof(unsigned), n->stream));
 	CU(cudaStreamSynchronize(n->stream));
 	n->loW = false;
 	return GL_OK;
@@ -663,7 +694,11 @@ static int run_gemm(gl_net* n, GemmArgs g, Operand a, Operand b, int64_t* launch
 		     (n->d.gemm == GL_GEMM_TCGEN05 || (long long)g.M * g.N * g.K >= (1ll << 24));
 	}
 	if (used_tc) *used_tc = tc;
-	if (!tc) g.C_lo = nullptr;
+	if (!tc)
+	{
+		g.C_lo = nullptr;
+		g.peer_maps = nullptr;  // the FFMA kernel writes the local C; the caller forwards it
+	}
 	cudaEvent_t pe0 = nullptr, pe1 = nullptr;
 	if (n->profile)
 	{
@@ -798,6 +833,14 @@ static int batched_window(gl_net* n, const float* X, const float* Y, int rows, i
 	if (int r = set_momentum_weights(n, rows, global_rows, first_pos)) return r;
 	int64_t launches = 0;
 	double* const sums2 = n->winSums ? n->winSums : n->dSums;
+	const bool push = n->world > 1 && n->dpPush;
+	const unsigned stepv = push ? ++n->dpStep : 0u;
+	DpPeers peerFlags, peerW;
+	for (int r = 0; r < DP_MAX_WORLD; ++r)
+	{
+		peerFlags.p[r] = n->dpPeerArena[r];
+		peerW.p[r] = n->dpPeerW[r];
+	}
 	CU(cudaEventRecord(n->ev0, n->stream));
 	CU(cudaMemsetAsync(sums2, 0, 2 * sizeof(double), n->stream));
 	CU(cudaMemsetAsync(n->dG + n->nw, 0, GL_MAX_WEIGHT_LAYERS * sizeof(float), n->stream));
@@ -867,14 +910,49 @@ static int batched_window(gl_net* n, const float* X, const float* Y, int rows, i
 			g.alpha = n->d.lr[l];
 			g.colterm = colterm;
 			g.sm_reserve = (n->world > 1 && n->dpOverlap && L <= n->H) ? n->dpReserveSms : 0;
-			if (int r = run_gemm(n, g, opD, op_act(n, l, X, rows), &launches)) return r;
+			if (push)
+			{
+				// the tensor-core epilogue stores every row band straight into its owner's memory
+				g.peer_maps = static_cast<const char*>(n->dpMaps) + (size_t)l * DP_MAX_WORLD * 128;
+				g.peer_bases = n->dpBases + (size_t)l * DP_MAX_WORLD;
+				g.band_rows = n->dpBand[l];
+			}
+			bool gtc = false;
+			if (int r = run_gemm(n, g, opD, op_act(n, l, X, rows), &launches, &gtc)) return r;
+			if (push && !gtc)
+			{
+				DpPeers slot;
+				for (int o = 0; o < DP_MAX_WORLD; ++o) slot.p[o] = n->hostBases[l][o];
+				CU(launch_dp_push_bands(n->dG + n->woff[l], no, ni, n->dpBand[l], slot, n->stream));
+				++launches;
+			}
 		}
 		if (l >= 1)
 		{
 			CU(launch_sum_scaled(n->dD[L], (int64_t)rows * no, n->d.lr[l], n->dG + n->nw + l, n->stream));
 			++launches;
 		}
-		if (n->world > 1 && n->dpOverlap)
+		if (push)
+		{
+			// this rank's contributions to layer l have been stored at their owners: tell them, and let
+			// the communication stream do this rank's own band (sum the sources in rank order, update,
+			// write the new weights into every replica) while the main stream goes on with the layers below
+			CU(launch_dp_signal(peerFlags, n->world, DP_WORD_GFLAG + l * DP_MAX_WORLD + n->rank, stepv, n->stream));
+			CU(cudaEventRecord(n->evGrad[l], n->stream));
+			CU(cudaStreamWaitEvent(n->commStream, n->evGrad[l], 0));
+			CU(launch_dp_wait(n->dpArena, DP_WORD_GFLAG + l * DP_MAX_WORLD, 1, n->world, 0, 0, stepv, n->dFlags + 1, 20 + l,
+			                  n->commStream));
+			const int band = n->dpBand[l];
+			int own_rows = no - n->rank * band;
+			own_rows = own_rows < 0 ? 0 : (own_rows > band ? band : own_rows);
+			const float* part = reinterpret_cast<const float*>(n->dpArena + DP_FLAG_BYTES) + n->dpSlotOff[l];
+			CU(launch_dp_reduce_update(part, n->dpSlotOff[n->H + 1], n->world, (long long)own_rows * ni, 1.0f / (float)global_rows,
+			                           n->woff[l] + (long long)n->rank * band * ni, peerW, n->rank, peerFlags,
+			                           l == 0 ? 148 * 4 : n->dpPushBlocks, n->commStream));
+			CU(launch_dp_signal(peerFlags, n->world, DP_WORD_WFLAG + l * DP_MAX_WORLD + n->rank, stepv, n->commStream));
+			launches += 4;
+		}
+		else if (n->world > 1 && n->dpOverlap)
 		{
 			// this layer's gradient is complete: reduce it on the communication stream while the main
 			// stream goes on with the layers below
@@ -884,7 +962,7 @@ static int batched_window(gl_net* n, const float* X, const float* Y, int rows, i
 			                    NCCL_SUM, n->comm, n->commStream));
 		}
 	}
-	if (n->world > 1)
+	if (n->world > 1 && !push)
 	{
 		if (n->dpOverlap)
 		{
@@ -914,10 +992,25 @@ static int batched_window(gl_net* n, const float* X, const float* Y, int rows, i
 		CU(cudaStreamSynchronize(n->stream));
 		n->bscaleRows = global_rows;
 	}
-	CU(launch_update(n->dW, n->dWlo, n->dG, n->nw, 1.0f / (float)global_rows, n->dBias, n->dG + n->nw, n->dBscale, n->H,
-	                 n->dFlags, n->stream));
-	++launches;
-	n->loW = n->dWlo != nullptr;
+	if (push)
+	{
+		// bias and loss sums of this rank to everyone; then wait until every owner's band of every layer
+		// and every rank's record have landed here, and finish the window locally
+		CU(launch_dp_small_push(n->dG + n->nw, sums2, peerFlags, n->world, n->rank, (int)(stepv & 1u), stepv, n->stream));
+		CU(launch_dp_wait(n->dpArena, DP_WORD_WFLAG, n->H + 1, n->world, DP_WORD_SFLAG, n->world, stepv, n->dFlags + 1, 40,
+		                  n->stream));
+		CU(launch_dp_finish(n->dpArena, n->world, (int)(stepv & 1u), n->dG + n->nw, sums2, n->dBias, n->dBscale, n->H, n->dFlags,
+		                    n->stream));
+		launches += 3;
+		n->loW = false;  // the low TF32 parts of the new weights are split off before the next product
+	}
+	else
+	{
+		CU(launch_update(n->dW, n->dWlo, n->dG, n->nw, 1.0f / (float)global_rows, n->dBias, n->dG + n->nw, n->dBscale, n->H,
+		                 n->dFlags, n->stream));
+		++launches;
+		n->loW = n->dWlo != nullptr;
+	}
 	CU(cudaEventRecord(n->ev1, n->stream));
 	n->launches += launches;
 	n->lastWindowLaunches = launches;
@@ -938,7 +1031,7 @@ static int batched_window(gl_net* n, const float* X, const float* Y, int rows, i
 		int flags[4];
 		CU(cudaMemcpy(flags, n->dFlags, sizeof flags, cudaMemcpyDeviceToHost));
 		out->nonfinite = flags[0] & 1;
-		if (flags[1]) return fail(GL_ERR_TIMEOUT, "a bounded wait inside the tensor-core kernel ran out (role %d)", flags[1]);
+		if (flags[1]) return fail(GL_ERR_TIMEOUT, "a bounded wait on the device ran out (code %d: 1-4 tensor-core pipeline, 20+ gradient exchange)", flags[1]);
 	}
 	return GL_OK;
 }
@@ -1063,7 +1156,7 @@ extern "C" int gl_train_window_host_result(gl_net* n, gl_metrics* out)
 		out->kernel_launches = sl.launches;
 		out->nonfinite = flags[0] & 1;
 	}
-	if (flags[1]) return fail(GL_ERR_TIMEOUT, "a bounded wait inside the tensor-core kernel ran out (role %d)", flags[1]);
+	if (flags[1]) return fail(GL_ERR_TIMEOUT, "a bounded wait on the device ran out (code %d: 1-4 tensor-core pipeline, 20+ gradient exchange)", flags[1]);
 	return GL_OK;
 }
 
@@ -1364,6 +1457,125 @@ extern "C" void gl_shard_range(int64_t rows, int32_t rank, int32_t world, int64_
 	if (count) *count = base + (rank < rem ? 1 : 0);
 }
 
+
+// Unmaps the peers' memory and frees this rank's exchange buffers (no collective inside).
+static void dp_push_release(gl_net* n)
+{
+	for (int r = 0; r < DP_MAX_WORLD; ++r)
+	{
+		if (r != n->rank)
+		{
+			if (n->dpPeerArena[r]) cudaIpcCloseMemHandle(n->dpPeerArena[r]);
+			if (n->dpPeerW[r]) cudaIpcCloseMemHandle(n->dpPeerW[r]);
+		}
+		n->dpPeerArena[r] = nullptr;
+		n->dpPeerW[r] = nullptr;
+	}
+	cudaFree(n->dpMaps);
+	cudaFree(n->dpBases);
+	cudaFree(n->dpArena);
+	n->dpMaps = nullptr;
+	n->dpBases = nullptr;
+	n->dpArena = nullptr;
+	n->dpPush = false;
+	cudaGetLastError();
+}
+
+// Sets up the gradient exchange over peer memory: bands, the exchange arena, the inter-process
+// mappings of every rank's arena and weight vector, the per-owner tensor maps.  Collective: every
+// rank of the communicator calls it.  On failure the handle stays on the NCCL path.
+static int dp_push_setup(gl_net* n)
+{
+	const int W = n->world;
+	if (W > DP_MAX_WORLD) return fail(GL_ERR_INVALID, "the peer-memory exchange handles at most %d ranks", DP_MAX_WORLD);
+	if (!g_nccl.AllGather) return fail(GL_ERR_COMM, "libnccl lacks ncclAllGather");
+	int64_t off = 0;
+	for (int l = 0; l <= n->H; ++l)
+	{
+		const int no = n->d.sizes[l + 1], ni = n->d.sizes[l];
+		const int per = (no + W - 1) / W;
+		n->dpBand[l] = ((per + 127) / 128) * 128;
+		n->dpSlotOff[l] = off;
+		const int64_t cap = (int64_t)(n->dpBand[l] < no ? n->dpBand[l] : no) * ni;
+		off += ((cap + 3) / 4) * 4;
+	}
+	n->dpSlotOff[n->H + 1] = off;
+	const size_t bytes = DP_FLAG_BYTES + (size_t)W * (size_t)off * sizeof(float);
+	CU(cudaMalloc(&n->dpArena, bytes));
+	CU(cudaMemset(n->dpArena, 0, bytes));
+	struct Rec { cudaIpcMemHandle_t arena, w; };
+	Rec mine;
+	CU(cudaIpcGetMemHandle(&mine.arena, n->dpArena));
+	CU(cudaIpcGetMemHandle(&mine.w, n->dW));
+	Rec* dRec = nullptr;
+	CU(cudaMalloc(&dRec, sizeof(Rec) * (size_t)(W + 1)));
+	CU(cudaMemcpy(dRec + W, &mine, sizeof mine, cudaMemcpyHostToDevice));
+	NC(g_nccl.AllGather(dRec + W, dRec, sizeof(Rec), NCCL_INT8, n->comm, n->stream));
+	CU(cudaStreamSynchronize(n->stream));
+	std::vector<Rec> all((size_t)W);
+	CU(cudaMemcpy(all.data(), dRec, sizeof(Rec) * (size_t)W, cudaMemcpyDeviceToHost));
+	int failed = 0;
+	for (int r = 0; r < W; ++r)
+	{
+		if (r == n->rank)
+		{
+			n->dpPeerArena[r] = n->dpArena;
+			n->dpPeerW[r] = n->dW;
+			continue;
+		}
+		if (cudaIpcOpenMemHandle(&n->dpPeerArena[r], all[(size_t)r].arena, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess ||
+		    cudaIpcOpenMemHandle(&n->dpPeerW[r], all[(size_t)r].w, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess)
+		{
+			cudaGetLastError();
+			failed = 1;
+			break;
+		}
+	}
+	// every rank must take the same path: agree on the outcome
+	int* dAgree = reinterpret_cast<int*>(dRec);
+	CU(cudaMemcpy(dAgree, &failed, sizeof failed, cudaMemcpyHostToDevice));
+	NC(g_nccl.AllReduce(dAgree, dAgree, 1, NCCL_INT32, NCCL_SUM, n->comm, n->stream));
+	CU(cudaStreamSynchronize(n->stream));
+	CU(cudaMemcpy(&failed, dAgree, sizeof failed, cudaMemcpyDeviceToHost));
+	if (failed)
+	{
+		dp_push_release(n);
+		cudaFree(dRec);
+		return fail(GL_ERR_COMM, "the ranks cannot map each other's device memory; staying on the NCCL all-reduce");
+	}
+	// per layer and owner: where this rank's contribution to the owner's band goes
+	const size_t nmaps = (size_t)GL_MAX_WEIGHT_LAYERS * DP_MAX_WORLD;
+	std::vector<unsigned char> raw(nmaps * 128 + 64);
+	unsigned char* maps = raw.data() + ((64 - ((uintptr_t)raw.data() & 63)) & 63);
+	std::vector<float*> bases(nmaps, nullptr);
+	for (int l = 0; l <= n->H; ++l)
+	{
+		const int no = n->d.sizes[l + 1], ni = n->d.sizes[l];
+		for (int o = 0; o < W; ++o)
+		{
+			int rows = no - o * n->dpBand[l];
+			rows = rows < 0 ? 0 : (rows > n->dpBand[l] ? n->dpBand[l] : rows);
+			float* base = reinterpret_cast<float*>(static_cast<char*>(n->dpPeerArena[o]) + DP_FLAG_BYTES) +
+			              (int64_t)n->rank * off + n->dpSlotOff[l];
+			bases[(size_t)l * DP_MAX_WORLD + o] = base;
+			n->hostBases[l][o] = base;
+			if (rows >= 128 && rows % 128 == 0 && ni % 128 == 0)
+				tc_make_store_map(maps + ((size_t)l * DP_MAX_WORLD + o) * 128, base, rows, ni, ni);
+		}
+	}
+	CU(cudaMalloc(&n->dpMaps, nmaps * 128));
+	CU(cudaMalloc(&n->dpBases, nmaps * sizeof(float*)));
+	CU(cudaMemcpy(n->dpMaps, maps, nmaps * 128, cudaMemcpyHostToDevice));
+	CU(cudaMemcpy(n->dpBases, bases.data(), nmaps * sizeof(float*), cudaMemcpyHostToDevice));
+	// nobody writes into a peer before every rank has zeroed and mapped everything
+	NC(g_nccl.AllReduce(dAgree, dAgree, 1, NCCL_INT32, NCCL_SUM, n->comm, n->stream));
+	CU(cudaStreamSynchronize(n->stream));
+	cudaFree(dRec);
+	n->dpPush = true;
+	n->dpStep = 0;
+	return GL_OK;
+}
+
 extern "C" int gl_dp_unique_id(void* id128)
 {
 	if (!id128) return fail(GL_ERR_INVALID, "gl_dp_unique_id: null argument");
@@ -1386,13 +1598,30 @@ extern "C" int gl_dp_init(gl_net* n, int32_t rank, int32_t world, const void* id
 	nccl_uid id;
 	memcpy(&id, id128, sizeof id);
 	NC(g_nccl.CommInitRank(&n->comm, world, id, rank));
-	CU(cudaStreamCreateWithFlags(&n->commStream, cudaStreamNonBlocking));
+	{
+		// the exchange work is short and sits on the critical path: let its CTAs go first
+		int lo = 0, hi = 0;
+		CU(cudaDeviceGetStreamPriorityRange(&lo, &hi));
+		CU(cudaStreamCreateWithPriority(&n->commStream, cudaStreamNonBlocking, hi));
+	}
 	for (int l = 0; l <= GL_MAX_WEIGHT_LAYERS; ++l) CU(cudaEventCreateWithFlags(&n->evGrad[l], cudaEventDisableTiming));
 	CU(cudaEventCreateWithFlags(&n->evComm, cudaEventDisableTiming));
 	if (const char* e = getenv("GLADES_DP_OVERLAP")) n->dpOverlap = atoi(e) != 0;
 	if (const char* e = getenv("GLADES_DP_RESERVE_SMS")) n->dpReserveSms = atoi(e);
+	if (const char* e = getenv("GLADES_DP_PUSH_BLOCKS")) n->dpPushBlocks = atoi(e) > 0 ? atoi(e) : 32;
+	// GLADES_DP_PUSH=0: the NCCL all-reduce path; =1: the exchange over peer memory or an error;
+	// unset: the exchange over peer memory when the ranks can map each other's memory, else NCCL
+	const char* e = getenv("GLADES_DP_PUSH");
+	const int want = e ? atoi(e) : -1;
+	if (want != 0)
+	{
+		const int r = dp_push_setup(n);
+		if (r != GL_OK && want == 1) return r;
+	}
 	return GL_OK;
 }
+
+extern "C" int gl_dp_mode(const gl_net* n) { return (n && n->world > 1) ? (n->dpPush ? 2 : 1) : 0; }
 
 extern "C" int gl_dp_set_window(gl_net* n, int32_t global_rows, int32_t first_global_pos)
 {
@@ -1470,7 +1699,7 @@ extern "C" int gl_sync(gl_net* n)
 	CU(cudaStreamSynchronize(n->stream));
 	int flags[4];
 	CU(cudaMemcpy(flags, n->dFlags, sizeof flags, cudaMemcpyDeviceToHost));
-	if (flags[1]) return fail(GL_ERR_TIMEOUT, "a bounded wait inside the tensor-core kernel ran out (role %d)", flags[1]);
+	if (flags[1]) return fail(GL_ERR_TIMEOUT, "a bounded wait on the device ran out (code %d: 1-4 tensor-core pipeline, 20+ gradient exchange)", flags[1]);
 	return GL_OK;
 }
 

@@ -48,11 +48,15 @@ struct TcSmem
 // chunk into fp32 registers with round-to-nearest adds while the MMA warp fills the other of two
 // tensor-memory accumulators.
 
-template <int BN, int BK, int STAGES, int SBUF>
+// PEER: the data-parallel weight-gradient variant, whose epilogue (learning rate, decay term) stores
+// each tile into the memory of the rank that owns its row band; a separate instantiation so that the
+// register allocation of the plain kernel stays as it was tuned.
+template <int BN, int BK, int STAGES, int SBUF, bool PEER>
 __global__ void __launch_bounds__(TcSmem<BN, BK, STAGES, SBUF>::THREADS, 1)
     gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapAlo,
                    const __grid_constant__ CUtensorMap mapB, const __grid_constant__ CUtensorMap mapBlo,
-                   const __grid_constant__ CUtensorMap mapC, const __grid_constant__ CUtensorMap mapClo, const TcParams p)
+                   const __grid_constant__ CUtensorMap mapC, const __grid_constant__ CUtensorMap mapClo, const TcParams p,
+                   const TcPeer peer)
 {
 	using S = TcSmem<BN, BK, STAGES, SBUF>;
 	constexpr int TC_BK = BK;
@@ -301,7 +305,24 @@ __global__ void __launch_bounds__(TcSmem<BN, BK, STAGES, SBUF>::THREADS, 1)
 			out.row0 = m0 + q * 32;
 			out.lane = lane;
 			out.direct = (p.debug & 2) != 0;
-			apply_epilogue(acc, out, p, row, col0);
+			if (PEER)
+			{
+				// the tile's rows lie inside one owner's band (bands are whole tiles): store them there
+				const int owner = m0 / peer.band_rows;
+				out.mapC = peer.maps + owner;
+				out.row0 = m0 - owner * peer.band_rows + q * 32;
+				if (out.direct) out.crow = peer.bases[owner] + (long long)(out.row0 + lane) * p.ldc + col0;
+				const float alpha = p.alpha;
+				if (p.colterm)
+				{
+					const float* ct = p.colterm + col0;
+					store_row(acc, out, [=](float g, int c) { return alpha * g + ct[c]; });
+				}
+				else
+					store_row(acc, out, [=](float g, int) { return alpha * g; });
+			}
+			else
+				apply_epilogue(acc, out, p, row, col0);
 		}
 		}
 		// every bulk store of this warp must have completed before the CTA may exit
@@ -364,16 +385,16 @@ bool make_map(CUtensorMap* m, const float* ptr, int mn, long long R, long long K
 	return r == CUDA_SUCCESS;
 }
 
-template <int BN, int BK, int STAGES, int SBUF>
+template <int BN, int BK, int STAGES, int SBUF, bool PEER = false>
 cudaError_t launch_cfg(const CUtensorMap& mA, const CUtensorMap& mAl, const CUtensorMap& mB, const CUtensorMap& mBl,
                        const CUtensorMap& mC, const CUtensorMap& mCl, const TcParams& p, int M, int N, int sm_reserve,
-                       cudaStream_t s)
+                       cudaStream_t s, const TcPeer& peer = TcPeer())
 {
 	using S = TcSmem<BN, BK, STAGES, SBUF>;
 	static bool attr_set = false;
 	if (!attr_set)
 	{
-		cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, BK, STAGES, SBUF>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
+		cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, BK, STAGES, SBUF, PEER>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
 		if (e != cudaSuccess) return e;
 		attr_set = true;
 	}
@@ -391,7 +412,7 @@ cudaError_t launch_cfg(const CUtensorMap& mA, const CUtensorMap& mAl, const CUte
 	int avail = sm_count - sm_reserve;
 	if (avail < 1) avail = 1;
 	const int grid = total < avail ? total : avail;
-	gemm_tc_kernel<BN, BK, STAGES, SBUF><<<grid, S::THREADS, S::TOTAL, s>>>(mA, mAl, mB, mBl, mC, mCl, q);
+	gemm_tc_kernel<BN, BK, STAGES, SBUF, PEER><<<grid, S::THREADS, S::TOTAL, s>>>(mA, mAl, mB, mBl, mC, mCl, q, peer);
 	return cudaGetLastError();
 }
 
@@ -421,6 +442,11 @@ __global__ void __launch_bounds__(256) scale_split_lo_kernel(const float* __rest
 }
 
 }  // namespace
+
+bool tc_make_store_map(void* out128, const float* base, long long rows, long long cols, long long ld)
+{
+	return make_map(reinterpret_cast<CUtensorMap*>(out128), base, 0, rows, cols, ld, 32, 32);
+}
 
 // k-block depth of the tile variant in use: 16 (default) or 32 (GLADES_TC_BK=32, kept for comparison)
 int tc::tc_bk()
@@ -461,7 +487,7 @@ cudaError_t launch_gemm_tc(const GemmArgs& g, const float* A_lo, const float* B_
 	// tile variant: 16-deep k-blocks with twice the stages by default; GLADES_TC_BK=32 selects the
 	// 32-deep blocks (kept for comparison runs)
 	const int bk = tc_bk();
-	const bool pair = tc_pair_supported(g);
+	const bool pair = !g.peer_maps && tc_pair_supported(g);
 	const int box_b = pair ? 128 : BN;  // a CTA of a pair loads half of the 256-wide B tile
 	CUtensorMap mA, mAl, mB, mBl;
 	if (!make_map(&mA, g.A, a_mn, g.M, g.K, lda, TC_BM, bk) || !make_map(&mAl, A_lo, a_mn, g.M, g.K, lda, TC_BM, bk) ||
@@ -491,6 +517,11 @@ cudaError_t launch_gemm_tc(const GemmArgs& g, const float* A_lo, const float* B_
 	p.relu_mask_in = g.relu_mask_in;
 	p.mask_ld = g.N / 32;
 	p.err_flag = err_flag;
+	TcPeer peer;
+	peer.maps = reinterpret_cast<const CUtensorMap*>(g.peer_maps);
+	peer.bases = g.peer_bases;
+	peer.band_rows = g.band_rows;
+	if (g.peer_maps && (g.band_rows < TC_BM || g.band_rows % TC_BM || g.C_lo)) return cudaErrorInvalidValue;
 	{
 		static int dbg = -1;
 		if (dbg < 0)
@@ -504,6 +535,12 @@ cudaError_t launch_gemm_tc(const GemmArgs& g, const float* A_lo, const float* B_
 	{
 		const CUtensorMap maps[6] = {mA, mAl, mB, mBl, mC, mCl};
 		return launch_gemm_tc_pair(maps, p, g.M, g.N, g.sm_reserve, s);
+	}
+	if (g.peer_maps)
+	{
+		if (g.epi != EPI_GRAD) return cudaErrorInvalidValue;
+		if (BN == 256) return launch_cfg<256, 16, 4, 1, true>(mA, mAl, mB, mBl, mC, mCl, p, g.M, g.N, g.sm_reserve, s, peer);
+		return launch_cfg<128, 16, 6, 2, true>(mA, mAl, mB, mBl, mC, mCl, p, g.M, g.N, g.sm_reserve, s, peer);
 	}
 	if (bk == 32)
 	{

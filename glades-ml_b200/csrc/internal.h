@@ -76,6 +76,11 @@ struct GemmArgs
 	unsigned* relu_mask_out;
 	const unsigned* relu_mask_in;
 	int sm_reserve;        // tensor-core kernel: leave this many SMs without a CTA (for a concurrent collective)
+	// tensor-core kernel, data-parallel weight gradient: row band o of C goes to rank o's memory through
+	// peer_maps[o] (device array of 128-byte tensor maps) / peer_bases[o]; NULL = everything to C
+	const void* peer_maps;
+	float* const* peer_bases;
+	int band_rows;
 };
 cudaError_t launch_gemm_ffma(const GemmArgs& g, cudaStream_t s);
 
@@ -123,6 +128,38 @@ struct SmallFusedArgs
 };
 size_t small_fused_smem_bytes(const NetView& n);
 cudaError_t launch_small_fused(const SmallFusedArgs& a, cudaStream_t s);
+
+// ---- data-parallel gradient exchange over peer memory (dp_push.cu) ---------------------------------
+// Every rank owns an exchange arena that all ranks map: a flag area of DP_FLAG_BYTES (32-bit window
+// counters written by peers, then the small per-rank records) followed by one gradient slot per
+// source rank.  Word indices inside the flag area:
+//   DP_WORD_GFLAG + l * DP_MAX_WORLD + src    src's contribution to layer l has landed here
+//   DP_WORD_WFLAG + l * DP_MAX_WORLD + owner  owner's band of the new layer-l weights has landed here
+//   DP_WORD_SFLAG + src                       src's bias / loss record has landed here
+//   DP_WORD_BAD + owner                       owner saw a non-finite weight (sticky)
+enum
+{
+	DP_MAX_WORLD = 8,
+	DP_WORD_GFLAG = 0,
+	DP_WORD_WFLAG = GL_MAX_WEIGHT_LAYERS * DP_MAX_WORLD,
+	DP_WORD_SFLAG = 2 * GL_MAX_WEIGHT_LAYERS * DP_MAX_WORLD,
+	DP_WORD_BAD = DP_WORD_SFLAG + DP_MAX_WORLD,
+	DP_SMALL_OFFSET = 2048,  // bytes: records [parity 2][rank DP_MAX_WORLD][DP_SMALL_BYTES]
+	DP_SMALL_BYTES = 128,    // GL_MAX_WEIGHT_LAYERS floats (bias sums) + 2 doubles (cost, accuracy sums)
+	DP_FLAG_BYTES = 4096
+};
+struct DpPeers { void* p[DP_MAX_WORLD]; };  // one pointer per rank (this rank's own entry is a local pointer)
+
+cudaError_t launch_dp_signal(const DpPeers& flags, int world, int word, unsigned value, cudaStream_t s);
+cudaError_t launch_dp_wait(const void* arena, int w0, int groups, int per_group, int extra0, int extra_n, unsigned value,
+                           int* status, int code, cudaStream_t s);
+cudaError_t launch_dp_push_bands(const float* G, int n_out, int n_in, int band, const DpPeers& slot, cudaStream_t s);
+cudaError_t launch_dp_reduce_update(const float* part, long long src_stride, int world, long long count, float inv_mb,
+                                    long long wbase, const DpPeers& W, int self, const DpPeers& flags, int blocks, cudaStream_t s);
+cudaError_t launch_dp_small_push(const float* gb, const double* sums2, const DpPeers& flags, int world, int self, int parity,
+                                 unsigned value, cudaStream_t s);
+cudaError_t launch_dp_finish(const void* arena, int world, int parity, float* gb_out, double* sums2_out, float* bias,
+                             const float* bscale, int H, int* status_flags, cudaStream_t s);
 
 // ---- synthetic inputs (synth.cu) ---------------------------------------------------------------
 cudaError_t launch_synth_fill(float* out, long long n, unsigned long long seed, unsigned stream_id, int dist,

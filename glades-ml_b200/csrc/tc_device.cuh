@@ -38,6 +38,16 @@ struct TcParams
 	int tiles_m, tiles_n;  // the CTAs walk the tiles_m * tiles_n output tiles persistently
 };
 
+// Data-parallel weight gradient: rows [o * band_rows, (o + 1) * band_rows) of C belong to rank o and
+// are stored straight into that rank's memory (maps[o] / bases[o] describe the band as a
+// [band_rows][N] matrix there) instead of into C.
+struct TcPeer
+{
+	const CUtensorMap* maps;  // device array, one map per owner
+	float* const* bases;      // device array, one base pointer per owner
+	int band_rows;
+};
+
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)

@@ -18,6 +18,10 @@ bool tc_gemm_supported(const GemmArgs& g);
 // err_flag: device int, set non-zero if a bounded wait inside the kernel ran out.
 cudaError_t launch_gemm_tc(const GemmArgs& g, const float* A_lo, const float* B_lo, int* err_flag, cudaStream_t s);
 
+// Tensor map (128 bytes, 64-byte aligned storage) over a row-major [rows][cols] fp32 matrix with 32 x 32
+// boxes, as the epilogue's bulk stores use it; for the per-owner bands of a data-parallel gradient.
+bool tc_make_store_map(void* out128, const float* base, long long rows, long long cols, long long ld);
+
 // lo[i] = tf32_round(src[i] - trunc_tf32(src[i])); with rowscale: first dst_scaled[i] = src[i] *
 // rowscale[i / ld] is formed (and stored), and lo is taken from that.
 cudaError_t launch_split_lo(const float* src, float* lo, long long count, cudaStream_t s);

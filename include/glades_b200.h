@@ -221,9 +221,17 @@ void gl_stop(gl_net* net);
 void gl_shard_range(int64_t rows, int32_t rank, int32_t world, int64_t* first, int64_t* count);
 /* Fills 128 bytes with an NCCL unique id (rank 0 calls it and hands the bytes to the others). */
 int gl_dp_unique_id(void* id128);
-/* Joins this handle to a data-parallel group; gradients, bias sums and metric sums of every
- * gl_train_window call are then all-reduced (sum) over the group before the update. */
+/* Joins this handle to a data-parallel group (collective: every rank calls it); gradients, bias
+ * sums and metric sums of every gl_train_window call are then summed over the group before the
+ * update.  With up to 8 ranks on GPUs that can map each other's memory the exchange runs over peer
+ * memory: the weight-gradient products store their row bands into the owning rank, which sums the
+ * sources in rank order, updates its band and writes the new weights into every replica.  Else
+ * (or with GLADES_DP_PUSH=0) it is one NCCL all-reduce per layer.  gl_destroy of such a handle is
+ * collective too.  The reference has no counterpart: its training loop is single-process
+ * (network.cpp:258-378). */
 int gl_dp_init(gl_net* net, int32_t rank, int32_t world, const void* id128);
+/* 0: not data parallel, 1: NCCL all-reduce per layer, 2: exchange over peer memory. */
+int gl_dp_mode(const gl_net* net);
 /* Position of this rank's shard inside the global window (used for the momentum weights) and
  * the global window length. */
 int gl_dp_set_window(gl_net* net, int32_t global_rows, int32_t first_global_pos);

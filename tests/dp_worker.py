@@ -3,8 +3,11 @@
 mode `cpu`:  each rank computes the batched-mode gradient of ITS shard of one global window with the
              CPU restatement, the contributions are summed with a gloo all-reduce, every rank
              applies the same update; rank 0 checks the result against a one-rank run.
-mode `gpu`:  the same through the library on one GPU per rank (its own NCCL all-reduce), checked
-             against a one-GPU run of the whole window on rank 0.
+mode `gpu`:  the same through the library on one GPU per rank (its own exchange: over peer memory,
+             or NCCL with GLADES_DP_PUSH=0), checked against a one-GPU run of the whole window on
+             rank 0.  Small layers: the products run on the FFMA kernel.
+mode `gpu_tc`: as `gpu` with layers wide enough for the tensor-core kernel, whose weight-gradient
+             epilogue stores its row bands straight into the owning rank's memory.
 Exit code 0 = parity holds on every rank.
 """
 import os
@@ -27,12 +30,15 @@ def main():
     g = ge.import_package()
     o = ge.import_oracle()
     rng = np.random.default_rng(123)  # same data on every rank
-    sizes = [128, 256, 128] if mode == "gpu" else [12, 20, 9, 4]
-    acts = ["relu", "softmax"] if mode == "gpu" else ["tanh", "relu", "sigmoid"]
-    rows = 512 if mode == "gpu" else 37   # 37 does not divide by 2: uneven shards
+    on_gpu = mode.startswith("gpu")
+    sizes = {"gpu": [128, 256, 128], "gpu_tc": [256, 512, 384, 256], "cpu": [12, 20, 9, 4]}[mode]
+    acts = {"gpu": ["relu", "softmax"], "gpu_tc": ["relu", "tanh", "softmax"], "cpu": ["tanh", "relu", "sigmoid"]}[mode]
+    rows = {"gpu": 512, "gpu_tc": 1024, "cpu": 37}[mode]   # 37 does not divide by 2: uneven shards
+    steps = 2 if mode != "gpu_tc" else 4
     momentum = 0.6
-    d = g.make_desc(sizes, acts, "classification", batch=rows, lr=0.05, momentum=momentum, mode=g.MODE_BATCHED,
-                    device=int(os.environ.get("LOCAL_RANK", "0")) if mode == "gpu" else 0)
+    gemm = g.GEMM_TCGEN05 if mode == "gpu_tc" else g.GEMM_AUTO
+    d = g.make_desc(sizes, acts, "classification", batch=rows, lr=0.05, momentum=momentum, mode=g.MODE_BATCHED, gemm=gemm,
+                    device=int(os.environ.get("LOCAL_RANK", "0")) if on_gpu else 0)
     x = rng.standard_normal((rows, sizes[0])).astype(np.float32)
     if acts[-1] == "softmax":
         y = np.zeros((rows, sizes[-1]), np.float32)
@@ -76,18 +82,23 @@ def main():
         net.set_data(x[first:first + count], y[first:first + count])
         net.dp_init(rank, world, lst[0])
         net.dp_set_window(rows, first)
-        for step in range(2):
+        want = os.environ.get("GLADES_DP_PUSH")
+        if want is not None and net.dp_mode() != (2 if want == "1" else 1):
+            print("dp mode %d does not match GLADES_DP_PUSH=%s" % (net.dp_mode(), want))
+            ok = False
+        for step in range(steps):
             m = net.train_window(0, count)
         wg, bg = net.get_weights()
         tw = torch.from_numpy(wg.copy())
         td.broadcast(tw, 0)
-        ok = np.array_equal(tw.numpy().view(np.uint32), wg.view(np.uint32))  # replicas identical
+        ok = ok and np.array_equal(tw.numpy().view(np.uint32), wg.view(np.uint32))  # replicas identical
         if rank == 0:
-            d1 = g.make_desc(sizes, acts, "classification", batch=rows, lr=0.05, momentum=momentum, mode=g.MODE_BATCHED)
+            d1 = g.make_desc(sizes, acts, "classification", batch=rows, lr=0.05, momentum=momentum, mode=g.MODE_BATCHED,
+                             gemm=gemm)
             one = g.Net(d1)
             one.set_weights(w, b)
             one.set_data(x, y)
-            for step in range(2):
+            for step in range(steps):
                 m1 = one.train_window(0, rows)
             w1, b1 = one.get_weights()
             err = float(np.max(np.abs(wg - w1)) / np.max(np.abs(w1)))

@@ -1,5 +1,6 @@
 """Data-parallel path: world_size-2 gloo ranks on CPU (sharding + the one exchange per window),
-and -- where two GPUs are visible -- the library's own NCCL all-reduce on one GPU per rank."""
+and -- where two GPUs are visible -- the library's own exchange on one GPU per rank, both over peer
+memory and through NCCL."""
 import os
 import socket
 import subprocess
@@ -19,10 +20,10 @@ def _free_port():
     return p
 
 
-def _launch(mode, nproc):
+def _launch(mode, nproc, **extra_env):
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(nproc), "--master-addr",
            "127.0.0.1", "--master-port", str(_free_port()), os.path.join(ROOT, "tests", "dp_worker.py"), mode]
-    env = dict(os.environ, OMP_NUM_THREADS="2")
+    env = dict(os.environ, OMP_NUM_THREADS="2", **extra_env)
     return subprocess.run(cmd, capture_output=True, text=True, timeout=900, env=env)
 
 
@@ -43,8 +44,11 @@ def test_two_gloo_ranks_reproduce_one_rank(oracle):
 
 
 @pytest.mark.gpu
-def test_two_gpus_reproduce_one_gpu(g):
+@pytest.mark.parametrize("mode,push", [("gpu", "1"), ("gpu", "0"), ("gpu_tc", "1"), ("gpu_tc", "0")])
+def test_two_gpus_reproduce_one_gpu(g, mode, push):
+    """push=1: the gradient exchange over peer memory (required, no silent NCCL fallback);
+    push=0: one NCCL all-reduce per layer."""
     if g.device_count() < 2:
         pytest.skip("needs two GPUs")
-    r = _launch("gpu", 2)
+    r = _launch(mode, 2, GLADES_DP_PUSH=push)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
