@@ -825,8 +825,46 @@ static int batched_forward(gl_net* n, const float* X, int rows, int64_t* launche
 	return 0;
 }
 
+// GLADES_DP_TRACE=1 (diagnostics): time stamps of one window's phases on both streams, printed per window.
+struct DpTrace
+{
+	bool on = false;
+	std::vector<cudaEvent_t> ev;
+	std::vector<std::string> name;
+	void mark(const char* what, int l, cudaStream_t s)
+	{
+		if (!on) return;
+		cudaEvent_t e;
+		cudaEventCreate(&e);
+		cudaEventRecord(e, s);
+		ev.push_back(e);
+		name.push_back(std::string(what) + (l >= 0 ? std::to_string(l) : std::string()));
+	}
+	void dump(int rank, cudaStream_t a, cudaStream_t b)
+	{
+		if (!on) return;
+		cudaStreamSynchronize(a);
+		if (b) cudaStreamSynchronize(b);
+		for (size_t i = 1; i < ev.size(); ++i)
+		{
+			float ms = 0;
+			cudaEventElapsedTime(&ms, ev[0], ev[i]);
+			fprintf(stderr, "[dp-trace r%d] %-18s %8.3f ms\n", rank, name[i].c_str(), ms);
+		}
+		for (cudaEvent_t e : ev) cudaEventDestroy(e);
+		ev.clear();
+		name.clear();
+	}
+};
+
 static int batched_window(gl_net* n, const float* X, const float* Y, int rows, int64_t metric_rows, gl_metrics* out)
 {
+	DpTrace tr;
+	{
+		static int t = -1;
+		if (t < 0) t = getenv("GLADES_DP_TRACE") ? 1 : 0;
+		tr.on = t == 1 && n->world > 1;
+	}
 	if (int r = ensure_work(n, rows)) return r;
 	const int global_rows = (n->world > 1 && n->globalRows > 0) ? n->globalRows : rows;
 	const int first_pos = (n->world > 1) ? n->firstPos : 0;
@@ -834,6 +872,7 @@ static int batched_window(gl_net* n, const float* X, const float* Y, int rows, i
 	int64_t launches = 0;
 	double* const sums2 = n->winSums ? n->winSums : n->dSums;
 	const bool push = n->world > 1 && n->dpPush;
+	bool lo_all = true;  // peer-memory exchange: every layer's low weight parts were refreshed beside the backward pass
 	const unsigned stepv = push ? ++n->dpStep : 0u;
 	DpPeers peerFlags, peerW;
 	for (int r = 0; r < DP_MAX_WORLD; ++r)
@@ -842,9 +881,11 @@ static int batched_window(gl_net* n, const float* X, const float* Y, int rows, i
 		peerW.p[r] = n->dpPeerW[r];
 	}
 	CU(cudaEventRecord(n->ev0, n->stream));
+	tr.mark("start", -1, n->stream);
 	CU(cudaMemsetAsync(sums2, 0, 2 * sizeof(double), n->stream));
 	CU(cudaMemsetAsync(n->dG + n->nw, 0, GL_MAX_WEIGHT_LAYERS * sizeof(float), n->stream));
 	if (int r = batched_forward(n, X, rows, &launches)) return r;
+	tr.mark("forward done", -1, n->stream);
 
 	HeadArgs h;
 	memset(&h, 0, sizeof h);
@@ -938,10 +979,12 @@ static int batched_window(gl_net* n, const float* X, const float* Y, int rows, i
 			// the communication stream do this rank's own band (sum the sources in rank order, update,
 			// write the new weights into every replica) while the main stream goes on with the layers below
 			CU(launch_dp_signal(peerFlags, n->world, DP_WORD_GFLAG + l * DP_MAX_WORLD + n->rank, stepv, n->stream));
+			tr.mark("grad stored L", l, n->stream);
 			CU(cudaEventRecord(n->evGrad[l], n->stream));
 			CU(cudaStreamWaitEvent(n->commStream, n->evGrad[l], 0));
 			CU(launch_dp_wait(n->dpArena, DP_WORD_GFLAG + l * DP_MAX_WORLD, 1, n->world, 0, 0, stepv, n->dFlags + 1, 20 + l,
 			                  n->commStream));
+			tr.mark("owner has all L", l, n->commStream);
 			const int band = n->dpBand[l];
 			int own_rows = no - n->rank * band;
 			own_rows = own_rows < 0 ? 0 : (own_rows > band ? band : own_rows);
@@ -950,7 +993,21 @@ static int batched_window(gl_net* n, const float* X, const float* Y, int rows, i
 			                           n->woff[l] + (long long)n->rank * band * ni, peerW, n->rank, peerFlags,
 			                           l == 0 ? 148 * 4 : n->dpPushBlocks, n->commStream));
 			CU(launch_dp_signal(peerFlags, n->world, DP_WORD_WFLAG + l * DP_MAX_WORLD + n->rank, stepv, n->commStream));
-			launches += 4;
+			tr.mark("band updated L", l, n->commStream);
+			// once every owner's band of this layer has landed here, split off the low TF32 parts of the
+			// layer's new weights -- still beside the backward pass for all but the last layer
+			CU(launch_dp_wait(n->dpArena, DP_WORD_WFLAG + l * DP_MAX_WORLD, 1, n->world, 0, 0, stepv, n->dFlags + 1, 40 + l,
+			                  n->commStream));
+			const int64_t cnt = n->woff[l + 1] - n->woff[l];
+			if (n->dWlo && cnt % 4 == 0 && n->woff[l] % 4 == 0)
+			{
+				CU(launch_split_lo(n->dW + n->woff[l], n->dWlo + n->woff[l], cnt, n->commStream));
+				++launches;
+			}
+			else
+				lo_all = false;
+			tr.mark("layer complete L", l, n->commStream);
+			launches += 5;
 		}
 		else if (n->world > 1 && n->dpOverlap)
 		{
@@ -997,12 +1054,15 @@ static int batched_window(gl_net* n, const float* X, const float* Y, int rows, i
 		// bias and loss sums of this rank to everyone; then wait until every owner's band of every layer
 		// and every rank's record have landed here, and finish the window locally
 		CU(launch_dp_small_push(n->dG + n->nw, sums2, peerFlags, n->world, n->rank, (int)(stepv & 1u), stepv, n->stream));
-		CU(launch_dp_wait(n->dpArena, DP_WORD_WFLAG, n->H + 1, n->world, DP_WORD_SFLAG, n->world, stepv, n->dFlags + 1, 40,
-		                  n->stream));
+		tr.mark("backward done", -1, n->stream);
+		CU(cudaEventRecord(n->evComm, n->commStream));
+		CU(launch_dp_wait(n->dpArena, 0, 0, 0, DP_WORD_SFLAG, n->world, stepv, n->dFlags + 1, 60, n->stream));
+		CU(cudaStreamWaitEvent(n->stream, n->evComm, 0));  // every layer's new weights have landed (and their low parts)
 		CU(launch_dp_finish(n->dpArena, n->world, (int)(stepv & 1u), n->dG + n->nw, sums2, n->dBias, n->dBscale, n->H, n->dFlags,
 		                    n->stream));
+		tr.mark("window done", -1, n->stream);
 		launches += 3;
-		n->loW = false;  // the low TF32 parts of the new weights are split off before the next product
+		n->loW = lo_all && n->dWlo != nullptr;
 	}
 	else
 	{
@@ -1012,6 +1072,7 @@ static int batched_window(gl_net* n, const float* X, const float* Y, int rows, i
 		n->loW = n->dWlo != nullptr;
 	}
 	CU(cudaEventRecord(n->ev1, n->stream));
+	tr.dump(n->rank, n->stream, n->commStream);
 	n->launches += launches;
 	n->lastWindowLaunches = launches;
 	if (out)

@@ -101,18 +101,34 @@ __global__ void __launch_bounds__(256) dp_reduce_update_kernel(const float* __re
 	int bad = 0;
 	if (((count | wbase | src_stride) & 3) == 0)
 	{
-		for (long long i = i0; i < (count >> 2); i += stride)
+		// two independent 16-byte chains per thread and iteration: the kernel runs on few CTAs beside the
+		// backward products, so its bandwidth comes from loads in flight per thread
+		const long long n4 = count >> 2;
+		for (long long i = i0; i < n4; i += 2 * stride)
 		{
+			const long long j = i + stride;
+			const bool two = j < n4;
 			float4 g = reinterpret_cast<const float4*>(part)[i];
+			float4 g2 = two ? reinterpret_cast<const float4*>(part)[j] : make_float4(0.f, 0.f, 0.f, 0.f);
 			for (int s = 1; s < world; ++s)
 			{
-				const float4 h = reinterpret_cast<const float4*>(part + (long long)s * src_stride)[i];
+				const float4* ps = reinterpret_cast<const float4*>(part + (long long)s * src_stride);
+				const float4 h = ps[i];
+				const float4 h2 = two ? ps[j] : make_float4(0.f, 0.f, 0.f, 0.f);
 				g.x += h.x; g.y += h.y; g.z += h.z; g.w += h.w;
+				g2.x += h2.x; g2.y += h2.y; g2.z += h2.z; g2.w += h2.w;
 			}
 			float4 w = reinterpret_cast<const float4*>(Wown)[i];
 			w.x -= g.x * inv_mb; w.y -= g.y * inv_mb; w.z -= g.z * inv_mb; w.w -= g.w * inv_mb;
 			if (!(isfinite(w.x) && isfinite(w.y) && isfinite(w.z) && isfinite(w.w))) bad = 1;
 			for (int r = 0; r < world; ++r) reinterpret_cast<float4*>(reinterpret_cast<float*>(W.p[r]) + wbase)[i] = w;
+			if (two)
+			{
+				float4 w2 = reinterpret_cast<const float4*>(Wown)[j];
+				w2.x -= g2.x * inv_mb; w2.y -= g2.y * inv_mb; w2.z -= g2.z * inv_mb; w2.w -= g2.w * inv_mb;
+				if (!(isfinite(w2.x) && isfinite(w2.y) && isfinite(w2.z) && isfinite(w2.w))) bad = 1;
+				for (int r = 0; r < world; ++r) reinterpret_cast<float4*>(reinterpret_cast<float*>(W.p[r]) + wbase)[j] = w2;
+			}
 		}
 	}
 	else

@@ -483,11 +483,13 @@ cudaError_t launch_gemm_tc(const GemmArgs& g, const float* A_lo, const float* B_
 	const int a_mn = (g.a_sk == 1) ? 0 : 1;
 	const int b_mn = (g.b_sk == 1) ? 0 : 1;
 	const long long lda = a_mn ? g.a_sk : g.a_sm, ldb = b_mn ? g.b_sk : g.b_sn;
-	const int BN = (g.N % 256 == 0) ? 256 : 128;
+	// 256-wide tiles unless they would leave more than half of the SMs without a tile
+	const bool pair = !g.peer_maps && tc_pair_supported(g);
+	const long long wide_tiles = (long long)(g.M / TC_BM) * (g.N / 256);
+	const int BN = (g.N % 256 == 0 && (pair || wide_tiles >= 74)) ? 256 : 128;
 	// tile variant: 16-deep k-blocks with twice the stages by default; GLADES_TC_BK=32 selects the
 	// 32-deep blocks (kept for comparison runs)
 	const int bk = tc_bk();
-	const bool pair = !g.peer_maps && tc_pair_supported(g);
 	const int box_b = pair ? 128 : BN;  // a CTA of a pair loads half of the 256-wide B tile
 	CUtensorMap mA, mAl, mB, mBl;
 	if (!make_map(&mA, g.A, a_mn, g.M, g.K, lda, TC_BM, bk) || !make_map(&mAl, A_lo, a_mn, g.M, g.K, lda, TC_BM, bk) ||
