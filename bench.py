@@ -283,30 +283,93 @@ def cpu_port_baseline(g, w, sample_rows, threads=None):
     return sample_rows / dt, cores, dt
 
 
+def _ref_worker(job):
+    """One single-threaded run of the reference's own compiled code (oracle/_ref) on `rows` rows."""
+    name, rows, seed = job
+    g = ge.import_package()
+    o = ge.import_oracle()
+    w = WORKLOADS[name]
+    sizes = w["sizes"]
+    rng = np.random.default_rng(seed)
+    x = rng.random((rows, sizes[0]), dtype=np.float32) if w["kind"] == "infer" else \
+        rng.standard_normal((rows, sizes[0])).astype(np.float32)
+    y = np.full((rows, sizes[-1]), 0.01, np.float32)
+    # the reference has no softmax: its native head (per-node sigmoid) stands in, same flop count
+    acts = ["sigmoid" if a == "softmax" else a for a in w["acts"]]
+    d = g.make_desc(sizes, acts, w["out"], batch=min(rows, w["batch"]), lr=w["lr"], momentum=w["momentum"],
+                    params=w.get("params"), mode=g.MODE_REFERENCE)
+    R = o.Reference(d, x, y, g.Metrics)
+    R.set_weights(student_weights(sizes), None)
+    t0 = time.perf_counter()
+    if w["kind"] == "train":
+        R.train_public(1)
+    else:
+        R.test_public()
+    dt = time.perf_counter() - t0
+    R.close()
+    return rows, dt
+
+
+def cpu_reference_baseline(name, rows_per_proc, procs):
+    """The compiled reference on the host cores.  Training is sequential by construction (one process);
+    inference rows are independent, so `procs` single-threaded processes run disjoint rows side by side
+    and their rows/s add up."""
+    import multiprocessing as mp
+    jobs = [(name, rows_per_proc, 11 + i) for i in range(procs)]
+    if procs == 1:
+        res = [_ref_worker(jobs[0])]
+    else:
+        with mp.get_context("spawn").Pool(procs) as pool:
+            res = pool.map(_ref_worker, jobs)
+    return sum(r / dt for r, dt in res), max(dt for _, dt in res)
+
+
+# bounded samples of the compiled reference per workload: rows per process, processes
+REF_SAMPLES = {"batched_inference": (16, "all"), "window_regressor": (768, 1)}
+
+
+def cpu_baseline_for(g, name, w):
+    """(value, cores, kind, sample text) of the CPU figure reported beside a workload: the reference's own
+    compiled code where a bounded sample of it can be timed, else the CPU port."""
+    o = ge.import_oracle()
+    if name in REF_SAMPLES and o.have_reference():
+        rows, procs = REF_SAMPLES[name]
+        procs = min(os.cpu_count() or 1, 8) if procs == "all" else procs
+        v, dt = cpu_reference_baseline(name, rows, procs)
+        head = " (per-node sigmoid head: the reference has no softmax)" if "softmax" in w["acts"] else ""
+        return v, procs, "reference", ("%d rows in each of %d single-threaded process(es) of the compiled reference%s, "
+                                       "%.1f s" % (rows, procs, head, dt))
+    train = w["kind"] == "train"
+    rows = 256 if train else 2048
+    v, cores, dt = cpu_port_baseline(g, w, rows)
+    note = "; the compiled reference needs ~669 s per training row at this shape (forward 2.6 s, backward 666 s)" \
+        if name == "wide_mlp" else ""
+    return v, cores, "port", ("%d rows of one window, CPU restatement of the same batched arithmetic (double "
+                              "accumulation, OpenMP), %.1f s%s" % (rows, dt, note))
+
+
 def run_reference_arm(args, g, w, rank, world):
-    """The CPU arm.  The reference's own compiled code (oracle/_ref) needs ~669 s for ONE training row
-    of this shape (forward 2.6 s, backward 666 s: the output layer copies the whole expected row per
-    edge, network.cpp:605-606), so a bounded sample of it cannot be timed inside a benchmark run; the
-    arm times the CPU port of the same arithmetic instead and says so."""
+    """The CPU arm: the reference's own compiled code (oracle/_ref) on a bounded sample where that is
+    feasible (inference rows, the window regressor's training rows).  For the wide MLP it needs ~669 s
+    for ONE training row (forward 2.6 s, backward 666 s: the output layer copies the whole expected row
+    per edge, network.cpp:605-606), so the arm times the CPU port of the same arithmetic there and says
+    so in `cpu_baseline.kind` / `.sample`."""
     if rank != 0:
         return
-    sample = 64 if w["kind"] == "train" else 512
     vals = []
-    for _ in range(max(1, min(args.steps, 3))):
-        v, cores, dt = cpu_port_baseline(g, w, sample)
+    for _ in range(max(1, min(args.steps, 2))):
+        v, cores, kind, sample = cpu_baseline_for(g, args.workload, w)
         vals.append(v)
     value = float(np.mean(vals))
+    unit = "samples/s" if w["kind"] == "train" else "rows/s"
     line = {
         "impl": "reference", "metric": "train_samples_per_s" if w["kind"] == "train" else "infer_rows_per_s",
-        "value": value, "unit": "samples/s" if w["kind"] == "train" else "rows/s", "n_gpus": world, "steps": len(vals),
-        "warmup": 0, "ms_per_step": 1000.0 * sample / value, "higher_is_better": True, "scaling": "weak",
+        "value": value, "unit": unit, "n_gpus": world, "steps": len(vals),
+        "warmup": 0, "ms_per_step": None, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": args.workload, "sizes": w["sizes"], "sample_rows_per_step": sample},
-        "cpu_baseline": {"value": value, "unit": "samples/s", "cores": cores, "kind": "port",
-                         "sample": "%d rows of one window per step, CPU restatement of the batched arithmetic "
-                                   "(double accumulation, OpenMP); the compiled reference itself needs ~669 s per "
-                                   "training row at this shape and is not timed here" % sample},
-        "e2e": {"value": value, "unit": "samples/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "config": {"workload": args.workload, "sizes": w["sizes"]},
+        "cpu_baseline": {"value": value, "unit": unit, "cores": cores, "kind": kind, "sample": sample},
+        "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
 
@@ -578,10 +641,8 @@ def main():
     if rank == 0:
         cpu = None
         if not args.no_cpu_baseline and world == 1:
-            v, cores, dtc = cpu_port_baseline(g, w, 256 if train else 2048)
-            cpu = {"value": v, "unit": "samples/s" if train else "rows/s", "cores": cores, "kind": "port",
-                   "sample": "%d rows of one window, CPU restatement of the same batched arithmetic (%.1f s)"
-                             % (256 if train else 2048, dtc)}
+            v, cores, kind, sample = cpu_baseline_for(g, args.workload, w)
+            cpu = {"value": v, "unit": "samples/s" if train else "rows/s", "cores": cores, "kind": kind, "sample": sample}
         line = {
             "metric": "train_samples_per_s" if train else "infer_rows_per_s",
             "value": value, "unit": "samples/s" if train else "rows/s", "n_gpus": world, "steps": args.steps,

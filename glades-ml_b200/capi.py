@@ -12,7 +12,7 @@ ACT = {"tanh": 0, "tanhp": 1, "sigmoid": 2, "sigmoidp": 3, "linear": 4, "relu": 
 OUT = {"regression": 0, "classification": 1, "kl": 2}
 MODE_REFERENCE, MODE_BATCHED = 0, 1
 BIAS_MEAN, BIAS_REFERENCE = 0, 1
-GEMM_AUTO, GEMM_FFMA, GEMM_TCGEN05 = 0, 1, 2
+GEMM_AUTO, GEMM_FFMA, GEMM_TCGEN05, GEMM_GRID_FUSED = 0, 1, 2, 3
 
 
 class NetDesc(C.Structure):
@@ -128,6 +128,8 @@ def lib():
         "gl_set_weights": (C.c_int, [vp, vp, vp]),
         "gl_get_weights": (C.c_int, [vp, vp, vp]),
         "gl_weight_count": (i64, [vp]),
+        "gl_save_state": (C.c_int, [vp, C.c_char_p]),
+        "gl_load_state": (C.c_int, [vp, C.c_char_p]),
         "gl_set_data": (C.c_int, [vp, vp, vp, i64]),
         "gl_set_data_device": (C.c_int, [vp, vp, vp, i64]),
         "gl_train_epochs": (C.c_int, [vp, i32, mp]),
@@ -233,6 +235,12 @@ class Net:
         b = np.empty(max(self.H, 1), np.float32)
         _check(lib().gl_get_weights(self.h, _ptr(w), _ptr(b)))
         return w, b[: self.H]
+
+    def save_state(self, path):
+        _check(lib().gl_save_state(self.h, str(path).encode()))
+
+    def load_state(self, path):
+        _check(lib().gl_load_state(self.h, str(path).encode()))
 
     def set_data(self, x, y):
         x, y = _f32(x), _f32(y)

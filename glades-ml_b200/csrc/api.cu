@@ -200,6 +200,13 @@ struct gl_net
 	size_t profUsed = 0;
 	cudaEvent_t tim0 = nullptr, tim1 = nullptr;
 
+	// whole-window cooperative kernel for mid-size networks (grid_fused.cu)
+	float* gfAct = nullptr;
+	float* gfDel = nullptr;
+	double* gfPart = nullptr;
+	int gfRows = 0, gfCtas = 0;
+	int gfOk = -1;  // -1 not decided yet
+
 	int epochs = 0;
 	volatile int stop = 0;
 	int64_t launches = 0;
@@ -255,6 +262,8 @@ static int use_device(const gl_net* n)
 	CU(cudaSetDevice(n->d.device));
 	return 0;
 }
+
+static bool grid_fused_fits(const gl_net* n);
 
 extern "C" int gl_create(const gl_net_desc* d, gl_net** out)
 {
@@ -321,6 +330,14 @@ extern "C" int gl_create(const gl_net_desc* d, gl_net** out)
 		int maxn = 1;
 		for (int l = 0; l <= H + 1; ++l) maxn = d->sizes[l] > maxn ? d->sizes[l] : maxn;
 		CU(cudaMalloc(&n->dColterm, maxn * sizeof(float)));
+	}
+	if (d->gemm < GL_GEMM_AUTO || d->gemm > GL_GEMM_GRID_FUSED || (d->gemm == GL_GEMM_GRID_FUSED && !grid_fused_fits(n)))
+	{
+		const bool range = d->gemm < GL_GEMM_AUTO || d->gemm > GL_GEMM_GRID_FUSED;
+		gl_destroy(n);
+		return fail(GL_ERR_INVALID, range ? "gl_create: bad engine id"
+		                                  : "gl_create: the network does not fit the whole-window cooperative kernel (batched mode, "
+		                                    "<= 7 hidden layers, layers <= 1024 wide, <= 512 Ki weights)");
 	}
 	*out = n;
 	return GL_OK;
@@ -389,6 +406,7 @@ extern "C" int gl_destroy(gl_net* n)
 	cudaFree(n->dLastOut);
 	cudaFree(n->dScratch); cudaFree(n->ownX); cudaFree(n->ownY); cudaFree(n->dColterm);
 	cudaFree(n->dXwin); cudaFree(n->dYwin);
+	cudaFree(n->gfAct); cudaFree(n->gfDel); cudaFree(n->gfPart);
 	for (int i = 0; i < 2; ++i)
 	{
 		cudaFree(n->slot[i].dX); cudaFree(n->slot[i].dY); cudaFree(n->slot[i].dSums);
@@ -481,6 +499,92 @@ extern "C" int gl_get_weights(gl_net* n, float* w, float* bias)
 		CU(cudaMemcpy(b, n->dBias, sizeof b, cudaMemcpyDeviceToHost));
 		for (int l = 1; l <= n->H; ++l) bias[l - 1] = b[l];
 	}
+	return GL_OK;
+}
+
+
+// ---- checkpoint: weights, scalar biases, epoch counter and (reference mode) the pending deltas ----
+namespace {
+struct StateHeader
+{
+	char magic[8];  // "GLB200S1"
+	int32_t n_layers;
+	int32_t sizes[GL_MAX_WEIGHT_LAYERS + 1];
+	int32_t mode;
+	int32_t batch_size;
+	int32_t epochs;
+	int32_t hist_len;   // pending deltas per edge (reference mode), 0 otherwise
+	int64_t nw;
+	int64_t hist_floats;  // floats of pending-delta history that follow the biases
+};
+}  // namespace
+
+extern "C" int gl_save_state(gl_net* n, const char* path)
+{
+	if (!n || !path) return fail(GL_ERR_INVALID, "gl_save_state: bad argument");
+	if (int r = use_device(n)) return r;
+	CU(cudaStreamSynchronize(n->stream));
+	StateHeader h;
+	memset(&h, 0, sizeof h);
+	memcpy(h.magic, "GLB200S1", 8);
+	h.n_layers = n->d.n_layers;
+	for (int l = 0; l <= n->H + 1; ++l) h.sizes[l] = n->d.sizes[l];
+	h.mode = n->d.mode;
+	h.batch_size = n->d.batch_size;
+	h.epochs = n->epochs;
+	h.nw = n->nw;
+	if (n->dHist)
+	{
+		CU(cudaMemcpy(&h.hist_len, n->dHistLen, sizeof(int), cudaMemcpyDeviceToHost));
+		h.hist_floats = n->nw * (int64_t)n->d.batch_size;
+	}
+	std::vector<float> buf((size_t)n->nw + GL_MAX_WEIGHT_LAYERS + (size_t)h.hist_floats);
+	CU(cudaMemcpy(buf.data(), n->dW, (size_t)n->nw * sizeof(float), cudaMemcpyDeviceToHost));
+	CU(cudaMemcpy(buf.data() + n->nw, n->dBias, GL_MAX_WEIGHT_LAYERS * sizeof(float), cudaMemcpyDeviceToHost));
+	if (h.hist_floats)
+		CU(cudaMemcpy(buf.data() + n->nw + GL_MAX_WEIGHT_LAYERS, n->dHist, (size_t)h.hist_floats * sizeof(float),
+		              cudaMemcpyDeviceToHost));
+	FILE* f = fopen(path, "wb");
+	if (!f) return fail(GL_ERR_INVALID, "gl_save_state: cannot open %s for writing", path);
+	const bool ok = fwrite(&h, sizeof h, 1, f) == 1 && fwrite(buf.data(), sizeof(float), buf.size(), f) == buf.size();
+	if (fclose(f) != 0 || !ok) return fail(GL_ERR_INVALID, "gl_save_state: short write to %s", path);
+	return GL_OK;
+}
+
+extern "C" int gl_load_state(gl_net* n, const char* path)
+{
+	if (!n || !path) return fail(GL_ERR_INVALID, "gl_load_state: bad argument");
+	if (int r = use_device(n)) return r;
+	FILE* f = fopen(path, "rb");
+	if (!f) return fail(GL_ERR_INVALID, "gl_load_state: cannot open %s", path);
+	StateHeader h;
+	if (fread(&h, sizeof h, 1, f) != 1 || memcmp(h.magic, "GLB200S1", 8) != 0)
+	{
+		fclose(f);
+		return fail(GL_ERR_INVALID, "gl_load_state: %s is not a state file", path);
+	}
+	bool same = h.n_layers == n->d.n_layers && h.nw == n->nw && h.mode == n->d.mode && h.batch_size == n->d.batch_size;
+	for (int l = 0; same && l <= n->H + 1; ++l) same = h.sizes[l] == n->d.sizes[l];
+	const int64_t want_hist = n->dHist ? n->nw * (int64_t)n->d.batch_size : 0;
+	if (!same || h.hist_floats != want_hist || h.hist_len < 0 || h.hist_len > n->d.batch_size)
+	{
+		fclose(f);
+		return fail(GL_ERR_INVALID, "gl_load_state: %s was written by a network of another shape, mode or minibatch size", path);
+	}
+	std::vector<float> buf((size_t)n->nw + GL_MAX_WEIGHT_LAYERS + (size_t)h.hist_floats);
+	const bool ok = fread(buf.data(), sizeof(float), buf.size(), f) == buf.size();
+	fclose(f);
+	if (!ok) return fail(GL_ERR_INVALID, "gl_load_state: %s is truncated", path);
+	// the stored biases are indexed by layer (entry 0 unused); gl_set_weights takes them from hidden layer 1 on.
+	// It also clears the history and the status words.
+	if (int r = gl_set_weights(n, buf.data(), buf.data() + n->nw + 1)) return r;
+	if (h.hist_floats)
+	{
+		CU(cudaMemcpy(n->dHist, buf.data() + n->nw + GL_MAX_WEIGHT_LAYERS, (size_t)h.hist_floats * sizeof(float),
+		              cudaMemcpyHostToDevice));
+		CU(cudaMemcpy(n->dHistLen, &h.hist_len, sizeof(int), cudaMemcpyHostToDevice));
+	}
+	n->epochs = h.epochs;
 	return GL_OK;
 }
 
@@ -857,6 +961,104 @@ struct DpTrace
 	}
 };
 
+
+// Metrics of a finished window step (when the caller wants them): waits for the stream.
+static int window_result(gl_net* n, gl_metrics* out, const double* sums2, int global_rows, int64_t launches)
+{
+	if (out)
+	{
+		CU(cudaStreamSynchronize(n->stream));
+		float ms = 0;
+		CU(cudaEventElapsedTime(&ms, n->ev0, n->ev1));
+		double sums[2];
+		CU(cudaMemcpy(sums, sums2, sizeof sums, cudaMemcpyDeviceToHost));
+		memset(out, 0, sizeof *out);
+		out->total_error = (float)sums[0];
+		out->total_accuracy = (float)(sums[1] / ((double)global_rows * (double)n->n_out));
+		out->epochs = n->epochs;
+		out->rows = global_rows;
+		out->device_ms = ms;
+		out->kernel_launches = launches;
+		int flags[4];
+		CU(cudaMemcpy(flags, n->dFlags, sizeof flags, cudaMemcpyDeviceToHost));
+		out->nonfinite = flags[0] & 1;
+		if (flags[1])
+			return fail(GL_ERR_TIMEOUT, "a bounded wait on the device ran out (code %d: 1-4 tensor-core pipeline, 20+ gradient exchange)", flags[1]);
+	}
+	return GL_OK;
+}
+
+// ---- whole-window cooperative kernel for mid-size networks ----------------------------------------
+// Fits: batched mode on one GPU, at most 7 hidden layers, layers at most 1024 wide, at most 512 Ki
+// weights (beyond that the per-layer tensor-core products win), shared memory within the SM's limit.
+static bool grid_fused_fits(const gl_net* n)
+{
+	if (n->d.mode != GL_MODE_BATCHED || n->H > 7 || n->nw > (1 << 19)) return false;
+	for (int l = 0; l <= n->H + 1; ++l)
+		if (n->d.sizes[l] > 1024) return false;
+	const NetView v = make_view(n);
+	return grid_fused_smem_bytes(v) <= (size_t)200 * 1024;
+}
+static bool grid_fused_ok(gl_net* n)
+{
+	if (n->world > 1) return false;
+	if (n->gfOk < 0)
+	{
+		const char* e = getenv("GLADES_GRID_FUSED");
+		const bool allowed = n->d.gemm == GL_GEMM_GRID_FUSED || (n->d.gemm == GL_GEMM_AUTO && !(e && atoi(e) == 0));
+		n->gfOk = (allowed && grid_fused_fits(n)) ? 1 : 0;
+	}
+	return n->gfOk == 1;
+}
+
+// Runs `n_epochs` passes over `rows` rows (windows of `mb`) in one cooperative launch; sums of the
+// last epoch land in sums_out[0..1] on the device.
+static int grid_fused_launch(gl_net* n, const float* X, const float* Y, int64_t rows, int mb, int n_epochs, int64_t metric_rows,
+                             double* epoch_sums)
+{
+	const NetView base = make_view(n);
+	const int tot = grid_fused_total_nodes(base);
+	if (n->gfRows < mb)
+	{
+		cudaFree(n->gfAct);
+		cudaFree(n->gfDel);
+		n->gfAct = n->gfDel = nullptr;
+		n->gfRows = 0;
+		CU(cudaMalloc(&n->gfAct, (size_t)mb * tot * sizeof(float)));
+		CU(cudaMalloc(&n->gfDel, (size_t)mb * tot * sizeof(float)));
+		n->gfRows = mb;
+	}
+	if (!n->gfPart)
+	{
+		int sms = 0;
+		CU(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, n->d.device));
+		n->gfCtas = sms;
+		CU(cudaMalloc(&n->gfPart, (size_t)sms * (2 + GL_MAX_WEIGHT_LAYERS) * sizeof(double)));
+	}
+	GridFusedArgs a;
+	memset(&a, 0, sizeof a);
+	a.net = base;
+	a.net.mb = mb;
+	a.X = X;
+	a.Y = Y;
+	a.rows = rows;
+	a.n_epochs = n_epochs;
+	a.bias_rule = n->d.bias_rule;
+	a.data_size = (float)(metric_rows * (int64_t)n->n_out);
+	a.actbuf = n->gfAct;
+	a.delbuf = n->gfDel;
+	a.part = n->gfPart;
+	a.part_ctas = n->gfCtas;
+	a.epoch_sums = epoch_sums;
+	a.confusion = n->dConf;
+	a.last_out = n->dLastOut;
+	a.flags = n->dFlags;
+	cudaError_t e = launch_grid_fused(a, nullptr, n->stream);
+	if (e != cudaSuccess) return fail(GL_ERR_CUDA, "whole-window cooperative kernel: %s", cudaGetErrorString(e));
+	n->loW = false;
+	return GL_OK;
+}
+
 static int batched_window(gl_net* n, const float* X, const float* Y, int rows, int64_t metric_rows, gl_metrics* out)
 {
 	DpTrace tr;
@@ -865,12 +1067,23 @@ static int batched_window(gl_net* n, const float* X, const float* Y, int rows, i
 		if (t < 0) t = getenv("GLADES_DP_TRACE") ? 1 : 0;
 		tr.on = t == 1 && n->world > 1;
 	}
-	if (int r = ensure_work(n, rows)) return r;
 	const int global_rows = (n->world > 1 && n->globalRows > 0) ? n->globalRows : rows;
+	double* const sums2 = n->winSums ? n->winSums : n->dSums;
+	int64_t launches = 0;
+	if (grid_fused_ok(n))
+	{
+		// mid-size network on one GPU: the whole window in one cooperative launch
+		CU(cudaEventRecord(n->ev0, n->stream));
+		if (int r = grid_fused_launch(n, X, Y, rows, rows, 1, metric_rows, sums2)) return r;
+		CU(cudaEventRecord(n->ev1, n->stream));
+		launches = 1;
+		n->launches += launches;
+		n->lastWindowLaunches = launches;
+		return window_result(n, out, sums2, global_rows, launches);
+	}
+	if (int r = ensure_work(n, rows)) return r;
 	const int first_pos = (n->world > 1) ? n->firstPos : 0;
 	if (int r = set_momentum_weights(n, rows, global_rows, first_pos)) return r;
-	int64_t launches = 0;
-	double* const sums2 = n->winSums ? n->winSums : n->dSums;
 	const bool push = n->world > 1 && n->dpPush;
 	bool lo_all = true;  // peer-memory exchange: every layer's low weight parts were refreshed beside the backward pass
 	const unsigned stepv = push ? ++n->dpStep : 0u;
@@ -1075,26 +1288,7 @@ static int batched_window(gl_net* n, const float* X, const float* Y, int rows, i
 	tr.dump(n->rank, n->stream, n->commStream);
 	n->launches += launches;
 	n->lastWindowLaunches = launches;
-	if (out)
-	{
-		CU(cudaStreamSynchronize(n->stream));
-		float ms = 0;
-		CU(cudaEventElapsedTime(&ms, n->ev0, n->ev1));
-		double sums[2];
-		CU(cudaMemcpy(sums, sums2, sizeof sums, cudaMemcpyDeviceToHost));
-		memset(out, 0, sizeof *out);
-		out->total_error = (float)sums[0];
-		out->total_accuracy = (float)(sums[1] / ((double)global_rows * (double)n->n_out));
-		out->epochs = n->epochs;
-		out->rows = global_rows;
-		out->device_ms = ms;
-		out->kernel_launches = launches;
-		int flags[4];
-		CU(cudaMemcpy(flags, n->dFlags, sizeof flags, cudaMemcpyDeviceToHost));
-		out->nonfinite = flags[0] & 1;
-		if (flags[1]) return fail(GL_ERR_TIMEOUT, "a bounded wait on the device ran out (code %d: 1-4 tensor-core pipeline, 20+ gradient exchange)", flags[1]);
-	}
-	return GL_OK;
+	return window_result(n, out, sums2, global_rows, launches);
 }
 
 extern "C" int gl_train_window(gl_net* n, int64_t first_row, int32_t rows, gl_metrics* out)
@@ -1225,7 +1419,7 @@ extern "C" int gl_train_window_host_result(gl_net* n, gl_metrics* out)
 // of the fused kernel (GLADES_SMALL_FUSED=0 keeps the per-layer kernels instead).
 static bool small_fused_ok(const gl_net* n)
 {
-	if (n->world > 1 || n->d.gemm == GL_GEMM_TCGEN05) return false;
+	if (n->world > 1 || n->d.gemm == GL_GEMM_TCGEN05 || n->d.gemm == GL_GEMM_GRID_FUSED) return false;
 	static int enabled = -1;
 	if (enabled < 0)
 	{
@@ -1269,6 +1463,29 @@ static int small_fused_train(gl_net* n, int n_epochs, gl_metrics* out)
 	return finish_metrics(n, out, (float)sums[0], (float)sums[1], n->rows, ms, 1, true);
 }
 
+// All epochs and windows of a mid-size network in one cooperative launch.
+static int grid_fused_train(gl_net* n, int n_epochs, gl_metrics* out)
+{
+	double* dEpoch = nullptr;
+	CU(cudaMalloc(&dEpoch, (size_t)2 * n_epochs * sizeof(double)));
+	CU(cudaMemsetAsync(n->dConf, 0, (size_t)n->n_out * n->n_out * sizeof(int), n->stream));
+	CU(cudaEventRecord(n->ev0, n->stream));
+	int r = grid_fused_launch(n, n->dX, n->dY, n->rows, n->d.batch_size, n_epochs, n->rows, dEpoch);
+	cudaError_t e = cudaSuccess;
+	if (r == GL_OK) e = cudaEventRecord(n->ev1, n->stream);
+	if (r == GL_OK && e == cudaSuccess) e = cudaStreamSynchronize(n->stream);
+	double sums[2] = {0, 0};
+	if (r == GL_OK && e == cudaSuccess) e = cudaMemcpy(sums, dEpoch + 2 * (n_epochs - 1), sizeof sums, cudaMemcpyDeviceToHost);
+	cudaFree(dEpoch);
+	if (r != GL_OK) return r;
+	if (e != cudaSuccess) return fail(GL_ERR_CUDA, "whole-window cooperative kernel: %s", cudaGetErrorString(e));
+	n->launches += 1;
+	n->epochs += n_epochs;
+	float ms = 0;
+	CU(cudaEventElapsedTime(&ms, n->ev0, n->ev1));
+	return finish_metrics(n, out, (float)sums[0], (float)sums[1], n->rows, ms, 1, true);
+}
+
 extern "C" int gl_train_epochs(gl_net* n, int32_t n_epochs, gl_metrics* out)
 {
 	if (!n || n_epochs < 1) return fail(GL_ERR_INVALID, "gl_train_epochs: bad argument");
@@ -1277,6 +1494,7 @@ extern "C" int gl_train_epochs(gl_net* n, int32_t n_epochs, gl_metrics* out)
 	n->stop = 0;
 	if (n->d.mode == GL_MODE_REFERENCE) return ref_train(n, n_epochs, out);
 	if (small_fused_ok(n)) return small_fused_train(n, n_epochs, out);
+	if (grid_fused_ok(n)) return grid_fused_train(n, n_epochs, out);
 	// batched mode: aligned windows of batch_size rows; epoch figures are sums over the windows
 	const int mb = n->d.batch_size;
 	gl_metrics last;

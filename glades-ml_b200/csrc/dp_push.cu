@@ -21,7 +21,7 @@
 namespace glb {
 namespace {
 
-constexpr long long DP_WAIT_CYCLES = 40000000000ll;  // about 20 s: a peer may be busy on the host for a while
+constexpr long long DP_WAIT_CYCLES = 20000000000ll;  // about 10 s: a peer may be busy on the host for a while
 
 __device__ __forceinline__ void st_flag(unsigned* p, unsigned v) { *reinterpret_cast<volatile unsigned*>(p) = v; }
 __device__ __forceinline__ unsigned ld_flag(const unsigned* p) { return *reinterpret_cast<const volatile unsigned*>(p); }
@@ -45,14 +45,17 @@ __global__ void dp_wait_kernel(const unsigned* flags, int w0, int groups, int pe
 	int word = -1;
 	if (t < groups * per_group) word = w0 + (t / per_group) * DP_MAX_WORLD + t % per_group;
 	else if (t < groups * per_group + extra_n) word = extra0 + (t - groups * per_group);
-	if (word >= 0)
+	// once any wait of this handle has run out, no later one spins again: the exchange is broken and the
+	// host reports it at its next status read
+	if (word >= 0 && *reinterpret_cast<volatile int*>(status) == 0)
 	{
 		const long long t0 = clock64();
 		while ((int)(ld_flag(flags + word) - value) < 0)
 		{
+			if (*reinterpret_cast<volatile int*>(status) != 0) break;
 			if (clock64() - t0 > DP_WAIT_CYCLES)
 			{
-				atomicExch(status, code);
+				atomicCAS(status, 0, code);
 				break;
 			}
 			__nanosleep(100);

@@ -129,6 +129,29 @@ struct SmallFusedArgs
 size_t small_fused_smem_bytes(const NetView& n);
 cudaError_t launch_small_fused(const SmallFusedArgs& a, cudaStream_t s);
 
+// ---- batched mode, mid-size network, one cooperative launch over all SMs (grid_fused.cu) ----------
+struct GridFusedArgs
+{
+	NetView net;         // net.mb = rows per window
+	const float* X;
+	const float* Y;
+	long long rows;      // rows this launch walks through, in windows of net.mb, n_epochs times
+	int n_epochs;
+	int bias_rule;
+	float data_size;     // the cost divisor: rows of the epoch * n_out
+	float* actbuf;       // [net.mb][total nodes] scratch: the window's activations
+	float* delbuf;       // [net.mb][total nodes] scratch: the window's deltas
+	double* part;        // [part_ctas][2 + GL_MAX_WEIGHT_LAYERS] per-CTA partial sums of a window
+	int part_ctas;
+	double* epoch_sums;  // [n_epochs][2]: cost sum, accuracy sum
+	int* confusion;      // [n_out][n_out]: the last epoch's counts are ADDED (the caller clears)
+	float* last_out;     // [n_out] or NULL
+	int* flags;
+};
+size_t grid_fused_smem_bytes(const NetView& n);
+int grid_fused_total_nodes(const NetView& n);
+cudaError_t launch_grid_fused(const GridFusedArgs& a, int* grid_out, cudaStream_t s);
+
 // ---- data-parallel gradient exchange over peer memory (dp_push.cu) ---------------------------------
 // Every rank owns an exchange arena that all ranks map: a flag area of DP_FLAG_BYTES (32-bit window
 // counters written by peers, then the small per-rank records) followed by one gradient slot per

@@ -198,6 +198,7 @@ class NNetwork
 	bool haveInit;
 	shmea::GList results;
 	std::vector<int32_t> lastConfusion;
+	std::string pendingState;
 
 	void run(DataInput*, int);
 	bool build(DataInput*);
@@ -228,6 +229,11 @@ public:
 	// without them the first train()/test() draws weights like Layer::initWeights does.
 	void setWeights(const std::vector<float>& w, const std::vector<float>& bias);
 	bool getWeights(std::vector<float>& w, std::vector<float>& bias) const;
+	// Checkpoint and true resume (weights, scalar biases, epoch counter, open-window pending deltas):
+	// NNetwork::save()/load() of the reference persist only the skeleton (network.cpp:701-722).
+	// loadState before the first train()/test() is applied when the device network is built.
+	bool saveState(const std::string& path) const;
+	bool loadState(const std::string& path);
 	float getError() const { return overallTotalError; }
 	float getClassAccuracy() const { return overallClassAccuracy; }
 	float getClassF1() const { return overallClassF1; }

@@ -298,6 +298,30 @@ bool NNetwork::getWeights(std::vector<float>& w, std::vector<float>& bias) const
 	return gl_get_weights(handle, &w[0], bias.empty() ? NULL : &bias[0]) == GL_OK;
 }
 
+bool NNetwork::saveState(const std::string& path) const
+{
+	if (!handle) return false;
+	if (gl_save_state(handle, path.c_str()) == GL_OK) return true;
+	fprintf(stderr, "[NN] %s\n", gl_last_error());
+	return false;
+}
+
+bool NNetwork::loadState(const std::string& path)
+{
+	if (!handle)
+	{
+		pendingState = path;  // applied by build()
+		return true;
+	}
+	if (gl_load_state(handle, path.c_str()) != GL_OK)
+	{
+		fprintf(stderr, "[NN] %s\n", gl_last_error());
+		return false;
+	}
+	epochs = gl_get_epochs(handle);
+	return true;
+}
+
 // What meat.build() did on the first run (network.cpp:127-128): pack the rows and create the
 // device network.  Every failure is the reference's silent return, plus one line on stderr.
 bool NNetwork::build(DataInput* d)
@@ -338,6 +362,17 @@ bool NNetwork::build(DataInput* d)
 		gl_destroy(handle);
 		handle = NULL;
 		return false;
+	}
+	if (!pendingState.empty())
+	{
+		const std::string path = pendingState;
+		pendingState.clear();
+		if (!loadState(path))
+		{
+			gl_destroy(handle);
+			handle = NULL;
+			return false;
+		}
 	}
 	return true;
 }

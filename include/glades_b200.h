@@ -51,10 +51,14 @@ enum { GL_MODE_REFERENCE = 0, GL_MODE_BATCHED = 1 };
  * per sample, network.cpp:585-587,653-656). */
 enum { GL_BIAS_MEAN = 0, GL_BIAS_REFERENCE = 1 };
 
-/* Matrix-product engine for batched mode: GL_GEMM_AUTO picks by shape; GL_GEMM_FFMA forces the
- * exact-fp32 FFMA tile kernel; GL_GEMM_TCGEN05 uses the TMA + tcgen05 3xTF32 kernel for every
- * product whose shape fits its tiles, however small (AUTO leaves small products on FFMA). */
-enum { GL_GEMM_AUTO = 0, GL_GEMM_FFMA = 1, GL_GEMM_TCGEN05 = 2 };
+/* Engine of batched mode.  GL_GEMM_AUTO picks by size: whole-network fused kernels for small and
+ * mid-size networks on one GPU (all weights in one SM's shared memory; or one cooperative launch
+ * over all SMs per window), else one matrix product per layer and pass, on the tensor cores where
+ * the shape fits and is large enough.  GL_GEMM_FFMA forces the per-layer products on the exact-fp32
+ * FFMA tile kernel; GL_GEMM_TCGEN05 forces them on the TMA + tcgen05 3xTF32 kernel wherever the
+ * shape fits its tiles, however small; GL_GEMM_GRID_FUSED forces the cooperative whole-window kernel
+ * (gl_create fails if the network does not fit it). */
+enum { GL_GEMM_AUTO = 0, GL_GEMM_FFMA = 1, GL_GEMM_TCGEN05 = 2, GL_GEMM_GRID_FUSED = 3 };
 
 typedef enum gl_status {
 	GL_OK = 0,
@@ -129,6 +133,15 @@ int gl_set_weights(gl_net* net, const float* w_flat, const float* bias);
 int gl_get_weights(gl_net* net, float* w_flat, float* bias);
 /* Total number of weights, sum of n_{l+1}*n_l. */
 int64_t gl_weight_count(const gl_net* net);
+
+/* Checkpoint and true resume: writes / reads one binary file holding the shapes, the flat weights,
+ * the scalar biases, the epoch counter and -- reference mode -- every edge's pending deltas of the
+ * open minibatch window, so that a loaded network continues exactly where the saved one stood.
+ * gl_load_state refuses a file written by a network of another shape, mode or minibatch size.
+ * The reference saves only the NNInfo skeleton; its weight persistence is commented out
+ * (Networks/network.cpp:701-722, State/LayerBuilder.cpp:659-709). */
+int gl_save_state(gl_net* net, const char* path);
+int gl_load_state(gl_net* net, const char* path);
 
 /* Replaces LayerBuilder::buildInputLayers (State/LayerBuilder.cpp:101-189) and the
  * DataInput::getTrainRow / getTrainExpectedRow reads of the loop (network.cpp:523,605): the rows

@@ -236,13 +236,24 @@ BATCHED_CASES = [
 ]
 
 
-@pytest.mark.parametrize("case", BATCHED_CASES, ids=lambda c: "-".join(map(str, c[0])) + "_" + str(c[3]))
-def test_batched_window_vs_restatement(g, oracle, case):
+GRID_FUSED_EXTRA = [
+    # the window regressor's shape, and layers wider than one pass of the kernel's 256 threads
+    ([32, 256, 256, 1], ["relu", "relu", "linear"], "regression", 1024, 0.9, 0.0, 0.0, 0),
+    ([40, 300, 520, 12], ["tanh", "relu", "softmax"], "classification", 203, 0.5, 0.0005, 0.0, 0),
+]
+
+
+@pytest.mark.parametrize("engine", ["ffma", "grid_fused"])
+@pytest.mark.parametrize("case", BATCHED_CASES + GRID_FUSED_EXTRA, ids=lambda c: "-".join(map(str, c[0])) + "_" + str(c[3]))
+def test_batched_window_vs_restatement(g, oracle, case, engine):
+    """One minibatch window, per-layer products on the FFMA kernel vs the whole window in one
+    cooperative launch (grid_fused): both against the CPU restatement of the batched arithmetic."""
     sizes, acts, out, rows, mom, wd1, wd2, brule = case
     rng = np.random.default_rng(sum(sizes) + rows)
     params = [0.05 if a == "leaky" else 1.0 for a in acts]
-    d = g.make_desc(sizes, acts, out, batch=rows, lr=0.05, momentum=mom, wd1=wd1, wd2=wd2, params=params,
-                    mode=g.MODE_BATCHED, bias_rule=brule, gemm=g.GEMM_FFMA)
+    d = g.make_desc(sizes, acts, out, batch=rows, lr=0.05 if rows < 1000 else 0.002, momentum=mom, wd1=wd1, wd2=wd2,
+                    params=params, mode=g.MODE_BATCHED, bias_rule=brule,
+                    gemm=g.GEMM_FFMA if engine == "ffma" else g.GEMM_GRID_FUSED)
     x = rng.standard_normal((rows, sizes[0])).astype(np.float32)
     if acts[-1] == "softmax":
         y = np.zeros((rows, sizes[-1]), np.float32)
@@ -256,7 +267,10 @@ def test_batched_window_vs_restatement(g, oracle, case):
     S = oracle.Restate(d, x, y, g.Metrics)
     S.set_weights(w, b)
     for step in range(2):  # two steps: the second one starts from updated weights
+        l0 = net.kernel_launches()
         m = net.train_window(0, rows)
+        if engine == "grid_fused":
+            assert net.kernel_launches() - l0 == 1, "the whole window must be one cooperative launch"
         cm = np.zeros((sizes[-1], sizes[-1]), np.int32)
         gr = S.window_grad(0, rows, confusion=cm)
         S.window_apply(gr, rows)
@@ -467,6 +481,75 @@ def test_small_network_fused_epochs_vs_restatement(g, oracle, case):
         assert diff <= (2 if epochs * rows > 200 else 0), "confusion counts differ by %d" % diff
     assert net.epochs() == epochs
     net.close()
+
+
+GRID_FUSED_EPOCH_CASES = [
+    # sizes, acts, out, rows, mb, momentum, bias_rule, epochs
+    ([32, 256, 256, 1], ["relu", "relu", "linear"], "regression", 2500, 1024, 0.9, 0, 2),   # ragged last window
+    ([20, 64, 48, 5], ["tanh", "relu", "softmax"], "classification", 333, 50, 0.6, 0, 3),
+    ([12, 40, 3], ["sigmoid", "sigmoid"], "classification", 90, 7, 0.0, 0, 2),          # windows shorter than a row group
+]
+
+
+@pytest.mark.parametrize("case", GRID_FUSED_EPOCH_CASES, ids=lambda c: "-".join(map(str, c[0])) + "_mb%d" % c[4])
+def test_grid_fused_epochs_vs_restatement(g, oracle, case):
+    """Whole training runs (epochs x windows, ragged tail included) of a mid-size network in ONE
+    cooperative launch, checked against the restatement walked window by window."""
+    sizes, acts, out, rows, mb, mom, brule, epochs = case
+    rng = np.random.default_rng(len(sizes) * 100 + rows)
+    d = g.make_desc(sizes, acts, out, batch=mb, lr=0.002 if mb > 500 else 0.05, momentum=mom, mode=g.MODE_BATCHED,
+                    bias_rule=brule, gemm=g.GEMM_GRID_FUSED)
+    x = rng.standard_normal((rows, sizes[0])).astype(np.float32)
+    if acts[-1] == "softmax":
+        y = np.zeros((rows, sizes[-1]), np.float32)
+        y[np.arange(rows), rng.integers(0, sizes[-1], rows)] = 1.0
+    elif out == "classification":
+        y = np.full((rows, sizes[-1]), 0.01, np.float32)
+        y[np.arange(rows), rng.integers(0, sizes[-1], rows)] = 0.99
+    else:
+        y = rng.uniform(0.05, 0.95, (rows, sizes[-1])).astype(np.float32)
+    w, b = _rand_net(rng, sizes, -0.15, 0.15)
+    net = g.Net(d)
+    net.set_weights(w, b)
+    net.set_data(x, y)
+    S = oracle.Restate(d, x, y, g.Metrics)
+    S.set_weights(w, b)
+    l0 = net.kernel_launches()
+    m = net.train_epochs(epochs)
+    assert net.kernel_launches() - l0 == 1
+    for ep in range(epochs):
+        cm = np.zeros((sizes[-1], sizes[-1]), np.int32)
+        cost = acc = 0.0
+        for r0 in range(0, rows, mb):
+            cnt = min(mb, rows - r0)
+            gr = S.window_grad(r0, cnt, confusion=cm)
+            S.window_apply(gr, cnt)
+            cost += gr[-2]
+            acc += gr[-1]
+    wg, bg = net.get_weights()
+    ws, bs = S.get_weights()
+    assert np.isfinite(ws).all(), "the case itself must stay finite"
+    ok, err = tensor_close(wg, ws, 2e-5)
+    assert ok, err
+    assert np.allclose(bg, bs, rtol=2e-4, atol=2e-6), (bg, bs)
+    assert abs(m.total_error - cost) <= 2e-5 * max(1.0, abs(cost))
+    assert abs(m.total_accuracy - acc / (rows * sizes[-1])) <= 2e-3
+    if out != "regression":
+        diff = int(np.abs(net.confusion() - cm).sum())
+        assert diff <= 2, "confusion counts differ by %d" % diff
+    assert net.epochs() == epochs and not m.nonfinite
+    # the last row's predictions, as the reference's getResults() hands them out
+    assert np.all(np.isfinite(net.last_outputs()))
+    net.close()
+
+
+def test_grid_fused_engine_is_refused_where_it_does_not_fit(g):
+    with pytest.raises(RuntimeError):
+        g.Net(g.make_desc([1024, 4096, 1024], ["relu", "sigmoid"], "regression", batch=64, lr=0.1, mode=g.MODE_BATCHED,
+                          gemm=g.GEMM_GRID_FUSED))
+    with pytest.raises(RuntimeError):
+        g.Net(g.make_desc([4, 8, 2], ["tanh", "sigmoid"], "regression", batch=4, lr=0.1, mode=g.MODE_REFERENCE,
+                          gemm=g.GEMM_GRID_FUSED))
 
 
 def test_pipelined_host_windows_equal_synchronous_ones(g):
