@@ -45,7 +45,7 @@ WORKLOADS = {
     "wide_mlp": dict(sizes=[1024, 4096, 4096, 1024], acts=["relu", "relu", "softmax"], batch=8192, lr=1e-2, momentum=0.0,
                      out="classification", kind="train"),
     "window_regressor": dict(sizes=[32, 256, 256, 1], acts=["relu", "relu", "linear"], batch=1024, lr=1e-3, momentum=0.9,
-                             out="regression", kind="train", params=[0.0, 0.0, 1.0]),
+                             out="regression", kind="train", params=[0.0, 0.0, 1.0], resident_rows=1 << 21),
     "batched_inference": dict(sizes=[784, 2048, 2048, 10], acts=["relu", "relu", "softmax"], batch=65536, lr=0.0,
                               momentum=0.0, out="classification", kind="infer"),
 }
@@ -406,7 +406,9 @@ def run_small(args, g, name):
     """The two small configs (sequential by construction, one GPU): whole training runs in one launch.
     One step = `epochs` epochs over the data set; value = samples/s; the CPU figure beside it is the
     reference's own compiled code (oracle/_ref) when it is present, else the CPU port."""
-    w = SMALL[name]
+    w = dict(SMALL[name])
+    if args.epochs > 0:
+        w["epochs"] = args.epochs
     x, y, w0 = small_data(name, w)
     peaks = measured_peaks()
     o = ge.import_oracle()
@@ -480,6 +482,7 @@ def main():
     ap.add_argument("--windows", type=int, default=0, help="resident windows per GPU (default: steps+warmup, max 64)")
     ap.add_argument("--gemm", default="auto", choices=["auto", "ffma", "tcgen05"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--epochs", type=int, default=0, help="small workloads: epochs per step (default: the config's)")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
@@ -508,6 +511,10 @@ def main():
         raise SystemExit("global batch %d does not split over %d GPUs" % (gb, world))
     lb = gb // world if train else gb  # training splits the window; inference shards whole batches
     nwin = args.windows or min(64, args.steps + args.warmup)
+    if not args.windows and train and nwin * lb * (sizes[0] + sizes[-1]) * 4 < 2 * 126e6 and "resident_rows" in w:
+        # small rows: keep the config's whole data set resident so that the windows the steps touch are
+        # larger than L2 together and each step reads rows no earlier step has touched
+        nwin = max(nwin, w["resident_rows"] // gb)
     rows = nwin * lb
     gemm = {"auto": g.GEMM_AUTO, "ffma": g.GEMM_FFMA, "tcgen05": g.GEMM_TCGEN05}[args.gemm]
 
@@ -620,22 +627,40 @@ def main():
     peaks = measured_peaks()
     tc = prof["tc"]
     ff = prof["ffma"]
-    dom = tc if tc["ms"] >= ff["ms"] else ff
-    dom_name = "gemm_tc_kernel (TMA + tcgen05 kind::tf32, 3xTF32)" if dom is tc else "gemm_ffma_kernel (fp32 FFMA)"
-    achieved = dom["flop"] / (dom["ms"] / 1000.0) / 1e12 if dom["ms"] > 0 else 0.0
-    roofline = {
-        "bound": "tensor", "kernel": dom_name, "achieved": achieved, "peak": peaks["tensor"], "unit": "TFLOP/s",
-        "frac": achieved / peaks["tensor"],
-        # DRAM bytes per launch of this kernel from one ncu capture of this very workload
-        # (profiles/gemm_tc_kernel_wide_mlp.md: 5.81 GB over the 8 products of a step); null elsewhere
-        "traffic": 0.726e9 if (dom is tc and args.workload == "wide_mlp" and world == 1) else None, "peak_source": peaks["source"] + " dense bf16 (sustained)",
-        "launches": dom["launches"], "avg_launch_ms": dom["ms"] / max(1, dom["launches"]),
-        "algorithmic_flop_per_launch": dom["flop"] / max(1, dom["launches"]),
-        "note": "achieved counts algorithmic fp32 flop (2*M*N*K per product); the 3xTF32 mode issues 3 TF32 MMAs per "
-                "product term, so the tensor pipe runs at 3x this figure and the mode's own ceiling is peak/6",
-        "frac_of_3xtf32_ceiling": achieved / (peaks["tensor"] / 6.0),
-        "share_of_step_ms": dom["ms"] / ms if ms > 0 else None,
-    }
+    if tc["ms"] == 0 and ff["ms"] == 0:
+        # no per-layer product ran: the whole step is one fused kernel (whole-window cooperative kernel)
+        bytes_per_sample = 4 * (sizes[0] + sizes[-1])
+        gbs = value * bytes_per_sample / 1e9
+        roofline = {
+            "bound": "hbm", "kernel": "grid_fused_kernel (whole window in one cooperative launch, fp32 FFMA)",
+            "achieved": gbs, "peak": peaks["hbm"], "unit": "GB/s", "frac": gbs / peaks["hbm"], "traffic": None,
+            "peak_source": peaks["source"] + " copy bandwidth",
+            "launches": int(launches), "avg_launch_ms": ms / max(1, int(launches)),
+            "algorithmic_bytes_per_launch": bytes_per_sample * samples_per_step,
+            "fp32_tflops": flop_per_sample(sizes, train) * value / 1e12,
+            "note": "algorithmic bytes = input row + target row per sample; the step is far from the HBM bound (arithmetic "
+                    "intensity %d flop/B): it is bound by fp32 FFMA issue and shared-memory latency on %d-row windows, see "
+                    "fp32_tflops" % (flop_per_sample(sizes, train) // bytes_per_sample, lb),
+        }
+        dom = None
+    else:
+        dom = tc if tc["ms"] >= ff["ms"] else ff
+        dom_name = "gemm_tc_kernel (TMA + tcgen05 kind::tf32, 3xTF32)" if dom is tc else "gemm_ffma_kernel (fp32 FFMA)"
+        achieved = dom["flop"] / (dom["ms"] / 1000.0) / 1e12 if dom["ms"] > 0 else 0.0
+        roofline = {
+            "bound": "tensor", "kernel": dom_name, "achieved": achieved, "peak": peaks["tensor"], "unit": "TFLOP/s",
+            "frac": achieved / peaks["tensor"],
+            # DRAM bytes per launch of this kernel from one ncu capture of this very workload
+            # (profiles/gemm_tc_kernel_wide_mlp.md: 5.81 GB over the 8 products of a step); null elsewhere
+            "traffic": 0.726e9 if (dom is tc and args.workload == "wide_mlp" and world == 1) else None,
+            "peak_source": peaks["source"] + " dense bf16 (sustained)",
+            "launches": dom["launches"], "avg_launch_ms": dom["ms"] / max(1, dom["launches"]),
+            "algorithmic_flop_per_launch": dom["flop"] / max(1, dom["launches"]),
+            "note": "achieved counts algorithmic fp32 flop (2*M*N*K per product); the 3xTF32 mode issues 3 TF32 MMAs per "
+                    "product term, so the tensor pipe runs at 3x this figure and the mode's own ceiling is peak/6",
+            "frac_of_3xtf32_ceiling": achieved / (peaks["tensor"] / 6.0),
+            "share_of_step_ms": dom["ms"] / ms if ms > 0 else None,
+        }
 
     line = None
     if rank == 0:
@@ -647,13 +672,17 @@ def main():
             "metric": "train_samples_per_s" if train else "infer_rows_per_s",
             "value": value, "unit": "samples/s" if train else "rows/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong" if train else "weak",
-            "vs_baseline": None, "dtype": "f32 (3xTF32 tensor-core products, fp32 accumulate)" if dom is tc else "f32",
+            "vs_baseline": None, "dtype": "f32 (3xTF32 tensor-core products, fp32 accumulate)" if (dom is not None and dom is tc) else "f32",
             "data": "synthetic",
             "config": {"workload": args.workload, "sizes": sizes, "global_batch": gb, "per_gpu_rows": lb,
                        "mode": "batched", "head": w["acts"][-1], "lr": w["lr"], "resident_windows_per_gpu": nwin,
-                       "l2": "inputs larger than L2: every step streams a distinct %.0f MB window plus %.0f MB of "
-                             "weights and ~1 GB of activations" % (lb * (sizes[0] + sizes[-1]) * 4 / 1e6,
-                                                                    net.nw * 4 / 1e6),
+                       "l2": ("inputs larger than L2: every step streams a distinct %.0f MB window plus %.0f MB of weights and "
+                              "%.0f MB of activations and deltas" % (lb * (sizes[0] + sizes[-1]) * 4 / 1e6, net.nw * 4 / 1e6,
+                                                                       2 * lb * sum(sizes) * 4 / 1e6))
+                             if lb * sum(sizes) * 8 + net.nw * 4 > 126e6 else
+                             "inputs larger than L2: %d resident windows (%.0f MB) and every step reads a window no earlier step "
+                             "has touched; the weights and the window's scratch (%.1f MB) stay in L2 by design"
+                             % (nwin, nwin * lb * (sizes[0] + sizes[-1]) * 4 / 1e6, (2 * lb * sum(sizes) + net.nw) * 4 / 1e6),
                        "parallelism": "dp%d" % world,
                        "gradient_exchange": {0: None, 1: "NCCL all-reduce per layer, overlapped with the backward pass",
                                              2: "row bands stored into their owner's memory by the gradient product's "

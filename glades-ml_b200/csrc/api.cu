@@ -204,7 +204,9 @@ struct gl_net
 	float* gfAct = nullptr;
 	float* gfDel = nullptr;
 	double* gfPart = nullptr;
-	int gfRows = 0, gfCtas = 0;
+	float* gfCk = nullptr;   // momentum table for windows of gfCkMb rows
+	unsigned long long* gfTiming = nullptr;  // GLADES_GF_TIMING=1: phase nanoseconds, printed when the handle goes
+	int gfRows = 0, gfCtas = 0, gfCkMb = 0, gfNc = 2;
 	int gfOk = -1;  // -1 not decided yet
 
 	int epochs = 0;
@@ -406,7 +408,15 @@ extern "C" int gl_destroy(gl_net* n)
 	cudaFree(n->dLastOut);
 	cudaFree(n->dScratch); cudaFree(n->ownX); cudaFree(n->ownY); cudaFree(n->dColterm);
 	cudaFree(n->dXwin); cudaFree(n->dYwin);
-	cudaFree(n->gfAct); cudaFree(n->gfDel); cudaFree(n->gfPart);
+	if (n->gfTiming)
+	{
+		unsigned long long tm[4] = {0, 0, 0, 0};
+		if (cudaMemcpy(tm, n->gfTiming, sizeof tm, cudaMemcpyDeviceToHost) == cudaSuccess)
+			fprintf(stderr, "[grid-fused] CTA 0: phase 1 %.3f ms, barrier %.3f ms, phase 2 %.3f ms, barrier %.3f ms\n", tm[0] * 1e-6,
+			        tm[1] * 1e-6, tm[2] * 1e-6, tm[3] * 1e-6);
+		cudaFree(n->gfTiming);
+	}
+	cudaFree(n->gfAct); cudaFree(n->gfDel); cudaFree(n->gfPart); cudaFree(n->gfCk);
 	for (int i = 0; i < 2; ++i)
 	{
 		cudaFree(n->slot[i].dX); cudaFree(n->slot[i].dY); cudaFree(n->slot[i].dSums);
@@ -1034,6 +1044,30 @@ static int grid_fused_launch(gl_net* n, const float* X, const float* Y, int64_t 
 		CU(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, n->d.device));
 		n->gfCtas = sms;
 		CU(cudaMalloc(&n->gfPart, (size_t)sms * (2 + GL_MAX_WEIGHT_LAYERS) * sizeof(double)));
+		n->gfNc = grid_fused_pick_nc(base, sms);
+	}
+	if (n->gfCkMb != mb)
+	{
+		// ck[l][k] = sum_{q<k} m_l^q, summed like the per-sample momentum history builds it up
+		std::vector<float> ck((size_t)(n->H + 1) * (mb + 1));
+		for (int l = 0; l <= n->H; ++l)
+		{
+			const double m = (double)n->d.momentum[l];
+			double sum = 0.0, pw = 1.0;
+			for (int k = 0; k <= mb; ++k)
+			{
+				ck[(size_t)l * (mb + 1) + k] = (m == 0.0) ? (k > 0 ? 1.0f : 0.0f) : (float)sum;
+				sum += pw;
+				pw *= m;
+			}
+		}
+		cudaFree(n->gfCk);
+		n->gfCk = nullptr;
+		n->gfCkMb = 0;
+		CU(cudaMalloc(&n->gfCk, ck.size() * sizeof(float)));
+		CU(cudaMemcpyAsync(n->gfCk, ck.data(), ck.size() * sizeof(float), cudaMemcpyHostToDevice, n->stream));
+		CU(cudaStreamSynchronize(n->stream));
+		n->gfCkMb = mb;
 	}
 	GridFusedArgs a;
 	memset(&a, 0, sizeof a);
@@ -1049,11 +1083,21 @@ static int grid_fused_launch(gl_net* n, const float* X, const float* Y, int64_t 
 	a.delbuf = n->gfDel;
 	a.part = n->gfPart;
 	a.part_ctas = n->gfCtas;
+	a.ck = n->gfCk;
+	a.nc = n->gfNc;
 	a.epoch_sums = epoch_sums;
 	a.confusion = n->dConf;
 	a.last_out = n->dLastOut;
 	a.flags = n->dFlags;
-	cudaError_t e = launch_grid_fused(a, nullptr, n->stream);
+	static int want_timing = -1;
+	if (want_timing < 0) want_timing = getenv("GLADES_GF_TIMING") ? 1 : 0;
+	if (want_timing && !n->gfTiming)
+	{
+		CU(cudaMalloc(&n->gfTiming, 4 * sizeof(unsigned long long)));
+		CU(cudaMemset(n->gfTiming, 0, 4 * sizeof(unsigned long long)));
+	}
+	a.timing = n->gfTiming;
+	cudaError_t e = launch_grid_fused(a, n->stream);
 	if (e != cudaSuccess) return fail(GL_ERR_CUDA, "whole-window cooperative kernel: %s", cudaGetErrorString(e));
 	n->loW = false;
 	return GL_OK;

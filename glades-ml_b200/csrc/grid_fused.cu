@@ -30,8 +30,140 @@ namespace {
 constexpr int GF_THREADS = 256;
 constexpr int GF_ROWS = 8;      // samples a CTA carries through the network together
 constexpr int GF_WT = 256 * 33;  // floats of the weight-tile buffer ([256][33] forward, [32][256] backward)
-constexpr int GF_TO = 16, GF_TI = 32, GF_TJ = 64;  // phase 2: weight tile 16 outputs x 32 inputs, 64 rows per step
+constexpr int GF_TO = 16, GF_TJ = 64;  // phase 2: weight tile 16 outputs x (16 * NC) inputs, 64 rows per step
+constexpr int GF_TI_MAX = 64;           // NC (weights per thread) is 2 or 4
 constexpr int GF_PART = 2 + GL_MAX_WEIGHT_LAYERS;  // doubles per CTA: cost, accuracy, bias-delta sums per layer
+
+// Phase 2, one 16 x (16 * NC) tile of layer l's weights: thread = one output row, NC input columns;
+// sums c_j * (lr * d_jo * a_ji + decay terms) over the window's rows in row order and applies the
+// update in place.  The 64-row tiles of deltas / activations / momentum weights travel global ->
+// registers -> shared memory, the next step's loads in flight while the current one is consumed.
+template <int NC>
+__device__ __forceinline__ void gf_grad_tile(const GridFusedArgs& a, int l, int o0, int i0, int len, int tot, int off_in,
+                                             int off_out, float* Dt, float* At, float* Ct, const float* ckl, float inv_len,
+                                             int& bad)
+{
+	constexpr int TI = 16 * NC;
+	constexpr int NA = GF_TJ * TI / GF_THREADS;  // activation values per thread and step
+	const NetView& n = a.net;
+	const int t = threadIdx.x;
+	const int ni = n.sizes[l], no = n.sizes[l + 1];
+	const float lr = n.lr[l], w1 = n.wd1[l] * lr, w2 = n.wd2[l] * lr;
+	const bool decay = w1 != 0.0f || w2 != 0.0f;
+	const int oo = t >> 4, ic = (t & 15) * NC;
+	float g[NC];
+#pragma unroll
+	for (int c = 0; c < NC; ++c) g[c] = 0.0f;
+	float pd[4], pa[NA], pc = 0.0f;
+	auto fetch = [&](int jb) {
+		const int jn = (len - jb) < GF_TJ ? (len - jb) : GF_TJ;
+#pragma unroll
+		for (int k = 0; k < 4; ++k)
+		{
+			const int e = t + k * GF_THREADS, jj = e / GF_TO, x = e - jj * GF_TO;
+			pd[k] = (jj < jn && o0 + x < no) ? __ldcg(a.delbuf + (size_t)(jb + jj) * tot + off_out + o0 + x) : 0.0f;
+		}
+#pragma unroll
+		for (int k = 0; k < NA; ++k)
+		{
+			const int e = t + k * GF_THREADS, jj = e / TI, x = e - jj * TI;
+			pa[k] = (jj < jn && i0 + x < ni) ? __ldcg(a.actbuf + (size_t)(jb + jj) * tot + off_in + i0 + x) : 0.0f;
+		}
+		if (t < GF_TJ) pc = (t < jn) ? ckl[len - (jb + t)] : 0.0f;
+	};
+	fetch(0);
+	for (int jb = 0; jb < len; jb += GF_TJ)
+	{
+		const int jn = (len - jb) < GF_TJ ? (len - jb) : GF_TJ;
+		__syncthreads();
+		if (t < GF_TJ) Ct[t] = pc;
+#pragma unroll
+		for (int k = 0; k < NA; ++k) At[t + k * GF_THREADS] = pa[k];
+		if (decay)
+		{
+#pragma unroll
+			for (int k = 0; k < 4; ++k) Dt[t + k * GF_THREADS] = pd[k];
+		}
+		else
+		{
+			// no decay terms: the tile holds c_j * lr * d_jo, and a row costs one multiply-add per weight.
+			// (c_j of row jj = e / 16 comes from the table again: Ct is only complete after the barrier.)
+#pragma unroll
+			for (int k = 0; k < 4; ++k)
+			{
+				const int jj = (t + k * GF_THREADS) / GF_TO;
+				Dt[t + k * GF_THREADS] = (jj < jn) ? pd[k] * lr * ckl[len - (jb + jj)] : 0.0f;
+			}
+		}
+		__syncthreads();
+		if (jb + GF_TJ < len) fetch(jb + GF_TJ);
+		auto step = [&](int jj) {
+			const float c = Ct[jj];
+			const float dv = lr * Dt[jj * GF_TO + oo];
+			float av[NC];
+			if (NC == 2)
+			{
+				const float2 v = *reinterpret_cast<const float2*>(At + jj * TI + ic);
+				av[0] = v.x; av[1] = v.y;
+			}
+			else
+			{
+				const float4 v = *reinterpret_cast<const float4*>(At + jj * TI + ic);
+				av[0] = v.x; av[1] = v.y; av[NC - 2] = v.z; av[NC - 1] = v.w;
+			}
+#pragma unroll
+			for (int q = 0; q < NC; ++q) g[q] = fmaf(c, fmaf(dv, av[q], fmaf(w1, fabsf(av[q]), w2 * av[q])), g[q]);
+		};
+		auto fast = [&](int jj) {
+			const float dv = Dt[jj * GF_TO + oo];
+			if (NC == 2)
+			{
+				const float2 v = *reinterpret_cast<const float2*>(At + jj * TI + ic);
+				g[0] = fmaf(dv, v.x, g[0]); g[1] = fmaf(dv, v.y, g[1]);
+			}
+			else
+			{
+				const float4 v = *reinterpret_cast<const float4*>(At + jj * TI + ic);
+				g[0] = fmaf(dv, v.x, g[0]); g[1] = fmaf(dv, v.y, g[1]);
+				g[NC - 2] = fmaf(dv, v.z, g[NC - 2]); g[NC - 1] = fmaf(dv, v.w, g[NC - 1]);
+			}
+		};
+		if (!decay)
+		{
+			if (jn == GF_TJ)
+			{
+				// full step: a fixed trip count lets the shared-memory loads of several rows overlap
+#pragma unroll 16
+				for (int jj = 0; jj < GF_TJ; ++jj) fast(jj);
+			}
+			else
+				for (int jj = 0; jj < jn; ++jj) fast(jj);
+		}
+		else if (jn == GF_TJ)
+		{
+#pragma unroll 16
+			for (int jj = 0; jj < GF_TJ; ++jj) step(jj);
+		}
+		else
+			for (int jj = 0; jj < jn; ++jj) step(jj);
+	}
+	const int o = o0 + oo;
+	if (o < no)
+	{
+		float* wp = n.W[l] + (size_t)o * ni + i0 + ic;
+#pragma unroll
+		for (int q = 0; q < NC; ++q)
+		{
+			if (i0 + ic + q < ni)
+			{
+				const float w = __ldcg(wp + q) - g[q] * inv_len;
+				if (!isfinite(w)) bad = 1;
+				wp[q] = w;
+			}
+		}
+	}
+}
+
 
 __global__ void __launch_bounds__(GF_THREADS, 1) grid_fused_kernel(const __grid_constant__ GridFusedArgs a)
 {
@@ -57,40 +189,40 @@ __global__ void __launch_bounds__(GF_THREADS, 1) grid_fused_kernel(const __grid_
 	float* Wt = Ds + (size_t)tot * GF_ROWS;
 	float* ck = Wt + GF_WT;
 	float* Dt = ck + (((size_t)(H + 1) * (mb + 1) + 3) & ~(size_t)3);  // [GF_TJ][GF_TO]
-	float* At = Dt + GF_TJ * GF_TO;               // [GF_TJ][GF_TI]
-	float* Ct = At + GF_TJ * GF_TI;               // [GF_TJ]
+	float* At = Dt + GF_TJ * GF_TO;               // [GF_TJ][16 * NC]
+	float* Ct = At + GF_TJ * GF_TI_MAX;           // [GF_TJ]
 	float* rowm = Ct + GF_TJ;                     // [GF_ROWS][2]: cost, accuracy of the group's rows
 	__shared__ double s_part[GF_PART];
 
-	// ck[l][k] = sum_{q<k} m_l^q: the weight of a sample with k samples of its window still to come (itself included)
-	for (int e = t; e < (H + 1) * (mb + 1); e += GF_THREADS)
-	{
-		const int l = e / (mb + 1), k = e - l * (mb + 1);
-		const double m = (double)n.mom[l];
-		double s = 0.0, pw = 1.0;
-		for (int q = 0; q < k; ++q)
-		{
-			s += pw;
-			pw *= m;
-			if (pw < 1e-30) break;
-		}
-		ck[e] = (m == 0.0) ? (k > 0 ? 1.0f : 0.0f) : (float)s;
-	}
+	// ck[l][k] = sum_{q<k} m_l^q: the weight of a sample with k samples of its window still to come (itself
+	// included); made once on the host, [H+1][mb+1]
+	for (int e = t; e < (H + 1) * (mb + 1); e += GF_THREADS) ck[e] = a.ck[e];
 	__syncthreads();
 
 	const bool classify = n.out_type != GL_OUT_REGRESSION;
 	const bool softmax = n.act[H] == GL_ACT_SOFTMAX;
 	const float data_size = a.data_size;
 
-	// phase-2 tile list: layer l has ceil(no/16) * ceil(ni/32) tiles
+	// phase-2 tile list: layer l has ceil(no/16) * ceil(ni/(16*NC)) tiles
+	const int tile_i = 16 * a.nc;
 	int tile_off[GL_MAX_WEIGHT_LAYERS + 1];
 	int tiles = 0;
 	for (int l = 0; l <= H; ++l)
 	{
 		tile_off[l] = tiles;
-		tiles += ((n.sizes[l + 1] + GF_TO - 1) / GF_TO) * ((n.sizes[l] + GF_TI - 1) / GF_TI);
+		tiles += ((n.sizes[l + 1] + GF_TO - 1) / GF_TO) * ((n.sizes[l] + tile_i - 1) / tile_i);
 	}
 	tile_off[H + 1] = tiles;
+
+	// optional phase timing (diagnostics): CTA 0, thread 0 adds up the nanoseconds of
+	// [phase 1, barrier, phase 2, barrier] in a.timing[0..3]
+	const bool timed = a.timing != nullptr && blockIdx.x == 0 && t == 0;
+	unsigned long long tm[4] = {0, 0, 0, 0}, t_a = 0, t_b = 0;
+	auto now = []() {
+		unsigned long long v;
+		asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(v));
+		return v;
+	};
 
 	int bad = 0;
 	for (int ep = 0; ep < a.n_epochs; ++ep)
@@ -102,6 +234,7 @@ __global__ void __launch_bounds__(GF_THREADS, 1) grid_fused_kernel(const __grid_
 			const int len = (int)((a.rows - r0) < mb ? (a.rows - r0) : mb);
 			const int groups = (len + GF_ROWS - 1) / GF_ROWS;
 			if (t < GF_PART) s_part[t] = 0.0;
+			if (timed) t_a = now();
 			// ================= phase 1: forward, head, deltas, GF_ROWS samples at a time
 			for (int gidx = blockIdx.x; gidx < groups; gidx += gridDim.x)
 			{
@@ -128,28 +261,57 @@ __global__ void __launch_bounds__(GF_THREADS, 1) grid_fused_kernel(const __grid_
 						float acc[GF_ROWS];
 #pragma unroll
 						for (int r = 0; r < GF_ROWS; ++r) acc[r] = 0.0f;
+						// weight tiles travel global -> registers -> shared memory, the next tile's loads in flight
+						// while the current one is consumed
+						float pre[32];
+						// this thread's part of a tile: column `lane`, rows warp, warp + 8, ... (kmax of them exist)
+						const float* wsrc = W + (size_t)(o0 + warp) * ni + lane;
+						const size_t wstep = (size_t)8 * ni;
+						const int kmax = (no - o0 - warp + 7) >> 3;  // may be <= 0 or > 32
+						const bool computes = o0 + t < no;
+						{
+							const float* q = wsrc;
+							const bool col = lane < ni;
+#pragma unroll
+							for (int k = 0; k < 32; ++k, q += wstep) pre[k] = (col && k < kmax) ? __ldcg(q) : 0.0f;
+						}
 						for (int i0 = 0; i0 < ni; i0 += 32)
 						{
 							__syncthreads();  // the tile's previous contents (and `in`) are settled
-							for (int e = t; e < GF_THREADS * 32; e += GF_THREADS)
-							{
-								const int oo = e >> 5, ii = e & 31;
-								const int o = o0 + oo, i = i0 + ii;
-								Wt[oo * 33 + ii] = (o < no && i < ni) ? __ldcg(W + (size_t)o * ni + i) : 0.0f;
-							}
+#pragma unroll
+							for (int k = 0; k < 32; ++k) Wt[(warp + 8 * k) * 33 + lane] = pre[k];
 							__syncthreads();
+							if (i0 + 32 < ni)
+							{
+								const float* q = wsrc + i0 + 32;
+								const bool col = i0 + 32 + lane < ni;
+#pragma unroll
+								for (int k = 0; k < 32; ++k, q += wstep) pre[k] = (col && k < kmax) ? __ldcg(q) : 0.0f;
+							}
 							const int lim = (ni - i0) < 32 ? (ni - i0) : 32;
 							const float* wrow = Wt + t * 33;
-							for (int ii = 0; ii < lim; ++ii)
-							{
+							const float* inb = in + (size_t)i0 * GF_ROWS;
+							auto step = [&](int ii) {
 								const float w = wrow[ii];
-								const float4 a0 = *reinterpret_cast<const float4*>(in + (size_t)(i0 + ii) * GF_ROWS);
-								const float4 a1 = *reinterpret_cast<const float4*>(in + (size_t)(i0 + ii) * GF_ROWS + 4);
+								const float4 a0 = *reinterpret_cast<const float4*>(inb + ii * GF_ROWS);
+								const float4 a1 = *reinterpret_cast<const float4*>(inb + ii * GF_ROWS + 4);
 								acc[0] = fmaf(w, a0.x, acc[0]); acc[1] = fmaf(w, a0.y, acc[1]);
 								acc[2] = fmaf(w, a0.z, acc[2]); acc[3] = fmaf(w, a0.w, acc[3]);
 								acc[4] = fmaf(w, a1.x, acc[4]); acc[5] = fmaf(w, a1.y, acc[5]);
 								acc[6] = fmaf(w, a1.z, acc[6]); acc[7] = fmaf(w, a1.w, acc[7]);
+							};
+							if (!computes)
+							{
+								// no output node for this thread in this pass: it only helps moving tiles
 							}
+							else if (lim == 32)
+							{
+								// full tile: a fixed trip count lets the shared-memory loads of several steps overlap
+#pragma unroll 16
+								for (int ii = 0; ii < 32; ++ii) step(ii);
+							}
+							else
+								for (int ii = 0; ii < lim; ++ii) step(ii);
 						}
 						const int o = o0 + t;
 						if (o < no)
@@ -254,27 +416,48 @@ __global__ void __launch_bounds__(GF_THREADS, 1) grid_fused_kernel(const __grid_
 						float acc[GF_ROWS];
 #pragma unroll
 						for (int r = 0; r < GF_ROWS; ++r) acc[r] = 0.0f;
+						float pre[32];
+						const bool computes = i0 + t < ni;  // also: this thread's column of the tiles exists
+						const float* wsrc = W + i0 + t;     // row o of the tile: wsrc + o * ni
+						{
+							const float* q = wsrc;
+#pragma unroll
+							for (int k = 0; k < 32; ++k, q += ni) pre[k] = (computes && k < no) ? __ldcg(q) : 0.0f;
+						}
 						for (int o0 = 0; o0 < no; o0 += 32)
 						{
 							__syncthreads();
-							for (int e = t; e < 32 * GF_THREADS; e += GF_THREADS)
-							{
-								const int oo = e >> 8, ii = e & 255;
-								const int o = o0 + oo, i = i0 + ii;
-								Wt[oo * GF_THREADS + ii] = (o < no && i < ni) ? __ldcg(W + (size_t)o * ni + i) : 0.0f;
-							}
+#pragma unroll
+							for (int k = 0; k < 32; ++k) Wt[k * GF_THREADS + t] = pre[k];
 							__syncthreads();
-							const int lim = (no - o0) < 32 ? (no - o0) : 32;
-							for (int oo = 0; oo < lim; ++oo)
+							if (o0 + 32 < no)
 							{
+								const float* q = wsrc + (size_t)(o0 + 32) * ni;
+								const int left = no - (o0 + 32);
+#pragma unroll
+								for (int k = 0; k < 32; ++k, q += ni) pre[k] = (computes && k < left) ? __ldcg(q) : 0.0f;
+							}
+							const int lim = (no - o0) < 32 ? (no - o0) : 32;
+							const float* dub = dup + (size_t)o0 * GF_ROWS;
+							auto step = [&](int oo) {
 								const float w = Wt[oo * GF_THREADS + t];
-								const float4 d0 = *reinterpret_cast<const float4*>(dup + (size_t)(o0 + oo) * GF_ROWS);
-								const float4 d1 = *reinterpret_cast<const float4*>(dup + (size_t)(o0 + oo) * GF_ROWS + 4);
+								const float4 d0 = *reinterpret_cast<const float4*>(dub + oo * GF_ROWS);
+								const float4 d1 = *reinterpret_cast<const float4*>(dub + oo * GF_ROWS + 4);
 								acc[0] = fmaf(w, d0.x, acc[0]); acc[1] = fmaf(w, d0.y, acc[1]);
 								acc[2] = fmaf(w, d0.z, acc[2]); acc[3] = fmaf(w, d0.w, acc[3]);
 								acc[4] = fmaf(w, d1.x, acc[4]); acc[5] = fmaf(w, d1.y, acc[5]);
 								acc[6] = fmaf(w, d1.z, acc[6]); acc[7] = fmaf(w, d1.w, acc[7]);
+							};
+							if (!computes)
+							{
 							}
+							else if (lim == 32)
+							{
+#pragma unroll 16
+								for (int oo = 0; oo < 32; ++oo) step(oo);
+							}
+							else
+								for (int oo = 0; oo < lim; ++oo) step(oo);
 						}
 						const int i = i0 + t;
 						if (i < ni)
@@ -320,7 +503,9 @@ __global__ void __launch_bounds__(GF_THREADS, 1) grid_fused_kernel(const __grid_
 			}
 			__syncthreads();
 			if (t < GF_PART) a.part[(size_t)blockIdx.x * GF_PART + t] = s_part[t];
+			if (timed) { t_b = now(); tm[0] += t_b - t_a; }
 			grid.sync();
+			if (timed) { t_a = now(); tm[1] += t_a - t_b; }
 
 			// ================= phase 2: gradient + update per weight tile; CTA 0 also the scalars
 			const float inv_len = 1.0f / (float)len;
@@ -328,56 +513,14 @@ __global__ void __launch_bounds__(GF_THREADS, 1) grid_fused_kernel(const __grid_
 			{
 				int l = 0;
 				while (tile >= tile_off[l + 1]) ++l;
-				const int ni = n.sizes[l], no = n.sizes[l + 1];
-				const int tiles_i = (ni + GF_TI - 1) / GF_TI;
+				const int tiles_i = (n.sizes[l] + tile_i - 1) / tile_i;
 				const int tl = tile - tile_off[l];
-				const int o0 = (tl / tiles_i) * GF_TO, i0 = (tl % tiles_i) * GF_TI;
-				const float lr = n.lr[l], w1 = n.wd1[l] * lr, w2 = n.wd2[l] * lr;
+				const int o0 = (tl / tiles_i) * GF_TO, i0 = (tl % tiles_i) * tile_i;
 				const float* ckl = ck + (size_t)l * (mb + 1);
-				const int oo = t >> 4, i2 = (t & 15) * 2;  // this thread's output row and its two input columns
-				float g0 = 0.0f, g1 = 0.0f;
-				for (int jb = 0; jb < len; jb += GF_TJ)
-				{
-					const int jn = (len - jb) < GF_TJ ? (len - jb) : GF_TJ;
-					__syncthreads();
-					for (int e = t; e < GF_TJ * GF_TO; e += GF_THREADS)
-					{
-						const int jj = e / GF_TO, x = e - jj * GF_TO;
-						Dt[e] = (jj < jn && o0 + x < no) ? __ldcg(a.delbuf + (size_t)(jb + jj) * tot + node_off[l + 1] + o0 + x) : 0.0f;
-					}
-					for (int e = t; e < GF_TJ * GF_TI; e += GF_THREADS)
-					{
-						const int jj = e / GF_TI, x = e - jj * GF_TI;
-						At[e] = (jj < jn && i0 + x < ni) ? __ldcg(a.actbuf + (size_t)(jb + jj) * tot + node_off[l] + i0 + x) : 0.0f;
-					}
-					if (t < GF_TJ) Ct[t] = (t < jn) ? ckl[len - (jb + t)] : 0.0f;
-					__syncthreads();
-					for (int jj = 0; jj < jn; ++jj)
-					{
-						const float c = Ct[jj];
-						const float dv = lr * Dt[jj * GF_TO + oo];
-						const float2 av = *reinterpret_cast<const float2*>(At + jj * GF_TI + i2);
-						g0 = fmaf(c, fmaf(dv, av.x, fmaf(w1, fabsf(av.x), w2 * av.x)), g0);
-						g1 = fmaf(c, fmaf(dv, av.y, fmaf(w1, fabsf(av.y), w2 * av.y)), g1);
-					}
-				}
-				const int o = o0 + oo;
-				if (o < no)
-				{
-					float* wp = n.W[l] + (size_t)o * ni + i0 + i2;
-					if (i0 + i2 < ni)
-					{
-						const float w = __ldcg(wp) - g0 * inv_len;
-						if (!isfinite(w)) bad = 1;
-						wp[0] = w;
-					}
-					if (i0 + i2 + 1 < ni)
-					{
-						const float w = __ldcg(wp + 1) - g1 * inv_len;
-						if (!isfinite(w)) bad = 1;
-						wp[1] = w;
-					}
-				}
+				if (a.nc == 2)
+					gf_grad_tile<2>(a, l, o0, i0, len, tot, node_off[l], node_off[l + 1], Dt, At, Ct, ckl, inv_len, bad);
+				else
+					gf_grad_tile<4>(a, l, o0, i0, len, tot, node_off[l], node_off[l + 1], Dt, At, Ct, ckl, inv_len, bad);
 			}
 			if (blockIdx.x == 0)
 			{
@@ -395,16 +538,27 @@ __global__ void __launch_bounds__(GF_THREADS, 1) grid_fused_kernel(const __grid_
 						n.bias[l] = nb;
 					}
 				}
-				if (t == 0)
+				if (warp == 0)
 				{
-					for (int b = 0; b < (int)gridDim.x; ++b)
+					// the CTAs' cost / accuracy partials: lanes stride over the CTAs, then a fixed shuffle tree
+					double c = 0.0, q = 0.0;
+					for (int b = lane; b < (int)gridDim.x; b += 32)
 					{
-						ecost += __ldcg(a.part + (size_t)b * GF_PART);
-						eacc += __ldcg(a.part + (size_t)b * GF_PART + 1);
+						c += __ldcg(a.part + (size_t)b * GF_PART);
+						q += __ldcg(a.part + (size_t)b * GF_PART + 1);
+					}
+					c = warp_sum_d(c);
+					q = warp_sum_d(q);
+					if (lane == 0)
+					{
+						ecost += c;
+						eacc += q;
 					}
 				}
 			}
+			if (timed) { t_b = now(); tm[2] += t_b - t_a; }
 			grid.sync();
+			if (timed) { t_a = now(); tm[3] += t_a - t_b; }
 		}
 		if (blockIdx.x == 0 && t == 0)
 		{
@@ -412,6 +566,8 @@ __global__ void __launch_bounds__(GF_THREADS, 1) grid_fused_kernel(const __grid_
 			a.epoch_sums[2 * ep + 1] = eacc;
 		}
 	}
+	if (timed)
+		for (int k = 0; k < 4; ++k) a.timing[k] += tm[k];
 	if (bad) atomicOr(a.flags, 1);
 }
 
@@ -421,7 +577,7 @@ size_t grid_fused_smem_bytes(const NetView& n)
 {
 	int tot = 0;
 	for (int l = 0; l <= n.H + 1; ++l) tot += n.sizes[l];
-	size_t f = 2 * (size_t)tot * GF_ROWS + GF_WT + (((size_t)(n.H + 1) * (n.mb + 1) + 3) & ~(size_t)3) + GF_TJ * GF_TO + GF_TJ * GF_TI + GF_TJ + 2 * GF_ROWS;
+	size_t f = 2 * (size_t)tot * GF_ROWS + GF_WT + (((size_t)(n.H + 1) * (n.mb + 1) + 3) & ~(size_t)3) + GF_TJ * GF_TO + GF_TJ * GF_TI_MAX + GF_TJ + 2 * GF_ROWS;
 	return f * sizeof(float) + 64;
 }
 
@@ -432,24 +588,32 @@ int grid_fused_total_nodes(const NetView& n)
 	return tot;
 }
 
-cudaError_t launch_grid_fused(const GridFusedArgs& a, int* grid_out, cudaStream_t s)
+int grid_fused_pick_nc(const NetView& n, int ctas)
+{
+	for (int nc = 2; nc <= 4; nc *= 2)
+	{
+		int tiles = 0;
+		for (int l = 0; l <= n.H; ++l) tiles += ((n.sizes[l + 1] + GF_TO - 1) / GF_TO) * ((n.sizes[l] + 16 * nc - 1) / (16 * nc));
+		if (tiles <= ctas) return nc;
+	}
+	return 4;
+}
+
+cudaError_t launch_grid_fused(const GridFusedArgs& a, cudaStream_t s)
 {
 	const size_t bytes = grid_fused_smem_bytes(a.net);
-	cudaError_t e = cudaFuncSetAttribute(grid_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
-	if (e != cudaSuccess) return e;
-	int dev = 0, sms = 0, per_sm = 0;
-	cudaGetDevice(&dev);
-	e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-	if (e != cudaSuccess) return e;
-	e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, grid_fused_kernel, GF_THREADS, bytes);
-	if (e != cudaSuccess) return e;
-	if (per_sm < 1) return cudaErrorInvalidConfiguration;
-	int grid = sms;  // one CTA per SM; a.part is sized for grid_fused_max_grid() CTAs
-	if (grid > a.part_ctas) grid = a.part_ctas;
-	if (grid_out) *grid_out = grid;
+	static size_t attr_bytes = 0;
+	if (bytes > attr_bytes)
+	{
+		cudaError_t e = cudaFuncSetAttribute(grid_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+		if (e != cudaSuccess) return e;
+		attr_bytes = bytes;
+	}
+	if (a.part_ctas < 1 || (a.nc != 2 && a.nc != 4)) return cudaErrorInvalidValue;
 	GridFusedArgs copy = a;
 	void* params[] = {&copy};
-	return cudaLaunchCooperativeKernel((void*)grid_fused_kernel, dim3((unsigned)grid), dim3(GF_THREADS), params, bytes, s);
+	// one CTA per SM (the shared-memory footprint allows no more), all co-resident as the grid barrier needs
+	return cudaLaunchCooperativeKernel((void*)grid_fused_kernel, dim3((unsigned)a.part_ctas), dim3(GF_THREADS), params, bytes, s);
 }
 
 }  // namespace glb

@@ -142,15 +142,20 @@ struct GridFusedArgs
 	float* actbuf;       // [net.mb][total nodes] scratch: the window's activations
 	float* delbuf;       // [net.mb][total nodes] scratch: the window's deltas
 	double* part;        // [part_ctas][2 + GL_MAX_WEIGHT_LAYERS] per-CTA partial sums of a window
-	int part_ctas;
+	int part_ctas;       // = the grid of the launch (one CTA per SM)
+	const float* ck;     // [H+1][net.mb+1]: ck[l][k] = sum_{q<k} momentum_l^q
+	int nc;              // weights per thread in the update phase (2 or 4): see grid_fused_pick_nc
 	double* epoch_sums;  // [n_epochs][2]: cost sum, accuracy sum
 	int* confusion;      // [n_out][n_out]: the last epoch's counts are ADDED (the caller clears)
 	float* last_out;     // [n_out] or NULL
 	int* flags;
+	unsigned long long* timing;  // optional diagnostics: ns spent in [phase 1, barrier, phase 2, barrier] by CTA 0
 };
 size_t grid_fused_smem_bytes(const NetView& n);
 int grid_fused_total_nodes(const NetView& n);
-cudaError_t launch_grid_fused(const GridFusedArgs& a, int* grid_out, cudaStream_t s);
+// smallest tile width whose tile count does not exceed `ctas` (else 4)
+int grid_fused_pick_nc(const NetView& n, int ctas);
+cudaError_t launch_grid_fused(const GridFusedArgs& a, cudaStream_t s);
 
 // ---- data-parallel gradient exchange over peer memory (dp_push.cu) ---------------------------------
 // Every rank owns an exchange arena that all ranks map: a flag area of DP_FLAG_BYTES (32-bit window
