@@ -205,6 +205,8 @@ struct gl_net
 	float* gfDel = nullptr;
 	double* gfPart = nullptr;
 	float* gfCk = nullptr;   // momentum table for windows of gfCkMb rows
+	void* gfMaps = nullptr;  // device array of the weight tensor maps (NULL: the register path)
+	bool gfMapsTried = false;
 	unsigned long long* gfTiming = nullptr;  // GLADES_GF_TIMING=1: phase nanoseconds, printed when the handle goes
 	int gfRows = 0, gfCtas = 0, gfCkMb = 0, gfNc = 2;
 	int gfOk = -1;  // -1 not decided yet
@@ -416,7 +418,7 @@ extern "C" int gl_destroy(gl_net* n)
 			        tm[1] * 1e-6, tm[2] * 1e-6, tm[3] * 1e-6);
 		cudaFree(n->gfTiming);
 	}
-	cudaFree(n->gfAct); cudaFree(n->gfDel); cudaFree(n->gfPart); cudaFree(n->gfCk);
+	cudaFree(n->gfAct); cudaFree(n->gfDel); cudaFree(n->gfPart); cudaFree(n->gfCk); cudaFree(n->gfMaps);
 	for (int i = 0; i < 2; ++i)
 	{
 		cudaFree(n->slot[i].dX); cudaFree(n->slot[i].dY); cudaFree(n->slot[i].dSums);
@@ -1046,6 +1048,30 @@ static int grid_fused_launch(gl_net* n, const float* X, const float* Y, int64_t 
 		CU(cudaMalloc(&n->gfPart, (size_t)sms * (2 + GL_MAX_WEIGHT_LAYERS) * sizeof(double)));
 		n->gfNc = grid_fused_pick_nc(base, sms);
 	}
+	if (!n->gfMapsTried)
+	{
+		// weight tiles by bulk tensor copies where every layer's rows are multiples of 16 bytes
+		n->gfMapsTried = true;
+		const char* e = getenv("GLADES_GF_TMA");
+		bool ok = !(e && atoi(e) == 0) && grid_fused_group_tiles(base) <= 512;
+		for (int l = 0; ok && l <= n->H; ++l) ok = n->d.sizes[l] % 4 == 0 && n->woff[l] % 4 == 0;
+		if (ok)
+		{
+			std::vector<unsigned char> raw((size_t)2 * (n->H + 1) * 128 + 64);
+			unsigned char* maps = raw.data() + ((64 - ((uintptr_t)raw.data() & 63)) & 63);
+			for (int l = 0; ok && l <= n->H; ++l)
+			{
+				const int ni = n->d.sizes[l], no = n->d.sizes[l + 1];
+				ok = tc_make_map2d(maps + (size_t)(2 * l) * 128, n->dW + n->woff[l], no, ni, ni, 32, 256, 1) &&
+				     tc_make_map2d(maps + (size_t)(2 * l + 1) * 128, n->dW + n->woff[l], no, ni, ni, 256, 32, 0);
+			}
+			if (ok)
+			{
+				CU(cudaMalloc(&n->gfMaps, (size_t)2 * (n->H + 1) * 128));
+				CU(cudaMemcpy(n->gfMaps, maps, (size_t)2 * (n->H + 1) * 128, cudaMemcpyHostToDevice));
+			}
+		}
+	}
 	if (n->gfCkMb != mb)
 	{
 		// ck[l][k] = sum_{q<k} m_l^q, summed like the per-sample momentum history builds it up
@@ -1085,6 +1111,7 @@ static int grid_fused_launch(gl_net* n, const float* X, const float* Y, int64_t 
 	a.part_ctas = n->gfCtas;
 	a.ck = n->gfCk;
 	a.nc = n->gfNc;
+	a.tma = n->gfMaps;
 	a.epoch_sums = epoch_sums;
 	a.confusion = n->dConf;
 	a.last_out = n->dLastOut;

@@ -448,6 +448,20 @@ bool tc_make_store_map(void* out128, const float* base, long long rows, long lon
 	return make_map(reinterpret_cast<CUtensorMap*>(out128), base, 0, rows, cols, ld, 32, 32);
 }
 
+bool tc_make_map2d(void* out128, const float* base, long long rows, long long cols, long long ld, int box_cols, int box_rows,
+                   int swizzle128)
+{
+	EncodeTiledFn fn = encode_fn();
+	if (!fn) return false;
+	cuuint64_t dim[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+	cuuint64_t str[1] = {(cuuint64_t)ld * 4};
+	cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
+	cuuint32_t es[2] = {1, 1};
+	return fn(reinterpret_cast<CUtensorMap*>(out128), CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, (void*)base, dim, str, box, es,
+	          CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+	          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 // k-block depth of the tile variant in use: 16 (default) or 32 (GLADES_TC_BK=32, kept for comparison)
 int tc::tc_bk()
 {

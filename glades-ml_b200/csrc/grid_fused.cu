@@ -19,12 +19,12 @@
 // the closed form of the reference's intra-window momentum history (State/node.cpp:278-292).
 #include <cooperative_groups.h>
 
-#include "common.cuh"
-#include "internal.h"
+#include "tc_device.cuh"
 
 namespace cg = cooperative_groups;
 
 namespace glb {
+using namespace tc;
 namespace {
 
 constexpr int GF_THREADS = 256;
@@ -32,6 +32,10 @@ constexpr int GF_ROWS = 8;      // samples a CTA carries through the network tog
 constexpr int GF_WT = 256 * 33;  // floats of the weight-tile buffer ([256][33] forward, [32][256] backward)
 constexpr int GF_TO = 16, GF_TJ = 64;  // phase 2: weight tile 16 outputs x (16 * NC) inputs, 64 rows per step
 constexpr int GF_TI_MAX = 64;           // NC (weights per thread) is 2 or 4
+constexpr int GF_NS = 3;                // stages of the weight-tile ring (bulk tensor copies, 32 KB each)
+constexpr int GF_STAGE = 32768;
+constexpr int GF_SEQ_MAX = 512;         // weight tiles one sample group walks through, at most, on the ring path
+static_assert(GF_WT * 4 <= GF_NS * GF_STAGE, "the register-path tile buffer lives inside the ring");
 constexpr int GF_PART = 2 + GL_MAX_WEIGHT_LAYERS;  // doubles per CTA: cost, accuracy, bias-delta sums per layer
 
 // Phase 2, one 16 x (16 * NC) tile of layer l's weights: thread = one output row, NC input columns;
@@ -133,7 +137,7 @@ __device__ __forceinline__ void gf_grad_tile(const GridFusedArgs& a, int l, int 
 			if (jn == GF_TJ)
 			{
 				// full step: a fixed trip count lets the shared-memory loads of several rows overlap
-#pragma unroll 16
+#pragma unroll 4
 				for (int jj = 0; jj < GF_TJ; ++jj) fast(jj);
 			}
 			else
@@ -141,7 +145,7 @@ __device__ __forceinline__ void gf_grad_tile(const GridFusedArgs& a, int l, int 
 		}
 		else if (jn == GF_TJ)
 		{
-#pragma unroll 16
+#pragma unroll 4
 			for (int jj = 0; jj < GF_TJ; ++jj) step(jj);
 		}
 		else
@@ -186,13 +190,68 @@ __global__ void __launch_bounds__(GF_THREADS, 1) grid_fused_kernel(const __grid_
 	// [H+1][mb+1] | phase-2 tiles | per-row metric scratch
 	float* As = sm;
 	float* Ds = As + (size_t)tot * GF_ROWS;
-	float* Wt = Ds + (size_t)tot * GF_ROWS;
-	float* ck = Wt + GF_WT;
+	float* ck = Ds + (size_t)tot * GF_ROWS;
 	float* Dt = ck + (((size_t)(H + 1) * (mb + 1) + 3) & ~(size_t)3);  // [GF_TJ][GF_TO]
 	float* At = Dt + GF_TJ * GF_TO;               // [GF_TJ][16 * NC]
 	float* Ct = At + GF_TJ * GF_TI_MAX;           // [GF_TJ]
 	float* rowm = Ct + GF_TJ;                     // [GF_ROWS][2]: cost, accuracy of the group's rows
+	int* seq = reinterpret_cast<int*>(rowm + 2 * GF_ROWS);  // [GF_SEQ_MAX][3]: tensor map, x, y of a group's weight tiles
+	// weight tiles: a ring of GF_NS stages filled by bulk tensor copies (1024-byte aligned for the
+	// 128-byte swizzle), or -- where the weights' layout does not allow tensor maps -- one tile buffer
+	// filled through registers
+	uint8_t* ring_gen;
+	{
+		uint8_t* after = reinterpret_cast<uint8_t*>(seq + 3 * GF_SEQ_MAX);
+		const uint32_t au = smem_u32(after);
+		ring_gen = after + (((au + 1023u) & ~1023u) - au);
+	}
+	const uint32_t ring = smem_u32(ring_gen);
+	float* Wt = reinterpret_cast<float*>(ring_gen);
 	__shared__ double s_part[GF_PART];
+	__shared__ uint64_t gf_bars[GF_NS];
+	__shared__ int gf_abort;
+	const bool use_tma = a.tma != nullptr;
+	const CUtensorMap* maps = reinterpret_cast<const CUtensorMap*>(a.tma);
+	int nsteps = 0;  // weight tiles per sample group
+	if (use_tma)
+	{
+		if (t == 0)
+		{
+			for (int sidx = 0; sidx < GF_NS; ++sidx) mbar_init(smem_u32(&gf_bars[sidx]), 1);
+			gf_abort = 0;
+			asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+		}
+		// the tile order of one group: forward layer by layer (output chunk, then input tile), then the
+		// hidden deltas from the top (input chunk, then output tile)
+		for (int l = 0; l <= H; ++l)
+			for (int o0 = 0; o0 < n.sizes[l + 1]; o0 += GF_THREADS)
+				for (int i0 = 0; i0 < n.sizes[l]; i0 += 32, ++nsteps)
+					if (t == 0) { seq[3 * nsteps] = 2 * l; seq[3 * nsteps + 1] = i0; seq[3 * nsteps + 2] = o0; }
+		for (int L = H + 1; L >= 2; --L)
+			for (int i0 = 0; i0 < n.sizes[L - 1]; i0 += GF_THREADS)
+				for (int o0 = 0; o0 < n.sizes[L]; o0 += 32, ++nsteps)
+					if (t == 0) { seq[3 * nsteps] = 2 * (L - 1) + 1; seq[3 * nsteps + 1] = i0; seq[3 * nsteps + 2] = o0; }
+	}
+	unsigned cs = 0;                         // ring steps consumed so far (every thread)
+	unsigned ps = 0, p_base = 0, p_end = 0;  // thread 0: steps issued, first and end step of the current window
+	bool dead = false;                       // a bounded wait ran out: stop waiting, finish the launch
+	auto issue = [&]() {
+		const int* e = seq + 3 * ((ps - p_base) % (unsigned)nsteps);
+		const uint32_t bar = smem_u32(&gf_bars[ps % GF_NS]);
+		mbar_expect_tx(bar, GF_STAGE);
+		tma_load_2d(ring + (ps % GF_NS) * GF_STAGE, maps + e[0], bar, e[1], e[2]);
+		++ps;
+	};
+	auto acquire = [&]() -> const float* {
+		const unsigned sidx = cs % GF_NS;
+		if (!dead && !mbar_wait(smem_u32(&gf_bars[sidx]), (cs / GF_NS) & 1u, &gf_abort, a.flags + 1, 30)) dead = true;
+		return reinterpret_cast<const float*>(ring_gen + sidx * GF_STAGE);
+	};
+	auto release = [&]() {
+		__syncthreads();  // every thread is done with the stage
+		++cs;
+		if (t == 0 && ps < p_end) issue();
+	};
 
 	// ck[l][k] = sum_{q<k} m_l^q: the weight of a sample with k samples of its window still to come (itself
 	// included); made once on the host, [H+1][mb+1]
@@ -234,6 +293,15 @@ __global__ void __launch_bounds__(GF_THREADS, 1) grid_fused_kernel(const __grid_
 			const int len = (int)((a.rows - r0) < mb ? (a.rows - r0) : mb);
 			const int groups = (len + GF_ROWS - 1) / GF_ROWS;
 			if (t < GF_PART) s_part[t] = 0.0;
+			if (use_tma && t == 0)
+			{
+				// this window's tiles: nsteps per group of this CTA; never run ahead into the next window,
+				// whose weights do not exist yet
+				const int mine = (groups > (int)blockIdx.x) ? (groups - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+				p_base = ps;
+				p_end = ps + (unsigned)(mine * nsteps);
+				for (int k = 0; k < GF_NS && ps < p_end; ++k) issue();
+			}
 			if (timed) t_a = now();
 			// ================= phase 1: forward, head, deltas, GF_ROWS samples at a time
 			for (int gidx = blockIdx.x; gidx < groups; gidx += gridDim.x)
@@ -247,6 +315,7 @@ __global__ void __launch_bounds__(GF_THREADS, 1) grid_fused_kernel(const __grid_
 					const int r = e / n.sizes[0], i = e - r * n.sizes[0];
 					As[i * GF_ROWS + r] = (r < valid) ? a.X[(r0 + j0 + r) * n.sizes[0] + i] : 0.0f;
 				}
+				if (use_tma) __syncthreads();
 				for (int l = 0; l <= H; ++l)
 				{
 					const int ni = n.sizes[l], no = n.sizes[l + 1];
@@ -261,57 +330,95 @@ __global__ void __launch_bounds__(GF_THREADS, 1) grid_fused_kernel(const __grid_
 						float acc[GF_ROWS];
 #pragma unroll
 						for (int r = 0; r < GF_ROWS; ++r) acc[r] = 0.0f;
-						// weight tiles travel global -> registers -> shared memory, the next tile's loads in flight
-						// while the current one is consumed
-						float pre[32];
-						// this thread's part of a tile: column `lane`, rows warp, warp + 8, ... (kmax of them exist)
-						const float* wsrc = W + (size_t)(o0 + warp) * ni + lane;
-						const size_t wstep = (size_t)8 * ni;
-						const int kmax = (no - o0 - warp + 7) >> 3;  // may be <= 0 or > 32
-						const bool computes = o0 + t < no;
+						if (use_tma)
 						{
-							const float* q = wsrc;
-							const bool col = lane < ni;
-#pragma unroll
-							for (int k = 0; k < 32; ++k, q += wstep) pre[k] = (col && k < kmax) ? __ldcg(q) : 0.0f;
-						}
-						for (int i0 = 0; i0 < ni; i0 += 32)
-						{
-							__syncthreads();  // the tile's previous contents (and `in`) are settled
-#pragma unroll
-							for (int k = 0; k < 32; ++k) Wt[(warp + 8 * k) * 33 + lane] = pre[k];
-							__syncthreads();
-							if (i0 + 32 < ni)
+							const bool computes = o0 + t < no;
+							for (int i0 = 0; i0 < ni; i0 += 32)
 							{
-								const float* q = wsrc + i0 + 32;
-								const bool col = i0 + 32 + lane < ni;
-#pragma unroll
+								// tile rows = output nodes o0.., 32 inputs each, 16-byte chunks XOR-swizzled by the row
+								const float* stg = acquire();
+								if (computes)
+								{
+									const float* inb = in + (size_t)i0 * GF_ROWS;
+									const float* wrow = stg + t * 32;
+									const int sw = t & 7;
+									auto stepw = [&](int ii, float w) {
+										const float4 a0 = *reinterpret_cast<const float4*>(inb + ii * GF_ROWS);
+										const float4 a1 = *reinterpret_cast<const float4*>(inb + ii * GF_ROWS + 4);
+										acc[0] = fmaf(w, a0.x, acc[0]); acc[1] = fmaf(w, a0.y, acc[1]);
+										acc[2] = fmaf(w, a0.z, acc[2]); acc[3] = fmaf(w, a0.w, acc[3]);
+										acc[4] = fmaf(w, a1.x, acc[4]); acc[5] = fmaf(w, a1.y, acc[5]);
+										acc[6] = fmaf(w, a1.z, acc[6]); acc[7] = fmaf(w, a1.w, acc[7]);
+									};
+									if (ni - i0 >= 32)
+									{
+#pragma unroll 2
+										for (int c = 0; c < 8; ++c)
+										{
+											const float4 w4 = *reinterpret_cast<const float4*>(wrow + ((c ^ sw) << 2));
+											stepw(4 * c, w4.x); stepw(4 * c + 1, w4.y); stepw(4 * c + 2, w4.z); stepw(4 * c + 3, w4.w);
+										}
+									}
+									else
+										for (int ii = 0; ii < ni - i0; ++ii) stepw(ii, wrow[(((ii >> 2) ^ sw) << 2) + (ii & 3)]);
+								}
+								release();
+							}
+						}
+						else
+						{
+							// weight tiles travel global -> registers -> shared memory, the next tile's loads in flight
+							// while the current one is consumed
+							float pre[32];
+							// this thread's part of a tile: column `lane`, rows warp, warp + 8, ... (kmax of them exist)
+							const float* wsrc = W + (size_t)(o0 + warp) * ni + lane;
+							const size_t wstep = (size_t)8 * ni;
+							const int kmax = (no - o0 - warp + 7) >> 3;  // may be <= 0 or > 32
+							const bool computes = o0 + t < no;
+							{
+								const float* q = wsrc;
+								const bool col = lane < ni;
+	#pragma unroll
 								for (int k = 0; k < 32; ++k, q += wstep) pre[k] = (col && k < kmax) ? __ldcg(q) : 0.0f;
 							}
-							const int lim = (ni - i0) < 32 ? (ni - i0) : 32;
-							const float* wrow = Wt + t * 33;
-							const float* inb = in + (size_t)i0 * GF_ROWS;
-							auto step = [&](int ii) {
-								const float w = wrow[ii];
-								const float4 a0 = *reinterpret_cast<const float4*>(inb + ii * GF_ROWS);
-								const float4 a1 = *reinterpret_cast<const float4*>(inb + ii * GF_ROWS + 4);
-								acc[0] = fmaf(w, a0.x, acc[0]); acc[1] = fmaf(w, a0.y, acc[1]);
-								acc[2] = fmaf(w, a0.z, acc[2]); acc[3] = fmaf(w, a0.w, acc[3]);
-								acc[4] = fmaf(w, a1.x, acc[4]); acc[5] = fmaf(w, a1.y, acc[5]);
-								acc[6] = fmaf(w, a1.z, acc[6]); acc[7] = fmaf(w, a1.w, acc[7]);
-							};
-							if (!computes)
+							for (int i0 = 0; i0 < ni; i0 += 32)
 							{
-								// no output node for this thread in this pass: it only helps moving tiles
+								__syncthreads();  // the tile's previous contents (and `in`) are settled
+	#pragma unroll
+								for (int k = 0; k < 32; ++k) Wt[(warp + 8 * k) * 33 + lane] = pre[k];
+								__syncthreads();
+								if (i0 + 32 < ni)
+								{
+									const float* q = wsrc + i0 + 32;
+									const bool col = i0 + 32 + lane < ni;
+	#pragma unroll
+									for (int k = 0; k < 32; ++k, q += wstep) pre[k] = (col && k < kmax) ? __ldcg(q) : 0.0f;
+								}
+								const int lim = (ni - i0) < 32 ? (ni - i0) : 32;
+								const float* wrow = Wt + t * 33;
+								const float* inb = in + (size_t)i0 * GF_ROWS;
+								auto step = [&](int ii) {
+									const float w = wrow[ii];
+									const float4 a0 = *reinterpret_cast<const float4*>(inb + ii * GF_ROWS);
+									const float4 a1 = *reinterpret_cast<const float4*>(inb + ii * GF_ROWS + 4);
+									acc[0] = fmaf(w, a0.x, acc[0]); acc[1] = fmaf(w, a0.y, acc[1]);
+									acc[2] = fmaf(w, a0.z, acc[2]); acc[3] = fmaf(w, a0.w, acc[3]);
+									acc[4] = fmaf(w, a1.x, acc[4]); acc[5] = fmaf(w, a1.y, acc[5]);
+									acc[6] = fmaf(w, a1.z, acc[6]); acc[7] = fmaf(w, a1.w, acc[7]);
+								};
+								if (!computes)
+								{
+									// no output node for this thread in this pass: it only helps moving tiles
+								}
+								else if (lim == 32)
+								{
+									// full tile: a fixed trip count lets the shared-memory loads of several steps overlap
+	#pragma unroll 4
+									for (int ii = 0; ii < 32; ++ii) step(ii);
+								}
+								else
+									for (int ii = 0; ii < lim; ++ii) step(ii);
 							}
-							else if (lim == 32)
-							{
-								// full tile: a fixed trip count lets the shared-memory loads of several steps overlap
-#pragma unroll 16
-								for (int ii = 0; ii < 32; ++ii) step(ii);
-							}
-							else
-								for (int ii = 0; ii < lim; ++ii) step(ii);
 						}
 						const int o = o0 + t;
 						if (o < no)
@@ -319,6 +426,7 @@ __global__ void __launch_bounds__(GF_THREADS, 1) grid_fused_kernel(const __grid_
 #pragma unroll
 							for (int r = 0; r < GF_ROWS; ++r) out[(size_t)o * GF_ROWS + r] = squash_b(acc[r] + b, act, par);
 						}
+						if (use_tma) __syncthreads();  // the next tile step reads these outputs without another barrier
 					}
 				}
 				__syncthreads();
@@ -416,48 +524,82 @@ __global__ void __launch_bounds__(GF_THREADS, 1) grid_fused_kernel(const __grid_
 						float acc[GF_ROWS];
 #pragma unroll
 						for (int r = 0; r < GF_ROWS; ++r) acc[r] = 0.0f;
-						float pre[32];
-						const bool computes = i0 + t < ni;  // also: this thread's column of the tiles exists
-						const float* wsrc = W + i0 + t;     // row o of the tile: wsrc + o * ni
+						if (use_tma)
 						{
-							const float* q = wsrc;
-#pragma unroll
-							for (int k = 0; k < 32; ++k, q += ni) pre[k] = (computes && k < no) ? __ldcg(q) : 0.0f;
+							const bool computes = i0 + t < ni;
+							for (int o0 = 0; o0 < no; o0 += 32)
+							{
+								// tile rows = 32 output nodes o0.., columns = input nodes i0.. (plain layout)
+								const float* stg = acquire();
+								if (computes)
+								{
+									const int lim = (no - o0) < 32 ? (no - o0) : 32;
+									const float* dub = dup + (size_t)o0 * GF_ROWS;
+									auto step = [&](int oo) {
+										const float w = stg[oo * GF_THREADS + t];
+										const float4 d0 = *reinterpret_cast<const float4*>(dub + oo * GF_ROWS);
+										const float4 d1 = *reinterpret_cast<const float4*>(dub + oo * GF_ROWS + 4);
+										acc[0] = fmaf(w, d0.x, acc[0]); acc[1] = fmaf(w, d0.y, acc[1]);
+										acc[2] = fmaf(w, d0.z, acc[2]); acc[3] = fmaf(w, d0.w, acc[3]);
+										acc[4] = fmaf(w, d1.x, acc[4]); acc[5] = fmaf(w, d1.y, acc[5]);
+										acc[6] = fmaf(w, d1.z, acc[6]); acc[7] = fmaf(w, d1.w, acc[7]);
+									};
+									if (lim == 32)
+									{
+#pragma unroll 4
+										for (int oo = 0; oo < 32; ++oo) step(oo);
+									}
+									else
+										for (int oo = 0; oo < lim; ++oo) step(oo);
+								}
+								release();
+							}
 						}
-						for (int o0 = 0; o0 < no; o0 += 32)
+						else
 						{
-							__syncthreads();
-#pragma unroll
-							for (int k = 0; k < 32; ++k) Wt[k * GF_THREADS + t] = pre[k];
-							__syncthreads();
-							if (o0 + 32 < no)
+							float pre[32];
+							const bool computes = i0 + t < ni;  // also: this thread's column of the tiles exists
+							const float* wsrc = W + i0 + t;     // row o of the tile: wsrc + o * ni
 							{
-								const float* q = wsrc + (size_t)(o0 + 32) * ni;
-								const int left = no - (o0 + 32);
-#pragma unroll
-								for (int k = 0; k < 32; ++k, q += ni) pre[k] = (computes && k < left) ? __ldcg(q) : 0.0f;
+								const float* q = wsrc;
+	#pragma unroll
+								for (int k = 0; k < 32; ++k, q += ni) pre[k] = (computes && k < no) ? __ldcg(q) : 0.0f;
 							}
-							const int lim = (no - o0) < 32 ? (no - o0) : 32;
-							const float* dub = dup + (size_t)o0 * GF_ROWS;
-							auto step = [&](int oo) {
-								const float w = Wt[oo * GF_THREADS + t];
-								const float4 d0 = *reinterpret_cast<const float4*>(dub + oo * GF_ROWS);
-								const float4 d1 = *reinterpret_cast<const float4*>(dub + oo * GF_ROWS + 4);
-								acc[0] = fmaf(w, d0.x, acc[0]); acc[1] = fmaf(w, d0.y, acc[1]);
-								acc[2] = fmaf(w, d0.z, acc[2]); acc[3] = fmaf(w, d0.w, acc[3]);
-								acc[4] = fmaf(w, d1.x, acc[4]); acc[5] = fmaf(w, d1.y, acc[5]);
-								acc[6] = fmaf(w, d1.z, acc[6]); acc[7] = fmaf(w, d1.w, acc[7]);
-							};
-							if (!computes)
+							for (int o0 = 0; o0 < no; o0 += 32)
 							{
+								__syncthreads();
+	#pragma unroll
+								for (int k = 0; k < 32; ++k) Wt[k * GF_THREADS + t] = pre[k];
+								__syncthreads();
+								if (o0 + 32 < no)
+								{
+									const float* q = wsrc + (size_t)(o0 + 32) * ni;
+									const int left = no - (o0 + 32);
+	#pragma unroll
+									for (int k = 0; k < 32; ++k, q += ni) pre[k] = (computes && k < left) ? __ldcg(q) : 0.0f;
+								}
+								const int lim = (no - o0) < 32 ? (no - o0) : 32;
+								const float* dub = dup + (size_t)o0 * GF_ROWS;
+								auto step = [&](int oo) {
+									const float w = Wt[oo * GF_THREADS + t];
+									const float4 d0 = *reinterpret_cast<const float4*>(dub + oo * GF_ROWS);
+									const float4 d1 = *reinterpret_cast<const float4*>(dub + oo * GF_ROWS + 4);
+									acc[0] = fmaf(w, d0.x, acc[0]); acc[1] = fmaf(w, d0.y, acc[1]);
+									acc[2] = fmaf(w, d0.z, acc[2]); acc[3] = fmaf(w, d0.w, acc[3]);
+									acc[4] = fmaf(w, d1.x, acc[4]); acc[5] = fmaf(w, d1.y, acc[5]);
+									acc[6] = fmaf(w, d1.z, acc[6]); acc[7] = fmaf(w, d1.w, acc[7]);
+								};
+								if (!computes)
+								{
+								}
+								else if (lim == 32)
+								{
+	#pragma unroll 4
+									for (int oo = 0; oo < 32; ++oo) step(oo);
+								}
+								else
+									for (int oo = 0; oo < lim; ++oo) step(oo);
 							}
-							else if (lim == 32)
-							{
-#pragma unroll 16
-								for (int oo = 0; oo < 32; ++oo) step(oo);
-							}
-							else
-								for (int oo = 0; oo < lim; ++oo) step(oo);
 						}
 						const int i = i0 + t;
 						if (i < ni)
@@ -577,8 +719,9 @@ size_t grid_fused_smem_bytes(const NetView& n)
 {
 	int tot = 0;
 	for (int l = 0; l <= n.H + 1; ++l) tot += n.sizes[l];
-	size_t f = 2 * (size_t)tot * GF_ROWS + GF_WT + (((size_t)(n.H + 1) * (n.mb + 1) + 3) & ~(size_t)3) + GF_TJ * GF_TO + GF_TJ * GF_TI_MAX + GF_TJ + 2 * GF_ROWS;
-	return f * sizeof(float) + 64;
+	size_t f = 2 * (size_t)tot * GF_ROWS + (((size_t)(n.H + 1) * (n.mb + 1) + 3) & ~(size_t)3) + GF_TJ * GF_TO + GF_TJ * GF_TI_MAX + GF_TJ + 2 * GF_ROWS + 3 * GF_SEQ_MAX;
+	// + alignment slack + the ring (its first stage doubles as the register-path tile buffer, GF_WT floats)
+	return f * sizeof(float) + 1024 + (size_t)GF_NS * GF_STAGE + 64;
 }
 
 int grid_fused_total_nodes(const NetView& n)
@@ -586,6 +729,14 @@ int grid_fused_total_nodes(const NetView& n)
 	int tot = 0;
 	for (int l = 0; l <= n.H + 1; ++l) tot += n.sizes[l];
 	return tot;
+}
+
+int grid_fused_group_tiles(const NetView& n)
+{
+	int steps = 0;
+	for (int l = 0; l <= n.H; ++l) steps += ((n.sizes[l + 1] + GF_THREADS - 1) / GF_THREADS) * ((n.sizes[l] + 31) / 32);
+	for (int L = n.H + 1; L >= 2; --L) steps += ((n.sizes[L - 1] + GF_THREADS - 1) / GF_THREADS) * ((n.sizes[L] + 31) / 32);
+	return steps;
 }
 
 int grid_fused_pick_nc(const NetView& n, int ctas)

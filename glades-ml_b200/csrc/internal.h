@@ -149,10 +149,17 @@ struct GridFusedArgs
 	int* confusion;      // [n_out][n_out]: the last epoch's counts are ADDED (the caller clears)
 	float* last_out;     // [n_out] or NULL
 	int* flags;
+	// Device array of 128-byte tensor maps, two per weight layer -- [2l]: W_l as [n_out][n_in] with boxes of
+	// 256 rows x 32 columns, 128-byte swizzle (forward tiles); [2l+1]: boxes of 32 rows x 256 columns, plain
+	// (hidden-delta tiles) -- or NULL: the weights' layout allows no tensor maps (rows not multiples of 16
+	// bytes) and the tiles travel through registers instead.
+	const void* tma;
 	unsigned long long* timing;  // optional diagnostics: ns spent in [phase 1, barrier, phase 2, barrier] by CTA 0
 };
 size_t grid_fused_smem_bytes(const NetView& n);
 int grid_fused_total_nodes(const NetView& n);
+// weight tiles one sample group walks through (the ring path needs <= 512)
+int grid_fused_group_tiles(const NetView& n);
 // smallest tile width whose tile count does not exceed `ctas` (else 4)
 int grid_fused_pick_nc(const NetView& n, int ctas);
 cudaError_t launch_grid_fused(const GridFusedArgs& a, cudaStream_t s);

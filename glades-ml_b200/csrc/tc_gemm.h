@@ -22,6 +22,11 @@ cudaError_t launch_gemm_tc(const GemmArgs& g, const float* A_lo, const float* B_
 // boxes, as the epilogue's bulk stores use it; for the per-owner bands of a data-parallel gradient.
 bool tc_make_store_map(void* out128, const float* base, long long rows, long long cols, long long ld);
 
+// General 2-D map over a row-major [rows][cols] fp32 matrix (row pitch ld floats, a multiple of 4; base
+// 16-byte aligned): boxes of box_rows x box_cols, 128-byte swizzle (box_cols must then be 32) or none.
+bool tc_make_map2d(void* out128, const float* base, long long rows, long long cols, long long ld, int box_cols, int box_rows,
+                   int swizzle128);
+
 // lo[i] = tf32_round(src[i] - trunc_tf32(src[i])); with rowscale: first dst_scaled[i] = src[i] *
 // rowscale[i / ld] is formed (and stored), and lo is taken from that.
 cudaError_t launch_split_lo(const float* src, float* lo, long long count, cudaStream_t s);
