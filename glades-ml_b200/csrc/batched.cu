@@ -117,36 +117,77 @@ __global__ void __launch_bounds__(256) gemm_skinny_kernel(const GemmArgs g)
 	const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, wpb = blockDim.x >> 5;
 	const float bias = (EPI == EPI_FORWARD && g.bias_ptr) ? *g.bias_ptr : 0.0f;
 	const int K4 = K >> 2;
-	for (long long m = (long long)blockIdx.x * wpb + warp; m < g.M; m += (long long)gridDim.x * wpb)
+	// a warp takes SK_ROWS consecutive rows at a time: every weight chunk read from shared memory serves
+	// all of them, and the rows' independent 16-byte loads keep HBM busy
+	constexpr int SK_ROWS = 4;
+	const long long groups = (g.M + SK_ROWS - 1) / SK_ROWS;
+	for (long long gi = (long long)blockIdx.x * wpb + warp; gi < groups; gi += (long long)gridDim.x * wpb)
 	{
-		const float4* arow = reinterpret_cast<const float4*>(g.A + m * g.a_sm);
-		float acc[SK_NMAX];
+		const long long m0 = gi * SK_ROWS;
+		const float4* arow[SK_ROWS];
 #pragma unroll
-		for (int n = 0; n < SK_NMAX; ++n) acc[n] = 0.0f;
-		for (int k4 = lane; k4 < K4; k4 += 32)
+		for (int r = 0; r < SK_ROWS; ++r)
 		{
-			const float4 a = arow[k4];
+			const long long m = (m0 + r < g.M) ? m0 + r : g.M - 1;  // the tail repeats the last row (not stored)
+			arow[r] = reinterpret_cast<const float4*>(g.A + m * g.a_sm);
+		}
+		float acc[SK_ROWS][SK_NMAX];
+#pragma unroll
+		for (int r = 0; r < SK_ROWS; ++r)
+#pragma unroll
+			for (int n = 0; n < SK_NMAX; ++n) acc[r][n] = 0.0f;
+		// two 16-byte chunks per row and lane in flight (8 loads) before the first is consumed
+		for (int k4 = lane; k4 < K4; k4 += 64)
+		{
+			const int k4b = k4 + 32;
+			const bool two = k4b < K4;
+			float4 a[SK_ROWS], b[SK_ROWS];
+#pragma unroll
+			for (int r = 0; r < SK_ROWS; ++r) a[r] = arow[r][k4];
+#pragma unroll
+			for (int r = 0; r < SK_ROWS; ++r) b[r] = two ? arow[r][k4b] : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
 			for (int n = 0; n < SK_NMAX; ++n)
 				if (n < N)
 				{
 					const float4 w = reinterpret_cast<const float4*>(sW + n * K)[k4];
-					acc[n] = fmaf(a.x, w.x, fmaf(a.y, w.y, fmaf(a.z, w.z, fmaf(a.w, w.w, acc[n]))));
+#pragma unroll
+					for (int r = 0; r < SK_ROWS; ++r)
+						acc[r][n] = fmaf(a[r].x, w.x, fmaf(a[r].y, w.y, fmaf(a[r].z, w.z, fmaf(a[r].w, w.w, acc[r][n]))));
 				}
+			if (two)
+			{
+#pragma unroll
+				for (int n = 0; n < SK_NMAX; ++n)
+					if (n < N)
+					{
+						const float4 w = reinterpret_cast<const float4*>(sW + n * K)[k4b];
+#pragma unroll
+						for (int r = 0; r < SK_ROWS; ++r)
+							acc[r][n] = fmaf(b[r].x, w.x, fmaf(b[r].y, w.y, fmaf(b[r].z, w.z, fmaf(b[r].w, w.w, acc[r][n]))));
+					}
+			}
 		}
 #pragma unroll
-		for (int n = 0; n < SK_NMAX; ++n)
-			if (n < N) acc[n] = warp_sum(acc[n]);
+		for (int r = 0; r < SK_ROWS; ++r)
+#pragma unroll
+			for (int n = 0; n < SK_NMAX; ++n)
+				if (n < N) acc[r][n] = warp_sum(acc[r][n]);
 		if (lane == 0)
 		{
 #pragma unroll
-			for (int n = 0; n < SK_NMAX; ++n)
-				if (n < N)
-				{
-					float v = acc[n];
-					if (EPI == EPI_FORWARD) v = squash_b(v + bias, g.act, g.par);
-					g.C[m * g.ldc + n] = v;
-				}
+			for (int r = 0; r < SK_ROWS; ++r)
+			{
+				if (m0 + r >= g.M) break;
+#pragma unroll
+				for (int n = 0; n < SK_NMAX; ++n)
+					if (n < N)
+					{
+						float v = acc[r][n];
+						if (EPI == EPI_FORWARD) v = squash_b(v + bias, g.act, g.par);
+						g.C[(m0 + r) * g.ldc + n] = v;
+					}
+			}
 		}
 	}
 }
@@ -162,8 +203,9 @@ cudaError_t launch_gemm_ffma(const GemmArgs& g, cudaStream_t s)
 	if (skinny_ok(g))
 	{
 		const size_t bytes = (size_t)g.N * g.K * sizeof(float);
-		long long blocks = (g.M + 7) / 8;
+		long long blocks = (g.M + 31) / 32;  // 8 warps x 4 rows per CTA pass
 		if (blocks > 148 * 4) blocks = 148 * 4;
+		if (blocks < 1) blocks = 1;
 		cudaError_t e;
 		if (g.epi == EPI_FORWARD)
 		{
