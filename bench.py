@@ -659,6 +659,9 @@ def main():
             "note": "achieved counts algorithmic fp32 flop (2*M*N*K per product); the 3xTF32 mode issues 3 TF32 MMAs per "
                     "product term, so the tensor pipe runs at 3x this figure and the mode's own ceiling is peak/6",
             "frac_of_3xtf32_ceiling": achieved / (peaks["tensor"] / 6.0),
+            # cuBLAS TF32 GEMM measured on this pool's B200s the way the bf16 peak was (8192^3, best of 10,
+            # CUDA events): 745.6 TFLOP/s burst, 591.7 over 300 in a row; a 3xTF32 product can reach a third
+            "frac_of_cublas_tf32_third": achieved / (745.6 / 3.0),
             "share_of_step_ms": dom["ms"] / ms if ms > 0 else None,
         }
 
