@@ -1920,6 +1920,40 @@ static int dp_push_setup(gl_net* n)
 	// nobody writes into a peer before every rank has zeroed and mapped everything
 	NC(g_nccl.AllReduce(dAgree, dAgree, 1, NCCL_INT32, NCCL_SUM, n->comm, n->stream));
 	CU(cudaStreamSynchronize(n->stream));
+	// Handshake over the mapped memory itself: every rank stores a pattern into its slot at every owner and
+	// raises a flag there; every rank then waits (a few seconds at most) for all flags and checks all
+	// patterns.  Only if that works on EVERY rank does the handle use the exchange over peer memory.
+	{
+		DpPeers heads, fl;
+		for (int r = 0; r < DP_MAX_WORLD; ++r)
+		{
+			fl.p[r] = n->dpPeerArena[r];
+			heads.p[r] = (r < W) ? static_cast<void*>(reinterpret_cast<float*>(static_cast<char*>(n->dpPeerArena[r]) + DP_FLAG_BYTES) +
+			                                          (int64_t)n->rank * off)
+			                     : nullptr;
+		}
+		int* dStatus = dAgree + 1;
+		int zero = 0;
+		CU(cudaMemcpy(dStatus, &zero, sizeof zero, cudaMemcpyHostToDevice));
+		CU(launch_dp_hello_write(heads, fl, W, n->rank, n->stream));
+		CU(launch_dp_wait(n->dpArena, 0, 0, 0, DP_WORD_HELLO, W, 1u, dStatus, 1, n->stream, 8000000000ll));
+		CU(launch_dp_hello_check(reinterpret_cast<const float*>(n->dpArena + DP_FLAG_BYTES), off, W, dStatus, 2, n->stream));
+		CU(cudaStreamSynchronize(n->stream));
+		int status = 0;
+		CU(cudaMemcpy(&status, dStatus, sizeof status, cudaMemcpyDeviceToHost));
+		failed = status != 0;
+		CU(cudaMemcpy(dAgree, &failed, sizeof failed, cudaMemcpyHostToDevice));
+		NC(g_nccl.AllReduce(dAgree, dAgree, 1, NCCL_INT32, NCCL_SUM, n->comm, n->stream));
+		CU(cudaStreamSynchronize(n->stream));
+		CU(cudaMemcpy(&failed, dAgree, sizeof failed, cudaMemcpyDeviceToHost));
+		if (failed)
+		{
+			dp_push_release(n);
+			cudaFree(dRec);
+			return fail(GL_ERR_COMM, "the handshake over peer memory failed on %d rank(s) (this rank: %s); staying on the NCCL all-reduce",
+			            failed, status == 0 ? "ok" : (status == 1 ? "a flag did not arrive" : "a pattern did not arrive"));
+		}
+	}
 	cudaFree(dRec);
 	n->dpPush = true;
 	n->dpStep = 0;

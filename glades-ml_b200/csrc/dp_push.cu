@@ -39,7 +39,7 @@ __global__ void dp_signal_kernel(DpPeers flags, int world, int word, unsigned va
 // Thread t waits until its flag word has reached `value`.  Words: groups x per_group starting at w0
 // with a stride of DP_MAX_WORLD words per group, then `extra_n` consecutive words from extra0.
 __global__ void dp_wait_kernel(const unsigned* flags, int w0, int groups, int per_group, int extra0, int extra_n,
-                               unsigned value, int* status, int code)
+                               unsigned value, int* status, int code, long long max_cycles)
 {
 	const int t = threadIdx.x;
 	int word = -1;
@@ -53,7 +53,7 @@ __global__ void dp_wait_kernel(const unsigned* flags, int w0, int groups, int pe
 		while ((int)(ld_flag(flags + word) - value) < 0)
 		{
 			if (*reinterpret_cast<volatile int*>(status) != 0) break;
-			if (clock64() - t0 > DP_WAIT_CYCLES)
+			if (clock64() - t0 > max_cycles)
 			{
 				atomicCAS(status, 0, code);
 				break;
@@ -62,6 +62,24 @@ __global__ void dp_wait_kernel(const unsigned* flags, int w0, int groups, int pe
 		}
 	}
 	__threadfence_system();
+}
+
+__global__ void dp_hello_write_kernel(DpPeers slot_heads, DpPeers flags, int world, int self)
+{
+	const int r = threadIdx.x;
+	if (r >= world) return;
+	float* dst = reinterpret_cast<float*>(slot_heads.p[r]);
+	for (int k = 0; k < 16; ++k) dst[k] = (float)((self + 1) * 1000 + k);
+	__threadfence_system();
+	st_flag(reinterpret_cast<unsigned*>(flags.p[r]) + DP_WORD_HELLO + self, 1u);
+}
+
+__global__ void dp_hello_check_kernel(const float* slots, long long slot_stride, int world, int* status, int code)
+{
+	const int src = threadIdx.x >> 4, k = threadIdx.x & 15;
+	if (src >= world) return;
+	const float v = *reinterpret_cast<const volatile float*>(slots + (long long)src * slot_stride + k);
+	if (v != (float)((src + 1) * 1000 + k)) atomicCAS(status, 0, code);
 }
 
 // Rows [o * band, ...) of the local gradient matrix G [n_out][n_in] -> slot of this rank at owner o.
@@ -205,13 +223,25 @@ cudaError_t launch_dp_signal(const DpPeers& flags, int world, int word, unsigned
 	return cudaGetLastError();
 }
 
+cudaError_t launch_dp_hello_write(const DpPeers& slot_heads, const DpPeers& flags, int world, int self, cudaStream_t s)
+{
+	dp_hello_write_kernel<<<1, 32, 0, s>>>(slot_heads, flags, world, self);
+	return cudaGetLastError();
+}
+
+cudaError_t launch_dp_hello_check(const float* slots, long long slot_stride, int world, int* status, int code, cudaStream_t s)
+{
+	dp_hello_check_kernel<<<1, 16 * DP_MAX_WORLD, 0, s>>>(slots, slot_stride, world, status, code);
+	return cudaGetLastError();
+}
+
 cudaError_t launch_dp_wait(const void* arena, int w0, int groups, int per_group, int extra0, int extra_n, unsigned value,
-                           int* status, int code, cudaStream_t s)
+                           int* status, int code, cudaStream_t s, long long max_cycles)
 {
 	const int need = groups * per_group + extra_n;
 	if (need < 1 || need > 1024) return cudaErrorInvalidValue;
 	dp_wait_kernel<<<1, ((need + 31) / 32) * 32, 0, s>>>(reinterpret_cast<const unsigned*>(arena), w0, groups, per_group, extra0,
-	                                                    extra_n, value, status, code);
+	                                                    extra_n, value, status, code, max_cycles > 0 ? max_cycles : DP_WAIT_CYCLES);
 	return cudaGetLastError();
 }
 

@@ -172,6 +172,7 @@ cudaError_t launch_grid_fused(const GridFusedArgs& a, cudaStream_t s);
 //   DP_WORD_WFLAG + l * DP_MAX_WORLD + owner  owner's band of the new layer-l weights has landed here
 //   DP_WORD_SFLAG + src                       src's bias / loss record has landed here
 //   DP_WORD_BAD + owner                       owner saw a non-finite weight (sticky)
+//   DP_WORD_HELLO + src                       set-up handshake: src's test pattern has landed in its slot here
 enum
 {
 	DP_MAX_WORLD = 8,
@@ -179,6 +180,7 @@ enum
 	DP_WORD_WFLAG = GL_MAX_WEIGHT_LAYERS * DP_MAX_WORLD,
 	DP_WORD_SFLAG = 2 * GL_MAX_WEIGHT_LAYERS * DP_MAX_WORLD,
 	DP_WORD_BAD = DP_WORD_SFLAG + DP_MAX_WORLD,
+	DP_WORD_HELLO = DP_WORD_BAD + DP_MAX_WORLD,  // + src: set-up handshake (src's test pattern has landed here)
 	DP_SMALL_OFFSET = 2048,  // bytes: records [parity 2][rank DP_MAX_WORLD][DP_SMALL_BYTES]
 	DP_SMALL_BYTES = 128,    // GL_MAX_WEIGHT_LAYERS floats (bias sums) + 2 doubles (cost, accuracy sums)
 	DP_FLAG_BYTES = 4096
@@ -186,8 +188,14 @@ enum
 struct DpPeers { void* p[DP_MAX_WORLD]; };  // one pointer per rank (this rank's own entry is a local pointer)
 
 cudaError_t launch_dp_signal(const DpPeers& flags, int world, int word, unsigned value, cudaStream_t s);
+// max_cycles <= 0: the default bound (about 10 s)
 cudaError_t launch_dp_wait(const void* arena, int w0, int groups, int per_group, int extra0, int extra_n, unsigned value,
-                           int* status, int code, cudaStream_t s);
+                           int* status, int code, cudaStream_t s, long long max_cycles = 0);
+// Set-up handshake.  hello_write: thread r < world stores the pattern (self + 1) * 1000 + k, k < 16, at the head of
+// this rank's slot in rank r's arena, then raises DP_WORD_HELLO + self there.  hello_check (after a wait on
+// those words): every source's pattern must be in its slot here, else *status = code.
+cudaError_t launch_dp_hello_write(const DpPeers& slot_heads, const DpPeers& flags, int world, int self, cudaStream_t s);
+cudaError_t launch_dp_hello_check(const float* slots, long long slot_stride, int world, int* status, int code, cudaStream_t s);
 cudaError_t launch_dp_push_bands(const float* G, int n_out, int n_in, int band, const DpPeers& slot, cudaStream_t s);
 cudaError_t launch_dp_reduce_update(const float* part, long long src_stride, int world, long long count, float inv_mb,
                                     long long wbase, const DpPeers& W, int self, const DpPeers& flags, int blocks, cudaStream_t s);
