@@ -338,14 +338,14 @@ def cpu_baseline_for(g, name, w):
         v, dt = cpu_reference_baseline(name, rows, procs)
         head = " (per-node sigmoid head: the reference has no softmax)" if "softmax" in w["acts"] else ""
         return v, procs, "reference", ("%d rows in each of %d single-threaded process(es) of the compiled reference%s, "
-                                       "%.1f s" % (rows, procs, head, dt))
+                                       "%.1f s" % (rows, procs, head, dt)), dt
     train = w["kind"] == "train"
     rows = 256 if train else 2048
     v, cores, dt = cpu_port_baseline(g, w, rows)
     note = "; the compiled reference needs ~669 s per training row at this shape (forward 2.6 s, backward 666 s)" \
         if name == "wide_mlp" else ""
     return v, cores, "port", ("%d rows of one window, CPU restatement of the same batched arithmetic (double "
-                              "accumulation, OpenMP), %.1f s%s" % (rows, dt, note))
+                              "accumulation, OpenMP), %.1f s%s" % (rows, dt, note)), dt
 
 
 def run_reference_arm(args, g, w, rank, world):
@@ -356,16 +356,17 @@ def run_reference_arm(args, g, w, rank, world):
     so in `cpu_baseline.kind` / `.sample`."""
     if rank != 0:
         return
-    vals = []
+    vals, secs = [], []
     for _ in range(max(1, min(args.steps, 2))):
-        v, cores, kind, sample = cpu_baseline_for(g, args.workload, w)
+        v, cores, kind, sample, dt = cpu_baseline_for(g, args.workload, w)
         vals.append(v)
+        secs.append(dt)
     value = float(np.mean(vals))
     unit = "samples/s" if w["kind"] == "train" else "rows/s"
     line = {
         "impl": "reference", "metric": "train_samples_per_s" if w["kind"] == "train" else "infer_rows_per_s",
         "value": value, "unit": unit, "n_gpus": world, "steps": len(vals),
-        "warmup": 0, "ms_per_step": None, "higher_is_better": True, "scaling": "weak",
+        "warmup": 0, "ms_per_step": 1000.0 * float(np.mean(secs)), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": args.workload, "sizes": w["sizes"]},
         "cpu_baseline": {"value": value, "unit": unit, "cores": cores, "kind": kind, "sample": sample},
@@ -669,7 +670,7 @@ def main():
     if rank == 0:
         cpu = None
         if not args.no_cpu_baseline and world == 1:
-            v, cores, kind, sample = cpu_baseline_for(g, args.workload, w)
+            v, cores, kind, sample, _ = cpu_baseline_for(g, args.workload, w)
             cpu = {"value": v, "unit": "samples/s" if train else "rows/s", "cores": cores, "kind": kind, "sample": sample}
         line = {
             "metric": "train_samples_per_s" if train else "infer_rows_per_s",

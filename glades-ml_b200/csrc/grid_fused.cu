@@ -169,6 +169,45 @@ __device__ __forceinline__ void gf_grad_tile(const GridFusedArgs& a, int l, int 
 }
 
 
+// Phase 2 for a layer with at most GF_NARROW output nodes (the usual regression head): one work item
+// per 256 input columns, thread = one column of every output row, straight from the window scratch
+// (the activations' reads are coalesced, the few deltas per row are broadcast loads).
+constexpr int GF_NARROW = 4;
+__device__ __forceinline__ void gf_grad_narrow(const GridFusedArgs& a, int l, int i0, int len, int tot, int off_in, int off_out,
+                                               const float* ckl, float inv_len, int& bad)
+{
+	const NetView& n = a.net;
+	const int ni = n.sizes[l], no = n.sizes[l + 1];
+	const int i = i0 + (int)threadIdx.x;
+	if (i >= ni) return;
+	const float lr = n.lr[l], w1 = n.wd1[l] * lr, w2 = n.wd2[l] * lr;
+	float g[GF_NARROW];
+#pragma unroll
+	for (int o = 0; o < GF_NARROW; ++o) g[o] = 0.0f;
+	const float* ap = a.actbuf + off_in + i;
+	const float* dp = a.delbuf + off_out;
+#pragma unroll 4
+	for (int j = 0; j < len; ++j)
+	{
+		const float av = __ldcg(ap + (size_t)j * tot);
+		const float c = ckl[len - j];
+		const float dec = fmaf(w1, fabsf(av), w2 * av);
+#pragma unroll
+		for (int o = 0; o < GF_NARROW; ++o)
+			if (o < no) g[o] = fmaf(c, fmaf(lr * __ldcg(dp + (size_t)j * tot + o), av, dec), g[o]);
+	}
+#pragma unroll
+	for (int o = 0; o < GF_NARROW; ++o)
+		if (o < no)
+		{
+			float* wp = n.W[l] + (size_t)o * ni + i;
+			const float w = __ldcg(wp) - g[o] * inv_len;
+			if (!isfinite(w)) bad = 1;
+			*wp = w;
+		}
+}
+
+
 __global__ void __launch_bounds__(GF_THREADS, 1) grid_fused_kernel(const __grid_constant__ GridFusedArgs a)
 {
 	extern __shared__ __align__(16) float sm[];
@@ -269,7 +308,8 @@ __global__ void __launch_bounds__(GF_THREADS, 1) grid_fused_kernel(const __grid_
 	for (int l = 0; l <= H; ++l)
 	{
 		tile_off[l] = tiles;
-		tiles += ((n.sizes[l + 1] + GF_TO - 1) / GF_TO) * ((n.sizes[l] + tile_i - 1) / tile_i);
+		tiles += (n.sizes[l + 1] <= GF_NARROW) ? (n.sizes[l] + GF_THREADS - 1) / GF_THREADS
+		                                       : ((n.sizes[l + 1] + GF_TO - 1) / GF_TO) * ((n.sizes[l] + tile_i - 1) / tile_i);
 	}
 	tile_off[H + 1] = tiles;
 
@@ -659,7 +699,9 @@ __global__ void __launch_bounds__(GF_THREADS, 1) grid_fused_kernel(const __grid_
 				const int tl = tile - tile_off[l];
 				const int o0 = (tl / tiles_i) * GF_TO, i0 = (tl % tiles_i) * tile_i;
 				const float* ckl = ck + (size_t)l * (mb + 1);
-				if (a.nc == 2)
+				if (n.sizes[l + 1] <= GF_NARROW)
+					gf_grad_narrow(a, l, tl * GF_THREADS, len, tot, node_off[l], node_off[l + 1], ckl, inv_len, bad);
+				else if (a.nc == 2)
 					gf_grad_tile<2>(a, l, o0, i0, len, tot, node_off[l], node_off[l + 1], Dt, At, Ct, ckl, inv_len, bad);
 				else
 					gf_grad_tile<4>(a, l, o0, i0, len, tot, node_off[l], node_off[l + 1], Dt, At, Ct, ckl, inv_len, bad);
@@ -744,7 +786,9 @@ int grid_fused_pick_nc(const NetView& n, int ctas)
 	for (int nc = 2; nc <= 4; nc *= 2)
 	{
 		int tiles = 0;
-		for (int l = 0; l <= n.H; ++l) tiles += ((n.sizes[l + 1] + GF_TO - 1) / GF_TO) * ((n.sizes[l] + 16 * nc - 1) / (16 * nc));
+		for (int l = 0; l <= n.H; ++l)
+			tiles += (n.sizes[l + 1] <= GF_NARROW) ? (n.sizes[l] + GF_THREADS - 1) / GF_THREADS
+			                                       : ((n.sizes[l + 1] + GF_TO - 1) / GF_TO) * ((n.sizes[l] + 16 * nc - 1) / (16 * nc));
 		if (tiles <= ctas) return nc;
 	}
 	return 4;
