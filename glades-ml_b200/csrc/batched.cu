@@ -107,11 +107,14 @@ __global__ void __launch_bounds__(FB_T) gemm_ffma_kernel(const GemmArgs g)
 // N partial sums are combined by warp shuffles.  Bound by reading A once from HBM.
 constexpr int SK_NMAX = 16;
 
-template <int EPI>
+// NN = the layer's width as a compile-time constant: the accumulators are registers and the inner loops carry
+// no per-column predicates (the first version's 16-way predicated body stalled on instruction fetch).
+template <int EPI, int NN>
 __global__ void __launch_bounds__(256) gemm_skinny_kernel(const GemmArgs g)
 {
 	extern __shared__ __align__(16) float sW[];  // [N][K]
-	const int K = g.K, N = g.N;
+	const int K = g.K;
+	constexpr int N = NN;
 	for (int e = threadIdx.x; e < N * K; e += blockDim.x) sW[e] = g.B[(long long)(e / K) * g.b_sn + (e % K)];
 	__syncthreads();
 	const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, wpb = blockDim.x >> 5;
@@ -131,11 +134,11 @@ __global__ void __launch_bounds__(256) gemm_skinny_kernel(const GemmArgs g)
 			const long long m = (m0 + r < g.M) ? m0 + r : g.M - 1;  // the tail repeats the last row (not stored)
 			arow[r] = reinterpret_cast<const float4*>(g.A + m * g.a_sm);
 		}
-		float acc[SK_ROWS][SK_NMAX];
+		float acc[SK_ROWS][NN];
 #pragma unroll
 		for (int r = 0; r < SK_ROWS; ++r)
 #pragma unroll
-			for (int n = 0; n < SK_NMAX; ++n) acc[r][n] = 0.0f;
+			for (int n = 0; n < NN; ++n) acc[r][n] = 0.0f;
 		// two 16-byte chunks per row and lane in flight (8 loads) before the first is consumed
 		for (int k4 = lane; k4 < K4; k4 += 64)
 		{
@@ -147,7 +150,7 @@ __global__ void __launch_bounds__(256) gemm_skinny_kernel(const GemmArgs g)
 #pragma unroll
 			for (int r = 0; r < SK_ROWS; ++r) b[r] = two ? arow[r][k4b] : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-			for (int n = 0; n < SK_NMAX; ++n)
+			for (int n = 0; n < NN; ++n)
 				if (n < N)
 				{
 					const float4 w = reinterpret_cast<const float4*>(sW + n * K)[k4];
@@ -158,7 +161,7 @@ __global__ void __launch_bounds__(256) gemm_skinny_kernel(const GemmArgs g)
 			if (two)
 			{
 #pragma unroll
-				for (int n = 0; n < SK_NMAX; ++n)
+				for (int n = 0; n < NN; ++n)
 					if (n < N)
 					{
 						const float4 w = reinterpret_cast<const float4*>(sW + n * K)[k4b];
@@ -171,7 +174,7 @@ __global__ void __launch_bounds__(256) gemm_skinny_kernel(const GemmArgs g)
 #pragma unroll
 		for (int r = 0; r < SK_ROWS; ++r)
 #pragma unroll
-			for (int n = 0; n < SK_NMAX; ++n)
+			for (int n = 0; n < NN; ++n)
 				if (n < N) acc[r][n] = warp_sum(acc[r][n]);
 		if (lane == 0)
 		{
@@ -180,7 +183,7 @@ __global__ void __launch_bounds__(256) gemm_skinny_kernel(const GemmArgs g)
 			{
 				if (m0 + r >= g.M) break;
 #pragma unroll
-				for (int n = 0; n < SK_NMAX; ++n)
+				for (int n = 0; n < NN; ++n)
 					if (n < N)
 					{
 						float v = acc[r][n];
@@ -206,19 +209,29 @@ cudaError_t launch_gemm_ffma(const GemmArgs& g, cudaStream_t s)
 		long long blocks = (g.M + 31) / 32;  // 8 warps x 4 rows per CTA pass
 		if (blocks > 148 * 4) blocks = 148 * 4;
 		if (blocks < 1) blocks = 1;
-		cudaError_t e;
-		if (g.epi == EPI_FORWARD)
+		cudaError_t e = cudaErrorInvalidValue;
+#define GL_SKINNY_CASE(NV)                                                                                                       \
+	case NV:                                                                                                                     \
+		if (g.epi == EPI_FORWARD)                                                                                                \
+		{                                                                                                                        \
+			e = cudaFuncSetAttribute(gemm_skinny_kernel<EPI_FORWARD, NV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes); \
+			if (e == cudaSuccess) gemm_skinny_kernel<EPI_FORWARD, NV><<<(unsigned)blocks, 256, bytes, s>>>(g);                    \
+		}                                                                                                                        \
+		else                                                                                                                     \
+		{                                                                                                                        \
+			e = cudaFuncSetAttribute(gemm_skinny_kernel<EPI_NONE, NV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);  \
+			if (e == cudaSuccess) gemm_skinny_kernel<EPI_NONE, NV><<<(unsigned)blocks, 256, bytes, s>>>(g);                       \
+		}                                                                                                                        \
+		break;
+		switch (g.N)
 		{
-			e = cudaFuncSetAttribute(gemm_skinny_kernel<EPI_FORWARD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
-			if (e != cudaSuccess) return e;
-			gemm_skinny_kernel<EPI_FORWARD><<<(unsigned)blocks, 256, bytes, s>>>(g);
+			GL_SKINNY_CASE(1) GL_SKINNY_CASE(2) GL_SKINNY_CASE(3) GL_SKINNY_CASE(4) GL_SKINNY_CASE(5) GL_SKINNY_CASE(6)
+			GL_SKINNY_CASE(7) GL_SKINNY_CASE(8) GL_SKINNY_CASE(9) GL_SKINNY_CASE(10) GL_SKINNY_CASE(11) GL_SKINNY_CASE(12)
+			GL_SKINNY_CASE(13) GL_SKINNY_CASE(14) GL_SKINNY_CASE(15) GL_SKINNY_CASE(16)
+		default: break;
 		}
-		else
-		{
-			e = cudaFuncSetAttribute(gemm_skinny_kernel<EPI_NONE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
-			if (e != cudaSuccess) return e;
-			gemm_skinny_kernel<EPI_NONE><<<(unsigned)blocks, 256, bytes, s>>>(g);
-		}
+#undef GL_SKINNY_CASE
+		if (e != cudaSuccess) return e;
 		return cudaGetLastError();
 	}
 	dim3 grid((g.N + FB_N - 1) / FB_N, (g.M + FB_M - 1) / FB_M);

@@ -170,43 +170,58 @@ __device__ __forceinline__ void gf_grad_tile(const GridFusedArgs& a, int l, int 
 
 
 // Phase 2 for a layer with at most GF_NARROW output nodes (the usual regression head): one work item
-// per 256 input columns, thread = one column of every output row, straight from the window scratch
-// (the activations' reads are coalesced, the few deltas per row are broadcast loads).
+// per GF_NCOLS input columns; thread = one column and one quarter of the window's rows, straight from
+// the window scratch (coalesced activation reads, broadcast delta reads, several rows' loads in
+// flight); the four quarters are added in fixed order through shared memory.
 constexpr int GF_NARROW = 4;
+constexpr int GF_NCOLS = 64;
 __device__ __forceinline__ void gf_grad_narrow(const GridFusedArgs& a, int l, int i0, int len, int tot, int off_in, int off_out,
-                                               const float* ckl, float inv_len, int& bad)
+                                               const float* ckl, float inv_len, float* red, int& bad)
 {
 	const NetView& n = a.net;
 	const int ni = n.sizes[l], no = n.sizes[l + 1];
-	const int i = i0 + (int)threadIdx.x;
-	if (i >= ni) return;
+	const int col = (int)threadIdx.x & (GF_NCOLS - 1), part = (int)threadIdx.x / GF_NCOLS;  // 4 parts
+	const int i = i0 + col;
 	const float lr = n.lr[l], w1 = n.wd1[l] * lr, w2 = n.wd2[l] * lr;
 	float g[GF_NARROW];
 #pragma unroll
 	for (int o = 0; o < GF_NARROW; ++o) g[o] = 0.0f;
-	const float* ap = a.actbuf + off_in + i;
-	const float* dp = a.delbuf + off_out;
-#pragma unroll 4
-	for (int j = 0; j < len; ++j)
+	if (i < ni)
 	{
-		const float av = __ldcg(ap + (size_t)j * tot);
-		const float c = ckl[len - j];
-		const float dec = fmaf(w1, fabsf(av), w2 * av);
+		const int q = (len + 3) / 4;
+		const int j_lo = part * q, j_hi = (j_lo + q) < len ? (j_lo + q) : len;
+		const float* ap = a.actbuf + off_in + i;
+		const float* dp = a.delbuf + off_out;
+#pragma unroll 8
+		for (int j = j_lo; j < j_hi; ++j)
+		{
+			const float av = __ldcg(ap + (size_t)j * tot);
+			const float c = ckl[len - j];
+			const float dec = fmaf(w1, fabsf(av), w2 * av);
+#pragma unroll
+			for (int o = 0; o < GF_NARROW; ++o)
+				if (o < no) g[o] = fmaf(c, fmaf(lr * __ldcg(dp + (size_t)j * tot + o), av, dec), g[o]);
+		}
+	}
+	__syncthreads();  // `red` may still be read as a tile buffer by a previous work item
+#pragma unroll
+	for (int o = 0; o < GF_NARROW; ++o) red[(part * GF_NCOLS + col) * GF_NARROW + o] = g[o];
+	__syncthreads();
+	if (part == 0 && i < ni)
+	{
 #pragma unroll
 		for (int o = 0; o < GF_NARROW; ++o)
-			if (o < no) g[o] = fmaf(c, fmaf(lr * __ldcg(dp + (size_t)j * tot + o), av, dec), g[o]);
+			if (o < no)
+			{
+				float sum = red[col * GF_NARROW + o];
+				for (int p2 = 1; p2 < GF_THREADS / GF_NCOLS; ++p2) sum += red[(p2 * GF_NCOLS + col) * GF_NARROW + o];
+				float* wp = n.W[l] + (size_t)o * ni + i;
+				const float w = __ldcg(wp) - sum * inv_len;
+				if (!isfinite(w)) bad = 1;
+				*wp = w;
+			}
 	}
-#pragma unroll
-	for (int o = 0; o < GF_NARROW; ++o)
-		if (o < no)
-		{
-			float* wp = n.W[l] + (size_t)o * ni + i;
-			const float w = __ldcg(wp) - g[o] * inv_len;
-			if (!isfinite(w)) bad = 1;
-			*wp = w;
-		}
 }
-
 
 __global__ void __launch_bounds__(GF_THREADS, 1) grid_fused_kernel(const __grid_constant__ GridFusedArgs a)
 {
@@ -308,7 +323,7 @@ __global__ void __launch_bounds__(GF_THREADS, 1) grid_fused_kernel(const __grid_
 	for (int l = 0; l <= H; ++l)
 	{
 		tile_off[l] = tiles;
-		tiles += (n.sizes[l + 1] <= GF_NARROW) ? (n.sizes[l] + GF_THREADS - 1) / GF_THREADS
+		tiles += (n.sizes[l + 1] <= GF_NARROW) ? (n.sizes[l] + GF_NCOLS - 1) / GF_NCOLS
 		                                       : ((n.sizes[l + 1] + GF_TO - 1) / GF_TO) * ((n.sizes[l] + tile_i - 1) / tile_i);
 	}
 	tile_off[H + 1] = tiles;
@@ -700,7 +715,7 @@ __global__ void __launch_bounds__(GF_THREADS, 1) grid_fused_kernel(const __grid_
 				const int o0 = (tl / tiles_i) * GF_TO, i0 = (tl % tiles_i) * tile_i;
 				const float* ckl = ck + (size_t)l * (mb + 1);
 				if (n.sizes[l + 1] <= GF_NARROW)
-					gf_grad_narrow(a, l, tl * GF_THREADS, len, tot, node_off[l], node_off[l + 1], ckl, inv_len, bad);
+					gf_grad_narrow(a, l, tl * GF_NCOLS, len, tot, node_off[l], node_off[l + 1], ckl, inv_len, Dt, bad);
 				else if (a.nc == 2)
 					gf_grad_tile<2>(a, l, o0, i0, len, tot, node_off[l], node_off[l + 1], Dt, At, Ct, ckl, inv_len, bad);
 				else
@@ -787,7 +802,7 @@ int grid_fused_pick_nc(const NetView& n, int ctas)
 	{
 		int tiles = 0;
 		for (int l = 0; l <= n.H; ++l)
-			tiles += (n.sizes[l + 1] <= GF_NARROW) ? (n.sizes[l] + GF_THREADS - 1) / GF_THREADS
+			tiles += (n.sizes[l + 1] <= GF_NARROW) ? (n.sizes[l] + GF_NCOLS - 1) / GF_NCOLS
 			                                       : ((n.sizes[l + 1] + GF_TO - 1) / GF_TO) * ((n.sizes[l] + 16 * nc - 1) / (16 * nc));
 		if (tiles <= ctas) return nc;
 	}
