@@ -236,7 +236,7 @@ struct gl_net
 	void* dpMaps = nullptr;              // device: [layer][owner] tensor maps of the owners' bands (this rank's slot)
 	float** dpBases = nullptr;           // device: [layer][owner] base pointers of the same
 	float* hostBases[GL_MAX_WEIGHT_LAYERS][DP_MAX_WORLD] = {};
-	int dpPushBlocks = 32;               // CTAs of an owner's update kernel while the backward pass still runs
+	int dpPushBlocks = 296;              // CTAs of an owner's update kernel while the backward pass still runs (8 GPUs: 32 -> 6.05 M, 128 -> 6.33 M, 296 -> 6.55 M, 592 -> 6.40 M samples/s)
 };
 
 static NetView make_view(const gl_net* n)
@@ -1009,7 +1009,7 @@ static bool grid_fused_fits(const gl_net* n)
 	for (int l = 0; l <= n->H + 1; ++l)
 		if (n->d.sizes[l] > 1024) return false;
 	const NetView v = make_view(n);
-	return grid_fused_smem_bytes(v) <= (size_t)200 * 1024;
+	return grid_fused_smem_bytes(v) <= (size_t)220 * 1024;
 }
 static bool grid_fused_ok(gl_net* n)
 {
@@ -1992,7 +1992,7 @@ extern "C" int gl_dp_init(gl_net* n, int32_t rank, int32_t world, const void* id
 	CU(cudaEventCreateWithFlags(&n->evComm, cudaEventDisableTiming));
 	if (const char* e = getenv("GLADES_DP_OVERLAP")) n->dpOverlap = atoi(e) != 0;
 	if (const char* e = getenv("GLADES_DP_RESERVE_SMS")) n->dpReserveSms = atoi(e);
-	if (const char* e = getenv("GLADES_DP_PUSH_BLOCKS")) n->dpPushBlocks = atoi(e) > 0 ? atoi(e) : 32;
+	if (const char* e = getenv("GLADES_DP_PUSH_BLOCKS")) n->dpPushBlocks = atoi(e) > 0 ? atoi(e) : 296;
 	// GLADES_DP_PUSH=0: the NCCL all-reduce path; =1: the exchange over peer memory or an error;
 	// unset: the exchange over peer memory when the ranks can map each other's memory, else NCCL
 	const char* e = getenv("GLADES_DP_PUSH");
