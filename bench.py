@@ -418,7 +418,10 @@ def run_small(args, g, name):
         d = g.make_desc(w["sizes"], w["acts"], w["out"], batch=w["batch"], lr=w["lr"], momentum=w["momentum"], mode=mode)
         net = g.Net(d)
         times, e2e = [], []
+        sampler = ClockSampler(0)
         for i in range(args.warmup + args.steps):
+            if i == args.warmup:
+                sampler.start()
             t0 = time.perf_counter()
             net.set_weights(w0, None)
             net.set_data(x, y)                       # host rows in, every step
@@ -427,6 +430,7 @@ def run_small(args, g, name):
             if i >= args.warmup:
                 times.append(m.device_ms / 1000.0)
                 e2e.append(dt)
+        clocks = sampler.stop()
         samples = w["rows"] * w["epochs"]
         value = samples / float(np.mean(times))
         bytes_per_sample = 4 * (w["sizes"][0] + w["sizes"][-1])
@@ -460,7 +464,8 @@ def run_small(args, g, name):
                        "l2": "data set far smaller than L2: the run is a sequential dependent chain, not a bandwidth test"},
             "e2e": {"value": samples / float(np.mean(e2e)), "unit": "samples/s",
                     "h2d_bytes_per_step": int(x.nbytes + y.nbytes + w0.nbytes), "d2h_bytes_per_step": 32},
-            "gpu_launches": 1,
+            "gpu_launches": args.steps,
+            "clocks": clocks,
             "roofline": {"bound": "hbm", "achieved": value * bytes_per_sample / 1e9, "peak": peaks["hbm"], "unit": "GB/s",
                          "frac": value * bytes_per_sample / 1e9 / peaks["hbm"], "traffic": None,
                          "note": "latency-bound: %s" % ("strictly sequential per-sample SGD" if mode_name == "reference"
