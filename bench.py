@@ -14,9 +14,10 @@ reference has; its own arithmetic is non-finite on this shape after the first sa
 
 `value`   train samples/s with the windows already resident in HBM (CUDA events on the library's
           stream, max over ranks).
-`e2e`     the same step through gl_train_window_host_submit / _result: every window's rows start in
-          pinned HOST memory and are copied in by the call, and every window's loss is read back; two
-          windows are in flight so the copy of one overlaps the compute of the other.
+`e2e`     the same step through gl_train_window_host_submit / _result (inference: gl_forward_host_submit
+          / _result): every window's rows start in pinned HOST memory and are copied in by the call, and
+          every window's loss (inference: plus every row's predicted class) is read back; two windows
+          are in flight so the copy of one overlaps the compute of the other.
 `roofline` the tensor-core layer-product kernel: algorithmic flop of its launches / their summed
           CUDA-event durations, against the measured dense bf16 peak of MEASURED_PEAKS.json.
 `cpu_baseline` the CPU restatement of the same batched arithmetic (oracle port, all host cores)
@@ -592,6 +593,7 @@ def main():
         L.gl_memcpy_d2h(py, C.c_void_p(dY.value + k * yb), yb, dev)
     mm = g.Metrics()
     h_out = np.empty(8, np.float32)
+    h_arg = np.empty(lb, np.int32)  # inference: every batch's predicted classes are read back
 
     def e2e_submit(i):
         px, py = pins[i % n_pin]
@@ -607,10 +609,20 @@ def main():
         """count steps, each with its own host->device copy and its own loss read-back; training keeps two
         windows in flight so that the copy of one overlaps the compute of the other."""
         if not train:
-            for i in range(count):
+            def fsubmit(i):
                 px, py = pins[i % n_pin]
-                if L.gl_forward_host(net.h, px, py, lb, None, None, C.byref(mm)) != 0:
+                if L.gl_forward_host_submit(net.h, px, py, lb) != 0:
                     raise RuntimeError(L.gl_last_error().decode())
+
+            def fresult():
+                if L.gl_forward_host_result(net.h, h_arg.ctypes.data_as(C.c_void_p), C.byref(mm)) != 0:
+                    raise RuntimeError(L.gl_last_error().decode())
+
+            fsubmit(0)
+            for i in range(1, count):
+                fsubmit(i)
+                fresult()
+            fresult()
             return
         e2e_submit(0)
         for i in range(1, count):
@@ -627,7 +639,9 @@ def main():
     plumb.barrier()
     dt = plumb.max(dt)
     e2e_value = samples_per_step * e2e_steps / dt
-    d2h_bytes = 16 + 16  # the loss / accuracy sums (2 doubles) and the status words (4 ints) read back every step
+    # the loss / accuracy sums (2 doubles) and the status words (4 ints) read back every step; inference also
+    # reads back the predicted class of every row
+    d2h_bytes = 16 + 16 + (0 if train else 4 * lb)
 
     # ---- roofline of the dominant kernel
     peaks = measured_peaks()

@@ -154,6 +154,8 @@ def lib():
         "gl_dp_init": (C.c_int, [vp, i32, i32, vp]),
         "gl_dp_set_window": (C.c_int, [vp, i32, i32]),
         "gl_dp_mode": (C.c_int, [vp]),
+        "gl_forward_host_submit": (C.c_int, [vp, vp, vp, i32]),
+        "gl_forward_host_result": (C.c_int, [vp, vp, mp]),
         "gl_synth_fill": (C.c_int, [vp, i64, u64, u32, i32, f32, f32, i32]),
         "gl_matmul_static": (C.c_int, [vp, i64, i64, vp, i64, i64, vp, i64, i32, i32, i32, i32]),
         "gl_matmul_static_error": (C.c_char_p, []),
@@ -296,6 +298,17 @@ class Net:
         m = Metrics()
         _check(lib().gl_forward_host(self.h, _ptr(x), _ptr(y), rows, _ptr(out), _ptr(am), C.byref(m)))
         return out, am, m
+
+    def submit_forward_host(self, x, y=None):
+        """Queues an inference batch from host rows (at most two in flight); the arrays must stay alive
+        (pinned memory gives the overlap) until the matching forward_result()."""
+        _check(lib().gl_forward_host_submit(self.h, _ptr(x), _ptr(y), x.shape[0]))
+
+    def forward_result(self, rows):
+        am = np.empty(rows, np.int32)
+        m = Metrics()
+        _check(lib().gl_forward_host_result(self.h, _ptr(am), C.byref(m)))
+        return am, m
 
     def activations(self, row):
         n = sum(self.desc.sizes[l] for l in range(1, self.desc.n_layers))

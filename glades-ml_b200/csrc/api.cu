@@ -142,6 +142,9 @@ struct gl_net
 		int64_t cap = 0;
 		double* dSums = nullptr;
 		double* hSums = nullptr;  // pinned: cost, accuracy, then the status words
+		int* hArg = nullptr;      // pinned: predicted classes of an inference batch (gl_forward_host_submit)
+		int64_t argCap = 0;
+		bool infer = false, hasY = false;
 		cudaEvent_t copied = nullptr, done = nullptr, t0 = nullptr;
 		int rows = 0, globalRows = 0;
 		int64_t launches = 0;
@@ -423,6 +426,9 @@ extern "C" int gl_destroy(gl_net* n)
 	{
 		cudaFree(n->slot[i].dX); cudaFree(n->slot[i].dY); cudaFree(n->slot[i].dSums);
 		if (n->slot[i].hSums) cudaFreeHost(n->slot[i].hSums);
+		if (n->slot[i].hArg) cudaFreeHost(n->slot[i].hArg);
+		n->slot[i].hArg = nullptr;
+		n->slot[i].argCap = 0;
 		if (n->slot[i].copied) cudaEventDestroy(n->slot[i].copied);
 		if (n->slot[i].done) cudaEventDestroy(n->slot[i].done);
 		if (n->slot[i].t0) cudaEventDestroy(n->slot[i].t0);
@@ -450,6 +456,9 @@ static int ensure_pinned(gl_net* n, size_t bytes)
 	{
 		cudaFree(n->slot[i].dX); cudaFree(n->slot[i].dY); cudaFree(n->slot[i].dSums);
 		if (n->slot[i].hSums) cudaFreeHost(n->slot[i].hSums);
+		if (n->slot[i].hArg) cudaFreeHost(n->slot[i].hArg);
+		n->slot[i].hArg = nullptr;
+		n->slot[i].argCap = 0;
 		if (n->slot[i].copied) cudaEventDestroy(n->slot[i].copied);
 		if (n->slot[i].done) cudaEventDestroy(n->slot[i].done);
 		if (n->slot[i].t0) cudaEventDestroy(n->slot[i].t0);
@@ -1454,6 +1463,7 @@ extern "C" int gl_train_window_host_submit(gl_net* n, const float* x, const floa
 	sl.globalRows = (int)win_rows;
 	sl.launches = n->lastWindowLaunches;
 	sl.pending = true;
+	sl.infer = false;
 	++n->submitted;
 	return GL_OK;
 }
@@ -1464,6 +1474,7 @@ extern "C" int gl_train_window_host_result(gl_net* n, gl_metrics* out)
 	if (n->submitted == n->collected) return fail(GL_ERR_STATE, "no window in flight");
 	if (int r = use_device(n)) return r;
 	gl_net::Slot& sl = n->slot[n->collected & 1];
+	if (sl.infer) return fail(GL_ERR_STATE, "the oldest call in flight is an inference batch: collect it with gl_forward_host_result");
 	CU(cudaEventSynchronize(sl.done));
 	sl.pending = false;
 	++n->collected;
@@ -1713,6 +1724,101 @@ extern "C" int gl_forward_host(gl_net* n, const float* x, const float* y, int64_
 	CU(cudaMemcpyAsync(n->dXwin, x, (size_t)rows * n->d.sizes[0] * sizeof(float), cudaMemcpyHostToDevice, n->stream));
 	if (y) CU(cudaMemcpyAsync(n->dYwin, y, (size_t)rows * n->n_out * sizeof(float), cudaMemcpyHostToDevice, n->stream));
 	return forward_rows(n, n->dXwin, y ? n->dYwin : nullptr, rows, rows, outputs, argmax, out);
+}
+
+// ---- inference from host buffers, two batches in flight -------------------------------------------
+extern "C" int gl_forward_host_submit(gl_net* n, const float* x, const float* y, int32_t rows)
+{
+	if (!n || !x || rows < 1) return fail(GL_ERR_INVALID, "gl_forward_host_submit: bad argument");
+	if (n->d.mode != GL_MODE_BATCHED) return fail(GL_ERR_STATE, "gl_forward_host_submit needs a batched-mode network");
+	if (rows > 65536) return fail(GL_ERR_INVALID, "gl_forward_host_submit: at most 65536 rows per batch");
+	if (n->submitted - n->collected >= 2) return fail(GL_ERR_STATE, "two batches are already in flight: collect a result first");
+	if (int r = use_device(n)) return r;
+	if (int r = ensure_work(n, rows)) return r;
+	if (!n->copyStream) CU(cudaStreamCreateWithFlags(&n->copyStream, cudaStreamNonBlocking));
+	gl_net::Slot& sl = n->slot[n->submitted & 1];
+	const bool used_before = sl.copied != nullptr;
+	if (int r = slot_prepare(n, sl, rows)) return r;
+	if (rows > sl.argCap)
+	{
+		if (sl.hArg) cudaFreeHost(sl.hArg);
+		sl.hArg = nullptr;
+		sl.argCap = 0;
+		CU(cudaMallocHost(&sl.hArg, (size_t)rows * sizeof(int)));
+		sl.argCap = rows;
+	}
+	if (used_before) CU(cudaStreamWaitEvent(n->copyStream, sl.done, 0));
+	CU(cudaMemcpyAsync(sl.dX, x, (size_t)rows * n->d.sizes[0] * sizeof(float), cudaMemcpyHostToDevice, n->copyStream));
+	if (y) CU(cudaMemcpyAsync(sl.dY, y, (size_t)rows * n->n_out * sizeof(float), cudaMemcpyHostToDevice, n->copyStream));
+	CU(cudaEventRecord(sl.copied, n->copyStream));
+	CU(cudaStreamWaitEvent(n->stream, sl.copied, 0));
+	CU(cudaEventRecord(sl.t0, n->stream));
+	CU(cudaMemsetAsync(sl.dSums, 0, 2 * sizeof(double), n->stream));
+	int64_t launches = 0;
+	if (int r = batched_forward(n, sl.dX, rows, &launches)) return r;
+	HeadArgs h;
+	memset(&h, 0, sizeof h);
+	h.P = n->dA[n->H + 1];
+	h.Y = y ? sl.dY : n->dA[n->H + 1];
+	h.rows = rows;
+	h.n = n->n_out;
+	h.out_type = n->d.output_type;
+	h.softmax = n->softmax;
+	h.data_size = (float)((int64_t)rows * (int64_t)n->n_out);
+	h.sums2 = y ? sl.dSums : nullptr;
+	h.argmax = n->dArgmax;
+	CU(launch_head(h, n->stream));
+	++launches;
+	CU(cudaMemcpyAsync(n->dLastOut, n->dA[n->H + 1] + (size_t)(rows - 1) * n->n_out, (size_t)n->n_out * sizeof(float),
+	                   cudaMemcpyDeviceToDevice, n->stream));
+	CU(cudaMemcpyAsync(sl.hArg, n->dArgmax, (size_t)rows * sizeof(int), cudaMemcpyDeviceToHost, n->stream));
+	CU(cudaMemcpyAsync(sl.hSums, sl.dSums, 2 * sizeof(double), cudaMemcpyDeviceToHost, n->stream));
+	CU(cudaMemcpyAsync(sl.hSums + 2, n->dFlags, 4 * sizeof(int), cudaMemcpyDeviceToHost, n->stream));
+	CU(cudaEventRecord(sl.done, n->stream));
+	n->launches += launches;
+	sl.rows = rows;
+	sl.globalRows = rows;
+	sl.launches = launches;
+	sl.pending = true;
+	sl.infer = true;
+	sl.hasY = y != nullptr;
+	++n->submitted;
+	return GL_OK;
+}
+
+extern "C" int gl_forward_host_result(gl_net* n, int32_t* argmax, gl_metrics* out)
+{
+	if (!n) return fail(GL_ERR_INVALID, "gl_forward_host_result: null handle");
+	if (n->submitted == n->collected) return fail(GL_ERR_STATE, "no batch in flight");
+	if (int r = use_device(n)) return r;
+	gl_net::Slot& sl = n->slot[n->collected & 1];
+	if (!sl.infer) return fail(GL_ERR_STATE, "the oldest call in flight is a training window: collect it with gl_train_window_host_result");
+	CU(cudaEventSynchronize(sl.done));
+	sl.pending = false;
+	sl.infer = false;
+	++n->collected;
+	int flags[4];
+	memcpy(flags, sl.hSums + 2, sizeof flags);
+	if (argmax) memcpy(argmax, sl.hArg, (size_t)sl.rows * sizeof(int));
+	if (out)
+	{
+		float ms = 0;
+		CU(cudaEventElapsedTime(&ms, sl.t0, sl.done));
+		memset(out, 0, sizeof *out);
+		if (sl.hasY)
+		{
+			out->total_error = (float)sl.hSums[0];
+			out->total_accuracy = (float)(sl.hSums[1] / ((double)sl.rows * (double)n->n_out));
+		}
+		out->epochs = n->epochs;
+		out->rows = sl.rows;
+		out->device_ms = ms;
+		out->kernel_launches = sl.launches;
+		out->nonfinite = flags[0] & 1;
+	}
+	if (flags[1])
+		return fail(GL_ERR_TIMEOUT, "a bounded wait on the device ran out (code %d: 1-4 tensor-core pipeline, 20+ gradient exchange)", flags[1]);
+	return GL_OK;
 }
 
 extern "C" int gl_get_activations(gl_net* n, int64_t row, float* out)

@@ -157,6 +157,14 @@ int gl_set_data_device(gl_net* net, const float* d_x, const float* d_y, int64_t 
  * in flight, so the copy of one overlaps the compute of the other.  No counterpart in the reference. */
 int gl_train_window_host_submit(gl_net* net, const float* x, const float* y, int32_t rows);
 int gl_train_window_host_result(gl_net* net, gl_metrics* out);
+/* Batched mode, inference from host buffers with two batches in flight (the test() pass of
+ * NNetwork::run, network.cpp:109-112,428, fed batch by batch): submit copies `rows` (<= 65536) rows
+ * in on a copy stream while the previous batch still computes and queues the forward pass; result
+ * waits for the OLDEST batch and hands out its predicted classes (argmax, `rows` ints, may be NULL)
+ * and -- when expected rows were given -- its cost / accuracy sums over that batch.  Confusion counts
+ * are not kept on this path.  Shares its two slots with gl_train_window_host_submit. */
+int gl_forward_host_submit(gl_net* net, const float* x, const float* y, int32_t rows);
+int gl_forward_host_result(gl_net* net, int32_t* argmax, gl_metrics* out);
 
 /* Replaces n iterations of the epoch loop of NNetwork::run with RUN_TRAIN
  * (network.cpp:173-256): every row through SGDHelper (forward, metrics, confusion counts,

@@ -588,3 +588,43 @@ def test_pipelined_host_windows_equal_synchronous_ones(g):
     assert np.array_equal(bits(wa), bits(wc)) and np.array_equal(bits(ba), bits(bc))
     a.close()
     c.close()
+
+
+def test_pipelined_inference_batches_equal_synchronous_ones(g):
+    """gl_forward_host_submit / _result keep two host batches in flight: classes and metric sums of every
+    batch must equal those of the one-at-a-time entry point; a third submit is refused, and a training
+    result call must not collect an inference batch."""
+    rng = np.random.default_rng(91)
+    sizes = [20, 48, 7]
+    d = g.make_desc(sizes, ["relu", "softmax"], "classification", batch=64, lr=0.05, mode=g.MODE_BATCHED)
+    w, b = _rand_net(rng, sizes)
+    net = g.Net(d)
+    net.set_weights(w, b)
+    batches = []
+    for rows in (64, 33, 64, 5):
+        x = rng.standard_normal((rows, sizes[0])).astype(np.float32)
+        y = np.zeros((rows, sizes[-1]), np.float32)
+        y[np.arange(rows), rng.integers(0, sizes[-1], rows)] = 1.0
+        batches.append((x, y))
+    want = [net.forward_host(x, y) for x, y in batches]
+    got = []
+    net.submit_forward_host(*batches[0])
+    net.submit_forward_host(*batches[1])
+    with pytest.raises(RuntimeError):
+        net.submit_forward_host(*batches[2])          # two in flight already
+    with pytest.raises(RuntimeError):
+        net.window_result()                           # the oldest call in flight is not a training window
+    got.append(net.forward_result(batches[0][0].shape[0]))
+    net.submit_forward_host(*batches[2])
+    got.append(net.forward_result(batches[1][0].shape[0]))
+    net.submit_forward_host(batches[3][0], None)      # no expected rows: classes only
+    got.append(net.forward_result(batches[2][0].shape[0]))
+    got.append(net.forward_result(batches[3][0].shape[0]))
+    with pytest.raises(RuntimeError):
+        net.forward_result(1)                         # nothing in flight
+    for k, ((_, am_w, m_w), (am_g, m_g)) in enumerate(zip(want, got)):
+        assert np.array_equal(am_w, am_g), k
+        if k < 3:
+            assert abs(m_w.total_error - m_g.total_error) <= 1e-6 * max(1.0, abs(m_w.total_error)), k
+            assert abs(m_w.total_accuracy - m_g.total_accuracy) <= 1e-4, k
+    net.close()
