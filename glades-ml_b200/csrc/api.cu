@@ -1,8 +1,10 @@
 // extern "C" layer of the B200-native glades feed-forward path (declared in include/glades_b200.h).
 // It owns the device memory of one network, packs rows and weights into contiguous row-major
-// device matrices, and drives the kernels of ref_mode.cu (reference arithmetic), batched.cu /
-// gemm_tcgen05.cu (batched arithmetic) and synth.cu.  There is no CPU compute path: every compute
-// entry point fails with GL_ERR_NO_DEVICE when no sm_100 device is present.
+// device matrices, and drives the kernels of ref_mode.cu (reference arithmetic), small_fused.cu /
+// grid_fused.cu / batched.cu / gemm_tcgen05.cu (batched arithmetic: whole-network, whole-window and
+// per-layer engines), dp_push.cu (data-parallel exchange over peer memory) and synth.cu.  There is no
+// CPU compute path: every compute entry point fails with GL_ERR_NO_DEVICE when no sm_100 device is
+// present.
 #include <dlfcn.h>
 #include <math.h>
 #include <stdarg.h>
