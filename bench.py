@@ -221,14 +221,26 @@ def dev_alloc(L, nbytes, dev):
     return p
 
 
-def build_wide_mlp_data(g, w, rows, dev, rank):
+def fill_shard(L, d_ptr, nwin, lb, gb, rank, width, seed, stream, dist, scale, offset, dev):
+    """Fills this rank's rows of `nwin` global windows from ONE global table [nwin * gb][width] of the
+    counter-based stream (seed, stream): window i of the rank holds global rows [i*gb + rank*lb, ... + lb).
+    The table -- and with it every global window -- is the same for any number of ranks."""
+    for i in range(nwin):
+        first = (i * gb + rank * lb) * width
+        dst = C.c_void_p(d_ptr.value + i * lb * width * 4)
+        if L.gl_synth_fill_at(dst, lb * width, first, seed, stream, dist, scale, offset, dev) != 0:
+            raise RuntimeError(L.gl_last_error().decode())
+
+
+def build_wide_mlp_data(g, w, nwin, lb, gb, dev, rank):
     """Resident synthetic shard: X ~ N(0,1) on the device, Y = one-hot argmax of the seeded teacher."""
     L = g.lib()
+    rows = nwin * lb
     n_in, n_out = w["sizes"][0], w["sizes"][-1]
     dX = dev_alloc(L, rows * n_in * 4, dev)
     dY = dev_alloc(L, rows * n_out * 4, dev)
-    # stream 0 = data; every rank draws its own index range of the same stream
-    assert L.gl_synth_fill(dX, rows * n_in, SEED + 4 + 1000 * rank, 0, 1, 1.0, 0.0, dev) == 0, L.gl_last_error()
+    # stream 0 = data: every rank fills its own rows of the one global table
+    fill_shard(L, dX, nwin, lb, gb, rank, n_in, SEED + 4, 0, 1, 1.0, 0.0, dev)
     rng = np.random.default_rng(SEED + 41)
     tsz = [n_in, 4096, n_out]
     tw = np.concatenate([(rng.standard_normal(tsz[i] * tsz[i + 1]) / np.sqrt(tsz[i])).astype(np.float32)
@@ -264,8 +276,12 @@ def cpu_port_baseline(g, w, sample_rows, threads=None):
     sample of one window.  Test infrastructure used as the reported CPU baseline only."""
     o = ge.import_oracle()
     sizes = w["sizes"]
-    cores = threads or os.cpu_count() or 1
-    os.environ.setdefault("OMP_NUM_THREADS", str(cores))
+    try:
+        avail = len(os.sched_getaffinity(0))
+    except AttributeError:
+        avail = os.cpu_count() or 1
+    # set explicitly: a launcher may have exported OMP_NUM_THREADS=1 (torchrun does); `cores` is what really runs
+    cores = o.set_threads(threads or avail)
     rng = np.random.default_rng(3)
     x = rng.standard_normal((sample_rows, sizes[0])).astype(np.float32)
     y = np.zeros((sample_rows, sizes[-1]), np.float32)
@@ -349,6 +365,14 @@ def cpu_baseline_for(g, name, w):
                               "accumulation, OpenMP), %.1f s%s" % (rows, dt, note)), dt
 
 
+def workload_config(name, w, world):
+    """The part of `config` that names the workload; the same for our arm and the reference arm."""
+    train = w["kind"] == "train"
+    gb = w["batch"]
+    return {"workload": name, "sizes": w["sizes"], "global_batch": gb, "per_gpu_rows": gb // world if train else gb,
+            "mode": "batched", "head": w["acts"][-1], "lr": w["lr"], "parallelism": "dp%d" % world}
+
+
 def run_reference_arm(args, g, w, rank, world):
     """The CPU arm: the reference's own compiled code (oracle/_ref) on a bounded sample where that is
     feasible (inference rows, the window regressor's training rows).  For the wide MLP it needs ~669 s
@@ -358,21 +382,29 @@ def run_reference_arm(args, g, w, rank, world):
     if rank != 0:
         return
     vals, secs = [], []
-    for _ in range(max(1, min(args.steps, 2))):
+    cores = kind = sample = None
+    for i in range(args.warmup + args.steps):
         v, cores, kind, sample, dt = cpu_baseline_for(g, args.workload, w)
-        vals.append(v)
-        secs.append(dt)
+        if i >= args.warmup:
+            vals.append(v)
+            secs.append(dt)
     value = float(np.mean(vals))
     unit = "samples/s" if w["kind"] == "train" else "rows/s"
     line = {
         "impl": "reference", "metric": "train_samples_per_s" if w["kind"] == "train" else "infer_rows_per_s",
-        "value": value, "unit": unit, "n_gpus": world, "steps": len(vals),
-        "warmup": 0, "ms_per_step": 1000.0 * float(np.mean(secs)), "higher_is_better": True, "scaling": "weak",
+        "value": value, "unit": unit, "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": 1000.0 * float(np.mean(secs)), "higher_is_better": True,
+        "scaling": "strong" if w["kind"] == "train" else "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": args.workload, "sizes": w["sizes"]},
+        "config": workload_config(args.workload, w, world),
         "cpu_baseline": {"value": value, "unit": unit, "cores": cores, "kind": kind, "sample": sample},
         "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
+    if args.workload == "wide_mlp":
+        # the compiled reference itself on this shape, timed once on one core of the development box (not
+        # re-run here: one row takes eleven minutes and its arithmetic leaves the finite range)
+        line["reference_measured_once"] = {"seconds_per_training_row": 668.7, "forward_s": 2.6, "backward_s": 666.0,
+                                           "samples_per_s": 1.0 / 668.7, "cores": 1, "finite": False}
     print(json.dumps(line), flush=True)
 
 
@@ -530,13 +562,16 @@ def main():
     net = g.Net(d)
     net.set_weights(student_weights(sizes), None)
     if args.workload == "wide_mlp":
-        dX, dY, labels = build_wide_mlp_data(g, w, rows, dev, rank)
+        dX, dY, labels = build_wide_mlp_data(g, w, nwin, lb, gb, dev, rank)
     else:
         dX = dev_alloc(L, rows * sizes[0] * 4, dev)
         dY = dev_alloc(L, rows * sizes[-1] * 4, dev)
         dist, sc, off = (0, 1.0, 0.0) if args.workload == "batched_inference" else (1, 1.0, 0.0)
-        assert L.gl_synth_fill(dX, rows * sizes[0], SEED + 1000 * rank, 0, dist, sc, off, dev) == 0
-        assert L.gl_synth_fill(dY, rows * sizes[-1], SEED + 7 + 1000 * rank, 3, 0, 0.98, 0.01, dev) == 0
+        # training: the rank's rows of each global window; inference: the rank's own whole batches
+        # (batch i of rank k is global batch i * world + k), both cut from one global table
+        tgb, trank = (gb, rank) if train else (gb * world, rank)
+        fill_shard(L, dX, nwin, lb, tgb, trank, sizes[0], SEED, 0, dist, sc, off, dev)
+        fill_shard(L, dY, nwin, lb, tgb, trank, sizes[-1], SEED + 7, 3, 0, 0.98, 0.01, dev)
         labels = None
     net.set_data_device(dX.value, dY.value, rows)
     if world > 1 and train:
@@ -554,29 +589,41 @@ def main():
             return net.train_window(r0, lb, want_metrics)
         return net.forward(r0, lb, want_outputs=False, want_argmax=False)[2]
 
-    # ---- resident timing (`value`)
+    # ---- resident timing (`value`): K steps per region, no per-launch events inside it; the region is run
+    # three times and the median is reported (all three are in the line), so that one noisy region of a
+    # few tens of milliseconds does not decide the number
     m_first = step(0, True)
     for i in range(1, args.warmup):
         step(i)
     net.sync()
-    plumb.barrier()
     launches0 = net.kernel_launches()
     sampler = ClockSampler(dev)
     sampler.start()
+    regions = []
+    for rep in range(3):
+        plumb.barrier()
+        net.timer_start()
+        for i in range(args.steps):
+            step(args.warmup + rep * args.steps + i)
+        r_ms = net.timer_stop()
+        net.sync()
+        plumb.barrier()
+        regions.append(plumb.max(r_ms))
+    clocks = sampler.stop()
+    launches = (net.kernel_launches() - launches0) // 3
+    ms = float(np.median(regions))
+    samples_per_step = gb if train else gb * world
+    value = samples_per_step * args.steps / (ms / 1000.0)
+    # ---- a separate, untimed-for-`value` pass with per-launch events around the layer products (roofline)
     net.profile_enable(True)
     net.timer_start()
     for i in range(args.steps):
         step(args.warmup + i)
-    ms = net.timer_stop()
+    prof_ms = plumb.max(net.timer_stop())
     net.sync()
     plumb.barrier()
     prof = net.profile_read()
     net.profile_enable(False)
-    clocks = sampler.stop()
-    launches = net.kernel_launches() - launches0
-    ms = plumb.max(ms)
-    samples_per_step = gb if train else gb * world
-    value = samples_per_step * args.steps / (ms / 1000.0)
     m_last = step(0, True) if train else None
 
     # ---- end to end through the host-buffer entry point (`e2e`)
@@ -670,8 +717,8 @@ def main():
         roofline = {
             "bound": "tensor", "kernel": dom_name, "achieved": achieved, "peak": peaks["tensor"], "unit": "TFLOP/s",
             "frac": achieved / peaks["tensor"],
-            # DRAM bytes per launch of this kernel from one ncu capture of this very workload
-            # (profiles/gemm_tc_kernel_wide_mlp.md: 5.81 GB over the 8 products of a step); null elsewhere
+            # DRAM bytes per launch of this kernel from one ncu capture of this very workload (5.81 GB over
+            # the 8 products of a step); null elsewhere
             "traffic": 0.726e9 if (dom is tc and args.workload == "wide_mlp" and world == 1) else None,
             "peak_source": peaks["source"] + " dense bf16 (sustained)",
             "launches": dom["launches"], "avg_launch_ms": dom["ms"] / max(1, dom["launches"]),
@@ -682,9 +729,16 @@ def main():
             # cuBLAS TF32 GEMM measured on this pool's B200s the way the bf16 peak was (8192^3, best of 10,
             # CUDA events): 745.6 TFLOP/s burst, 591.7 over 300 in a row; a 3xTF32 product can reach a third
             "frac_of_cublas_tf32_third": achieved / (745.6 / 3.0),
-            "share_of_step_ms": dom["ms"] / ms if ms > 0 else None,
+            "share_of_step_ms": dom["ms"] / prof_ms if prof_ms > 0 else None,
         }
 
+    # sum and sum of magnitudes of the final weights (after warm-up, the timed regions, the profiled pass
+    # and the end-to-end steps: the same sequence of global windows for every N)
+    checksum = None
+    if train and rank == 0:
+        wfin, bfin = net.get_weights()
+        checksum = {"sum": float(np.sum(wfin, dtype=np.float64)), "sum_abs": float(np.sum(np.abs(wfin), dtype=np.float64)),
+                    "bias": [float(v) for v in bfin]}
     line = None
     if rank == 0:
         cpu = None
@@ -697,8 +751,10 @@ def main():
             "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong" if train else "weak",
             "vs_baseline": None, "dtype": "f32 (3xTF32 tensor-core products, fp32 accumulate)" if (dom is not None and dom is tc) else "f32",
             "data": "synthetic",
-            "config": {"workload": args.workload, "sizes": sizes, "global_batch": gb, "per_gpu_rows": lb,
-                       "mode": "batched", "head": w["acts"][-1], "lr": w["lr"], "resident_windows_per_gpu": nwin,
+            "config": dict(workload_config(args.workload, w, world), **{
+                       "resident_windows_per_gpu": nwin,
+                       "timed_region": "median of 3 regions of %d steps each (CUDA events, max over ranks); per-launch "
+                                       "events only in a separate pass" % args.steps,
                        "l2": ("inputs larger than L2: every step streams a distinct %.0f MB window plus %.0f MB of weights and "
                               "%.0f MB of activations and deltas" % (lb * (sizes[0] + sizes[-1]) * 4 / 1e6, net.nw * 4 / 1e6,
                                                                        2 * lb * sum(sizes) * 4 / 1e6))
@@ -706,18 +762,21 @@ def main():
                              "inputs larger than L2: %d resident windows (%.0f MB) and every step reads a window no earlier step "
                              "has touched; the weights and the window's scratch (%.1f MB) stay in L2 by design"
                              % (nwin, nwin * lb * (sizes[0] + sizes[-1]) * 4 / 1e6, (2 * lb * sum(sizes) + net.nw) * 4 / 1e6),
-                       "parallelism": "dp%d" % world,
                        "gradient_exchange": {0: None, 1: "NCCL all-reduce per layer, overlapped with the backward pass",
                                              2: "row bands stored into their owner's memory by the gradient product's "
-                                                "epilogue over NVLink; owner sums, updates, writes every replica"}[dp_mode]},
+                                                "epilogue over NVLink; owner sums, updates, writes every replica"}[dp_mode]}),
             "e2e": {"value": e2e_value, "unit": "samples/s" if train else "rows/s", "h2d_bytes_per_step": xb + yb,
                     "d2h_bytes_per_step": d2h_bytes, "steps": e2e_steps},
             "gpu_launches": int(launches),
             "clocks": clocks,
             "roofline": roofline,
             "cpu_baseline": cpu,
+            "region_ms": regions,
+            # the same global windows are trained for every number of GPUs (one global table, see fill_shard), so
+            # these three agree across N up to the fp32 summation order
             "loss_first_window": m_first.total_error if m_first else None,
             "loss_after": m_last.total_error if m_last else None,
+            "weights_checksum": checksum,
             "flop_per_sample": flop_per_sample(sizes, train),
             "step_tflops": flop_per_sample(sizes, train) * samples_per_step / (ms / args.steps / 1000.0) / 1e12,
         }

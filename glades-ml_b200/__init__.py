@@ -9,5 +9,5 @@ compute entry point returns GL_ERR_NO_DEVICE without an sm_100 device.
 from .capi import (  # noqa: F401
     GL_MAX_WEIGHT_LAYERS, ACT, OUT, MODE_REFERENCE, MODE_BATCHED, BIAS_MEAN, BIAS_REFERENCE,
     GEMM_AUTO, GEMM_FFMA, GEMM_TCGEN05, GEMM_GRID_FUSED, NetDesc, Metrics, GladesError, Net, lib, lib_path,
-    make_desc, weight_count, shard_range, device_count,
+    make_desc, weight_count, shard_range, device_count, tc_variant_counts,
 )

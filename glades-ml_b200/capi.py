@@ -157,6 +157,9 @@ def lib():
         "gl_forward_host_submit": (C.c_int, [vp, vp, vp, i32]),
         "gl_forward_host_result": (C.c_int, [vp, vp, mp]),
         "gl_synth_fill": (C.c_int, [vp, i64, u64, u32, i32, f32, f32, i32]),
+        "gl_selftest_bounded_wait": (C.c_int, [vp, i64, C.POINTER(C.c_double)]),
+        "gl_synth_fill_at": (C.c_int, [vp, i64, i64, u64, u32, i32, f32, f32, i32]),
+        "gl_tc_variant_counts": (None, [C.POINTER(i64)]),
         "gl_matmul_static": (C.c_int, [vp, i64, i64, vp, i64, i64, vp, i64, i32, i32, i32, i32]),
         "gl_matmul_static_error": (C.c_char_p, []),
         "gl_onehot_fill": (C.c_int, [vp, vp, i64, i32, f32, f32, i32]),
@@ -166,6 +169,7 @@ def lib():
         "gl_profile_read": (C.c_int, [vp, C.POINTER(C.c_double)]),
         "gl_device_alloc": (C.c_int, [C.POINTER(vp), i64, i32]),
         "gl_device_free": (C.c_int, [vp, i32]),
+        "gl_device_mem_info": (C.c_int, [i32, C.POINTER(i64), C.POINTER(i64)]),
         "gl_memcpy_h2d": (C.c_int, [vp, vp, i64, i32]),
         "gl_memcpy_d2h": (C.c_int, [vp, vp, i64, i32]),
         "gl_host_alloc_pinned": (C.c_int, [C.POINTER(vp), i64]),
@@ -186,6 +190,13 @@ def _check(st):
 
 def device_count():
     return lib().gl_device_count()
+
+
+def tc_variant_counts():
+    """Tensor-core product launches of this process: [128-wide, 256-wide, several tiles per CTA, peer-store]."""
+    out = (C.c_int64 * 4)()
+    lib().gl_tc_variant_counts(out)
+    return [int(v) for v in out]
 
 
 def shard_range(rows, rank, world):
@@ -339,6 +350,12 @@ class Net:
 
     def sync(self):
         _check(lib().gl_sync(self.h))
+
+    def selftest_bounded_wait(self, max_cycles):
+        """Queues a wait on a flag nobody raises; returns the device milliseconds it took to give up."""
+        ms = C.c_double()
+        _check(lib().gl_selftest_bounded_wait(self.h, int(max_cycles), C.byref(ms)))
+        return ms.value
 
     def timer_start(self):
         _check(lib().gl_timer_start(self.h))

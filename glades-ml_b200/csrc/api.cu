@@ -233,6 +233,7 @@ struct gl_net
 	// gradient exchange over peer memory (dp_push.cu); dpPush == false: the NCCL all-reduce path
 	bool dpPush = false;
 	unsigned dpStep = 0;                 // window counter, the value the flags are raised to
+	void* dpRec = nullptr;               // set-up scratch: gathered handles / agreement words (allocated before the communicator)
 	char* dpArena = nullptr;             // this rank's arena: flag area, then one gradient slot per source rank
 	void* dpPeerArena[DP_MAX_WORLD] = {}; // every rank's arena as mapped here (own entry = dpArena)
 	void* dpPeerW[DP_MAX_WORLD] = {};     // every rank's weight vector as mapped here (own entry = dW)
@@ -409,6 +410,7 @@ extern "C" int gl_destroy(gl_net* n)
 	for (int l = 0; l <= GL_MAX_WEIGHT_LAYERS; ++l) if (n->evGrad[l]) cudaEventDestroy(n->evGrad[l]);
 	if (n->evComm) cudaEventDestroy(n->evComm);
 	free_work(n);
+	cudaFree(n->dpRec);
 	cudaFree(n->dWlo);
 	cudaFree(n->dW); cudaFree(n->dBias); cudaFree(n->dG); cudaFree(n->dBscale); cudaFree(n->dFlags);
 	cudaFree(n->dSums); cudaFree(n->dSumsF); cudaFree(n->dConf); cudaFree(n->dHist); cudaFree(n->dHistLen);
@@ -1942,6 +1944,15 @@ static void dp_push_release(gl_net* n)
 // Sets up the gradient exchange over peer memory: bands, the exchange arena, the inter-process
 // mappings of every rank's arena and weight vector, the per-owner tensor maps.  Collective: every
 // rank of the communicator calls it.  On failure the handle stays on the NCCL path.
+//
+// The function contains four collectives (gather of the handles, two agreements, the handshake's
+// agreement).  A rank must never leave between them while its peers wait inside the next one, so a
+// local failure (allocation, handle export, mapping, copy) is only recorded; it travels to the next
+// agreement, after which all ranks release and return together.  The gather buffer n->dpRec was
+// allocated by gl_dp_init before the communicator existed.
+namespace {
+struct DpRec { cudaIpcMemHandle_t arena, w; };
+}
 static int dp_push_setup(gl_net* n)
 {
 	const int W = n->world;
@@ -1959,21 +1970,27 @@ static int dp_push_setup(gl_net* n)
 	}
 	n->dpSlotOff[n->H + 1] = off;
 	const size_t bytes = DP_FLAG_BYTES + (size_t)W * (size_t)off * sizeof(float);
-	CU(cudaMalloc(&n->dpArena, bytes));
-	CU(cudaMemset(n->dpArena, 0, bytes));
-	struct Rec { cudaIpcMemHandle_t arena, w; };
-	Rec mine;
-	CU(cudaIpcGetMemHandle(&mine.arena, n->dpArena));
-	CU(cudaIpcGetMemHandle(&mine.w, n->dW));
-	Rec* dRec = nullptr;
-	CU(cudaMalloc(&dRec, sizeof(Rec) * (size_t)(W + 1)));
-	CU(cudaMemcpy(dRec + W, &mine, sizeof mine, cudaMemcpyHostToDevice));
-	NC(g_nccl.AllGather(dRec + W, dRec, sizeof(Rec), NCCL_INT8, n->comm, n->stream));
-	CU(cudaStreamSynchronize(n->stream));
-	std::vector<Rec> all((size_t)W);
-	CU(cudaMemcpy(all.data(), dRec, sizeof(Rec) * (size_t)W, cudaMemcpyDeviceToHost));
 	int failed = 0;
-	for (int r = 0; r < W; ++r)
+	char why[160] = "";
+	auto local = [&](cudaError_t e, const char* what) {
+		if (e == cudaSuccess || failed) return;
+		failed = 1;
+		snprintf(why, sizeof why, "%s: %s", what, cudaGetErrorString(e));
+		cudaGetLastError();
+	};
+	DpRec* dRec = static_cast<DpRec*>(n->dpRec);
+	DpRec mine;
+	memset(&mine, 0, sizeof mine);
+	local(cudaMalloc(&n->dpArena, bytes), "exchange arena");
+	if (!failed) local(cudaMemset(n->dpArena, 0, bytes), "clearing the exchange arena");
+	if (!failed) local(cudaIpcGetMemHandle(&mine.arena, n->dpArena), "exporting the exchange arena");
+	if (!failed) local(cudaIpcGetMemHandle(&mine.w, n->dW), "exporting the weights");
+	local(cudaMemcpy(dRec + W, &mine, sizeof mine, cudaMemcpyHostToDevice), "staging the handles");
+	NC(g_nccl.AllGather(dRec + W, dRec, sizeof(DpRec), NCCL_INT8, n->comm, n->stream));
+	local(cudaStreamSynchronize(n->stream), "gathering the handles");
+	std::vector<DpRec> all((size_t)W);
+	local(cudaMemcpy(all.data(), dRec, sizeof(DpRec) * (size_t)W, cudaMemcpyDeviceToHost), "reading the handles");
+	for (int r = 0; r < W && !failed; ++r)
 	{
 		if (r == n->rank)
 		{
@@ -1981,53 +1998,58 @@ static int dp_push_setup(gl_net* n)
 			n->dpPeerW[r] = n->dW;
 			continue;
 		}
-		if (cudaIpcOpenMemHandle(&n->dpPeerArena[r], all[(size_t)r].arena, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess ||
-		    cudaIpcOpenMemHandle(&n->dpPeerW[r], all[(size_t)r].w, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess)
-		{
-			cudaGetLastError();
-			failed = 1;
-			break;
-		}
-	}
-	// every rank must take the same path: agree on the outcome
-	int* dAgree = reinterpret_cast<int*>(dRec);
-	CU(cudaMemcpy(dAgree, &failed, sizeof failed, cudaMemcpyHostToDevice));
-	NC(g_nccl.AllReduce(dAgree, dAgree, 1, NCCL_INT32, NCCL_SUM, n->comm, n->stream));
-	CU(cudaStreamSynchronize(n->stream));
-	CU(cudaMemcpy(&failed, dAgree, sizeof failed, cudaMemcpyDeviceToHost));
-	if (failed)
-	{
-		dp_push_release(n);
-		cudaFree(dRec);
-		return fail(GL_ERR_COMM, "the ranks cannot map each other's device memory; staying on the NCCL all-reduce");
+		local(cudaIpcOpenMemHandle(&n->dpPeerArena[r], all[(size_t)r].arena, cudaIpcMemLazyEnablePeerAccess), "mapping a peer's arena");
+		if (!failed) local(cudaIpcOpenMemHandle(&n->dpPeerW[r], all[(size_t)r].w, cudaIpcMemLazyEnablePeerAccess), "mapping a peer's weights");
 	}
 	// per layer and owner: where this rank's contribution to the owner's band goes
 	const size_t nmaps = (size_t)GL_MAX_WEIGHT_LAYERS * DP_MAX_WORLD;
-	std::vector<unsigned char> raw(nmaps * 128 + 64);
-	unsigned char* maps = raw.data() + ((64 - ((uintptr_t)raw.data() & 63)) & 63);
-	std::vector<float*> bases(nmaps, nullptr);
-	for (int l = 0; l <= n->H; ++l)
+	if (!failed)
 	{
-		const int no = n->d.sizes[l + 1], ni = n->d.sizes[l];
-		for (int o = 0; o < W; ++o)
+		std::vector<unsigned char> raw(nmaps * 128 + 64);
+		unsigned char* maps = raw.data() + ((64 - ((uintptr_t)raw.data() & 63)) & 63);
+		std::vector<float*> bases(nmaps, nullptr);
+		for (int l = 0; l <= n->H; ++l)
 		{
-			int rows = no - o * n->dpBand[l];
-			rows = rows < 0 ? 0 : (rows > n->dpBand[l] ? n->dpBand[l] : rows);
-			float* base = reinterpret_cast<float*>(static_cast<char*>(n->dpPeerArena[o]) + DP_FLAG_BYTES) +
-			              (int64_t)n->rank * off + n->dpSlotOff[l];
-			bases[(size_t)l * DP_MAX_WORLD + o] = base;
-			n->hostBases[l][o] = base;
-			if (rows >= 128 && rows % 128 == 0 && ni % 128 == 0)
-				tc_make_store_map(maps + ((size_t)l * DP_MAX_WORLD + o) * 128, base, rows, ni, ni);
+			const int no = n->d.sizes[l + 1], ni = n->d.sizes[l];
+			for (int o = 0; o < W; ++o)
+			{
+				int rows = no - o * n->dpBand[l];
+				rows = rows < 0 ? 0 : (rows > n->dpBand[l] ? n->dpBand[l] : rows);
+				float* base = reinterpret_cast<float*>(static_cast<char*>(n->dpPeerArena[o]) + DP_FLAG_BYTES) +
+				              (int64_t)n->rank * off + n->dpSlotOff[l];
+				bases[(size_t)l * DP_MAX_WORLD + o] = base;
+				n->hostBases[l][o] = base;
+				if (rows >= 128 && rows % 128 == 0 && ni % 128 == 0)
+					tc_make_store_map(maps + ((size_t)l * DP_MAX_WORLD + o) * 128, base, rows, ni, ni);
+			}
 		}
+		local(cudaMalloc(&n->dpMaps, nmaps * 128), "tensor maps of the owners' bands");
+		if (!failed) local(cudaMalloc(&n->dpBases, nmaps * sizeof(float*)), "base pointers of the owners' bands");
+		if (!failed) local(cudaMemcpy(n->dpMaps, maps, nmaps * 128, cudaMemcpyHostToDevice), "uploading the tensor maps");
+		if (!failed) local(cudaMemcpy(n->dpBases, bases.data(), nmaps * sizeof(float*), cudaMemcpyHostToDevice), "uploading the base pointers");
 	}
-	CU(cudaMalloc(&n->dpMaps, nmaps * 128));
-	CU(cudaMalloc(&n->dpBases, nmaps * sizeof(float*)));
-	CU(cudaMemcpy(n->dpMaps, maps, nmaps * 128, cudaMemcpyHostToDevice));
-	CU(cudaMemcpy(n->dpBases, bases.data(), nmaps * sizeof(float*), cudaMemcpyHostToDevice));
-	// nobody writes into a peer before every rank has zeroed and mapped everything
-	NC(g_nccl.AllReduce(dAgree, dAgree, 1, NCCL_INT32, NCCL_SUM, n->comm, n->stream));
-	CU(cudaStreamSynchronize(n->stream));
+	// Every rank must take the same path: agree on the outcome.  This all-reduce is also the point after
+	// which every rank has zeroed and mapped everything, so nobody writes into a peer before it.
+	int* dAgree = reinterpret_cast<int*>(dRec);
+	int total_failed = failed;
+	{
+		cudaError_t e = cudaMemcpy(dAgree, &failed, sizeof failed, cudaMemcpyHostToDevice);
+		if (e != cudaSuccess && !failed)
+		{
+			// this rank cannot even report: it still joins the collective (with whatever the word holds) and fails locally
+			local(e, "staging the agreement word");
+		}
+		NC(g_nccl.AllReduce(dAgree, dAgree, 1, NCCL_INT32, NCCL_SUM, n->comm, n->stream));
+		local(cudaStreamSynchronize(n->stream), "agreeing on the mappings");
+		if (cudaMemcpy(&total_failed, dAgree, sizeof total_failed, cudaMemcpyDeviceToHost) != cudaSuccess) total_failed = 1;
+		if (failed && !total_failed) total_failed = 1;
+	}
+	if (total_failed)
+	{
+		dp_push_release(n);
+		return fail(GL_ERR_COMM, "the ranks cannot set up the exchange over each other's device memory (%d rank(s) failed; this rank: %s); "
+		                         "staying on the NCCL all-reduce", total_failed, failed ? why : "ok");
+	}
 	// Handshake over the mapped memory itself: every rank stores a pattern into its slot at every owner and
 	// raises a flag there; every rank then waits (a few seconds at most) for all flags and checks all
 	// patterns.  Only if that works on EVERY rank does the handle use the exchange over peer memory.
@@ -2041,28 +2063,27 @@ static int dp_push_setup(gl_net* n)
 			                     : nullptr;
 		}
 		int* dStatus = dAgree + 1;
-		int zero = 0;
-		CU(cudaMemcpy(dStatus, &zero, sizeof zero, cudaMemcpyHostToDevice));
-		CU(launch_dp_hello_write(heads, fl, W, n->rank, n->stream));
-		CU(launch_dp_wait(n->dpArena, 0, 0, 0, DP_WORD_HELLO, W, 1u, dStatus, 1, n->stream, 8000000000ll));
-		CU(launch_dp_hello_check(reinterpret_cast<const float*>(n->dpArena + DP_FLAG_BYTES), off, W, dStatus, 2, n->stream));
-		CU(cudaStreamSynchronize(n->stream));
-		int status = 0;
-		CU(cudaMemcpy(&status, dStatus, sizeof status, cudaMemcpyDeviceToHost));
-		failed = status != 0;
-		CU(cudaMemcpy(dAgree, &failed, sizeof failed, cudaMemcpyHostToDevice));
+		int zero = 0, status = 0;
+		local(cudaMemcpy(dStatus, &zero, sizeof zero, cudaMemcpyHostToDevice), "clearing the handshake status");
+		if (!failed) local(launch_dp_hello_write(heads, fl, W, n->rank, n->stream), "handshake store");
+		if (!failed) local(launch_dp_wait(n->dpArena, 0, 0, 0, DP_WORD_HELLO, W, 1u, dStatus, 1, n->stream, 8000000000ll), "handshake wait");
+		if (!failed) local(launch_dp_hello_check(reinterpret_cast<const float*>(n->dpArena + DP_FLAG_BYTES), off, W, dStatus, 2, n->stream), "handshake check");
+		local(cudaStreamSynchronize(n->stream), "handshake");
+		if (!failed) local(cudaMemcpy(&status, dStatus, sizeof status, cudaMemcpyDeviceToHost), "reading the handshake status");
+		int bad = (failed || status != 0) ? 1 : 0;
+		total_failed = bad;
+		cudaMemcpy(dAgree, &bad, sizeof bad, cudaMemcpyHostToDevice);
 		NC(g_nccl.AllReduce(dAgree, dAgree, 1, NCCL_INT32, NCCL_SUM, n->comm, n->stream));
-		CU(cudaStreamSynchronize(n->stream));
-		CU(cudaMemcpy(&failed, dAgree, sizeof failed, cudaMemcpyDeviceToHost));
-		if (failed)
+		local(cudaStreamSynchronize(n->stream), "agreeing on the handshake");
+		if (cudaMemcpy(&total_failed, dAgree, sizeof total_failed, cudaMemcpyDeviceToHost) != cudaSuccess) total_failed = 1;
+		if (bad && !total_failed) total_failed = 1;
+		if (total_failed)
 		{
 			dp_push_release(n);
-			cudaFree(dRec);
 			return fail(GL_ERR_COMM, "the handshake over peer memory failed on %d rank(s) (this rank: %s); staying on the NCCL all-reduce",
-			            failed, status == 0 ? "ok" : (status == 1 ? "a flag did not arrive" : "a pattern did not arrive"));
+			            total_failed, failed ? why : (status == 0 ? "ok" : (status == 1 ? "a flag did not arrive" : "a pattern did not arrive")));
 		}
 	}
-	cudaFree(dRec);
 	n->dpPush = true;
 	n->dpStep = 0;
 	return GL_OK;
@@ -2089,6 +2110,9 @@ extern "C" int gl_dp_init(gl_net* n, int32_t rank, int32_t world, const void* id
 	if (int r = nccl_load()) return r;
 	nccl_uid id;
 	memcpy(&id, id128, sizeof id);
+	// scratch of the collective set-up below: allocated before any collective, so that a failure here
+	// cannot strand the peers inside one
+	if (!n->dpRec) CU(cudaMalloc(&n->dpRec, (size_t)(DP_MAX_WORLD + 1) * 2 * sizeof(cudaIpcMemHandle_t) + 64));
 	NC(g_nccl.CommInitRank(&n->comm, world, id, rank));
 	{
 		// the exchange work is short and sits on the critical path: let its CTAs go first
@@ -2182,6 +2206,13 @@ extern "C" int gl_profile_read(gl_net* n, double* out6)
 }
 
 extern "C" int64_t gl_tensor_core_launches(const gl_net* n) { return n ? n->tcLaunches : 0; }
+extern "C" void gl_tc_variant_counts(int64_t* out4)
+{
+	if (!out4) return;
+	long long c[4];
+	tc_variant_counts(c);
+	for (int i = 0; i < 4; ++i) out4[i] = c[i];
+}
 extern "C" int64_t gl_kernel_launches(const gl_net* n) { return n ? n->launches : 0; }
 
 extern "C" int gl_sync(gl_net* n)
@@ -2192,6 +2223,32 @@ extern "C" int gl_sync(gl_net* n)
 	int flags[4];
 	CU(cudaMemcpy(flags, n->dFlags, sizeof flags, cudaMemcpyDeviceToHost));
 	if (flags[1]) return fail(GL_ERR_TIMEOUT, "a bounded wait on the device ran out (code %d: 1-4 tensor-core pipeline, 20+ gradient exchange)", flags[1]);
+	return GL_OK;
+}
+
+// Self-test of the bounded device waits: queues the exchange's wait kernel on a flag word that nothing
+// ever raises, with a limit of `max_cycles` SM clock cycles.  The wait gives up when the limit runs out
+// and records code 99 in the handle's status word; the next status read (gl_sync, a window's metrics)
+// then reports GL_ERR_TIMEOUT, later waits of the handle return at once (the condition is sticky), and
+// gl_set_weights clears it.  *waited_ms receives the device time the wait took.
+extern "C" int gl_selftest_bounded_wait(gl_net* n, int64_t max_cycles, double* waited_ms)
+{
+	if (!n || max_cycles < 1 || max_cycles > 4000000000ll)
+		return fail(GL_ERR_INVALID, "gl_selftest_bounded_wait: the limit must be between 1 and 4e9 cycles (about 2 s)");
+	if (int r = use_device(n)) return r;
+	unsigned* words = nullptr;
+	CU(cudaMalloc(&words, 256));
+	cudaError_t e = cudaMemsetAsync(words, 0, 256, n->stream);
+	if (e == cudaSuccess) e = cudaEventRecord(n->ev0, n->stream);
+	if (e == cudaSuccess) e = launch_dp_wait(words, 0, 0, 0, 0, 1, 1u, n->dFlags + 1, 99, n->stream, max_cycles);
+	if (e == cudaSuccess) e = cudaEventRecord(n->ev1, n->stream);
+	if (e == cudaSuccess) e = cudaStreamSynchronize(n->stream);
+	float ms = 0;
+	if (e == cudaSuccess) e = cudaEventElapsedTime(&ms, n->ev0, n->ev1);
+	cudaFree(words);
+	if (e != cudaSuccess) return fail(GL_ERR_CUDA, "gl_selftest_bounded_wait: %s", cudaGetErrorString(e));
+	if (waited_ms) *waited_ms = ms;
+	n->launches += 1;
 	return GL_OK;
 }
 
@@ -2245,7 +2302,19 @@ extern "C" int gl_synth_fill(float* d_out, int64_t count, uint64_t seed, uint32_
 	if (!d_out || count < 0) return fail(GL_ERR_INVALID, "gl_synth_fill: bad argument");
 	if (gl_device_count() < 1) return fail(GL_ERR_NO_DEVICE, "no sm_100 CUDA device");
 	CU(cudaSetDevice(device));
-	CU(launch_synth_fill(d_out, count, seed, stream_id, dist, scale, offset, 0));
+	CU(launch_synth_fill(d_out, count, 0, seed, stream_id, dist, scale, offset, 0));
+	CU(cudaDeviceSynchronize());
+	return GL_OK;
+}
+
+extern "C" int gl_synth_fill_at(float* d_out, int64_t count, int64_t first_index, uint64_t seed, uint32_t stream_id, int32_t dist,
+                                float scale, float offset, int32_t device)
+{
+	if (!d_out || count < 0 || first_index < 0) return fail(GL_ERR_INVALID, "gl_synth_fill_at: bad argument");
+	if (dist == 1 && (first_index & 1)) return fail(GL_ERR_INVALID, "gl_synth_fill_at: normal draws come in pairs, first_index must be even");
+	if (gl_device_count() < 1) return fail(GL_ERR_NO_DEVICE, "no sm_100 CUDA device");
+	CU(cudaSetDevice(device));
+	CU(launch_synth_fill(d_out, count, first_index, seed, stream_id, dist, scale, offset, 0));
 	CU(cudaDeviceSynchronize());
 	return GL_OK;
 }
@@ -2271,6 +2340,15 @@ extern "C" int gl_device_alloc(void** p, int64_t bytes, int32_t device)
 	if (gl_device_count() < 1) return fail(GL_ERR_NO_DEVICE, "no sm_100 CUDA device");
 	CU(cudaSetDevice(device));
 	CU(cudaMalloc(p, (size_t)bytes));
+	return GL_OK;
+}
+extern "C" int gl_device_mem_info(int32_t device, int64_t* free_bytes, int64_t* total_bytes)
+{
+	CU(cudaSetDevice(device));
+	size_t f = 0, t = 0;
+	CU(cudaMemGetInfo(&f, &t));
+	if (free_bytes) *free_bytes = (int64_t)f;
+	if (total_bytes) *total_bytes = (int64_t)t;
 	return GL_OK;
 }
 extern "C" int gl_device_free(void* p, int32_t device)

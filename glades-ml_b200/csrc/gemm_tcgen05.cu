@@ -19,11 +19,18 @@
 // [batch][node]) through MN-major descriptors, so no transposed copies exist.
 // Every wait on an mbarrier is bounded: when it runs out the kernel raises *err_flag, leaves its
 // loops, waits (bounded) for the copies it still has in flight, frees its tensor memory and returns.
+#include <atomic>
+
 #include "tc_device.cuh"
 
 namespace glb {
 using namespace tc;
 namespace {
+
+// launches per tile variant since the library was loaded (diagnostics for the tests: which instantiation
+// a shape ran on): [0] 128-wide tiles, [1] 256-wide tiles, [2] launches whose CTAs walked more than one
+// tile each, [3] launches of the data-parallel variant that stores into the owners' memory
+std::atomic<long long> g_variant_counts[4];
 
 // BK = fp32 elements per k-block: 32 (128-byte rows, 128-byte swizzle) or 16 (64-byte rows, 64-byte
 // swizzle).  The shallower block with twice the stages keeps more bytes in flight for the same
@@ -391,27 +398,35 @@ cudaError_t launch_cfg(const CUtensorMap& mA, const CUtensorMap& mAl, const CUte
                        cudaStream_t s, const TcPeer& peer = TcPeer())
 {
 	using S = TcSmem<BN, BK, STAGES, SBUF>;
-	static bool attr_set = false;
-	if (!attr_set)
+	// the shared-memory opt-in and the SM count belong to a device, not to the process
+	constexpr int kMaxDev = 64;
+	static bool attr_set[kMaxDev] = {};
+	static int sm_counts[kMaxDev] = {};
+	int dev = 0;
+	if (cudaError_t e = cudaGetDevice(&dev)) return e;
+	const int slot = (dev >= 0 && dev < kMaxDev) ? dev : -1;
+	if (slot < 0 || !attr_set[slot])
 	{
 		cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, BK, STAGES, SBUF, PEER>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
 		if (e != cudaSuccess) return e;
-		attr_set = true;
+		if (slot >= 0) attr_set[slot] = true;
 	}
 	TcParams q = p;
 	q.tiles_m = M / TC_BM;
 	q.tiles_n = N / BN;
-	static int sm_count = 0;
+	int sm_count = slot >= 0 ? sm_counts[slot] : 0;
 	if (!sm_count)
 	{
-		int dev = 0;
-		cudaGetDevice(&dev);
 		if (cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm_count < 1) sm_count = 148;
+		if (slot >= 0) sm_counts[slot] = sm_count;
 	}
 	const int total = q.tiles_m * q.tiles_n;
 	int avail = sm_count - sm_reserve;
 	if (avail < 1) avail = 1;
 	const int grid = total < avail ? total : avail;
+	g_variant_counts[BN == 256 ? 1 : 0].fetch_add(1, std::memory_order_relaxed);
+	if (total > grid) g_variant_counts[2].fetch_add(1, std::memory_order_relaxed);
+	if (PEER) g_variant_counts[3].fetch_add(1, std::memory_order_relaxed);
 	gemm_tc_kernel<BN, BK, STAGES, SBUF, PEER><<<grid, S::THREADS, S::TOTAL, s>>>(mA, mAl, mB, mBl, mC, mCl, q, peer);
 	return cudaGetLastError();
 }
@@ -442,6 +457,11 @@ __global__ void __launch_bounds__(256) scale_split_lo_kernel(const float* __rest
 }
 
 }  // namespace
+
+void tc_variant_counts(long long out4[4])
+{
+	for (int i = 0; i < 4; ++i) out4[i] = g_variant_counts[i].load(std::memory_order_relaxed);
+}
 
 bool tc_make_store_map(void* out128, const float* base, long long rows, long long cols, long long ld)
 {

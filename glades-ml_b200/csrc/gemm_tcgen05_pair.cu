@@ -353,23 +353,14 @@ bool tc::tc_pair_supported(const GemmArgs& g)
 
 cudaError_t tc::launch_gemm_tc_pair(const CUtensorMap maps[6], const TcParams& p, int M, int N, int sm_reserve, cudaStream_t s)
 {
-	static bool attr_set = false;
-	if (!attr_set)
-	{
-		cudaError_t e = cudaFuncSetAttribute(gemm_tc_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, P_TOTAL);
-		if (e != cudaSuccess) return e;
-		attr_set = true;
-	}
+	// per launch: the opt-in and the SM count belong to the current device, not to the process
+	if (cudaError_t e = cudaFuncSetAttribute(gemm_tc_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, P_TOTAL)) return e;
 	TcParams q = p;
 	q.tiles_m = M / 256;
 	q.tiles_n = N / P_BN;
-	static int sm_count = 0;
-	if (!sm_count)
-	{
-		int dev = 0;
-		cudaGetDevice(&dev);
-		if (cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm_count < 2) sm_count = 148;
-	}
+	int sm_count = 0, dev = 0;
+	if (cudaError_t e = cudaGetDevice(&dev)) return e;
+	if (cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm_count < 2) sm_count = 148;
 	int pairs = (sm_count - sm_reserve) / 2;
 	if (pairs < 1) pairs = 1;
 	const int total = q.tiles_m * q.tiles_n;

@@ -205,7 +205,8 @@ cudaError_t launch_dp_finish(const void* arena, int world, int parity, float* gb
                              const float* bscale, int H, int* status_flags, cudaStream_t s);
 
 // ---- synthetic inputs (synth.cu) ---------------------------------------------------------------
-cudaError_t launch_synth_fill(float* out, long long n, unsigned long long seed, unsigned stream_id, int dist,
+// out[j] = element (first + j) of stream `stream_id`; `first` must be even for dist 1
+cudaError_t launch_synth_fill(float* out, long long n, long long first, unsigned long long seed, unsigned stream_id, int dist,
                               float scale, float offset, cudaStream_t s);
 
 // y[r][c] = (c == labels[r]) ? on : off  (expected rows in the reference's one-hot convention)

@@ -17,9 +17,12 @@
 // low-part regions are rewritten for exactly the extents this call's product reads.
 //
 // The array's name is only a host-side stand-in in host code; the device address is fetched once
-// per device with cudaGetSymbolAddress (with that device current) and handed to the kernels.  That
-// set-up happens inside the first call on a device, so make that first call outside any stream
-// capture.
+// per device with cudaGetSymbolAddress (with that device current) and handed to the kernels.  The same
+// set-up creates one private non-blocking stream per device: every piece of GPU work of this entry
+// point runs on it, so a call neither waits for nor holds up the caller's other streams (the legacy
+// default stream would serialise with all of them).  The set-up happens inside the first call on a
+// device, so make that first call outside any stream capture.  The call leaves the caller's current
+// device as it found it.
 #include <mutex>
 
 #include <stdio.h>
@@ -37,11 +40,13 @@ static __device__ __align__(256) float g_static_scratch[GL_STATIC_SCRATCH_FLOATS
 namespace {
 constexpr int kMaxDevices = 64;
 float* g_scratch_addr[kMaxDevices] = {};
+cudaStream_t g_stream[kMaxDevices] = {};
 std::mutex g_setup_mutex;
 thread_local char g_static_err[256];
 
-// Once per device, with that device current: the device address of the static array.
-cudaError_t scratch_for_current_device(int device, float** out)
+// Once per device, with that device current: the device address of the static array and the private
+// stream this entry point works on.
+cudaError_t scratch_for_current_device(int device, float** out, cudaStream_t* stream)
 {
 	std::lock_guard<std::mutex> lock(g_setup_mutex);
 	if (!g_scratch_addr[device])
@@ -49,11 +54,24 @@ cudaError_t scratch_for_current_device(int device, float** out)
 		float* p = nullptr;
 		cudaError_t e = cudaGetSymbolAddress((void**)&p, g_static_scratch);
 		if (e != cudaSuccess) return e;
+		cudaStream_t st = nullptr;
+		e = cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking);
+		if (e != cudaSuccess) return e;
+		g_stream[device] = st;
 		g_scratch_addr[device] = p;
 	}
 	*out = g_scratch_addr[device];
+	*stream = g_stream[device];
 	return cudaSuccess;
 }
+
+// Puts the caller's current device back when the entry point returns, whichever way it returns.
+struct DeviceRestore
+{
+	int prev = -1;
+	DeviceRestore() { if (cudaGetDevice(&prev) != cudaSuccess) { prev = -1; cudaGetLastError(); } }
+	~DeviceRestore() { if (prev >= 0) cudaSetDevice(prev); }
+};
 }  // namespace
 
 extern "C" const char* gl_matmul_static_error(void) { return g_static_err; }
@@ -67,6 +85,15 @@ extern "C" int gl_matmul_static(const float* d_a, int64_t a_sm, int64_t a_sk, co
 	{
 		snprintf(g_static_err, sizeof g_static_err, "gl_matmul_static: bad argument");
 		return GL_ERR_INVALID;
+	}
+	{
+		int major = 0;
+		if (gl_device_count() < 1 || cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device) != cudaSuccess || major != 10)
+		{
+			cudaGetLastError();
+			snprintf(g_static_err, sizeof g_static_err, "gl_matmul_static: device %d is not an sm_100 device (there is no CPU path)", device);
+			return GL_ERR_NO_DEVICE;
+		}
 	}
 	GemmArgs g;
 	memset(&g, 0, sizeof g);
@@ -92,9 +119,11 @@ extern "C" int gl_matmul_static(const float* d_a, int64_t a_sm, int64_t a_sk, co
 		         "each; use gl_matmul (which allocates) for larger products", ca, cb, (long long)GL_STATIC_MAX_OPERAND_FLOATS);
 		return GL_ERR_TOO_LARGE;
 	}
+	DeviceRestore restore;
 	cudaError_t e = cudaSetDevice(device);
 	float* scratch = nullptr;
-	if (e == cudaSuccess) e = scratch_for_current_device(device, &scratch);
+	cudaStream_t st = nullptr;
+	if (e == cudaSuccess) e = scratch_for_current_device(device, &scratch, &st);
 	if (e != cudaSuccess)
 	{
 		snprintf(g_static_err, sizeof g_static_err, "gl_matmul_static: set-up failed: %s", cudaGetErrorString(e));
@@ -104,13 +133,15 @@ extern "C" int gl_matmul_static(const float* d_a, int64_t a_sm, int64_t a_sk, co
 	float* a_lo = scratch + GL_STATIC_HEADER_FLOATS;
 	float* b_lo = a_lo + GL_STATIC_MAX_OPERAND_FLOATS;
 	// the status word must start at zero; the low parts are fully rewritten below
-	e = cudaMemsetAsync(flag, 0, GL_STATIC_HEADER_FLOATS * sizeof(float), 0);
-	if (e == cudaSuccess) e = launch_split_lo(d_a, a_lo, ca, 0);
-	if (e == cudaSuccess) e = launch_split_lo(d_b, b_lo, cb, 0);
-	if (e == cudaSuccess) e = launch_gemm_tc(g, a_lo, b_lo, flag, 0);
-	if (e == cudaSuccess) e = cudaStreamSynchronize(0);
+	// (all on the private stream: the product reads the caller's operands, so the caller's own work
+	// that produces them must have finished before this call, as with gl_matmul)
+	e = cudaMemsetAsync(flag, 0, GL_STATIC_HEADER_FLOATS * sizeof(float), st);
+	if (e == cudaSuccess) e = launch_split_lo(d_a, a_lo, ca, st);
+	if (e == cudaSuccess) e = launch_split_lo(d_b, b_lo, cb, st);
+	if (e == cudaSuccess) e = launch_gemm_tc(g, a_lo, b_lo, flag, st);
 	int hflag = 0;
-	if (e == cudaSuccess) e = cudaMemcpy(&hflag, flag, sizeof hflag, cudaMemcpyDeviceToHost);
+	if (e == cudaSuccess) e = cudaMemcpyAsync(&hflag, flag, sizeof hflag, cudaMemcpyDeviceToHost, st);
+	if (e == cudaSuccess) e = cudaStreamSynchronize(st);
 	if (e != cudaSuccess)
 	{
 		snprintf(g_static_err, sizeof g_static_err, "gl_matmul_static: %s", cudaGetErrorString(e));

@@ -28,12 +28,15 @@ __device__ __forceinline__ unsigned philox_u32(unsigned long long seed, unsigned
 	return c0;
 }
 
-__global__ void __launch_bounds__(256) synth_fill_kernel(float* out, long long n, unsigned long long seed,
+// out[j] = element (first + j) of the stream, j < n; `first` must be even for dist 1 (pairs of elements
+// share one Box-Muller draw).
+__global__ void __launch_bounds__(256) synth_fill_kernel(float* out, long long n, long long first, unsigned long long seed,
                                                           unsigned stream_id, int dist, float scale, float offset)
 {
 	const long long stride = (long long)gridDim.x * blockDim.x;
-	for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride)
+	for (long long j = (long long)blockIdx.x * blockDim.x + threadIdx.x; j < n; j += stride)
 	{
+		const long long i = first + j;
 		float v;
 		if (dist == 0)
 			v = __fmul_rn((float)(philox_u32(seed, stream_id, (unsigned long long)i) >> 8), 1.0f / 16777216.0f);
@@ -46,17 +49,18 @@ __global__ void __launch_bounds__(256) synth_fill_kernel(float* out, long long n
 			const double ang = 6.283185307179586 * (double)u2;
 			v = (float)(rad * ((i & 1) ? sin(ang) : cos(ang)));
 		}
-		out[i] = __fadd_rn(offset, __fmul_rn(scale, v));
+		out[j] = __fadd_rn(offset, __fmul_rn(scale, v));
 	}
 }
 
-cudaError_t launch_synth_fill(float* out, long long n, unsigned long long seed, unsigned stream_id, int dist,
+cudaError_t launch_synth_fill(float* out, long long n, long long first, unsigned long long seed, unsigned stream_id, int dist,
                               float scale, float offset, cudaStream_t s)
 {
+	if (first < 0 || (dist == 1 && (first & 1))) return cudaErrorInvalidValue;
 	long long blocks = (n + 255) / 256;
 	if (blocks > 148 * 16) blocks = 148 * 16;
 	if (blocks < 1) blocks = 1;
-	synth_fill_kernel<<<(unsigned)blocks, 256, 0, s>>>(out, n, seed, stream_id, dist, scale, offset);
+	synth_fill_kernel<<<(unsigned)blocks, 256, 0, s>>>(out, n, first, seed, stream_id, dist, scale, offset);
 	return cudaGetLastError();
 }
 

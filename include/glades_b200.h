@@ -207,10 +207,22 @@ int gl_get_epochs(const gl_net* net);
 /* Waits for the handle's queued device work (gl_train_window with out == NULL returns before the
  * device has finished) and reports a tensor-core kernel whose bounded wait ran out. */
 int gl_sync(gl_net* net);
+/* Self-test of the failure path of the bounded device waits: queues the gradient exchange's wait
+ * kernel on a flag that nothing raises, limited to max_cycles SM cycles (<= 4e9).  The wait gives
+ * up, returns and leaves code 99 in the handle's status word: the next gl_sync reports
+ * GL_ERR_TIMEOUT, later waits of the handle return at once, gl_set_weights clears the condition.
+ * The context stays usable throughout.  waited_ms (may be NULL): device time of the wait.
+ * No counterpart in the reference. */
+int gl_selftest_bounded_wait(gl_net* net, int64_t max_cycles, double* waited_ms);
 /* Diagnostics: kernels launched by this handle so far, and how many of them were tensor-core
  * (tcgen05) products.  No counterpart in the reference. */
 int64_t gl_kernel_launches(const gl_net* net);
 int64_t gl_tensor_core_launches(const gl_net* net);
+/* Diagnostics: tensor-core product launches of this process per tile variant -- out4[0] 128-wide
+ * tiles, [1] 256-wide tiles, [2] launches whose persistent CTAs walked more than one tile each,
+ * [3] launches of the data-parallel variant whose epilogue stores into the owning rank's memory.
+ * Lets a test assert which instantiation a shape ran on.  No counterpart in the reference. */
+void gl_tc_variant_counts(int64_t* out4);
 /* Diagnostic matrix product on device buffers, C[m][n] = sum_k A(m,k)*B(n,k) with
  * A(m,k) = d_a[m*a_sm + k*a_sk] and B(n,k) = d_b[n*b_sn + k*b_sk]; engine GL_GEMM_FFMA or
  * GL_GEMM_TCGEN05 (M % 128 == 0, N % 128 == 0, K % 16 == 0, each operand contiguous in k or in
@@ -226,9 +238,12 @@ int gl_matmul(const float* d_a, int64_t a_sm, int64_t a_sk, const float* d_b, in
  * GPU that loads the library; the call allocates nothing.  Limits: tensor-core engine only (shape
  * rules of gl_matmul), each operand at most 2 Mi floats as addressed by its strides (else
  * GL_ERR_TOO_LARGE).  All calls share the array: do not let two calls overlap on the GPU.  The first
- * call on a device looks the array's address up and should be made outside any stream capture.
- * The call returns after the product has finished.  gl_matmul_static_error() gives the text of this
- * entry point's last failure on the calling thread. */
+ * call on a device looks the array's address up and creates the private non-blocking stream that all
+ * of this entry point's GPU work runs on; make that first call outside any stream capture.  Because
+ * the stream is private and non-blocking, a call neither waits for nor stalls the caller's other
+ * streams -- so the operands must be complete (their producers synchronised) before the call.  The
+ * call returns after the product has finished and leaves the caller's current device unchanged.
+ * gl_matmul_static_error() gives the text of this entry point's last failure on the calling thread. */
 int gl_matmul_static(const float* d_a, int64_t a_sm, int64_t a_sk, const float* d_b, int64_t b_sn, int64_t b_sk,
                      float* d_c, int64_t ldc, int32_t m, int32_t n, int32_t k, int32_t device);
 const char* gl_matmul_static_error(void);
@@ -264,6 +279,12 @@ int gl_dp_set_window(gl_net* net, int32_t global_rows, int32_t first_global_pos)
 int gl_synth_fill(float* d_out, int64_t n, uint64_t seed, uint32_t stream, int32_t dist, float scale, float offset,
                   int32_t device);
 
+/* The same stream from element `first_index` on: d_out[j] = element first_index + j.  Ranks that fill
+ * their own row ranges of one global table use it so that the table does not depend on how many
+ * ranks there are.  first_index must be even for dist 1 (two elements share one Box-Muller draw). */
+int gl_synth_fill_at(float* d_out, int64_t n, int64_t first_index, uint64_t seed, uint32_t stream, int32_t dist,
+                     float scale, float offset, int32_t device);
+
 /* Expected rows from class labels, on the device: d_y[r][c] = (c == labels[r]) ? on : off
  * (the reference's one-hot encoder writes 0.99 / 0.01, GMath/OHE.cpp:159-198).  labels is a host
  * array. */
@@ -282,6 +303,8 @@ int gl_profile_read(gl_net* net, double* out6);
 /* ---- raw device helpers for callers that keep data resident ---------------------------- */
 int gl_device_alloc(void** d_ptr, int64_t bytes, int32_t device);
 int gl_device_free(void* d_ptr, int32_t device);
+/* Free and total device memory in bytes (cudaMemGetInfo). */
+int gl_device_mem_info(int32_t device, int64_t* free_bytes, int64_t* total_bytes);
 int gl_memcpy_h2d(void* d_dst, const void* h_src, int64_t bytes, int32_t device);
 int gl_memcpy_d2h(void* h_dst, const void* d_src, int64_t bytes, int32_t device);
 int gl_host_alloc_pinned(void** h_ptr, int64_t bytes);

@@ -55,6 +55,8 @@ def restate_lib():
         L.rs_window_grad.argtypes = [vp, i64, i32, i32, i32, vp, vp, i64]
         L.rs_window_apply.argtypes = [vp, vp, i32]
         L.rs_set_math_mode.argtypes = [i32]
+        L.rs_set_threads.argtypes = [i32]
+        L.rs_get_threads.restype = i32
         for name in ("rs_squash", "rs_act_der"):
             fn = getattr(L, name)
             fn.restype = f32
@@ -251,6 +253,14 @@ class Reference(_Base):
 
     def train_row(self, row):
         self.L.ref_train_row(self.h, row)
+
+
+def set_threads(t):
+    """Sets the OpenMP thread count of the restatement's loops (overriding a launcher's OMP_NUM_THREADS)
+    and returns the count they will really use (1 when the library was built without OpenMP)."""
+    L = restate_lib()
+    L.rs_set_threads(int(t))
+    return int(L.rs_get_threads())
 
 
 def synth_fill(n, seed, stream, dist, scale=1.0, offset=0.0):

@@ -49,6 +49,17 @@ typedef struct rs_net {
 static int g_math_mode = 0;
 void rs_set_math_mode(int m) { g_math_mode = m; }
 
+/* Threads of the OpenMP loops below.  A launcher may export OMP_NUM_THREADS=1 for its children (torchrun
+ * does); a caller that wants all cores says so here.  rs_get_threads reports what the loops will use. */
+#ifdef _OPENMP
+#include <omp.h>
+void rs_set_threads(int t) { if (t >= 1) omp_set_num_threads(t); }
+int rs_get_threads(void) { return omp_get_max_threads(); }
+#else
+void rs_set_threads(int t) { (void)t; }
+int rs_get_threads(void) { return 1; }
+#endif
+
 static float f_exp(float v) { return g_math_mode ? (float)exp((double)v) : expf(v); }
 static float f_tanh(float v) { return g_math_mode ? (float)tanh((double)v) : tanhf(v); }
 static float f_log(float v) { return g_math_mode ? (float)log((double)v) : logf(v); }

@@ -418,6 +418,15 @@ def test_synth_fill_matches_cpu_generator(g, oracle):
     L.gl_device_free(p, 0)
 
 
+def near_tie_rows(outputs, tol=2e-4):
+    """Rows whose two largest outputs lie within `tol` (relative to the larger, floor 1): the only rows on
+    which two correct fp32 evaluations with differently ordered sums may predict different classes."""
+    if outputs.shape[1] < 2:
+        return 0
+    top = np.sort(outputs.astype(np.float64), axis=1)[:, -2:]
+    return int(np.sum(top[:, 1] - top[:, 0] <= tol * np.maximum(1.0, np.abs(top[:, 1]))))
+
+
 SMALL_FUSED_CASES = [
     # sizes, acts, out, rows, mb, momentum, wd1, wd2, bias_rule, epochs
     ([10, 32, 32, 1], ["tanh", "tanh", "sigmoid"], "regression", 1024, 32, 0.0, 0.0, 0.0, 0, 3),
@@ -462,8 +471,11 @@ def test_small_network_fused_epochs_vs_restatement(g, oracle, case):
     for ep in range(epochs):
         cm = np.zeros((sizes[-1], sizes[-1]), np.int32)
         cost = acc = 0.0
+        ties = 0
         for r0 in range(0, rows, mb):
             cnt = min(mb, rows - r0)
+            if out != "regression" and ep == epochs - 1:
+                ties += near_tie_rows(S.forward_block(r0, cnt)[0])  # this window's predictions, before its update
             gr = S.window_grad(r0, cnt, confusion=cm)
             S.window_apply(gr, cnt)
             cost += gr[-2]
@@ -477,8 +489,10 @@ def test_small_network_fused_epochs_vs_restatement(g, oracle, case):
     assert abs(m.total_error - cost) <= 2e-5 * max(1.0, abs(cost))
     assert abs(m.total_accuracy - acc / (rows * sizes[-1])) <= 2e-3
     if out != "regression":
+        # identical counts, except that a row whose two best outputs tie within the tolerance may land in
+        # another cell (one count less in one cell, one more in another)
         diff = int(np.abs(net.confusion() - cm).sum())
-        assert diff <= (2 if epochs * rows > 200 else 0), "confusion counts differ by %d" % diff
+        assert diff <= 2 * ties, "confusion counts differ by %d with %d near-tie rows" % (diff, ties)
     assert net.epochs() == epochs
     net.close()
 
@@ -520,8 +534,11 @@ def test_grid_fused_epochs_vs_restatement(g, oracle, case):
     for ep in range(epochs):
         cm = np.zeros((sizes[-1], sizes[-1]), np.int32)
         cost = acc = 0.0
+        ties = 0
         for r0 in range(0, rows, mb):
             cnt = min(mb, rows - r0)
+            if out != "regression" and ep == epochs - 1:
+                ties += near_tie_rows(S.forward_block(r0, cnt)[0])  # this window's predictions, before its update
             gr = S.window_grad(r0, cnt, confusion=cm)
             S.window_apply(gr, cnt)
             cost += gr[-2]
@@ -536,7 +553,7 @@ def test_grid_fused_epochs_vs_restatement(g, oracle, case):
     assert abs(m.total_accuracy - acc / (rows * sizes[-1])) <= 2e-3
     if out != "regression":
         diff = int(np.abs(net.confusion() - cm).sum())
-        assert diff <= 2, "confusion counts differ by %d" % diff
+        assert diff <= 2 * ties, "confusion counts differ by %d with %d near-tie rows" % (diff, ties)
     assert net.epochs() == epochs and not m.nonfinite
     # the last row's predictions, as the reference's getResults() hands them out
     assert np.all(np.isfinite(net.last_outputs()))

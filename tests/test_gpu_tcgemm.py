@@ -45,6 +45,67 @@ def test_tc_matmul_all_layouts(g, a_mn, b_mn, M, N, K):
         L.gl_device_free(p, 0)
 
 
+def _matmul_case(g, M, N, K, a_mn, b_mn, seed, positive=False):
+    """One gl_matmul on the tensor-core engine against the float64 product; returns the worst error in
+    units of sum_k |a||b| and the change of the per-variant launch counters."""
+    L = g.lib()
+    rng = np.random.default_rng(seed)
+    draw = (lambda s: rng.random(s, dtype=np.float32) + 0.25) if positive else \
+        (lambda s: rng.standard_normal(s, dtype=np.float32))
+    A = draw((M, K))
+    B = draw((N, K))
+    A_mem = np.ascontiguousarray(A.T) if a_mn else A
+    B_mem = np.ascontiguousarray(B.T) if b_mn else B
+    a_sm, a_sk = (1, M) if a_mn else (K, 1)
+    b_sn, b_sk = (1, N) if b_mn else (K, 1)
+    dA, dB = _dev(L, A_mem), _dev(L, B_mem)
+    out = np.full((M, N), np.nan, np.float32)
+    dC = _dev(L, out)
+    before = g.tc_variant_counts()
+    st = L.gl_matmul(dA, a_sm, a_sk, dB, b_sn, b_sk, dC, N, M, N, K, g.GEMM_TCGEN05, 0)
+    assert st == 0, L.gl_last_error()
+    after = g.tc_variant_counts()
+    assert L.gl_memcpy_d2h(out.ctypes.data_as(C.c_void_p), dC, out.nbytes, 0) == 0
+    for p in (dA, dB, dC):
+        L.gl_device_free(p, 0)
+    ref = A.astype(np.float64) @ B.astype(np.float64).T
+    bound = np.abs(A).astype(np.float64) @ np.abs(B).astype(np.float64).T
+    err = float(np.max(np.abs(out.astype(np.float64) - ref) / bound))
+    return err, [a - b for a, b in zip(after, before)]
+
+
+# The variant the wide-MLP and inference steps run on: 256-wide tiles, persistent CTAs that walk several
+# tiles each in bands of 16 row tiles, pipeline and accumulator barriers that keep counting across tiles,
+# deep K.  (M, N, K, A MN-major, B MN-major, all-positive operands)
+WIDE_CASES = [
+    # 320 wide tiles on 148 CTAs, all four operand layouts, shallow K: the tile walk and the barrier
+    # phases across tiles (2 to 3 tiles per CTA, a partial last band: 32 row tiles = 2 bands of 16)
+    (4096, 2560, 256, 0, 0, False), (4096, 2560, 256, 0, 1, False), (4096, 2560, 256, 1, 1, False),
+    (4096, 2560, 256, 1, 0, False),
+    # row-tile count that is not a multiple of the band (24 = 16 + 8): the short last band
+    (3072, 1536, 272, 0, 0, False),
+    # the layer products of the wide-MLP window step at 2048 rows: forward (K-major x K-major), error
+    # propagation (weights read MN-major), weight gradient (both operands MN-major, K = rows)
+    (2048, 4096, 4096, 0, 0, False), (2048, 4096, 4096, 0, 1, False), (4096, 4096, 2048, 1, 1, False),
+    # the first layer's gradient at the full 8192-row window: K = 8192, 128 wide tiles
+    (4096, 1024, 8192, 1, 1, False),
+    # all-positive operands: the worst case for the tensor core's truncating accumulation at deep K
+    (2048, 2560, 4096, 0, 0, True),
+    # one tile per CTA but 256 wide and deep: 80 wide tiles
+    (2048, 1280, 4096, 0, 0, False),
+]
+
+
+@pytest.mark.parametrize("M,N,K,a_mn,b_mn,positive", WIDE_CASES)
+def test_tc_matmul_wide_persistent_variant(g, M, N, K, a_mn, b_mn, positive):
+    err, dc = _matmul_case(g, M, N, K, a_mn, b_mn, seed=M + 3 * N + 7 * K + a_mn + 2 * b_mn, positive=positive)
+    assert err <= 4e-6, "error %.3g of sum|a||b|" % err
+    tiles = (M // 128) * (N // 256)
+    assert dc[1] == 1 and dc[0] == 0, "the 256-wide instantiation did not run: %r" % (dc,)
+    if tiles > 148:
+        assert dc[2] == 1, "%d tiles but no CTA walked more than one" % tiles
+
+
 def test_tc_matmul_rejects_odd_shapes(g):
     L = g.lib()
     a = np.zeros((100, 32), np.float32)
@@ -111,3 +172,91 @@ def test_cta_pair_variant_in_a_subprocess():
     r = subprocess.run([sys.executable, "-m", "pytest", os.path.abspath(__file__), "-x", "-q", "-m", "gpu", "-k",
                         "all_layouts and 256"], capture_output=True, text=True, env=env, timeout=600)
     assert r.returncode == 0, r.stdout[-1500:] + r.stderr[-500:]
+
+
+def _onehot(rows, n, labels):
+    y = np.zeros((rows, n), np.float32)
+    y[np.arange(rows), labels] = 1.0
+    return y
+
+
+def test_wide_mlp_window_on_the_benchmarked_variant_vs_restatement(g, oracle):
+    """One batched-mode window of the wide-MLP student itself (1024-4096-4096-1024, ReLU/ReLU/softmax,
+    cross-entropy, lr 1e-2, weights U(+-1/sqrt(n_in))) on 1024 rows, against the double-accumulating CPU
+    restatement: loss, every updated weight within 1e-5 of the largest weight, identical predicted
+    classes.  At this size the layer products run on the 256-wide persistent tiles (the instantiation
+    the benchmark measures), several tiles per CTA for the 4096 x 4096 gradient."""
+    sizes = [1024, 4096, 4096, 1024]
+    rows = 1024
+    rng = np.random.default_rng(404)
+    x = rng.standard_normal((rows, sizes[0]), dtype=np.float32)
+    y = _onehot(rows, sizes[-1], rng.integers(0, sizes[-1], rows))
+    w = np.concatenate([rng.uniform(-1, 1, sizes[i] * sizes[i + 1]).astype(np.float32) / np.float32(np.sqrt(sizes[i]))
+                        for i in range(3)])
+    b = np.array([0.01, -0.02], np.float32)
+    d = g.make_desc(sizes, ["relu", "relu", "softmax"], "classification", batch=rows, lr=1e-2, mode=g.MODE_BATCHED)
+    net = g.Net(d)
+    net.set_weights(w, b)
+    net.set_data(x, y)
+    S = oracle.Restate(d, x, y, g.Metrics)
+    S.set_weights(w, b)
+    before = g.tc_variant_counts()
+    m = net.train_window(0, rows)
+    dc = [a - c for a, c in zip(g.tc_variant_counts(), before)]
+    assert dc[1] >= 6 and dc[2] >= 1, "expected the 256-wide persistent variant, saw %r" % (dc,)
+    gr = S.window_grad(0, rows)
+    S.window_apply(gr, rows)
+    wg, bg = net.get_weights()
+    ws, bs = S.get_weights()
+    lo = 0
+    for l in range(3):
+        hi = lo + sizes[l] * sizes[l + 1]
+        # the update itself (new - old) carries the whole gradient: compare it, not only the weights
+        ug = wg[lo:hi].astype(np.float64) - w[lo:hi]
+        us = ws[lo:hi].astype(np.float64) - w[lo:hi]
+        assert np.max(np.abs(wg[lo:hi].astype(np.float64) - ws[lo:hi])) <= 1e-5 * np.max(np.abs(ws[lo:hi])), "layer %d weights" % l
+        assert np.max(np.abs(ug - us)) <= 2e-4 * np.max(np.abs(us)) + 1e-9, "layer %d update" % l
+        lo = hi
+    assert np.allclose(bg, bs, rtol=1e-4, atol=1e-7)
+    assert abs(m.total_error - gr[-2]) <= 1e-5 * max(1.0, abs(gr[-2]))
+    # predictions from identical weights: same classes for every row
+    S.set_weights(wg, bg)
+    out_g, am_g, _ = net.forward(0, rows)
+    out_s, am_s = S.forward_block(0, rows)
+    assert np.max(np.abs(out_g - out_s)) <= 1e-5 * max(1.0, float(np.max(np.abs(out_s))))
+    assert np.array_equal(am_g, am_s)
+    net.close()
+    S.close()
+
+
+def test_inference_net_forward_on_the_benchmarked_variant_vs_restatement(g, oracle):
+    """Forward pass of the batched-inference net (784-2048-2048-10, ReLU/ReLU/softmax, weights
+    U(-0.05, 0.05), rows U(0,1)) on 2048 rows against the restatement: probabilities within 1e-5 and the
+    same predicted class for every row.  The two hidden products run on the 256-wide tiles."""
+    sizes = [784, 2048, 2048, 10]
+    rows = 2048
+    rng = np.random.default_rng(505)
+    x = rng.random((rows, sizes[0]), dtype=np.float32)
+    y = np.full((rows, sizes[-1]), 0.01, np.float32)
+    nw = sum(sizes[i] * sizes[i + 1] for i in range(3))
+    w = rng.uniform(-0.05, 0.05, nw).astype(np.float32)
+    d = g.make_desc(sizes, ["relu", "relu", "softmax"], "classification", batch=rows, lr=0.0, mode=g.MODE_BATCHED)
+    net = g.Net(d)
+    net.set_weights(w, np.array([0.01, 0.02], np.float32))
+    net.set_data(x, y)
+    S = oracle.Restate(d, x, y, g.Metrics)
+    S.set_weights(w, np.array([0.01, 0.02], np.float32))
+    before = g.tc_variant_counts()
+    out_g, am_g, _ = net.forward(0, rows)
+    dc = [a - c for a, c in zip(g.tc_variant_counts(), before)]
+    assert dc[1] == 2, "the two hidden products should run on 256-wide tiles, saw %r" % (dc,)
+    out_s, am_s = S.forward_block(0, rows)
+    assert np.max(np.abs(out_g - out_s)) <= 1e-5
+    diff = np.nonzero(am_g != am_s)[0]
+    # a row may only differ where its two best classes tie within the tolerance
+    for r in diff:
+        top = np.sort(out_s[r])[-2:]
+        assert top[1] - top[0] <= 2e-5, "row %d: classes differ with a margin of %g" % (r, top[1] - top[0])
+    assert diff.size == 0 or diff.size <= 2
+    net.close()
+    S.close()

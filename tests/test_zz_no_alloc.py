@@ -63,6 +63,32 @@ def test_static_scratch_product_matches_allocating_product_twice(g):
         assert float(np.max(np.abs(got - ref) / bound)) <= 4e-6
 
 
+def _free_bytes(L):
+    f, t = C.c_int64(), C.c_int64()
+    assert L.gl_device_mem_info(0, C.byref(f), C.byref(t)) == 0
+    return f.value
+
+
+def test_static_scratch_product_allocates_no_device_memory(g):
+    """After the first call on a device (which looks the array up and creates the private stream), a call
+    must leave the device's free memory exactly as it found it; the allocating entry point is the control
+    (its scratch is freed again, so it too ends where it started, but only this one never moves it)."""
+    L = g.lib()
+    rng = np.random.default_rng(7)
+    M, N, K = 256, 256, 512
+    A = rng.standard_normal((M, K)).astype(np.float32)
+    B = rng.standard_normal((N, K)).astype(np.float32)
+    dA, dB = _dev(L, A), _dev(L, B)
+    dC = _dev(L, np.zeros((M, N), np.float32))
+    assert L.gl_matmul_static(dA, K, 1, dB, K, 1, dC, N, M, N, K, 0) == 0, L.gl_matmul_static_error()
+    before = _free_bytes(L)
+    for _ in range(3):
+        assert L.gl_matmul_static(dA, K, 1, dB, K, 1, dC, N, M, N, K, 0) == 0, L.gl_matmul_static_error()
+        assert _free_bytes(L) == before
+    for p in (dA, dB, dC):
+        L.gl_device_free(p, 0)
+
+
 def test_static_scratch_product_rejects_oversize_and_odd_shapes(g):
     L = g.lib()
     small = np.zeros((128, 32), np.float32)
