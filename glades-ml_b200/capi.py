@@ -56,10 +56,11 @@ class Metrics(C.Structure):
 
 
 def make_desc(sizes, acts, out_type, batch=1, lr=0.01, momentum=0.0, wd1=0.0, wd2=0.0, params=None,
-              mode=MODE_REFERENCE, bias_rule=BIAS_MEAN, gemm=GEMM_AUTO, device=0):
+              mode=MODE_REFERENCE, bias_rule=BIAS_MEAN, gemm=GEMM_AUTO, device=0, p_dropout=0.0):
     """Descriptor for layer sizes n_0..n_{H+1}; acts[l] is the activation producing layer l+1.
 
-    lr / momentum / wd1 / wd2 / params may be scalars or per-weight-layer lists (NNInfo index l)."""
+    lr / momentum / wd1 / wd2 / params may be scalars or per-weight-layer lists (NNInfo index l);
+    p_dropout a scalar or a list per node layer 0..H (input and hidden layers)."""
     d = NetDesc()
     nl = len(sizes)
     assert 3 <= nl <= GL_MAX_WEIGHT_LAYERS + 1 and len(acts) == nl - 1
@@ -75,7 +76,7 @@ def make_desc(sizes, acts, out_type, batch=1, lr=0.01, momentum=0.0, wd1=0.0, wd
         d.momentum[l] = per(momentum, l)
         d.wd1[l] = per(wd1, l)
         d.wd2[l] = per(wd2, l)
-        d.p_dropout[l] = 0.0
+        d.p_dropout[l] = per(p_dropout, l)
         a = acts[l]
         d.activation[l] = ACT[a] if isinstance(a, str) else int(a)
         d.act_param[l] = per(params, l) if params is not None else 0.0

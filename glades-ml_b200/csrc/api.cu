@@ -162,6 +162,17 @@ struct gl_net
 	float* dHist = nullptr;
 	int* dHistLen = nullptr;
 	float* dScratch = nullptr;
+	// reference mode with dropout: per-edge history lengths and last deltas, the error accumulators that
+	// survive a row, and one epoch's node flags (drawn on the host with rand(), in the reference's order)
+	bool dropout = false;
+	int maskStride = 0;
+	int* dHlen = nullptr;
+	float* dHlast = nullptr;
+	float* dErrState = nullptr;
+	unsigned char* dMasks = nullptr;
+	int64_t maskCapRows = 0;
+	std::vector<unsigned char> hMasks;
+	std::vector<unsigned char> dropFlags;  // the flags of the current row, carried over where a layer draws nothing
 	// data
 	const float* dX = nullptr;
 	const float* dY = nullptr;
@@ -287,7 +298,9 @@ extern "C" int gl_create(const gl_net_desc* d, gl_net** out)
 	if (d->mode != GL_MODE_REFERENCE && d->mode != GL_MODE_BATCHED) return fail(GL_ERR_INVALID, "gl_create: bad mode");
 	for (int l = 0; l <= H; ++l)
 	{
-		if (d->p_dropout[l] != 0.0f) return fail(GL_ERR_INVALID, "gl_create: dropout is not supported on this path");
+		if (d->p_dropout[l] != 0.0f && d->mode != GL_MODE_REFERENCE)
+			return fail(GL_ERR_INVALID, "gl_create: dropout runs in reference mode only (p_dropout[%d] = %g)", l, (double)d->p_dropout[l]);
+		if (!(d->p_dropout[l] >= 0.0f)) return fail(GL_ERR_INVALID, "gl_create: p_dropout[%d] is negative or not a number", l);
 		const int a = d->activation[l];
 		if (a < 0 || a > GL_ACT_SOFTMAX) return fail(GL_ERR_INVALID, "gl_create: bad activation id %d", a);
 		if (a == GL_ACT_SOFTMAX && (l != H || d->mode != GL_MODE_BATCHED))
@@ -332,6 +345,21 @@ extern "C" int gl_create(const gl_net_desc* d, gl_net** out)
 		CU(cudaMemset(n->dHist, 0, (size_t)n->nw * d->batch_size * sizeof(float)));
 		CU(cudaMalloc(&n->dHistLen, sizeof(int)));
 		CU(cudaMemset(n->dHistLen, 0, sizeof(int)));
+		for (int l = 0; l <= H; ++l)
+		{
+			if (d->p_dropout[l] != 0.0f) n->dropout = true;
+			n->maskStride += d->sizes[l];
+		}
+		if (n->dropout)
+		{
+			CU(cudaMalloc(&n->dHlen, (size_t)n->nw * sizeof(int)));
+			CU(cudaMemset(n->dHlen, 0, (size_t)n->nw * sizeof(int)));
+			CU(cudaMalloc(&n->dHlast, (size_t)n->nw * sizeof(float)));
+			CU(cudaMemset(n->dHlast, 0, (size_t)n->nw * sizeof(float)));
+			CU(cudaMalloc(&n->dErrState, (size_t)n->total_nodes * sizeof(float)));
+			CU(cudaMemset(n->dErrState, 0, (size_t)n->total_nodes * sizeof(float)));
+			n->dropFlags.assign((size_t)n->maskStride, 0);
+		}
 	}
 	else
 	{
@@ -410,6 +438,7 @@ extern "C" int gl_destroy(gl_net* n)
 	for (int l = 0; l <= GL_MAX_WEIGHT_LAYERS; ++l) if (n->evGrad[l]) cudaEventDestroy(n->evGrad[l]);
 	if (n->evComm) cudaEventDestroy(n->evComm);
 	free_work(n);
+	cudaFree(n->dHlen); cudaFree(n->dHlast); cudaFree(n->dErrState); cudaFree(n->dMasks);
 	cudaFree(n->dpRec);
 	cudaFree(n->dWlo);
 	cudaFree(n->dW); cudaFree(n->dBias); cudaFree(n->dG); cudaFree(n->dBscale); cudaFree(n->dFlags);
@@ -504,6 +533,12 @@ extern "C" int gl_set_weights(gl_net* n, const float* w, const float* bias)
 		CU(cudaMemsetAsync(n->dHist, 0, (size_t)n->nw * n->d.batch_size * sizeof(float), n->stream));
 		CU(cudaMemsetAsync(n->dHistLen, 0, sizeof(int), n->stream));
 	}
+	if (n->dropout)
+	{
+		CU(cudaMemsetAsync(n->dHlen, 0, (size_t)n->nw * sizeof(int), n->stream));
+		CU(cudaMemsetAsync(n->dHlast, 0, (size_t)n->nw * sizeof(float), n->stream));
+		CU(cudaMemsetAsync(n->dErrState, 0, (size_t)n->total_nodes * sizeof(float), n->stream));
+	}
 	CU(cudaMemsetAsync(n->dFlags, 0, 4 * sizeof(int), n->stream));
 	if (n->dpArena)  // the owners' sticky "non-finite weight" words belong to the old weights
 		CU(cudaMemsetAsync(n->dpArena + DP_WORD_BAD * sizeof(unsigned), 0, DP_MAX_WORLD * sizeof(unsigned), n->stream));
@@ -569,9 +604,21 @@ extern "C" int gl_save_state(gl_net* n, const char* path)
 	if (h.hist_floats)
 		CU(cudaMemcpy(buf.data() + n->nw + GL_MAX_WEIGHT_LAYERS, n->dHist, (size_t)h.hist_floats * sizeof(float),
 		              cudaMemcpyDeviceToHost));
+	// a network with dropout also carries every edge's own history length and last delta, and the error
+	// accumulators that survive a row: format "S2", the three arrays appended
+	std::vector<float> extra;
+	if (n->dropout)
+	{
+		memcpy(h.magic, "GLB200S2", 8);
+		extra.resize((size_t)2 * n->nw + (size_t)n->total_nodes);
+		CU(cudaMemcpy(extra.data(), n->dHlen, (size_t)n->nw * sizeof(int), cudaMemcpyDeviceToHost));
+		CU(cudaMemcpy(extra.data() + n->nw, n->dHlast, (size_t)n->nw * sizeof(float), cudaMemcpyDeviceToHost));
+		CU(cudaMemcpy(extra.data() + 2 * n->nw, n->dErrState, (size_t)n->total_nodes * sizeof(float), cudaMemcpyDeviceToHost));
+	}
 	FILE* f = fopen(path, "wb");
 	if (!f) return fail(GL_ERR_INVALID, "gl_save_state: cannot open %s for writing", path);
-	const bool ok = fwrite(&h, sizeof h, 1, f) == 1 && fwrite(buf.data(), sizeof(float), buf.size(), f) == buf.size();
+	const bool ok = fwrite(&h, sizeof h, 1, f) == 1 && fwrite(buf.data(), sizeof(float), buf.size(), f) == buf.size() &&
+	                (extra.empty() || fwrite(extra.data(), sizeof(float), extra.size(), f) == extra.size());
 	if (fclose(f) != 0 || !ok) return fail(GL_ERR_INVALID, "gl_save_state: short write to %s", path);
 	return GL_OK;
 }
@@ -583,10 +630,17 @@ extern "C" int gl_load_state(gl_net* n, const char* path)
 	FILE* f = fopen(path, "rb");
 	if (!f) return fail(GL_ERR_INVALID, "gl_load_state: cannot open %s", path);
 	StateHeader h;
-	if (fread(&h, sizeof h, 1, f) != 1 || memcmp(h.magic, "GLB200S1", 8) != 0)
+	if (fread(&h, sizeof h, 1, f) != 1 || (memcmp(h.magic, "GLB200S1", 8) != 0 && memcmp(h.magic, "GLB200S2", 8) != 0))
 	{
 		fclose(f);
 		return fail(GL_ERR_INVALID, "gl_load_state: %s is not a state file", path);
+	}
+	const bool with_dropout = memcmp(h.magic, "GLB200S2", 8) == 0;
+	if (with_dropout != n->dropout)
+	{
+		fclose(f);
+		return fail(GL_ERR_INVALID, "gl_load_state: %s was written by a network %s dropout, this one is %s", path,
+		            with_dropout ? "with" : "without", n->dropout ? "with" : "without");
 	}
 	bool same = h.n_layers == n->d.n_layers && h.nw == n->nw && h.mode == n->d.mode && h.batch_size == n->d.batch_size;
 	for (int l = 0; same && l <= n->H + 1; ++l) same = h.sizes[l] == n->d.sizes[l];
@@ -597,7 +651,9 @@ extern "C" int gl_load_state(gl_net* n, const char* path)
 		return fail(GL_ERR_INVALID, "gl_load_state: %s was written by a network of another shape, mode or minibatch size", path);
 	}
 	std::vector<float> buf((size_t)n->nw + GL_MAX_WEIGHT_LAYERS + (size_t)h.hist_floats);
-	const bool ok = fread(buf.data(), sizeof(float), buf.size(), f) == buf.size();
+	std::vector<float> extra(with_dropout ? (size_t)2 * n->nw + (size_t)n->total_nodes : 0);
+	const bool ok = fread(buf.data(), sizeof(float), buf.size(), f) == buf.size() &&
+	                (extra.empty() || fread(extra.data(), sizeof(float), extra.size(), f) == extra.size());
 	fclose(f);
 	if (!ok) return fail(GL_ERR_INVALID, "gl_load_state: %s is truncated", path);
 	// the stored biases are indexed by layer (entry 0 unused); gl_set_weights takes them from hidden layer 1 on.
@@ -608,6 +664,12 @@ extern "C" int gl_load_state(gl_net* n, const char* path)
 		CU(cudaMemcpy(n->dHist, buf.data() + n->nw + GL_MAX_WEIGHT_LAYERS, (size_t)h.hist_floats * sizeof(float),
 		              cudaMemcpyHostToDevice));
 		CU(cudaMemcpy(n->dHistLen, &h.hist_len, sizeof(int), cudaMemcpyHostToDevice));
+	}
+	if (with_dropout)
+	{
+		CU(cudaMemcpy(n->dHlen, extra.data(), (size_t)n->nw * sizeof(int), cudaMemcpyHostToDevice));
+		CU(cudaMemcpy(n->dHlast, extra.data() + n->nw, (size_t)n->nw * sizeof(float), cudaMemcpyHostToDevice));
+		CU(cudaMemcpy(n->dErrState, extra.data() + 2 * n->nw, (size_t)n->total_nodes * sizeof(float), cudaMemcpyHostToDevice));
 	}
 	n->epochs = h.epochs;
 	return GL_OK;
@@ -695,6 +757,74 @@ static int finish_metrics(gl_net* n, gl_metrics* out, float tot_err, float tot_a
 
 // ------------------------------------------------------------------------------------------------
 // reference mode
+
+// Layer::generateDropout (State/layer.cpp:102-134) for one layer of one row: the rate is the integer
+// percentage int(p * 100.0f); a rate < 0 or >= 100 draws nothing and leaves the flags as they are;
+// otherwise one rand() per node, dropped when rand() % 100 + 1 <= rate, the whole layer drawn again
+// while every node came out dropped.
+static void draw_layer_flags(unsigned char* flag, int size, float p)
+{
+	const int rate = (int)(p * 100.0f);
+	if (rate < 0 || rate >= 100) return;
+	bool all;
+	do
+	{
+		all = true;
+		for (int i = 0; i < size; ++i)
+		{
+			const int dart = (rand() % 100) + 1;
+			if (dart <= rate) flag[i] = 1;
+			else
+			{
+				flag[i] = 0;
+				all = false;
+			}
+		}
+	} while (all);
+}
+
+// LayerBuilder::scrambleDropout (State/LayerBuilder.cpp:497-523) for `rows` consecutive rows: per row the
+// input layer first, then the hidden layers in order -- the C library's rand() is consumed exactly as the
+// reference consumes it, so after the same srand() the same nodes drop.  Leaves the flags on the device.
+static int draw_and_upload_masks(gl_net* n, int64_t rows)
+{
+	const size_t stride = (size_t)n->maskStride;
+	n->hMasks.resize((size_t)rows * stride);
+	for (int64_t r = 0; r < rows; ++r)
+	{
+		int off = 0;
+		for (int j = 0; j <= n->H; ++j)
+		{
+			draw_layer_flags(n->dropFlags.data() + off, n->d.sizes[j], n->d.p_dropout[j]);
+			off += n->d.sizes[j];
+		}
+		memcpy(n->hMasks.data() + (size_t)r * stride, n->dropFlags.data(), stride);
+	}
+	if (n->maskCapRows < rows)
+	{
+		cudaFree(n->dMasks);
+		n->dMasks = nullptr;
+		n->maskCapRows = 0;
+		CU(cudaMalloc(&n->dMasks, (size_t)rows * stride));
+		n->maskCapRows = rows;
+	}
+	CU(cudaMemcpyAsync(n->dMasks, n->hMasks.data(), (size_t)rows * stride, cudaMemcpyHostToDevice, n->stream));
+	CU(cudaStreamSynchronize(n->stream));  // hMasks is pageable and reused by the next epoch
+	return 0;
+}
+
+static void fill_dropout_args(gl_net* n, RefTrainArgs& a)
+{
+	a.masks = n->dMasks;
+	a.mask_stride = n->maskStride;
+	for (int l = 0; l <= n->H; ++l)
+	{
+		a.hlen[l] = n->dHlen + n->woff[l];
+		a.hlast[l] = n->dHlast + n->woff[l];
+	}
+	a.err_state = n->dErrState;
+}
+
 static int ref_train(gl_net* n, int n_epochs, gl_metrics* out)
 {
 	if (n->sumsFCap < n_epochs)
@@ -721,13 +851,41 @@ static int ref_train(gl_net* n, int n_epochs, gl_metrics* out)
 	a.weights_in_smem = ref_train_smem_bytes(a.net, true) <= (size_t)227 * 1024;
 	if (!a.weights_in_smem && ref_train_smem_bytes(a.net, false) > (size_t)227 * 1024)
 		return fail(GL_ERR_TOO_LARGE, "reference mode: %d nodes do not fit the per-sample shared-memory vectors", n->total_nodes);
+	float ms = 0;
+	int launches = 1;
+	if (n->dropout)
+	{
+		// one launch per epoch: each epoch's node flags are drawn (rand(), the reference's order) before it
+		if (ref_train_dropout_smem_bytes(a.net) > (size_t)227 * 1024)
+			return fail(GL_ERR_TOO_LARGE, "reference mode with dropout: %d nodes do not fit the per-sample shared-memory vectors", n->total_nodes);
+		a.train = 1;
+		launches = 0;
+		for (int ep = 0; ep < n_epochs && !n->stop; ++ep)
+		{
+			if (int r = draw_and_upload_masks(n, n->rows)) return r;
+			fill_dropout_args(n, a);
+			a.epoch_sums = n->dSumsF;
+			CU(cudaEventRecord(n->ev0, n->stream));
+			CU(launch_ref_train(a, n->stream));
+			CU(cudaEventRecord(n->ev1, n->stream));
+			CU(cudaStreamSynchronize(n->stream));
+			float t = 0;
+			CU(cudaEventElapsedTime(&t, n->ev0, n->ev1));
+			ms += t;
+			++launches;
+			n->epochs += 1;
+		}
+		n->launches += launches;
+		float sums[2];
+		CU(cudaMemcpy(sums, n->dSumsF, sizeof sums, cudaMemcpyDeviceToHost));
+		return finish_metrics(n, out, sums[0], sums[1], n->rows, ms, launches, true);
+	}
 	CU(cudaEventRecord(n->ev0, n->stream));
 	CU(launch_ref_train(a, n->stream));
 	CU(cudaEventRecord(n->ev1, n->stream));
 	CU(cudaStreamSynchronize(n->stream));
 	n->launches += 1;
 	n->epochs += n_epochs;
-	float ms = 0;
 	CU(cudaEventElapsedTime(&ms, n->ev0, n->ev1));
 	float sums[2];
 	CU(cudaMemcpy(sums, n->dSumsF + 2 * (n_epochs - 1), sizeof sums, cudaMemcpyDeviceToHost));
@@ -1611,9 +1769,91 @@ extern "C" int gl_train_epochs(gl_net* n, int32_t n_epochs, gl_metrics* out)
 }
 
 // ------------------------------------------------------------------------------------------------
+// Reference mode with dropout: the test pass draws node flags per row too (SGDHelper calls scrambleDropout
+// whatever the run type, network.cpp:408-411).  One launch of the sample-loop kernel without its backward
+// half; outputs and activations come back through temporary device buffers.
+static int ref_forward_dropout(gl_net* n, const float* X, const float* Y, int64_t rows, int64_t metric_rows, float* outputs,
+                               int32_t* argmax, float* acts_last, gl_metrics* out)
+{
+	if (int r = draw_and_upload_masks(n, rows)) return r;
+	if (n->sumsFCap < 1)
+	{
+		CU(cudaMalloc(&n->dSumsF, 2 * sizeof(float)));
+		n->sumsFCap = 1;
+	}
+	RefTrainArgs a;
+	memset(&a, 0, sizeof a);
+	a.net = make_view(n);
+	if (ref_train_dropout_smem_bytes(a.net) > (size_t)227 * 1024)
+		return fail(GL_ERR_TOO_LARGE, "reference mode with dropout: %d nodes do not fit the per-sample shared-memory vectors", n->total_nodes);
+	for (int l = 0; l <= n->H; ++l) a.hist[l] = n->dHist + n->woff[l] * n->d.batch_size;
+	a.hist_len = n->dHistLen;
+	a.X = X;
+	a.Y = Y;
+	a.rows = rows;
+	a.data_rows = metric_rows;
+	a.n_epochs = 1;
+	a.epoch_sums = n->dSumsF;
+	a.confusion = n->dConf;
+	a.last_out = n->dLastOut;
+	a.flags = n->dFlags;
+	a.train = 0;
+	fill_dropout_args(n, a);
+	float* dOut = nullptr;
+	float* dActs = nullptr;
+	const bool want_out = outputs || argmax;
+	if (want_out) CU(cudaMalloc(&dOut, (size_t)rows * n->n_out * sizeof(float)));
+	cudaError_t e = cudaSuccess;
+	if (acts_last) e = cudaMalloc(&dActs, (size_t)(n->total_nodes - n->d.sizes[0]) * sizeof(float));
+	a.outputs = dOut;
+	a.acts_out = dActs;
+	if (e == cudaSuccess) e = cudaEventRecord(n->ev0, n->stream);
+	if (e == cudaSuccess) e = launch_ref_train(a, n->stream);
+	if (e == cudaSuccess) e = cudaEventRecord(n->ev1, n->stream);
+	if (e == cudaSuccess) e = cudaStreamSynchronize(n->stream);
+	std::vector<float> hOut;
+	if (e == cudaSuccess && want_out)
+	{
+		hOut.resize((size_t)rows * n->n_out);
+		e = cudaMemcpy(hOut.data(), dOut, hOut.size() * sizeof(float), cudaMemcpyDeviceToHost);
+	}
+	if (e == cudaSuccess && acts_last)
+		e = cudaMemcpy(acts_last, dActs, (size_t)(n->total_nodes - n->d.sizes[0]) * sizeof(float), cudaMemcpyDeviceToHost);
+	cudaFree(dOut);
+	cudaFree(dActs);
+	if (e != cudaSuccess) return fail(GL_ERR_CUDA, "reference-mode forward with dropout: %s", cudaGetErrorString(e));
+	n->launches += 1;
+	if (outputs) memcpy(outputs, hOut.data(), hOut.size() * sizeof(float));
+	if (argmax)
+		for (int64_t r = 0; r < rows; ++r)
+		{
+			// GMath::naiveVectorDecomp (GMath/gmath.cpp:435-455): strict > from 0, first maximum wins, -1 for none
+			float mx = 0.0f;
+			int idx = -1;
+			for (int o = 0; o < n->n_out; ++o)
+				if (hOut[(size_t)r * n->n_out + o] > mx)
+				{
+					mx = hOut[(size_t)r * n->n_out + o];
+					idx = o;
+				}
+			argmax[r] = idx;
+		}
+	if (out)
+	{
+		float ms = 0;
+		CU(cudaEventElapsedTime(&ms, n->ev0, n->ev1));
+		float sums[2] = {0, 0};
+		if (Y) CU(cudaMemcpy(sums, n->dSumsF, sizeof sums, cudaMemcpyDeviceToHost));
+		return finish_metrics(n, out, sums[0], sums[1], rows, ms, 1, Y != nullptr);
+	}
+	return GL_OK;
+}
+
 static int forward_rows(gl_net* n, const float* X, const float* Y, int64_t rows, int64_t metric_rows, float* outputs,
                         int32_t* argmax, gl_metrics* out)
 {
+	if (n->d.mode == GL_MODE_REFERENCE && n->dropout)
+		return ref_forward_dropout(n, X, Y, rows, metric_rows, outputs, argmax, nullptr, out);
 	const int64_t chunk_max = (n->d.mode == GL_MODE_REFERENCE) ? 65536 : (rows < 65536 ? rows : 65536);
 	if (int r = ensure_work(n, chunk_max < rows ? chunk_max : rows)) return r;
 	int64_t launches = 0;
@@ -1830,6 +2070,8 @@ extern "C" int gl_get_activations(gl_net* n, int64_t row, float* out)
 	if (!n || !out) return fail(GL_ERR_INVALID, "gl_get_activations: null argument");
 	if (!n->dX || row < 0 || row >= n->rows) return fail(GL_ERR_STATE, "gl_get_activations: no such row");
 	if (int r = use_device(n)) return r;
+	if (n->d.mode == GL_MODE_REFERENCE && n->dropout)  // draws this row's node flags like any forward of the reference
+		return ref_forward_dropout(n, n->dX + row * n->d.sizes[0], nullptr, 1, 1, nullptr, nullptr, out, nullptr);
 	if (int r = ensure_work(n, 1)) return r;
 	int64_t launches = 0;
 	const float* X = n->dX + row * n->d.sizes[0];
@@ -1873,6 +2115,24 @@ extern "C" int gl_get_pending_delta(gl_net* n, int32_t k, float* out)
 	if (!n || !out) return fail(GL_ERR_INVALID, "gl_get_pending_delta: null argument");
 	if (n->d.mode != GL_MODE_REFERENCE) return fail(GL_ERR_STATE, "pending deltas exist in reference mode only");
 	if (int r = use_device(n)) return r;
+	if (n->dropout)
+	{
+		// every edge has its own history length
+		memset(out, 0, (size_t)n->nw * sizeof(float));
+		if (k < 0 || k >= n->d.batch_size) return GL_OK;
+		std::vector<int> len((size_t)n->nw);
+		std::vector<float> slice((size_t)n->nw);
+		CU(cudaMemcpy(len.data(), n->dHlen, len.size() * sizeof(int), cudaMemcpyDeviceToHost));
+		for (int l = 0; l <= n->H; ++l)
+		{
+			const int64_t cnt = n->woff[l + 1] - n->woff[l];
+			CU(cudaMemcpy(slice.data() + n->woff[l], n->dHist + n->woff[l] * n->d.batch_size + (int64_t)k * cnt, cnt * sizeof(float),
+			              cudaMemcpyDeviceToHost));
+		}
+		for (int64_t e = 0; e < n->nw; ++e)
+			if (k < len[(size_t)e]) out[e] = slice[(size_t)e];
+		return GL_OK;
+	}
 	int len = 0;
 	CU(cudaMemcpy(&len, n->dHistLen, sizeof len, cudaMemcpyDeviceToHost));
 	if (k < 0 || k >= len || k >= n->d.batch_size)

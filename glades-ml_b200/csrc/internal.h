@@ -38,8 +38,18 @@ struct RefTrainArgs
 	float* last_out;                    // [n_out]: predictions of the last row of the last epoch
 	int* flags;                         // [0] non-finite weight seen after the call
 	int weights_in_smem;                // stage W and hist in shared memory for the whole launch
+	// dropout (masks != NULL selects the dropout kernel: one epoch per launch, n_epochs is ignored)
+	const unsigned char* masks;         // [rows][mask_stride]: 1 = node dropped; node layers 0..H side by side
+	int mask_stride;                    // n_0 + ... + n_H
+	int train;                          // 0: forward + metrics only (the test pass drops nodes too)
+	int* hlen[GL_MAX_WEIGHT_LAYERS];    // per edge: deltas pushed since its last apply
+	float* hlast[GL_MAX_WEIGHT_LAYERS]; // per edge: the last pushed delta
+	float* err_state;                   // [total nodes]: error accumulators carried from launch to launch
+	long long data_rows;                // rows of the data set for the cost divisor (0: `rows`)
+	float* acts_out;                    // optional: activations of layers 1..H+1 of the LAST row, concatenated
 };
 size_t ref_train_smem_bytes(const NetView& n, bool weights_in_smem);
+size_t ref_train_dropout_smem_bytes(const NetView& n);
 cudaError_t launch_ref_train(const RefTrainArgs& a, cudaStream_t s);
 
 // Exact-order forward of rows [first, first+rows): one thread per (row, output node), k ascending.

@@ -268,6 +268,249 @@ __global__ void __launch_bounds__(1024, 1) ref_train_kernel(const __grid_constan
 	if (bad) atomicOr(a.flags, 1);
 }
 
+// ---------------------------------------------------------------------------------------------
+// The same sample loop with dropped nodes (LayerBuilder::scrambleDropout, State/LayerBuilder.cpp:497-523;
+// the flags are drawn on the host in the reference's rand() order and arrive as one byte per node of
+// every non-output layer, [rows][mask_stride]).  What changes (network.cpp:476-508,620-662):
+//   forward   an edge counts only when both of its nodes are kept; the sum of a node runs over its kept
+//             inputs in i order; a dropped node gets squash(0 + bias);
+//   backward  a dropped pair uses the raw accumulator E_o as its delta (no derivative factor), pushes,
+//             applies and subtracts nothing, but still feeds E_i += E_i + E_o * W_oi; E_o is cleared
+//             only when the pair (n_in - 1, o) is kept, so hidden accumulators can survive a row (they
+//             are carried from launch to launch in a.err_state);
+//   history   every edge has its own history length (a dropped pair pushes nothing): hlen / hlast hold
+//             the length and the last pushed delta per edge, hist its first mb entries; an apply sums
+//             those first mb entries (Node::applyDeltas, node.cpp:299-301) and empties the history.
+// One epoch per launch (the host draws each epoch's flags before it).  Weights, histories and flags stay
+// in global memory (one CTA: they sit in L1/L2); the per-sample vectors are in shared memory.
+__global__ void __launch_bounds__(1024, 1) ref_train_dropout_kernel(const __grid_constant__ RefTrainArgs a)
+{
+	extern __shared__ __align__(16) float smem[];
+	const NetView& n = a.net;
+	const int H = n.H;
+	const int T = blockDim.x;
+	const int t = threadIdx.x;
+	const int n_out = n.sizes[H + 1];
+
+	int total_nodes = 0;
+	for (int l = 0; l <= H + 1; ++l) total_nodes += n.sizes[l];
+
+	float* act_base = smem;
+	float* err_base = act_base + total_nodes;
+	float* dvec = err_base + total_nodes;    // E_o * act'(a_o): the delta of a kept pair
+	float* basev = dvec + total_nodes;       // lr * delta
+	float* rawv = basev + total_nodes;       // E_o itself: the delta of a dropped pair
+	float* sbias = rawv + total_nodes;
+	float* mcost = sbias + GL_MAX_WEIGHT_LAYERS;
+	float* macc = mcost + n_out;
+
+	float* actp[GL_MAX_WEIGHT_LAYERS + 1];
+	float* errp[GL_MAX_WEIGHT_LAYERS + 1];
+	int moff[GL_MAX_WEIGHT_LAYERS + 1];
+	{
+		int off = 0;
+		for (int l = 0; l <= H + 1; ++l)
+		{
+			actp[l] = act_base + off;
+			errp[l] = err_base + off;
+			moff[l] = off;  // node layer l's flags start here inside a row of flags (l <= H)
+			off += n.sizes[l];
+		}
+	}
+	for (int e = t; e < total_nodes; e += T) err_base[e] = a.err_state[e];
+	if (t < GL_MAX_WEIGHT_LAYERS) sbias[t] = n.bias[t];
+	__shared__ float s_tot_err, s_tot_acc;
+	if (t == 0)
+	{
+		s_tot_err = 0.0f;
+		s_tot_acc = 0.0f;
+	}
+	const float data_size = (float)((a.data_rows > 0 ? a.data_rows : a.rows) * (long long)n_out);
+	const bool classify = n.out_type != GL_OUT_REGRESSION;
+	if (classify)
+		for (int e = t; e < n_out * n_out; e += T) a.confusion[e] = 0;
+	__syncthreads();
+
+	for (long long r = 0; r < a.rows; ++r)
+	{
+		const unsigned char* mrow = a.masks + r * a.mask_stride;
+		// ---------------- forward
+		for (int i = t; i < n.sizes[0]; i += T) actp[0][i] = a.X[r * n.sizes[0] + i];
+		__syncthreads();
+		for (int l = 0; l <= H; ++l)
+		{
+			const int ni = n.sizes[l], no = n.sizes[l + 1];
+			const float* W = n.W[l];
+			const float* ain = actp[l];
+			const unsigned char* din = mrow + moff[l];
+			const unsigned char* dout = (l + 1 <= H) ? mrow + moff[l + 1] : nullptr;
+			for (int o = t; o < no; o += T)
+			{
+				float z = 0.0f;
+				if (!(dout && dout[o]))
+				{
+					const float* wr = W + (size_t)o * ni;
+					for (int i = 0; i < ni; ++i)
+						if (!din[i]) z = __fadd_rn(z, __fmul_rn(wr[i], ain[i]));
+				}
+				if (l >= 1) z = __fadd_rn(z, sbias[l]);
+				actp[l + 1][o] = squash_x(z, n.act[l], n.par[l]);
+			}
+			__syncthreads();
+		}
+		// ---------------- metrics
+		const float* yr = a.Y ? a.Y + r * n_out : nullptr;  // forward-only calls may come without expected rows
+		if (yr)
+			for (int o = t; o < n_out; o += T)
+			{
+				mcost[o] = cost_x(yr[o], actp[H + 1][o], data_size, n.out_type);
+				macc[o] = node_accuracy_x(yr[o], actp[H + 1][o]);
+			}
+		__syncthreads();
+		if (t == 0 && yr)
+		{
+			const float* p = actp[H + 1];
+			float te = s_tot_err, ta = s_tot_acc;
+			for (int o = 0; o < n_out; ++o)
+			{
+				te = __fadd_rn(te, mcost[o]);
+				ta = __fadd_rn(ta, macc[o]);
+			}
+			s_tot_err = te;
+			s_tot_acc = ta;
+			if (classify)
+			{
+				int ie = argmax_ref(yr, n_out), ip = argmax_ref(p, n_out);
+				if (ie >= 0 && ip >= 0) a.confusion[ie * n_out + ip] += 1;
+			}
+		}
+		if (a.outputs)
+			for (int o = t; o < n_out; o += T) a.outputs[r * n_out + o] = actp[H + 1][o];
+		if (a.last_out && r == a.rows - 1)
+			for (int o = t; o < n_out; o += T) a.last_out[o] = actp[H + 1][o];
+		if (a.acts_out && r == a.rows - 1)
+			for (int e = t; e < total_nodes - n.sizes[0]; e += T) a.acts_out[e] = act_base[n.sizes[0] + e];
+		if (!a.train || !yr)
+		{
+			__syncthreads();
+			continue;
+		}
+
+		// ---------------- backward
+		const bool apply = (r % n.mb) == 0;
+		for (int L = H + 1; L >= 1; --L)
+		{
+			const int l = L - 1;
+			const int ni = n.sizes[l], no = n.sizes[L];
+			const float lr = n.lr[l], mom = n.mom[l];
+			const unsigned char* din = mrow + moff[l];
+			const unsigned char* dout = (L <= H) ? mrow + moff[L] : nullptr;
+			const bool last_in_kept = !din[ni - 1];
+			for (int o = t; o < no; o += T)
+			{
+				float E, der = 1.0f;
+				if (L == H + 1)
+					E = __fadd_rn(0.0f, cost_der_x(yr[o], actp[L][o], n.out_type));
+				else
+				{
+					E = errp[L][o];
+					der = act_der_x(actp[L][o], n.act[l], 0.01f);
+					// cleared by the pair (n_in - 1, o), and only when that pair is kept
+					if (last_in_kept && !dout[o]) errp[L][o] = 0.0f;
+				}
+				const float d = __fmul_rn(E, der);
+				rawv[o] = E;
+				dvec[o] = d;
+				basev[o] = __fmul_rn(lr, d);
+			}
+			__syncthreads();
+			float* W = n.W[l];
+			float* hist = a.hist[l];
+			int* hlen = a.hlen[l];
+			float* hlast = a.hlast[l];
+			const size_t cnt = (size_t)ni * no;
+			const float wl1 = __fmul_rn(n.wd1[l], lr), wl2 = __fmul_rn(n.wd2[l], lr);
+			const float fmb = (float)n.mb;
+			for (int i = t; i < ni; i += T)
+			{
+				const float ai = actp[l][i];
+				const float c3 = __fmul_rn(wl1, fabsf(ai));
+				const float c4 = __fmul_rn(wl2, ai);
+				const bool in_dropped = din[i] != 0;
+				float E = (l >= 1) ? errp[l][i] : 0.0f;
+				for (int o = 0; o < no; ++o)
+				{
+					const size_t e = (size_t)o * ni + i;
+					const bool dropped = in_dropped || (dout && dout[o]);
+					float w = W[e];
+					float dd = rawv[o];
+					if (!dropped)
+					{
+						dd = dvec[o];
+						int len = hlen[e];
+						const float last = (len > 0) ? hlast[e] : 0.0f;
+						const float delta = __fadd_rn(
+						    __fadd_rn(__fadd_rn(__fmul_rn(basev[o], ai), __fmul_rn(mom, last)), c3), c4);
+						if (len < n.mb) hist[(size_t)len * cnt + e] = delta;
+						hlast[e] = delta;
+						++len;
+						if (apply)
+						{
+							float s = 0.0f;
+							const int q_end = len < n.mb ? len : n.mb;
+							for (int q = 0; q < q_end; ++q) s = __fadd_rn(s, hist[(size_t)q * cnt + e]);
+							s = __fdiv_rn(s, fmb);
+							w = __fsub_rn(w, s);
+							W[e] = w;
+							len = 0;
+						}
+						hlen[e] = len;
+					}
+					if (l >= 1)
+					{
+						const float tt = __fadd_rn(E, __fmul_rn(dd, w));
+						E = __fadd_rn(E, tt);
+					}
+				}
+				if (l >= 1) errp[l][i] = E;
+			}
+			// scalar bias recurrence over the kept pairs, i outer, o inner: one sequential chain
+			if (l >= 1 && t == T - 1)
+			{
+				float b = sbias[l];
+				for (int i = 0; i < ni; ++i)
+				{
+					if (din[i]) continue;
+					for (int o = 0; o < no; ++o)
+						if (!(dout && dout[o])) b = __fsub_rn(b, basev[o]);
+				}
+				sbias[l] = b;
+			}
+			__syncthreads();
+		}
+	}
+	if (t == 0)
+	{
+		a.epoch_sums[0] = s_tot_err;
+		a.epoch_sums[1] = s_tot_acc;
+	}
+	__syncthreads();
+	for (int e = t; e < total_nodes; e += T) a.err_state[e] = err_base[e];
+	int bad = 0;
+	for (int l = 0; l <= H; ++l)
+	{
+		const int cnt = n.sizes[l] * n.sizes[l + 1];
+		for (int e = t; e < cnt; e += T)
+			if (!isfinite(n.W[l][e])) bad = 1;
+	}
+	if (t < GL_MAX_WEIGHT_LAYERS)
+	{
+		n.bias[t] = sbias[t];
+		if (t >= 1 && t <= H && !isfinite(sbias[t])) bad = 1;
+	}
+	if (bad) atomicOr(a.flags, 1);
+}
+
 static int total_nodes_of(const NetView& n)
 {
 	int s = 0;
@@ -283,12 +526,25 @@ size_t ref_train_smem_bytes(const NetView& n, bool weights_in_smem)
 	return f * sizeof(float);
 }
 
+size_t ref_train_dropout_smem_bytes(const NetView& n)
+{
+	return (5 * (size_t)total_nodes_of(n) + GL_MAX_WEIGHT_LAYERS + 2 * (size_t)n.sizes[n.H + 1]) * sizeof(float);
+}
+
 cudaError_t launch_ref_train(const RefTrainArgs& a, cudaStream_t s)
 {
 	int maxw = 1;
 	for (int l = 0; l <= a.net.H + 1; ++l) maxw = a.net.sizes[l] > maxw ? a.net.sizes[l] : maxw;
 	int T = ((maxw + 1 + 31) / 32) * 32;  // one spare thread for the bias chain
 	if (T > 1024) T = 1024;
+	if (a.masks)
+	{
+		const size_t bytes = ref_train_dropout_smem_bytes(a.net);
+		cudaError_t e = cudaFuncSetAttribute(ref_train_dropout_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+		if (e != cudaSuccess) return e;
+		ref_train_dropout_kernel<<<1, T, bytes, s>>>(a);
+		return cudaGetLastError();
+	}
 	const size_t bytes = ref_train_smem_bytes(a.net, a.weights_in_smem != 0);
 	cudaError_t e = cudaFuncSetAttribute(ref_train_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
 	if (e != cudaSuccess) return e;

@@ -84,7 +84,10 @@ typedef struct gl_net_desc {
 	float momentum[GL_MAX_WEIGHT_LAYERS];
 	float wd1[GL_MAX_WEIGHT_LAYERS];
 	float wd2[GL_MAX_WEIGHT_LAYERS];
-	float p_dropout[GL_MAX_WEIGHT_LAYERS];     /* must be 0: dropout is not on this path yet */
+	float p_dropout[GL_MAX_WEIGHT_LAYERS];     /* dropout probability of NODE layer j = 0..H (0 = input), as the loop
+	                                            * uses it: [0] = NNInfo::getPInput(), [j] = getPDropout(j-1), whose
+	                                            * index 0 is again the input layer's value (nninfo.cpp:140-146,
+	                                            * 321-333).  Reference mode only; see gl_train_epochs. */
 	int32_t activation[GL_MAX_WEIGHT_LAYERS];
 	float act_param[GL_MAX_WEIGHT_LAYERS];
 	int32_t output_type;                       /* GL_OUT_* (NNInfo::getOutputType) */
@@ -168,7 +171,15 @@ int gl_forward_host_result(gl_net* net, int32_t* argmax, gl_metrics* out);
 
 /* Replaces n iterations of the epoch loop of NNetwork::run with RUN_TRAIN
  * (network.cpp:173-256): every row through SGDHelper (forward, metrics, confusion counts,
- * backward, update).  out (may be NULL) receives the last epoch's figures. */
+ * backward, update).  out (may be NULL) receives the last epoch's figures.
+ * Dropout (reference mode, any p_dropout != 0; replaces LayerBuilder::scrambleDropout and
+ * Layer::generateDropout, State/LayerBuilder.cpp:497-523, State/layer.cpp:102-134, and the skip rules
+ * of network.cpp:480-488,620-657): before every epoch -- and before every gl_forward /
+ * gl_get_activations, the reference drops nodes in its test pass too -- the library draws the node
+ * flags of all rows on the host with the C library's rand(), one call per node in the reference's
+ * order (per row: input layer, then hidden layers; integer-percent threshold rand() % 100 + 1 <=
+ * int(p * 100); a layer that came out all dropped is drawn again; int(p * 100) >= 100 draws nothing).
+ * After the same srand() the same nodes drop as in the reference. */
 int gl_train_epochs(gl_net* net, int32_t n_epochs, gl_metrics* out);
 /* Batched mode: one window step (forward, backward, update) over rows
  * [first_row, first_row+rows) of the resident data.  Under data parallelism each rank passes its

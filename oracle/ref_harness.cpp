@@ -113,6 +113,13 @@ void* ref_create(const gl_net_desc* d, const float* x, const float* y, int64_t r
 	// weightDecay1 (Structure/nninfo.cpp:305-306), so the reference cannot express wd2[0] != wd1[0].
 	if (d->wd2[0] != d->wd1[0])
 		return NULL;
+	// Dropout, effective values too: p_dropout[j] is the probability the loop uses for node layer j.  The
+	// loop reads getPInput() for the input layer and getPDropout(i) for hidden layer i, and getPDropout(0)
+	// is again the input layer's value (Structure/nninfo.cpp:140-146,321-333; network.cpp:408-411): the
+	// reference cannot express p_dropout[1] != p_dropout[0], and hidden layer k's own value is what
+	// governs hidden layer k+1.
+	if (d->p_dropout[1] != d->p_dropout[0])
+		return NULL;
 	RefNet* r = new RefNet();
 	r->desc = *d;
 	r->x.assign(x, x + (size_t)rows * d->sizes[0]);
@@ -124,7 +131,7 @@ void* ref_create(const gl_net_desc* d, const float* x, const float* y, int64_t r
 	std::vector<HiddenLayerInfo*> hidden;
 	for (int l = 1; l <= H; ++l)
 		hidden.push_back(new HiddenLayerInfo(d->sizes[l], d->lr[l], d->momentum[l], d->wd1[l], d->wd2[l],
-		                                     d->p_dropout[l], d->activation[l], d->act_param[l]));
+		                                     l + 1 <= H ? d->p_dropout[l + 1] : 0.0f, d->activation[l], d->act_param[l]));
 	OutputLayerInfo* out = new OutputLayerInfo(d->sizes[H + 1], d->output_type);
 	r->info = new NNInfo("oracle", in, hidden, out);
 	r->di = new ArrayInput(&r->x[0], &r->y[0], (unsigned int)rows, d->sizes[0], d->sizes[H + 1]);

@@ -44,6 +44,12 @@ typedef struct rs_net {
 	float tot_err, tot_acc;
 	int epochs;
 	int math_mode;     /* 0 glibc single precision (reference); 1 double then round (kernel) */
+	/* dropout (reference mode, any p_dropout != 0): the current row's flags per non-output node layer,
+	 * and per-edge histories of their own length (a dropped pair pushes nothing) */
+	int dropout_on;
+	unsigned char* drop[GL_MAX_WEIGHT_LAYERS + 1]; /* drop[l][i] = 1: node i of layer l is dropped, l = 0..H */
+	int32_t* hlen[GL_MAX_WEIGHT_LAYERS];           /* entries pushed on edge e since its last clear */
+	float* hlast[GL_MAX_WEIGHT_LAYERS];            /* the last pushed entry (the momentum term reads it) */
 } rs_net;
 
 static int g_math_mode = 0;
@@ -168,13 +174,22 @@ rs_net* rs_create(const gl_net_desc* d, const float* x, const float* y, int64_t 
 	}
 	int no = d->sizes[n->H + 1];
 	n->cm = (int32_t*)calloc((size_t)no * no, sizeof(int32_t));
+	for (int l = 0; l <= n->H; ++l)
+		if (d->p_dropout[l] != 0.0f) n->dropout_on = 1;
+	if (n->dropout_on && d->mode == GL_MODE_REFERENCE)
+		for (int l = 0; l <= n->H; ++l)
+		{
+			n->drop[l] = (unsigned char*)calloc(d->sizes[l], 1);
+			n->hlen[l] = (int32_t*)calloc(wcount(n, l), sizeof(int32_t));
+			n->hlast[l] = (float*)calloc(wcount(n, l), sizeof(float));
+		}
 	return n;
 }
 
 void rs_destroy(rs_net* n)
 {
 	if (!n) return;
-	for (int l = 0; l <= n->H; ++l) { free(n->w[l]); free(n->hist[l]); }
+	for (int l = 0; l <= n->H; ++l) { free(n->w[l]); free(n->hist[l]); free(n->drop[l]); free(n->hlen[l]); free(n->hlast[l]); }
 	for (int l = 0; l <= n->H + 1; ++l) { free(n->act[l]); free(n->err[l]); }
 	free(n->cm);
 	free(n);
@@ -193,6 +208,12 @@ void rs_set_weights(rs_net* n, const float* w, const float* bias)
 	}
 	n->hist_len = 0;
 	for (int l = 0; l <= n->H + 1; ++l) memset(n->err[l], 0, n->d.sizes[l] * sizeof(float));
+	for (int l = 0; l <= n->H; ++l)
+		if (n->hlen[l])
+		{
+			memset(n->hlen[l], 0, wcount(n, l) * sizeof(int32_t));
+			memset(n->hlast[l], 0, wcount(n, l) * sizeof(float));
+		}
 }
 
 void rs_get_weights(const rs_net* n, float* w, float* bias)
@@ -213,7 +234,10 @@ void rs_get_pending_delta(const rs_net* n, int k, float* out)
 	{
 		size_t c = wcount(n, l);
 		for (size_t e = 0; e < c; ++e)
-			out[j++] = (k < n->hist_len) ? n->hist[l][(size_t)k * c + e] : 0.0f;
+		{
+			const int len = n->hlen[l] ? n->hlen[l][e] : n->hist_len;
+			out[j++] = (k < len && k < n->d.batch_size) ? n->hist[l][(size_t)k * c + e] : 0.0f;
+		}
 	}
 }
 
@@ -329,6 +353,143 @@ static void backward_row(rs_net* n, int64_t r)
 	n->hist_len = apply ? 0 : k + 1;
 }
 
+
+/* ------------------------------------------------------------------------------------------
+ * Dropout (reference mode).  LayerBuilder::scrambleDropout (State/LayerBuilder.cpp:497-523) runs
+ * before EVERY row, in training and in testing (network.cpp:408-411): Layer::generateDropout
+ * (State/layer.cpp:102-134) for the row's input layer with NNInfo::getPInput(), then for hidden
+ * layer i with NNInfo::getPDropout(i) -- whose index 0 is the INPUT layer's value (nninfo.cpp:321-333),
+ * so the first hidden layer drops with the input layer's probability and the last hidden layer's own
+ * value is never read.  The descriptor carries the resolved values: p_dropout[j] is what the loop uses
+ * for node layer j (0 = input, 1..H hidden).
+ * The rate is an integer percentage, int(p * 100.0f); a rate < 0 or >= 100 draws nothing and leaves the
+ * flags alone (all clear); otherwise one rand() per node, dart = rand() % 100 + 1, dropped when
+ * dart <= rate, the whole layer redrawn while every node dropped.
+ * ------------------------------------------------------------------------------------------ */
+static void draw_layer_dropout(unsigned char* flag, int size, float p)
+{
+	int rate = (int)(p * 100.0f);
+	if (rate < 0 || rate >= 100) return;
+	int all;
+	do
+	{
+		all = 1;
+		for (int i = 0; i < size; ++i)
+		{
+			int dart = (rand() % 100) + 1;
+			if (dart <= rate) flag[i] = 1;
+			else { flag[i] = 0; all = 0; }
+		}
+	} while (all);
+}
+
+static void draw_row_dropout(rs_net* n)
+{
+	for (int j = 0; j <= n->H; ++j) draw_layer_dropout(n->drop[j], n->d.sizes[j], n->d.p_dropout[j]);
+}
+
+/* ForwardPass with dropped nodes (network.cpp:476-508): an edge is activated only when both of its
+ * nodes are kept; the node's sum runs over its activated edges in i order (node.cpp:82-93); a dropped
+ * node therefore gets squash(0 + bias). */
+static void forward_row_dropout(rs_net* n, int64_t r)
+{
+	const gl_net_desc* d = &n->d;
+	memcpy(n->act[0], n->x + (size_t)r * d->sizes[0], d->sizes[0] * sizeof(float));
+	for (int l = 0; l <= n->H; ++l)
+	{
+		const int ni = d->sizes[l], no = d->sizes[l + 1];
+		const float* W = n->w[l];
+		const float* a = n->act[l];
+		const unsigned char* din = n->drop[l];
+		const unsigned char* dout = (l + 1 <= n->H) ? n->drop[l + 1] : NULL;
+		for (int o = 0; o < no; ++o)
+		{
+			float z = 0.0f;
+			if (!(dout && dout[o]))
+				for (int i = 0; i < ni; ++i)
+				{
+					if (din[i]) continue;
+					float prod = W[(size_t)o * ni + i] * a[i];
+					z = z + prod;
+				}
+			if (l >= 1) z = z + n->bias[l];
+			n->act[l + 1][o] = rs_squash(z, d->activation[l], d->act_param[l]);
+		}
+	}
+}
+
+/* BackPropagation with dropped nodes (network.cpp:577-668).  For a dropped pair the node delta is the
+ * raw accumulator (no derivative factor), nothing is pushed, applied or subtracted from the bias, and
+ * the accumulator is not cleared -- but the pair still feeds the input node's accumulator
+ * (network.cpp:659-662).  The clear happens on the pair with i == n_in - 1 only when that pair is kept
+ * (network.cpp:630-632), so accumulators of hidden nodes can survive into the next row.  Each edge's
+ * history has its own length (Edge::prevDelta): Node::applyDeltas sums its first mb entries
+ * (node.cpp:299-301) and the clear empties it, whatever its length. */
+static void backward_row_dropout(rs_net* n, int64_t r)
+{
+	const gl_net_desc* d = &n->d;
+	const int mb = d->batch_size;
+	const int apply = (r % mb) == 0;
+	const float* e = n->y + (size_t)r * d->sizes[n->H + 1];
+	for (int L = n->H + 1; L >= 1; --L)
+	{
+		const int l = L - 1;
+		const int ni = d->sizes[l], no = d->sizes[L];
+		float* W = n->w[l];
+		float* hist = n->hist[l];
+		int32_t* hlen = n->hlen[l];
+		float* hlast = n->hlast[l];
+		const size_t cnt = (size_t)ni * no;
+		const float lr = d->lr[l], m = d->momentum[l], wd1 = d->wd1[l], wd2 = d->wd2[l];
+		float* EL = n->err[L];
+		float* El = n->err[l];
+		const unsigned char* din = n->drop[l];
+		const unsigned char* dout = (L <= n->H) ? n->drop[L] : NULL;
+		for (int i = 0; i < ni; ++i)
+		{
+			const float ai = n->act[l][i];
+			for (int o = 0; o < no; ++o)
+			{
+				float der = 1.0f;
+				if (L == n->H + 1)
+					EL[o] = 0.0f + rs_cost_der(e[o], n->act[L][o], d->output_type);
+				else
+					der = rs_act_der(n->act[L][o], d->activation[l], 0.01f);
+				const int dropped = din[i] || (dout && dout[o]);
+				float dd = EL[o];
+				size_t eidx = (size_t)o * ni + i;
+				if (!dropped)
+				{
+					dd = dd * der;
+					if (i == ni - 1) EL[o] = 0.0f;
+					float base = lr * dd;
+					float last = (hlen[eidx] > 0) ? hlast[eidx] : 0.0f;
+					float absa = ai < 0.0f ? -ai : ai;
+					float delta = (((base * ai) + (m * last)) + (wd1 * lr * absa)) + (wd2 * lr * ai);
+					if (hlen[eidx] < mb) hist[(size_t)hlen[eidx] * cnt + eidx] = delta;
+					hlast[eidx] = delta;
+					hlen[eidx] += 1;
+					if (apply)
+					{
+						float s = 0.0f;
+						for (int t = 0; t < mb; ++t)
+							s += (t < hlen[eidx]) ? hist[(size_t)t * cnt + eidx] : 0.0f;
+						s /= (float)mb;
+						W[eidx] = W[eidx] - s;
+						hlen[eidx] = 0;
+					}
+					if (l >= 1) n->bias[l] = n->bias[l] - base;
+				}
+				if (l >= 1)
+				{
+					float t = El[i] + (dd * W[eidx]);
+					El[i] += t;
+				}
+			}
+		}
+	}
+}
+
 static void finish_class_metrics(const rs_net* n, gl_metrics* m)
 {
 	/* CMatrix::updateResultParams + getters, cmatrix.cpp:100-266 */
@@ -382,10 +543,20 @@ int rs_epoch(rs_net* n, int run_type, gl_metrics* m, int32_t* confusion, float* 
 	memset(n->cm, 0, (size_t)no * no * sizeof(int32_t));
 	for (int64_t r = 0; r < n->rows; ++r)
 	{
-		forward_row(n, r);
+		if (n->dropout_on)
+		{
+			draw_row_dropout(n);
+			forward_row_dropout(n, r);
+		}
+		else
+			forward_row(n, r);
 		metrics_row(n, r);
 		if (outputs) memcpy(outputs + (size_t)r * no, n->act[n->H + 1], no * sizeof(float));
-		if (run_type == 0) backward_row(n, r);
+		if (run_type == 0)
+		{
+			if (n->dropout_on) backward_row_dropout(n, r);
+			else backward_row(n, r);
+		}
 	}
 	if (run_type == 0) n->epochs += 1;
 	fill_metrics(n, m);
@@ -395,7 +566,13 @@ int rs_epoch(rs_net* n, int run_type, gl_metrics* m, int32_t* confusion, float* 
 
 int rs_forward_row(rs_net* n, int64_t row, float* acts)
 {
-	forward_row(n, row);
+	if (n->dropout_on)
+	{
+		draw_row_dropout(n);
+		forward_row_dropout(n, row);
+	}
+	else
+		forward_row(n, row);
 	size_t k = 0;
 	for (int l = 1; l <= n->H + 1; ++l)
 	{
@@ -407,6 +584,13 @@ int rs_forward_row(rs_net* n, int64_t row, float* acts)
 
 int rs_train_row(rs_net* n, int64_t row)
 {
+	if (n->dropout_on)
+	{
+		draw_row_dropout(n);
+		forward_row_dropout(n, row);
+		backward_row_dropout(n, row);
+		return 0;
+	}
 	forward_row(n, row);
 	backward_row(n, row);
 	return 0;

@@ -42,12 +42,19 @@ def load_golden(name):
 
 def desc_from_meta(g, meta, **over):
     kw = dict(batch=meta.get("batch", 1), lr=meta.get("lr", 0.0), momentum=meta.get("momentum", 0.0),
-              wd1=meta.get("wd1", 0.0), wd2=meta.get("wd2", 0.0), params=meta.get("params"))
+              wd1=meta.get("wd1", 0.0), wd2=meta.get("wd2", 0.0), params=meta.get("params"),
+              p_dropout=meta.get("p_dropout", 0.0))
     kw.update(over)
     out = meta.get("out")
     if out is None:
         out = "classification" if meta["sizes"][-1] > 1 else "regression"
     return g.make_desc(meta["sizes"], meta["acts"], out, **kw)
+
+
+def libc_srand(seed):
+    """Seeds the C library's rand(), which the dropout flags are drawn from (State/layer.cpp:123)."""
+    import ctypes
+    ctypes.CDLL(None).srand(int(seed))
 
 
 def bits(a):

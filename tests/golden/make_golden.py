@@ -31,6 +31,13 @@ o = ge.import_oracle()
 
 SEED = 0x474C4144  # "GLAD"
 
+# `--only a,b,...` rewrites just the named fixtures (everything is still computed, in the same order, so
+# the seeded inputs of the others do not move)
+ONLY = None
+for _i, _a in enumerate(sys.argv):
+    if _a == "--only" and _i + 1 < len(sys.argv):
+        ONLY = set(sys.argv[_i + 1].split(","))
+
 
 def gaussian_classes(rng, rows, n_in, n_cls, interleaved=True):
     means = rng.uniform(-2, 2, (n_cls, n_in))
@@ -42,21 +49,31 @@ def gaussian_classes(rng, rows, n_in, n_cls, interleaved=True):
 
 
 def save(name, meta, **arrays):
+    if ONLY is not None and name not in ONLY:
+        print("kept %s" % name)
+        return
     path = os.path.join(HERE, name + ".npz")
     np.savez_compressed(path, meta=np.array(json.dumps(meta)), **arrays)
     print("wrote %s (%.1f KB)" % (name, os.path.getsize(path) / 1024.0))
 
 
 def trajectory(name, sizes, acts, out, x, y, mb, lr, mom, epochs, snapshots, w_range, seed, params=None, wd1=0.0,
-               wd2=0.0):
+               wd2=0.0, p_dropout=0.0, srand=None):
+    """`p_dropout` (per node layer) with `srand`: the C library's generator is seeded once before the run;
+    the reference then draws its dropout flags from rand() row by row (State/layer.cpp:102-134)."""
+    import ctypes
+    libc = ctypes.CDLL(None)
     rng = np.random.default_rng(seed)
-    d = capi.make_desc(sizes, acts, out, batch=mb, lr=lr, momentum=mom, wd1=wd1, wd2=wd2, params=params)
+    d = capi.make_desc(sizes, acts, out, batch=mb, lr=lr, momentum=mom, wd1=wd1, wd2=wd2, params=params,
+                       p_dropout=p_dropout)
     nw = capi.weight_count(d)
     w0 = rng.uniform(-w_range, w_range, nw).astype(np.float32)
     b0 = rng.uniform(-0.1, 0.1, len(sizes) - 2).astype(np.float32)
     R = o.Reference(d, x, y, capi.Metrics)
     R.set_weights(w0, b0)
     mets, cms, ws, bs, outs = [], [], [], [], []
+    if srand is not None:
+        libc.srand(srand)
     for e in range(1, epochs + 1):
         m, cm, outp = R.epoch(0, True)
         if e in snapshots:
@@ -68,17 +85,28 @@ def trajectory(name, sizes, acts, out, x, y, mb, lr, mom, epochs, snapshots, w_r
             bs.append(b)
             outs.append(outp)
     pend = np.stack([R.pending_delta(k) for k in range(mb)])
+    extra = {}
+    if srand is not None:
+        # the test pass drops nodes too (SGDHelper draws the flags whatever the run type)
+        libc.srand(srand + 1)
+        mt, cmt, outt = R.epoch(1, True)
+        extra = dict(test_metrics=np.array([mt.total_error, mt.total_accuracy], np.float32), test_confusion=cmt,
+                     test_outputs=outt)
     # cross-check the public path: a second reference object trained with NNetwork::train()
     R2 = o.Reference(d, x, y, capi.Metrics)
     R2.set_weights(w0, b0)
+    if srand is not None:
+        libc.srand(srand)
     R2.train_public(epochs)
     w2, b2 = R2.get_weights()
     assert np.array_equal(w2.view(np.uint32), ws[-1].view(np.uint32)), "public train() differs from row-driven epochs"
     assert np.array_equal(b2.view(np.uint32), bs[-1].view(np.uint32))
     meta = dict(kind="trajectory", sizes=sizes, acts=acts, out=out, batch=mb, lr=lr, momentum=mom, wd1=wd1, wd2=wd2,
                 params=params, epochs=epochs, snapshots=sorted(snapshots))
+    if srand is not None:
+        meta.update(p_dropout=p_dropout, srand=srand)
     save(name, meta, x=x, y=y, w0=w0, b0=b0, metrics=np.array(mets, np.float32), confusion=np.array(cms, np.int32),
-         w=np.array(ws), b=np.array(bs), outputs=np.array(outs), pending=pend)
+         w=np.array(ws), b=np.array(bs), outputs=np.array(outs), pending=pend, **extra)
 
 
 def init_fixture():
@@ -156,6 +184,32 @@ def main():
     ym = rng.uniform(0, 1, (20, 2)).astype(np.float32)
     trajectory("traj_mixed_acts_mb5", [3, 4, 4, 4, 2], ["leaky", "tanhp", "sigmoidp", "linear"], "regression", xm, ym,
                5, 0.01, 0.2, 3, {1, 3}, 0.5, 28, params=[0.05, 0.1, 0.1, 0.7])
+
+    # the KL cost (GMath/gmath.cpp:283,310-313,343) and the STEP activation (gmath.cpp:90-99), each through
+    # whole training runs; own generators, so the fixtures above keep their inputs
+    rk = np.random.default_rng(41)
+    xk, yk = gaussian_classes(rk, 60, 4, 3)
+    trajectory("traj_kl_4_6_3_mb2", [4, 6, 3], ["tanh", "sigmoid"], "kl", xk, yk, 2, 0.01, 0.4, 4, {1, 4}, 0.5, 29)
+    xs = rk.uniform(-1, 1, (48, 5)).astype(np.float32)
+    ys = rk.uniform(0.1, 0.9, (48, 2)).astype(np.float32)
+    trajectory("traj_step_5_6_4_2_mb3", [5, 6, 4, 2], ["step", "tanh", "sigmoid"], "regression", xs, ys, 3, 0.02, 0.3,
+               3, {1, 3}, 0.5, 30, params=[0.5, 0.0, 0.0])
+    # dropout: online and minibatch, one and two hidden layers, momentum (per-edge histories of unequal
+    # length), a layer that draws but never drops (p = 0) and one that draws nothing (p = 1)
+    xd, yd = gaussian_classes(rk, 45, 4, 3)
+    trajectory("traj_dropout_4_5_3_mb1", [4, 5, 3], ["sigmoid", "sigmoid"], "classification", xd, yd, 1, 0.01, 0.0, 5,
+               {1, 5}, 0.5, 31, p_dropout=0.2, srand=101)
+    xd2 = rk.uniform(0, 1, (50, 6)).astype(np.float32)
+    yd2 = rk.uniform(0.1, 0.9, (50, 2)).astype(np.float32)
+    trajectory("traj_dropout_6_8_7_2_mb4", [6, 8, 7, 2], ["tanh", "sigmoid", "sigmoid"], "regression", xd2, yd2, 4,
+               0.01, 0.5, 4, {1, 2, 4}, 0.4, 32, p_dropout=[0.3, 0.3, 0.25], srand=102)
+    trajectory("traj_dropout_6_8_7_2_mb7", [6, 8, 7, 2], ["relu", "tanh", "linear"], "regression", xd2[:45], yd2[:45],
+               7, 0.001, 0.7, 3, {1, 3}, 0.4, 33, params=[0.0, 0.0, 1.0], p_dropout=[0.0, 0.0, 0.4], srand=103)
+    xd3, yd3 = gaussian_classes(rk, 20, 5, 3)
+    trajectory("traj_dropout_5_6_3_mb3", [5, 6, 3], ["tanh", "sigmoid"], "classification", xd3, yd3, 3, 0.01, 0.3, 4,
+               {1, 4}, 0.5, 34, p_dropout=[1.0, 1.0], srand=104)
+    trajectory("traj_dropout_5_6_3_half", [5, 6, 3], ["tanh", "sigmoid"], "classification", xd3, yd3, 3, 0.01, 0.3, 4,
+               {1, 4}, 0.5, 35, p_dropout=0.5, srand=105)
 
     # ---- config 1 as written (lr 0.1): the reference goes non-finite; record the first such row
     d = capi.make_desc([4, 16, 3], ["sigmoid", "sigmoid"], "classification", batch=1, lr=0.1, momentum=0.9)
@@ -245,10 +299,10 @@ def main():
 
     forward_case("fwd_cfg3_32_256_256_1", [32, 256, 256, 1], ["relu", "relu", "linear"], 8, 1.0 / np.sqrt(32.0), 3,
                  walk_windows, params=[0.0, 0.0, 1.0])
-    forward_case("fwd_cfg5_784_2048_2048_10", [784, 2048, 2048, 10], ["relu", "relu", "sigmoid"], 3, 0.05, 5,
+    forward_case("fwd_cfg5_784_2048_2048_10", [784, 2048, 2048, 10], ["relu", "relu", "sigmoid"], 8, 0.05, 5,
                  lambda n, k: rngx.uniform(0, 1, (n, k)).astype(np.float32))
     if os.environ.get("GOLDEN_SKIP_CFG4") != "1":
-        forward_case("fwd_cfg4_1024_4096_4096_1024", [1024, 4096, 4096, 1024], ["relu", "relu", "sigmoid"], 2,
+        forward_case("fwd_cfg4_1024_4096_4096_1024", [1024, 4096, 4096, 1024], ["relu", "relu", "sigmoid"], 8,
                      1.0 / 32.0, 4, lambda n, k: rngx.standard_normal((n, k)).astype(np.float32))
     print("done in %.1fs" % (time.time() - t0))
 

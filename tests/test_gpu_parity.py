@@ -16,7 +16,7 @@ import os
 import numpy as np
 import pytest
 
-from conftest import GOLDEN, bits, desc_from_meta, load_golden, rel_err
+from conftest import GOLDEN, bits, desc_from_meta, libc_srand, load_golden, rel_err
 
 pytestmark = pytest.mark.gpu
 
@@ -57,25 +57,45 @@ def test_reference_mode_trajectory_bit_exact_vs_restatement(g, oracle, cr_math, 
     net.set_data(z["x"], z["y"])
     S = oracle.Restate(d, z["x"], z["y"], g.Metrics)
     S.set_weights(z["w0"], z["b0"])
+    # Each side runs its whole trajectory by itself: with dropout both draw their node flags from the C
+    # library's rand(), which is seeded once before a run and must not be shared between two runs.
+    if "srand" in meta:
+        libc_srand(meta["srand"])
     done = 0
+    got = []
     for e in meta["snapshots"]:
         m = net.train_epochs(e - done)
+        done = e
+        got.append((m, net.get_weights(), net.confusion() if meta["out"] != "regression" else None))
+    if "srand" in meta:
+        libc_srand(meta["srand"])
+    done = 0
+    for (m, (w, b), cm), e in zip(got, meta["snapshots"]):
         for _ in range(e - done):
             ms, cms, _ = S.epoch(0)
         done = e
-        w, b = net.get_weights()
         ws, bs = S.get_weights()
         assert np.array_equal(bits(w), bits(ws)), "weights differ at epoch %d" % e
         assert np.array_equal(bits(b), bits(bs)), "bias differs at epoch %d" % e
         assert m.total_error == ms.total_error and m.total_accuracy == ms.total_accuracy
         if meta["out"] != "regression":
-            assert np.array_equal(net.confusion(), cms)
+            assert np.array_equal(cm, cms)
             for k in ("class_accuracy", "class_precision", "class_recall", "class_specificity", "class_f1"):
                 a, bb = getattr(m, k), getattr(ms, k)
                 assert a == bb or (np.isnan(a) and np.isnan(bb)), k
     for q in range(meta["batch"]):
         assert np.array_equal(bits(net.pending_delta(q)), bits(S.pending_delta(q)))
     assert net.epochs() == meta["epochs"]
+    if "srand" in meta:
+        # the test pass drops nodes too: same flags after the same seed, same outputs bit for bit
+        libc_srand(meta["srand"] + 1)
+        out_g, am_g, mt = net.forward(0, z["x"].shape[0])
+        libc_srand(meta["srand"] + 1)
+        mst, cmst, out_s = S.epoch(1, True)
+        assert np.array_equal(bits(out_g), bits(out_s))
+        assert mt.total_error == mst.total_error and mt.total_accuracy == mst.total_accuracy
+        if meta["out"] != "regression":
+            assert np.array_equal(net.confusion(), cmst)
     net.close()
 
 
@@ -83,6 +103,7 @@ def test_reference_mode_trajectory_bit_exact_vs_restatement(g, oracle, cr_math, 
 # where the net has no transcendental function, else the stated fp32 tolerance 1e-5 -- one-ulp libm
 # differences grow to about 1.5e-6 over the longest run here (200 epochs of online SGD)
 GOLDEN_RTOL = {"traj_relu_6_5_4_2_mb7": 0.0}
+# (dropout flags are integers: with them identical, the dropout fixtures keep the same tolerance)
 
 
 @pytest.mark.parametrize("name", TRAJ)
@@ -92,6 +113,8 @@ def test_reference_mode_trajectory_vs_golden(g, name):
     net = g.Net(d)
     net.set_weights(z["w0"], z["b0"])
     net.set_data(z["x"], z["y"])
+    if "srand" in meta:
+        libc_srand(meta["srand"])  # the run that made the fixture seeded rand() once, before its first epoch
     done = 0
     for k, e in enumerate(meta["snapshots"]):
         m = net.train_epochs(e - done)

@@ -7,13 +7,13 @@ import os
 import numpy as np
 import pytest
 
-from conftest import GOLDEN, bits, desc_from_meta, load_golden
+from conftest import GOLDEN, bits, desc_from_meta, libc_srand, load_golden
 
 TRAJ = sorted(os.path.basename(p)[:-4] for p in glob.glob(os.path.join(GOLDEN, "traj_*.npz")))
 
 
 def test_golden_present():
-    assert len(TRAJ) >= 8
+    assert len(TRAJ) >= 15 and sum(n.startswith("traj_dropout") for n in TRAJ) >= 5
     for n in ("kat_scalar", "cfg2_step", "cfg1_lr01_nonfinite", "fwd_cfg3_32_256_256_1",
               "fwd_cfg5_784_2048_2048_10", "fwd_cfg4_1024_4096_4096_1024"):
         assert os.path.exists(os.path.join(GOLDEN, n + ".npz"))
@@ -53,6 +53,8 @@ def test_restatement_reproduces_golden_trajectory(g, oracle, name):
     S.set_weights(z["w0"], z["b0"])
     snaps = meta["snapshots"]
     k = 0
+    if "srand" in meta:
+        libc_srand(meta["srand"])  # dropout flags come from rand(), seeded once before the run
     for e in range(1, meta["epochs"] + 1):
         m, cm, out = S.epoch(0, True)
         if e in snaps:
@@ -68,6 +70,12 @@ def test_restatement_reproduces_golden_trajectory(g, oracle, name):
             k += 1
     for q in range(meta["batch"]):
         assert np.array_equal(bits(S.pending_delta(q)), bits(z["pending"][q]))
+    if "srand" in meta:
+        # the test pass drops nodes too
+        libc_srand(meta["srand"] + 1)
+        m, cm, out = S.epoch(1, True)
+        assert np.array_equal(bits(np.array([m.total_error, m.total_accuracy], np.float32)), bits(z["test_metrics"]))
+        assert np.array_equal(cm, z["test_confusion"]) and np.array_equal(bits(out), bits(z["test_outputs"]))
 
 
 def test_restatement_nonfinite_row(g, oracle):
@@ -139,11 +147,14 @@ def test_restatement_forward_wide(g, oracle, name):
 def test_restatement_vs_compiled_reference_live(g, oracle):
     """Where oracle/_ref exists: fresh seeded nets, reference vs restatement, bit for bit."""
     rng = np.random.default_rng(99)
-    cases = [([3, 7, 2], ["tanh", "sigmoid"], "regression", 5, 0.4), ([4, 6, 5, 3], ["relu", "sigmoid", "sigmoid"],
-                                                                     "classification", 2, 0.0)]
-    for sizes, acts, out, mb, mom in cases:
+    cases = [([3, 7, 2], ["tanh", "sigmoid"], "regression", 5, 0.4, 0.0),
+             ([4, 6, 5, 3], ["relu", "sigmoid", "sigmoid"], "classification", 2, 0.0, 0.0),
+             # dropout: both sides draw their flags from the C library's rand(), re-seeded before each side's epoch
+             ([4, 6, 5, 3], ["tanh", "sigmoid", "sigmoid"], "classification", 3, 0.6, [0.25, 0.25, 0.5]),
+             ([3, 7, 2], ["sigmoid", "sigmoid"], "regression", 1, 0.0, 0.33)]
+    for sizes, acts, out, mb, mom, pdrop in cases:
         rows = 23
-        d = g.make_desc(sizes, acts, out, batch=mb, lr=0.02, momentum=mom)
+        d = g.make_desc(sizes, acts, out, batch=mb, lr=0.02, momentum=mom, p_dropout=pdrop)
         x = rng.uniform(-1, 1, (rows, sizes[0])).astype(np.float32)
         y = rng.uniform(0.05, 0.95, (rows, sizes[-1])).astype(np.float32)
         w = rng.uniform(-0.5, 0.5, g.weight_count(d)).astype(np.float32)
@@ -152,8 +163,10 @@ def test_restatement_vs_compiled_reference_live(g, oracle):
         S = oracle.Restate(d, x, y, g.Metrics)
         R.set_weights(w, b)
         S.set_weights(w, b)
-        for _ in range(3):
+        for ep in range(3):
+            libc_srand(900 + ep)
             mr, cr, outr = R.epoch(0, True)
+            libc_srand(900 + ep)
             ms, cs, outs = S.epoch(0, True)
         wr, br = R.get_weights()
         ws, bs = S.get_weights()
