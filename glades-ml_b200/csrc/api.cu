@@ -237,10 +237,19 @@ struct gl_net
 	int bscaleRows = -1;
 	// gradient all-reduce overlapped with the rest of the backward pass
 	cudaStream_t commStream = nullptr;
+	// peer-memory exchange: layer l's exchange runs on its own stream (round robin over DP_COMM_STREAMS) so
+	// that a small layer's update does not queue behind a large one's; evLayer[l] fires when every owner's band
+	// of layer l's new weights (and their low TF32 parts) has landed here.  The next use of W_l waits for it --
+	// normally the next window's forward product of that layer, so the tail of the exchange overlaps the next
+	// window instead of ending this one.
+	enum { DP_COMM_STREAMS = 4 };
+	cudaStream_t layerStream[DP_COMM_STREAMS] = {};
+	cudaEvent_t evLayer[GL_MAX_WEIGHT_LAYERS] = {};
+	bool layerPending[GL_MAX_WEIGHT_LAYERS] = {};
 	cudaEvent_t evGrad[GL_MAX_WEIGHT_LAYERS + 1] = {};
 	cudaEvent_t evComm = nullptr;
 	int dpOverlap = 1;
-	int dpReserveSms = 8;
+	int dpReserveSms = 20;  // upper bound; a product keeps fewer free where that saves it a wave of tiles
 	// gradient exchange over peer memory (dp_push.cu); dpPush == false: the NCCL all-reduce path
 	bool dpPush = false;
 	unsigned dpStep = 0;                 // window counter, the value the flags are raised to
@@ -281,6 +290,25 @@ static NetView make_view(const gl_net* n)
 static int use_device(const gl_net* n)
 {
 	CU(cudaSetDevice(n->d.device));
+	return 0;
+}
+
+// Peer-memory exchange: makes the compute stream wait until layer l's new weights have landed (no-op when
+// nothing is outstanding).
+static int dp_wait_layer(gl_net* n, int l)
+{
+	if (n->layerPending[l])
+	{
+		CU(cudaStreamWaitEvent(n->stream, n->evLayer[l], 0));
+		n->layerPending[l] = false;
+	}
+	return 0;
+}
+// The same for every layer: before anything but the next window's own products reads or replaces the weights.
+static int dp_join(gl_net* n)
+{
+	for (int l = 0; l <= n->H; ++l)
+		if (int r = dp_wait_layer(n, l)) return r;
 	return 0;
 }
 
@@ -425,6 +453,8 @@ extern "C" int gl_destroy(gl_net* n)
 	cudaSetDevice(n->d.device);
 	if (n->stream) cudaStreamSynchronize(n->stream);
 	if (n->commStream) cudaStreamSynchronize(n->commStream);
+	for (int i = 0; i < gl_net::DP_COMM_STREAMS; ++i)
+		if (n->layerStream[i]) cudaStreamSynchronize(n->layerStream[i]);
 	if (n->dpArena)
 	{
 		// peers may still be writing into this rank's memory, and this rank maps theirs: meet once
@@ -435,6 +465,9 @@ extern "C" int gl_destroy(gl_net* n)
 	}
 	if (n->comm && g_nccl.CommDestroy) g_nccl.CommDestroy(n->comm);
 	if (n->commStream) cudaStreamDestroy(n->commStream);
+	for (int i = 0; i < gl_net::DP_COMM_STREAMS; ++i)
+		if (n->layerStream[i]) cudaStreamDestroy(n->layerStream[i]);
+	for (int l = 0; l < GL_MAX_WEIGHT_LAYERS; ++l) if (n->evLayer[l]) cudaEventDestroy(n->evLayer[l]);
 	for (int l = 0; l <= GL_MAX_WEIGHT_LAYERS; ++l) if (n->evGrad[l]) cudaEventDestroy(n->evGrad[l]);
 	if (n->evComm) cudaEventDestroy(n->evComm);
 	free_work(n);
@@ -524,6 +557,7 @@ extern "C" int gl_set_weights(gl_net* n, const float* w, const float* bias)
 {
 	if (!n || !w) return fail(GL_ERR_INVALID, "gl_set_weights: null argument");
 	if (int r = use_device(n)) return r;
+	if (int r = dp_join(n)) return r;
 	if (int r = upload(n, n->dW, w, (size_t)n->nw)) return r;
 	float b[GL_MAX_WEIGHT_LAYERS] = {0};
 	for (int l = 1; l <= n->H; ++l) b[l] = bias ? bias[l - 1] : 0.0f;
@@ -551,6 +585,7 @@ extern "C" int gl_get_weights(gl_net* n, float* w, float* bias)
 {
 	if (!n || !w) return fail(GL_ERR_INVALID, "gl_get_weights: null argument");
 	if (int r = use_device(n)) return r;
+	if (int r = dp_join(n)) return r;
 	CU(cudaStreamSynchronize(n->stream));
 	CU(cudaMemcpy(w, n->dW, (size_t)n->nw * sizeof(float), cudaMemcpyDeviceToHost));
 	if (bias)
@@ -583,6 +618,7 @@ extern "C" int gl_save_state(gl_net* n, const char* path)
 {
 	if (!n || !path) return fail(GL_ERR_INVALID, "gl_save_state: bad argument");
 	if (int r = use_device(n)) return r;
+	if (int r = dp_join(n)) return r;
 	CU(cudaStreamSynchronize(n->stream));
 	StateHeader h;
 	memset(&h, 0, sizeof h);
@@ -1077,6 +1113,26 @@ static Operand op_delta(gl_net* n, int L, int rows)
 	return o;
 }
 
+// SMs a data-parallel product leaves free for the exchange kernels that run beside it: as many as
+// dpReserveSms, but never so many that the product's tiles need another wave.
+static int dp_reserve_for(const gl_net* n, int M, int N)
+{
+	if (!(n->world > 1 && n->dpOverlap) || n->dpReserveSms <= 0) return 0;
+	static int sms = 0;
+	if (!sms)
+	{
+		if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, n->d.device) != cudaSuccess || sms < 1) sms = 148;
+	}
+	const long long wide = (long long)(M / 128) * (N / 256);
+	const long long tiles = (N % 256 == 0 && wide >= 74) ? wide : (long long)(M / 128) * (N / 128);
+	if (tiles < 1) return n->dpReserveSms;
+	const int floor_r = n->dpReserveSms < 8 ? n->dpReserveSms : 8;
+	const long long waves = (tiles + (sms - floor_r) - 1) / (sms - floor_r);
+	int r = n->dpReserveSms;
+	while (r > floor_r && (tiles + (sms - r) - 1) / (sms - r) > waves) --r;
+	return r;
+}
+
 // Forward of `rows` rows starting at device pointer X; activations land in dA[1..H+1].
 static int batched_forward(gl_net* n, const float* X, int rows, int64_t* launches)
 {
@@ -1084,6 +1140,7 @@ static int batched_forward(gl_net* n, const float* X, int rows, int64_t* launche
 	n->loX = false;
 	for (int l = 0; l <= n->H; ++l)
 	{
+		if (int r = dp_wait_layer(n, l)) return r;
 		GemmArgs g;
 		memset(&g, 0, sizeof g);
 		g.A = in;
@@ -1103,6 +1160,7 @@ static int batched_forward(gl_net* n, const float* X, int rows, int64_t* launche
 		// products need no separate split pass (not for the last layer: the head rewrites it)
 		g.C_lo = (l < n->H && fuse_lo_in_epilogue()) ? n->dAlo[l + 1] : nullptr;
 		g.relu_mask_out = (l < n->H) ? n->dMask[l + 1] : nullptr;
+		g.sm_reserve = dp_reserve_for(n, g.M, g.N);  // the previous window's exchange may still be finishing beside it
 		bool tc = false;
 		if (int r = run_gemm(n, g, op_act(n, l, X, rows), op_w(n, l), launches, &tc)) return r;
 		n->loA[l + 1] = tc && g.C_lo != nullptr;
@@ -1127,11 +1185,13 @@ struct DpTrace
 		ev.push_back(e);
 		name.push_back(std::string(what) + (l >= 0 ? std::to_string(l) : std::string()));
 	}
-	void dump(int rank, cudaStream_t a, cudaStream_t b)
+	void dump(int rank, cudaStream_t a, cudaStream_t b, cudaStream_t* more, int n_more)
 	{
 		if (!on) return;
 		cudaStreamSynchronize(a);
 		if (b) cudaStreamSynchronize(b);
+		for (int i = 0; i < n_more; ++i)
+			if (more[i]) cudaStreamSynchronize(more[i]);
 		for (size_t i = 1; i < ev.size(); ++i)
 		{
 			float ms = 0;
@@ -1362,31 +1422,49 @@ static int batched_window(gl_net* n, const float* X, const float* Y, int rows, i
 	CU(cudaMemcpyAsync(n->dLastOut, n->dA[n->H + 1] + (size_t)(rows - 1) * n->n_out, (size_t)n->n_out * sizeof(float),
 	                   cudaMemcpyDeviceToDevice, n->stream));
 
-	for (int L = n->H + 1; L >= 1; --L)
+	// Error propagation first, down the whole chain: D_{H+1} -> D_H -> ... -> D_1.  None of the weight
+	// gradients below changes what it reads (a layer's new weights are written only after every rank has
+	// signalled that layer's gradient, which it does after these products).
+	for (int L = n->H + 1; L >= 2; --L)
 	{
 		const int l = L - 1;
 		const int ni = n->d.sizes[l], no = n->d.sizes[L];
+		GemmArgs g;
+		memset(&g, 0, sizeof g);
+		g.A = n->dD[L]; g.a_sm = no; g.a_sk = 1;
+		g.B = n->dW + n->woff[l]; g.b_sn = 1; g.b_sk = ni;
+		g.C = n->dD[l]; g.ldc = ni;
+		g.M = rows; g.N = ni; g.K = no;
+		g.epi = EPI_ERRPROP;
+		g.aux = n->dA[l]; g.ld_aux = ni;
+		g.act = n->d.activation[l - 1];
+		g.par = 0.01f;  // the reference passes a fixed 0.01, network.cpp:618
+		g.C_lo = fuse_lo_in_epilogue() ? n->dDlo[l] : nullptr;
+		g.relu_mask_in = n->maskValid[l] ? n->dMask[l] : nullptr;
+		g.sm_reserve = dp_reserve_for(n, g.M, g.N);
+		bool tc = false;
+		if (int r = run_gemm(n, g, op_delta(n, L, rows), op_w(n, l), &launches, &tc)) return r;
+		n->loD[l] = tc && g.C_lo != nullptr;
+	}
+	tr.mark("deltas done", -1, n->stream);
+	// Then the weight gradients, largest layer first: under data parallelism each one starts its layer's
+	// exchange, and the largest exchange gets the remaining products to hide under.
+	int order[GL_MAX_WEIGHT_LAYERS];
+	for (int l = 0; l <= n->H; ++l) order[l] = l;
+	for (int i = 1; i <= n->H; ++i)
+		for (int j = i; j > 0 && (n->woff[order[j] + 1] - n->woff[order[j]]) > (n->woff[order[j - 1] + 1] - n->woff[order[j - 1]]); --j)
+		{
+			const int t = order[j];
+			order[j] = order[j - 1];
+			order[j - 1] = t;
+		}
+	for (int oi = 0; oi <= n->H; ++oi)
+	{
+		const int l = order[oi];
+		const int L = l + 1;
+		const int ni = n->d.sizes[l], no = n->d.sizes[L];
 		const float* Al = (l == 0) ? X : n->dA[l];
 		const Operand opD = op_delta(n, L, rows);
-		if (l >= 1)
-		{
-			GemmArgs g;
-			memset(&g, 0, sizeof g);
-			g.A = n->dD[L]; g.a_sm = no; g.a_sk = 1;
-			g.B = n->dW + n->woff[l]; g.b_sn = 1; g.b_sk = ni;
-			g.C = n->dD[l]; g.ldc = ni;
-			g.M = rows; g.N = ni; g.K = no;
-			g.epi = EPI_ERRPROP;
-			g.aux = n->dA[l]; g.ld_aux = ni;
-			g.act = n->d.activation[l - 1];
-			g.par = 0.01f;  // the reference passes a fixed 0.01, network.cpp:618
-			g.C_lo = fuse_lo_in_epilogue() ? n->dDlo[l] : nullptr;
-			g.relu_mask_in = n->maskValid[l] ? n->dMask[l] : nullptr;
-			g.sm_reserve = (n->world > 1 && n->dpOverlap) ? n->dpReserveSms : 0;
-			bool tc = false;
-			if (int r = run_gemm(n, g, opD, op_w(n, l), &launches, &tc)) return r;
-			n->loD[l] = tc && g.C_lo != nullptr;
-		}
 		const float* colterm = nullptr;
 		if (n->d.wd1[l] != 0.0f || n->d.wd2[l] != 0.0f)
 		{
@@ -1405,13 +1483,14 @@ static int batched_window(gl_net* n, const float* X, const float* Y, int rows, i
 			g.epi = EPI_GRAD;
 			g.alpha = n->d.lr[l];
 			g.colterm = colterm;
-			g.sm_reserve = (n->world > 1 && n->dpOverlap && L <= n->H) ? n->dpReserveSms : 0;
+			g.sm_reserve = dp_reserve_for(n, no, ni);
 			if (push)
 			{
 				// the tensor-core epilogue stores every row band straight into its owner's memory
 				g.peer_maps = static_cast<const char*>(n->dpMaps) + (size_t)l * DP_MAX_WORLD * 128;
 				g.peer_bases = n->dpBases + (size_t)l * DP_MAX_WORLD;
 				g.band_rows = n->dpBand[l];
+				g.peer_self = n->rank;
 			}
 			bool gtc = false;
 			if (int r = run_gemm(n, g, opD, op_act(n, l, X, rows), &launches, &gtc)) return r;
@@ -1430,44 +1509,45 @@ static int batched_window(gl_net* n, const float* X, const float* Y, int rows, i
 		}
 		if (push)
 		{
-			// this rank's contributions to layer l have been stored at their owners: tell them, and let
-			// the communication stream do this rank's own band (sum the sources in rank order, update,
-			// write the new weights into every replica) while the main stream goes on with the layers below
+			// this rank's contributions to layer l have been stored at their owners: tell them, and let the
+			// layer's exchange stream do this rank's own band (sum the sources in rank order, update, write the
+			// new weights into every replica) while the compute stream goes on with the other gradients
+			cudaStream_t cs = n->layerStream[l % gl_net::DP_COMM_STREAMS];
 			CU(launch_dp_signal(peerFlags, n->world, DP_WORD_GFLAG + l * DP_MAX_WORLD + n->rank, stepv, n->stream));
 			tr.mark("grad stored L", l, n->stream);
 			CU(cudaEventRecord(n->evGrad[l], n->stream));
-			CU(cudaStreamWaitEvent(n->commStream, n->evGrad[l], 0));
-			CU(launch_dp_wait(n->dpArena, DP_WORD_GFLAG + l * DP_MAX_WORLD, 1, n->world, 0, 0, stepv, n->dFlags + 1, 20 + l,
-			                  n->commStream));
-			tr.mark("owner has all L", l, n->commStream);
+			CU(cudaStreamWaitEvent(cs, n->evGrad[l], 0));
+			CU(launch_dp_wait(n->dpArena, DP_WORD_GFLAG + l * DP_MAX_WORLD, 1, n->world, 0, 0, stepv, n->dFlags + 1, 20 + l, cs));
+			tr.mark("owner has all L", l, cs);
 			const int band = n->dpBand[l];
 			int own_rows = no - n->rank * band;
 			own_rows = own_rows < 0 ? 0 : (own_rows > band ? band : own_rows);
 			const float* part = reinterpret_cast<const float*>(n->dpArena + DP_FLAG_BYTES) + n->dpSlotOff[l];
 			CU(launch_dp_reduce_update(part, n->dpSlotOff[n->H + 1], n->world, (long long)own_rows * ni, 1.0f / (float)global_rows,
 			                           n->woff[l] + (long long)n->rank * band * ni, peerW, n->rank, peerFlags,
-			                           l == 0 ? 148 * 4 : n->dpPushBlocks, n->commStream));
-			CU(launch_dp_signal(peerFlags, n->world, DP_WORD_WFLAG + l * DP_MAX_WORLD + n->rank, stepv, n->commStream));
-			tr.mark("band updated L", l, n->commStream);
+			                           oi == n->H ? 148 * 4 : n->dpPushBlocks, cs));
+			CU(launch_dp_signal(peerFlags, n->world, DP_WORD_WFLAG + l * DP_MAX_WORLD + n->rank, stepv, cs));
+			tr.mark("band updated L", l, cs);
 			// once every owner's band of this layer has landed here, split off the low TF32 parts of the
-			// layer's new weights -- still beside the backward pass for all but the last layer
-			CU(launch_dp_wait(n->dpArena, DP_WORD_WFLAG + l * DP_MAX_WORLD, 1, n->world, 0, 0, stepv, n->dFlags + 1, 40 + l,
-			                  n->commStream));
+			// layer's new weights; evLayer[l] then releases the next product that reads W_l
+			CU(launch_dp_wait(n->dpArena, DP_WORD_WFLAG + l * DP_MAX_WORLD, 1, n->world, 0, 0, stepv, n->dFlags + 1, 40 + l, cs));
 			const int64_t cnt = n->woff[l + 1] - n->woff[l];
 			if (n->dWlo && cnt % 4 == 0 && n->woff[l] % 4 == 0)
 			{
-				CU(launch_split_lo(n->dW + n->woff[l], n->dWlo + n->woff[l], cnt, n->commStream));
+				CU(launch_split_lo(n->dW + n->woff[l], n->dWlo + n->woff[l], cnt, cs));
 				++launches;
 			}
 			else
 				lo_all = false;
-			tr.mark("layer complete L", l, n->commStream);
+			tr.mark("layer complete L", l, cs);
+			CU(cudaEventRecord(n->evLayer[l], cs));
+			n->layerPending[l] = true;
 			launches += 5;
 		}
 		else if (n->world > 1 && n->dpOverlap)
 		{
-			// this layer's gradient is complete: reduce it on the communication stream while the main
-			// stream goes on with the layers below
+			// this layer's gradient is complete: reduce it on the communication stream while the compute
+			// stream goes on with the other gradients
 			CU(cudaEventRecord(n->evGrad[l], n->stream));
 			CU(cudaStreamWaitEvent(n->commStream, n->evGrad[l], 0));
 			NC(g_nccl.AllReduce(n->dG + n->woff[l], n->dG + n->woff[l], (size_t)(n->woff[l + 1] - n->woff[l]), NCCL_FLOAT32,
@@ -1510,9 +1590,9 @@ static int batched_window(gl_net* n, const float* X, const float* Y, int rows, i
 		// and every rank's record have landed here, and finish the window locally
 		CU(launch_dp_small_push(n->dG + n->nw, sums2, peerFlags, n->world, n->rank, (int)(stepv & 1u), stepv, n->stream));
 		tr.mark("backward done", -1, n->stream);
-		CU(cudaEventRecord(n->evComm, n->commStream));
 		CU(launch_dp_wait(n->dpArena, 0, 0, 0, DP_WORD_SFLAG, n->world, stepv, n->dFlags + 1, 60, n->stream));
-		CU(cudaStreamWaitEvent(n->stream, n->evComm, 0));  // every layer's new weights have landed (and their low parts)
+		// (the layers' new weights are NOT awaited here: the next product that reads W_l waits for evLayer[l],
+		// so the end of the exchange runs under the next window's forward pass; see dp_wait_layer / dp_join)
 		CU(launch_dp_finish(n->dpArena, n->world, (int)(stepv & 1u), n->dG + n->nw, sums2, n->dBias, n->dBscale, n->H, n->dFlags,
 		                    n->stream));
 		tr.mark("window done", -1, n->stream);
@@ -1527,7 +1607,7 @@ static int batched_window(gl_net* n, const float* X, const float* Y, int rows, i
 		n->loW = n->dWlo != nullptr;
 	}
 	CU(cudaEventRecord(n->ev1, n->stream));
-	tr.dump(n->rank, n->stream, n->commStream);
+	tr.dump(n->rank, n->stream, n->commStream, n->layerStream, gl_net::DP_COMM_STREAMS);
 	n->launches += launches;
 	n->lastWindowLaunches = launches;
 	return window_result(n, out, sums2, global_rows, launches);
@@ -2381,6 +2461,12 @@ extern "C" int gl_dp_init(gl_net* n, int32_t rank, int32_t world, const void* id
 		CU(cudaStreamCreateWithPriority(&n->commStream, cudaStreamNonBlocking, hi));
 	}
 	for (int l = 0; l <= GL_MAX_WEIGHT_LAYERS; ++l) CU(cudaEventCreateWithFlags(&n->evGrad[l], cudaEventDisableTiming));
+	{
+		int lo = 0, hi = 0;
+		CU(cudaDeviceGetStreamPriorityRange(&lo, &hi));
+		for (int i = 0; i < gl_net::DP_COMM_STREAMS; ++i) CU(cudaStreamCreateWithPriority(&n->layerStream[i], cudaStreamNonBlocking, hi));
+		for (int l = 0; l < GL_MAX_WEIGHT_LAYERS; ++l) CU(cudaEventCreateWithFlags(&n->evLayer[l], cudaEventDisableTiming));
+	}
 	CU(cudaEventCreateWithFlags(&n->evComm, cudaEventDisableTiming));
 	if (const char* e = getenv("GLADES_DP_OVERLAP")) n->dpOverlap = atoi(e) != 0;
 	if (const char* e = getenv("GLADES_DP_RESERVE_SMS")) n->dpReserveSms = atoi(e);
@@ -2424,6 +2510,7 @@ extern "C" int gl_timer_stop(gl_net* n, double* ms)
 {
 	if (!n || !ms || !n->tim0) return fail(GL_ERR_INVALID, "gl_timer_stop: bad argument");
 	if (int r = use_device(n)) return r;
+	if (int r = dp_join(n)) return r;  // the timed work includes the end of the last window's gradient exchange
 	CU(cudaEventRecord(n->tim1, n->stream));
 	CU(cudaEventSynchronize(n->tim1));
 	float f = 0;
@@ -2479,6 +2566,7 @@ extern "C" int gl_sync(gl_net* n)
 {
 	if (!n) return fail(GL_ERR_INVALID, "gl_sync: null handle");
 	if (int r = use_device(n)) return r;
+	if (int r = dp_join(n)) return r;
 	CU(cudaStreamSynchronize(n->stream));
 	int flags[4];
 	CU(cudaMemcpy(flags, n->dFlags, sizeof flags, cudaMemcpyDeviceToHost));

@@ -95,6 +95,33 @@ __global__ void __launch_bounds__(TcSmem<BN, BK, STAGES, SBUF>::THREADS, 1)
 	const int total_tiles = p.tiles_m * p.tiles_n;
 	constexpr int TC_BAND = 16;
 	auto tile_origin = [&](int t, int& m0, int& n0) {
+		if (PEER)
+		{
+			// Data-parallel weight gradient: the tiles are walked owner band by owner band, m-fastest inside a
+			// band, and every rank starts with the band of the rank after it.  At any moment the ranks of the
+			// group therefore store into different owners, so no owner's NVLink ingress carries more than one
+			// sender's stream (all ranks walking the bands in the same order would aim all their stores at the same
+			// owner at once).  This rank's own band comes last: its stores are local.
+			const int band_mt = peer.band_rows / TC_BM;
+			const int nbands = (p.tiles_m + band_mt - 1) / band_mt;
+			int left = t;
+			for (int s = 0; s < nbands; ++s)
+			{
+				const int band = (peer.self + 1 + s) % nbands;
+				const int mt_in = min(band_mt, p.tiles_m - band * band_mt);
+				const int cnt = mt_in * p.tiles_n;
+				if (left < cnt)
+				{
+					m0 = (band * band_mt + left % mt_in) * TC_BM;
+					n0 = (left / mt_in) * BN;
+					return;
+				}
+				left -= cnt;
+			}
+			m0 = 0;  // not reached: t < tiles_m * tiles_n
+			n0 = 0;
+			return;
+		}
 		const int band_tiles = TC_BAND * p.tiles_n;
 		const int band = t / band_tiles;
 		const int in_band = t - band * band_tiles;
@@ -557,6 +584,7 @@ cudaError_t launch_gemm_tc(const GemmArgs& g, const float* A_lo, const float* B_
 	peer.maps = reinterpret_cast<const CUtensorMap*>(g.peer_maps);
 	peer.bases = g.peer_bases;
 	peer.band_rows = g.band_rows;
+	peer.self = g.peer_self;
 	if (g.peer_maps && (g.band_rows < TC_BM || g.band_rows % TC_BM || g.C_lo)) return cudaErrorInvalidValue;
 	{
 		static int dbg = -1;

@@ -91,6 +91,7 @@ struct GemmArgs
 	const void* peer_maps;
 	float* const* peer_bases;
 	int band_rows;
+	int peer_self;         // this rank (the walk over the owners' bands starts with the rank after it)
 };
 cudaError_t launch_gemm_ffma(const GemmArgs& g, cudaStream_t s);
 

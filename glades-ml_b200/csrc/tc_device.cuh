@@ -46,6 +46,7 @@ struct TcPeer
 	const CUtensorMap* maps;  // device array, one map per owner
 	float* const* bases;      // device array, one base pointer per owner
 	int band_rows;
+	int self;                 // this rank: its CTAs walk the owners' bands starting with owner self + 1
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }

@@ -8,6 +8,9 @@ mode `gpu`:  the same through the library on one GPU per rank (its own exchange:
              rank 0.  Small layers: the products run on the FFMA kernel.
 mode `gpu_tc`: as `gpu` with layers wide enough for the tensor-core kernel, whose weight-gradient
              epilogue stores its row bands straight into the owning rank's memory.
+mode `gpu_tc_wide`: as `gpu_tc` with a 2560 -> 2048 layer: its gradient product has 160 tiles of 128 x 256,
+             so the data-parallel epilogue runs on the 256-wide persistent variant with several tiles per
+             CTA (the instantiation the multi-GPU benchmark measures), over four consecutive windows.
 Exit code 0 = parity holds on every rank.
 """
 import os
@@ -31,12 +34,15 @@ def main():
     o = ge.import_oracle()
     rng = np.random.default_rng(123)  # same data on every rank
     on_gpu = mode.startswith("gpu")
-    sizes = {"gpu": [128, 256, 128], "gpu_tc": [256, 512, 384, 256], "cpu": [12, 20, 9, 4]}[mode]
-    acts = {"gpu": ["relu", "softmax"], "gpu_tc": ["relu", "tanh", "softmax"], "cpu": ["tanh", "relu", "sigmoid"]}[mode]
-    rows = {"gpu": 512, "gpu_tc": 1024, "cpu": 37}[mode]   # 37 does not divide by 2: uneven shards
-    steps = 2 if mode != "gpu_tc" else 4
-    momentum = 0.6
-    gemm = g.GEMM_TCGEN05 if mode == "gpu_tc" else g.GEMM_AUTO
+    sizes = {"gpu": [128, 256, 128], "gpu_tc": [256, 512, 384, 256], "gpu_tc_wide": [512, 2560, 2048, 256],
+             "cpu": [12, 20, 9, 4]}[mode]
+    acts = {"gpu": ["relu", "softmax"], "gpu_tc": ["relu", "tanh", "softmax"], "gpu_tc_wide": ["relu", "relu", "softmax"],
+            "cpu": ["tanh", "relu", "sigmoid"]}[mode]
+    rows = {"gpu": 512, "gpu_tc": 1024, "gpu_tc_wide": 1024, "cpu": 37}[mode]   # 37 does not divide by 2: uneven shards
+    steps = 4 if mode.startswith("gpu_tc") else 2
+    momentum = 0.0 if mode == "gpu_tc_wide" else 0.6
+    gemm = g.GEMM_TCGEN05 if mode.startswith("gpu_tc") else g.GEMM_AUTO
+    w_range = 0.03 if mode == "gpu_tc_wide" else 0.2
     d = g.make_desc(sizes, acts, "classification", batch=rows, lr=0.05, momentum=momentum, mode=g.MODE_BATCHED, gemm=gemm,
                     device=int(os.environ.get("LOCAL_RANK", "0")) if on_gpu else 0)
     x = rng.standard_normal((rows, sizes[0])).astype(np.float32)
@@ -46,7 +52,7 @@ def main():
     else:
         y = rng.uniform(0.05, 0.95, (rows, sizes[-1])).astype(np.float32)
     nw = g.weight_count(d)
-    w = rng.uniform(-0.2, 0.2, nw).astype(np.float32)
+    w = rng.uniform(-w_range, w_range, nw).astype(np.float32)
     b = rng.uniform(-0.1, 0.1, len(sizes) - 2).astype(np.float32)
     first, count = g.shard_range(rows, rank, world)
     ok = True
@@ -86,9 +92,16 @@ def main():
         if want is not None and net.dp_mode() != (2 if want == "1" else 1):
             print("dp mode %d does not match GLADES_DP_PUSH=%s" % (net.dp_mode(), want))
             ok = False
+        before = g.tc_variant_counts()
         for step in range(steps):
-            m = net.train_window(0, count)
+            # only the last window asks for its figures: the others are queued back to back, so the end of one
+            # window's exchange runs under the next window's forward pass
+            m = net.train_window(0, count, want_metrics=(step == steps - 1))
         wg, bg = net.get_weights()
+        dc = [a - c for a, c in zip(g.tc_variant_counts(), before)]
+        if mode == "gpu_tc_wide" and net.dp_mode() == 2 and not (dc[3] >= steps and dc[1] >= steps and dc[2] >= steps):
+            print("the 256-wide persistent peer-store variant did not run: %r" % (dc,))
+            ok = False
         tw = torch.from_numpy(wg.copy())
         td.broadcast(tw, 0)
         ok = ok and np.array_equal(tw.numpy().view(np.uint32), wg.view(np.uint32))  # replicas identical

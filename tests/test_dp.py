@@ -44,7 +44,8 @@ def test_two_gloo_ranks_reproduce_one_rank(oracle):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("mode,push", [("gpu", "1"), ("gpu", "0"), ("gpu_tc", "1"), ("gpu_tc", "0")])
+@pytest.mark.parametrize("mode,push", [("gpu", "1"), ("gpu", "0"), ("gpu_tc", "1"), ("gpu_tc", "0"), ("gpu_tc_wide", "1"),
+                                       ("gpu_tc_wide", "0")])
 def test_two_gpus_reproduce_one_gpu(g, mode, push):
     """push=1: the gradient exchange over peer memory (required, no silent NCCL fallback);
     push=0: one NCCL all-reduce per layer."""
