@@ -174,6 +174,26 @@ def test_cta_pair_variant_in_a_subprocess():
     assert r.returncode == 0, r.stdout[-1500:] + r.stderr[-500:]
 
 
+def _rows_clear_of_relu_threshold(rng, draw, x, W0, W1, b1, margin=1e-5):
+    """The reference's ReLU is discontinuous: 0 below 0.046, the identity above (GMath/gmath.cpp:62-68).  A
+    hidden pre-activation within fp32 rounding of 0.046 may fall on either side in two correct fp32
+    evaluations, and the two then differ by far more than any rounding tolerance.  So that the comparisons
+    below measure the kernels and not that coin toss, rows with a pre-activation of either hidden layer
+    within `margin` of the threshold (float64 evaluation) are drawn again until none is left."""
+    W0 = W0.astype(np.float64)
+    W1 = W1.astype(np.float64)
+    todo = np.arange(x.shape[0])
+    for _ in range(100):
+        z1 = x[todo].astype(np.float64) @ W0.T
+        z2 = np.where(z1 < 0.046, 0.0, z1) @ W1.T + float(b1)
+        bad = np.any(np.abs(z1 - 0.046) < margin, axis=1) | np.any(np.abs(z2 - 0.046) < margin, axis=1)
+        todo = todo[bad]
+        if todo.size == 0:
+            return x
+        x[todo] = draw(todo.size)
+    raise AssertionError("could not clear the rows of the ReLU threshold")
+
+
 def _onehot(rows, n, labels):
     y = np.zeros((rows, n), np.float32)
     y[np.arange(rows), labels] = 1.0
@@ -185,7 +205,8 @@ def test_wide_mlp_window_on_the_benchmarked_variant_vs_restatement(g, oracle):
     cross-entropy, lr 1e-2, weights U(+-1/sqrt(n_in))) on 1024 rows, against the double-accumulating CPU
     restatement: loss, every updated weight within 1e-5 of the largest weight, identical predicted
     classes.  At this size the layer products run on the 256-wide persistent tiles (the instantiation
-    the benchmark measures), several tiles per CTA for the 4096 x 4096 gradient."""
+    the benchmark measures), several tiles per CTA for the 4096 x 4096 gradient.  The rows are drawn so
+    that no hidden pre-activation lies within 1e-5 of the discontinuity of the reference's ReLU."""
     sizes = [1024, 4096, 4096, 1024]
     rows = 1024
     rng = np.random.default_rng(404)
@@ -194,6 +215,9 @@ def test_wide_mlp_window_on_the_benchmarked_variant_vs_restatement(g, oracle):
     w = np.concatenate([rng.uniform(-1, 1, sizes[i] * sizes[i + 1]).astype(np.float32) / np.float32(np.sqrt(sizes[i]))
                         for i in range(3)])
     b = np.array([0.01, -0.02], np.float32)
+    n01, n12 = sizes[0] * sizes[1], sizes[1] * sizes[2]
+    x = _rows_clear_of_relu_threshold(rng, lambda k: rng.standard_normal((k, sizes[0]), dtype=np.float32), x,
+                                      w[:n01].reshape(sizes[1], sizes[0]), w[n01:n01 + n12].reshape(sizes[2], sizes[1]), b[0])
     d = g.make_desc(sizes, ["relu", "relu", "softmax"], "classification", batch=rows, lr=1e-2, mode=g.MODE_BATCHED)
     net = g.Net(d)
     net.set_weights(w, b)
@@ -211,16 +235,14 @@ def test_wide_mlp_window_on_the_benchmarked_variant_vs_restatement(g, oracle):
     lo = 0
     for l in range(3):
         hi = lo + sizes[l] * sizes[l + 1]
-        assert np.max(np.abs(wg[lo:hi].astype(np.float64) - ws[lo:hi])) <= 1e-5 * np.max(np.abs(ws[lo:hi])), "layer %d weights" % l
-        # The update itself (new - old) carries the whole gradient, so compare it too.  Both sides round the
-        # new weight to fp32 (one ulp of the largest weight between them), and the reference's ReLU is
-        # discontinuous (0 below 0.046, GMath/gmath.cpp:62-68): of the 8 M hidden pre-activations of this
-        # window one or two lie within rounding of the threshold and may fall on either side, which moves the
-        # updates of the layers below by about 1e-3 of their largest entry.
+        scale = float(np.max(np.abs(ws[lo:hi])))
+        assert np.max(np.abs(wg[lo:hi].astype(np.float64) - ws[lo:hi])) <= 1e-5 * scale, "layer %d weights" % l
+        # the update itself (new - old) carries the whole gradient: within 1e-3 of its largest entry plus the
+        # rounding of the stored weight on both sides (the update is 1e-4 of the weight), 1e-4 on average
         ug = wg[lo:hi].astype(np.float64) - w[lo:hi]
         us = ws[lo:hi].astype(np.float64) - w[lo:hi]
-        ulp = float(np.spacing(np.float32(np.max(np.abs(ws[lo:hi])))))
-        assert np.max(np.abs(ug - us)) <= 5e-3 * np.max(np.abs(us)) + 2 * ulp, "layer %d update" % l
+        ulp = float(np.spacing(np.float32(scale)))
+        assert np.max(np.abs(ug - us)) <= 1e-3 * np.max(np.abs(us)) + 2 * ulp, "layer %d update" % l
         assert np.mean(np.abs(ug - us)) <= 1e-4 * np.max(np.abs(us)) + ulp, "layer %d update, mean" % l
         lo = hi
     assert np.allclose(bg, bs, rtol=1e-4, atol=1e-7)
@@ -238,7 +260,8 @@ def test_wide_mlp_window_on_the_benchmarked_variant_vs_restatement(g, oracle):
 def test_inference_net_forward_on_the_benchmarked_variant_vs_restatement(g, oracle):
     """Forward pass of the batched-inference net (784-2048-2048-10, ReLU/ReLU/softmax, weights
     U(-0.05, 0.05), rows U(0,1)) on 2048 rows against the restatement: probabilities within 1e-5 and the
-    same predicted class for every row.  The two hidden products run on the 256-wide tiles."""
+    same predicted class for every row.  The two hidden products run on the 256-wide tiles.  Rows are drawn
+    clear of the discontinuity of the reference's ReLU (see _rows_clear_of_relu_threshold)."""
     sizes = [784, 2048, 2048, 10]
     rows = 2048
     rng = np.random.default_rng(505)
@@ -246,6 +269,9 @@ def test_inference_net_forward_on_the_benchmarked_variant_vs_restatement(g, orac
     y = np.full((rows, sizes[-1]), 0.01, np.float32)
     nw = sum(sizes[i] * sizes[i + 1] for i in range(3))
     w = rng.uniform(-0.05, 0.05, nw).astype(np.float32)
+    n01, n12 = sizes[0] * sizes[1], sizes[1] * sizes[2]
+    x = _rows_clear_of_relu_threshold(rng, lambda k: rng.random((k, sizes[0]), dtype=np.float32), x,
+                                      w[:n01].reshape(sizes[1], sizes[0]), w[n01:n01 + n12].reshape(sizes[2], sizes[1]), 0.01)
     d = g.make_desc(sizes, ["relu", "relu", "softmax"], "classification", batch=rows, lr=0.0, mode=g.MODE_BATCHED)
     net = g.Net(d)
     net.set_weights(w, np.array([0.01, 0.02], np.float32))
