@@ -146,6 +146,8 @@ def lib():
         "gl_get_last_outputs": (C.c_int, [vp, vp]),
         "gl_get_epochs": (C.c_int, [vp]),
         "gl_stop": (None, [vp]),
+        "gl_snapshot_submit": (C.c_int, [vp]),
+        "gl_snapshot_collect": (C.c_int, [vp, vp, vp, vp, i32]),
         "gl_sync": (C.c_int, [vp]),
         "gl_kernel_launches": (i64, [vp]),
         "gl_tensor_core_launches": (i64, [vp]),
@@ -163,6 +165,7 @@ def lib():
         "gl_tc_variant_counts": (None, [C.POINTER(i64)]),
         "gl_matmul_static": (C.c_int, [vp, i64, i64, vp, i64, i64, vp, i64, i32, i32, i32, i32]),
         "gl_matmul_static_error": (C.c_char_p, []),
+        "gl_standardize_table": (C.c_int, [vp, i64, i32, vp, vp, vp, i32, vp, C.POINTER(i32), vp, C.POINTER(i32), vp, i32]),
         "gl_onehot_fill": (C.c_int, [vp, vp, i64, i32, f32, f32, i32]),
         "gl_timer_start": (C.c_int, [vp]),
         "gl_timer_stop": (C.c_int, [vp, C.POINTER(C.c_double)]),
@@ -348,6 +351,21 @@ class Net:
 
     def stop(self):
         lib().gl_stop(self.h)
+
+    def snapshot_submit(self):
+        _check(lib().gl_snapshot_submit(self.h))
+
+    def snapshot_collect(self, wait=True):
+        """(weights, biases, last-row pre-activations), or None when wait is False and the copy still runs."""
+        w = np.empty(self.nw, np.float32)
+        b = np.empty(max(self.H, 1), np.float32)
+        n = sum(self.desc.sizes[l] for l in range(1, self.desc.n_layers))
+        z = np.empty(n, np.float32)
+        st = lib().gl_snapshot_collect(self.h, _ptr(w), _ptr(b), _ptr(z), 1 if wait else 0)
+        if st == 1:
+            return None
+        _check(st)
+        return w, b[: self.H], z
 
     def sync(self):
         _check(lib().gl_sync(self.h))

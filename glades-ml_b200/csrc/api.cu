@@ -162,6 +162,14 @@ struct gl_net
 	float* dHist = nullptr;
 	int* dHistLen = nullptr;
 	float* dScratch = nullptr;
+	// asynchronous snapshot for live views (gl_snapshot_submit / _collect): weights | layer-indexed biases |
+	// pre-activations of the last row, copied device-to-device beside the compute stream, then to pinned memory
+	float* dPreact = nullptr;   // [total nodes - n_0]
+	float* dSnap = nullptr;
+	float* hSnap = nullptr;
+	cudaStream_t snapStream = nullptr;
+	cudaEvent_t evSnapSrc = nullptr, evSnapCopied = nullptr, evSnapReady = nullptr;
+	bool snapPending = false;
 	// reference mode with dropout: per-edge history lengths and last deltas, the error accumulators that
 	// survive a row, and one epoch's node flags (drawn on the host with rand(), in the reference's order)
 	bool dropout = false;
@@ -367,6 +375,8 @@ extern "C" int gl_create(const gl_net_desc* d, gl_net** out)
 	CU(cudaMemset(n->dLastOut, 0, (size_t)n->n_out * sizeof(float)));
 	CU(cudaMalloc(&n->dConf, (size_t)n->n_out * n->n_out * sizeof(int)));
 	CU(cudaMemset(n->dConf, 0, (size_t)n->n_out * n->n_out * sizeof(int)));
+	CU(cudaMalloc(&n->dPreact, (size_t)(n->total_nodes - d->sizes[0]) * sizeof(float)));
+	CU(cudaMemset(n->dPreact, 0, (size_t)(n->total_nodes - d->sizes[0]) * sizeof(float)));
 	if (d->mode == GL_MODE_REFERENCE)
 	{
 		CU(cudaMalloc(&n->dHist, (size_t)n->nw * d->batch_size * sizeof(float)));
@@ -472,6 +482,13 @@ extern "C" int gl_destroy(gl_net* n)
 	if (n->evComm) cudaEventDestroy(n->evComm);
 	free_work(n);
 	cudaFree(n->dHlen); cudaFree(n->dHlast); cudaFree(n->dErrState); cudaFree(n->dMasks);
+	if (n->snapStream) cudaStreamSynchronize(n->snapStream);
+	cudaFree(n->dPreact); cudaFree(n->dSnap);
+	if (n->hSnap) cudaFreeHost(n->hSnap);
+	if (n->evSnapSrc) cudaEventDestroy(n->evSnapSrc);
+	if (n->evSnapCopied) cudaEventDestroy(n->evSnapCopied);
+	if (n->evSnapReady) cudaEventDestroy(n->evSnapReady);
+	if (n->snapStream) cudaStreamDestroy(n->snapStream);
 	cudaFree(n->dpRec);
 	cudaFree(n->dWlo);
 	cudaFree(n->dW); cudaFree(n->dBias); cudaFree(n->dG); cudaFree(n->dBscale); cudaFree(n->dFlags);
@@ -884,6 +901,7 @@ static int ref_train(gl_net* n, int n_epochs, gl_metrics* out)
 	a.outputs = nullptr;
 	a.last_out = n->dLastOut;
 	a.flags = n->dFlags;
+	a.preact_out = n->dPreact;
 	a.weights_in_smem = ref_train_smem_bytes(a.net, true) <= (size_t)227 * 1024;
 	if (!a.weights_in_smem && ref_train_smem_bytes(a.net, false) > (size_t)227 * 1024)
 		return fail(GL_ERR_TOO_LARGE, "reference mode: %d nodes do not fit the per-sample shared-memory vectors", n->total_nodes);
@@ -1878,6 +1896,7 @@ static int ref_forward_dropout(gl_net* n, const float* X, const float* Y, int64_
 	a.last_out = n->dLastOut;
 	a.flags = n->dFlags;
 	a.train = 0;
+	a.preact_out = n->dPreact;
 	fill_dropout_args(n, a);
 	float* dOut = nullptr;
 	float* dActs = nullptr;
@@ -2574,6 +2593,77 @@ extern "C" int gl_sync(gl_net* n)
 	return GL_OK;
 }
 
+// ---- asynchronous snapshot for live views -------------------------------------------------------------
+// What the reference's GUI callbacks read after an epoch (Networks/network.cpp:258-357): every weight
+// (LayerBuilder::getWeights, State/LayerBuilder.cpp:390-410), and the pre-activations of the last row
+// (network.cpp:510-514).  submit() queues, behind the work already on the compute stream, a device-to-device
+// copy into a snapshot buffer on a side stream -- the compute stream only waits for that short copy, then
+// goes on training -- and the copy of the snapshot into pinned host memory after it.  collect() hands the
+// oldest submitted snapshot out.  One snapshot may be in flight.
+static size_t snap_floats(const gl_net* n) { return (size_t)n->nw + GL_MAX_WEIGHT_LAYERS + (size_t)(n->total_nodes - n->d.sizes[0]); }
+
+extern "C" int gl_snapshot_submit(gl_net* n)
+{
+	if (!n) return fail(GL_ERR_INVALID, "gl_snapshot_submit: null handle");
+	if (n->snapPending) return fail(GL_ERR_STATE, "a snapshot is already in flight: collect it first");
+	if (int r = use_device(n)) return r;
+	if (int r = dp_join(n)) return r;
+	if (!n->snapStream)
+	{
+		CU(cudaStreamCreateWithFlags(&n->snapStream, cudaStreamNonBlocking));
+		CU(cudaEventCreateWithFlags(&n->evSnapSrc, cudaEventDisableTiming));
+		CU(cudaEventCreateWithFlags(&n->evSnapCopied, cudaEventDisableTiming));
+		CU(cudaEventCreateWithFlags(&n->evSnapReady, cudaEventDisableTiming));
+		CU(cudaMalloc(&n->dSnap, snap_floats(n) * sizeof(float)));
+		CU(cudaMallocHost(&n->hSnap, snap_floats(n) * sizeof(float)));
+	}
+	if (n->d.mode == GL_MODE_BATCHED && n->dX && n->rows > 0)
+	{
+		// batched mode keeps no pre-activations: they are evaluated for the last resident row, in the exact
+		// summation order, under the weights as they stand now
+		if (int r = ensure_work(n, 1)) return r;
+		const NetView v = make_view(n);
+		CU(launch_ref_forward(v, n->dX + (n->rows - 1) * n->d.sizes[0], 1, n->dA, n->stream, n->dPreact));
+		n->launches += n->H + 1;
+	}
+	const size_t np = (size_t)(n->total_nodes - n->d.sizes[0]);
+	CU(cudaEventRecord(n->evSnapSrc, n->stream));
+	CU(cudaStreamWaitEvent(n->snapStream, n->evSnapSrc, 0));
+	CU(cudaMemcpyAsync(n->dSnap, n->dW, (size_t)n->nw * sizeof(float), cudaMemcpyDeviceToDevice, n->snapStream));
+	CU(cudaMemcpyAsync(n->dSnap + n->nw, n->dBias, GL_MAX_WEIGHT_LAYERS * sizeof(float), cudaMemcpyDeviceToDevice, n->snapStream));
+	CU(cudaMemcpyAsync(n->dSnap + n->nw + GL_MAX_WEIGHT_LAYERS, n->dPreact, np * sizeof(float), cudaMemcpyDeviceToDevice, n->snapStream));
+	CU(cudaEventRecord(n->evSnapCopied, n->snapStream));
+	CU(cudaStreamWaitEvent(n->stream, n->evSnapCopied, 0));  // later training may overwrite the weights only after the copy
+	CU(cudaMemcpyAsync(n->hSnap, n->dSnap, snap_floats(n) * sizeof(float), cudaMemcpyDeviceToHost, n->snapStream));
+	CU(cudaEventRecord(n->evSnapReady, n->snapStream));
+	n->snapPending = true;
+	return GL_OK;
+}
+
+// Returns GL_OK and fills w (flat weights), bias (H floats, hidden layers 1..H) and preact (pre-activations
+// of layers 1..H+1 of the last row, concatenated) -- each may be NULL -- or 1 when wait == 0 and the snapshot
+// has not reached host memory yet.
+extern "C" int gl_snapshot_collect(gl_net* n, float* w, float* bias, float* preact, int32_t wait)
+{
+	if (!n) return fail(GL_ERR_INVALID, "gl_snapshot_collect: null handle");
+	if (!n->snapPending) return fail(GL_ERR_STATE, "no snapshot in flight");
+	if (int r = use_device(n)) return r;
+	if (!wait)
+	{
+		const cudaError_t q = cudaEventQuery(n->evSnapReady);
+		if (q == cudaErrorNotReady) return 1;
+		if (q != cudaSuccess) return fail(GL_ERR_CUDA, "gl_snapshot_collect: %s", cudaGetErrorString(q));
+	}
+	else
+		CU(cudaEventSynchronize(n->evSnapReady));
+	n->snapPending = false;
+	if (w) memcpy(w, n->hSnap, (size_t)n->nw * sizeof(float));
+	if (bias)
+		for (int l = 1; l <= n->H; ++l) bias[l - 1] = n->hSnap[n->nw + l];
+	if (preact) memcpy(preact, n->hSnap + n->nw + GL_MAX_WEIGHT_LAYERS, (size_t)(n->total_nodes - n->d.sizes[0]) * sizeof(float));
+	return GL_OK;
+}
+
 // Self-test of the bounded device waits: queues the exchange's wait kernel on a flag word that nothing
 // ever raises, with a limit of `max_cycles` SM clock cycles.  The wait gives up when the limit runs out
 // and records code 99 in the handle's status word; the next status read (gl_sync, a window's metrics)
@@ -2679,6 +2769,94 @@ extern "C" int gl_onehot_fill(float* d_y, const int32_t* labels, int64_t rows, i
 	if (e == cudaSuccess) e = cudaDeviceSynchronize();
 	cudaFree(dl);
 	if (e != cudaSuccess) return fail(GL_ERR_CUDA, "gl_onehot_fill: %s", cudaGetErrorString(e));
+	return GL_OK;
+}
+
+// ---- input standardisation ---------------------------------------------------------------------
+extern "C" int gl_standardize_table(const float* d_raw, int64_t rows, int32_t cols, const int32_t* kind, const int32_t* classes,
+                                    const int32_t* to_output, int32_t flag, float* d_x, int32_t* nx, float* d_y, int32_t* ny,
+                                    float* stats_out, int32_t device)
+{
+	if (!d_raw || rows < 1 || cols < 1 || !kind || !classes || !to_output || !nx || !ny || (flag != 0 && flag != 1))
+		return fail(GL_ERR_INVALID, "gl_standardize_table: bad argument");
+	if (gl_device_count() < 1) return fail(GL_ERR_NO_DEVICE, "no sm_100 CUDA device: this library has no CPU path");
+	CU(cudaSetDevice(device));
+	int classification = 0;
+	for (int c = 0; c < cols; ++c)
+	{
+		if (kind[c] != 0 && kind[c] != 1) return fail(GL_ERR_INVALID, "gl_standardize_table: kind[%d] must be 0 or 1", c);
+		if (kind[c] == 1)
+		{
+			if (classes[c] < 1) return fail(GL_ERR_INVALID, "gl_standardize_table: categorical column %d has no classes", c);
+			classification = 1;
+		}
+	}
+	// pass 1: extrema.  Raw column 0 starts from its own first cell (a neutral start gives the same extrema),
+	// every other column from 0.0 (NumberInput.cpp:105-109).
+	std::vector<int> st((size_t)cols * 4, 0);
+	for (int c = 0; c < cols; ++c)
+	{
+		st[4 * (size_t)c] = (c == 0) ? 0x7FFFFFFF : float_order_host(0.0f);
+		st[4 * (size_t)c + 1] = (c == 0) ? (int)0x80000000 : float_order_host(0.0f);
+	}
+	int* dStats = nullptr;
+	int* dKind = nullptr;
+	void* dPlan = nullptr;
+	CU(cudaMalloc(&dStats, st.size() * sizeof(int)));
+	cudaError_t e = cudaMemcpy(dStats, st.data(), st.size() * sizeof(int), cudaMemcpyHostToDevice);
+	if (e == cudaSuccess) e = launch_column_minmax(d_raw, rows, cols, dStats, 0);
+	if (e == cudaSuccess && flag == 1)
+	{
+		e = cudaMalloc(&dKind, (size_t)cols * sizeof(int));
+		if (e == cudaSuccess) e = cudaMemcpy(dKind, kind, (size_t)cols * sizeof(int), cudaMemcpyHostToDevice);
+		if (e == cudaSuccess) e = launch_column_mean_stdev(d_raw, rows, cols, dKind, reinterpret_cast<float*>(dStats), 0);
+	}
+	if (e == cudaSuccess) e = cudaMemcpy(st.data(), dStats, st.size() * sizeof(int), cudaMemcpyDeviceToHost);
+	// the layout: columns keep their raw order inside each destination; a numeric column whose range is 0 is
+	// copied unscaled and lands in the input matrix whatever its output mark (NumberInput.cpp:166-171)
+	std::vector<int> plan((size_t)cols * 4);
+	int cx = 0, cy = 0;
+	if (e == cudaSuccess)
+		for (int c = 0; c < cols; ++c)
+		{
+			int dst = to_output[c] ? 1 : 0;
+			int width = 1;
+			if (kind[c] == 1) width = classes[c];
+			else if (flag == 0 && order_float_host(st[4 * (size_t)c + 1]) - order_float_host(st[4 * (size_t)c]) == 0.0f) dst = 0;
+			plan[4 * (size_t)c] = kind[c];
+			plan[4 * (size_t)c + 1] = classes[c];
+			plan[4 * (size_t)c + 2] = dst;
+			plan[4 * (size_t)c + 3] = dst ? cy : cx;
+			(dst ? cy : cx) += width;
+		}
+	int status = GL_OK;
+	if (e == cudaSuccess && (d_x || d_y))
+	{
+		if (*nx != cx || *ny != cy || (cx > 0 && !d_x) || (cy > 0 && !d_y))
+			status = fail(GL_ERR_INVALID, "gl_standardize_table: the table standardises to %d input and %d expected columns, the caller gave %d and %d",
+			              cx, cy, *nx, *ny);
+		else
+		{
+			e = cudaMalloc(&dPlan, plan.size() * sizeof(int));
+			if (e == cudaSuccess) e = cudaMemcpy(dPlan, plan.data(), plan.size() * sizeof(int), cudaMemcpyHostToDevice);
+			if (e == cudaSuccess) e = launch_column_transform(d_raw, rows, cols, dPlan, dStats, flag, classification, d_x, cx, d_y, cy, 0);
+			if (e == cudaSuccess) e = cudaDeviceSynchronize();
+		}
+	}
+	cudaFree(dStats);
+	cudaFree(dKind);
+	cudaFree(dPlan);
+	if (e != cudaSuccess) return fail(GL_ERR_CUDA, "gl_standardize_table: %s", cudaGetErrorString(e));
+	if (status != GL_OK) return status;
+	*nx = cx;
+	*ny = cy;
+	if (stats_out)
+		for (int c = 0; c < cols; ++c)
+		{
+			stats_out[4 * (size_t)c] = order_float_host(st[4 * (size_t)c]);
+			stats_out[4 * (size_t)c + 1] = order_float_host(st[4 * (size_t)c + 1]);
+			memcpy(&stats_out[4 * (size_t)c + 2], &st[4 * (size_t)c + 2], 2 * sizeof(float));
+		}
 	return GL_OK;
 }
 

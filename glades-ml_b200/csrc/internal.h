@@ -47,6 +47,9 @@ struct RefTrainArgs
 	float* err_state;                   // [total nodes]: error accumulators carried from launch to launch
 	long long data_rows;                // rows of the data set for the cost divisor (0: `rows`)
 	float* acts_out;                    // optional: activations of layers 1..H+1 of the LAST row, concatenated
+	float* preact_out;                  // optional: pre-activations (sum + bias, before the activation function) of
+	                                    // layers 1..H+1 for the LAST row of the LAST epoch, concatenated: what the
+	                                    // reference collects for its live view (network.cpp:510-514)
 };
 size_t ref_train_smem_bytes(const NetView& n, bool weights_in_smem);
 size_t ref_train_dropout_smem_bytes(const NetView& n);
@@ -54,7 +57,9 @@ cudaError_t launch_ref_train(const RefTrainArgs& a, cudaStream_t s);
 
 // Exact-order forward of rows [first, first+rows): one thread per (row, output node), k ascending.
 // acts: per-layer activation buffers [rows][n_l] for l = 1..H+1 (device).
-cudaError_t launch_ref_forward(const NetView& n, const float* X, long long rows, float* const* acts, cudaStream_t s);
+// zout (optional): pre-activations of layers 1..H+1 of row 0 of the call, concatenated
+cudaError_t launch_ref_forward(const NetView& n, const float* X, long long rows, float* const* acts, cudaStream_t s,
+                               float* zout = nullptr);
 // Sequential (row-major) metric accumulation over predictions P [rows][n_out] against Y.
 cudaError_t launch_ref_metrics(const NetView& n, const float* P, const float* Y, long long rows, long long data_rows,
                                float* sums2, int* confusion, cudaStream_t s);
@@ -214,6 +219,17 @@ cudaError_t launch_dp_small_push(const float* gb, const double* sums2, const DpP
                                  unsigned value, cudaStream_t s);
 cudaError_t launch_dp_finish(const void* arena, int world, int parity, float* gb_out, double* sums2_out, float* bias,
                              const float* bscale, int H, int* status_flags, cudaStream_t s);
+
+// ---- input standardisation (preprocess.cu) -------------------------------------------------------
+// d_stats: device [cols][4] words per column: order image of the minimum, of the maximum (ints), then the
+// mean and the standard deviation (floats).  The caller presets the two images to the column's start values.
+cudaError_t launch_column_minmax(const float* raw, long long rows, int cols, int* d_stats, cudaStream_t s);
+cudaError_t launch_column_mean_stdev(const float* raw, long long rows, int cols, const int* d_kind, float* d_stats, cudaStream_t s);
+// d_plan: device array of `cols` records {kind, classes, destination matrix (0 X, 1 Y), first destination column}
+cudaError_t launch_column_transform(const float* raw, long long rows, int cols, const void* d_plan, const int* d_stats, int flag,
+                                    int classification, float* X, int ldx, float* Y, int ldy, cudaStream_t s);
+int float_order_host(float f);    // the order-preserving integer image used for the min / max atomics
+float order_float_host(int i);
 
 // ---- synthetic inputs (synth.cu) ---------------------------------------------------------------
 // out[j] = element (first + j) of stream `stream_id`; `first` must be even for dist 1

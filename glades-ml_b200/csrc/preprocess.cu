@@ -1,0 +1,181 @@
+// Input standardisation on the device: the step in front of the training loop,
+// NumberInput::standardizeInputTable (DataObjects/NumberInput.cpp:43-285) with the one-hot vectors of
+// OHE::operator[] (GMath/OHE.cpp:159-198), on a raw table that already lies in HBM as a row-major
+// [rows][cols] fp32 matrix (a categorical column holds each cell's category index, in order of first
+// appearance -- the strings themselves stay on the host).
+//
+// Pass 1, column statistics.  Minimum and maximum do not depend on the order of the rows, so they are
+// reduced in parallel: the grid's threads stride over the row-major cells with coalesced reads (the stride
+// is a multiple of the column count, so a thread stays on one column and keeps its extrema in registers)
+// and merge with atomics on an order-preserving integer image of the floats.  The reference starts the running minimum and maximum from the first cell
+// only for raw column 0 and from 0.0 for every other column (NumberInput.cpp:105-109): columns other than
+// 0 therefore start their reduction at 0.  The mean and the standard deviation (z-score mode only) are
+// sequential fp32 sums in row order in the reference (:118-121,236-249), so they run as one thread per
+// column walking the rows -- coalesced across the columns of a warp -- to stay bit-identical.
+// Pass 2, transform.  One thread per (row, raw column): scale with separately rounded fp32 operations
+// in the reference's order, ((x - min) / range) * 0.98 + 0.01 (any categorical column in the table) or
+// (x - min) / range, or (x - mean) / stdev, and write the cell -- or the 0.99 / 0.01 one-hot group of a
+// categorical cell -- at its place in the input matrix X or the expected matrix Y.
+// HBM traffic: rows * cols * 4 bytes read twice, rows * (nx + ny) * 4 bytes written once.
+#include <string.h>
+
+#include "common.cuh"
+#include "internal.h"
+
+namespace glb {
+namespace {
+
+__device__ __forceinline__ int float_order(float f)
+{
+	// monotone map float -> int (so that integer atomicMin / atomicMax order floats)
+	const int i = __float_as_int(f);
+	return i >= 0 ? i : i ^ 0x7FFFFFFF;
+}
+__device__ __forceinline__ float order_float(int i) { return __int_as_float(i >= 0 ? i : i ^ 0x7FFFFFFF); }
+
+// stats: [cols][4] = min image, max image (ints, pre-set by the host to the images of the start values),
+// mean, stdev
+__global__ void __launch_bounds__(256) minmax_kernel(const float* __restrict__ raw, long long rows, int cols, int* stats)
+{
+	// thread t handles column t % cols of rows t / cols + k * rows_per_pass: consecutive threads read
+	// consecutive addresses
+	const long long total = rows * (long long)cols;
+	const long long stride = (long long)gridDim.x * blockDim.x;
+	const long long start = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+	// when the stride is a multiple of cols every thread stays on one column and can keep its extrema in
+	// registers; the launch rounds the grid so that this holds
+	const int c = (int)(start % cols);
+	float mn = __int_as_float(0x7F800000), mx = __int_as_float(0xFF800000);
+	bool any = false;
+	for (long long i = start; i < total; i += stride)
+	{
+		const float v = raw[i];
+		mn = fminf(mn, v);
+		mx = fmaxf(mx, v);
+		any = true;
+	}
+	if (any)
+	{
+		atomicMin(stats + 4 * c, float_order(mn));
+		atomicMax(stats + 4 * c + 1, float_order(mx));
+	}
+}
+
+__global__ void __launch_bounds__(128) mean_stdev_kernel(const float* __restrict__ raw, long long rows, int cols,
+                                                          const int* __restrict__ kind, float* stats)
+{
+	const int c = blockIdx.x * blockDim.x + threadIdx.x;
+	if (c >= cols || kind[c] != 0) return;
+	// sequential fp32 sums in row order, as the reference accumulates them
+	float mean = 0.0f;
+	for (long long r = 0; r < rows; ++r) mean = __fadd_rn(mean, raw[r * cols + c]);
+	mean = __fdiv_rn(mean, (float)(unsigned int)rows);
+	float sd = 0.0f;
+	for (long long r = 0; r < rows; ++r)
+	{
+		const float d = __fsub_rn(raw[r * cols + c], mean);
+		sd = __fadd_rn(sd, __fmul_rn(d, d));
+	}
+	sd = __fsqrt_rn(__fdiv_rn(sd, (float)((unsigned int)rows - 1u)));
+	stats[4 * c + 2] = mean;
+	stats[4 * c + 3] = sd;
+}
+
+struct ColumnPlan
+{
+	int kind;     // 0 numeric, 1 categorical
+	int classes;  // categorical: one-hot width
+	int dst;      // 0: X, 1: Y
+	int at;       // first destination column
+};
+
+__global__ void __launch_bounds__(256) transform_kernel(const float* __restrict__ raw, long long rows, int cols,
+                                                         const ColumnPlan* __restrict__ plan, const int* __restrict__ stats,
+                                                         int flag, int classification, float* __restrict__ X, int ldx,
+                                                         float* __restrict__ Y, int ldy)
+{
+	const long long total = rows * (long long)cols;
+	const long long stride = (long long)gridDim.x * blockDim.x;
+	for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride)
+	{
+		const long long r = i / cols;
+		const int c = (int)(i - r * cols);
+		const ColumnPlan p = plan[c];
+		float* dst = p.dst ? Y + r * ldy : X + r * ldx;
+		float v = raw[i];
+		if (p.kind == 1)
+		{
+			const int id = (int)v;
+			for (int k = 0; k < p.classes; ++k) dst[p.at + k] = (k == id) ? 0.99f : 0.01f;
+			continue;
+		}
+		if (flag == 0)
+		{
+			const float mn = order_float(stats[4 * c]), mx = order_float(stats[4 * c + 1]);
+			const float range = __fsub_rn(mx, mn);
+			if (range != 0.0f)
+			{
+				v = __fdiv_rn(__fsub_rn(v, mn), range);
+				if (classification) v = __fadd_rn(__fmul_rn(v, 0.98f), 0.01f);
+			}
+		}
+		else
+			v = __fdiv_rn(__fsub_rn(v, __int_as_float(stats[4 * c + 2])), __int_as_float(stats[4 * c + 3]));
+		dst[p.at] = v;
+	}
+}
+
+}  // namespace
+
+// d_stats: device [cols][4] ints, already holding the order images of every column's start values for the
+// minimum and the maximum.  d_plan: device array of `cols` ColumnPlan records (four ints each).
+cudaError_t launch_column_minmax(const float* raw, long long rows, int cols, int* d_stats, cudaStream_t s)
+{
+	const long long total = rows * (long long)cols;
+	if (total < 1) return cudaSuccess;
+	// grid * 256 must be a multiple of cols so that each thread keeps to one column
+	long long threads = (total + 3) / 4;  // about four cells per thread
+	const long long cap = 148ll * 8 * 256;
+	if (threads > cap) threads = cap;
+	long long per = 256ll * cols;  // lcm(256, cols) divides this
+	long long grid_threads = ((threads + per - 1) / per) * per;
+	long long blocks = grid_threads / 256;
+	if (blocks < cols) blocks = cols;  // still a multiple of cols: grid * 256 = cols * 256 * k
+	blocks = ((blocks + cols - 1) / cols) * cols;
+	minmax_kernel<<<(unsigned)blocks, 256, 0, s>>>(raw, rows, cols, d_stats);
+	return cudaGetLastError();
+}
+
+cudaError_t launch_column_mean_stdev(const float* raw, long long rows, int cols, const int* d_kind, float* d_stats, cudaStream_t s)
+{
+	mean_stdev_kernel<<<(cols + 127) / 128, 128, 0, s>>>(raw, rows, cols, d_kind, d_stats);
+	return cudaGetLastError();
+}
+
+cudaError_t launch_column_transform(const float* raw, long long rows, int cols, const void* d_plan, const int* d_stats, int flag,
+                                    int classification, float* X, int ldx, float* Y, int ldy, cudaStream_t s)
+{
+	const long long total = rows * (long long)cols;
+	if (total < 1) return cudaSuccess;
+	long long blocks = (total + 255) / 256;
+	if (blocks > 148 * 16) blocks = 148 * 16;
+	transform_kernel<<<(unsigned)blocks, 256, 0, s>>>(raw, rows, cols, static_cast<const ColumnPlan*>(d_plan), d_stats, flag,
+	                                                  classification, X, ldx, Y, ldy);
+	return cudaGetLastError();
+}
+
+int float_order_host(float f)
+{
+	int i;
+	memcpy(&i, &f, sizeof i);
+	return i >= 0 ? i : i ^ 0x7FFFFFFF;
+}
+float order_float_host(int i)
+{
+	i = i >= 0 ? i : i ^ 0x7FFFFFFF;
+	float f;
+	memcpy(&f, &i, sizeof f);
+	return f;
+}
+
+}  // namespace glb

@@ -129,6 +129,7 @@ __global__ void __launch_bounds__(1024, 1) ref_train_kernel(const __grid_constan
 					for (int i = 0; i < ni; ++i) z = __fadd_rn(z, __fmul_rn(wr[i], ain[i]));
 					if (l >= 1) z = __fadd_rn(z, sbias[l]);
 					actp[l + 1][o] = squash_x(z, n.act[l], n.par[l]);
+					if (a.preact_out && last_epoch && r == a.rows - 1) a.preact_out[(actp[l + 1] - actp[1]) + o] = z;
 				}
 				__syncthreads();
 			}
@@ -355,6 +356,7 @@ __global__ void __launch_bounds__(1024, 1) ref_train_dropout_kernel(const __grid
 				}
 				if (l >= 1) z = __fadd_rn(z, sbias[l]);
 				actp[l + 1][o] = squash_x(z, n.act[l], n.par[l]);
+				if (a.preact_out && r == a.rows - 1) a.preact_out[(actp[l + 1] - actp[1]) + o] = z;
 			}
 			__syncthreads();
 		}
@@ -564,6 +566,7 @@ struct FwdLayerArgs
 	int ni, no, l, act;
 	float par;
 	long long rows;
+	float* zout;       // optional: pre-activations of row 0, `no` floats
 };
 
 __global__ void ref_forward_layer_kernel(const FwdLayerArgs f)
@@ -579,11 +582,13 @@ __global__ void ref_forward_layer_kernel(const FwdLayerArgs f)
 	for (int i = 0; i < f.ni; ++i) z = __fadd_rn(z, __fmul_rn(w[i], x[i]));
 	if (f.l >= 1) z = __fadd_rn(z, f.bias[f.l]);
 	f.out[idx] = squash_x(z, f.act, f.par);
+	if (f.zout && r == 0) f.zout[o] = z;
 }
 
-cudaError_t launch_ref_forward(const NetView& n, const float* X, long long rows, float* const* acts, cudaStream_t s)
+cudaError_t launch_ref_forward(const NetView& n, const float* X, long long rows, float* const* acts, cudaStream_t s, float* zout)
 {
 	const float* in = X;
+	int zoff = 0;
 	for (int l = 0; l <= n.H; ++l)
 	{
 		FwdLayerArgs f;
@@ -597,6 +602,8 @@ cudaError_t launch_ref_forward(const NetView& n, const float* X, long long rows,
 		f.act = n.act[l];
 		f.par = n.par[l];
 		f.rows = rows;
+		f.zout = zout ? zout + zoff : nullptr;
+		zoff += n.sizes[l + 1];
 		const long long total = rows * f.no;
 		const int T = 128;
 		ref_forward_layer_kernel<<<(unsigned)((total + T - 1) / T), T, 0, s>>>(f);

@@ -5,6 +5,7 @@
 #include "glades_b200.hpp"
 
 #include <math.h>
+#include <pthread.h>
 #include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
@@ -254,22 +255,202 @@ void drawInitialWeights(const NNInfo& info, unsigned int featureCount, std::vect
 }
 
 // ---------------------------------------------------------------------------------------------
+NNetwork::NNetwork()
+    : di(NULL), skeleton(NULL), handle(NULL), running(false), epochs(0), overallTotalError(0.0f),
+      overallTotalAccuracy(0.0f), overallClassAccuracy(0.0f), overallClassPrecision(0.0f), overallClassRecall(0.0f),
+      overallClassSpecificity(0.0f), overallClassF1(0.0f), minibatchSize(1), mode(GL_MODE_REFERENCE), deviceOrdinal(0),
+      quiet(false), haveInit(false), serverInstance(NULL), cConnection(NULL), firstRunActivation(false), ownsSkeleton(false)
+{
+	const char* m = getenv("GLADES_B200_MODE");
+	if (m && strcmp(m, "batched") == 0) mode = GL_MODE_BATCHED;
+}
+
 NNetwork::NNetwork(NNInfo* newNNInfo)
     : di(NULL), skeleton(NULL), handle(NULL), running(false), epochs(0), overallTotalError(0.0f),
       overallTotalAccuracy(0.0f), overallClassAccuracy(0.0f), overallClassPrecision(0.0f), overallClassRecall(0.0f),
-      overallClassSpecificity(0.0f), overallClassF1(0.0f), minibatchSize(1), mode(GL_MODE_REFERENCE), quiet(false),
-      haveInit(false)
+      overallClassSpecificity(0.0f), overallClassF1(0.0f), minibatchSize(1), mode(GL_MODE_REFERENCE), deviceOrdinal(0),
+      quiet(false), haveInit(false), serverInstance(NULL), cConnection(NULL), firstRunActivation(false), ownsSkeleton(false)
 {
+	const char* m = getenv("GLADES_B200_MODE");
+	if (m && strcmp(m, "batched") == 0) mode = GL_MODE_BATCHED;
 	if (!newNNInfo) return;
 	skeleton = newNNInfo;
 	minibatchSize = skeleton->getBatchSize();
-	const char* m = getenv("GLADES_B200_MODE");
-	if (m && strcmp(m, "batched") == 0) mode = GL_MODE_BATCHED;
 }
 
 NNetwork::~NNetwork()
 {
 	if (handle) gl_destroy(handle);
+	if (ownsSkeleton) delete skeleton;
+}
+
+int64_t NNetwork::getCurrentTimeMilliseconds() const
+{
+	struct timespec ts;
+	clock_gettime(CLOCK_REALTIME, &ts);
+	return (int64_t)ts.tv_sec * 1000 + ts.tv_nsec / 1000000;
+}
+
+void NNetwork::setServer(GNet::GServer* newServer, GNet::Connection* newConnection)
+{
+	serverInstance = newServer;
+	cConnection = newConnection;
+}
+
+// NNetwork::load / save (network.cpp:701-722): the skeleton only.
+bool NNetwork::load(const std::string& netName, const std::string& directory)
+{
+	NNInfo* info = NNInfo::load(netName, directory);
+	if (!info) return false;
+	if (ownsSkeleton) delete skeleton;
+	skeleton = info;
+	ownsSkeleton = true;
+	minibatchSize = skeleton->getBatchSize();
+	return true;
+}
+
+bool NNetwork::save(const std::string& directory) const
+{
+	if (!skeleton) return false;
+	return skeleton->save(directory);
+}
+
+// ---- live view -------------------------------------------------------------------------------
+// After an epoch whose frame is due, queueFrame() notes the epoch's figures and queues an asynchronous
+// snapshot of the weights and the last row's pre-activations (gl_snapshot_submit: training only waits for a
+// device-to-device copy).  The frame is sent when the snapshot has reached host memory -- at the next due
+// frame or at the end of the run -- so the copy to the host runs under the following epochs.
+void NNetwork::queueFrame()
+{
+	if (frame.pending) sendFrame();
+	if (gl_snapshot_submit(handle) != GL_OK)
+	{
+		fprintf(stderr, "[NN] %s\n", gl_last_error());
+		return;
+	}
+	frame.pending = true;
+	frame.epochs = epochs;
+	frame.error = overallTotalError;
+	frame.accuracy = overallTotalAccuracy;
+	frame.confusion = lastConfusion;
+	// CMatrix::getOverallFalseAlarm / getOverallRecall (GMath/cmatrix.cpp:178-243), as fractions
+	const int c = (int)skeleton->getOutputLayerSize();
+	float fa = 0.0f, rec = 0.0f;
+	if ((int)lastConfusion.size() == c * c)
+		for (int k = 0; k < c; ++k)
+		{
+			int tp = lastConfusion[(size_t)k * c + k], tn = 0, fp = 0, fn = 0;
+			for (int j = 0; j < c; ++j)
+				if (j != k)
+				{
+					tn += lastConfusion[(size_t)j * c + j];
+					fp += lastConfusion[(size_t)j * c + k];
+					fn += lastConfusion[(size_t)k * c + j];
+				}
+			fa += ((float)fp) / ((float)(tn + fp));
+			rec += ((float)tp) / ((float)(tp + fn));
+		}
+	frame.falseAlarm = fa / (float)c;
+	frame.recall = rec / (float)c;
+}
+
+void NNetwork::sendFrame()
+{
+	if (!frame.pending) return;
+	frame.pending = false;
+	const int H = skeleton->numHiddenLayers();
+	std::vector<int> sizes;
+	sizes.push_back((int)di->getFeatureCount());
+	for (int l = 0; l < H; ++l) sizes.push_back(skeleton->getHiddenLayerSize(l));
+	sizes.push_back((int)skeleton->getOutputLayerSize());
+	size_t nw = 0, nz = 0;
+	for (int l = 0; l <= H; ++l)
+	{
+		nw += (size_t)sizes[l] * sizes[l + 1];
+		nz += sizes[l + 1];
+	}
+	std::vector<float> w(nw), z(nz);
+	if (gl_snapshot_collect(handle, &w[0], NULL, &z[0], 1) != GL_OK)
+	{
+		fprintf(stderr, "[NN] %s\n", gl_last_error());
+		return;
+	}
+	if (!serverInstance || !cConnection) return;
+	const bool classify = skeleton->getOutputType() == GMath::CLASSIFICATION || skeleton->getOutputType() == GMath::KL;
+	if (frame.epochs > 0)
+	{
+		// the learning curve: (epochs - 1, error)
+		shmea::GList wData, argData;
+		wData.addInt(frame.epochs - 1);
+		wData.addFloat(frame.error);
+		argData.addString("PROGRESSIVE");
+		shmea::ServiceData* cData = new shmea::ServiceData(cConnection, "GUI_Callback");
+		cData->set(wData);
+		cData->setArgList(argData);
+		serverInstance->send(cData);
+		// the layer sizes on the first frame of a run, then the last row's pre-activations, ',' after every layer
+		argData.clear();
+		argData.addString("ACTIVATIONS");
+		cData = new shmea::ServiceData(cConnection, "GUI_Callback");
+		shmea::GList act;
+		if (!firstRunActivation)
+		{
+			firstRunActivation = true;
+			for (size_t l = 0; l < sizes.size(); ++l) act.addInt(sizes[l]);
+		}
+		else
+		{
+			size_t k = 0;
+			for (int l = 1; l <= H + 1; ++l)
+			{
+				for (int o = 0; o < sizes[l]; ++o) act.addFloat(z[k++]);
+				act.addString(",");
+			}
+		}
+		cData->set(act);
+		cData->setArgList(argData);
+		serverInstance->send(cData);
+		// every weight, node by node (',' after a node's edges), layer by layer (';' after a layer)
+		argData.clear();
+		argData.addString("WEIGHTS");
+		shmea::GList wl;
+		size_t k = 0;
+		for (int l = 0; l <= H; ++l)
+		{
+			for (int o = 0; o < sizes[l + 1]; ++o)
+			{
+				for (int i = 0; i < sizes[l]; ++i) wl.addFloat(w[k++]);
+				wl.addString(",");
+			}
+			wl.addString(";");
+		}
+		cData = new shmea::ServiceData(cConnection, "GUI_Callback");
+		cData->set(wl);
+		cData->setArgList(argData);
+		serverInstance->send(cData);
+	}
+	{
+		shmea::GList argData, wData;
+		argData.addString("ACC");
+		wData.addInt(frame.epochs);
+		wData.addFloat(frame.accuracy);
+		shmea::ServiceData* cData = new shmea::ServiceData(cConnection, "GUI_Callback");
+		cData->set(wData);
+		cData->setArgList(argData);
+		serverInstance->send(cData);
+	}
+	if (classify)
+	{
+		shmea::GList argData;
+		argData.addString("CONF");
+		argData.addFloat(frame.falseAlarm);
+		argData.addFloat(frame.recall);
+		shmea::ServiceData* cData = new shmea::ServiceData(cConnection, "GUI_Callback");
+		const int c = (int)skeleton->getOutputLayerSize();
+		cData->setTable(frame.confusion, c, c);
+		cData->setArgList(argData);
+		serverInstance->send(cData);
+	}
 }
 
 void NNetwork::stop()
@@ -332,15 +513,25 @@ bool NNetwork::build(DataInput* d)
 		fprintf(stderr, "[NN] %s: skeleton cannot be expressed on the device path\n", skeleton->getName().c_str());
 		return false;
 	}
+	desc.device = deviceOrdinal;
 	const unsigned int rows = d->getTrainSize(), nIn = d->getFeatureCount(), nOut = skeleton->getOutputLayerSize();
-	std::vector<float> x((size_t)rows * nIn), y((size_t)rows * nOut);
-	for (unsigned int r = 0; r < rows; ++r)
+	// rows that already lie in device memory (a NumberInput standardised on the GPU) are used where they are
+	const float *devX = NULL, *devY = NULL;
+	int devOrdinal = 0;
+	const bool onDevice = d->deviceRows(&devX, &devY, &devOrdinal) && devX && devY && devOrdinal == deviceOrdinal;
+	std::vector<float> x, y;
+	if (!onDevice)
 	{
-		// one row copy per row (the reference copies the whole row per cell, LayerBuilder.cpp:139)
-		const shmea::GList xr = d->getTrainRow(r);
-		const shmea::GList yr = d->getTrainExpectedRow(r);
-		for (unsigned int c = 0; c < nIn; ++c) x[(size_t)r * nIn + c] = xr.getFloat(c);
-		for (unsigned int c = 0; c < nOut; ++c) y[(size_t)r * nOut + c] = yr.getFloat(c);
+		x.resize((size_t)rows * nIn);
+		y.resize((size_t)rows * nOut);
+		for (unsigned int r = 0; r < rows; ++r)
+		{
+			// one row copy per row (the reference copies the whole row per cell, LayerBuilder.cpp:139)
+			const shmea::GList xr = d->getTrainRow(r);
+			const shmea::GList yr = d->getTrainExpectedRow(r);
+			for (unsigned int c = 0; c < nIn; ++c) x[(size_t)r * nIn + c] = xr.getFloat(c);
+			for (unsigned int c = 0; c < nOut; ++c) y[(size_t)r * nOut + c] = yr.getFloat(c);
+		}
 	}
 	if (gl_create(&desc, &handle) != GL_OK)
 	{
@@ -356,7 +547,7 @@ bool NNetwork::build(DataInput* d)
 	}
 	if ((int64_t)initW.size() != gl_weight_count(handle) ||
 	    gl_set_weights(handle, &initW[0], initB.empty() ? NULL : &initB[0]) != GL_OK ||
-	    gl_set_data(handle, &x[0], &y[0], rows) != GL_OK)
+	    (onDevice ? gl_set_data_device(handle, devX, devY, rows) : gl_set_data(handle, &x[0], &y[0], rows)) != GL_OK)
 	{
 		fprintf(stderr, "[NN] %s\n", (int64_t)initW.size() != gl_weight_count(handle) ? "weight vector has the wrong length" : gl_last_error());
 		gl_destroy(handle);
@@ -405,6 +596,9 @@ void NNetwork::run(DataInput* newDataInput, int runType)
 		}
 	}
 	running = true;
+	firstRunActivation = false;
+	learningCurve.clear();  // resetGraphs(), network.cpp:168,761-768
+	int64_t lastUpdateTime = 0;
 	std::vector<float> lastOut(nOut);
 	while (running)
 	{
@@ -446,9 +640,25 @@ void NNetwork::run(DataInput* newDataInput, int runType)
 				fflush(stdout);
 			}
 		}
+		if (runType == RUN_TRAIN)
+		{
+			if (epochs > 0)
+			{
+				learningCurve.addInt(epochs - 1);
+				learningCurve.addFloat(overallTotalError);
+			}
+			// the live view: every epoch below 10, then at most every 16 ms (network.cpp:262-264)
+			const int64_t ms = getCurrentTimeMilliseconds();
+			if (serverInstance && cConnection && (epochs < 10 || ms - lastUpdateTime > 16))
+			{
+				queueFrame();
+				lastUpdateTime = ms;
+			}
+		}
 		if (terminator.triggered(time(NULL), epochs, overallTotalAccuracy)) break;
 		if (runType == RUN_TEST) break;
 	}
+	sendFrame();  // the frame still in flight, if any
 	// `results` holds the last row's (expected, predicted) pairs, as after the reference's last
 	// SGDHelper call (network.cpp:529-530)
 	results.clear();
@@ -470,17 +680,132 @@ void NNetwork::run(DataInput* newDataInput, int runType)
 	running = false;
 }
 
-NNetwork* train(NNetwork* net, DataInput* di)
+// ---------------------------------------------------------------------------------------------
+MetaNetwork::MetaNetwork(const std::string& newName) : name(newName), collectionType(ONE_TO_ONE) {}
+
+MetaNetwork::MetaNetwork(NNInfo* networkInfo, int subnetCount) : collectionType(subnetCount > 1 ? ONE_TO_MANY : ONE_TO_ONE)
 {
-	if (!net || !di) return NULL;  // glades::train returns NULL on NULL arguments (main.cpp:84-85)
-	net->train(di);
-	return net;
+	if (networkInfo) name = networkInfo->getName();
+	for (int i = 0; i < subnetCount; ++i) addSubnet(networkInfo);
 }
-NNetwork* test(NNetwork* net, DataInput* di)
+
+MetaNetwork::~MetaNetwork()
 {
-	if (!net || !di) return NULL;
-	net->test(di);
-	return net;
+	name = "";
+	clearSubnets();  // like the reference, the collection does not delete its networks (metanetwork.cpp:78-82,147-150)
+}
+
+void MetaNetwork::addSubnet(NNInfo* networkInfo)
+{
+	if (!networkInfo) return;
+	subnets.push_back(new NNetwork(networkInfo));
+}
+
+void MetaNetwork::addSubnet(NNetwork* cNetwork)
+{
+	if (!cNetwork) return;
+	subnets.push_back(cNetwork);
+}
+
+NNetwork* MetaNetwork::getSubnet(unsigned int index) { return index < subnets.size() ? subnets[index] : NULL; }
+
+std::string MetaNetwork::getSubnetName(unsigned int index) const
+{
+	return index < subnets.size() ? subnets[index]->getName() : std::string();
+}
+
+NNetwork* MetaNetwork::getSubnetByName(const std::string& newName) const
+{
+	for (size_t i = 0; i < subnets.size(); ++i)
+		if (subnets[i]->getName() == newName) return subnets[i];
+	return NULL;
+}
+
+namespace {
+struct ReplicaJob
+{
+	std::vector<NNetwork*> nets;
+	DataInput* di;
+};
+void* replicaThread(void* p)
+{
+	ReplicaJob* job = static_cast<ReplicaJob*>(p);
+	for (size_t i = 0; i < job->nets.size(); ++i) job->nets[i]->train(job->di);
+	return NULL;
+}
+}  // namespace
+
+int MetaNetwork::trainReplicas(DataInput* newDataInput)
+{
+	if (!newDataInput || subnets.empty()) return 0;
+	int gpus = gl_device_count();
+	if (gpus < 1) gpus = 1;
+	if (gpus > (int)subnets.size()) gpus = (int)subnets.size();
+	// subnet i runs on GPU i % gpus; one host thread drives each GPU's networks one after the other (a
+	// handle belongs to one host thread at a time, distinct handles may run from distinct threads)
+	std::vector<ReplicaJob> jobs((size_t)gpus);
+	for (size_t i = 0; i < subnets.size(); ++i)
+	{
+		subnets[i]->setDevice((int)(i % (size_t)gpus));
+		jobs[i % (size_t)gpus].nets.push_back(subnets[i]);
+		jobs[i % (size_t)gpus].di = newDataInput;
+	}
+	std::vector<pthread_t> threads((size_t)gpus);
+	for (int g = 0; g < gpus; ++g) pthread_create(&threads[(size_t)g], NULL, replicaThread, &jobs[(size_t)g]);
+	for (int g = 0; g < gpus; ++g) pthread_join(threads[(size_t)g], NULL);
+	return gpus;
+}
+
+// glades::train / glades::test, main.cpp:82-243
+static MetaNetwork* runAll(MetaNetwork* meta, DataInput* di, GNet::GServer* server, GNet::Connection* connection, bool training)
+{
+	const std::vector<NNetwork*> subnets = meta->getSubnets();
+	for (size_t i = 0; i < subnets.size(); ++i)
+	{
+		if (server && connection) subnets[i]->setServer(server, connection);
+		if (training) subnets[i]->train(di);
+		else subnets[i]->test(di);
+	}
+	return meta;
+}
+
+MetaNetwork* train(NNInfo* networkInfo, DataInput* di, GNet::GServer* server, GNet::Connection* connection)
+{
+	if (!networkInfo) return NULL;
+	MetaNetwork* meta = new MetaNetwork(networkInfo->getName());
+	meta->addSubnet(networkInfo);
+	return runAll(meta, di, server, connection, true);
+}
+MetaNetwork* train(NNetwork* cNetwork, DataInput* di, GNet::GServer* server, GNet::Connection* connection)
+{
+	if (!cNetwork) return NULL;
+	MetaNetwork* meta = new MetaNetwork(cNetwork->getName());
+	meta->addSubnet(cNetwork);
+	return runAll(meta, di, server, connection, true);
+}
+MetaNetwork* train(MetaNetwork* meta, DataInput* di, GNet::GServer* server, GNet::Connection* connection)
+{
+	if (!meta) return NULL;
+	return runAll(meta, di, server, connection, true);
+}
+MetaNetwork* test(NNInfo* networkInfo, DataInput* di, GNet::GServer* server, GNet::Connection* connection)
+{
+	if (!networkInfo) return NULL;
+	MetaNetwork* meta = new MetaNetwork(networkInfo->getName());
+	meta->addSubnet(networkInfo);
+	return runAll(meta, di, server, connection, false);
+}
+MetaNetwork* test(NNetwork* cNetwork, DataInput* di, GNet::GServer* server, GNet::Connection* connection)
+{
+	if (!cNetwork) return NULL;
+	MetaNetwork* meta = new MetaNetwork(cNetwork->getName());
+	meta->addSubnet(cNetwork);
+	return runAll(meta, di, server, connection, false);
+}
+MetaNetwork* test(MetaNetwork* meta, DataInput* di, GNet::GServer* server, GNet::Connection* connection)
+{
+	if (!meta) return NULL;
+	return runAll(meta, di, server, connection, false);
 }
 
 }  // namespace glades_b200

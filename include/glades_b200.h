@@ -259,6 +259,18 @@ int gl_matmul_static(const float* d_a, int64_t a_sm, int64_t a_sk, const float* 
                      float* d_c, int64_t ldc, int32_t m, int32_t n, int32_t k, int32_t device);
 const char* gl_matmul_static_error(void);
 
+/* Asynchronous snapshot for live views: replaces what the reference's GUI callbacks read after an
+ * epoch (Networks/network.cpp:258-357) -- every weight (LayerBuilder::getWeights,
+ * State/LayerBuilder.cpp:390-410) and the pre-activations of the epoch's last row (network.cpp:510-514;
+ * reference mode records them during the pass, batched mode evaluates them for the last resident row
+ * under the current weights).  submit queues, behind the work already queued on the handle, a
+ * device-to-device copy on a side stream (training waits only for that copy) followed by the copy into
+ * pinned host memory; it returns at once.  collect hands the snapshot out: w flat weights, bias H floats,
+ * preact the pre-activations of layers 1..H+1 concatenated (each may be NULL); with wait == 0 it
+ * returns 1 instead of blocking while the copy is still under way.  One snapshot may be in flight. */
+int gl_snapshot_submit(gl_net* net);
+int gl_snapshot_collect(gl_net* net, float* w, float* bias, float* preact, int32_t wait);
+
 /* Replaces NNetwork::stop (network.cpp:99-102): async-signal-safe; the flag is looked at between
  * epochs of gl_train_epochs. */
 void gl_stop(gl_net* net);
@@ -300,6 +312,26 @@ int gl_synth_fill_at(float* d_out, int64_t n, int64_t first_index, uint64_t seed
  * (the reference's one-hot encoder writes 0.99 / 0.01, GMath/OHE.cpp:159-198).  labels is a host
  * array. */
 int gl_onehot_fill(float* d_y, const int32_t* labels, int64_t rows, int32_t n, float on, float off, int32_t device);
+
+/* ---- input standardisation -------------------------------------------------------------- */
+/* Replaces the arithmetic of NumberInput::standardizeInputTable (DataObjects/NumberInput.cpp:43-285)
+ * and the one-hot vectors of OHE::operator[] (GMath/OHE.cpp:159-198) for a raw table that lies in
+ * device memory as a row-major [rows][cols] fp32 matrix.  Column c is numeric (kind[c] = 0) or
+ * categorical (kind[c] = 1: each cell holds its category's index in order of first appearance, the
+ * order OHE::addString builds; classes[c] categories, expanded to that many 0.99 / 0.01 columns);
+ * to_output[c] = 1 sends it to the expected-rows matrix d_y, else to the input matrix d_x; columns
+ * keep their raw order inside each matrix.  flag: 0 min-max, 1 z-score (GMath/gmath.h:53-54).
+ * Kept from the reference: the running minimum / maximum start from 0.0 for every raw column but the
+ * first (NumberInput.cpp:105-109); numeric columns scale to [0.01, 0.99] when the table has any
+ * categorical column, else to [0, 1] (:196-214); a min-max column with range 0 is copied unscaled into
+ * the INPUT matrix whatever its output mark (:166-171); mean and deviation are sequential fp32 sums.
+ * Because of the range-0 rule the widths depend on the data: call once with d_x = d_y = NULL to get
+ * *nx and *ny, allocate [rows][*nx] and [rows][*ny], and call again with those widths.
+ * stats_out (host, may be NULL): [cols][4] = minimum, maximum, mean, deviation (the last two in z-score
+ * mode only).  Results are bit-identical to the reference's. */
+int gl_standardize_table(const float* d_raw, int64_t rows, int32_t cols, const int32_t* kind, const int32_t* classes,
+                         const int32_t* to_output, int32_t flag, float* d_x, int32_t* nx, float* d_y, int32_t* ny,
+                         float* stats_out, int32_t device);
 
 /* ---- measurement helpers (no counterpart in the reference) ------------------------------ */
 /* CUDA events on the handle's own stream around whatever is queued between the two calls. */

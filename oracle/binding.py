@@ -55,6 +55,7 @@ def restate_lib():
         L.rs_window_grad.argtypes = [vp, i64, i32, i32, i32, vp, vp, i64]
         L.rs_window_apply.argtypes = [vp, vp, i32]
         L.rs_set_math_mode.argtypes = [i32]
+        L.rs_standardize_table.argtypes = [vp, i64, i32, vp, vp, vp, i32, vp, i32, vp, i32]
         L.rs_set_threads.argtypes = [i32]
         L.rs_get_threads.restype = i32
         for name in ("rs_squash", "rs_act_der"):
@@ -261,6 +262,28 @@ def set_threads(t):
     L = restate_lib()
     L.rs_set_threads(int(t))
     return int(L.rs_get_threads())
+
+
+def standardize_plan(raw, types):
+    """kind / classes arrays of a raw table whose categorical columns (type 1) hold category indices."""
+    kind = np.array([1 if t == 1 else 0 for t in types], np.int32)
+    classes = np.array([int(raw[:, c].max()) + 1 if t == 1 else 0 for c, t in enumerate(types)], np.int32)
+    return kind, classes
+
+
+def standardize_table(raw, types, outputs, flag, nx, ny):
+    """The CPU restatement of NumberInput::standardizeInputTable on a flat raw table."""
+    raw = np.ascontiguousarray(raw, np.float32)
+    rows, cols = raw.shape
+    kind, classes = standardize_plan(raw, types)
+    outs = np.array(outputs, np.int32)
+    x = np.zeros((rows, nx), np.float32)
+    y = np.zeros((rows, ny), np.float32)
+    rc = restate_lib().rs_standardize_table(_ptr(raw), rows, cols, _ptr(kind), _ptr(classes), _ptr(outs), flag, _ptr(x), nx,
+                                            _ptr(y), ny)
+    if rc != 0:
+        raise ValueError("the table does not standardise to %d input and %d expected columns" % (nx, ny))
+    return x, y
 
 
 def synth_fill(n, seed, stream, dist, scale=1.0, offset=0.0):

@@ -15,9 +15,12 @@
 #include <stdlib.h>
 #include <string.h>
 #include <unistd.h>
+#include <string>
 #include <vector>
 
 #include "Backend/Machine Learning/DataObjects/DataInput.h"
+#include "Backend/Machine Learning/DataObjects/NumberInput.h"
+#include "Backend/Machine Learning/GMath/OHE.h"
 #include "Backend/Machine Learning/GMath/cmatrix.h"
 #include "Backend/Machine Learning/GMath/gmath.h"
 #include "Backend/Machine Learning/Networks/network.h"
@@ -30,6 +33,20 @@
 #include "Backend/Machine Learning/Structure/outputlayerinfo.h"
 
 #include "glades_b200.h"
+
+// shim/shmea_shim.cpp
+namespace shmea {
+void shimRegisterTable(const char* name, const GTable& t);
+struct ShimMessage
+{
+	std::string command, kind;
+	std::vector<double> args, payload;
+	int rows, cols;
+};
+void shimClearMessages();
+size_t shimMessageCount();
+const ShimMessage& shimMessage(size_t i);
+}
 
 namespace {
 
@@ -358,6 +375,112 @@ int ref_train_row(void* h, int64_t row)
 		r->net->confusionMatrix.build(r->info->getOutputLayerSize());
 	r->net->SGDHelper((unsigned int)row, glades::NNetwork::RUN_TRAIN);
 	return 0;
+}
+
+// NumberInput::standardizeInputTable (DataObjects/NumberInput.cpp:43-285) with GMath/OHE.cpp, the
+// reference's own code, on a typed raw table built from flat arrays and handed over through the shim's
+// table registry (the reference reads it with its "file" constructor).
+//   col_type[c]    0: float cells, 1: string cells (category k is the string "s<k>", k = (int)value),
+//                  2: int cells
+//   col_output[c]  1: the column is marked as an output column of the raw table
+// x_out / y_out receive trainTable / trainExpectedTable row-major; their column counts come back in
+// nx / ny (call with x_out == NULL first to size the buffers).  Returns the row count of trainTable.
+int64_t ref_number_input(const float* values, int64_t rows, int cols, const int* col_type, const int* col_output,
+                         int standardize_flag, float* x_out, int* nx, float* y_out, int* ny)
+{
+	std::vector<shmea::GString> headers;
+	for (int c = 0; c < cols; ++c)
+	{
+		char h[32];
+		snprintf(h, sizeof h, "col%d", c);
+		headers.push_back(shmea::GString(h));
+	}
+	shmea::GTable raw(',', headers);
+	for (int64_t r = 0; r < rows; ++r)
+	{
+		shmea::GList row;
+		for (int c = 0; c < cols; ++c)
+		{
+			const float v = values[(size_t)r * cols + c];
+			if (col_type[c] == 1)
+			{
+				char sbuf[32];
+				snprintf(sbuf, sizeof sbuf, "s%d", (int)v);
+				row.addString(sbuf);
+			}
+			else if (col_type[c] == 2)
+				row.addInt((int)v);
+			else
+				row.addFloat(v);
+		}
+		raw.addRow(row);
+	}
+	for (int c = 0; c < cols; ++c)
+		if (col_output[c])
+			raw.toggleOutput(c);
+	shmea::shimRegisterTable("oracle-raw-table", raw);
+	glades::NumberInput in;
+	{
+		Quiet q;
+		in.standardizeInputTable(shmea::GString("oracle-raw-table"), standardize_flag);
+	}
+	const int cx = (int)in.trainTable.numberOfCols(), cy = (int)in.trainExpectedTable.numberOfCols();
+	if (nx) *nx = cx;
+	if (ny) *ny = cy;
+	const int64_t outRows = in.trainTable.numberOfRows();
+	if (x_out)
+		for (int64_t r = 0; r < outRows; ++r)
+			for (int c = 0; c < cx; ++c)
+				x_out[(size_t)r * cx + c] = in.trainTable.getCell(r, c).getFloat();
+	if (y_out)
+		for (int64_t r = 0; r < (int64_t)in.trainExpectedTable.numberOfRows(); ++r)
+			for (int c = 0; c < cy; ++c)
+				y_out[(size_t)r * cy + c] = in.trainExpectedTable.getCell(r, c).getFloat();
+	for (unsigned int c = 0; c < in.OHEMaps.size(); ++c)
+		delete in.OHEMaps[c];
+	return outRows;
+}
+
+// NNetwork::train() with a server and a connection attached: the reference then streams its GUI messages
+// (Networks/network.cpp:258-357) through GNet::GServer::send, which the shim records.  The terminator is set
+// to `epochs`; below 10 epochs every epoch sends (the 60 Hz throttle starts at epoch 10, network.cpp:264).
+// The messages come back flattened into `out` (at most `cap` doubles; the needed count is returned):
+//   per message: kind id (0 PROGRESSIVE, 1 ACTIVATIONS, 2 WEIGHTS, 3 ACC, 4 CONF, -1 other), number of
+//   extra arguments, the arguments, payload rows, payload columns (0, 0 for a list), payload length, payload.
+// A string cell of a payload (the ',' and ';' separators) is 1e9 + its character code.
+int64_t ref_train_gui(void* h, int epochs, double* out, int64_t cap)
+{
+	RefNet* r = (RefNet*)h;
+	shmea::shimClearMessages();
+	{
+		Quiet q;
+		r->net->setServer((GNet::GServer*)0x10, (GNet::Connection*)0x10);
+		r->net->terminator.setEpoch(r->net->epochs - 1 + epochs);  // run() starts from epochs = 1 (see ref_create)
+		r->net->train(r->di);
+		r->net->setServer(NULL, NULL);
+	}
+	static const char* kinds[] = {"PROGRESSIVE", "ACTIVATIONS", "WEIGHTS", "ACC", "CONF"};
+	int64_t k = 0;
+	for (size_t i = 0; i < shmea::shimMessageCount(); ++i)
+	{
+		const shmea::ShimMessage& m = shmea::shimMessage(i);
+		double id = -1;
+		for (int t = 0; t < 5; ++t)
+			if (m.kind == kinds[t])
+				id = t;
+		std::vector<double> rec;
+		rec.push_back(id);
+		rec.push_back((double)m.args.size());
+		rec.insert(rec.end(), m.args.begin(), m.args.end());
+		rec.push_back(m.rows);
+		rec.push_back(m.cols);
+		rec.push_back((double)m.payload.size());
+		rec.insert(rec.end(), m.payload.begin(), m.payload.end());
+		for (size_t j = 0; j < rec.size(); ++j, ++k)
+			if (out && k < cap)
+				out[k] = rec[j];
+	}
+	return k;
 }
 
 // Scalar functions of GMath, for known-answer tables.

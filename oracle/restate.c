@@ -850,3 +850,84 @@ void rs_synth_fill(float* out, int64_t n, uint64_t seed, uint32_t stream, int di
 		out[i] = offset + scale * v;
 	}
 }
+
+/* ------------------------------------------------------------------------------------------
+ * Input standardisation: NumberInput::standardizeInputTable (DataObjects/NumberInput.cpp:43-285) and
+ * the one-hot vectors of OHE::operator[] (GMath/OHE.cpp:159-198), restated on a flat raw table.
+ *   raw[r*cols + c]   the cell as a float; for a categorical column the category's index in order of
+ *                     first appearance (the order OHE::addString builds, OHE.cpp:54-64)
+ *   kind[c]           0 numeric, 1 categorical with classes[c] categories
+ *   to_output[c]      1: the column goes to the expected-rows table
+ *   flag              0 MINMAX, 1 ZSCORE (GMath/gmath.h:53-54)
+ * Facts of the reference that are kept: the running minimum and maximum start from the first cell only
+ * for raw column 0 and from 0.0 for every other column (NumberInput.cpp:105-109); a table with any
+ * categorical column scales numeric columns to [0.01, 0.99], else to [0, 1] (:196-214); a column whose
+ * (zero-including) range is 0 is copied unscaled and always lands in the INPUT table (:166-171); the mean
+ * is a sequential fp32 sum divided once (:118-121), the deviation sqrt(sum((x-mean)^2) / (rows-1)).
+ * Columns keep their raw order inside each output table.  x / y are row-major with nx / ny columns.
+ * Returns 0, or -1 when the outputs' widths do not match the plan.
+ * ------------------------------------------------------------------------------------------ */
+int rs_standardize_table(const float* raw, int64_t rows, int cols, const int* kind, const int* classes,
+                         const int* to_output, int flag, float* x, int nx, float* y, int ny)
+{
+	int classification = 0;
+	for (int c = 0; c < cols; ++c)
+		if (kind[c] == 1) classification = 1;
+	int cx = 0, cy = 0;
+	for (int c = 0; c < cols; ++c)
+	{
+		if (kind[c] == 1)
+		{
+			float* dst = to_output[c] ? y : x;
+			const int ld = to_output[c] ? ny : nx;
+			int* at = to_output[c] ? &cy : &cx;
+			if (*at + classes[c] > ld) return -1;
+			for (int k = 0; k < classes[c]; ++k)
+				for (int64_t r = 0; r < rows; ++r)
+					dst[(size_t)r * ld + *at + k] = ((int)raw[(size_t)r * cols + c] == k) ? 0.99f : 0.01f;
+			*at += classes[c];
+			continue;
+		}
+		float fMin = 0.0f, fMax = 0.0f, fMean = 0.0f;
+		for (int64_t r = 0; r < rows; ++r)
+		{
+			const float cell = raw[(size_t)r * cols + c];
+			if (r == 0 && c == 0) { fMin = cell; fMax = cell; }
+			if (cell < fMin) fMin = cell;
+			if (cell > fMax) fMax = cell;
+			fMean += cell;
+			if (r == rows - 1) fMean /= (float)(unsigned int)rows;
+		}
+		int out = to_output[c];
+		float fStDev = 0.0f;
+		const float xRange = fMax - fMin;
+		if (flag == 0 && xRange == 0.0f) out = 0;  /* constant column: copied, to the input table */
+		if (flag == 1)
+		{
+			for (int64_t r = 0; r < rows; ++r)
+			{
+				const float cell = raw[(size_t)r * cols + c];
+				fStDev += ((cell - fMean) * (cell - fMean));
+			}
+			fStDev = sqrtf(fStDev / (float)((unsigned int)rows - 1u));
+		}
+		float* dst = out ? y : x;
+		const int ld = out ? ny : nx;
+		int* at = out ? &cy : &cx;
+		if (*at + 1 > ld) return -1;
+		for (int64_t r = 0; r < rows; ++r)
+		{
+			float cell = raw[(size_t)r * cols + c];
+			if (flag == 0)
+			{
+				if (xRange != 0.0f)
+					cell = classification ? ((((cell - fMin) / (xRange)) * 0.98f) + 0.01f) : ((cell - fMin) / (xRange));
+			}
+			else
+				cell = ((cell - fMean) / fStDev);
+			dst[(size_t)r * ld + *at] = cell;
+		}
+		*at += 1;
+	}
+	return (cx == nx && cy == ny) ? 0 : -1;
+}

@@ -17,11 +17,16 @@
 #include "Backend/Database/GString.h"
 #include "Backend/Database/GList.h"
 #include "Backend/Database/GTable.h"
+#include "Backend/Database/GObject.h"
+#include "Backend/Database/ServiceData.h"
 
 #include <stdint.h>
 #include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
+
+#include <map>
+#include <string>
 
 namespace shmea {
 
@@ -148,6 +153,19 @@ GString::GString(const GType& g) : GType("")
 GString::~GString() {}
 
 unsigned int GString::length() const { return blockSize; }
+GString GString::intTOstring(int v)
+{
+	char buf[32];
+	snprintf(buf, sizeof buf, "%d", v);
+	return GString(buf);
+}
+GString GString::operator+=(const GString& o)
+{
+	std::string joined(block.get(), blockSize);
+	joined.append(o.c_str(), o.length());
+	set(STRING_TYPE, joined.data(), (int64_t)joined.size());
+	return *this;
+}
 bool GString::operator==(const GString& o) const
 {
 	return blockSize == o.blockSize && memcmp(block.get(), o.block.get(), blockSize) == 0;
@@ -169,6 +187,7 @@ void GList::addInt(int v) { items.push_back(GType(v)); }
 void GList::addLong(int64_t v) { items.push_back(GType(v)); }
 void GList::addString(const char* s) { items.push_back(GType(s)); }
 void GList::addString(const GString& s) { items.push_back(GType(s.c_str(), s.length())); }
+void GList::addGType(const GType& v) { items.push_back(v); }
 void GList::clear() { items.clear(); }
 void GList::setGType(unsigned int i, const GType& v)
 {
@@ -205,6 +224,68 @@ GTable::GTable(const GTable& o)
 }
 GTable::~GTable() {}
 
+// The reference reads its raw tables with GTable(file name, delimiter, TYPE_FILE)
+// (DataObjects/NumberInput.cpp:47).  shmea's file importer -- how it types the cells of a CSV file and
+// which column it marks as output -- is not part of the reference tree, so this shim does not imitate
+// it: the harness registers an already typed table under a name, and the "file" constructor hands out
+// a copy of the table registered under that name (an empty table for an unknown name).
+static std::map<std::string, GTable>& tableRegistry()
+{
+	static std::map<std::string, GTable> reg;
+	return reg;
+}
+void shimRegisterTable(const char* name, const GTable& t) { tableRegistry()[name] = t; }
+GTable::GTable(const GString& fname, char d, int) : delimiter(d), xMin(0.0f), xMax(0.0f), xRange(0.0f)
+{
+	std::map<std::string, GTable>::const_iterator it = tableRegistry().find(std::string(fname.c_str(), fname.length()));
+	if (it != tableRegistry().end())
+		*this = it->second;
+}
+void GTable::operator=(const GTable& o)
+{
+	delimiter = o.delimiter;
+	header = o.header;
+	cells = o.cells;
+	xMin = o.xMin;
+	xMax = o.xMax;
+	xRange = o.xRange;
+	outputColumns = o.outputColumns;
+}
+// Appends a column: one cell per row (rows are created for the first column of an empty table).
+void GTable::addCol(const GString& h, const GList& col, unsigned int)
+{
+	header.push_back(h);
+	if (cells.size() < col.size())
+		cells.resize(col.size());
+	for (unsigned int r = 0; r < col.size(); ++r)
+		cells[r].addGType(col[r]);
+}
+GList GTable::getRow(unsigned int r) const { return r < cells.size() ? cells[r] : GList(); }
+GList GTable::getCol(unsigned int c) const
+{
+	GList out;
+	for (unsigned int r = 0; r < cells.size(); ++r)
+		out.addGType(cells[r][c]);
+	return out;
+}
+bool GTable::isOutput(unsigned int c) const
+{
+	for (unsigned int i = 0; i < outputColumns.size(); ++i)
+		if (outputColumns[i] == c)
+			return true;
+	return false;
+}
+void GTable::toggleOutput(unsigned int c)
+{
+	for (unsigned int i = 0; i < outputColumns.size(); ++i)
+		if (outputColumns[i] == c)
+		{
+			outputColumns.erase(outputColumns.begin() + i);
+			return;
+		}
+	outputColumns.push_back(c);
+}
+
 void GTable::addRow(const GList& r) { cells.push_back(r); }
 void GTable::clear()
 {
@@ -238,10 +319,100 @@ const GList& GTable::operator[](unsigned int r) const
 	static const GList empty;
 	return r < cells.size() ? cells[r] : empty;
 }
+const GList& GTable::operator[](int r) const { return (*this)[(unsigned int)(r < 0 ? 0 : r)]; }
 void GTable::print() const
 {
 	for (unsigned int r = 0; r < cells.size(); ++r)
 		cells[r].print();
 }
 
+// ---------------------------------------------------------------- GObject / ServiceData (GUI messages)
+GObject::GObject() {}
+GObject::~GObject() {}
+
+ServiceData::ServiceData(GNet::Connection* c, GString cmd)
+	: cConnection(c), timesent(0), command(cmd), serviceNum(0), responseServiceNum(0), type(TYPE_ACK)
+{
+}
+ServiceData::~ServiceData() {}
+void ServiceData::set(const GList& l)
+{
+	repList = l;
+	type = TYPE_LIST;
+}
+void ServiceData::set(const GTable& t)
+{
+	repTable = t;
+	type = TYPE_TABLE;
+}
+void ServiceData::setArgList(const GList& l) { argList = l; }
+GString ServiceData::getCommand() const { return command; }
+int ServiceData::getType() const { return type; }
+const GList& ServiceData::getArgList() const { return argList; }
+const GList& ServiceData::getList() const { return repList; }
+const GTable& ServiceData::getTable() const { return repTable; }
+
+// What the reference hands to GNet::GServer::send (Networks/network.cpp:258-357), flattened: the argument
+// list and the payload (a list, or a table row by row) as doubles; a string cell becomes its first
+// character's code plus 1e9 (the payloads only carry the separators ',' and ';' and, in the argument
+// list, the message kind, which is kept as text).
+struct ShimMessage
+{
+	std::string command, kind;
+	std::vector<double> args, payload;
+	int rows, cols;
+};
+static std::vector<ShimMessage>& messageLog()
+{
+	static std::vector<ShimMessage> log;
+	return log;
+}
+static double cellValue(const GType& g)
+{
+	if (g.getType() == GType::STRING_TYPE)
+		return 1e9 + (double)(unsigned char)(g.size() ? g.c_str()[0] : 0);
+	return g.getDouble();
+}
+void shimClearMessages() { messageLog().clear(); }
+size_t shimMessageCount() { return messageLog().size(); }
+const ShimMessage& shimMessage(size_t i) { return messageLog()[i]; }
+void shimRecordMessage(const ServiceData* d, const GString& command, const GList& args, int type, const GList& list,
+                       const GTable& table)
+{
+	ShimMessage m;
+	m.command = std::string(command.c_str(), command.length());
+	m.rows = m.cols = 0;
+	for (unsigned int i = 0; i < args.size(); ++i)
+	{
+		const GType a = args[i];
+		if (i == 0 && a.getType() == GType::STRING_TYPE)
+			m.kind = std::string(a.c_str(), a.size());
+		else
+			m.args.push_back(cellValue(a));
+	}
+	if (type == ServiceData::TYPE_TABLE)
+	{
+		m.rows = (int)table.numberOfRows();
+		m.cols = (int)table.numberOfCols();
+		for (int r = 0; r < m.rows; ++r)
+			for (int c = 0; c < m.cols; ++c)
+				m.payload.push_back(cellValue(table.getCell(r, c)));
+	}
+	else
+		for (unsigned int i = 0; i < list.size(); ++i)
+			m.payload.push_back(cellValue(list[i]));
+	messageLog().push_back(m);
+	(void)d;
+}
+
 } // namespace shmea
+
+// GNet::GServer::send(shmea::ServiceData*, bool, bool), defined by its mangled name because the class
+// declaration drags in the whole networking layer (include/Backend/Networking/main.h:119).  The reference
+// only needs a non-NULL server pointer to call it; `self` is never touched.
+extern "C" void _ZN4GNet7GServer4sendEPN5shmea11ServiceDataEbb(void* self, shmea::ServiceData* d, bool, bool)
+{
+	(void)self;
+	if (d)
+		shmea::shimRecordMessage(d, d->getCommand(), d->getArgList(), d->getType(), d->getList(), d->getTable());
+}

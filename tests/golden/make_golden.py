@@ -129,6 +129,97 @@ def init_fixture():
     save("init_weights", dict(kind="init", cases=cases), **arrays)
 
 
+def standardize_fixture():
+    """NumberInput::standardizeInputTable + OHE, the reference's own code (DataObjects/NumberInput.cpp:43-285,
+    GMath/OHE.cpp), on typed raw tables handed over through the shim's table registry.  Column types: 0 float
+    cells, 1 string cells (category k is the text "s<k>"), 2 int cells."""
+    import ctypes as C
+    L = o.reference_lib()
+    L.ref_number_input.restype = C.c_int64
+    L.ref_number_input.argtypes = [C.c_void_p, C.c_int64, C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p,
+                                   C.c_void_p, C.c_void_p]
+
+    def run(vals, types, outs, flag):
+        vals = np.ascontiguousarray(vals, np.float32)
+        rows, cols = vals.shape
+        t, oc = np.array(types, np.int32), np.array(outs, np.int32)
+        nx, ny = C.c_int(), C.c_int()
+        L.ref_number_input(vals.ctypes.data, rows, cols, t.ctypes.data, oc.ctypes.data, flag, None, C.byref(nx), None, C.byref(ny))
+        x = np.zeros((rows, nx.value), np.float32)
+        y = np.zeros((rows, ny.value), np.float32)
+        L.ref_number_input(vals.ctypes.data, rows, cols, t.ctypes.data, oc.ctypes.data, flag, x.ctypes.data, C.byref(nx),
+                           y.ctypes.data, C.byref(ny))
+        return x, y
+
+    rng = np.random.default_rng(61)
+    arrays, cases = {}, []
+    shapes = [(150, 5, [0, 0, 0, 0, 1], [0, 0, 0, 0, 1], 0),      # four measurements and a class name: the classic table shape
+              (64, 4, [0, 0, 2, 0], [0, 0, 0, 1], 0),             # regression: [0, 1] scaling, an int column
+              (64, 4, [0, 0, 2, 0], [0, 1, 0, 1], 1),             # z-score
+              (40, 6, [1, 0, 1, 2, 0, 0], [0, 0, 1, 0, 1, 0], 0),  # categorical inputs and outputs mixed
+              (33, 3, [0, 0, 0], [0, 0, 1], 0),                   # constant and all-positive columns (the zero-start rule)
+              (400, 32, [0] * 32, [0] * 31 + [1], 0)]             # a wider table
+    for k, (rows, cols, types, outs, flag) in enumerate(shapes):
+        v = rng.uniform(-4, 6, (rows, cols)).astype(np.float32)
+        for c in range(cols):
+            if types[c] == 1:
+                ids = rng.integers(0, 3 + c % 3, rows)
+                seen = {}
+                for i, t in enumerate(ids):   # category indices in order of first appearance
+                    seen.setdefault(int(t), len(seen))
+                    ids[i] = seen[int(t)]
+                v[:, c] = ids
+            elif types[c] == 2:
+                v[:, c] = np.round(v[:, c])
+        if k == 4:
+            v[:, 0] = 2.5                      # constant: range (from 0) is 2.5, so it IS scaled
+            v[:, 1] = np.abs(v[:, 1]) + 1.0    # all positive: the minimum stays 0
+        if k == 1:
+            v[:, 1] = 0.0                      # constant zero: range 0, copied unscaled into the input table
+        x, y = run(v, types, outs, flag)
+        arrays.update({"raw%d" % k: v, "x%d" % k: x, "y%d" % k: y})
+        cases.append(dict(rows=rows, cols=cols, types=types, outputs=outs, flag=flag))
+    save("standardize", dict(kind="standardize", cases=cases), **arrays)
+
+
+def gui_fixture():
+    """The live-view messages NNetwork::run sends through GNet::GServer::send when a server and a connection
+    are attached (Networks/network.cpp:258-357), recorded by the shim, for runs of fewer than 10 epochs (every
+    epoch sends).  The harness starts run() at epoch 1 (it must keep run() from rebuilding the network), so the
+    epoch labels in the stream start at 2: `epoch_base` says so."""
+    import ctypes as C
+    L = o.reference_lib()
+    L.ref_train_gui.restype = C.c_int64
+    L.ref_train_gui.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_int64]
+    rng = np.random.default_rng(71)
+    arrays, cases = {}, []
+    nets = [dict(sizes=[3, 4, 2], acts=["tanh", "sigmoid"], out="classification", rows=12, batch=2, lr=0.05, momentum=0.3, epochs=5),
+            dict(sizes=[5, 6, 4, 1], acts=["relu", "relu", "linear"], out="regression", rows=20, batch=4, lr=0.01, momentum=0.5,
+                 epochs=4, params=[0.0, 0.0, 1.0])]
+    for k, c in enumerate(nets):
+        sizes = c["sizes"]
+        x = rng.uniform(0, 1, (c["rows"], sizes[0])).astype(np.float32)
+        if c["out"] == "classification":
+            y = np.full((c["rows"], sizes[-1]), 0.01, np.float32)
+            y[np.arange(c["rows"]), rng.integers(0, sizes[-1], c["rows"])] = 0.99
+        else:
+            y = rng.uniform(0.1, 0.9, (c["rows"], sizes[-1])).astype(np.float32)
+        d = capi.make_desc(sizes, c["acts"], c["out"], batch=c["batch"], lr=c["lr"], momentum=c["momentum"], params=c.get("params"))
+        w0 = rng.uniform(-0.5, 0.5, capi.weight_count(d)).astype(np.float32)
+        b0 = rng.uniform(-0.1, 0.1, len(sizes) - 2).astype(np.float32)
+        R = o.Reference(d, x, y, capi.Metrics)
+        R.set_weights(w0, b0)
+        n = L.ref_train_gui(R.h, c["epochs"], None, 0)
+        R = o.Reference(d, x, y, capi.Metrics)
+        R.set_weights(w0, b0)
+        buf = np.zeros(n, np.float64)
+        assert L.ref_train_gui(R.h, c["epochs"], buf.ctypes.data, n) == n
+        w_end, b_end = R.get_weights()
+        arrays.update({"x%d" % k: x, "y%d" % k: y, "w0_%d" % k: w0, "b0_%d" % k: b0, "stream%d" % k: buf, "w_end%d" % k: w_end})
+        cases.append(dict(c, epoch_base=1))
+    save("gui_stream", dict(kind="gui", cases=cases), **arrays)
+
+
 def main():
     t0 = time.time()
     if "--only-init" in sys.argv:
@@ -210,6 +301,10 @@ def main():
                {1, 4}, 0.5, 34, p_dropout=[1.0, 1.0], srand=104)
     trajectory("traj_dropout_5_6_3_half", [5, 6, 3], ["tanh", "sigmoid"], "classification", xd3, yd3, 3, 0.01, 0.3, 4,
                {1, 4}, 0.5, 35, p_dropout=0.5, srand=105)
+
+    # ---- D. the step in front of the loop and the step behind it
+    standardize_fixture()
+    gui_fixture()
 
     # ---- config 1 as written (lr 0.1): the reference goes non-finite; record the first such row
     d = capi.make_desc([4, 16, 3], ["sigmoid", "sigmoid"], "classification", batch=1, lr=0.1, momentum=0.9)

@@ -7,6 +7,12 @@
 //   host_tool init  <case> <out>        draws initial weights after srand(seed) and writes them
 //   host_tool run   <case> <out>        trains / tests on the GPU through NNetwork and writes
 //                                       weights, biases, metrics, results, confusion counts
+//   host_tool gui   <case> <out>        trains with a recording server attached and writes the live-view
+//                                       messages, flattened like the oracle harness flattens the reference's
+//   host_tool replicas <case> <out> <k> trains k replicas through MetaNetwork::trainReplicas (one per GPU,
+//                                       round robin) and writes every replica's weights
+//   host_tool standardize <table> <out> standardises a typed raw table through NumberInput on the GPU and
+//                                       writes the input and expected matrices
 #include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
@@ -67,6 +73,49 @@ static NNInfo* makeInfo(const Case& c)
 	return new NNInfo("case", in, hidden, out);
 }
 
+// A server that records what the live view sends, flattened as the oracle harness flattens the reference's
+// messages: kind id, number of extra arguments, the arguments, payload rows, payload columns, payload
+// length, payload; a text cell is 1e9 + its first character's code.
+struct RecordingServer : public GNet::GServer
+{
+	std::vector<double> log;
+	static double cell(const shmea::GList& l, unsigned int i)
+	{
+		if (l.isString(i))
+		{
+			const std::string s = l.getString(i);
+			return 1e9 + (double)(unsigned char)(s.empty() ? 0 : s[0]);
+		}
+		return (double)l.getFloat(i);
+	}
+	void send(shmea::ServiceData* d, bool, bool)
+	{
+		static const char* kinds[] = {"PROGRESSIVE", "ACTIVATIONS", "WEIGHTS", "ACC", "CONF"};
+		const shmea::GList& args = d->getArgList();
+		double id = -1;
+		for (int t = 0; t < 5; ++t)
+			if (args.size() > 0 && args.getString(0) == kinds[t]) id = t;
+		log.push_back(id);
+		log.push_back(args.size() > 0 ? (double)(args.size() - 1) : 0.0);
+		for (unsigned int i = 1; i < args.size(); ++i) log.push_back(cell(args, i));
+		if (d->getType() == shmea::ServiceData::TYPE_TABLE)
+		{
+			log.push_back(d->getTableRows());
+			log.push_back(d->getTableCols());
+			log.push_back((double)d->getTableCells().size());
+			for (size_t i = 0; i < d->getTableCells().size(); ++i) log.push_back((double)d->getTableCells()[i]);
+		}
+		else
+		{
+			log.push_back(0);
+			log.push_back(0);
+			log.push_back((double)d->getList().size());
+			for (unsigned int i = 0; i < d->getList().size(); ++i) log.push_back(cell(d->getList(), i));
+		}
+		delete d;
+	}
+};
+
 #define CHECK(expr)                                                       \
 	do                                                                    \
 	{                                                                     \
@@ -123,6 +172,53 @@ static int unitChecks()
 	net.setQuiet(true);
 	net.train(NULL);
 	CHECK(net.getEpochs() == 0);
+	// one-hot maps (GMath/OHE.cpp): categories in order of first appearance, 0.99 / 0.01 vectors, decoding
+	OHE ohe;
+	ohe.addString("b");
+	ohe.addString("a");
+	ohe.addString("b");
+	CHECK(ohe.size() == 2 && ohe.indexAt("a") == 1 && ohe.indexAt("zzz") == -1 && ohe.classCount["b"] == 2.0);
+	CHECK(ohe["a"][0] == 0.01f && ohe["a"][1] == 0.99f && ohe["zzz"][0] == 0.01f && ohe["zzz"][1] == 0.01f);
+	std::vector<float> probe(2);
+	probe[0] = 0.2f;
+	probe[1] = 0.7f;
+	CHECK(ohe[probe] == "a" && ohe.classAt(0) == "b" && ohe.classAt(9) == "");
+	ohe.setRange(-1.0f, 3.0f, 0.0f);
+	CHECK(ohe.standardize(3.0f) == 0.99f && ohe.standardize(-1.0f) == 0.01f);
+	// the skeleton's table form (Structure/nninfo.cpp:711-798): save, load, same getters
+	{
+		char dir[] = "/tmp/glades_b200_unit_XXXXXX";
+		CHECK(mkdtemp(dir) != NULL);
+		CHECK(info.save(dir));
+		NNInfo* back = NNInfo::load("unit", dir);
+		CHECK(back != NULL && back->numHiddenLayers() == 2 && back->getBatchSize() == 4 && back->getOutputLayerSize() == 3);
+		CHECK(back->getLearningRate(0) == 0.1f && back->getLearningRate(2) == 0.3f && back->getWeightDecay2(1) == 0.004f);
+		CHECK(back->getActivationType(2) == GMath::RELU && back->getOutputType() == GMath::CLASSIFICATION);
+		CHECK(back->getHiddenLayerSize(0) == 16 && back->getHiddenLayerSize(1) == 8 && back->getActivationParam(1) == 0.7f);
+		CHECK(NNInfo::load("missing", dir) == NULL);
+		NNetwork loaded;
+		CHECK(loaded.load("unit", dir) && loaded.getName() == "unit" && loaded.getNNInfo()->numHiddenLayers() == 2);
+		CHECK(!loaded.load("missing", dir));
+		// a raw table from a comma-separated file: typing by the first cell, last column marked as output
+		const std::string csv = std::string(dir) + "/t.csv";
+		FILE* tf = fopen(csv.c_str(), "w");
+		CHECK(tf != NULL);
+		fprintf(tf, "len,colour,kind\n1.5,red,x\n2.5,blue,y\n-3,red,x\n");
+		fclose(tf);
+		RawTable rt;
+		CHECK(RawTable::fromCSV(csv, rt, 1) && rt.rows == 3 && rt.numberOfCols() == 3);
+		CHECK(!rt.isString[0] && rt.isString[1] && rt.isString[2] && !rt.isOutput[1] && rt.isOutput[2]);
+		CHECK(rt.numbers[0][2] == -3.0f && rt.texts[1][1] == "blue");
+		CHECK(!RawTable::fromCSV(std::string(dir) + "/none.csv", rt, 1));
+		delete back;
+	}
+	// collections: NULL arguments, names, look-up (Networks/metanetwork.cpp)
+	CHECK(train((NNInfo*)NULL, &ai) == NULL && test((MetaNetwork*)NULL, &ai) == NULL);
+	MetaNetwork meta(&info, 3);
+	CHECK(meta.size() == 3 && meta.getName() == "unit" && meta.getSubnetName(2) == "unit" && meta.getSubnet(3) == NULL);
+	CHECK(meta.getSubnetByName("unit") == meta.getSubnet(0) && meta.getSubnetByName("other") == NULL);
+	meta.addSubnet((NNetwork*)NULL);
+	CHECK(meta.size() == 3);
 	// shard arithmetic of the C ABI
 	int64_t f = 0, c = 0;
 	gl_shard_range(10, 0, 3, &f, &c);
@@ -142,10 +238,68 @@ static int unitChecks()
 	return 0;
 }
 
+// standardize: <table> = int32 rows, cols, flag; int32 type[cols] (0 number, 1 string: cell k is the text "s<k>");
+// int32 output[cols]; float32 cells[rows][cols].  <out> = int32 rows, nx, ny; float32 X[rows][nx]; Y[rows][ny].
+static int standardizeTable(const char* in, const char* outPath)
+{
+	FILE* f = fopen(in, "rb");
+	if (!f) return 2;
+	int hdr[3];
+	if (!rd(f, hdr, sizeof hdr)) return 2;
+	const int rows = hdr[0], cols = hdr[1], flag = hdr[2];
+	std::vector<int> type(cols), output(cols);
+	std::vector<float> cells((size_t)rows * cols);
+	if (!rd(f, &type[0], 4 * cols) || !rd(f, &output[0], 4 * cols) || !rd(f, &cells[0], 4 * cells.size())) return 2;
+	fclose(f);
+	RawTable raw;
+	for (int c = 0; c < cols; ++c)
+	{
+		char h[32];
+		snprintf(h, sizeof h, "col%d", c);
+		if (type[c] == 1)
+		{
+			std::vector<std::string> col(rows);
+			for (int r = 0; r < rows; ++r)
+			{
+				char s[32];
+				snprintf(s, sizeof s, "s%d", (int)cells[(size_t)r * cols + c]);
+				col[r] = s;
+			}
+			raw.addStringCol(h, col, output[c] != 0);
+		}
+		else
+		{
+			std::vector<float> col(rows);
+			for (int r = 0; r < rows; ++r) col[r] = cells[(size_t)r * cols + c];
+			raw.addNumberCol(h, col, output[c] != 0);
+		}
+	}
+	NumberInput ni;
+	if (!ni.standardizeInputTable(raw, flag)) return 5;
+	FILE* out = fopen(outPath, "wb");
+	if (!out) return 2;
+	const int dims[3] = {(int)ni.getTrainSize(), (int)ni.getFeatureCount(), (int)ni.getOutputCount()};
+	fwrite(dims, 4, 3, out);
+	// through the row getters, like a caller of the reference reads them
+	for (int r = 0; r < dims[0]; ++r)
+	{
+		const shmea::GList row = ni.getTrainRow(r);
+		for (int c = 0; c < dims[1]; ++c) { const float v = row.getFloat(c); fwrite(&v, 4, 1, out); }
+	}
+	for (int r = 0; r < dims[0]; ++r)
+	{
+		const shmea::GList row = ni.getTrainExpectedRow(r);
+		for (int c = 0; c < dims[2]; ++c) { const float v = row.getFloat(c); fwrite(&v, 4, 1, out); }
+	}
+	fclose(out);
+	return 0;
+}
+
 int main(int argc, char** argv)
 {
 	if (argc >= 2 && strcmp(argv[1], "unit") == 0) return unitChecks();
 	if (argc < 4) return 2;
+	if (strcmp(argv[1], "standardize") == 0) return standardizeTable(argv[2], argv[3]);
 	Case c;
 	if (!loadCase(argv[2], c)) { fprintf(stderr, "cannot read case %s\n", argv[2]); return 2; }
 	NNInfo* info = makeInfo(c);
@@ -161,6 +315,59 @@ int main(int argc, char** argv)
 		return 0;
 	}
 	ArrayInput di(&c.x[0], &c.y[0], c.rows, c.sizes[0], c.sizes[c.nLayers - 1]);
+	if (strcmp(argv[1], "replicas") == 0)
+	{
+		// k replicas of the same network, same injected weights, trained side by side; every replica must end
+		// with the weights of a single run
+		const int k = argc >= 5 ? atoi(argv[4]) : 2;
+		MetaNetwork meta(info, k);
+		for (int i = 0; i < k; ++i)
+		{
+			NNetwork* sub = meta.getSubnet(i);
+			sub->setQuiet(true);
+			sub->setMode(c.mode);
+			sub->setWeights(c.w, c.b);
+			sub->terminator.setEpoch(c.epochs);
+		}
+		const int gpus = meta.trainReplicas(&di);
+		fwrite(&gpus, 4, 1, out);
+		fwrite(&k, 4, 1, out);
+		for (int i = 0; i < k; ++i)
+		{
+			std::vector<float> w, b;
+			if (!meta.getSubnet(i)->getWeights(w, b)) { fclose(out); return 4; }
+			const int e = meta.getSubnet(i)->getEpochs(), nw = (int)w.size();
+			fwrite(&e, 4, 1, out);
+			fwrite(&nw, 4, 1, out);
+			fwrite(&w[0], 4, nw, out);
+			delete meta.getSubnet(i);
+		}
+		fclose(out);
+		delete info;
+		return 0;
+	}
+	if (strcmp(argv[1], "gui") == 0)
+	{
+		RecordingServer server;
+		GNet::Connection connection;
+		NNetwork net(info);
+		net.setQuiet(true);
+		net.setMode(c.mode);
+		net.setWeights(c.w, c.b);
+		net.terminator.setEpoch(c.epochs);
+		MetaNetwork* meta = train(&net, &di, &server, &connection);
+		if (!meta || meta->size() != 1 || meta->getSubnet(0) != &net) return 6;
+		delete meta;
+		const shmea::GList curve = net.getLearningCurve();
+		const int n = (int)server.log.size(), nc = (int)curve.size();
+		fwrite(&n, 4, 1, out);
+		if (n) fwrite(&server.log[0], 8, n, out);
+		fwrite(&nc, 4, 1, out);
+		for (int i = 0; i < nc; ++i) { const float v = curve.getFloat(i); fwrite(&v, 4, 1, out); }
+		fclose(out);
+		delete info;
+		return 0;
+	}
 	NNetwork net(info);
 	net.setQuiet(true);
 	net.setMode(c.mode);
@@ -169,8 +376,10 @@ int main(int argc, char** argv)
 	// like nn-test.cpp:69-75: terminator on the epoch count, accuracy below the bar before training
 	net.terminator.setEpoch(c.epochs);
 	if (net.getAccuracy() >= 95.0f) return 3;
-	if (c.runType == NNetwork::RUN_TRAIN) train(&net, &di);
-	else test(&net, &di);
+	// glades::train / glades::test hand back a new collection that holds the network (main.cpp:112-134)
+	MetaNetwork* ran = (c.runType == NNetwork::RUN_TRAIN) ? train(&net, &di) : test(&net, &di);
+	if (!ran || ran->getSubnet(0) != &net) return 6;
+	delete ran;
 	std::vector<float> w, b;
 	if (!net.getWeights(w, b)) { fclose(out); return 4; }
 	const int epochs = net.getEpochs();

@@ -192,3 +192,16 @@ def test_batched_restatement_matches_sharded_sum(g, oracle):
     a = S.window_grad(0, 20, global_rows=rows, first_pos=0)
     b = S.window_grad(20, 12, global_rows=rows, first_pos=20)
     assert np.allclose(a + b, whole, rtol=1e-12, atol=1e-14)
+
+
+def test_restatement_standardize_vs_golden(oracle):
+    """NumberInput::standardizeInputTable + OHE: the C restatement against tables standardised by the reference's
+    own code -- categorical columns, int columns, both scalings, z-score, constant columns, the minimum that
+    starts from zero.  Bit for bit."""
+    meta, z = load_golden("standardize")
+    assert len(meta["cases"]) >= 6
+    for k, c in enumerate(meta["cases"]):
+        x, y = oracle.standardize_table(z["raw%d" % k], c["types"], c["outputs"], c["flag"], z["x%d" % k].shape[1],
+                                        z["y%d" % k].shape[1])
+        assert np.array_equal(bits(x), bits(z["x%d" % k])), "case %d inputs" % k
+        assert np.array_equal(bits(y), bits(z["y%d" % k])), "case %d expected" % k
