@@ -197,8 +197,9 @@ def device_count():
 
 
 def tc_variant_counts():
-    """Tensor-core product launches of this process: [128-wide, 256-wide, several tiles per CTA, peer-store]."""
-    out = (C.c_int64 * 4)()
+    """Tensor-core product launches of this process: [128-wide, 256-wide, several tiles per CTA, peer-store,
+    last wave split along k]."""
+    out = (C.c_int64 * 5)()
     lib().gl_tc_variant_counts(out)
     return [int(v) for v in out]
 

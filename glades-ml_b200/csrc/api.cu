@@ -215,6 +215,9 @@ struct gl_net
 	bool loD[GL_MAX_WEIGHT_LAYERS + 2] = {};
 	int64_t tcLaunches = 0;
 	int64_t lastWindowLaunches = 0;
+	// workspace for splitting a partial wave of tiles along k (all tensor-core products of the compute stream)
+	TcSplitK sk = {nullptr, nullptr, nullptr, 0};
+	unsigned skEpoch = 0;
 	// optional per-launch timing of the layer products (gl_profile_enable)
 	bool profile = false;
 	std::vector<cudaEvent_t> profEv;   // pairs
@@ -490,6 +493,7 @@ extern "C" int gl_destroy(gl_net* n)
 	if (n->evSnapReady) cudaEventDestroy(n->evSnapReady);
 	if (n->snapStream) cudaStreamDestroy(n->snapStream);
 	cudaFree(n->dpRec);
+	cudaFree(n->sk.work); cudaFree(n->sk.flags);
 	cudaFree(n->dWlo);
 	cudaFree(n->dW); cudaFree(n->dBias); cudaFree(n->dG); cudaFree(n->dBscale); cudaFree(n->dFlags);
 	cudaFree(n->dSums); cudaFree(n->dSumsF); cudaFree(n->dConf); cudaFree(n->dHist); cudaFree(n->dHistLen);
@@ -971,6 +975,16 @@ static int ensure_work(gl_net* n, int64_t rows)
 		CU(cudaMalloc(&n->dDc, (size_t)rows * maxn * sizeof(float)));
 		CU(cudaMalloc(&n->dDclo, (size_t)rows * maxn * sizeof(float)));
 		if (!n->dWlo) CU(cudaMalloc(&n->dWlo, (size_t)(n->nw + 4) * sizeof(float)));
+		if (!n->sk.work && !(getenv("GLADES_TC_SPLITK") && atoi(getenv("GLADES_TC_SPLITK")) == 0))
+		{
+			int sms = 0;
+			CU(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, n->d.device));
+			CU(cudaMalloc(&n->sk.work, (size_t)sms * 128 * 256 * sizeof(float)));
+			CU(cudaMalloc(&n->sk.flags, (size_t)sms * 8 * sizeof(unsigned)));
+			CU(cudaMemset(n->sk.flags, 0, (size_t)sms * 8 * sizeof(unsigned)));
+			n->sk.epoch = &n->skEpoch;
+			n->sk.slots = (size_t)sms;
+		}
 	}
 	n->capRows = rows;
 	return 0;
@@ -1087,6 +1101,7 @@ static int run_gemm(gl_net* n, GemmArgs g, Operand a, Operand b, int64_t* launch
 		++*launches;
 		*b.valid = true;
 	}
+	g.sk = n->sk.work ? &n->sk : nullptr;
 	if (pe0) CU(cudaEventRecord(pe0, n->stream));
 	CU(launch_gemm_tc(g, a.lo_use, b.lo_use, n->dFlags + 1, n->stream));
 	if (pe1) CU(cudaEventRecord(pe1, n->stream));
@@ -2572,12 +2587,12 @@ extern "C" int gl_profile_read(gl_net* n, double* out6)
 }
 
 extern "C" int64_t gl_tensor_core_launches(const gl_net* n) { return n ? n->tcLaunches : 0; }
-extern "C" void gl_tc_variant_counts(int64_t* out4)
+extern "C" void gl_tc_variant_counts(int64_t* out5)
 {
-	if (!out4) return;
-	long long c[4];
+	if (!out5) return;
+	long long c[5];
 	tc_variant_counts(c);
-	for (int i = 0; i < 4; ++i) out4[i] = c[i];
+	for (int i = 0; i < 5; ++i) out5[i] = c[i];
 }
 extern "C" int64_t gl_kernel_launches(const gl_net* n) { return n ? n->launches : 0; }
 
@@ -2721,13 +2736,27 @@ extern "C" int gl_matmul(const float* dA, int64_t a_sm, int64_t a_sk, const floa
 	CU(cudaMalloc(&blo, (size_t)(cb + 4) * sizeof(float)));
 	CU(cudaMalloc(&flag, sizeof(int)));
 	CU(cudaMemset(flag, 0, sizeof(int)));
+	// a workspace of its own for the split of a partial wave of tiles along k (GLADES_TC_SPLITK=0: none)
+	TcSplitK sk = {nullptr, nullptr, nullptr, 0};
+	unsigned epoch = 0;
+	if (!(getenv("GLADES_TC_SPLITK") && atoi(getenv("GLADES_TC_SPLITK")) == 0))
+	{
+		int sms = 0;
+		CU(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
+		CU(cudaMalloc(&sk.work, (size_t)sms * 128 * 256 * sizeof(float)));
+		CU(cudaMalloc(&sk.flags, (size_t)sms * 8 * sizeof(unsigned)));
+		CU(cudaMemset(sk.flags, 0, (size_t)sms * 8 * sizeof(unsigned)));
+		sk.epoch = &epoch;
+		sk.slots = (size_t)sms;
+		g.sk = &sk;
+	}
 	cudaError_t e = launch_split_lo(dA, alo, (ca / 4) * 4, 0);
 	if (e == cudaSuccess) e = launch_split_lo(dB, blo, (cb / 4) * 4, 0);
 	if (e == cudaSuccess) e = launch_gemm_tc(g, alo, blo, flag, 0);
 	if (e == cudaSuccess) e = cudaDeviceSynchronize();
 	int hflag = 0;
 	if (e == cudaSuccess) e = cudaMemcpy(&hflag, flag, sizeof hflag, cudaMemcpyDeviceToHost);
-	cudaFree(alo); cudaFree(blo); cudaFree(flag);
+	cudaFree(alo); cudaFree(blo); cudaFree(flag); cudaFree(sk.work); cudaFree(sk.flags);
 	if (e != cudaSuccess) return fail(GL_ERR_CUDA, "gl_matmul: %s", cudaGetErrorString(e));
 	if (hflag) return fail(GL_ERR_TIMEOUT, "gl_matmul: a bounded wait inside the tensor-core kernel ran out (role %d)", hflag);
 	return GL_OK;

@@ -29,8 +29,9 @@ namespace {
 
 // launches per tile variant since the library was loaded (diagnostics for the tests: which instantiation
 // a shape ran on): [0] 128-wide tiles, [1] 256-wide tiles, [2] launches whose CTAs walked more than one
-// tile each, [3] launches of the data-parallel variant that stores into the owners' memory
-std::atomic<long long> g_variant_counts[4];
+// tile each, [3] launches of the data-parallel variant that stores into the owners' memory, [4] launches
+// that split their last wave of tiles along k
+std::atomic<long long> g_variant_counts[5];
 
 // BK = fp32 elements per k-block: 32 (128-byte rows, 128-byte swizzle) or 16 (64-byte rows, 64-byte
 // swizzle).  The shallower block with twice the stages keeps more bytes in flight for the same
@@ -86,7 +87,6 @@ __global__ void __launch_bounds__(TcSmem<BN, BK, STAGES, SBUF>::THREADS, 1)
 	const int warp = threadIdx.x >> 5;
 	const int lane = threadIdx.x & 31;
 	const int KB = p.K / TC_BK;
-	const int NCHUNK = (KB + TC_CHUNK_KB - 1) / TC_CHUNK_KB;
 	// Persistent CTAs: tile t of this CTA is blockIdx.x + i * gridDim.x.  Tiles are numbered m-fastest
 	// inside bands of TC_BAND m-tiles, so that the CTAs running at one time share a band of A rows
 	// and a few B column blocks in L2.  All three roles walk the same sequence; the stage and
@@ -163,13 +163,15 @@ __global__ void __launch_bounds__(TcSmem<BN, BK, STAGES, SBUF>::THREADS, 1)
 	{
 		// ------------------------------------------------ TMA producer
 		int issued = 0;
-		int it = 0;  // k-blocks issued so far, over all tiles
+		int it = 0;  // k-blocks issued so far, over all work items
 		bool ok = true;
-		for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x)
+		TcWork work(blockIdx.x, gridDim.x, KB, total_tiles, p.sk_work ? p.sk_full_tiles : total_tiles);
+		int t, kb0, kb1;
+		while (ok && work.next(t, kb0, kb1))
 		{
 		int m0, n0;
 		tile_origin(t, m0, n0);
-		for (int kb = 0; kb < KB; ++kb, ++it)
+		for (int kb = kb0; kb < kb1; ++kb, ++it)
 		{
 			const int s = it % STAGES;
 			const uint32_t ph = (uint32_t)(it / STAGES) & 1u;
@@ -235,15 +237,16 @@ __global__ void __launch_bounds__(TcSmem<BN, BK, STAGES, SBUF>::THREADS, 1)
 		const uint32_t b_lbo = p.b_mn ? MN_LBO : 0u, b_sbo = p.b_mn ? 512u : K_SBO, b_kstep = p.b_mn ? 1024u : 32u;
 		const uint32_t a_lt = p.a_mn ? 1u : K_LT, b_lt = p.b_mn ? 1u : K_LT;
 		bool ok = true;
-		int it = 0;  // k-blocks consumed so far, over all tiles
-		int gc = 0;  // accumulator chunks started so far, over all tiles
-		for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x)
-		for (int kb = 0; kb < KB && ok; ++kb, ++it)
+		int it = 0;  // k-blocks consumed so far, over all work items
+		int gc = 0;  // accumulator chunks started so far, over all work items
+		TcWork work(blockIdx.x, gridDim.x, KB, total_tiles, p.sk_work ? p.sk_full_tiles : total_tiles);
+		int t, kb0, kb1;
+		while (ok && work.next(t, kb0, kb1))
+		for (int kb = kb0; kb < kb1 && ok; ++kb, ++it)
 		{
 			const int s = it % STAGES;
 			const uint32_t ph = (uint32_t)(it / STAGES) & 1u;
-			const int kin = kb % TC_CHUNK_KB;
-			if (kin == 0 && kb != 0) ++gc;
+			const int kin = (kb - kb0) % TC_CHUNK_KB;  // chunks count from the item's first k-block
 			const int chunk = gc;
 			const int buf = chunk & 1;
 			const uint32_t tmem_d = tmem_base + (uint32_t)(buf * BN);
@@ -280,8 +283,11 @@ __global__ void __launch_bounds__(TcSmem<BN, BK, STAGES, SBUF>::THREADS, 1)
 				umma_tf32(tmem_d, dA, dB, idesc, 1u);
 			}
 			umma_commit(bar0 + 8 * (STAGES + s));  // frees the stage once these MMAs have read it
-			if (kin == TC_CHUNK_KB - 1 || kb == KB - 1) umma_commit(bar_acc_full + 8 * buf);  // chunk complete
-			if (kb == KB - 1) ++gc;  // the next tile starts a new chunk
+			if (kin == TC_CHUNK_KB - 1 || kb == kb1 - 1)
+			{
+				umma_commit(bar_acc_full + 8 * buf);  // chunk complete
+				++gc;
+			}
 		}
 	}
 	else if (warp >= 2)
@@ -291,15 +297,18 @@ __global__ void __launch_bounds__(TcSmem<BN, BK, STAGES, SBUF>::THREADS, 1)
 		const int half = (warp - 2) >> 2;  // which 128 columns of the tile
 		bool ok = true;
 		int piece_turn = 0;
-		int gc = 0;  // accumulator chunks drained so far, over all tiles
-		for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x)
+		int gc = 0;  // accumulator chunks drained so far, over all work items
+		TcWork work(blockIdx.x, gridDim.x, KB, total_tiles, p.sk_work ? p.sk_full_tiles : total_tiles);
+		int t, kb0, kb1;
+		while (ok && work.next(t, kb0, kb1))
 		{
 		int m0, n0;
 		tile_origin(t, m0, n0);
+		const int nchunk = (kb1 - kb0 + TC_CHUNK_KB - 1) / TC_CHUNK_KB;
 		float acc[128];
 #pragma unroll
 		for (int i = 0; i < 128; ++i) acc[i] = 0.0f;
-		for (int c_in = 0; c_in < NCHUNK && ok; ++c_in, ++gc)
+		for (int c_in = 0; c_in < nchunk && ok; ++c_in, ++gc)
 		{
 			const int buf = gc & 1;
 			const uint32_t use = (uint32_t)(gc >> 1);
@@ -322,6 +331,56 @@ __global__ void __launch_bounds__(TcSmem<BN, BK, STAGES, SBUF>::THREADS, 1)
 			asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
 			__syncwarp();
 			if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar_acc_empty + 8 * buf) : "memory");
+		}
+		if (ok && kb0 != 0)
+		{
+			// a partial: the tile's finisher (an earlier CTA) adds it.  Layout of this warp's 32 x 128 block in the
+			// CTA's workspace slot: 32 pieces of 512 bytes, piece v = columns 4v..4v+3 of the 32 rows (one float4
+			// per lane), so every store instruction of the warp writes 512 contiguous bytes.
+			float4* ws = reinterpret_cast<float4*>(p.sk_work + (size_t)blockIdx.x * (TC_BM * BN) + (size_t)(warp - 2) * 4096);
+#pragma unroll
+			for (int v = 0; v < 32; ++v) ws[v * 32 + lane] = make_float4(acc[4 * v], acc[4 * v + 1], acc[4 * v + 2], acc[4 * v + 3]);
+			__threadfence();
+			__syncwarp();
+			if (lane == 0)
+				asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p.sk_flags + (size_t)blockIdx.x * 8 + (warp - 2)), "r"(p.sk_epoch) : "memory");
+			continue;
+		}
+		if (ok && kb1 != KB)
+		{
+			// the tile's finisher: the rest of the tile's k-blocks were computed by the next CTAs as their first
+			// items; add their partials in CTA order
+			const int tile_end = (t - work.full + 1) * KB;
+			for (int j = blockIdx.x + 1; j < (int)gridDim.x && work.share_begin(j) < tile_end && ok; ++j)
+			{
+				if (work.share_begin(j + 1) <= work.share_begin(j)) continue;  // an empty share
+				const unsigned* flag = p.sk_flags + (size_t)j * 8 + (warp - 2);
+				unsigned seen;
+				const long long t0 = clock64();
+				for (;;)
+				{
+					asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(flag) : "memory");
+					if (seen == p.sk_epoch) break;
+					if (*abort_flag || clock64() - t0 > TC_WAIT_CYCLES)
+					{
+						*abort_flag = 1;
+						atomicExch(p.err_flag, 5);
+						ok = false;
+						break;
+					}
+				}
+				if (!ok) break;
+				const float4* ws = reinterpret_cast<const float4*>(p.sk_work + (size_t)j * (TC_BM * BN) + (size_t)(warp - 2) * 4096);
+#pragma unroll
+				for (int v = 0; v < 32; ++v)
+				{
+					const float4 w4 = __ldcg(ws + v * 32 + lane);
+					acc[4 * v] += w4.x;
+					acc[4 * v + 1] += w4.y;
+					acc[4 * v + 2] += w4.z;
+					acc[4 * v + 3] += w4.w;
+				}
+			}
 		}
 		if (ok && !(p.debug & 1))
 		{
@@ -422,7 +481,7 @@ bool make_map(CUtensorMap* m, const float* ptr, int mn, long long R, long long K
 template <int BN, int BK, int STAGES, int SBUF, bool PEER = false>
 cudaError_t launch_cfg(const CUtensorMap& mA, const CUtensorMap& mAl, const CUtensorMap& mB, const CUtensorMap& mBl,
                        const CUtensorMap& mC, const CUtensorMap& mCl, const TcParams& p, int M, int N, int sm_reserve,
-                       cudaStream_t s, const TcPeer& peer = TcPeer())
+                       cudaStream_t s, const TcPeer& peer = TcPeer(), const TcSplitK* sk = nullptr)
 {
 	using S = TcSmem<BN, BK, STAGES, SBUF>;
 	// the shared-memory opt-in and the SM count belong to a device, not to the process
@@ -450,10 +509,29 @@ cudaError_t launch_cfg(const CUtensorMap& mA, const CUtensorMap& mAl, const CUte
 	const int total = q.tiles_m * q.tiles_n;
 	int avail = sm_count - sm_reserve;
 	if (avail < 1) avail = 1;
-	const int grid = total < avail ? total : avail;
+	int grid = total < avail ? total : avail;
+	// Split the last, partial wave of tiles along k over all CTAs where that wave would leave a tenth or more of
+	// the SMs idle (128 tiles on 148 SMs; 32 tiles of a narrow layer) and the caller gave a workspace.
+	q.sk_full_tiles = total;
+	const int KB = p.K / BK;
+	if (q.sk_work && sk && KB >= 8)
+	{
+		const int g2 = avail;
+		const int full = (total / g2) * g2;
+		const int rem = total - full;
+		if (rem > 0 && (g2 - rem) * 10 >= g2 && (long long)rem * KB >= 4ll * g2 && (size_t)g2 <= sk->slots &&
+		    (long long)(g2 + 1) * rem * KB < (1ll << 31))
+		{
+			grid = g2;
+			q.sk_full_tiles = full;
+			q.sk_epoch = ++*sk->epoch;
+		}
+	}
+	if (q.sk_full_tiles == total) q.sk_work = nullptr;
 	g_variant_counts[BN == 256 ? 1 : 0].fetch_add(1, std::memory_order_relaxed);
 	if (total > grid) g_variant_counts[2].fetch_add(1, std::memory_order_relaxed);
 	if (PEER) g_variant_counts[3].fetch_add(1, std::memory_order_relaxed);
+	if (q.sk_work) g_variant_counts[4].fetch_add(1, std::memory_order_relaxed);
 	gemm_tc_kernel<BN, BK, STAGES, SBUF, PEER><<<grid, S::THREADS, S::TOTAL, s>>>(mA, mAl, mB, mBl, mC, mCl, q, peer);
 	return cudaGetLastError();
 }
@@ -485,9 +563,9 @@ __global__ void __launch_bounds__(256) scale_split_lo_kernel(const float* __rest
 
 }  // namespace
 
-void tc_variant_counts(long long out4[4])
+void tc_variant_counts(long long out5[5])
 {
-	for (int i = 0; i < 4; ++i) out4[i] = g_variant_counts[i].load(std::memory_order_relaxed);
+	for (int i = 0; i < 5; ++i) out5[i] = g_variant_counts[i].load(std::memory_order_relaxed);
 }
 
 bool tc_make_store_map(void* out128, const float* base, long long rows, long long cols, long long ld)
@@ -547,7 +625,9 @@ cudaError_t launch_gemm_tc(const GemmArgs& g, const float* A_lo, const float* B_
 	// 256-wide tiles unless they would leave more than half of the SMs without a tile
 	const bool pair = !g.peer_maps && tc_pair_supported(g);
 	const long long wide_tiles = (long long)(g.M / TC_BM) * (g.N / 256);
-	const int BN = (g.N % 256 == 0 && (pair || wide_tiles >= 74)) ? 256 : 128;
+	// (with a split-k workspace a few wide tiles still fill the GPU: their k-blocks are dealt out over all CTAs)
+	const bool can_split = g.sk && g.sk->work && g.K / tc_bk() >= 8;
+	const int BN = (g.N % 256 == 0 && (pair || wide_tiles >= 74 || (can_split && wide_tiles >= 16))) ? 256 : 128;
 	// tile variant: 16-deep k-blocks with twice the stages by default; GLADES_TC_BK=32 selects the
 	// 32-deep blocks (kept for comparison runs)
 	const int bk = tc_bk();
@@ -580,6 +660,11 @@ cudaError_t launch_gemm_tc(const GemmArgs& g, const float* A_lo, const float* B_
 	p.relu_mask_in = g.relu_mask_in;
 	p.mask_ld = g.N / 32;
 	p.err_flag = err_flag;
+	p.sk_work = can_split ? g.sk->work : nullptr;
+	p.sk_flags = can_split ? g.sk->flags : nullptr;
+	p.sk_epoch = 0;
+	p.sk_full_tiles = 0;
+	const TcSplitK* sk = can_split ? g.sk : nullptr;
 	TcPeer peer;
 	peer.maps = reinterpret_cast<const CUtensorMap*>(g.peer_maps);
 	peer.bases = g.peer_bases;
@@ -603,8 +688,8 @@ cudaError_t launch_gemm_tc(const GemmArgs& g, const float* A_lo, const float* B_
 	if (g.peer_maps)
 	{
 		if (g.epi != EPI_GRAD) return cudaErrorInvalidValue;
-		if (BN == 256) return launch_cfg<256, 16, 4, 1, true>(mA, mAl, mB, mBl, mC, mCl, p, g.M, g.N, g.sm_reserve, s, peer);
-		return launch_cfg<128, 16, 6, 2, true>(mA, mAl, mB, mBl, mC, mCl, p, g.M, g.N, g.sm_reserve, s, peer);
+		if (BN == 256) return launch_cfg<256, 16, 4, 1, true>(mA, mAl, mB, mBl, mC, mCl, p, g.M, g.N, g.sm_reserve, s, peer, sk);
+		return launch_cfg<128, 16, 6, 2, true>(mA, mAl, mB, mBl, mC, mCl, p, g.M, g.N, g.sm_reserve, s, peer, sk);
 	}
 	if (bk == 32)
 	{
@@ -621,9 +706,9 @@ cudaError_t launch_gemm_tc(const GemmArgs& g, const float* A_lo, const float* B_
 			st = (e && atoi(e) == 3) ? 3 : 4;
 		}
 		if (st == 3) return launch_cfg<256, 16, 3, 2>(mA, mAl, mB, mBl, mC, mCl, p, g.M, g.N, g.sm_reserve, s);
-		return launch_cfg<256, 16, 4, 1>(mA, mAl, mB, mBl, mC, mCl, p, g.M, g.N, g.sm_reserve, s);
+		return launch_cfg<256, 16, 4, 1>(mA, mAl, mB, mBl, mC, mCl, p, g.M, g.N, g.sm_reserve, s, TcPeer(), sk);
 	}
-	return launch_cfg<128, 16, 6, 2>(mA, mAl, mB, mBl, mC, mCl, p, g.M, g.N, g.sm_reserve, s);
+	return launch_cfg<128, 16, 6, 2>(mA, mAl, mB, mBl, mC, mCl, p, g.M, g.N, g.sm_reserve, s, TcPeer(), sk);
 }
 
 cudaError_t launch_split_lo(const float* src, float* lo, long long count, cudaStream_t s)

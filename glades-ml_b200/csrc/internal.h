@@ -66,6 +66,16 @@ cudaError_t launch_ref_metrics(const NetView& n, const float* P, const float* Y,
 
 // ---- batched mode (batched.cu) ---------------------------------------------------------------
 enum { EPI_NONE = 0, EPI_FORWARD = 1, EPI_ERRPROP = 2, EPI_GRAD = 3 };
+// Workspace of the tensor-core kernel's split of a partial wave of tiles along k: one 128 x 256 fp32 partial
+// tile and eight flag words per CTA, and the host-side launch counter the flags are compared with.  One
+// workspace serves the launches of ONE stream (consecutive launches reuse it; the flags only ever grow).
+struct TcSplitK
+{
+	float* work;       // device, slots * 128 * 256 floats
+	unsigned* flags;   // device, slots * 8 words, zero-initialised
+	unsigned* epoch;   // host counter
+	size_t slots;      // CTAs the workspace has room for
+};
 struct GemmArgs
 {
 	// C[M][N] (ldc) = sum_k A(m,k) * B(n,k);  A(m,k) = A[m*a_sm + k*a_sk], B(n,k) = B[n*b_sn + k*b_sk]
@@ -97,6 +107,7 @@ struct GemmArgs
 	float* const* peer_bases;
 	int band_rows;
 	int peer_self;         // this rank (the walk over the owners' bands starts with the rank after it)
+	const TcSplitK* sk;    // tensor-core kernel: workspace for splitting a partial wave of tiles along k, or NULL
 };
 cudaError_t launch_gemm_ffma(const GemmArgs& g, cudaStream_t s);
 

@@ -36,6 +36,56 @@ struct TcParams
 	int mask_ld;           // words per row of the ReLU masks (= N / 32)
 	int debug;             // experiments only: bit 0 skips the global stores of the epilogue
 	int tiles_m, tiles_n;  // the CTAs walk the tiles_m * tiles_n output tiles persistently
+	// Split of the last, partial wave of tiles along k ("stream-K", see TcWork): the first sk_full_tiles tiles
+	// are whole-tile work items; the k-blocks of the remaining tiles are dealt out evenly over the CTAs.
+	// sk_work == NULL: every tile is a whole-tile item.
+	float* sk_work;        // [grid][128 x BN] fp32: a CTA's partial tile, if it has one
+	unsigned* sk_flags;    // [grid][8]: launch number, per epilogue warp, once that warp's part of the partial is stored
+	unsigned sk_epoch;     // this launch's number (flags only ever grow)
+	int sk_full_tiles;
+};
+
+// The work items of one CTA, the same sequence for the producer, the MMA lane and the epilogue warps.
+// First the whole tiles t = cta, cta + grid, ... below sk_full_tiles.  Then the CTA's share of the remaining
+// tiles' k-blocks: with R tiles of KB k-blocks left, CTA c owns the units [c * R * KB / grid, (c + 1) * R * KB / grid)
+// of the sequence (tile 0 k-block 0, tile 0 k-block 1, ..., tile R - 1 k-block KB - 1) -- at most the tail of one tile
+// (a PARTIAL: its accumulators go to the CTA's workspace slot), whole tiles, and the head of one more tile (the
+// tile's FINISHER: it adds the partials of the CTAs that hold the rest of the tile, in CTA order, and runs the
+// epilogue).  A CTA computes its partial first and finishes a tile last, so a finisher rarely waits.  The split
+// depends only on the shape and the grid, and the partials are added in a fixed order: results are reproducible.
+struct TcWork
+{
+	// (ints: the launch only splits when grid * units fits 31 bits)
+	int grid, KB, full, units;
+	int u, u1;  // units of the split region still to do: [u, u1)
+	int t;      // next whole tile of the first phase
+	__device__ TcWork(int cta, int grid_, int KB_, int total, int full_)
+	    : grid(grid_), KB(KB_), full(full_), units((total - full_) * KB_), t(cta)
+	{
+		u = share_begin(cta);
+		u1 = share_begin(cta + 1);
+	}
+	// tile, k-block range [kb0, kb1) of the next item; false when the CTA is done
+	__device__ bool next(int& tile, int& kb0, int& kb1)
+	{
+		if (t < full)
+		{
+			tile = t;
+			kb0 = 0;
+			kb1 = KB;
+			t += grid;
+			return true;
+		}
+		if (u >= u1) return false;
+		const int tr = u / KB;
+		tile = full + tr;
+		kb0 = u - tr * KB;
+		kb1 = min(KB, kb0 + (u1 - u));
+		u += kb1 - kb0;
+		return true;
+	}
+	// first unit of CTA j's share
+	__device__ int share_begin(int j) const { return (int)(((unsigned)j * (unsigned)units) / (unsigned)grid); }
 };
 
 // Data-parallel weight gradient: rows [o * band_rows, (o + 1) * band_rows) of C belong to rank o and

@@ -19,8 +19,9 @@ bool tc_gemm_supported(const GemmArgs& g);
 cudaError_t launch_gemm_tc(const GemmArgs& g, const float* A_lo, const float* B_lo, int* err_flag, cudaStream_t s);
 
 // Launch counts per tile variant since the library was loaded: [0] 128-wide tiles, [1] 256-wide tiles,
-// [2] launches whose persistent CTAs walked more than one tile each, [3] data-parallel (peer-store) launches.
-void tc_variant_counts(long long out4[4]);
+// [2] launches whose persistent CTAs walked more than one tile each, [3] data-parallel (peer-store) launches,
+// [4] launches that split their last wave of tiles along k.
+void tc_variant_counts(long long out5[5]);
 
 // Tensor map (128 bytes, 64-byte aligned storage) over a row-major [rows][cols] fp32 matrix with 32 x 32
 // boxes, as the epilogue's bulk stores use it; for the per-owner bands of a data-parallel gradient.

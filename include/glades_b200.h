@@ -229,11 +229,12 @@ int gl_selftest_bounded_wait(gl_net* net, int64_t max_cycles, double* waited_ms)
  * (tcgen05) products.  No counterpart in the reference. */
 int64_t gl_kernel_launches(const gl_net* net);
 int64_t gl_tensor_core_launches(const gl_net* net);
-/* Diagnostics: tensor-core product launches of this process per tile variant -- out4[0] 128-wide
+/* Diagnostics: tensor-core product launches of this process per tile variant -- out5[0] 128-wide
  * tiles, [1] 256-wide tiles, [2] launches whose persistent CTAs walked more than one tile each,
- * [3] launches of the data-parallel variant whose epilogue stores into the owning rank's memory.
+ * [3] launches of the data-parallel variant whose epilogue stores into the owning rank's memory,
+ * [4] launches that split their last, partial wave of tiles along k over all CTAs.
  * Lets a test assert which instantiation a shape ran on.  No counterpart in the reference. */
-void gl_tc_variant_counts(int64_t* out4);
+void gl_tc_variant_counts(int64_t* out5);
 /* Diagnostic matrix product on device buffers, C[m][n] = sum_k A(m,k)*B(n,k) with
  * A(m,k) = d_a[m*a_sm + k*a_sk] and B(n,k) = d_b[n*b_sn + k*b_sk]; engine GL_GEMM_FFMA or
  * GL_GEMM_TCGEN05 (M % 128 == 0, N % 128 == 0, K % 16 == 0, each operand contiguous in k or in

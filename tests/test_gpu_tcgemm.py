@@ -102,8 +102,33 @@ def test_tc_matmul_wide_persistent_variant(g, M, N, K, a_mn, b_mn, positive):
     assert err <= 4e-6, "error %.3g of sum|a||b|" % err
     tiles = (M // 128) * (N // 256)
     assert dc[1] == 1 and dc[0] == 0, "the 256-wide instantiation did not run: %r" % (dc,)
+    assert len(dc) == 5
     if tiles > 148:
         assert dc[2] == 1, "%d tiles but no CTA walked more than one" % tiles
+
+
+# Shapes whose last wave of tiles would leave a tenth or more of the SMs idle: the kernel deals the k-blocks of
+# those tiles out over all CTAs, a CTA that holds the tail of a tile stores its partial accumulators and the CTA
+# that holds the head adds the partials in a fixed order and runs the epilogue.  (M, N, K, A MN-major, B MN-major)
+SPLIT_CASES = [
+    (1024, 4096, 1024, 0, 0),   # 128 wide tiles on 148 SMs: every CTA gets 0.86 of a tile
+    (1024, 4096, 1024, 1, 1),   # the same as a weight-gradient product
+    (1024, 1024, 4096, 0, 0),   # 32 wide tiles, deep k: a tile is shared by four or five CTAs
+    (1024, 1024, 4096, 0, 1),
+    (4096, 4096, 1024, 1, 1),   # 512 tiles: three whole waves, then 68 tiles split
+    (1024, 2048, 272, 0, 0),    # 64 wide tiles, 17 k-blocks each: shares that end inside a chunk of 8 k-blocks
+    (2048, 1152, 784, 0, 0),    # 128-wide tiles (1152 is no multiple of 256): 144 tiles, 49 k-blocks
+]
+
+
+@pytest.mark.parametrize("M,N,K,a_mn,b_mn", SPLIT_CASES)
+def test_tc_matmul_split_last_wave(g, M, N, K, a_mn, b_mn):
+    err, dc = _matmul_case(g, M, N, K, a_mn, b_mn, seed=5 * M + 3 * N + K + a_mn + 2 * b_mn)
+    assert err <= 4e-6, "error %.3g of sum|a||b|" % err
+    assert dc[4] == 1, "the last wave was not split along k: %r" % (dc,)
+    # all-positive operands: partial sums of one sign, the worst case for a lost or doubled partial
+    err, dc = _matmul_case(g, M, N, K, a_mn, b_mn, seed=7, positive=True)
+    assert err <= 4e-6 and dc[4] == 1
 
 
 def test_tc_matmul_rejects_odd_shapes(g):
