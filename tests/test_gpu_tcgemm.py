@@ -117,7 +117,7 @@ SPLIT_CASES = [
     (1024, 1024, 4096, 0, 1),
     (4096, 4096, 1024, 1, 1),   # 512 tiles: three whole waves, then 68 tiles split
     (1024, 2048, 272, 0, 0),    # 64 wide tiles, 17 k-blocks each: shares that end inside a chunk of 8 k-blocks
-    (2048, 1152, 784, 0, 0),    # 128-wide tiles (1152 is no multiple of 256): 144 tiles, 49 k-blocks
+    (1792, 1152, 784, 0, 0),    # 128-wide tiles (1152 is no multiple of 256): 126 tiles, 49 k-blocks
 ]
 
 
