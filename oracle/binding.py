@@ -55,6 +55,7 @@ def restate_lib():
         L.rs_window_grad.argtypes = [vp, i64, i32, i32, i32, vp, vp, i64]
         L.rs_window_apply.argtypes = [vp, vp, i32]
         L.rs_set_math_mode.argtypes = [i32]
+        L.rs_window_step_fast.argtypes = [vp, i64, i32, vp]
         L.rs_standardize_table.argtypes = [vp, i64, i32, vp, vp, vp, i32, vp, i32, vp, i32]
         L.rs_set_threads.argtypes = [i32]
         L.rs_get_threads.restype = i32
@@ -195,6 +196,13 @@ class Restate(_Base):
         g = self.window_grad(first, cnt)
         self.window_apply(g, cnt)
         return g
+
+    def train_window_fast(self, first, cnt):
+        """The same window step with blocked fp32 products on all host cores (fastport.c): the timed CPU
+        baseline, not the checker.  Returns the window's cost sum."""
+        cost = C.c_float()
+        self.L.rs_window_step_fast(self.h, first, cnt, C.byref(cost))
+        return cost.value
 
 
 class Reference(_Base):

@@ -52,6 +52,13 @@ typedef struct rs_net {
 	float* hlast[GL_MAX_WEIGHT_LAYERS];            /* the last pushed entry (the momentum term reads it) */
 } rs_net;
 
+/* accessors for fastport.c (the timed CPU baseline), which works on the same network object */
+const gl_net_desc* rs_desc(const rs_net* n) { return &n->d; }
+float* rs_weights(rs_net* n, int l) { return n->w[l]; }
+float* rs_biases(rs_net* n) { return n->bias; }
+const float* rs_x(const rs_net* n) { return n->x; }
+const float* rs_y(const rs_net* n) { return n->y; }
+
 static int g_math_mode = 0;
 void rs_set_math_mode(int m) { g_math_mode = m; }
 

@@ -205,3 +205,33 @@ def test_restatement_standardize_vs_golden(oracle):
                                         z["y%d" % k].shape[1])
         assert np.array_equal(bits(x), bits(z["x%d" % k])), "case %d inputs" % k
         assert np.array_equal(bits(y), bits(z["y%d" % k])), "case %d expected" % k
+
+
+def test_fast_cpu_port_matches_restatement(g, oracle):
+    """The timed CPU baseline (oracle/fastport.c: blocked fp32 products) against the double-accumulating
+    restatement on one window: momentum, decay, both heads, odd sizes that do not fill the register tiles."""
+    rng = np.random.default_rng(31)
+    cases = [([12, 20, 9, 4], ["tanh", "relu", "softmax"], "classification", 37, 0.6, 0.0, 0),
+             ([33, 40, 17, 5], ["relu", "leaky", "sigmoid"], "regression", 50, 0.0, 0.001, 0),
+             ([70, 130, 3], ["sigmoid", "sigmoid"], "classification", 300, 0.3, 0.0, 1)]
+    for sizes, acts, out, rows, mom, wd, brule in cases:
+        x = rng.standard_normal((rows, sizes[0])).astype(np.float32)
+        if acts[-1] == "softmax":
+            y = np.zeros((rows, sizes[-1]), np.float32)
+            y[np.arange(rows), rng.integers(0, sizes[-1], rows)] = 1.0
+        else:
+            y = rng.uniform(0.1, 0.9, (rows, sizes[-1])).astype(np.float32)
+        d = g.make_desc(sizes, acts, out, batch=rows, lr=0.005 if brule else 0.05, momentum=mom, wd1=wd, wd2=wd,
+                        params=[0.05] * (len(sizes) - 1), mode=g.MODE_BATCHED, bias_rule=brule)
+        w = rng.uniform(-0.3, 0.3, g.weight_count(d)).astype(np.float32)
+        b = rng.uniform(-0.1, 0.1, len(sizes) - 2).astype(np.float32)
+        A = oracle.Restate(d, x, y, g.Metrics)
+        A.set_weights(w, b)
+        gr = A.train_window(0, rows)
+        B = oracle.Restate(d, x, y, g.Metrics)
+        B.set_weights(w, b)
+        cost = B.train_window_fast(0, rows)
+        wa, ba = A.get_weights()
+        wb, bb = B.get_weights()
+        assert np.max(np.abs(wa - wb)) <= 1e-5 * np.max(np.abs(wa)), sizes
+        assert np.allclose(ba, bb, rtol=1e-4, atol=1e-6) and abs(cost - gr[-2]) <= 1e-5 * max(1.0, abs(gr[-2]))
