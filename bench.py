@@ -514,13 +514,96 @@ def run_small(args, g, name):
         net.close()
 
 
+def run_standardize(args, g):
+    """The step in front of the loop: standardisation of a raw table that lies in HBM (gl_standardize_table).
+    One step = one 1 M x 33 table (the window regressor's data set: 32 inputs and the target, 138 MB, larger than
+    L2), min-max scaling.  value = rows/s resident; e2e = the same from a pinned host table, copy in and
+    standardised matrices back out included.  HBM roofline: algorithmic bytes = the table read once and the
+    standardised matrices written once (the kernels read the table twice: extrema, then transform)."""
+    o = ge.import_oracle()
+    L = g.lib()
+    rows, cols = 1 << 20, 33
+    kind = np.zeros(cols, np.int32)
+    classes = np.zeros(cols, np.int32)
+    outs = np.zeros(cols, np.int32)
+    outs[-1] = 1
+    d_raw = dev_alloc(L, rows * cols * 4, 0)
+    assert L.gl_synth_fill(d_raw, rows * cols, SEED + 9, 0, 1, 4.0, 0.0, 0) == 0
+    nx, ny = C.c_int32(), C.c_int32()
+    ptrs = (kind.ctypes.data_as(C.c_void_p), classes.ctypes.data_as(C.c_void_p), outs.ctypes.data_as(C.c_void_p))
+    assert L.gl_standardize_table(d_raw, rows, cols, *ptrs, 0, None, C.byref(nx), None, C.byref(ny), None, 0) == 0
+    d_x = dev_alloc(L, rows * nx.value * 4, 0)
+    d_y = dev_alloc(L, rows * ny.value * 4, 0)
+    import torch
+    sampler = ClockSampler(0)
+    times = []
+    for i in range(args.warmup + args.steps):
+        if i == args.warmup:
+            sampler.start()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        ev0.record()   # the entry point works on the legacy default stream, which torch's current stream is
+        st = L.gl_standardize_table(d_raw, rows, cols, *ptrs, 0, d_x, C.byref(nx), d_y, C.byref(ny), None, 0)
+        ev1.record()
+        torch.cuda.synchronize()
+        assert st == 0, L.gl_last_error()
+        if i >= args.warmup:
+            times.append(ev0.elapsed_time(ev1) / 1000.0)
+    clocks = sampler.stop()
+    # end to end: pinned host table in, standardised matrices out
+    h_raw, h_x, h_y = C.c_void_p(), C.c_void_p(), C.c_void_p()
+    assert L.gl_host_alloc_pinned(C.byref(h_raw), rows * cols * 4) == 0
+    assert L.gl_host_alloc_pinned(C.byref(h_x), rows * nx.value * 4) == 0
+    assert L.gl_host_alloc_pinned(C.byref(h_y), rows * ny.value * 4) == 0
+    L.gl_memcpy_d2h(h_raw, d_raw, rows * cols * 4, 0)
+    e2e = []
+    for i in range(3 + min(args.steps, 10)):
+        t0 = time.perf_counter()
+        L.gl_memcpy_h2d(d_raw, h_raw, rows * cols * 4, 0)
+        assert L.gl_standardize_table(d_raw, rows, cols, *ptrs, 0, d_x, C.byref(nx), d_y, C.byref(ny), None, 0) == 0
+        L.gl_memcpy_d2h(h_x, d_x, rows * nx.value * 4, 0)
+        L.gl_memcpy_d2h(h_y, d_y, rows * ny.value * 4, 0)
+        if i >= 3:
+            e2e.append(time.perf_counter() - t0)
+    peaks = measured_peaks()
+    t = float(np.mean(times))
+    alg_bytes = rows * cols * 4 + rows * (nx.value + ny.value) * 4
+    cpu = None
+    if not args.no_cpu_baseline:
+        sample = 1 << 17
+        raw = o.synth_fill(sample * cols, SEED + 9, 0, 1, 4.0, 0.0).reshape(sample, cols)
+        t0 = time.perf_counter()
+        o.standardize_table(raw, [0] * cols, list(outs), 0, nx.value, ny.value)
+        dt = time.perf_counter() - t0
+        cpu = {"value": sample / dt, "unit": "rows/s", "cores": 1, "kind": "port",
+               "sample": "%d rows x %d columns, C restatement of NumberInput::standardizeInputTable (pinned bit for bit to the "
+                         "reference's code), %.2f s" % (sample, cols, dt)}
+    line = {
+        "metric": "standardize_rows_per_s", "value": rows / t, "unit": "rows/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": 1000.0 * t, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "standardize", "rows": rows, "cols": cols, "flag": "minmax",
+                   "l2": "inputs larger than L2: a 138 MB table is read and 138 MB of matrices are written per step"},
+        "e2e": {"value": rows / float(np.mean(e2e)), "unit": "rows/s", "h2d_bytes_per_step": rows * cols * 4,
+                "d2h_bytes_per_step": rows * (nx.value + ny.value) * 4},
+        "gpu_launches": 2 * args.steps, "clocks": clocks,
+        "roofline": {"bound": "hbm", "kernel": "minmax_kernel + transform_kernel (one call)", "achieved": alg_bytes / t / 1e9,
+                     "peak": peaks["hbm"], "unit": "GB/s", "frac": alg_bytes / t / 1e9 / peaks["hbm"], "traffic": None,
+                     "peak_source": peaks["source"] + " copy bandwidth",
+                     "note": "the call also allocates and frees its 528-byte statistics buffer and reads the extrema back "
+                             "to the host between the two kernels (the layout depends on them)"},
+        "cpu_baseline": cpu,
+    }
+    print(json.dumps(line), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="wide_mlp", choices=sorted(WORKLOADS) + sorted(SMALL))
+    ap.add_argument("--workload", default="wide_mlp", choices=sorted(WORKLOADS) + sorted(SMALL) + ["standardize"])
     ap.add_argument("--windows", type=int, default=0, help="resident windows per GPU (default: steps+warmup, max 64)")
     ap.add_argument("--gemm", default="auto", choices=["auto", "ffma", "tcgen05"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -531,6 +614,10 @@ def main():
 
     rank, world, local = dist_env()
     g = ge.import_package()
+    if args.workload == "standardize":
+        if rank == 0 and args.impl == "ours":
+            run_standardize(args, g)
+        return
     if args.workload in SMALL:
         if rank == 0 and args.impl == "ours":
             run_small(args, g, args.workload)
