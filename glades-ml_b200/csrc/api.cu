@@ -12,6 +12,7 @@
 #include <stdlib.h>
 #include <string.h>
 
+#include <mutex>
 #include <string>
 #include <vector>
 
@@ -1631,6 +1632,10 @@ static int batched_window(gl_net* n, const float* X, const float* Y, int rows, i
 		tr.mark("window done", -1, n->stream);
 		launches += 3;
 		n->loW = lo_all && n->dWlo != nullptr;
+		// a network with a layer whose low parts cannot be split per layer refreshes them as a whole before its
+		// next tensor-core product, which reads every layer's weights: all layers must have landed by then
+		if (!lo_all)
+			if (int r = dp_join(n)) return r;
 	}
 	else
 	{
@@ -2802,6 +2807,21 @@ extern "C" int gl_onehot_fill(float* d_y, const int32_t* labels, int64_t rows, i
 }
 
 // ---- input standardisation ---------------------------------------------------------------------
+// Per-device scratch of gl_standardize_table (column statistics, kinds, plan: 36 bytes per column), kept between
+// calls: a call then costs two kernels and one small read-back, not three allocations.  One call at a time per
+// device (the mutex); the buffers grow with the widest table seen and live until the process ends.
+namespace {
+struct StdScratch
+{
+	int* stats = nullptr;
+	int* kind = nullptr;
+	void* plan = nullptr;
+	int cap = 0;
+};
+StdScratch g_stdScratch[64];
+std::mutex g_stdMutex[64];
+}  // namespace
+
 extern "C" int gl_standardize_table(const float* d_raw, int64_t rows, int32_t cols, const int32_t* kind, const int32_t* classes,
                                     const int32_t* to_output, int32_t flag, float* d_x, int32_t* nx, float* d_y, int32_t* ny,
                                     float* stats_out, int32_t device)
@@ -2828,16 +2848,28 @@ extern "C" int gl_standardize_table(const float* d_raw, int64_t rows, int32_t co
 		st[4 * (size_t)c] = (c == 0) ? 0x7FFFFFFF : float_order_host(0.0f);
 		st[4 * (size_t)c + 1] = (c == 0) ? (int)0x80000000 : float_order_host(0.0f);
 	}
-	int* dStats = nullptr;
-	int* dKind = nullptr;
-	void* dPlan = nullptr;
-	CU(cudaMalloc(&dStats, st.size() * sizeof(int)));
+	if (device < 0 || device >= 64) return fail(GL_ERR_INVALID, "gl_standardize_table: device ordinal out of range");
+	std::lock_guard<std::mutex> lock(g_stdMutex[device]);
+	StdScratch& sc = g_stdScratch[device];
+	if (sc.cap < cols)
+	{
+		cudaFree(sc.stats);
+		cudaFree(sc.kind);
+		cudaFree(sc.plan);
+		sc = StdScratch();
+		CU(cudaMalloc(&sc.stats, (size_t)cols * 4 * sizeof(int)));
+		CU(cudaMalloc(&sc.kind, (size_t)cols * sizeof(int)));
+		CU(cudaMalloc(&sc.plan, (size_t)cols * 4 * sizeof(int)));
+		sc.cap = cols;
+	}
+	int* dStats = sc.stats;
+	int* dKind = sc.kind;
+	void* dPlan = sc.plan;
 	cudaError_t e = cudaMemcpy(dStats, st.data(), st.size() * sizeof(int), cudaMemcpyHostToDevice);
 	if (e == cudaSuccess) e = launch_column_minmax(d_raw, rows, cols, dStats, 0);
 	if (e == cudaSuccess && flag == 1)
 	{
-		e = cudaMalloc(&dKind, (size_t)cols * sizeof(int));
-		if (e == cudaSuccess) e = cudaMemcpy(dKind, kind, (size_t)cols * sizeof(int), cudaMemcpyHostToDevice);
+		e = cudaMemcpy(dKind, kind, (size_t)cols * sizeof(int), cudaMemcpyHostToDevice);
 		if (e == cudaSuccess) e = launch_column_mean_stdev(d_raw, rows, cols, dKind, reinterpret_cast<float*>(dStats), 0);
 	}
 	if (e == cudaSuccess) e = cudaMemcpy(st.data(), dStats, st.size() * sizeof(int), cudaMemcpyDeviceToHost);
@@ -2866,15 +2898,11 @@ extern "C" int gl_standardize_table(const float* d_raw, int64_t rows, int32_t co
 			              cx, cy, *nx, *ny);
 		else
 		{
-			e = cudaMalloc(&dPlan, plan.size() * sizeof(int));
-			if (e == cudaSuccess) e = cudaMemcpy(dPlan, plan.data(), plan.size() * sizeof(int), cudaMemcpyHostToDevice);
+			e = cudaMemcpy(dPlan, plan.data(), plan.size() * sizeof(int), cudaMemcpyHostToDevice);
 			if (e == cudaSuccess) e = launch_column_transform(d_raw, rows, cols, dPlan, dStats, flag, classification, d_x, cx, d_y, cy, 0);
-			if (e == cudaSuccess) e = cudaDeviceSynchronize();
+			if (e == cudaSuccess) e = cudaStreamSynchronize(0);
 		}
 	}
-	cudaFree(dStats);
-	cudaFree(dKind);
-	cudaFree(dPlan);
 	if (e != cudaSuccess) return fail(GL_ERR_CUDA, "gl_standardize_table: %s", cudaGetErrorString(e));
 	if (status != GL_OK) return status;
 	*nx = cx;

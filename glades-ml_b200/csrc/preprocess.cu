@@ -34,16 +34,22 @@ __device__ __forceinline__ int float_order(float f)
 __device__ __forceinline__ float order_float(int i) { return __int_as_float(i >= 0 ? i : i ^ 0x7FFFFFFF); }
 
 // stats: [cols][4] = min image, max image (ints, pre-set by the host to the images of the start values),
-// mean, stdev
+// mean, stdev.  Thread t of the grid handles column t % cols of every (grid size / cols)-th row: the grid size
+// is a multiple of cols, so a thread stays on one column (extrema in registers, no division in the loop) while
+// consecutive threads read consecutive addresses.  A block merges its threads' extrema in shared memory and
+// issues one global atomic per column it touched.
 __global__ void __launch_bounds__(256) minmax_kernel(const float* __restrict__ raw, long long rows, int cols, int* stats)
 {
-	// thread t handles column t % cols of rows t / cols + k * rows_per_pass: consecutive threads read
-	// consecutive addresses
+	extern __shared__ int sext[];  // [2][cols]: images of the block's minimum and maximum per column
+	for (int c = threadIdx.x; c < cols; c += blockDim.x)
+	{
+		sext[c] = 0x7FFFFFFF;
+		sext[cols + c] = (int)0x80000000;
+	}
+	__syncthreads();
 	const long long total = rows * (long long)cols;
 	const long long stride = (long long)gridDim.x * blockDim.x;
 	const long long start = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-	// when the stride is a multiple of cols every thread stays on one column and can keep its extrema in
-	// registers; the launch rounds the grid so that this holds
 	const int c = (int)(start % cols);
 	float mn = __int_as_float(0x7F800000), mx = __int_as_float(0xFF800000);
 	bool any = false;
@@ -56,8 +62,14 @@ __global__ void __launch_bounds__(256) minmax_kernel(const float* __restrict__ r
 	}
 	if (any)
 	{
-		atomicMin(stats + 4 * c, float_order(mn));
-		atomicMax(stats + 4 * c + 1, float_order(mx));
+		atomicMin(sext + c, float_order(mn));
+		atomicMax(sext + cols + c, float_order(mx));
+	}
+	__syncthreads();
+	for (int k = threadIdx.x; k < cols; k += blockDim.x)
+	{
+		if (sext[k] != 0x7FFFFFFF) atomicMin(stats + 4 * k, sext[k]);
+		if (sext[cols + k] != (int)0x80000000) atomicMax(stats + 4 * k + 1, sext[cols + k]);
 	}
 }
 
@@ -89,6 +101,8 @@ struct ColumnPlan
 	int at;       // first destination column
 };
 
+// The same geometry as minmax_kernel: a thread stays on one raw column, so its plan record and scale factors
+// are loaded once; the row advances by (grid size / cols) per iteration.
 __global__ void __launch_bounds__(256) transform_kernel(const float* __restrict__ raw, long long rows, int cols,
                                                          const ColumnPlan* __restrict__ plan, const int* __restrict__ stats,
                                                          int flag, int classification, float* __restrict__ X, int ldx,
@@ -96,23 +110,29 @@ __global__ void __launch_bounds__(256) transform_kernel(const float* __restrict_
 {
 	const long long total = rows * (long long)cols;
 	const long long stride = (long long)gridDim.x * blockDim.x;
-	for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride)
+	const long long start = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+	if (start >= total) return;
+	const int c = (int)(start % cols);
+	long long r = start / cols;
+	const long long rstep = stride / cols;
+	const ColumnPlan p = plan[c];
+	float* const base = p.dst ? Y : X;
+	const long long ld = p.dst ? ldy : ldx;
+	const float mn = order_float(stats[4 * c]), mx = order_float(stats[4 * c + 1]);
+	const float range = __fsub_rn(mx, mn);
+	const float mean = __int_as_float(stats[4 * c + 2]), sd = __int_as_float(stats[4 * c + 3]);
+	for (long long i = start; i < total; i += stride, r += rstep)
 	{
-		const long long r = i / cols;
-		const int c = (int)(i - r * cols);
-		const ColumnPlan p = plan[c];
-		float* dst = p.dst ? Y + r * ldy : X + r * ldx;
+		float* dst = base + r * ld + p.at;
 		float v = raw[i];
 		if (p.kind == 1)
 		{
 			const int id = (int)v;
-			for (int k = 0; k < p.classes; ++k) dst[p.at + k] = (k == id) ? 0.99f : 0.01f;
+			for (int k = 0; k < p.classes; ++k) dst[k] = (k == id) ? 0.99f : 0.01f;
 			continue;
 		}
 		if (flag == 0)
 		{
-			const float mn = order_float(stats[4 * c]), mx = order_float(stats[4 * c + 1]);
-			const float range = __fsub_rn(mx, mn);
 			if (range != 0.0f)
 			{
 				v = __fdiv_rn(__fsub_rn(v, mn), range);
@@ -120,8 +140,8 @@ __global__ void __launch_bounds__(256) transform_kernel(const float* __restrict_
 			}
 		}
 		else
-			v = __fdiv_rn(__fsub_rn(v, __int_as_float(stats[4 * c + 2])), __int_as_float(stats[4 * c + 3]));
-		dst[p.at] = v;
+			v = __fdiv_rn(__fsub_rn(v, mean), sd);
+		*dst = v;
 	}
 }
 
@@ -129,20 +149,24 @@ __global__ void __launch_bounds__(256) transform_kernel(const float* __restrict_
 
 // d_stats: device [cols][4] ints, already holding the order images of every column's start values for the
 // minimum and the maximum.  d_plan: device array of `cols` ColumnPlan records (four ints each).
+// blocks of 256 threads for a pass over rows * cols cells: about eight cells per thread, at most 16 blocks per SM,
+// and a multiple of cols, so that the grid size is a multiple of cols (a thread then stays on one column)
+static unsigned column_pass_blocks(long long total, int cols)
+{
+	long long blocks = (total / 8 + 255) / 256;
+	const long long cap = 148ll * 16;
+	if (blocks > cap) blocks = cap;
+	if (blocks < 1) blocks = 1;
+	blocks = ((blocks + cols - 1) / cols) * cols;
+	return (unsigned)blocks;
+}
+
 cudaError_t launch_column_minmax(const float* raw, long long rows, int cols, int* d_stats, cudaStream_t s)
 {
 	const long long total = rows * (long long)cols;
 	if (total < 1) return cudaSuccess;
-	// grid * 256 must be a multiple of cols so that each thread keeps to one column
-	long long threads = (total + 3) / 4;  // about four cells per thread
-	const long long cap = 148ll * 8 * 256;
-	if (threads > cap) threads = cap;
-	long long per = 256ll * cols;  // lcm(256, cols) divides this
-	long long grid_threads = ((threads + per - 1) / per) * per;
-	long long blocks = grid_threads / 256;
-	if (blocks < cols) blocks = cols;  // still a multiple of cols: grid * 256 = cols * 256 * k
-	blocks = ((blocks + cols - 1) / cols) * cols;
-	minmax_kernel<<<(unsigned)blocks, 256, 0, s>>>(raw, rows, cols, d_stats);
+	if (cols > 6000) return cudaErrorInvalidValue;  // the block's extrema live in shared memory
+	minmax_kernel<<<column_pass_blocks(total, cols), 256, (size_t)2 * cols * sizeof(int), s>>>(raw, rows, cols, d_stats);
 	return cudaGetLastError();
 }
 
@@ -157,9 +181,7 @@ cudaError_t launch_column_transform(const float* raw, long long rows, int cols, 
 {
 	const long long total = rows * (long long)cols;
 	if (total < 1) return cudaSuccess;
-	long long blocks = (total + 255) / 256;
-	if (blocks > 148 * 16) blocks = 148 * 16;
-	transform_kernel<<<(unsigned)blocks, 256, 0, s>>>(raw, rows, cols, static_cast<const ColumnPlan*>(d_plan), d_stats, flag,
+	transform_kernel<<<column_pass_blocks(total, cols), 256, 0, s>>>(raw, rows, cols, static_cast<const ColumnPlan*>(d_plan), d_stats, flag,
 	                                                  classification, X, ldx, Y, ldy);
 	return cudaGetLastError();
 }

@@ -53,3 +53,14 @@ def test_two_gpus_reproduce_one_gpu(g, mode, push):
         pytest.skip("needs two GPUs")
     r = _launch(mode, 2, GLADES_DP_PUSH=push)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("ranks", [4, 8])
+def test_more_gpus_reproduce_one_gpu(g, ranks):
+    """The exchange over peer memory with 4 and 8 ranks (bands of 4 and 2 row tiles, the rotated walk over the
+    owners' bands, four windows queued back to back) against the one-GPU run."""
+    if g.device_count() < ranks:
+        pytest.skip("needs %d GPUs" % ranks)
+    r = _launch("gpu_tc_wide", ranks, GLADES_DP_PUSH="1")
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
