@@ -607,6 +607,8 @@ def main():
     ap.add_argument("--windows", type=int, default=0, help="resident windows per GPU (default: steps+warmup, max 64)")
     ap.add_argument("--gemm", default="auto", choices=["auto", "ffma", "tcgen05"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--batch", type=int, default=0,
+                    help="override the workload's global batch (diagnostic runs, e.g. 1024 = one GPU's share of the 8-GPU step)")
     ap.add_argument("--epochs", type=int, default=0, help="small workloads: epochs per step (default: the config's)")
     args = ap.parse_args()
     if args.warmup < 3:
@@ -622,7 +624,9 @@ def main():
         if rank == 0 and args.impl == "ours":
             run_small(args, g, args.workload)
         return
-    w = WORKLOADS[args.workload]
+    w = dict(WORKLOADS[args.workload])
+    if args.batch > 0:
+        w["batch"] = args.batch
     if args.impl == "reference":
         run_reference_arm(args, g, w, rank, world)
         return

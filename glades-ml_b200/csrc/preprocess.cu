@@ -53,7 +53,16 @@ __global__ void __launch_bounds__(256) minmax_kernel(const float* __restrict__ r
 	const int c = (int)(start % cols);
 	float mn = __int_as_float(0x7F800000), mx = __int_as_float(0xFF800000);
 	bool any = false;
-	for (long long i = start; i < total; i += stride)
+	// four independent loads in flight per thread: the pass is a pure stream, bandwidth comes from bytes in flight
+	long long i = start;
+	for (; i + 3 * stride < total; i += 4 * stride)
+	{
+		const float v0 = raw[i], v1 = raw[i + stride], v2 = raw[i + 2 * stride], v3 = raw[i + 3 * stride];
+		mn = fminf(fminf(mn, v0), fminf(v1, fminf(v2, v3)));
+		mx = fmaxf(fmaxf(mx, v0), fmaxf(v1, fmaxf(v2, v3)));
+		any = true;
+	}
+	for (; i < total; i += stride)
 	{
 		const float v = raw[i];
 		mn = fminf(mn, v);
@@ -121,15 +130,13 @@ __global__ void __launch_bounds__(256) transform_kernel(const float* __restrict_
 	const float mn = order_float(stats[4 * c]), mx = order_float(stats[4 * c + 1]);
 	const float range = __fsub_rn(mx, mn);
 	const float mean = __int_as_float(stats[4 * c + 2]), sd = __int_as_float(stats[4 * c + 3]);
-	for (long long i = start; i < total; i += stride, r += rstep)
-	{
-		float* dst = base + r * ld + p.at;
-		float v = raw[i];
+	auto put = [&](long long row, float v) {
+		float* dst = base + row * ld + p.at;
 		if (p.kind == 1)
 		{
 			const int id = (int)v;
 			for (int k = 0; k < p.classes; ++k) dst[k] = (k == id) ? 0.99f : 0.01f;
-			continue;
+			return;
 		}
 		if (flag == 0)
 		{
@@ -142,13 +149,22 @@ __global__ void __launch_bounds__(256) transform_kernel(const float* __restrict_
 		else
 			v = __fdiv_rn(__fsub_rn(v, mean), sd);
 		*dst = v;
+	};
+	// four independent loads in flight per thread before the first is consumed
+	long long i = start;
+	for (; i + 3 * stride < total; i += 4 * stride, r += 4 * rstep)
+	{
+		const float v0 = raw[i], v1 = raw[i + stride], v2 = raw[i + 2 * stride], v3 = raw[i + 3 * stride];
+		put(r, v0);
+		put(r + rstep, v1);
+		put(r + 2 * rstep, v2);
+		put(r + 3 * rstep, v3);
 	}
+	for (; i < total; i += stride, r += rstep) put(r, raw[i]);
 }
 
 }  // namespace
 
-// d_stats: device [cols][4] ints, already holding the order images of every column's start values for the
-// minimum and the maximum.  d_plan: device array of `cols` ColumnPlan records (four ints each).
 // blocks of 256 threads for a pass over rows * cols cells: about eight cells per thread, at most 16 blocks per SM,
 // and a multiple of cols, so that the grid size is a multiple of cols (a thread then stays on one column)
 static unsigned column_pass_blocks(long long total, int cols)
