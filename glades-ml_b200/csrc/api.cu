@@ -217,7 +217,7 @@ struct gl_net
 	int64_t tcLaunches = 0;
 	int64_t lastWindowLaunches = 0;
 	// workspace for splitting a partial wave of tiles along k (all tensor-core products of the compute stream)
-	TcSplitK sk = {nullptr, nullptr, nullptr, 0};
+	TcSplitK sk = {nullptr, nullptr, nullptr, 0, 0};
 	unsigned skEpoch = 0;
 	// optional per-launch timing of the layer products (gl_profile_enable)
 	bool profile = false;
@@ -985,6 +985,7 @@ static int ensure_work(gl_net* n, int64_t rows)
 			CU(cudaMemset(n->sk.flags, 0, (size_t)sms * 8 * sizeof(unsigned)));
 			n->sk.epoch = &n->skEpoch;
 			n->sk.slots = (size_t)sms;
+			n->sk.min_idle_pct = tc_splitk_min_idle_pct();
 		}
 	}
 	n->capRows = rows;
@@ -2753,6 +2754,7 @@ extern "C" int gl_matmul(const float* dA, int64_t a_sm, int64_t a_sk, const floa
 		CU(cudaMemset(sk.flags, 0, (size_t)sms * 8 * sizeof(unsigned)));
 		sk.epoch = &epoch;
 		sk.slots = (size_t)sms;
+		sk.min_idle_pct = tc_splitk_min_idle_pct();
 		g.sk = &sk;
 	}
 	cudaError_t e = launch_split_lo(dA, alo, (ca / 4) * 4, 0);

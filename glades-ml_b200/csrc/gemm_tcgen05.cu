@@ -510,8 +510,10 @@ cudaError_t launch_cfg(const CUtensorMap& mA, const CUtensorMap& mAl, const CUte
 	int avail = sm_count - sm_reserve;
 	if (avail < 1) avail = 1;
 	int grid = total < avail ? total : avail;
-	// Split the last, partial wave of tiles along k over all CTAs where that wave would leave a tenth or more of
-	// the SMs idle (128 tiles on 148 SMs; 32 tiles of a narrow layer) and the caller gave a workspace.
+	// Split the last, partial wave of tiles along k over all CTAs where that wave would leave a quarter or more of
+	// the SMs idle (32 tiles of a narrow layer; 68 tiles after three whole waves) and the caller gave a workspace.
+	// Not below that: CTAs that share a tile's operands then sit at different k offsets, the operands stop being
+	// fetched once and shared through L2, and 128 tiles on 148 SMs measured 17-30 % slower split than whole.
 	q.sk_full_tiles = total;
 	const int KB = p.K / BK;
 	if (q.sk_work && sk && KB >= 8)
@@ -519,7 +521,7 @@ cudaError_t launch_cfg(const CUtensorMap& mA, const CUtensorMap& mAl, const CUte
 		const int g2 = avail;
 		const int full = (total / g2) * g2;
 		const int rem = total - full;
-		if (rem > 0 && (g2 - rem) * 10 >= g2 && (long long)rem * KB >= 4ll * g2 && (size_t)g2 <= sk->slots &&
+		if (rem > 0 && (g2 - rem) * 100 >= g2 * sk->min_idle_pct && (long long)rem * KB >= 4ll * g2 && (size_t)g2 <= sk->slots &&
 		    (long long)(g2 + 1) * rem * KB < (1ll << 31))
 		{
 			grid = g2;
@@ -563,6 +565,12 @@ __global__ void __launch_bounds__(256) scale_split_lo_kernel(const float* __rest
 
 }  // namespace
 
+int tc_splitk_min_idle_pct()
+{
+	const char* e = getenv("GLADES_TC_SPLITK_IDLE");
+	const int v = e ? atoi(e) : 25;
+	return v < 1 ? 1 : (v > 100 ? 100 : v);
+}
 void tc_variant_counts(long long out5[5])
 {
 	for (int i = 0; i < 5; ++i) out5[i] = g_variant_counts[i].load(std::memory_order_relaxed);

@@ -75,7 +75,10 @@ struct TcSplitK
 	unsigned* flags;   // device, slots * 8 words, zero-initialised
 	unsigned* epoch;   // host counter
 	size_t slots;      // CTAs the workspace has room for
+	int min_idle_pct;  // split only where the last wave would leave at least this share of the SMs idle
 };
+// the share of idle SMs from which a last wave is split (GLADES_TC_SPLITK_IDLE, percent; default 25)
+int tc_splitk_min_idle_pct();
 struct GemmArgs
 {
 	// C[M][N] (ldc) = sum_k A(m,k) * B(n,k);  A(m,k) = A[m*a_sm + k*a_sk], B(n,k) = B[n*b_sn + k*b_sk]

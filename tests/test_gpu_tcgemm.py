@@ -107,8 +107,7 @@ def test_tc_matmul_wide_persistent_variant(g, M, N, K, a_mn, b_mn, positive):
         assert dc[2] == 1, "%d tiles but no CTA walked more than one" % tiles
 
 
-# Shapes whose last wave of tiles would leave a tenth or more of the SMs idle: the kernel deals the k-blocks of
-# those tiles out over all CTAs, a CTA that holds the tail of a tile stores its partial accumulators and the CTA
+# Shapes whose last wave of tiles leaves SMs idle: the kernel deals the k-blocks of those tiles out over all CTAs, a CTA that holds the tail of a tile stores its partial accumulators and the CTA
 # that holds the head adds the partials in a fixed order and runs the epilogue.  (M, N, K, A MN-major, B MN-major)
 SPLIT_CASES = [
     (1024, 4096, 1024, 0, 0),   # 128 wide tiles on 148 SMs: every CTA gets 0.86 of a tile
@@ -121,14 +120,30 @@ SPLIT_CASES = [
 ]
 
 
+# By default only a last wave that leaves a quarter of the SMs idle is split; these cases lower the threshold to
+# a tenth so that the geometries with 0.86 of a tile per CTA (most tiles shared by two CTAs) stay covered.
 @pytest.mark.parametrize("M,N,K,a_mn,b_mn", SPLIT_CASES)
-def test_tc_matmul_split_last_wave(g, M, N, K, a_mn, b_mn):
+def test_tc_matmul_split_last_wave(g, monkeypatch, M, N, K, a_mn, b_mn):
+    monkeypatch.setenv("GLADES_TC_SPLITK_IDLE", "10")
     err, dc = _matmul_case(g, M, N, K, a_mn, b_mn, seed=5 * M + 3 * N + K + a_mn + 2 * b_mn)
     assert err <= 4e-6, "error %.3g of sum|a||b|" % err
     assert dc[4] == 1, "the last wave was not split along k: %r" % (dc,)
     # all-positive operands: partial sums of one sign, the worst case for a lost or doubled partial
     err, dc = _matmul_case(g, M, N, K, a_mn, b_mn, seed=7, positive=True)
     assert err <= 4e-6 and dc[4] == 1
+
+
+def test_tc_matmul_split_rule_default(g, monkeypatch):
+    """Default rule: 128 tiles on 148 SMs (13 % idle) stay whole, 32 and 68-tile last waves are split."""
+    monkeypatch.delenv("GLADES_TC_SPLITK_IDLE", raising=False)
+    monkeypatch.delenv("GLADES_TC_SPLITK", raising=False)
+    import torch
+    if torch.cuda.get_device_properties(0).multi_processor_count != 148:
+        pytest.skip("the tile counts of this test are chosen for 148 SMs")
+    for (M, N, K), split in (((1024, 4096, 1024), 0), ((1024, 1024, 4096), 1), ((4096, 4096, 512), 1)):
+        err, dc = _matmul_case(g, M, N, K, 0, 0, seed=11)
+        assert err <= 4e-6
+        assert dc[4] == split, "M=%d N=%d K=%d: split %d, expected %d" % (M, N, K, dc[4], split)
 
 
 def test_tc_matmul_rejects_odd_shapes(g):
