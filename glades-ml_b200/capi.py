@@ -151,6 +151,7 @@ def lib():
         "gl_sync": (C.c_int, [vp]),
         "gl_kernel_launches": (i64, [vp]),
         "gl_tensor_core_launches": (i64, [vp]),
+        "gl_window_cluster_ctas": (C.c_int32, [vp]),
         "gl_matmul": (C.c_int, [vp, i64, i64, vp, i64, i64, vp, i64, i32, i32, i32, i32, i32]),
         "gl_shard_range": (None, [i64, i32, i32, C.POINTER(i64), C.POINTER(i64)]),
         "gl_dp_unique_id": (C.c_int, [vp]),
@@ -399,6 +400,9 @@ class Net:
 
     def tensor_core_launches(self):
         return lib().gl_tensor_core_launches(self.h)
+
+    def window_cluster_ctas(self):
+        return lib().gl_window_cluster_ctas(self.h)
 
     def dp_init(self, rank, world, id_bytes):
         buf = (C.c_char * 128).from_buffer_copy(id_bytes)

@@ -238,6 +238,7 @@ struct gl_net
 	unsigned long long* gfTiming = nullptr;  // GLADES_GF_TIMING=1: phase nanoseconds, printed when the handle goes
 	int gfRows = 0, gfCtas = 0, gfCkMb = 0, gfNc = 2;
 	int gfOk = -1;  // -1 not decided yet
+	int gfClusterCtas = -1;  // CTAs of the cluster variant's grid; 0: the variant does not apply; -1 not decided yet
 
 	int epochs = 0;
 	volatile int stop = 0;
@@ -1314,6 +1315,20 @@ static int grid_fused_launch(gl_net* n, const float* X, const float* Y, int64_t 
 		CU(cudaMalloc(&n->gfPart, (size_t)sms * (2 + GL_MAX_WEIGHT_LAYERS) * sizeof(double)));
 		n->gfNc = grid_fused_pick_nc(base, sms);
 	}
+	if (n->gfClusterCtas < 0)
+	{
+		// the cluster variant where the network allows it and the device can hold whole clusters (GLADES_GF_CLUSTER=0: never)
+		const char* e = getenv("GLADES_GF_CLUSTER");
+		int ctas = 0;
+		if (!(e && atoi(e) == 0) && cluster_fused_fits(base))
+		{
+			bool aligned = true;
+			for (int l = 0; l <= n->H; ++l) aligned = aligned && n->woff[l] % 4 == 0;
+			if (aligned) ctas = cluster_fused_max_ctas(base);
+			if (ctas > n->gfCtas) ctas = (n->gfCtas / 8) * 8;
+		}
+		n->gfClusterCtas = ctas >= 16 ? ctas : 0;
+	}
 	if (!n->gfMapsTried)
 	{
 		// weight tiles by bulk tensor copies where every layer's rows are multiples of 16 bytes
@@ -1390,8 +1405,11 @@ static int grid_fused_launch(gl_net* n, const float* X, const float* Y, int64_t 
 		CU(cudaMemset(n->gfTiming, 0, 4 * sizeof(unsigned long long)));
 	}
 	a.timing = n->gfTiming;
-	cudaError_t e = launch_grid_fused(a, n->stream);
-	if (e != cudaSuccess) return fail(GL_ERR_CUDA, "whole-window cooperative kernel: %s", cudaGetErrorString(e));
+	const bool cluster = n->gfClusterCtas > 0 && (((uintptr_t)X | (uintptr_t)Y) & 15) == 0;
+	if (cluster) a.part_ctas = n->gfClusterCtas;
+	cudaError_t e = cluster ? launch_cluster_fused(a, n->stream) : launch_grid_fused(a, n->stream);
+	if (e != cudaSuccess)
+		return fail(GL_ERR_CUDA, "whole-window cooperative kernel%s: %s", cluster ? " (cluster variant)" : "", cudaGetErrorString(e));
 	n->loW = false;
 	return GL_OK;
 }
@@ -2601,6 +2619,7 @@ extern "C" void gl_tc_variant_counts(int64_t* out5)
 	for (int i = 0; i < 5; ++i) out5[i] = c[i];
 }
 extern "C" int64_t gl_kernel_launches(const gl_net* n) { return n ? n->launches : 0; }
+extern "C" int32_t gl_window_cluster_ctas(const gl_net* n) { return n ? n->gfClusterCtas : -1; }
 
 extern "C" int gl_sync(gl_net* n)
 {

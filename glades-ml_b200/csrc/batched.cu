@@ -139,37 +139,42 @@ __global__ void __launch_bounds__(256) gemm_skinny_kernel(const GemmArgs g)
 		for (int r = 0; r < SK_ROWS; ++r)
 #pragma unroll
 			for (int n = 0; n < NN; ++n) acc[r][n] = 0.0f;
-		// two 16-byte chunks per row and lane in flight (8 loads) before the first is consumed
-		for (int k4 = lane; k4 < K4; k4 += 64)
-		{
-			const int k4b = k4 + 32;
-			const bool two = k4b < K4;
-			float4 a[SK_ROWS], b[SK_ROWS];
-#pragma unroll
-			for (int r = 0; r < SK_ROWS; ++r) a[r] = arow[r][k4];
-#pragma unroll
-			for (int r = 0; r < SK_ROWS; ++r) b[r] = two ? arow[r][k4b] : make_float4(0.f, 0.f, 0.f, 0.f);
+		// Two 16-byte chunks per row and lane, rotated: while one set of four loads is consumed the other set is in
+		// flight, so the warp always has loads outstanding (loading both sets and then computing on both left
+		// HBM idle during the arithmetic: 2.7 TB/s).
+		auto consume = [&](const float4 (&v)[SK_ROWS], int kq) {
 #pragma unroll
 			for (int n = 0; n < NN; ++n)
 				if (n < N)
 				{
-					const float4 w = reinterpret_cast<const float4*>(sW + n * K)[k4];
+					const float4 w = reinterpret_cast<const float4*>(sW + n * K)[kq];
 #pragma unroll
 					for (int r = 0; r < SK_ROWS; ++r)
-						acc[r][n] = fmaf(a[r].x, w.x, fmaf(a[r].y, w.y, fmaf(a[r].z, w.z, fmaf(a[r].w, w.w, acc[r][n]))));
+						acc[r][n] = fmaf(v[r].x, w.x, fmaf(v[r].y, w.y, fmaf(v[r].z, w.z, fmaf(v[r].w, w.w, acc[r][n]))));
 				}
+		};
+		float4 a[SK_ROWS], b[SK_ROWS];
+		if (lane < K4)
+		{
+#pragma unroll
+			for (int r = 0; r < SK_ROWS; ++r) a[r] = arow[r][lane];
+		}
+		for (int k4 = lane; k4 < K4; k4 += 64)
+		{
+			const int k4b = k4 + 32, k4n = k4 + 64;
+			const bool two = k4b < K4;
 			if (two)
 			{
 #pragma unroll
-				for (int n = 0; n < NN; ++n)
-					if (n < N)
-					{
-						const float4 w = reinterpret_cast<const float4*>(sW + n * K)[k4b];
-#pragma unroll
-						for (int r = 0; r < SK_ROWS; ++r)
-							acc[r][n] = fmaf(b[r].x, w.x, fmaf(b[r].y, w.y, fmaf(b[r].z, w.z, fmaf(b[r].w, w.w, acc[r][n]))));
-					}
+				for (int r = 0; r < SK_ROWS; ++r) b[r] = arow[r][k4b];
 			}
+			consume(a, k4);
+			if (k4n < K4)
+			{
+#pragma unroll
+				for (int r = 0; r < SK_ROWS; ++r) a[r] = arow[r][k4n];
+			}
+			if (two) consume(b, k4b);
 		}
 #pragma unroll
 		for (int r = 0; r < SK_ROWS; ++r)

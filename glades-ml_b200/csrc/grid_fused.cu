@@ -770,6 +770,627 @@ __global__ void __launch_bounds__(GF_THREADS, 1) grid_fused_kernel(const __grid_
 	if (bad) atomicOr(a.flags, 1);
 }
 
+// =================================================================================================
+// Cluster variant of the whole-window kernel.
+//
+// grid_fused_kernel's phase 1 is bound by how fast ONE SM gets the network's weights delivered: every CTA
+// streams all of them per sample group.  Here a thread-block cluster of CF_CS CTAs carries CF_R rows through the
+// network together and every CTA owns 1/CF_CS of each layer's NODES: it keeps the weight rows of its nodes
+// (forward) and the weight columns of its nodes (hidden deltas) in shared memory for the whole window -- read
+// from L2 once per window instead of once per sample group -- computes its nodes' activations for the
+// CF_R rows and stores them into the activation buffers of all CF_CS CTAs over distributed shared memory
+// (st.shared::cluster; no multicast loads), one cluster barrier per layer.  The head runs on every CTA's own
+// copy (side effects from cluster rank 0 only).  Activations and deltas go to the same window scratch as in
+// grid_fused_kernel, and phase 2 sums the window's rows per weight tile -- here with a 4 x 4 register tile per
+// lane and the 64 rows of a step dealt over the eight warps, whose partial sums are added in warp order.
+// Everything is deterministic.  All barriers are executed unconditionally by every thread of every CTA.
+constexpr int CF_CS = 8;   // CTAs per cluster (the portable maximum)
+constexpr int CF_R = 32;   // rows a cluster carries through the network together
+constexpr int CF_TI = 32;  // phase 2: weight tile 16 outputs x 32 inputs
+
+struct CfPlan
+{
+	int tot;                                  // nodes of the network
+	int node_off[GL_MAX_WEIGHT_LAYERS + 2];   // first node of layer j
+	int sl[GL_MAX_WEIGHT_LAYERS + 2];         // nodes of layer j one CTA owns (a multiple of 4)
+	int d_off[GL_MAX_WEIGHT_LAYERS + 2];      // first row of layer j's deltas in the delta buffer (j >= 1)
+	int d_rows;                               // rows of the delta buffer (each layer rounded up to 4 nodes)
+	int wf[GL_MAX_WEIGHT_LAYERS + 1];         // float offset of the forward slice of weight layer l
+	int wb[GL_MAX_WEIGHT_LAYERS + 1];         // float offset of the delta slice of node layer j (1..H)
+	int rowm;                                 // float offset of the per-row metric scratch
+	int floats;                               // dynamic shared memory, floats
+};
+constexpr int CF_P2_FLOATS = GF_TJ * GF_TO + GF_TJ * CF_TI + GF_TJ + 8 * GF_TO * CF_TI;  // phase-2 buffers (aliased)
+
+__host__ __device__ inline void cf_plan(const NetView& n, CfPlan& p)
+{
+	const int H = n.H;
+	int tot = 0;
+	for (int j = 0; j <= H + 1; ++j)
+	{
+		p.node_off[j] = tot;
+		tot += n.sizes[j];
+		p.sl[j] = (((n.sizes[j] + CF_CS - 1) / CF_CS) + 3) & ~3;
+	}
+	p.tot = tot;
+	int dr = 0;
+	p.d_off[0] = 0;
+	for (int j = 1; j <= H + 1; ++j)
+	{
+		p.d_off[j] = dr;
+		dr += (n.sizes[j] + 3) & ~3;
+	}
+	p.d_rows = dr;
+	int f = (tot + dr) * CF_R;
+	for (int l = 0; l <= H; ++l)
+	{
+		p.wf[l] = f;
+		f += p.sl[l + 1] * (n.sizes[l] + 4);
+	}
+	p.wb[0] = 0;
+	for (int j = 1; j <= H; ++j)
+	{
+		p.wb[j] = f;
+		f += p.sl[j] * (((n.sizes[j + 1] + 3) & ~3) + 4);
+	}
+	p.rowm = f;
+	f += 2 * CF_R;
+	p.floats = f > CF_P2_FLOATS ? f : CF_P2_FLOATS;
+}
+
+__device__ __forceinline__ uint32_t cl_rank()
+{
+	uint32_t r;
+	asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+	return r;
+}
+// every thread of every CTA of the cluster; orders shared::cluster stores before it against loads after it
+__device__ __forceinline__ void cl_sync()
+{
+	asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t cl_map(uint32_t local_addr, uint32_t rank)
+{
+	uint32_t r;
+	asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_addr), "r"(rank));
+	return r;
+}
+__device__ __forceinline__ void cl_store4(uint32_t cluster_addr, float x, float y, float z, float w)
+{
+	asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(cluster_addr), "f"(x), "f"(y), "f"(z), "f"(w) : "memory");
+}
+
+// s[q] = sum_k InT[k][4 * sq + q] * Wsl[n][k] (q = 0..3) for the CTA's `cnt` nodes n; InT is [K][CF_R], Wsl is
+// [cnt][K + 4], K a multiple of 4.  Thread = one node and four rows (eight row quads x 32 nodes per pass); where
+// the CTA owns at most 8 nodes a warp takes one node and its four lane groups a quarter of k each, added in
+// lane-group order.  epi(n, sq, s0, s1, s2, s3) runs once per node and row quad.
+template <typename Epi>
+__device__ __forceinline__ void cf_product(const float* InT, int K, const float* Wsl, int cnt, Epi epi)
+{
+	const int t = threadIdx.x, sq = t & 7;
+	const int ws = K + 4;
+	const float* in = InT + 4 * sq;
+	auto dot = [&](const float* w, int k0, int k1, float& a0, float& a1, float& a2, float& a3) {
+#pragma unroll 2
+		for (int k = k0; k < k1; k += 4)
+		{
+			const float4 wv = *reinterpret_cast<const float4*>(w + k);
+			const float4 x0 = *reinterpret_cast<const float4*>(in + (size_t)(k + 0) * CF_R);
+			const float4 x1 = *reinterpret_cast<const float4*>(in + (size_t)(k + 1) * CF_R);
+			const float4 x2 = *reinterpret_cast<const float4*>(in + (size_t)(k + 2) * CF_R);
+			const float4 x3 = *reinterpret_cast<const float4*>(in + (size_t)(k + 3) * CF_R);
+			a0 = fmaf(wv.x, x0.x, a0); a1 = fmaf(wv.x, x0.y, a1); a2 = fmaf(wv.x, x0.z, a2); a3 = fmaf(wv.x, x0.w, a3);
+			a0 = fmaf(wv.y, x1.x, a0); a1 = fmaf(wv.y, x1.y, a1); a2 = fmaf(wv.y, x1.z, a2); a3 = fmaf(wv.y, x1.w, a3);
+			a0 = fmaf(wv.z, x2.x, a0); a1 = fmaf(wv.z, x2.y, a1); a2 = fmaf(wv.z, x2.z, a2); a3 = fmaf(wv.z, x2.w, a3);
+			a0 = fmaf(wv.w, x3.x, a0); a1 = fmaf(wv.w, x3.y, a1); a2 = fmaf(wv.w, x3.z, a2); a3 = fmaf(wv.w, x3.w, a3);
+		}
+	};
+	if (cnt <= 8)
+	{
+		const int n = t >> 5, kc = (t >> 3) & 3;
+		const int chunk = (((K + 3) / 4) + 3) & ~3;
+		float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
+		if (n < cnt)
+		{
+			const int k0 = kc * chunk, k1 = (k0 + chunk) < K ? (k0 + chunk) : K;
+			dot(Wsl + (size_t)n * ws, k0, k1, a0, a1, a2, a3);
+		}
+		// whole warps take part in the shuffles (n is uniform in a warp)
+#pragma unroll
+		for (int off = 8; off <= 16; off <<= 1)
+		{
+			a0 += __shfl_xor_sync(0xffffffffu, a0, off);
+			a1 += __shfl_xor_sync(0xffffffffu, a1, off);
+			a2 += __shfl_xor_sync(0xffffffffu, a2, off);
+			a3 += __shfl_xor_sync(0xffffffffu, a3, off);
+		}
+		if (n < cnt && kc == 0) epi(n, sq, a0, a1, a2, a3);
+		return;
+	}
+	for (int nb = 0; nb < cnt; nb += 32)
+	{
+		const int n = nb + (t >> 3);
+		if (n < cnt)
+		{
+			float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
+			dot(Wsl + (size_t)n * ws, 0, K, a0, a1, a2, a3);
+			epi(n, sq, a0, a1, a2, a3);
+		}
+	}
+}
+
+// Phase 2, one 16 x 32 tile of layer l's weights.  Lane = 4 outputs x 4 inputs (four output groups x eight input
+// groups), warp w takes rows 8w..8w+7 of every 64-row step; the eight warps' partial sums are added in warp order
+// and the update is applied in place.  Tiles of deltas / activations travel global -> registers -> shared memory,
+// the next step's loads in flight while the current one is consumed.
+__device__ __forceinline__ void cf_grad_tile(const GridFusedArgs& a, int l, int o0, int i0, int len, int tot, int off_in, int off_out,
+                                             float* Dt, float* At, float* Ct, float* red, const float* ckl, float inv_len, int& bad)
+{
+	constexpr int NA = GF_TJ * CF_TI / GF_THREADS;  // 8 activation values per thread and step
+	const NetView& n = a.net;
+	const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+	const int ni = n.sizes[l], no = n.sizes[l + 1];
+	const float lr = n.lr[l], w1 = n.wd1[l] * lr, w2 = n.wd2[l] * lr;
+	const bool decay = w1 != 0.0f || w2 != 0.0f;
+	const int og = lane >> 3, ig = lane & 7;
+	float g[4][4];
+#pragma unroll
+	for (int x = 0; x < 4; ++x)
+#pragma unroll
+		for (int y = 0; y < 4; ++y) g[x][y] = 0.0f;
+	float pd[4], pa[NA], pc = 0.0f;
+	auto fetch = [&](int jb) {
+		const int jn = (len - jb) < GF_TJ ? (len - jb) : GF_TJ;
+#pragma unroll
+		for (int k = 0; k < 4; ++k)
+		{
+			const int e = t + k * GF_THREADS, jj = e / GF_TO, x = e - jj * GF_TO;
+			pd[k] = (jj < jn && o0 + x < no) ? __ldcg(a.delbuf + (size_t)(jb + jj) * tot + off_out + o0 + x) : 0.0f;
+		}
+#pragma unroll
+		for (int k = 0; k < NA; ++k)
+		{
+			const int e = t + k * GF_THREADS, jj = e / CF_TI, x = e - jj * CF_TI;
+			pa[k] = (jj < jn && i0 + x < ni) ? __ldcg(a.actbuf + (size_t)(jb + jj) * tot + off_in + i0 + x) : 0.0f;
+		}
+		if (t < GF_TJ) pc = (t < jn) ? __ldg(ckl + (len - (jb + t))) : 0.0f;
+	};
+	fetch(0);
+	for (int jb = 0; jb < len; jb += GF_TJ)
+	{
+		const int jn = (len - jb) < GF_TJ ? (len - jb) : GF_TJ;
+		__syncthreads();
+		if (t < GF_TJ) Ct[t] = pc;
+#pragma unroll
+		for (int k = 0; k < NA; ++k) At[t + k * GF_THREADS] = pa[k];
+		if (decay)
+		{
+#pragma unroll
+			for (int k = 0; k < 4; ++k) Dt[t + k * GF_THREADS] = pd[k];
+		}
+		else
+		{
+			// no decay terms: the tile holds c_j * lr * d_jo, and a row costs one multiply-add per weight
+#pragma unroll
+			for (int k = 0; k < 4; ++k)
+			{
+				const int jj = (t + k * GF_THREADS) / GF_TO;
+				Dt[t + k * GF_THREADS] = (jj < jn) ? pd[k] * lr * __ldg(ckl + (len - (jb + jj))) : 0.0f;
+			}
+		}
+		__syncthreads();
+		if (jb + GF_TJ < len) fetch(jb + GF_TJ);
+#pragma unroll 4
+		for (int q = 0; q < 8; ++q)
+		{
+			const int jj = warp * 8 + q;  // rows beyond the window hold zeros
+			const float4 dv = *reinterpret_cast<const float4*>(Dt + jj * GF_TO + og * 4);
+			const float4 av = *reinterpret_cast<const float4*>(At + jj * CF_TI + ig * 4);
+			const float d4[4] = {dv.x, dv.y, dv.z, dv.w};
+			const float a4[4] = {av.x, av.y, av.z, av.w};
+			if (!decay)
+			{
+#pragma unroll
+				for (int x = 0; x < 4; ++x)
+#pragma unroll
+					for (int y = 0; y < 4; ++y) g[x][y] = fmaf(d4[x], a4[y], g[x][y]);
+			}
+			else
+			{
+				const float c = Ct[jj];
+				float dec[4];
+#pragma unroll
+				for (int y = 0; y < 4; ++y) dec[y] = fmaf(w1, fabsf(a4[y]), w2 * a4[y]);
+#pragma unroll
+				for (int x = 0; x < 4; ++x)
+#pragma unroll
+					for (int y = 0; y < 4; ++y) g[x][y] = fmaf(c, fmaf(lr * d4[x], a4[y], dec[y]), g[x][y]);
+			}
+		}
+	}
+	// the warps' partial sums: red[warp][output 0..15][input 0..31]
+#pragma unroll
+	for (int x = 0; x < 4; ++x)
+		*reinterpret_cast<float4*>(red + warp * (GF_TO * CF_TI) + (og * 4 + x) * CF_TI + ig * 4) = make_float4(g[x][0], g[x][1], g[x][2], g[x][3]);
+	__syncthreads();
+#pragma unroll
+	for (int k = 0; k < GF_TO * CF_TI / GF_THREADS; ++k)
+	{
+		const int e = t + k * GF_THREADS;
+		const int o = o0 + e / CF_TI, i = i0 + (e & (CF_TI - 1));
+		float sum = red[e];
+#pragma unroll
+		for (int w = 1; w < 8; ++w) sum += red[w * (GF_TO * CF_TI) + e];
+		if (o < no && i < ni)
+		{
+			float* wp = n.W[l] + (size_t)o * ni + i;
+			const float wv = __ldcg(wp) - sum * inv_len;
+			if (!isfinite(wv)) bad = 1;
+			*wp = wv;
+		}
+	}
+}
+
+__global__ void __launch_bounds__(GF_THREADS, 1) cluster_fused_kernel(const __grid_constant__ GridFusedArgs a)
+{
+	extern __shared__ __align__(16) float sm[];
+	cg::grid_group grid = cg::this_grid();
+	const NetView& n = a.net;
+	const int H = n.H;
+	const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+	const int n_out = n.sizes[H + 1];
+	const int mb = n.mb;
+	const int crank = (int)cl_rank();
+	const int cid = (int)blockIdx.x / CF_CS, nclusters = (int)gridDim.x / CF_CS;
+	__shared__ CfPlan P;
+	__shared__ double s_part[GF_PART];
+	if (t == 0) cf_plan(n, P);
+	__syncthreads();
+	const int tot = P.tot;
+	float* AT = sm;                          // [tot][CF_R] activations, node-major
+	float* DT = sm + (size_t)tot * CF_R;     // [d_rows][CF_R] deltas of node layers 1..H+1
+	float* rowm = sm + P.rowm;               // [CF_R][2]: cost, accuracy of the pass's rows
+	// phase-2 buffers alias the phase-1 region (the phases are separated by grid barriers)
+	float* Dt = sm;
+	float* At = Dt + GF_TJ * GF_TO;
+	float* Ct = At + GF_TJ * CF_TI;
+	float* red = Ct + GF_TJ;
+	const uint32_t at_addr = smem_u32(AT), dt_addr = smem_u32(DT);
+
+	const bool classify = n.out_type != GL_OUT_REGRESSION;
+	const bool softmax = n.act[H] == GL_ACT_SOFTMAX;
+	const float data_size = a.data_size;
+
+	// phase-2 work items: layer l has ceil(no/16) * ceil(ni/32) tiles, or ceil(ni/64) column groups where no <= 4
+	int tile_off[GL_MAX_WEIGHT_LAYERS + 2];
+	int tiles = 0;
+	for (int l = 0; l <= H; ++l)
+	{
+		tile_off[l] = tiles;
+		tiles += (n.sizes[l + 1] <= GF_NARROW) ? (n.sizes[l] + GF_NCOLS - 1) / GF_NCOLS
+		                                       : ((n.sizes[l + 1] + GF_TO - 1) / GF_TO) * ((n.sizes[l] + CF_TI - 1) / CF_TI);
+	}
+	tile_off[H + 1] = tiles;
+
+	const bool timed = a.timing != nullptr && blockIdx.x == 0 && t == 0;
+	unsigned long long tm[4] = {0, 0, 0, 0}, t_a = 0, t_b = 0;
+	auto now = []() {
+		unsigned long long v;
+		asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(v));
+		return v;
+	};
+
+	cl_sync();  // every CTA of the cluster is running before the first store into its shared memory
+	int bad = 0;
+	for (int ep = 0; ep < a.n_epochs; ++ep)
+	{
+		const bool last_epoch = ep == a.n_epochs - 1;
+		double ecost = 0.0, eacc = 0.0;  // CTA 0, thread 0
+		for (long long r0 = 0; r0 < a.rows; r0 += mb)
+		{
+			const int len = (int)((a.rows - r0) < mb ? (a.rows - r0) : mb);
+			const int passes = (len + CF_R - 1) / CF_R;
+			if (t < GF_PART) s_part[t] = 0.0;
+			if (timed) t_a = now();
+			// ---- this window's weights of the CTA's nodes: rows of W_l (forward), columns of W_j (hidden deltas)
+			for (int l = 0; l <= H; ++l)
+			{
+				const int K = n.sizes[l], nb0 = crank * P.sl[l + 1];
+				int cnt = n.sizes[l + 1] - nb0;
+				cnt = cnt < 0 ? 0 : (cnt > P.sl[l + 1] ? P.sl[l + 1] : cnt);
+				const float* src = n.W[l] + (size_t)nb0 * K;
+				float* dst = sm + P.wf[l];
+				const int kq = K >> 2;
+				for (int e = t; e < cnt * kq; e += GF_THREADS)
+				{
+					const int r = e / kq, k = (e - r * kq) << 2;
+					*reinterpret_cast<float4*>(dst + (size_t)r * (K + 4) + k) = __ldcg(reinterpret_cast<const float4*>(src + (size_t)r * K + k));
+				}
+			}
+			for (int j = 1; j <= H; ++j)
+			{
+				const int ni = n.sizes[j], no = n.sizes[j + 1], K4 = (no + 3) & ~3, i0 = crank * P.sl[j];
+				int cnt = ni - i0;
+				cnt = cnt < 0 ? 0 : (cnt > P.sl[j] ? P.sl[j] : cnt);
+				const float* src = n.W[j] + i0;
+				float* dst = sm + P.wb[j];
+				for (int e = t; e < cnt * K4; e += GF_THREADS)
+				{
+					const int o = e / cnt, i = e - o * cnt;
+					dst[(size_t)i * (K4 + 4) + o] = (o < no) ? __ldcg(src + (size_t)o * ni + i) : 0.0f;
+				}
+			}
+			__syncthreads();
+			// ================= phase 1: forward, head, deltas, CF_R rows per cluster pass
+			for (int pass = cid; pass < passes; pass += nclusters)
+			{
+				const int j0 = pass * CF_R;
+				const int valid = (len - j0) < CF_R ? (len - j0) : CF_R;
+				{
+					// inputs of the pass, transposed to [node][row]; every CTA reads them itself
+					const int n0 = n.sizes[0], kq = n0 >> 2;
+					for (int e = t; e < CF_R * kq; e += GF_THREADS)
+					{
+						const int r = e / kq, i = (e - r * kq) << 2;
+						float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+						if (r < valid) v = *reinterpret_cast<const float4*>(a.X + (size_t)(r0 + j0 + r) * n0 + i);
+						AT[(i + 0) * CF_R + r] = v.x;
+						AT[(i + 1) * CF_R + r] = v.y;
+						AT[(i + 2) * CF_R + r] = v.z;
+						AT[(i + 3) * CF_R + r] = v.w;
+					}
+				}
+				__syncthreads();
+				for (int l = 0; l <= H; ++l)
+				{
+					const int nb0 = crank * P.sl[l + 1];
+					int cnt = n.sizes[l + 1] - nb0;
+					cnt = cnt < 0 ? 0 : (cnt > P.sl[l + 1] ? P.sl[l + 1] : cnt);
+					const float b = (l >= 1) ? __ldcg(n.bias + l) : 0.0f;
+					const int act = n.act[l];
+					const float par = n.par[l];
+					const int out_node = P.node_off[l + 1] + nb0;
+					const bool hidden = l < H;
+					cf_product(AT + (size_t)P.node_off[l] * CF_R, n.sizes[l], sm + P.wf[l], cnt,
+					           [&](int nn, int sq, float s0, float s1, float s2, float s3) {
+						           const float v0 = squash_b(s0 + b, act, par), v1 = squash_b(s1 + b, act, par);
+						           const float v2 = squash_b(s2 + b, act, par), v3 = squash_b(s3 + b, act, par);
+						           const uint32_t local = at_addr + (uint32_t)(((out_node + nn) * CF_R + 4 * sq) * 4);
+#pragma unroll
+						           for (int dst = 0; dst < CF_CS; ++dst) cl_store4(cl_map(local, (uint32_t)dst), v0, v1, v2, v3);
+						           if (hidden)
+						           {
+							           float* ga = a.actbuf + (size_t)(j0 + 4 * sq) * tot + out_node + nn;
+							           if (4 * sq + 0 < valid) ga[0] = v0;
+							           if (4 * sq + 1 < valid) ga[(size_t)tot] = v1;
+							           if (4 * sq + 2 < valid) ga[(size_t)2 * tot] = v2;
+							           if (4 * sq + 3 < valid) ga[(size_t)3 * tot] = v3;
+						           }
+					           });
+					cl_sync();  // the layer's activations have landed in every CTA of the cluster
+				}
+				// ---- head on this CTA's copy: warp = four rows of the pass; side effects from cluster rank 0 only
+				for (int rr = 0; rr < CF_R / 8; ++rr)
+				{
+					const int r = warp * (CF_R / 8) + rr;
+					float* p = AT + (size_t)P.node_off[H + 1] * CF_R + r;  // stride CF_R
+					float* dout = DT + (size_t)P.d_off[H + 1] * CF_R + r;
+					float c_acc = 0.0f, a_acc = 0.0f, be = 0.0f, bp = 0.0f;
+					int ie = -1, ip = -1;
+					if (r < valid)
+					{
+						const float* y = a.Y + (r0 + j0 + r) * n_out;
+						float mx = -INFINITY, inv_den = 1.0f;
+						if (softmax)
+						{
+							for (int o = lane; o < n_out; o += 32) mx = fmaxf(mx, p[(size_t)o * CF_R]);
+							mx = warp_max(mx);
+							float den = 0.0f;
+							for (int o = lane; o < n_out; o += 32) den += expf(p[(size_t)o * CF_R] - mx);
+							inv_den = 1.0f / warp_sum(den);
+						}
+						for (int o = lane; o < n_out; o += 32)
+						{
+							float pv = p[(size_t)o * CF_R];
+							const float e = y[o];
+							float cost, d;
+							if (softmax)
+							{
+								pv = expf(pv - mx) * inv_den;
+								p[(size_t)o * CF_R] = pv;
+								cost = (e != 0.0f) ? -(e * logf(pv)) / data_size : 0.0f;
+								d = pv - e;
+							}
+							else if (n.out_type == GL_OUT_REGRESSION)
+							{
+								const float tt = e - pv;
+								cost = tt * tt / data_size;
+								d = 2.0f * (pv - e);
+							}
+							else if (n.out_type == GL_OUT_CLASSIFICATION)
+							{
+								cost = -((e * logf(pv)) + ((1.0f - e) * logf(1.0f - pv))) / data_size;
+								d = (pv - e) / ((1.0f - pv) * pv);
+							}
+							else
+							{
+								cost = logf(e / pv) / data_size;
+								d = -(e / pv);
+							}
+							dout[(size_t)o * CF_R] = d;
+							if (crank == 0)
+							{
+								a.actbuf[(size_t)(j0 + r) * tot + P.node_off[H + 1] + o] = pv;
+								a.delbuf[(size_t)(j0 + r) * tot + P.node_off[H + 1] + o] = d;
+							}
+							c_acc += cost;
+							a_acc += fmaxf((1.0f - fminf(fabsf(pv - e), 1.0f)) * 100.0f, 0.0f);
+							if (e > be) { be = e; ie = o; }
+							if (pv > bp) { bp = pv; ip = o; }
+						}
+						c_acc = warp_sum(c_acc);
+						a_acc = warp_sum(a_acc);
+#pragma unroll
+						for (int off = 16; off > 0; off >>= 1)
+						{
+							const float oe = __shfl_xor_sync(0xffffffffu, be, off);
+							const int oie = __shfl_xor_sync(0xffffffffu, ie, off);
+							if (oie >= 0 && (ie < 0 || oe > be || (oe == be && oie < ie))) { be = oe; ie = oie; }
+							const float op = __shfl_xor_sync(0xffffffffu, bp, off);
+							const int oip = __shfl_xor_sync(0xffffffffu, ip, off);
+							if (oip >= 0 && (ip < 0 || op > bp || (op == bp && oip < ip))) { bp = op; ip = oip; }
+						}
+						if (crank == 0)
+						{
+							if (lane == 0 && classify && last_epoch && ie >= 0 && ip >= 0) atomicAdd(a.confusion + ie * n_out + ip, 1);
+							if (a.last_out && last_epoch && r0 + j0 + r == a.rows - 1)
+								for (int o = lane; o < n_out; o += 32) a.last_out[o] = p[(size_t)o * CF_R];
+						}
+					}
+					else
+					{
+						for (int o = lane; o < n_out; o += 32) dout[(size_t)o * CF_R] = 0.0f;
+					}
+					// rows of the delta buffer beyond the layer's nodes (rounded up to 4) take part in the next product as zeros
+					for (int o = n_out + lane; o < ((n_out + 3) & ~3); o += 32) dout[(size_t)o * CF_R] = 0.0f;
+					if (lane == 0)
+					{
+						rowm[2 * r] = c_acc;
+						rowm[2 * r + 1] = a_acc;
+					}
+				}
+				__syncthreads();
+				// ---- hidden deltas of the CTA's nodes: D_j = (D_{j+1} W_j) * act'(A_j)
+				for (int j = H; j >= 1; --j)
+				{
+					const int i0 = crank * P.sl[j];
+					int cnt = n.sizes[j] - i0;
+					cnt = cnt < 0 ? 0 : (cnt > P.sl[j] ? P.sl[j] : cnt);
+					const int act = n.act[j - 1];
+					const int node = P.node_off[j] + i0, drow = P.d_off[j] + i0;
+					const bool gather = j >= 2;
+					cf_product(DT + (size_t)P.d_off[j + 1] * CF_R, (n.sizes[j + 1] + 3) & ~3, sm + P.wb[j], cnt,
+					           [&](int nn, int sq, float s0, float s1, float s2, float s3) {
+						           const float4 av = *reinterpret_cast<const float4*>(AT + (size_t)(node + nn) * CF_R + 4 * sq);
+						           const float d0 = (4 * sq + 0 < valid) ? s0 * act_der_b(av.x, act, 0.01f) : 0.0f;
+						           const float d1 = (4 * sq + 1 < valid) ? s1 * act_der_b(av.y, act, 0.01f) : 0.0f;
+						           const float d2 = (4 * sq + 2 < valid) ? s2 * act_der_b(av.z, act, 0.01f) : 0.0f;
+						           const float d3 = (4 * sq + 3 < valid) ? s3 * act_der_b(av.w, act, 0.01f) : 0.0f;
+						           if (gather)
+						           {
+							           const uint32_t local = dt_addr + (uint32_t)(((drow + nn) * CF_R + 4 * sq) * 4);
+#pragma unroll
+							           for (int dst = 0; dst < CF_CS; ++dst) cl_store4(cl_map(local, (uint32_t)dst), d0, d1, d2, d3);
+						           }
+						           float* gd = a.delbuf + (size_t)(j0 + 4 * sq) * tot + node + nn;
+						           if (4 * sq + 0 < valid) gd[0] = d0;
+						           if (4 * sq + 1 < valid) gd[(size_t)tot] = d1;
+						           if (4 * sq + 2 < valid) gd[(size_t)2 * tot] = d2;
+						           if (4 * sq + 3 < valid) gd[(size_t)3 * tot] = d3;
+					           });
+					if (gather) cl_sync();
+				}
+				// the inputs of the pass belong to the window scratch too (phase 2 of layer 0 reads them)
+				{
+					const int n0 = n.sizes[0];
+					for (int e = t + crank * GF_THREADS; e < valid * n0; e += GF_THREADS * CF_CS)
+					{
+						const int r = e / n0, i = e - r * n0;
+						a.actbuf[(size_t)(j0 + r) * tot + i] = AT[(size_t)i * CF_R + r];
+					}
+				}
+				if (crank == 0)
+				{
+					if (warp >= 1 && warp <= H)
+					{
+						// scalar-bias delta of hidden layer `warp`: sum of the deltas of the layer above, this pass's rows
+						const int l = warp, no = n.sizes[l + 1];
+						double s = 0.0;
+						for (int e = lane; e < no * CF_R; e += 32) s += (double)DT[(size_t)P.d_off[l + 1] * CF_R + e];
+						s = warp_sum_d(s);
+						if (lane == 0) s_part[2 + l] += s;
+					}
+					if (t == 0)
+					{
+						for (int r = 0; r < valid; ++r)
+						{
+							s_part[0] += (double)rowm[2 * r];
+							s_part[1] += (double)rowm[2 * r + 1];
+						}
+					}
+				}
+				cl_sync();  // nobody of the cluster reads this pass's buffers any more: the next pass may overwrite them
+			}
+			__syncthreads();
+			if (t < GF_PART) a.part[(size_t)blockIdx.x * GF_PART + t] = s_part[t];
+			if (timed) { t_b = now(); tm[0] += t_b - t_a; }
+			grid.sync();
+			if (timed) { t_a = now(); tm[1] += t_a - t_b; }
+
+			// ================= phase 2: gradient + update per weight tile; CTA 0 also the scalars
+			const float inv_len = 1.0f / (float)len;
+			for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x)
+			{
+				int l = 0;
+				while (tile >= tile_off[l + 1]) ++l;
+				const int tiles_i = (n.sizes[l] + CF_TI - 1) / CF_TI;
+				const int tl = tile - tile_off[l];
+				const float* ckl = a.ck + (size_t)l * (mb + 1);
+				__syncthreads();  // the previous work item's buffers are no longer read
+				if (n.sizes[l + 1] <= GF_NARROW)
+					gf_grad_narrow(a, l, tl * GF_NCOLS, len, tot, P.node_off[l], P.node_off[l + 1], ckl, inv_len, Dt, bad);
+				else
+					cf_grad_tile(a, l, (tl / tiles_i) * GF_TO, (tl % tiles_i) * CF_TI, len, tot, P.node_off[l], P.node_off[l + 1], Dt, At, Ct,
+					             red, ckl, inv_len, bad);
+			}
+			if (blockIdx.x == 0)
+			{
+				if (warp >= 1 && warp <= H)
+				{
+					const int l = warp;
+					double s = 0.0;
+					for (int b = lane; b < (int)gridDim.x; b += 32) s += __ldcg(a.part + (size_t)b * GF_PART + 2 + l);
+					s = warp_sum_d(s) * (double)n.lr[l];
+					if (lane == 0)
+					{
+						const float nb = __ldcg(n.bias + l) -
+						                 ((a.bias_rule == GL_BIAS_REFERENCE) ? (float)(s * (double)n.sizes[l]) : (float)(s / (double)len));
+						if (!isfinite(nb)) bad = 1;
+						n.bias[l] = nb;
+					}
+				}
+				if (warp == 0)
+				{
+					double c = 0.0, q = 0.0;
+					for (int b = lane; b < (int)gridDim.x; b += 32)
+					{
+						c += __ldcg(a.part + (size_t)b * GF_PART);
+						q += __ldcg(a.part + (size_t)b * GF_PART + 1);
+					}
+					c = warp_sum_d(c);
+					q = warp_sum_d(q);
+					if (lane == 0)
+					{
+						ecost += c;
+						eacc += q;
+					}
+				}
+			}
+			if (timed) { t_b = now(); tm[2] += t_b - t_a; }
+			grid.sync();
+			if (timed) { t_a = now(); tm[3] += t_a - t_b; }
+		}
+		if (blockIdx.x == 0 && t == 0)
+		{
+			a.epoch_sums[2 * ep] = ecost;
+			a.epoch_sums[2 * ep + 1] = eacc;
+		}
+	}
+	if (timed)
+		for (int k = 0; k < 4; ++k) a.timing[k] += tm[k];
+	if (bad) atomicOr(a.flags, 1);
+}
+
 }  // namespace
 
 size_t grid_fused_smem_bytes(const NetView& n)
@@ -812,18 +1433,85 @@ int grid_fused_pick_nc(const NetView& n, int ctas)
 cudaError_t launch_grid_fused(const GridFusedArgs& a, cudaStream_t s)
 {
 	const size_t bytes = grid_fused_smem_bytes(a.net);
-	static size_t attr_bytes = 0;
-	if (bytes > attr_bytes)
 	{
+		// the attribute belongs to the current device: set it per launch (a cheap call) rather than cache it per process
 		cudaError_t e = cudaFuncSetAttribute(grid_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
 		if (e != cudaSuccess) return e;
-		attr_bytes = bytes;
 	}
 	if (a.part_ctas < 1 || (a.nc != 2 && a.nc != 4)) return cudaErrorInvalidValue;
 	GridFusedArgs copy = a;
 	void* params[] = {&copy};
 	// one CTA per SM (the shared-memory footprint allows no more), all co-resident as the grid barrier needs
 	return cudaLaunchCooperativeKernel((void*)grid_fused_kernel, dim3((unsigned)a.part_ctas), dim3(GF_THREADS), params, bytes, s);
+}
+
+// ---- cluster variant: host side ------------------------------------------------------------------
+size_t cluster_fused_smem_bytes(const NetView& n)
+{
+	CfPlan p;
+	cf_plan(n, p);
+	return (size_t)p.floats * sizeof(float);
+}
+
+// The variant wants every layer that is read as an input (0..H) to be a multiple of 4 nodes (16-byte rows for
+// the vector loads), at least one hidden layer, and its buffers inside one SM's shared memory.
+bool cluster_fused_fits(const NetView& n)
+{
+	if (n.H < 1) return false;
+	for (int l = 0; l <= n.H; ++l)
+		if (n.sizes[l] % 4 != 0) return false;
+	return cluster_fused_smem_bytes(n) <= (size_t)226 * 1024;
+}
+
+static cudaError_t cluster_fused_config(const NetView& n, cudaLaunchConfig_t& cfg, cudaLaunchAttribute* attrs, unsigned grid, cudaStream_t s)
+{
+	const size_t bytes = cluster_fused_smem_bytes(n);
+	cudaError_t e = cudaFuncSetAttribute(cluster_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+	if (e != cudaSuccess) return e;
+	memset(&cfg, 0, sizeof cfg);
+	cfg.gridDim = dim3(grid);
+	cfg.blockDim = dim3(GF_THREADS);
+	cfg.dynamicSmemBytes = bytes;
+	cfg.stream = s;
+	attrs[0].id = cudaLaunchAttributeClusterDimension;
+	attrs[0].val.clusterDim.x = CF_CS;
+	attrs[0].val.clusterDim.y = 1;
+	attrs[0].val.clusterDim.z = 1;
+	attrs[1].id = cudaLaunchAttributeCooperative;
+	attrs[1].val.cooperative = 1;
+	cfg.attrs = attrs;
+	cfg.numAttrs = 2;
+	return cudaSuccess;
+}
+
+// CTAs of the largest co-resident grid of whole clusters on the current device (0: the variant cannot run here)
+int cluster_fused_max_ctas(const NetView& n)
+{
+	cudaLaunchConfig_t cfg;
+	cudaLaunchAttribute attrs[2];
+	if (cluster_fused_config(n, cfg, attrs, CF_CS, 0) != cudaSuccess)
+	{
+		cudaGetLastError();
+		return 0;
+	}
+	cfg.numAttrs = 1;  // the occupancy query takes the cluster shape; co-residency is what it reports
+	int clusters = 0;
+	if (cudaOccupancyMaxActiveClusters(&clusters, cluster_fused_kernel, &cfg) != cudaSuccess)
+	{
+		cudaGetLastError();
+		return 0;
+	}
+	return clusters * CF_CS;
+}
+
+cudaError_t launch_cluster_fused(const GridFusedArgs& a, cudaStream_t s)
+{
+	if (a.part_ctas < CF_CS || a.part_ctas % CF_CS != 0) return cudaErrorInvalidValue;
+	cudaLaunchConfig_t cfg;
+	cudaLaunchAttribute attrs[2];
+	cudaError_t e = cluster_fused_config(a.net, cfg, attrs, (unsigned)a.part_ctas, s);
+	if (e != cudaSuccess) return e;
+	return cudaLaunchKernelEx(&cfg, cluster_fused_kernel, a);
 }
 
 }  // namespace glb

@@ -193,6 +193,13 @@ int grid_fused_group_tiles(const NetView& n);
 // smallest tile width whose tile count does not exceed `ctas` (else 4)
 int grid_fused_pick_nc(const NetView& n, int ctas);
 cudaError_t launch_grid_fused(const GridFusedArgs& a, cudaStream_t s);
+// cluster variant (thread-block clusters of 8 CTAs share a group of rows, every CTA owning an eighth of each
+// layer's nodes with their weights resident in shared memory): same arguments, part_ctas = a multiple of 8 that
+// cluster_fused_max_ctas allows; nc and tma are not used
+bool cluster_fused_fits(const NetView& n);
+size_t cluster_fused_smem_bytes(const NetView& n);
+int cluster_fused_max_ctas(const NetView& n);
+cudaError_t launch_cluster_fused(const GridFusedArgs& a, cudaStream_t s);
 
 // ---- data-parallel gradient exchange over peer memory (dp_push.cu) ---------------------------------
 // Every rank owns an exchange arena that all ranks map: a flag area of DP_FLAG_BYTES (32-bit window

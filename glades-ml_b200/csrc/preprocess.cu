@@ -165,12 +165,12 @@ __global__ void __launch_bounds__(256) transform_kernel(const float* __restrict_
 
 }  // namespace
 
-// blocks of 256 threads for a pass over rows * cols cells: about eight cells per thread, at most 16 blocks per SM,
-// and a multiple of cols, so that the grid size is a multiple of cols (a thread then stays on one column)
-static unsigned column_pass_blocks(long long total, int cols)
+// blocks of 256 threads for a pass over rows * cols cells: about eight cells per thread, at most per_sm blocks per
+// SM, and a multiple of cols, so that the grid size is a multiple of cols (a thread then stays on one column)
+static unsigned column_pass_blocks(long long total, int cols, int per_sm)
 {
 	long long blocks = (total / 8 + 255) / 256;
-	const long long cap = 148ll * 16;
+	const long long cap = 148ll * per_sm;
 	if (blocks > cap) blocks = cap;
 	if (blocks < 1) blocks = 1;
 	blocks = ((blocks + cols - 1) / cols) * cols;
@@ -182,7 +182,8 @@ cudaError_t launch_column_minmax(const float* raw, long long rows, int cols, int
 	const long long total = rows * (long long)cols;
 	if (total < 1) return cudaSuccess;
 	if (cols > 6000) return cudaErrorInvalidValue;  // the block's extrema live in shared memory
-	minmax_kernel<<<column_pass_blocks(total, cols), 256, (size_t)2 * cols * sizeof(int), s>>>(raw, rows, cols, d_stats);
+	// every block ends with two atomics per column on the same 2 * cols words: fewer, longer blocks
+	minmax_kernel<<<column_pass_blocks(total, cols, 6), 256, (size_t)2 * cols * sizeof(int), s>>>(raw, rows, cols, d_stats);
 	return cudaGetLastError();
 }
 
@@ -197,7 +198,7 @@ cudaError_t launch_column_transform(const float* raw, long long rows, int cols, 
 {
 	const long long total = rows * (long long)cols;
 	if (total < 1) return cudaSuccess;
-	transform_kernel<<<column_pass_blocks(total, cols), 256, 0, s>>>(raw, rows, cols, static_cast<const ColumnPlan*>(d_plan), d_stats, flag,
+	transform_kernel<<<column_pass_blocks(total, cols, 16), 256, 0, s>>>(raw, rows, cols, static_cast<const ColumnPlan*>(d_plan), d_stats, flag,
 	                                                  classification, X, ldx, Y, ldy);
 	return cudaGetLastError();
 }

@@ -266,12 +266,34 @@ GRID_FUSED_EXTRA = [
 ]
 
 
-@pytest.mark.parametrize("engine", ["ffma", "grid_fused"])
+def _cluster_variant_applies(sizes):
+    """The whole-window kernel's thread-block-cluster variant takes networks with a hidden layer whose input and
+    hidden widths are multiples of 4 and whose per-CTA buffers fit one SM's shared memory (the same arithmetic as
+    the library's cf_plan)."""
+    H = len(sizes) - 2
+    if H < 1 or any(s % 4 for s in sizes[:-1]):
+        return False
+    r4 = lambda v: (v + 3) & ~3
+    sl = [r4((s + 7) // 8) for s in sizes]
+    floats = (sum(sizes) + sum(r4(s) for s in sizes[1:])) * 32
+    floats += sum(sl[l + 1] * (sizes[l] + 4) for l in range(H + 1))
+    floats += sum(sl[j] * (r4(sizes[j + 1]) + 4) for j in range(1, H + 1)) + 64
+    return floats * 4 <= 226 * 1024
+
+
+@pytest.mark.parametrize("engine", ["ffma", "grid_fused", "grid_fused_no_cluster"])
 @pytest.mark.parametrize("case", BATCHED_CASES + GRID_FUSED_EXTRA, ids=lambda c: "-".join(map(str, c[0])) + "_" + str(c[3]))
-def test_batched_window_vs_restatement(g, oracle, case, engine):
+def test_batched_window_vs_restatement(g, oracle, monkeypatch, case, engine):
     """One minibatch window, per-layer products on the FFMA kernel vs the whole window in one
-    cooperative launch (grid_fused): both against the CPU restatement of the batched arithmetic."""
+    cooperative launch (grid_fused; its cluster variant where the network allows it, and the plain variant
+    forced): all against the CPU restatement of the batched arithmetic."""
     sizes, acts, out, rows, mom, wd1, wd2, brule = case
+    if engine == "grid_fused_no_cluster":
+        if not _cluster_variant_applies(sizes):
+            pytest.skip("the plain variant is what the grid_fused case of this network runs already")
+        monkeypatch.setenv("GLADES_GF_CLUSTER", "0")
+    else:
+        monkeypatch.delenv("GLADES_GF_CLUSTER", raising=False)
     rng = np.random.default_rng(sum(sizes) + rows)
     params = [0.05 if a == "leaky" else 1.0 for a in acts]
     d = g.make_desc(sizes, acts, out, batch=rows, lr=0.05 if rows < 1000 else 0.002, momentum=mom, wd1=wd1, wd2=wd2,
@@ -292,8 +314,10 @@ def test_batched_window_vs_restatement(g, oracle, case, engine):
     for step in range(2):  # two steps: the second one starts from updated weights
         l0 = net.kernel_launches()
         m = net.train_window(0, rows)
-        if engine == "grid_fused":
+        if engine.startswith("grid_fused"):
             assert net.kernel_launches() - l0 == 1, "the whole window must be one cooperative launch"
+            want_cluster = engine == "grid_fused" and _cluster_variant_applies(sizes)
+            assert (net.window_cluster_ctas() > 0) == want_cluster, net.window_cluster_ctas()
         cm = np.zeros((sizes[-1], sizes[-1]), np.int32)
         gr = S.window_grad(0, rows, confusion=cm)
         S.window_apply(gr, rows)
@@ -528,11 +552,18 @@ GRID_FUSED_EPOCH_CASES = [
 ]
 
 
+@pytest.mark.parametrize("cluster", ["cluster", "plain"])
 @pytest.mark.parametrize("case", GRID_FUSED_EPOCH_CASES, ids=lambda c: "-".join(map(str, c[0])) + "_mb%d" % c[4])
-def test_grid_fused_epochs_vs_restatement(g, oracle, case):
+def test_grid_fused_epochs_vs_restatement(g, oracle, monkeypatch, case, cluster):
     """Whole training runs (epochs x windows, ragged tail included) of a mid-size network in ONE
-    cooperative launch, checked against the restatement walked window by window."""
+    cooperative launch, checked against the restatement walked window by window -- on the cluster variant of
+    the kernel and on the plain one."""
     sizes, acts, out, rows, mb, mom, brule, epochs = case
+    if cluster == "plain":
+        monkeypatch.setenv("GLADES_GF_CLUSTER", "0")
+    else:
+        monkeypatch.delenv("GLADES_GF_CLUSTER", raising=False)
+        assert _cluster_variant_applies(sizes)
     rng = np.random.default_rng(len(sizes) * 100 + rows)
     d = g.make_desc(sizes, acts, out, batch=mb, lr=0.002 if mb > 500 else 0.05, momentum=mom, mode=g.MODE_BATCHED,
                     bias_rule=brule, gemm=g.GEMM_GRID_FUSED)
@@ -554,6 +585,7 @@ def test_grid_fused_epochs_vs_restatement(g, oracle, case):
     l0 = net.kernel_launches()
     m = net.train_epochs(epochs)
     assert net.kernel_launches() - l0 == 1
+    assert (net.window_cluster_ctas() > 0) == (cluster == "cluster"), net.window_cluster_ctas()
     for ep in range(epochs):
         cm = np.zeros((sizes[-1], sizes[-1]), np.int32)
         cost = acc = 0.0
