@@ -236,7 +236,7 @@ struct gl_net
 	void* gfMaps = nullptr;  // device array of the weight tensor maps (NULL: the register path)
 	bool gfMapsTried = false;
 	unsigned long long* gfTiming = nullptr;  // GLADES_GF_TIMING=1: phase nanoseconds, printed when the handle goes
-	int gfRows = 0, gfCtas = 0, gfCkMb = 0, gfNc = 2;
+	int gfRows = 0, gfCtas = 0, gfCkMb = 0;
 	int gfOk = -1;  // -1 not decided yet
 	int gfClusterCtas = -1;  // CTAs of the cluster variant's grid; 0: the variant does not apply; -1 not decided yet
 
@@ -504,10 +504,15 @@ extern "C" int gl_destroy(gl_net* n)
 	cudaFree(n->dXwin); cudaFree(n->dYwin);
 	if (n->gfTiming)
 	{
-		unsigned long long tm[4] = {0, 0, 0, 0};
+		unsigned long long tm[16] = {};
 		if (cudaMemcpy(tm, n->gfTiming, sizeof tm, cudaMemcpyDeviceToHost) == cudaSuccess)
+		{
 			fprintf(stderr, "[grid-fused] CTA 0: phase 1 %.3f ms, barrier %.3f ms, phase 2 %.3f ms, barrier %.3f ms\n", tm[0] * 1e-6,
 			        tm[1] * 1e-6, tm[2] * 1e-6, tm[3] * 1e-6);
+			if (tm[4])
+				fprintf(stderr, "[grid-fused] cluster variant, inside phase 1: weights %.3f ms, forward %.3f ms, head %.3f ms, deltas %.3f ms, pass end %.3f ms\n",
+				        tm[4] * 1e-6, tm[5] * 1e-6, tm[6] * 1e-6, tm[7] * 1e-6, tm[8] * 1e-6);
+		}
 		cudaFree(n->gfTiming);
 	}
 	cudaFree(n->gfAct); cudaFree(n->gfDel); cudaFree(n->gfPart); cudaFree(n->gfCk); cudaFree(n->gfMaps);
@@ -1296,7 +1301,7 @@ static int grid_fused_launch(gl_net* n, const float* X, const float* Y, int64_t 
                              double* epoch_sums)
 {
 	const NetView base = make_view(n);
-	const int tot = grid_fused_total_nodes(base);
+	const int tot = grid_fused_scratch_pitch(base);
 	if (n->gfRows < mb)
 	{
 		cudaFree(n->gfAct);
@@ -1313,14 +1318,14 @@ static int grid_fused_launch(gl_net* n, const float* X, const float* Y, int64_t 
 		CU(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, n->d.device));
 		n->gfCtas = sms;
 		CU(cudaMalloc(&n->gfPart, (size_t)sms * (2 + GL_MAX_WEIGHT_LAYERS) * sizeof(double)));
-		n->gfNc = grid_fused_pick_nc(base, sms);
 	}
 	if (n->gfClusterCtas < 0)
 	{
-		// the cluster variant where the network allows it and the device can hold whole clusters (GLADES_GF_CLUSTER=0: never)
+		// the cluster variant only on request (GLADES_GF_CLUSTER=1; it measured slower than the plain kernel), where the
+		// network allows it and the device can hold whole clusters
 		const char* e = getenv("GLADES_GF_CLUSTER");
 		int ctas = 0;
-		if (!(e && atoi(e) == 0) && cluster_fused_fits(base))
+		if (e && atoi(e) == 1 && cluster_fused_fits(base))
 		{
 			bool aligned = true;
 			for (int l = 0; l <= n->H; ++l) aligned = aligned && n->woff[l] % 4 == 0;
@@ -1391,7 +1396,6 @@ static int grid_fused_launch(gl_net* n, const float* X, const float* Y, int64_t 
 	a.part = n->gfPart;
 	a.part_ctas = n->gfCtas;
 	a.ck = n->gfCk;
-	a.nc = n->gfNc;
 	a.tma = n->gfMaps;
 	a.epoch_sums = epoch_sums;
 	a.confusion = n->dConf;
@@ -1401,8 +1405,8 @@ static int grid_fused_launch(gl_net* n, const float* X, const float* Y, int64_t 
 	if (want_timing < 0) want_timing = getenv("GLADES_GF_TIMING") ? 1 : 0;
 	if (want_timing && !n->gfTiming)
 	{
-		CU(cudaMalloc(&n->gfTiming, 4 * sizeof(unsigned long long)));
-		CU(cudaMemset(n->gfTiming, 0, 4 * sizeof(unsigned long long)));
+		CU(cudaMalloc(&n->gfTiming, 16 * sizeof(unsigned long long)));
+		CU(cudaMemset(n->gfTiming, 0, 16 * sizeof(unsigned long long)));
 	}
 	a.timing = n->gfTiming;
 	const bool cluster = n->gfClusterCtas > 0 && (((uintptr_t)X | (uintptr_t)Y) & 15) == 0;

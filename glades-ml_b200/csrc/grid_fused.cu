@@ -30,180 +30,236 @@ namespace {
 constexpr int GF_THREADS = 256;
 constexpr int GF_ROWS = 8;      // samples a CTA carries through the network together
 constexpr int GF_WT = 256 * 33;  // floats of the weight-tile buffer ([256][33] forward, [32][256] backward)
-constexpr int GF_TO = 16, GF_TJ = 64;  // phase 2: weight tile 16 outputs x (16 * NC) inputs, 64 rows per step
-constexpr int GF_TI_MAX = 64;           // NC (weights per thread) is 2 or 4
+constexpr int GF_TO = 16, GF_TJ = 64;  // phase 2: weight tile 16 outputs x 32 inputs, 64 rows per stage
 constexpr int GF_NS = 3;                // stages of the weight-tile ring (bulk tensor copies, 32 KB each)
 constexpr int GF_STAGE = 32768;
 constexpr int GF_SEQ_MAX = 512;         // weight tiles one sample group walks through, at most, on the ring path
 static_assert(GF_WT * 4 <= GF_NS * GF_STAGE, "the register-path tile buffer lives inside the ring");
 constexpr int GF_PART = 2 + GL_MAX_WEIGHT_LAYERS;  // doubles per CTA: cost, accuracy, bias-delta sums per layer
 
-// Phase 2, one 16 x (16 * NC) tile of layer l's weights: thread = one output row, NC input columns;
-// sums c_j * (lr * d_jo * a_ji + decay terms) over the window's rows in row order and applies the
-// update in place.  The 64-row tiles of deltas / activations / momentum weights travel global ->
-// registers -> shared memory, the next step's loads in flight while the current one is consumed.
-template <int NC>
-__device__ __forceinline__ void gf_grad_tile(const GridFusedArgs& a, int l, int o0, int i0, int len, int tot, int off_in,
-                                             int off_out, float* Dt, float* At, float* Ct, const float* ckl, float inv_len,
-                                             int& bad)
+// ---- phase 2, asynchronous fill ------------------------------------------------------------------
+// One 16 x 32 tile of layer l's weights.  The window's deltas and activations reach shared memory through a ring
+// of GF_P2_STAGES 64-row stages filled by 4-byte cp.async copies (zero-filled outside the window or the layer):
+// three stages are in flight while one is consumed, so a step no longer waits one L2 round trip (the former
+// global -> registers -> shared memory fill with one step of prefetch did: 16 steps x 1.2 us per tile).
+// Lane = 4 outputs x 4 inputs (four output groups x eight input groups: 16 multiply-adds per two 16-byte loads),
+// warp w takes rows 8w..8w+7 of every stage; the eight warps' partial sums are added in warp order and the update
+// is applied in place.  Deterministic; the sum is no longer one chain in row order.
+constexpr int GF_P2_TI = 32;
+constexpr int GF_P2_STAGES = 6;   // tile path: five stages in flight while one is consumed
+constexpr int GF_P2N_STAGES = 4;  // narrow-layer path (its stages are larger)
+constexpr int GF_P2_STAGE_FLOATS = GF_TJ * GF_TO + GF_TJ * GF_P2_TI + GF_TJ;          // deltas, activations, momentum weights
+constexpr int GF_P2_FLOATS = GF_P2_STAGES * GF_P2_STAGE_FLOATS + 8 * GF_TO * GF_P2_TI;  // + the warps' partial sums
+static_assert(GF_P2_FLOATS * 4 <= GF_NS * GF_STAGE, "the phase-2 stages live inside the weight-tile ring");
+static_assert((GF_P2_STAGE_FLOATS * 4) % 16 == 0, "stages keep the 16-byte alignment of the vector loads");
+
+__device__ __forceinline__ void cp_async4(uint32_t dst, const float* src, bool valid)
 {
-	constexpr int TI = 16 * NC;
-	constexpr int NA = GF_TJ * TI / GF_THREADS;  // activation values per thread and step
+	const int bytes = valid ? 4 : 0;  // 0: nothing is read, the destination is zero-filled
+	asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+}
+// 16 bytes, of which the first `floats` (0..4) values are read and the rest zero-filled; both addresses 16-byte aligned
+__device__ __forceinline__ void cp_async16(uint32_t dst, const float* src, int floats)
+{
+	const int bytes = floats <= 0 ? 0 : (floats >= 4 ? 16 : floats * 4);
+	asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+__device__ __forceinline__ void gf_grad_tile_async(const GridFusedArgs& a, int l, int o0, int i0, int len, int pitch, int off_in,
+                                                   int off_out, float* stages, const float* ckl, float inv_len, int& bad)
+{
 	const NetView& n = a.net;
-	const int t = threadIdx.x;
+	const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
 	const int ni = n.sizes[l], no = n.sizes[l + 1];
 	const float lr = n.lr[l], w1 = n.wd1[l] * lr, w2 = n.wd2[l] * lr;
 	const bool decay = w1 != 0.0f || w2 != 0.0f;
-	const int oo = t >> 4, ic = (t & 15) * NC;
-	float g[NC];
+	const int og = lane >> 3, ig = lane & 7;
+	float* red = stages + GF_P2_STAGES * GF_P2_STAGE_FLOATS;
+	const uint32_t st_addr = smem_u32(stages);
+	float g[4][4];
 #pragma unroll
-	for (int c = 0; c < NC; ++c) g[c] = 0.0f;
-	float pd[4], pa[NA], pc = 0.0f;
-	auto fetch = [&](int jb) {
-		const int jn = (len - jb) < GF_TJ ? (len - jb) : GF_TJ;
+	for (int x = 0; x < 4; ++x)
 #pragma unroll
-		for (int k = 0; k < 4; ++k)
+		for (int y = 0; y < 4; ++y) g[x][y] = 0.0f;
+	const int steps = (len + GF_TJ - 1) / GF_TJ;
+	// one 16-byte copy of deltas and two of activations per thread and stage (the scratch rows and the layers'
+	// first columns are 16-byte aligned), one 4-byte copy of a momentum weight for the first 64 threads
+	const int d_jj = t >> 2, d_x = (t & 3) << 2;
+	auto issue = [&](int s) {
+		if (s < steps)
 		{
-			const int e = t + k * GF_THREADS, jj = e / GF_TO, x = e - jj * GF_TO;
-			pd[k] = (jj < jn && o0 + x < no) ? __ldcg(a.delbuf + (size_t)(jb + jj) * tot + off_out + o0 + x) : 0.0f;
-		}
+			const int jb = s * GF_TJ;
+			const int jn = (len - jb) < GF_TJ ? (len - jb) : GF_TJ;
+			const uint32_t base = st_addr + (uint32_t)((s % GF_P2_STAGES) * GF_P2_STAGE_FLOATS * 4);
+			{
+				const int left = (d_jj < jn) ? no - (o0 + d_x) : 0;
+				cp_async16(base + (uint32_t)t * 16, left > 0 ? a.delbuf + (size_t)(jb + d_jj) * pitch + off_out + o0 + d_x : a.delbuf, left);
+			}
 #pragma unroll
-		for (int k = 0; k < NA; ++k)
-		{
-			const int e = t + k * GF_THREADS, jj = e / TI, x = e - jj * TI;
-			pa[k] = (jj < jn && i0 + x < ni) ? __ldcg(a.actbuf + (size_t)(jb + jj) * tot + off_in + i0 + x) : 0.0f;
+			for (int k = 0; k < 2; ++k)
+			{
+				const int e = t + k * GF_THREADS, jj = e >> 3, x = (e & 7) << 2;
+				const int left = (jj < jn) ? ni - (i0 + x) : 0;
+				cp_async16(base + (uint32_t)(GF_TJ * GF_TO * 4) + (uint32_t)e * 16,
+				           left > 0 ? a.actbuf + (size_t)(jb + jj) * pitch + off_in + i0 + x : a.actbuf, left);
+			}
+			if (t < GF_TJ)
+			{
+				const bool ok = t < jn;
+				cp_async4(base + (uint32_t)(GF_TJ * GF_TO + GF_TJ * GF_P2_TI + t) * 4, ok ? ckl + (len - (jb + t)) : ckl, ok);
+			}
 		}
-		if (t < GF_TJ) pc = (t < jn) ? ckl[len - (jb + t)] : 0.0f;
+		cp_async_commit();  // one group per step, empty ones included: the wait counts groups
 	};
-	fetch(0);
-	for (int jb = 0; jb < len; jb += GF_TJ)
+	__syncthreads();  // the previous work item no longer reads the stages
+#pragma unroll
+	for (int s = 0; s < GF_P2_STAGES - 1; ++s) issue(s);
+	for (int s = 0; s < steps; ++s)
 	{
-		const int jn = (len - jb) < GF_TJ ? (len - jb) : GF_TJ;
-		__syncthreads();
-		if (t < GF_TJ) Ct[t] = pc;
-#pragma unroll
-		for (int k = 0; k < NA; ++k) At[t + k * GF_THREADS] = pa[k];
-		if (decay)
+		cp_async_wait<GF_P2_STAGES - 2>();  // this thread's copies of stage s have landed
+		__syncthreads();                    // everybody's have; and stage s - 1 is no longer read
+		issue(s + GF_P2_STAGES - 1);        // refills the stage consumed in the previous step
+		const float* Dt = stages + (s % GF_P2_STAGES) * GF_P2_STAGE_FLOATS;
+		const float* At = Dt + GF_TJ * GF_TO;
+		const float* Ct = At + GF_TJ * GF_P2_TI;
+#pragma unroll 4
+		for (int q = 0; q < 8; ++q)
 		{
-#pragma unroll
-			for (int k = 0; k < 4; ++k) Dt[t + k * GF_THREADS] = pd[k];
-		}
-		else
-		{
-			// no decay terms: the tile holds c_j * lr * d_jo, and a row costs one multiply-add per weight.
-			// (c_j of row jj = e / 16 comes from the table again: Ct is only complete after the barrier.)
-#pragma unroll
-			for (int k = 0; k < 4; ++k)
-			{
-				const int jj = (t + k * GF_THREADS) / GF_TO;
-				Dt[t + k * GF_THREADS] = (jj < jn) ? pd[k] * lr * ckl[len - (jb + jj)] : 0.0f;
-			}
-		}
-		__syncthreads();
-		if (jb + GF_TJ < len) fetch(jb + GF_TJ);
-		auto step = [&](int jj) {
+			const int jj = warp * 8 + q;  // rows beyond the window hold zeros
+			const float4 dv = *reinterpret_cast<const float4*>(Dt + jj * GF_TO + og * 4);
+			const float4 av = *reinterpret_cast<const float4*>(At + jj * GF_P2_TI + ig * 4);
 			const float c = Ct[jj];
-			const float dv = lr * Dt[jj * GF_TO + oo];
-			float av[NC];
-			if (NC == 2)
+			const float d4[4] = {dv.x, dv.y, dv.z, dv.w};
+			const float a4[4] = {av.x, av.y, av.z, av.w};
+			if (!decay)
 			{
-				const float2 v = *reinterpret_cast<const float2*>(At + jj * TI + ic);
-				av[0] = v.x; av[1] = v.y;
-			}
-			else
-			{
-				const float4 v = *reinterpret_cast<const float4*>(At + jj * TI + ic);
-				av[0] = v.x; av[1] = v.y; av[NC - 2] = v.z; av[NC - 1] = v.w;
-			}
+				// c_j * lr * d_jo first (rounded as the staged fill used to round it), then one multiply-add per weight
 #pragma unroll
-			for (int q = 0; q < NC; ++q) g[q] = fmaf(c, fmaf(dv, av[q], fmaf(w1, fabsf(av[q]), w2 * av[q])), g[q]);
-		};
-		auto fast = [&](int jj) {
-			const float dv = Dt[jj * GF_TO + oo];
-			if (NC == 2)
-			{
-				const float2 v = *reinterpret_cast<const float2*>(At + jj * TI + ic);
-				g[0] = fmaf(dv, v.x, g[0]); g[1] = fmaf(dv, v.y, g[1]);
+				for (int x = 0; x < 4; ++x)
+				{
+					const float dx = d4[x] * lr * c;
+#pragma unroll
+					for (int y = 0; y < 4; ++y) g[x][y] = fmaf(dx, a4[y], g[x][y]);
+				}
 			}
 			else
 			{
-				const float4 v = *reinterpret_cast<const float4*>(At + jj * TI + ic);
-				g[0] = fmaf(dv, v.x, g[0]); g[1] = fmaf(dv, v.y, g[1]);
-				g[NC - 2] = fmaf(dv, v.z, g[NC - 2]); g[NC - 1] = fmaf(dv, v.w, g[NC - 1]);
+				float dec[4];
+#pragma unroll
+				for (int y = 0; y < 4; ++y) dec[y] = fmaf(w1, fabsf(a4[y]), w2 * a4[y]);
+#pragma unroll
+				for (int x = 0; x < 4; ++x)
+#pragma unroll
+					for (int y = 0; y < 4; ++y) g[x][y] = fmaf(c, fmaf(lr * d4[x], a4[y], dec[y]), g[x][y]);
 			}
-		};
-		if (!decay)
-		{
-			if (jn == GF_TJ)
-			{
-				// full step: a fixed trip count lets the shared-memory loads of several rows overlap
-#pragma unroll 4
-				for (int jj = 0; jj < GF_TJ; ++jj) fast(jj);
-			}
-			else
-				for (int jj = 0; jj < jn; ++jj) fast(jj);
 		}
-		else if (jn == GF_TJ)
-		{
-#pragma unroll 4
-			for (int jj = 0; jj < GF_TJ; ++jj) step(jj);
-		}
-		else
-			for (int jj = 0; jj < jn; ++jj) step(jj);
 	}
-	const int o = o0 + oo;
-	if (o < no)
-	{
-		float* wp = n.W[l] + (size_t)o * ni + i0 + ic;
+	cp_async_wait<0>();
+	// the warps' partial sums: red[warp][output 0..15][input 0..31] (not part of the stages)
 #pragma unroll
-		for (int q = 0; q < NC; ++q)
+	for (int x = 0; x < 4; ++x)
+		*reinterpret_cast<float4*>(red + warp * (GF_TO * GF_P2_TI) + (og * 4 + x) * GF_P2_TI + ig * 4) = make_float4(g[x][0], g[x][1], g[x][2], g[x][3]);
+	__syncthreads();
+#pragma unroll
+	for (int k = 0; k < GF_TO * GF_P2_TI / GF_THREADS; ++k)
+	{
+		const int e = t + k * GF_THREADS;
+		const int o = o0 + e / GF_P2_TI, i = i0 + (e & (GF_P2_TI - 1));
+		float sum = red[e];
+#pragma unroll
+		for (int w = 1; w < 8; ++w) sum += red[w * (GF_TO * GF_P2_TI) + e];
+		if (o < no && i < ni)
 		{
-			if (i0 + ic + q < ni)
-			{
-				const float w = __ldcg(wp + q) - g[q] * inv_len;
-				if (!isfinite(w)) bad = 1;
-				wp[q] = w;
-			}
+			float* wp = n.W[l] + (size_t)o * ni + i;
+			const float wv = __ldcg(wp) - sum * inv_len;
+			if (!isfinite(wv)) bad = 1;
+			*wp = wv;
 		}
 	}
 }
 
 
-// Phase 2 for a layer with at most GF_NARROW output nodes (the usual regression head): one work item
-// per GF_NCOLS input columns; thread = one column and one quarter of the window's rows, straight from
-// the window scratch (coalesced activation reads, broadcast delta reads, several rows' loads in
-// flight); the four quarters are added in fixed order through shared memory.
+// Phase 2 for a layer with at most GF_NARROW output nodes (the usual regression head): one work item per GF_NCOLS
+// input columns, the same ring of 64-row stages (activations [64][64], deltas [64][4], momentum weights [64]);
+// thread = one column and the rows 16p..16p+15 of every stage (p = thread / 64); the four parts are added in fixed
+// order through shared memory.
 constexpr int GF_NARROW = 4;
 constexpr int GF_NCOLS = 64;
-__device__ __forceinline__ void gf_grad_narrow(const GridFusedArgs& a, int l, int i0, int len, int tot, int off_in, int off_out,
-                                               const float* ckl, float inv_len, float* red, int& bad)
+constexpr int GF_P2N_STAGE_FLOATS = GF_TJ * GF_NCOLS + GF_TJ * GF_NARROW + GF_TJ;
+constexpr int GF_P2N_FLOATS = GF_P2N_STAGES * GF_P2N_STAGE_FLOATS + GF_THREADS * GF_NARROW;
+static_assert(GF_P2N_FLOATS * 4 <= GF_NS * GF_STAGE, "the narrow-layer stages live inside the weight-tile ring");
+constexpr int GF_P2_MAX_FLOATS = GF_P2N_FLOATS > GF_P2_FLOATS ? GF_P2N_FLOATS : GF_P2_FLOATS;
+__device__ __forceinline__ void gf_grad_narrow(const GridFusedArgs& a, int l, int i0, int len, int pitch, int off_in, int off_out,
+                                               const float* ckl, float inv_len, float* stages, int& bad)
 {
 	const NetView& n = a.net;
+	const int t = threadIdx.x;
 	const int ni = n.sizes[l], no = n.sizes[l + 1];
-	const int col = (int)threadIdx.x & (GF_NCOLS - 1), part = (int)threadIdx.x / GF_NCOLS;  // 4 parts
+	const int col = t & (GF_NCOLS - 1), part = t / GF_NCOLS;  // 4 parts
 	const int i = i0 + col;
 	const float lr = n.lr[l], w1 = n.wd1[l] * lr, w2 = n.wd2[l] * lr;
+	float* red = stages + GF_P2N_STAGES * GF_P2N_STAGE_FLOATS;
+	const uint32_t st_addr = smem_u32(stages);
 	float g[GF_NARROW];
 #pragma unroll
 	for (int o = 0; o < GF_NARROW; ++o) g[o] = 0.0f;
-	if (i < ni)
-	{
-		const int q = (len + 3) / 4;
-		const int j_lo = part * q, j_hi = (j_lo + q) < len ? (j_lo + q) : len;
-		const float* ap = a.actbuf + off_in + i;
-		const float* dp = a.delbuf + off_out;
-#pragma unroll 8
-		for (int j = j_lo; j < j_hi; ++j)
+	const int steps = (len + GF_TJ - 1) / GF_TJ;
+	auto issue = [&](int s) {
+		if (s < steps)
 		{
-			const float av = __ldcg(ap + (size_t)j * tot);
-			const float c = ckl[len - j];
-			const float dec = fmaf(w1, fabsf(av), w2 * av);
+			const int jb = s * GF_TJ;
+			const int jn = (len - jb) < GF_TJ ? (len - jb) : GF_TJ;
+			const uint32_t base = st_addr + (uint32_t)((s % GF_P2N_STAGES) * GF_P2N_STAGE_FLOATS * 4);
 #pragma unroll
-			for (int o = 0; o < GF_NARROW; ++o)
-				if (o < no) g[o] = fmaf(c, fmaf(lr * __ldcg(dp + (size_t)j * tot + o), av, dec), g[o]);
+			for (int k = 0; k < 4; ++k)
+			{
+				const int e = t + k * GF_THREADS, jj = e >> 4, x = (e & 15) << 2;
+				const int left = (jj < jn) ? ni - (i0 + x) : 0;
+				cp_async16(base + (uint32_t)e * 16, left > 0 ? a.actbuf + (size_t)(jb + jj) * pitch + off_in + i0 + x : a.actbuf, left);
+			}
+			if (t < GF_TJ)
+			{
+				const int left = (t < jn) ? no : 0;
+				cp_async16(base + (uint32_t)(GF_TJ * GF_NCOLS * 4) + (uint32_t)t * 16, left > 0 ? a.delbuf + (size_t)(jb + t) * pitch + off_out : a.delbuf,
+				           left);
+			}
+			else if (t < 2 * GF_TJ)
+			{
+				const int r = t - GF_TJ;
+				const bool ok = r < jn;
+				cp_async4(base + (uint32_t)(GF_TJ * GF_NCOLS + GF_TJ * GF_NARROW + r) * 4, ok ? ckl + (len - (jb + r)) : ckl, ok);
+			}
+		}
+		cp_async_commit();
+	};
+	__syncthreads();  // the previous work item no longer reads the stages
+#pragma unroll
+	for (int s = 0; s < GF_P2N_STAGES - 1; ++s) issue(s);
+	for (int s = 0; s < steps; ++s)
+	{
+		cp_async_wait<GF_P2N_STAGES - 2>();
+		__syncthreads();
+		issue(s + GF_P2N_STAGES - 1);
+		const float* At = stages + (s % GF_P2N_STAGES) * GF_P2N_STAGE_FLOATS;
+		const float* Dt = At + GF_TJ * GF_NCOLS;
+		const float* Ct = Dt + GF_TJ * GF_NARROW;
+#pragma unroll 4
+		for (int q = 0; q < GF_TJ / 4; ++q)
+		{
+			const int jj = part * (GF_TJ / 4) + q;  // rows beyond the window hold zeros (c = 0)
+			const float av = At[jj * GF_NCOLS + col];
+			const float4 dv = *reinterpret_cast<const float4*>(Dt + jj * GF_NARROW);
+			const float c = Ct[jj];
+			const float dec = fmaf(w1, fabsf(av), w2 * av);
+			const float d4[4] = {dv.x, dv.y, dv.z, dv.w};
+#pragma unroll
+			for (int o = 0; o < GF_NARROW; ++o) g[o] = fmaf(c, fmaf(lr * d4[o], av, dec), g[o]);
 		}
 	}
-	__syncthreads();  // `red` may still be read as a tile buffer by a previous work item
+	cp_async_wait<0>();
 #pragma unroll
 	for (int o = 0; o < GF_NARROW; ++o) red[(part * GF_NCOLS + col) * GF_NARROW + o] = g[o];
 	__syncthreads();
@@ -223,6 +279,19 @@ __device__ __forceinline__ void gf_grad_narrow(const GridFusedArgs& a, int l, in
 	}
 }
 
+// The window scratch: one row per sample, layer l's nodes from column soff[l] on; every layer starts at a multiple
+// of 4 columns and the pitch is one too, so that rows and layers are 16-byte aligned for the copies of phase 2.
+__host__ __device__ inline int gf_scratch_layout(const NetView& n, int* soff)
+{
+	int c = 0;
+	for (int l = 0; l <= n.H + 1; ++l)
+	{
+		soff[l] = c;
+		c += (n.sizes[l] + 3) & ~3;
+	}
+	return c;
+}
+
 __global__ void __launch_bounds__(GF_THREADS, 1) grid_fused_kernel(const __grid_constant__ GridFusedArgs a)
 {
 	extern __shared__ __align__(16) float sm[];
@@ -233,22 +302,15 @@ __global__ void __launch_bounds__(GF_THREADS, 1) grid_fused_kernel(const __grid_
 	const int n_out = n.sizes[H + 1];
 	const int mb = n.mb;
 
+	// layer l's nodes start at node_off[l], a multiple of 4, in shared memory and in the window scratch alike
+	// (tot = the scratch's pitch); the few padding nodes are carried along and never read as values
 	int node_off[GL_MAX_WEIGHT_LAYERS + 2];
-	int tot = 0;
-	for (int l = 0; l <= H + 1; ++l)
-	{
-		node_off[l] = tot;
-		tot += n.sizes[l];
-	}
-	// shared memory: activations [tot][GF_ROWS] | deltas [tot][GF_ROWS] | weight tile | momentum table
-	// [H+1][mb+1] | phase-2 tiles | per-row metric scratch
+	const int tot = gf_scratch_layout(n, node_off);
+	// shared memory: activations [tot][GF_ROWS] | deltas [tot][GF_ROWS] | per-row metric scratch | tile list |
+	// weight-tile ring (phase 2 reuses it for its stages)
 	float* As = sm;
 	float* Ds = As + (size_t)tot * GF_ROWS;
-	float* ck = Ds + (size_t)tot * GF_ROWS;
-	float* Dt = ck + (((size_t)(H + 1) * (mb + 1) + 3) & ~(size_t)3);  // [GF_TJ][GF_TO]
-	float* At = Dt + GF_TJ * GF_TO;               // [GF_TJ][16 * NC]
-	float* Ct = At + GF_TJ * GF_TI_MAX;           // [GF_TJ]
-	float* rowm = Ct + GF_TJ;                     // [GF_ROWS][2]: cost, accuracy of the group's rows
+	float* rowm = Ds + (size_t)tot * GF_ROWS;  // [GF_ROWS][2]: cost, accuracy of the group's rows
 	int* seq = reinterpret_cast<int*>(rowm + 2 * GF_ROWS);  // [GF_SEQ_MAX][3]: tensor map, x, y of a group's weight tiles
 	// weight tiles: a ring of GF_NS stages filled by bulk tensor copies (1024-byte aligned for the
 	// 128-byte swizzle), or -- where the weights' layout does not allow tensor maps -- one tile buffer
@@ -307,17 +369,15 @@ __global__ void __launch_bounds__(GF_THREADS, 1) grid_fused_kernel(const __grid_
 		if (t == 0 && ps < p_end) issue();
 	};
 
-	// ck[l][k] = sum_{q<k} m_l^q: the weight of a sample with k samples of its window still to come (itself
-	// included); made once on the host, [H+1][mb+1]
-	for (int e = t; e < (H + 1) * (mb + 1); e += GF_THREADS) ck[e] = a.ck[e];
-	__syncthreads();
+	// a.ck[l][k] = sum_{q<k} m_l^q: the weight of a sample with k samples of its window still to come (itself
+	// included); made once on the host, [H+1][mb+1], read by phase 2 straight from global memory
 
 	const bool classify = n.out_type != GL_OUT_REGRESSION;
 	const bool softmax = n.act[H] == GL_ACT_SOFTMAX;
 	const float data_size = a.data_size;
 
-	// phase-2 tile list: layer l has ceil(no/16) * ceil(ni/(16*NC)) tiles
-	const int tile_i = 16 * a.nc;
+	// phase-2 tile list: layer l has ceil(no/16) * ceil(ni/32) tiles
+	const int tile_i = GF_P2_TI;
 	int tile_off[GL_MAX_WEIGHT_LAYERS + 1];
 	int tiles = 0;
 	for (int l = 0; l <= H; ++l)
@@ -677,7 +737,7 @@ __global__ void __launch_bounds__(GF_THREADS, 1) grid_fused_kernel(const __grid_
 					for (int e = t; e < tot; e += GF_THREADS)
 					{
 						ga[e] = As[(size_t)e * GF_ROWS + r];
-						if (e >= n.sizes[0]) gd[e] = Ds[(size_t)e * GF_ROWS + r];
+						if (e >= node_off[1]) gd[e] = Ds[(size_t)e * GF_ROWS + r];
 					}
 				}
 				if (warp >= 1 && warp <= H)
@@ -713,13 +773,12 @@ __global__ void __launch_bounds__(GF_THREADS, 1) grid_fused_kernel(const __grid_
 				const int tiles_i = (n.sizes[l] + tile_i - 1) / tile_i;
 				const int tl = tile - tile_off[l];
 				const int o0 = (tl / tiles_i) * GF_TO, i0 = (tl % tiles_i) * tile_i;
-				const float* ckl = ck + (size_t)l * (mb + 1);
+				// the weight-tile ring is idle in this phase (every tile of the window has been consumed, the next
+				// window's are issued after the grid barrier): it holds the stages of the asynchronous fill
 				if (n.sizes[l + 1] <= GF_NARROW)
-					gf_grad_narrow(a, l, tl * GF_NCOLS, len, tot, node_off[l], node_off[l + 1], ckl, inv_len, Dt, bad);
-				else if (a.nc == 2)
-					gf_grad_tile<2>(a, l, o0, i0, len, tot, node_off[l], node_off[l + 1], Dt, At, Ct, ckl, inv_len, bad);
+					gf_grad_narrow(a, l, tl * GF_NCOLS, len, tot, node_off[l], node_off[l + 1], a.ck + (size_t)l * (mb + 1), inv_len, Wt, bad);
 				else
-					gf_grad_tile<4>(a, l, o0, i0, len, tot, node_off[l], node_off[l + 1], Dt, At, Ct, ckl, inv_len, bad);
+					gf_grad_tile_async(a, l, o0, i0, len, tot, node_off[l], node_off[l + 1], Wt, a.ck + (size_t)l * (mb + 1), inv_len, bad);
 			}
 			if (blockIdx.x == 0)
 			{
@@ -786,7 +845,6 @@ __global__ void __launch_bounds__(GF_THREADS, 1) grid_fused_kernel(const __grid_
 // Everything is deterministic.  All barriers are executed unconditionally by every thread of every CTA.
 constexpr int CF_CS = 8;   // CTAs per cluster (the portable maximum)
 constexpr int CF_R = 32;   // rows a cluster carries through the network together
-constexpr int CF_TI = 32;  // phase 2: weight tile 16 outputs x 32 inputs
 
 struct CfPlan
 {
@@ -798,9 +856,10 @@ struct CfPlan
 	int wf[GL_MAX_WEIGHT_LAYERS + 1];         // float offset of the forward slice of weight layer l
 	int wb[GL_MAX_WEIGHT_LAYERS + 1];         // float offset of the delta slice of node layer j (1..H)
 	int rowm;                                 // float offset of the per-row metric scratch
+	int soff[GL_MAX_WEIGHT_LAYERS + 2];       // the window scratch: first column of layer j
+	int pitch;                                // and its pitch
 	int floats;                               // dynamic shared memory, floats
 };
-constexpr int CF_P2_FLOATS = GF_TJ * GF_TO + GF_TJ * CF_TI + GF_TJ + 8 * GF_TO * CF_TI;  // phase-2 buffers (aliased)
 
 __host__ __device__ inline void cf_plan(const NetView& n, CfPlan& p)
 {
@@ -835,7 +894,8 @@ __host__ __device__ inline void cf_plan(const NetView& n, CfPlan& p)
 	}
 	p.rowm = f;
 	f += 2 * CF_R;
-	p.floats = f > CF_P2_FLOATS ? f : CF_P2_FLOATS;
+	p.pitch = gf_scratch_layout(n, p.soff);
+	p.floats = f > GF_P2_MAX_FLOATS ? f : GF_P2_MAX_FLOATS;  // the phase-2 stages alias the phase-1 buffers
 }
 
 __device__ __forceinline__ uint32_t cl_rank()
@@ -919,118 +979,6 @@ __device__ __forceinline__ void cf_product(const float* InT, int K, const float*
 	}
 }
 
-// Phase 2, one 16 x 32 tile of layer l's weights.  Lane = 4 outputs x 4 inputs (four output groups x eight input
-// groups), warp w takes rows 8w..8w+7 of every 64-row step; the eight warps' partial sums are added in warp order
-// and the update is applied in place.  Tiles of deltas / activations travel global -> registers -> shared memory,
-// the next step's loads in flight while the current one is consumed.
-__device__ __forceinline__ void cf_grad_tile(const GridFusedArgs& a, int l, int o0, int i0, int len, int tot, int off_in, int off_out,
-                                             float* Dt, float* At, float* Ct, float* red, const float* ckl, float inv_len, int& bad)
-{
-	constexpr int NA = GF_TJ * CF_TI / GF_THREADS;  // 8 activation values per thread and step
-	const NetView& n = a.net;
-	const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
-	const int ni = n.sizes[l], no = n.sizes[l + 1];
-	const float lr = n.lr[l], w1 = n.wd1[l] * lr, w2 = n.wd2[l] * lr;
-	const bool decay = w1 != 0.0f || w2 != 0.0f;
-	const int og = lane >> 3, ig = lane & 7;
-	float g[4][4];
-#pragma unroll
-	for (int x = 0; x < 4; ++x)
-#pragma unroll
-		for (int y = 0; y < 4; ++y) g[x][y] = 0.0f;
-	float pd[4], pa[NA], pc = 0.0f;
-	auto fetch = [&](int jb) {
-		const int jn = (len - jb) < GF_TJ ? (len - jb) : GF_TJ;
-#pragma unroll
-		for (int k = 0; k < 4; ++k)
-		{
-			const int e = t + k * GF_THREADS, jj = e / GF_TO, x = e - jj * GF_TO;
-			pd[k] = (jj < jn && o0 + x < no) ? __ldcg(a.delbuf + (size_t)(jb + jj) * tot + off_out + o0 + x) : 0.0f;
-		}
-#pragma unroll
-		for (int k = 0; k < NA; ++k)
-		{
-			const int e = t + k * GF_THREADS, jj = e / CF_TI, x = e - jj * CF_TI;
-			pa[k] = (jj < jn && i0 + x < ni) ? __ldcg(a.actbuf + (size_t)(jb + jj) * tot + off_in + i0 + x) : 0.0f;
-		}
-		if (t < GF_TJ) pc = (t < jn) ? __ldg(ckl + (len - (jb + t))) : 0.0f;
-	};
-	fetch(0);
-	for (int jb = 0; jb < len; jb += GF_TJ)
-	{
-		const int jn = (len - jb) < GF_TJ ? (len - jb) : GF_TJ;
-		__syncthreads();
-		if (t < GF_TJ) Ct[t] = pc;
-#pragma unroll
-		for (int k = 0; k < NA; ++k) At[t + k * GF_THREADS] = pa[k];
-		if (decay)
-		{
-#pragma unroll
-			for (int k = 0; k < 4; ++k) Dt[t + k * GF_THREADS] = pd[k];
-		}
-		else
-		{
-			// no decay terms: the tile holds c_j * lr * d_jo, and a row costs one multiply-add per weight
-#pragma unroll
-			for (int k = 0; k < 4; ++k)
-			{
-				const int jj = (t + k * GF_THREADS) / GF_TO;
-				Dt[t + k * GF_THREADS] = (jj < jn) ? pd[k] * lr * __ldg(ckl + (len - (jb + jj))) : 0.0f;
-			}
-		}
-		__syncthreads();
-		if (jb + GF_TJ < len) fetch(jb + GF_TJ);
-#pragma unroll 4
-		for (int q = 0; q < 8; ++q)
-		{
-			const int jj = warp * 8 + q;  // rows beyond the window hold zeros
-			const float4 dv = *reinterpret_cast<const float4*>(Dt + jj * GF_TO + og * 4);
-			const float4 av = *reinterpret_cast<const float4*>(At + jj * CF_TI + ig * 4);
-			const float d4[4] = {dv.x, dv.y, dv.z, dv.w};
-			const float a4[4] = {av.x, av.y, av.z, av.w};
-			if (!decay)
-			{
-#pragma unroll
-				for (int x = 0; x < 4; ++x)
-#pragma unroll
-					for (int y = 0; y < 4; ++y) g[x][y] = fmaf(d4[x], a4[y], g[x][y]);
-			}
-			else
-			{
-				const float c = Ct[jj];
-				float dec[4];
-#pragma unroll
-				for (int y = 0; y < 4; ++y) dec[y] = fmaf(w1, fabsf(a4[y]), w2 * a4[y]);
-#pragma unroll
-				for (int x = 0; x < 4; ++x)
-#pragma unroll
-					for (int y = 0; y < 4; ++y) g[x][y] = fmaf(c, fmaf(lr * d4[x], a4[y], dec[y]), g[x][y]);
-			}
-		}
-	}
-	// the warps' partial sums: red[warp][output 0..15][input 0..31]
-#pragma unroll
-	for (int x = 0; x < 4; ++x)
-		*reinterpret_cast<float4*>(red + warp * (GF_TO * CF_TI) + (og * 4 + x) * CF_TI + ig * 4) = make_float4(g[x][0], g[x][1], g[x][2], g[x][3]);
-	__syncthreads();
-#pragma unroll
-	for (int k = 0; k < GF_TO * CF_TI / GF_THREADS; ++k)
-	{
-		const int e = t + k * GF_THREADS;
-		const int o = o0 + e / CF_TI, i = i0 + (e & (CF_TI - 1));
-		float sum = red[e];
-#pragma unroll
-		for (int w = 1; w < 8; ++w) sum += red[w * (GF_TO * CF_TI) + e];
-		if (o < no && i < ni)
-		{
-			float* wp = n.W[l] + (size_t)o * ni + i;
-			const float wv = __ldcg(wp) - sum * inv_len;
-			if (!isfinite(wv)) bad = 1;
-			*wp = wv;
-		}
-	}
-}
-
 __global__ void __launch_bounds__(GF_THREADS, 1) cluster_fused_kernel(const __grid_constant__ GridFusedArgs a)
 {
 	extern __shared__ __align__(16) float sm[];
@@ -1047,14 +995,11 @@ __global__ void __launch_bounds__(GF_THREADS, 1) cluster_fused_kernel(const __gr
 	if (t == 0) cf_plan(n, P);
 	__syncthreads();
 	const int tot = P.tot;
+	const int pitch = P.pitch;
 	float* AT = sm;                          // [tot][CF_R] activations, node-major
 	float* DT = sm + (size_t)tot * CF_R;     // [d_rows][CF_R] deltas of node layers 1..H+1
 	float* rowm = sm + P.rowm;               // [CF_R][2]: cost, accuracy of the pass's rows
-	// phase-2 buffers alias the phase-1 region (the phases are separated by grid barriers)
-	float* Dt = sm;
-	float* At = Dt + GF_TJ * GF_TO;
-	float* Ct = At + GF_TJ * CF_TI;
-	float* red = Ct + GF_TJ;
+	// the phase-2 stages alias the phase-1 region (the phases are separated by grid barriers)
 	const uint32_t at_addr = smem_u32(AT), dt_addr = smem_u32(DT);
 
 	const bool classify = n.out_type != GL_OUT_REGRESSION;
@@ -1068,12 +1013,12 @@ __global__ void __launch_bounds__(GF_THREADS, 1) cluster_fused_kernel(const __gr
 	{
 		tile_off[l] = tiles;
 		tiles += (n.sizes[l + 1] <= GF_NARROW) ? (n.sizes[l] + GF_NCOLS - 1) / GF_NCOLS
-		                                       : ((n.sizes[l + 1] + GF_TO - 1) / GF_TO) * ((n.sizes[l] + CF_TI - 1) / CF_TI);
+		                                       : ((n.sizes[l + 1] + GF_TO - 1) / GF_TO) * ((n.sizes[l] + GF_P2_TI - 1) / GF_P2_TI);
 	}
 	tile_off[H + 1] = tiles;
 
 	const bool timed = a.timing != nullptr && blockIdx.x == 0 && t == 0;
-	unsigned long long tm[4] = {0, 0, 0, 0}, t_a = 0, t_b = 0;
+	unsigned long long tm[9] = {0, 0, 0, 0, 0, 0, 0, 0, 0}, t_a = 0, t_b = 0, t_c = 0, t_d = 0;
 	auto now = []() {
 		unsigned long long v;
 		asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(v));
@@ -1121,6 +1066,7 @@ __global__ void __launch_bounds__(GF_THREADS, 1) cluster_fused_kernel(const __gr
 				}
 			}
 			__syncthreads();
+			if (timed) { t_c = now(); tm[4] += t_c - t_a; }
 			// ================= phase 1: forward, head, deltas, CF_R rows per cluster pass
 			for (int pass = cid; pass < passes; pass += nclusters)
 			{
@@ -1149,7 +1095,7 @@ __global__ void __launch_bounds__(GF_THREADS, 1) cluster_fused_kernel(const __gr
 					const float b = (l >= 1) ? __ldcg(n.bias + l) : 0.0f;
 					const int act = n.act[l];
 					const float par = n.par[l];
-					const int out_node = P.node_off[l + 1] + nb0;
+					const int out_node = P.node_off[l + 1] + nb0, out_col = P.soff[l + 1] + nb0;
 					const bool hidden = l < H;
 					cf_product(AT + (size_t)P.node_off[l] * CF_R, n.sizes[l], sm + P.wf[l], cnt,
 					           [&](int nn, int sq, float s0, float s1, float s2, float s3) {
@@ -1160,15 +1106,16 @@ __global__ void __launch_bounds__(GF_THREADS, 1) cluster_fused_kernel(const __gr
 						           for (int dst = 0; dst < CF_CS; ++dst) cl_store4(cl_map(local, (uint32_t)dst), v0, v1, v2, v3);
 						           if (hidden)
 						           {
-							           float* ga = a.actbuf + (size_t)(j0 + 4 * sq) * tot + out_node + nn;
+							           float* ga = a.actbuf + (size_t)(j0 + 4 * sq) * pitch + out_col + nn;
 							           if (4 * sq + 0 < valid) ga[0] = v0;
-							           if (4 * sq + 1 < valid) ga[(size_t)tot] = v1;
-							           if (4 * sq + 2 < valid) ga[(size_t)2 * tot] = v2;
-							           if (4 * sq + 3 < valid) ga[(size_t)3 * tot] = v3;
+							           if (4 * sq + 1 < valid) ga[(size_t)pitch] = v1;
+							           if (4 * sq + 2 < valid) ga[(size_t)2 * pitch] = v2;
+							           if (4 * sq + 3 < valid) ga[(size_t)3 * pitch] = v3;
 						           }
 					           });
 					cl_sync();  // the layer's activations have landed in every CTA of the cluster
 				}
+				if (timed) { t_d = now(); tm[5] += t_d - t_c; t_c = t_d; }
 				// ---- head on this CTA's copy: warp = four rows of the pass; side effects from cluster rank 0 only
 				for (int rr = 0; rr < CF_R / 8; ++rr)
 				{
@@ -1220,8 +1167,8 @@ __global__ void __launch_bounds__(GF_THREADS, 1) cluster_fused_kernel(const __gr
 							dout[(size_t)o * CF_R] = d;
 							if (crank == 0)
 							{
-								a.actbuf[(size_t)(j0 + r) * tot + P.node_off[H + 1] + o] = pv;
-								a.delbuf[(size_t)(j0 + r) * tot + P.node_off[H + 1] + o] = d;
+								a.actbuf[(size_t)(j0 + r) * pitch + P.soff[H + 1] + o] = pv;
+								a.delbuf[(size_t)(j0 + r) * pitch + P.soff[H + 1] + o] = d;
 							}
 							c_acc += cost;
 							a_acc += fmaxf((1.0f - fminf(fabsf(pv - e), 1.0f)) * 100.0f, 0.0f);
@@ -1260,6 +1207,7 @@ __global__ void __launch_bounds__(GF_THREADS, 1) cluster_fused_kernel(const __gr
 					}
 				}
 				__syncthreads();
+				if (timed) { t_d = now(); tm[6] += t_d - t_c; t_c = t_d; }
 				// ---- hidden deltas of the CTA's nodes: D_j = (D_{j+1} W_j) * act'(A_j)
 				for (int j = H; j >= 1; --j)
 				{
@@ -1267,7 +1215,7 @@ __global__ void __launch_bounds__(GF_THREADS, 1) cluster_fused_kernel(const __gr
 					int cnt = n.sizes[j] - i0;
 					cnt = cnt < 0 ? 0 : (cnt > P.sl[j] ? P.sl[j] : cnt);
 					const int act = n.act[j - 1];
-					const int node = P.node_off[j] + i0, drow = P.d_off[j] + i0;
+					const int node = P.node_off[j] + i0, drow = P.d_off[j] + i0, dcol = P.soff[j] + i0;
 					const bool gather = j >= 2;
 					cf_product(DT + (size_t)P.d_off[j + 1] * CF_R, (n.sizes[j + 1] + 3) & ~3, sm + P.wb[j], cnt,
 					           [&](int nn, int sq, float s0, float s1, float s2, float s3) {
@@ -1282,21 +1230,22 @@ __global__ void __launch_bounds__(GF_THREADS, 1) cluster_fused_kernel(const __gr
 #pragma unroll
 							           for (int dst = 0; dst < CF_CS; ++dst) cl_store4(cl_map(local, (uint32_t)dst), d0, d1, d2, d3);
 						           }
-						           float* gd = a.delbuf + (size_t)(j0 + 4 * sq) * tot + node + nn;
+						           float* gd = a.delbuf + (size_t)(j0 + 4 * sq) * pitch + dcol + nn;
 						           if (4 * sq + 0 < valid) gd[0] = d0;
-						           if (4 * sq + 1 < valid) gd[(size_t)tot] = d1;
-						           if (4 * sq + 2 < valid) gd[(size_t)2 * tot] = d2;
-						           if (4 * sq + 3 < valid) gd[(size_t)3 * tot] = d3;
+						           if (4 * sq + 1 < valid) gd[(size_t)pitch] = d1;
+						           if (4 * sq + 2 < valid) gd[(size_t)2 * pitch] = d2;
+						           if (4 * sq + 3 < valid) gd[(size_t)3 * pitch] = d3;
 					           });
 					if (gather) cl_sync();
 				}
+				if (timed) { t_d = now(); tm[7] += t_d - t_c; t_c = t_d; }
 				// the inputs of the pass belong to the window scratch too (phase 2 of layer 0 reads them)
 				{
 					const int n0 = n.sizes[0];
 					for (int e = t + crank * GF_THREADS; e < valid * n0; e += GF_THREADS * CF_CS)
 					{
 						const int r = e / n0, i = e - r * n0;
-						a.actbuf[(size_t)(j0 + r) * tot + i] = AT[(size_t)i * CF_R + r];
+						a.actbuf[(size_t)(j0 + r) * pitch + i] = AT[(size_t)i * CF_R + r];
 					}
 				}
 				if (crank == 0)
@@ -1320,6 +1269,7 @@ __global__ void __launch_bounds__(GF_THREADS, 1) cluster_fused_kernel(const __gr
 					}
 				}
 				cl_sync();  // nobody of the cluster reads this pass's buffers any more: the next pass may overwrite them
+				if (timed) { t_d = now(); tm[8] += t_d - t_c; t_c = t_d; }
 			}
 			__syncthreads();
 			if (t < GF_PART) a.part[(size_t)blockIdx.x * GF_PART + t] = s_part[t];
@@ -1333,15 +1283,14 @@ __global__ void __launch_bounds__(GF_THREADS, 1) cluster_fused_kernel(const __gr
 			{
 				int l = 0;
 				while (tile >= tile_off[l + 1]) ++l;
-				const int tiles_i = (n.sizes[l] + CF_TI - 1) / CF_TI;
+				const int tiles_i = (n.sizes[l] + GF_P2_TI - 1) / GF_P2_TI;
 				const int tl = tile - tile_off[l];
 				const float* ckl = a.ck + (size_t)l * (mb + 1);
-				__syncthreads();  // the previous work item's buffers are no longer read
 				if (n.sizes[l + 1] <= GF_NARROW)
-					gf_grad_narrow(a, l, tl * GF_NCOLS, len, tot, P.node_off[l], P.node_off[l + 1], ckl, inv_len, Dt, bad);
+					gf_grad_narrow(a, l, tl * GF_NCOLS, len, pitch, P.soff[l], P.soff[l + 1], ckl, inv_len, sm, bad);
 				else
-					cf_grad_tile(a, l, (tl / tiles_i) * GF_TO, (tl % tiles_i) * CF_TI, len, tot, P.node_off[l], P.node_off[l + 1], Dt, At, Ct,
-					             red, ckl, inv_len, bad);
+					gf_grad_tile_async(a, l, (tl / tiles_i) * GF_TO, (tl % tiles_i) * GF_P2_TI, len, pitch, P.soff[l], P.soff[l + 1], sm,
+					                   ckl, inv_len, bad);
 			}
 			if (blockIdx.x == 0)
 			{
@@ -1387,7 +1336,7 @@ __global__ void __launch_bounds__(GF_THREADS, 1) cluster_fused_kernel(const __gr
 		}
 	}
 	if (timed)
-		for (int k = 0; k < 4; ++k) a.timing[k] += tm[k];
+		for (int k = 0; k < 9; ++k) a.timing[k] += tm[k];
 	if (bad) atomicOr(a.flags, 1);
 }
 
@@ -1395,11 +1344,17 @@ __global__ void __launch_bounds__(GF_THREADS, 1) cluster_fused_kernel(const __gr
 
 size_t grid_fused_smem_bytes(const NetView& n)
 {
-	int tot = 0;
-	for (int l = 0; l <= n.H + 1; ++l) tot += n.sizes[l];
-	size_t f = 2 * (size_t)tot * GF_ROWS + (((size_t)(n.H + 1) * (n.mb + 1) + 3) & ~(size_t)3) + GF_TJ * GF_TO + GF_TJ * GF_TI_MAX + GF_TJ + 2 * GF_ROWS + 3 * GF_SEQ_MAX;
+	int off[GL_MAX_WEIGHT_LAYERS + 2];
+	const int tot = gf_scratch_layout(n, off);
+	size_t f = 2 * (size_t)tot * GF_ROWS + 2 * GF_ROWS + 3 * GF_SEQ_MAX;
 	// + alignment slack + the ring (its first stage doubles as the register-path tile buffer, GF_WT floats)
 	return f * sizeof(float) + 1024 + (size_t)GF_NS * GF_STAGE + 64;
+}
+
+int grid_fused_scratch_pitch(const NetView& n)
+{
+	int soff[GL_MAX_WEIGHT_LAYERS + 2];
+	return gf_scratch_layout(n, soff);
 }
 
 int grid_fused_total_nodes(const NetView& n)
@@ -1417,19 +1372,6 @@ int grid_fused_group_tiles(const NetView& n)
 	return steps;
 }
 
-int grid_fused_pick_nc(const NetView& n, int ctas)
-{
-	for (int nc = 2; nc <= 4; nc *= 2)
-	{
-		int tiles = 0;
-		for (int l = 0; l <= n.H; ++l)
-			tiles += (n.sizes[l + 1] <= GF_NARROW) ? (n.sizes[l] + GF_NCOLS - 1) / GF_NCOLS
-			                                       : ((n.sizes[l + 1] + GF_TO - 1) / GF_TO) * ((n.sizes[l] + 16 * nc - 1) / (16 * nc));
-		if (tiles <= ctas) return nc;
-	}
-	return 4;
-}
-
 cudaError_t launch_grid_fused(const GridFusedArgs& a, cudaStream_t s)
 {
 	const size_t bytes = grid_fused_smem_bytes(a.net);
@@ -1438,7 +1380,7 @@ cudaError_t launch_grid_fused(const GridFusedArgs& a, cudaStream_t s)
 		cudaError_t e = cudaFuncSetAttribute(grid_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
 		if (e != cudaSuccess) return e;
 	}
-	if (a.part_ctas < 1 || (a.nc != 2 && a.nc != 4)) return cudaErrorInvalidValue;
+	if (a.part_ctas < 1) return cudaErrorInvalidValue;
 	GridFusedArgs copy = a;
 	void* params[] = {&copy};
 	// one CTA per SM (the shared-memory footprint allows no more), all co-resident as the grid barrier needs

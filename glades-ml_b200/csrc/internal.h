@@ -169,12 +169,11 @@ struct GridFusedArgs
 	int n_epochs;
 	int bias_rule;
 	float data_size;     // the cost divisor: rows of the epoch * n_out
-	float* actbuf;       // [net.mb][total nodes] scratch: the window's activations
-	float* delbuf;       // [net.mb][total nodes] scratch: the window's deltas
+	float* actbuf;       // [net.mb][grid_fused_scratch_pitch] scratch: the window's activations
+	float* delbuf;       // [net.mb][grid_fused_scratch_pitch] scratch: the window's deltas
 	double* part;        // [part_ctas][2 + GL_MAX_WEIGHT_LAYERS] per-CTA partial sums of a window
 	int part_ctas;       // = the grid of the launch (one CTA per SM)
 	const float* ck;     // [H+1][net.mb+1]: ck[l][k] = sum_{q<k} momentum_l^q
-	int nc;              // weights per thread in the update phase (2 or 4): see grid_fused_pick_nc
 	double* epoch_sums;  // [n_epochs][2]: cost sum, accuracy sum
 	int* confusion;      // [n_out][n_out]: the last epoch's counts are ADDED (the caller clears)
 	float* last_out;     // [n_out] or NULL
@@ -188,14 +187,14 @@ struct GridFusedArgs
 };
 size_t grid_fused_smem_bytes(const NetView& n);
 int grid_fused_total_nodes(const NetView& n);
+// floats per row of the window scratch (every layer padded to a multiple of 4 columns)
+int grid_fused_scratch_pitch(const NetView& n);
 // weight tiles one sample group walks through (the ring path needs <= 512)
 int grid_fused_group_tiles(const NetView& n);
-// smallest tile width whose tile count does not exceed `ctas` (else 4)
-int grid_fused_pick_nc(const NetView& n, int ctas);
 cudaError_t launch_grid_fused(const GridFusedArgs& a, cudaStream_t s);
 // cluster variant (thread-block clusters of 8 CTAs share a group of rows, every CTA owning an eighth of each
 // layer's nodes with their weights resident in shared memory): same arguments, part_ctas = a multiple of 8 that
-// cluster_fused_max_ctas allows; nc and tma are not used
+// cluster_fused_max_ctas allows; tma is not used
 bool cluster_fused_fits(const NetView& n);
 size_t cluster_fused_smem_bytes(const NetView& n);
 int cluster_fused_max_ctas(const NetView& n);

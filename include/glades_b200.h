@@ -230,8 +230,8 @@ int gl_selftest_bounded_wait(gl_net* net, int64_t max_cycles, double* waited_ms)
 int64_t gl_kernel_launches(const gl_net* net);
 int64_t gl_tensor_core_launches(const gl_net* net);
 /* Diagnostics: CTAs of the whole-window kernel's thread-block-cluster variant on this handle: > 0 once a window has
- * run on it, 0 where the variant does not apply (network shape, device, GLADES_GF_CLUSTER=0), -1 before the first
- * whole-window launch decided.  No counterpart in the reference. */
+ * run on it, 0 where the variant is not in use (it is opt-in: GLADES_GF_CLUSTER=1; network shape; device), -1 before
+ * the first whole-window launch decided.  No counterpart in the reference. */
 int32_t gl_window_cluster_ctas(const gl_net* net);
 /* Diagnostics: tensor-core product launches of this process per tile variant -- out5[0] 128-wide
  * tiles, [1] 256-wide tiles, [2] launches whose persistent CTAs walked more than one tile each,

@@ -281,17 +281,17 @@ def _cluster_variant_applies(sizes):
     return floats * 4 <= 226 * 1024
 
 
-@pytest.mark.parametrize("engine", ["ffma", "grid_fused", "grid_fused_no_cluster"])
+@pytest.mark.parametrize("engine", ["ffma", "grid_fused", "grid_fused_cluster"])
 @pytest.mark.parametrize("case", BATCHED_CASES + GRID_FUSED_EXTRA, ids=lambda c: "-".join(map(str, c[0])) + "_" + str(c[3]))
 def test_batched_window_vs_restatement(g, oracle, monkeypatch, case, engine):
     """One minibatch window, per-layer products on the FFMA kernel vs the whole window in one
-    cooperative launch (grid_fused; its cluster variant where the network allows it, and the plain variant
-    forced): all against the CPU restatement of the batched arithmetic."""
+    cooperative launch (grid_fused, and its opt-in thread-block-cluster variant where the network allows it):
+    all against the CPU restatement of the batched arithmetic."""
     sizes, acts, out, rows, mom, wd1, wd2, brule = case
-    if engine == "grid_fused_no_cluster":
+    if engine == "grid_fused_cluster":
         if not _cluster_variant_applies(sizes):
-            pytest.skip("the plain variant is what the grid_fused case of this network runs already")
-        monkeypatch.setenv("GLADES_GF_CLUSTER", "0")
+            pytest.skip("the cluster variant does not take this network")
+        monkeypatch.setenv("GLADES_GF_CLUSTER", "1")
     else:
         monkeypatch.delenv("GLADES_GF_CLUSTER", raising=False)
     rng = np.random.default_rng(sum(sizes) + rows)
@@ -316,8 +316,7 @@ def test_batched_window_vs_restatement(g, oracle, monkeypatch, case, engine):
         m = net.train_window(0, rows)
         if engine.startswith("grid_fused"):
             assert net.kernel_launches() - l0 == 1, "the whole window must be one cooperative launch"
-            want_cluster = engine == "grid_fused" and _cluster_variant_applies(sizes)
-            assert (net.window_cluster_ctas() > 0) == want_cluster, net.window_cluster_ctas()
+            assert (net.window_cluster_ctas() > 0) == (engine == "grid_fused_cluster"), net.window_cluster_ctas()
         cm = np.zeros((sizes[-1], sizes[-1]), np.int32)
         gr = S.window_grad(0, rows, confusion=cm)
         S.window_apply(gr, rows)
@@ -560,9 +559,9 @@ def test_grid_fused_epochs_vs_restatement(g, oracle, monkeypatch, case, cluster)
     the kernel and on the plain one."""
     sizes, acts, out, rows, mb, mom, brule, epochs = case
     if cluster == "plain":
-        monkeypatch.setenv("GLADES_GF_CLUSTER", "0")
-    else:
         monkeypatch.delenv("GLADES_GF_CLUSTER", raising=False)
+    else:
+        monkeypatch.setenv("GLADES_GF_CLUSTER", "1")
         assert _cluster_variant_applies(sizes)
     rng = np.random.default_rng(len(sizes) * 100 + rows)
     d = g.make_desc(sizes, acts, out, batch=mb, lr=0.002 if mb > 500 else 0.05, momentum=mom, mode=g.MODE_BATCHED,
