@@ -140,8 +140,9 @@ __global__ void __launch_bounds__(256) gemm_skinny_kernel(const GemmArgs g)
 #pragma unroll
 			for (int n = 0; n < NN; ++n) acc[r][n] = 0.0f;
 		// Two 16-byte chunks per row and lane, rotated: while one set of four loads is consumed the other set is in
-		// flight, so the warp always has loads outstanding (loading both sets and then computing on both left
-		// HBM idle during the arithmetic: 2.7 TB/s).
+		// flight, so the warp always has loads outstanding.  (Measured the same 2.7 TB/s as loading both sets and
+		// then computing on both: with 16 warps per SM the kernel is bound by the latency of the bytes it can keep
+		// in flight -- 123 registers, 80 KB of weights in shared memory per block -- not by instruction issue.)
 		auto consume = [&](const float4 (&v)[SK_ROWS], int kq) {
 #pragma unroll
 			for (int n = 0; n < NN; ++n)

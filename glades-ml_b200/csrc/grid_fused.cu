@@ -292,6 +292,10 @@ __host__ __device__ inline int gf_scratch_layout(const NetView& n, int* soff)
 	return c;
 }
 
+// USE_TMA: the weight tiles arrive through the ring of bulk tensor copies (a.tma != NULL), else through registers.
+// Two instantiations rather than a run-time flag: each carries one tile path only, which halves the body the
+// instruction cache has to hold (instruction fetch showed among the kernel's stalls).
+template <bool USE_TMA>
 __global__ void __launch_bounds__(GF_THREADS, 1) grid_fused_kernel(const __grid_constant__ GridFusedArgs a)
 {
 	extern __shared__ __align__(16) float sm[];
@@ -326,7 +330,7 @@ __global__ void __launch_bounds__(GF_THREADS, 1) grid_fused_kernel(const __grid_
 	__shared__ double s_part[GF_PART];
 	__shared__ uint64_t gf_bars[GF_NS];
 	__shared__ int gf_abort;
-	const bool use_tma = a.tma != nullptr;
+	constexpr bool use_tma = USE_TMA;
 	const CUtensorMap* maps = reinterpret_cast<const CUtensorMap*>(a.tma);
 	int nsteps = 0;  // weight tiles per sample group
 	if (use_tma)
@@ -1377,14 +1381,16 @@ cudaError_t launch_grid_fused(const GridFusedArgs& a, cudaStream_t s)
 	const size_t bytes = grid_fused_smem_bytes(a.net);
 	{
 		// the attribute belongs to the current device: set it per launch (a cheap call) rather than cache it per process
-		cudaError_t e = cudaFuncSetAttribute(grid_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+		cudaError_t e = a.tma ? cudaFuncSetAttribute(grid_fused_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes)
+		                      : cudaFuncSetAttribute(grid_fused_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
 		if (e != cudaSuccess) return e;
 	}
 	if (a.part_ctas < 1) return cudaErrorInvalidValue;
 	GridFusedArgs copy = a;
 	void* params[] = {&copy};
 	// one CTA per SM (the shared-memory footprint allows no more), all co-resident as the grid barrier needs
-	return cudaLaunchCooperativeKernel((void*)grid_fused_kernel, dim3((unsigned)a.part_ctas), dim3(GF_THREADS), params, bytes, s);
+	void* fn = a.tma ? (void*)grid_fused_kernel<true> : (void*)grid_fused_kernel<false>;
+	return cudaLaunchCooperativeKernel(fn, dim3((unsigned)a.part_ctas), dim3(GF_THREADS), params, bytes, s);
 }
 
 // ---- cluster variant: host side ------------------------------------------------------------------
