@@ -2841,6 +2841,7 @@ struct StdScratch
 	int* stats = nullptr;
 	int* kind = nullptr;
 	void* plan = nullptr;
+	int* host = nullptr;  // pinned staging: [cols][4] statistics, [cols][4] plan, [cols] kinds
 	int cap = 0;
 };
 StdScratch g_stdScratch[64];
@@ -2881,26 +2882,37 @@ extern "C" int gl_standardize_table(const float* d_raw, int64_t rows, int32_t co
 		cudaFree(sc.stats);
 		cudaFree(sc.kind);
 		cudaFree(sc.plan);
+		cudaFreeHost(sc.host);
 		sc = StdScratch();
 		CU(cudaMalloc(&sc.stats, (size_t)cols * 4 * sizeof(int)));
 		CU(cudaMalloc(&sc.kind, (size_t)cols * sizeof(int)));
 		CU(cudaMalloc(&sc.plan, (size_t)cols * 4 * sizeof(int)));
+		CU(cudaMallocHost(&sc.host, (size_t)cols * 9 * sizeof(int)));
 		sc.cap = cols;
 	}
 	int* dStats = sc.stats;
 	int* dKind = sc.kind;
 	void* dPlan = sc.plan;
-	cudaError_t e = cudaMemcpy(dStats, st.data(), st.size() * sizeof(int), cudaMemcpyHostToDevice);
+	// the small records travel through pinned staging as asynchronous copies on the stream of the kernels: one
+	// wait for the extrema (the layout depends on them), one at the end
+	int* hStats = sc.host;
+	int* hPlan = sc.host + (size_t)cols * 4;
+	int* hKind = sc.host + (size_t)cols * 8;
+	memcpy(hStats, st.data(), st.size() * sizeof(int));
+	cudaError_t e = cudaMemcpyAsync(dStats, hStats, st.size() * sizeof(int), cudaMemcpyHostToDevice, 0);
 	if (e == cudaSuccess) e = launch_column_minmax(d_raw, rows, cols, dStats, 0);
 	if (e == cudaSuccess && flag == 1)
 	{
-		e = cudaMemcpy(dKind, kind, (size_t)cols * sizeof(int), cudaMemcpyHostToDevice);
+		memcpy(hKind, kind, (size_t)cols * sizeof(int));
+		e = cudaMemcpyAsync(dKind, hKind, (size_t)cols * sizeof(int), cudaMemcpyHostToDevice, 0);
 		if (e == cudaSuccess) e = launch_column_mean_stdev(d_raw, rows, cols, dKind, reinterpret_cast<float*>(dStats), 0);
 	}
-	if (e == cudaSuccess) e = cudaMemcpy(st.data(), dStats, st.size() * sizeof(int), cudaMemcpyDeviceToHost);
+	if (e == cudaSuccess) e = cudaMemcpyAsync(hStats, dStats, st.size() * sizeof(int), cudaMemcpyDeviceToHost, 0);
+	if (e == cudaSuccess) e = cudaStreamSynchronize(0);
+	if (e == cudaSuccess) memcpy(st.data(), hStats, st.size() * sizeof(int));
 	// the layout: columns keep their raw order inside each destination; a numeric column whose range is 0 is
 	// copied unscaled and lands in the input matrix whatever its output mark (NumberInput.cpp:166-171)
-	std::vector<int> plan((size_t)cols * 4);
+	int* plan = hPlan;
 	int cx = 0, cy = 0;
 	if (e == cudaSuccess)
 		for (int c = 0; c < cols; ++c)
@@ -2923,7 +2935,7 @@ extern "C" int gl_standardize_table(const float* d_raw, int64_t rows, int32_t co
 			              cx, cy, *nx, *ny);
 		else
 		{
-			e = cudaMemcpy(dPlan, plan.data(), plan.size() * sizeof(int), cudaMemcpyHostToDevice);
+			e = cudaMemcpyAsync(dPlan, plan, (size_t)cols * 4 * sizeof(int), cudaMemcpyHostToDevice, 0);
 			if (e == cudaSuccess) e = launch_column_transform(d_raw, rows, cols, dPlan, dStats, flag, classification, d_x, cx, d_y, cy, 0);
 			if (e == cudaSuccess) e = cudaStreamSynchronize(0);
 		}

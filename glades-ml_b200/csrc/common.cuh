@@ -162,6 +162,22 @@ __device__ __forceinline__ float tf32_lo(float v)
 	return __uint_as_float(t);
 }
 
+// ---- asynchronous global -> shared copies (cp.async); destinations are 32-bit shared-window addresses ----
+__device__ __forceinline__ void cp_async4(uint32_t dst, const float* src, bool valid)
+{
+	const int bytes = valid ? 4 : 0;  // 0: nothing is read, the destination is zero-filled
+	asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+}
+// 16 bytes, of which the first `floats` (0..4) values are read and the rest zero-filled; both addresses 16-byte aligned
+__device__ __forceinline__ void cp_async16(uint32_t dst, const float* src, int floats)
+{
+	const int bytes = floats <= 0 ? 0 : (floats >= 4 ? 16 : floats * 4);
+	asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
 __device__ __forceinline__ float warp_sum(float v)
 {
 #pragma unroll

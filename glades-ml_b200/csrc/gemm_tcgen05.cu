@@ -514,9 +514,11 @@ cudaError_t launch_cfg(const CUtensorMap& mA, const CUtensorMap& mAl, const CUte
 	// the SMs idle (32 tiles of a narrow layer; 68 tiles after three whole waves) and the caller gave a workspace.
 	// Not below that: CTAs that share a tile's operands then sit at different k offsets, the operands stop being
 	// fetched once and shared through L2, and 128 tiles on 148 SMs measured 17-30 % slower split than whole.
+	// The data-parallel variant (epilogue stores into peers' memory) is never split: with the SMs it leaves to the
+	// exchange its tile counts are whole waves, and the combination has no parity test.
 	q.sk_full_tiles = total;
 	const int KB = p.K / BK;
-	if (q.sk_work && sk && KB >= 8)
+	if (q.sk_work && sk && KB >= 8 && !PEER)
 	{
 		const int g2 = avail;
 		const int full = (total / g2) * g2;

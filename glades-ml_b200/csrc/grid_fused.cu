@@ -53,21 +53,6 @@ constexpr int GF_P2_FLOATS = GF_P2_STAGES * GF_P2_STAGE_FLOATS + 8 * GF_TO * GF_
 static_assert(GF_P2_FLOATS * 4 <= GF_NS * GF_STAGE, "the phase-2 stages live inside the weight-tile ring");
 static_assert((GF_P2_STAGE_FLOATS * 4) % 16 == 0, "stages keep the 16-byte alignment of the vector loads");
 
-__device__ __forceinline__ void cp_async4(uint32_t dst, const float* src, bool valid)
-{
-	const int bytes = valid ? 4 : 0;  // 0: nothing is read, the destination is zero-filled
-	asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
-}
-// 16 bytes, of which the first `floats` (0..4) values are read and the rest zero-filled; both addresses 16-byte aligned
-__device__ __forceinline__ void cp_async16(uint32_t dst, const float* src, int floats)
-{
-	const int bytes = floats <= 0 ? 0 : (floats >= 4 ? 16 : floats * 4);
-	asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
-
 __device__ __forceinline__ void gf_grad_tile_async(const GridFusedArgs& a, int l, int o0, int i0, int len, int pitch, int off_in,
                                                    int off_out, float* stages, const float* ckl, float inv_len, int& bad)
 {

@@ -37,6 +37,9 @@ __device__ __forceinline__ int argmax_ref(const float* v, int n)
 	return idx;
 }
 
+// the epoch's confusion counts stay in shared memory up to this many cells
+constexpr int REF_CONF_SMEM = 1024;
+
 __global__ void __launch_bounds__(1024, 1) ref_train_kernel(const __grid_constant__ RefTrainArgs a)
 {
 	extern __shared__ __align__(16) float smem[];
@@ -57,7 +60,14 @@ __global__ void __launch_bounds__(1024, 1) ref_train_kernel(const __grid_constan
 	float* sbias = basev + total_nodes;  // GL_MAX_WEIGHT_LAYERS floats
 	float* mcost = sbias + GL_MAX_WEIGHT_LAYERS;  // per output node: cost and accuracy of this sample
 	float* macc = mcost + n_out;
-	float* wcur = macc + n_out;
+	// the next sample's input and target rows arrive by asynchronous copies while the current sample runs (the
+	// sample loop is one dependent chain: a global load at its head would be paid in full every sample)
+	float* xbuf = macc + n_out;               // [2][n_in]
+	float* ybuf = xbuf + 2 * n.sizes[0];      // [2][n_out]
+	// the confusion counts of the running epoch, where they fit (else straight in global memory)
+	const bool conf_smem = n_out * n_out <= REF_CONF_SMEM;
+	int* sconf = reinterpret_cast<int*>(ybuf + 2 * n_out);
+	float* wcur = reinterpret_cast<float*>(sconf + (conf_smem ? n_out * n_out : 0));
 
 	float* actp[GL_MAX_WEIGHT_LAYERS + 1];
 	float* errp[GL_MAX_WEIGHT_LAYERS + 1];
@@ -99,6 +109,15 @@ __global__ void __launch_bounds__(1024, 1) ref_train_kernel(const __grid_constan
 
 	const float data_size = (float)(a.rows * (long long)n_out);
 	const bool classify = n.out_type != GL_OUT_REGRESSION;
+	int* const conf = conf_smem ? sconf : a.confusion;
+	const uint32_t xb_addr = (uint32_t)__cvta_generic_to_shared(xbuf), yb_addr = (uint32_t)__cvta_generic_to_shared(ybuf);
+	auto prefetch = [&](long long row, int buf) {
+		for (int i = t; i < n.sizes[0]; i += T) cp_async4(xb_addr + (uint32_t)(buf * n.sizes[0] + i) * 4, a.X + row * n.sizes[0] + i, true);
+		for (int o = t; o < n_out; o += T) cp_async4(yb_addr + (uint32_t)(buf * n_out + o) * 4, a.Y + row * n_out + o, true);
+		cp_async_commit();
+	};
+	if (a.n_epochs > 0 && a.rows > 0) prefetch(0, 0);
+	int buf = 0;
 
 	for (int ep = 0; ep < a.n_epochs; ++ep)
 	{
@@ -109,14 +128,22 @@ __global__ void __launch_bounds__(1024, 1) ref_train_kernel(const __grid_constan
 			s_tot_acc = 0.0f;
 		}
 		if (classify)
-			for (int e = t; e < n_out * n_out; e += T) a.confusion[e] = 0;
+			for (int e = t; e < n_out * n_out; e += T) conf[e] = 0;
 		__syncthreads();
 
 		for (long long r = 0; r < a.rows; ++r)
 		{
-			// ---------------- forward
-			for (int i = t; i < n.sizes[0]; i += T) actp[0][i] = a.X[r * n.sizes[0] + i];
+			// ---------------- this sample's rows have landed; the next sample's start travelling
+			cp_async_wait<0>();
 			__syncthreads();
+			actp[0] = xbuf + buf * n.sizes[0];
+			const float* yr = ybuf + buf * n_out;
+			{
+				const long long nr = (r + 1 < a.rows) ? r + 1 : ((ep + 1 < a.n_epochs) ? 0 : -1);
+				if (nr >= 0) prefetch(nr, buf ^ 1);  // that buffer was last read by the previous sample, whose end all threads have passed
+			}
+			buf ^= 1;
+			// ---------------- forward
 			for (int l = 0; l <= H; ++l)
 			{
 				const int ni = n.sizes[l], no = n.sizes[l + 1];
@@ -134,7 +161,6 @@ __global__ void __launch_bounds__(1024, 1) ref_train_kernel(const __grid_constan
 				__syncthreads();
 			}
 			// ---------------- metrics: sequential fp32 sums in (row, output) order
-			const float* yr = a.Y + r * n_out;
 			// the per-node values are independent (computed in parallel); only their accumulation into the
 			// epoch sums is order-sensitive and stays on one thread
 			for (int o = t; o < n_out; o += T)
@@ -157,7 +183,7 @@ __global__ void __launch_bounds__(1024, 1) ref_train_kernel(const __grid_constan
 				if (classify)
 				{
 					int ie = argmax_ref(yr, n_out), ip = argmax_ref(p, n_out);
-					if (ie >= 0 && ip >= 0) a.confusion[ie * n_out + ip] += 1;
+					if (ie >= 0 && ip >= 0) conf[ie * n_out + ip] += 1;
 				}
 			}
 			if (a.outputs && last_epoch)
@@ -214,7 +240,7 @@ __global__ void __launch_bounds__(1024, 1) ref_train_kernel(const __grid_constan
 							float s = 0.0f;
 							for (int q = 0; q < k; ++q) s = __fadd_rn(s, hist[(size_t)q * cnt + e]);
 							s = __fadd_rn(s, delta);
-							s = __fdiv_rn(s, fmb);
+							if (fmb != 1.0f) s = __fdiv_rn(s, fmb);  // x / 1 is x in IEEE arithmetic: the division is skipped, not changed
 							w = __fsub_rn(w, s);
 							W[e] = w;
 						}
@@ -244,6 +270,8 @@ __global__ void __launch_bounds__(1024, 1) ref_train_kernel(const __grid_constan
 			a.epoch_sums[2 * ep + 0] = s_tot_err;
 			a.epoch_sums[2 * ep + 1] = s_tot_acc;
 		}
+		if (classify && conf_smem && last_epoch)
+			for (int e = t; e < n_out * n_out; e += T) a.confusion[e] = sconf[e];
 		__syncthreads();
 	}
 
@@ -522,7 +550,10 @@ static int total_nodes_of(const NetView& n)
 
 size_t ref_train_smem_bytes(const NetView& n, bool weights_in_smem)
 {
-	size_t f = 4 * (size_t)total_nodes_of(n) + GL_MAX_WEIGHT_LAYERS + 2 * (size_t)n.sizes[n.H + 1];
+	const size_t n_out = (size_t)n.sizes[n.H + 1];
+	size_t f = 4 * (size_t)total_nodes_of(n) + GL_MAX_WEIGHT_LAYERS + 2 * n_out;
+	f += 2 * ((size_t)n.sizes[0] + n_out);                       // double-buffered input and target rows
+	if (n_out * n_out <= (size_t)REF_CONF_SMEM) f += n_out * n_out;  // confusion counts
 	if (weights_in_smem)
 		for (int l = 0; l <= n.H; ++l) f += (size_t)n.sizes[l] * n.sizes[l + 1] * (1 + (size_t)n.mb);
 	return f * sizeof(float);
