@@ -181,6 +181,35 @@ def test_reference_mode_cfg2_step_level(g, oracle, cr_math):
     net.close()
 
 
+@pytest.mark.parametrize("sizes,rows,mb", [([6, 9, 40], 23, 1), ([5, 7, 3], 1, 1), ([8, 12, 33], 17, 4)])
+def test_reference_mode_live_vs_restatement_row_prefetch_and_wide_head(g, oracle, cr_math, sizes, rows, mb):
+    """Reference mode, three epochs in one launch, against the restatement bit for bit: the kernel fetches the
+    next sample's rows while the current one runs (wrapping to row 0 at an epoch's end; a one-row data set
+    prefetches its own row), and keeps an epoch's confusion counts in shared memory up to 1024 cells --
+    40 x 40 and 33 x 33 heads take the global-memory path."""
+    rng = np.random.default_rng(sum(sizes) + rows)
+    d = g.make_desc(sizes, ["relu", "sigmoid"], "classification", batch=mb, lr=0.05, momentum=0.5, mode=g.MODE_REFERENCE)
+    x = rng.uniform(-1, 1, (rows, sizes[0])).astype(np.float32)
+    y = np.full((rows, sizes[-1]), 0.01, np.float32)
+    y[np.arange(rows), rng.integers(0, sizes[-1], rows)] = 0.99
+    w = rng.uniform(-0.3, 0.3, g.weight_count(d)).astype(np.float32)
+    b = rng.uniform(-0.1, 0.1, len(sizes) - 2).astype(np.float32)
+    net = g.Net(d)
+    net.set_weights(w, b)
+    net.set_data(x, y)
+    m = net.train_epochs(3)
+    S = oracle.Restate(d, x, y, g.Metrics)
+    S.set_weights(w, b)
+    for _ in range(3):
+        ms, cms, _ = S.epoch(0)
+    wg, bg = net.get_weights()
+    ws, bs = S.get_weights()
+    assert np.array_equal(bits(wg), bits(ws)) and np.array_equal(bits(bg), bits(bs))
+    assert m.total_error == ms.total_error and m.total_accuracy == ms.total_accuracy
+    assert np.array_equal(net.confusion(), cms)
+    net.close()
+
+
 @pytest.mark.parametrize("name", ["fwd_cfg3_32_256_256_1", "fwd_cfg5_784_2048_2048_10", "fwd_cfg4_1024_4096_4096_1024"])
 def test_forward_wide_shapes_vs_golden(g, oracle, name):
     """Forward parity on the wide shapes, sampled rows, against the compiled reference's activations:
