@@ -509,6 +509,9 @@ extern "C" int gl_destroy(gl_net* n)
 		{
 			fprintf(stderr, "[grid-fused] CTA 0: phase 1 %.3f ms, barrier %.3f ms, phase 2 %.3f ms, barrier %.3f ms\n", tm[0] * 1e-6,
 			        tm[1] * 1e-6, tm[2] * 1e-6, tm[3] * 1e-6);
+			if (tm[11])
+				fprintf(stderr, "[grid-fused] inside phase 1: forward %.3f ms, head %.3f ms, deltas %.3f ms, tail %.3f ms; of which waits for weight tiles %.3f ms, barriers releasing them %.3f ms; thread 0's arithmetic in %llu forward tile steps %.3f ms\n",
+				        tm[11] * 1e-6, tm[12] * 1e-6, tm[13] * 1e-6, tm[14] * 1e-6, tm[9] * 1e-6, tm[10] * 1e-6, tm[8], tm[15] * 1e-6);
 			if (tm[4])
 				fprintf(stderr, "[grid-fused] cluster variant, inside phase 1: weights %.3f ms, forward %.3f ms, head %.3f ms, deltas %.3f ms, pass end %.3f ms\n",
 				        tm[4] * 1e-6, tm[5] * 1e-6, tm[6] * 1e-6, tm[7] * 1e-6, tm[8] * 1e-6);

@@ -304,9 +304,16 @@ __global__ void __launch_bounds__(GF_THREADS, 1) grid_fused_kernel(const __grid_
 	// weight tiles: a ring of GF_NS stages filled by bulk tensor copies (1024-byte aligned for the
 	// 128-byte swizzle), or -- where the weights' layout does not allow tensor maps -- one tile buffer
 	// filled through registers
+	// A narrow output layer (at most GF_NARROW nodes: the usual regression head) does not go through weight tiles --
+	// a [256 outputs] x [32 inputs] tile would carry one useful row and leave 255 threads idle for n_in / 32
+	// steps.  Its few weight rows are copied to shared memory once per window (wn); the forward product splits the
+	// inputs over the threads and adds the partial sums in a fixed order, the hidden deltas read wn directly.
+	const bool narrow_head = n.sizes[H + 1] <= GF_NARROW && H >= 1;
+	float* wn = reinterpret_cast<float*>(seq + 3 * GF_SEQ_MAX);          // [n_out][n_H]
+	float* nred = wn + (narrow_head ? ((n.sizes[H + 1] * n.sizes[H] + 3) & ~3) : 0);  // [8 warps][GF_ROWS][GF_NARROW]
 	uint8_t* ring_gen;
 	{
-		uint8_t* after = reinterpret_cast<uint8_t*>(seq + 3 * GF_SEQ_MAX);
+		uint8_t* after = reinterpret_cast<uint8_t*>(nred + (narrow_head ? 8 * GF_ROWS * GF_NARROW : 0));
 		const uint32_t au = smem_u32(after);
 		ring_gen = after + (((au + 1023u) & ~1023u) - au);
 	}
@@ -328,15 +335,26 @@ __global__ void __launch_bounds__(GF_THREADS, 1) grid_fused_kernel(const __grid_
 		}
 		// the tile order of one group: forward layer by layer (output chunk, then input tile), then the
 		// hidden deltas from the top (input chunk, then output tile)
-		for (int l = 0; l <= H; ++l)
+		for (int l = 0; l <= H - (narrow_head ? 1 : 0); ++l)
 			for (int o0 = 0; o0 < n.sizes[l + 1]; o0 += GF_THREADS)
 				for (int i0 = 0; i0 < n.sizes[l]; i0 += 32, ++nsteps)
 					if (t == 0) { seq[3 * nsteps] = 2 * l; seq[3 * nsteps + 1] = i0; seq[3 * nsteps + 2] = o0; }
-		for (int L = H + 1; L >= 2; --L)
+		for (int L = H + 1 - (narrow_head ? 1 : 0); L >= 2; --L)
 			for (int i0 = 0; i0 < n.sizes[L - 1]; i0 += GF_THREADS)
 				for (int o0 = 0; o0 < n.sizes[L]; o0 += 32, ++nsteps)
 					if (t == 0) { seq[3 * nsteps] = 2 * (L - 1) + 1; seq[3 * nsteps + 1] = i0; seq[3 * nsteps + 2] = o0; }
 	}
+	// optional phase timing (diagnostics): CTA 0, thread 0 adds up the nanoseconds of
+	// [phase 1, barrier, phase 2, barrier] in a.timing[0..3]
+	const bool timed = a.timing != nullptr && blockIdx.x == 0 && t == 0;
+	unsigned long long tm[16] = {}, t_a = 0, t_b = 0, t_c = 0, t_d = 0;
+	// tm[9..14]: inside phase 1 -- waits for weight tiles, the barriers that release them, forward, head, deltas, tail
+	auto now = []() {
+		unsigned long long v;
+		asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(v));
+		return v;
+	};
+
 	unsigned cs = 0;                         // ring steps consumed so far (every thread)
 	unsigned ps = 0, p_base = 0, p_end = 0;  // thread 0: steps issued, first and end step of the current window
 	bool dead = false;                       // a bounded wait ran out: stop waiting, finish the launch
@@ -349,11 +367,17 @@ __global__ void __launch_bounds__(GF_THREADS, 1) grid_fused_kernel(const __grid_
 	};
 	auto acquire = [&]() -> const float* {
 		const unsigned sidx = cs % GF_NS;
+		unsigned long long t0 = 0;
+		if (timed) t0 = now();
 		if (!dead && !mbar_wait(smem_u32(&gf_bars[sidx]), (cs / GF_NS) & 1u, &gf_abort, a.flags + 1, 30)) dead = true;
+		if (timed) tm[9] += now() - t0;
 		return reinterpret_cast<const float*>(ring_gen + sidx * GF_STAGE);
 	};
 	auto release = [&]() {
+		unsigned long long t0 = 0;
+		if (timed) t0 = now();
 		__syncthreads();  // every thread is done with the stage
+		if (timed) tm[10] += now() - t0;
 		++cs;
 		if (t == 0 && ps < p_end) issue();
 	};
@@ -377,16 +401,6 @@ __global__ void __launch_bounds__(GF_THREADS, 1) grid_fused_kernel(const __grid_
 	}
 	tile_off[H + 1] = tiles;
 
-	// optional phase timing (diagnostics): CTA 0, thread 0 adds up the nanoseconds of
-	// [phase 1, barrier, phase 2, barrier] in a.timing[0..3]
-	const bool timed = a.timing != nullptr && blockIdx.x == 0 && t == 0;
-	unsigned long long tm[4] = {0, 0, 0, 0}, t_a = 0, t_b = 0;
-	auto now = []() {
-		unsigned long long v;
-		asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(v));
-		return v;
-	};
-
 	int bad = 0;
 	for (int ep = 0; ep < a.n_epochs; ++ep)
 	{
@@ -406,12 +420,15 @@ __global__ void __launch_bounds__(GF_THREADS, 1) grid_fused_kernel(const __grid_
 				p_end = ps + (unsigned)(mine * nsteps);
 				for (int k = 0; k < GF_NS && ps < p_end; ++k) issue();
 			}
+			if (narrow_head)
+				for (int e = t; e < n.sizes[H + 1] * n.sizes[H]; e += GF_THREADS) wn[e] = __ldcg(n.W[H] + e);  // visible after the group's first barrier
 			if (timed) t_a = now();
 			// ================= phase 1: forward, head, deltas, GF_ROWS samples at a time
 			for (int gidx = blockIdx.x; gidx < groups; gidx += gridDim.x)
 			{
 				const int j0 = gidx * GF_ROWS;
 				const int valid = (len - j0) < GF_ROWS ? (len - j0) : GF_ROWS;
+				if (timed) t_c = now();
 				__syncthreads();
 				// inputs of the group, transposed to [node][row]
 				for (int e = t; e < n.sizes[0] * GF_ROWS; e += GF_THREADS)
@@ -429,6 +446,44 @@ __global__ void __launch_bounds__(GF_THREADS, 1) grid_fused_kernel(const __grid_
 					const float b = (l >= 1) ? __ldcg(n.bias + l) : 0.0f;
 					const int act = n.act[l];
 					const float par = n.par[l];
+					if (narrow_head && l == H)
+					{
+						// thread = (row r, input class q): inputs i = q, q + 32, ...; the four classes of a warp are added
+						// by shuffles, the eight warps' sums through shared memory in warp order
+						const int r = t & 7, q = t >> 3;
+						if (!use_tma) __syncthreads();  // the register path ends a layer without a barrier: the inputs must be complete
+						float s4[GF_NARROW];
+#pragma unroll
+						for (int o = 0; o < GF_NARROW; ++o) s4[o] = 0.0f;
+						for (int i = q; i < ni; i += 32)
+						{
+							const float av = in[(size_t)i * GF_ROWS + r];
+#pragma unroll
+							for (int o = 0; o < GF_NARROW; ++o)
+								if (o < no) s4[o] = fmaf(wn[o * ni + i], av, s4[o]);
+						}
+#pragma unroll
+						for (int o = 0; o < GF_NARROW; ++o)
+						{
+							s4[o] += __shfl_xor_sync(0xffffffffu, s4[o], 8);
+							s4[o] += __shfl_xor_sync(0xffffffffu, s4[o], 16);
+						}
+						if (lane < GF_ROWS)
+						{
+#pragma unroll
+							for (int o = 0; o < GF_NARROW; ++o) nred[(warp * GF_ROWS + lane) * GF_NARROW + o] = s4[o];
+						}
+						__syncthreads();
+						if (t < GF_ROWS * no)
+						{
+							const int rr = t % GF_ROWS, o = t / GF_ROWS;
+							float z = nred[rr * GF_NARROW + o];
+							for (int w = 1; w < 8; ++w) z += nred[(w * GF_ROWS + rr) * GF_NARROW + o];
+							out[(size_t)o * GF_ROWS + rr] = squash_b(z + b, act, par);
+						}
+						__syncthreads();
+						continue;
+					}
 					for (int o0 = 0; o0 < no; o0 += GF_THREADS)
 					{
 						float acc[GF_ROWS];
@@ -441,6 +496,8 @@ __global__ void __launch_bounds__(GF_THREADS, 1) grid_fused_kernel(const __grid_
 							{
 								// tile rows = output nodes o0.., 32 inputs each, 16-byte chunks XOR-swizzled by the row
 								const float* stg = acquire();
+								unsigned long long tq = 0;
+								if (timed) tq = now();
 								if (computes)
 								{
 									const float* inb = in + (size_t)i0 * GF_ROWS;
@@ -456,16 +513,33 @@ __global__ void __launch_bounds__(GF_THREADS, 1) grid_fused_kernel(const __grid_
 									};
 									if (ni - i0 >= 32)
 									{
-#pragma unroll 2
+										// the activations of four inputs (eight 16-byte broadcast loads) are fetched before the
+										// 32 multiply-adds that use them, and the loop is unrolled so that the next group's loads
+										// issue under the current group's arithmetic: with two warps per scheduler the step is
+										// bound by shared-memory latency, not by issue slots
+#pragma unroll 4
 										for (int c = 0; c < 8; ++c)
 										{
 											const float4 w4 = *reinterpret_cast<const float4*>(wrow + ((c ^ sw) << 2));
-											stepw(4 * c, w4.x); stepw(4 * c + 1, w4.y); stepw(4 * c + 2, w4.z); stepw(4 * c + 3, w4.w);
+											const float* ib = inb + 4 * c * GF_ROWS;
+											float4 x[8];
+#pragma unroll
+											for (int q = 0; q < 8; ++q) x[q] = *reinterpret_cast<const float4*>(ib + 4 * q);
+											const float wv[4] = {w4.x, w4.y, w4.z, w4.w};
+#pragma unroll
+											for (int q = 0; q < 4; ++q)
+											{
+												acc[0] = fmaf(wv[q], x[2 * q].x, acc[0]); acc[1] = fmaf(wv[q], x[2 * q].y, acc[1]);
+												acc[2] = fmaf(wv[q], x[2 * q].z, acc[2]); acc[3] = fmaf(wv[q], x[2 * q].w, acc[3]);
+												acc[4] = fmaf(wv[q], x[2 * q + 1].x, acc[4]); acc[5] = fmaf(wv[q], x[2 * q + 1].y, acc[5]);
+												acc[6] = fmaf(wv[q], x[2 * q + 1].z, acc[6]); acc[7] = fmaf(wv[q], x[2 * q + 1].w, acc[7]);
+											}
 										}
 									}
 									else
 										for (int ii = 0; ii < ni - i0; ++ii) stepw(ii, wrow[(((ii >> 2) ^ sw) << 2) + (ii & 3)]);
 								}
+								if (timed) { tm[15] += now() - tq; tm[8] += 1; }
 								release();
 							}
 						}
@@ -534,6 +608,7 @@ __global__ void __launch_bounds__(GF_THREADS, 1) grid_fused_kernel(const __grid_
 					}
 				}
 				__syncthreads();
+				if (timed) { t_d = now(); tm[11] += t_d - t_c; t_c = t_d; }
 				// ---- head: warp = sample of the group
 				if (warp < GF_ROWS)
 				{
@@ -615,6 +690,7 @@ __global__ void __launch_bounds__(GF_THREADS, 1) grid_fused_kernel(const __grid_
 					}
 				}
 				__syncthreads();
+				if (timed) { t_d = now(); tm[12] += t_d - t_c; t_c = t_d; }
 				// ---- hidden deltas: D_l = (D_{l+1} W_l) * act'(A_l), thread = input node
 				for (int L = H + 1; L >= 2; --L)
 				{
@@ -623,6 +699,34 @@ __global__ void __launch_bounds__(GF_THREADS, 1) grid_fused_kernel(const __grid_
 					const float* W = n.W[l];
 					const float* dup = Ds + (size_t)node_off[L] * GF_ROWS;
 					const int act = n.act[l - 1];
+					if (narrow_head && L == H + 1)
+					{
+						// D_H = (D_out W_H) * act'(A_H) from the shared copy of the head's weights: thread = input node
+						for (int i = t; i < ni; i += GF_THREADS)
+						{
+							float acc[GF_ROWS];
+#pragma unroll
+							for (int r = 0; r < GF_ROWS; ++r) acc[r] = 0.0f;
+							for (int o = 0; o < no; ++o)
+							{
+								const float w = wn[o * ni + i];
+								const float4 d0 = *reinterpret_cast<const float4*>(dup + o * GF_ROWS);
+								const float4 d1 = *reinterpret_cast<const float4*>(dup + o * GF_ROWS + 4);
+								acc[0] = fmaf(w, d0.x, acc[0]); acc[1] = fmaf(w, d0.y, acc[1]);
+								acc[2] = fmaf(w, d0.z, acc[2]); acc[3] = fmaf(w, d0.w, acc[3]);
+								acc[4] = fmaf(w, d1.x, acc[4]); acc[5] = fmaf(w, d1.y, acc[5]);
+								acc[6] = fmaf(w, d1.z, acc[6]); acc[7] = fmaf(w, d1.w, acc[7]);
+							}
+#pragma unroll
+							for (int r = 0; r < GF_ROWS; ++r)
+							{
+								const float av = As[(size_t)(node_off[l] + i) * GF_ROWS + r];
+								Ds[(size_t)(node_off[l] + i) * GF_ROWS + r] = (r < valid) ? acc[r] * act_der_b(av, act, 0.01f) : 0.0f;
+							}
+						}
+						__syncthreads();
+						continue;
+					}
 					for (int i0 = 0; i0 < ni; i0 += GF_THREADS)
 					{
 						float acc[GF_ROWS];
@@ -650,8 +754,25 @@ __global__ void __launch_bounds__(GF_THREADS, 1) grid_fused_kernel(const __grid_
 									};
 									if (lim == 32)
 									{
-#pragma unroll 4
-										for (int oo = 0; oo < 32; ++oo) step(oo);
+										// loads of eight rows of the tile first, then their 64 multiply-adds (see the forward loop)
+#pragma unroll 2
+										for (int ob = 0; ob < 32; ob += 8)
+										{
+											float wv[8];
+											float4 d[16];
+#pragma unroll
+											for (int q = 0; q < 8; ++q) wv[q] = stg[(ob + q) * GF_THREADS + t];
+#pragma unroll
+											for (int q = 0; q < 16; ++q) d[q] = *reinterpret_cast<const float4*>(dub + ob * GF_ROWS + 4 * q);
+#pragma unroll
+											for (int q = 0; q < 8; ++q)
+											{
+												acc[0] = fmaf(wv[q], d[2 * q].x, acc[0]); acc[1] = fmaf(wv[q], d[2 * q].y, acc[1]);
+												acc[2] = fmaf(wv[q], d[2 * q].z, acc[2]); acc[3] = fmaf(wv[q], d[2 * q].w, acc[3]);
+												acc[4] = fmaf(wv[q], d[2 * q + 1].x, acc[4]); acc[5] = fmaf(wv[q], d[2 * q + 1].y, acc[5]);
+												acc[6] = fmaf(wv[q], d[2 * q + 1].z, acc[6]); acc[7] = fmaf(wv[q], d[2 * q + 1].w, acc[7]);
+											}
+										}
 									}
 									else
 										for (int oo = 0; oo < lim; ++oo) step(oo);
@@ -718,6 +839,7 @@ __global__ void __launch_bounds__(GF_THREADS, 1) grid_fused_kernel(const __grid_
 					}
 					__syncthreads();
 				}
+				if (timed) { t_d = now(); tm[13] += t_d - t_c; t_c = t_d; }
 				// ---- the group's activations and deltas to the window scratch ([row][node]); partial sums
 				for (int r = 0; r < valid; ++r)
 				{
@@ -749,7 +871,7 @@ __global__ void __launch_bounds__(GF_THREADS, 1) grid_fused_kernel(const __grid_
 			}
 			__syncthreads();
 			if (t < GF_PART) a.part[(size_t)blockIdx.x * GF_PART + t] = s_part[t];
-			if (timed) { t_b = now(); tm[0] += t_b - t_a; }
+			if (timed) { t_b = now(); tm[0] += t_b - t_a; if (t_c) tm[14] += t_b - t_c; }
 			grid.sync();
 			if (timed) { t_a = now(); tm[1] += t_a - t_b; }
 
@@ -814,7 +936,7 @@ __global__ void __launch_bounds__(GF_THREADS, 1) grid_fused_kernel(const __grid_
 		}
 	}
 	if (timed)
-		for (int k = 0; k < 4; ++k) a.timing[k] += tm[k];
+		for (int k = 0; k < 16; ++k) a.timing[k] += tm[k];
 	if (bad) atomicOr(a.flags, 1);
 }
 
@@ -1336,6 +1458,8 @@ size_t grid_fused_smem_bytes(const NetView& n)
 	int off[GL_MAX_WEIGHT_LAYERS + 2];
 	const int tot = gf_scratch_layout(n, off);
 	size_t f = 2 * (size_t)tot * GF_ROWS + 2 * GF_ROWS + 3 * GF_SEQ_MAX;
+	if (n.sizes[n.H + 1] <= GF_NARROW && n.H >= 1)  // the narrow head's weights and the partial sums of its forward product
+		f += (((size_t)n.sizes[n.H + 1] * n.sizes[n.H] + 3) & ~(size_t)3) + 8 * GF_ROWS * GF_NARROW;
 	// + alignment slack + the ring (its first stage doubles as the register-path tile buffer, GF_WT floats)
 	return f * sizeof(float) + 1024 + (size_t)GF_NS * GF_STAGE + 64;
 }
@@ -1355,9 +1479,10 @@ int grid_fused_total_nodes(const NetView& n)
 
 int grid_fused_group_tiles(const NetView& n)
 {
+	const int skip = (n.sizes[n.H + 1] <= GF_NARROW && n.H >= 1) ? 1 : 0;  // a narrow head goes without tiles
 	int steps = 0;
-	for (int l = 0; l <= n.H; ++l) steps += ((n.sizes[l + 1] + GF_THREADS - 1) / GF_THREADS) * ((n.sizes[l] + 31) / 32);
-	for (int L = n.H + 1; L >= 2; --L) steps += ((n.sizes[L - 1] + GF_THREADS - 1) / GF_THREADS) * ((n.sizes[L] + 31) / 32);
+	for (int l = 0; l <= n.H - skip; ++l) steps += ((n.sizes[l + 1] + GF_THREADS - 1) / GF_THREADS) * ((n.sizes[l] + 31) / 32);
+	for (int L = n.H + 1 - skip; L >= 2; --L) steps += ((n.sizes[L - 1] + GF_THREADS - 1) / GF_THREADS) * ((n.sizes[L] + 31) / 32);
 	return steps;
 }
 

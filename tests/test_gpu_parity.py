@@ -181,14 +181,16 @@ def test_reference_mode_cfg2_step_level(g, oracle, cr_math):
     net.close()
 
 
-@pytest.mark.parametrize("sizes,rows,mb", [([6, 9, 40], 23, 1), ([5, 7, 3], 1, 1), ([8, 12, 33], 17, 4)])
-def test_reference_mode_live_vs_restatement_row_prefetch_and_wide_head(g, oracle, cr_math, sizes, rows, mb):
+# (the reference's hidden error sum doubles per output node, network.cpp:660-662: a 40-wide head multiplies the
+# first node's term by 2^39, so these cases need a tiny learning rate to stay finite)
+@pytest.mark.parametrize("sizes,rows,mb,lr", [([6, 9, 40], 23, 1, 2e-13), ([5, 7, 3], 1, 1, 0.05), ([8, 12, 33], 17, 4, 1e-11)])
+def test_reference_mode_live_vs_restatement_row_prefetch_and_wide_head(g, oracle, cr_math, sizes, rows, mb, lr):
     """Reference mode, three epochs in one launch, against the restatement bit for bit: the kernel fetches the
     next sample's rows while the current one runs (wrapping to row 0 at an epoch's end; a one-row data set
     prefetches its own row), and keeps an epoch's confusion counts in shared memory up to 1024 cells --
     40 x 40 and 33 x 33 heads take the global-memory path."""
     rng = np.random.default_rng(sum(sizes) + rows)
-    d = g.make_desc(sizes, ["relu", "sigmoid"], "classification", batch=mb, lr=0.05, momentum=0.5, mode=g.MODE_REFERENCE)
+    d = g.make_desc(sizes, ["relu", "sigmoid"], "classification", batch=mb, lr=lr, momentum=0.5, mode=g.MODE_REFERENCE)
     x = rng.uniform(-1, 1, (rows, sizes[0])).astype(np.float32)
     y = np.full((rows, sizes[-1]), 0.01, np.float32)
     y[np.arange(rows), rng.integers(0, sizes[-1], rows)] = 0.99
@@ -204,6 +206,7 @@ def test_reference_mode_live_vs_restatement_row_prefetch_and_wide_head(g, oracle
         ms, cms, _ = S.epoch(0)
     wg, bg = net.get_weights()
     ws, bs = S.get_weights()
+    assert np.isfinite(ws).all() and not np.array_equal(ws, w), "the case itself must stay finite and must train"
     assert np.array_equal(bits(wg), bits(ws)) and np.array_equal(bits(bg), bits(bs))
     assert m.total_error == ms.total_error and m.total_accuracy == ms.total_accuracy
     assert np.array_equal(net.confusion(), cms)
