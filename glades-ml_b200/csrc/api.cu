@@ -260,6 +260,8 @@ struct gl_net
 	cudaEvent_t evLayer[GL_MAX_WEIGHT_LAYERS] = {};
 	bool layerPending[GL_MAX_WEIGHT_LAYERS] = {};
 	cudaEvent_t evGrad[GL_MAX_WEIGHT_LAYERS + 1] = {};
+	cudaEvent_t evRead[GL_MAX_WEIGHT_LAYERS] = {};  // the window's last product that reads the OLD W_l has finished
+	size_t dpStageOff = 0;  // byte offset of the weight staging vector inside every rank's arena
 	cudaEvent_t evComm = nullptr;
 	int dpOverlap = 1;
 	int dpReserveSms = 20;  // upper bound; a product keeps fewer free where that saves it a wave of tiles
@@ -484,6 +486,7 @@ extern "C" int gl_destroy(gl_net* n)
 		if (n->layerStream[i]) cudaStreamDestroy(n->layerStream[i]);
 	for (int l = 0; l < GL_MAX_WEIGHT_LAYERS; ++l) if (n->evLayer[l]) cudaEventDestroy(n->evLayer[l]);
 	for (int l = 0; l <= GL_MAX_WEIGHT_LAYERS; ++l) if (n->evGrad[l]) cudaEventDestroy(n->evGrad[l]);
+	for (int l = 0; l < GL_MAX_WEIGHT_LAYERS; ++l) if (n->evRead[l]) cudaEventDestroy(n->evRead[l]);
 	if (n->evComm) cudaEventDestroy(n->evComm);
 	free_work(n);
 	cudaFree(n->dHlen); cudaFree(n->dHlast); cudaFree(n->dErrState); cudaFree(n->dMasks);
@@ -1449,11 +1452,11 @@ static int batched_window(gl_net* n, const float* X, const float* Y, int rows, i
 	const bool push = n->world > 1 && n->dpPush;
 	bool lo_all = true;  // peer-memory exchange: every layer's low weight parts were refreshed beside the backward pass
 	const unsigned stepv = push ? ++n->dpStep : 0u;
-	DpPeers peerFlags, peerW;
+	DpPeers peerFlags, peerStage;
 	for (int r = 0; r < DP_MAX_WORLD; ++r)
 	{
 		peerFlags.p[r] = n->dpPeerArena[r];
-		peerW.p[r] = n->dpPeerW[r];
+		peerStage.p[r] = n->dpPeerArena[r] ? static_cast<char*>(n->dpPeerArena[r]) + n->dpStageOff : nullptr;
 	}
 	CU(cudaEventRecord(n->ev0, n->stream));
 	tr.mark("start", -1, n->stream);
@@ -1482,11 +1485,9 @@ static int batched_window(gl_net* n, const float* X, const float* Y, int rows, i
 	CU(cudaMemcpyAsync(n->dLastOut, n->dA[n->H + 1] + (size_t)(rows - 1) * n->n_out, (size_t)n->n_out * sizeof(float),
 	                   cudaMemcpyDeviceToDevice, n->stream));
 
-	// Error propagation first, down the whole chain: D_{H+1} -> D_H -> ... -> D_1.  None of the weight
-	// gradients below changes what it reads (a layer's new weights are written only after every rank has
-	// signalled that layer's gradient, which it does after these products).
-	for (int L = n->H + 1; L >= 2; --L)
-	{
+	// ---- backward pass: two kinds of product per layer, as lambdas so that the order can depend on the exchange
+	// D_{L-1} = (D_L W_{L-1}) * act'(A_{L-1}): the one product of the backward pass that reads W_{L-1}
+	auto errprop = [&](int L) -> int {
 		const int l = L - 1;
 		const int ni = n->d.sizes[l], no = n->d.sizes[L];
 		GemmArgs g;
@@ -1505,22 +1506,12 @@ static int batched_window(gl_net* n, const float* X, const float* Y, int rows, i
 		bool tc = false;
 		if (int r = run_gemm(n, g, op_delta(n, L, rows), op_w(n, l), &launches, &tc)) return r;
 		n->loD[l] = tc && g.C_lo != nullptr;
-	}
-	tr.mark("deltas done", -1, n->stream);
-	// Then the weight gradients, largest layer first: under data parallelism each one starts its layer's
-	// exchange, and the largest exchange gets the remaining products to hide under.
-	int order[GL_MAX_WEIGHT_LAYERS];
-	for (int l = 0; l <= n->H; ++l) order[l] = l;
-	for (int i = 1; i <= n->H; ++i)
-		for (int j = i; j > 0 && (n->woff[order[j] + 1] - n->woff[order[j]]) > (n->woff[order[j - 1] + 1] - n->woff[order[j - 1]]); --j)
-		{
-			const int t = order[j];
-			order[j] = order[j - 1];
-			order[j - 1] = t;
-		}
-	for (int oi = 0; oi <= n->H; ++oi)
-	{
-		const int l = order[oi];
+		if (push) CU(cudaEventRecord(n->evRead[l], n->stream));  // the old W_l is not read again in this window
+		return 0;
+	};
+	// G_l = D_{l+1}^T A_l (times learning rate, plus decay terms); under data parallelism followed by the first half
+	// of the layer's exchange.  `last`: no product follows, the owner's update may take the whole GPU.
+	auto gradient = [&](int l, bool last) -> int {
 		const int L = l + 1;
 		const int ni = n->d.sizes[l], no = n->d.sizes[L];
 		const float* Al = (l == 0) ? X : n->dA[l];
@@ -1571,7 +1562,7 @@ static int batched_window(gl_net* n, const float* X, const float* Y, int rows, i
 		{
 			// this rank's contributions to layer l have been stored at their owners: tell them, and let the
 			// layer's exchange stream do this rank's own band (sum the sources in rank order, update, write the
-			// new weights into every replica) while the compute stream goes on with the other gradients
+			// new weights into every replica's STAGING vector) while the compute stream goes on
 			cudaStream_t cs = n->layerStream[l % gl_net::DP_COMM_STREAMS];
 			CU(launch_dp_signal(peerFlags, n->world, DP_WORD_GFLAG + l * DP_MAX_WORLD + n->rank, stepv, n->stream));
 			tr.mark("grad stored L", l, n->stream);
@@ -1584,25 +1575,11 @@ static int batched_window(gl_net* n, const float* X, const float* Y, int rows, i
 			own_rows = own_rows < 0 ? 0 : (own_rows > band ? band : own_rows);
 			const float* part = reinterpret_cast<const float*>(n->dpArena + DP_FLAG_BYTES) + n->dpSlotOff[l];
 			CU(launch_dp_reduce_update(part, n->dpSlotOff[n->H + 1], n->world, (long long)own_rows * ni, 1.0f / (float)global_rows,
-			                           n->woff[l] + (long long)n->rank * band * ni, peerW, n->rank, peerFlags,
-			                           oi == n->H ? 148 * 4 : n->dpPushBlocks, cs));
+			                           n->woff[l] + (long long)n->rank * band * ni, n->dW, peerStage, n->rank, peerFlags,
+			                           last ? 148 * 4 : n->dpPushBlocks, cs));
 			CU(launch_dp_signal(peerFlags, n->world, DP_WORD_WFLAG + l * DP_MAX_WORLD + n->rank, stepv, cs));
 			tr.mark("band updated L", l, cs);
-			// once every owner's band of this layer has landed here, split off the low TF32 parts of the
-			// layer's new weights; evLayer[l] then releases the next product that reads W_l
-			CU(launch_dp_wait(n->dpArena, DP_WORD_WFLAG + l * DP_MAX_WORLD, 1, n->world, 0, 0, stepv, n->dFlags + 1, 40 + l, cs));
-			const int64_t cnt = n->woff[l + 1] - n->woff[l];
-			if (n->dWlo && cnt % 4 == 0 && n->woff[l] % 4 == 0)
-			{
-				CU(launch_split_lo(n->dW + n->woff[l], n->dWlo + n->woff[l], cnt, cs));
-				++launches;
-			}
-			else
-				lo_all = false;
-			tr.mark("layer complete L", l, cs);
-			CU(cudaEventRecord(n->evLayer[l], cs));
-			n->layerPending[l] = true;
-			launches += 5;
+			launches += 4;
 		}
 		else if (n->world > 1 && n->dpOverlap)
 		{
@@ -1613,6 +1590,67 @@ static int batched_window(gl_net* n, const float* X, const float* Y, int rows, i
 			NC(g_nccl.AllReduce(n->dG + n->woff[l], n->dG + n->woff[l], (size_t)(n->woff[l + 1] - n->woff[l]), NCCL_FLOAT32,
 			                    NCCL_SUM, n->comm, n->commStream));
 		}
+		return 0;
+	};
+	if (push)
+	{
+		// Exchange over peer memory: the owners write a layer's new weights into staging vectors, so nothing that
+		// this window still reads is overwritten and every gradient can be taken as early as its delta exists --
+		// hidden layers from the top (each preceded by the error propagation that makes its delta), the output
+		// layer's gradient last: its weights are the last ones the next window's forward pass needs, so its
+		// exchange has the longest stretch to hide under.  The largest exchanges thus start early and run under the
+		// rest of the backward pass instead of piling up on NVLink behind the last product.
+		for (int l = n->H - 1; l >= 0; --l)
+		{
+			if (int r = errprop(l + 2)) return r;
+			if (int r = gradient(l, false)) return r;
+		}
+		tr.mark("deltas done", -1, n->stream);
+		if (int r = gradient(n->H, true)) return r;
+		// second half of every layer's exchange, queued now that this window's readers of the old weights are all
+		// on the compute stream: once every owner's band of layer l has landed in this rank's staging vector and
+		// the product that read the old W_l has finished, copy the layer into the weights (splitting off the low
+		// TF32 parts on the way); evLayer[l] then releases the next product that reads W_l
+		const float* stage = reinterpret_cast<const float*>(n->dpArena + n->dpStageOff);
+		for (int k = 0; k <= n->H; ++k)
+		{
+			const int l = (k < n->H) ? n->H - 1 - k : n->H;  // the order the exchanges were started in
+			cudaStream_t cs = n->layerStream[l % gl_net::DP_COMM_STREAMS];
+			CU(launch_dp_wait(n->dpArena, DP_WORD_WFLAG + l * DP_MAX_WORLD, 1, n->world, 0, 0, stepv, n->dFlags + 1, 40 + l, cs));
+			if (l >= 1) CU(cudaStreamWaitEvent(cs, n->evRead[l], 0));
+			const int64_t cnt = n->woff[l + 1] - n->woff[l];
+			if (n->dWlo && cnt % 4 == 0 && n->woff[l] % 4 == 0)
+				CU(launch_copy_split_lo(stage + n->woff[l], n->dW + n->woff[l], n->dWlo + n->woff[l], cnt, cs));
+			else
+			{
+				CU(cudaMemcpyAsync(n->dW + n->woff[l], stage + n->woff[l], (size_t)cnt * sizeof(float), cudaMemcpyDeviceToDevice, cs));
+				lo_all = false;
+			}
+			tr.mark("layer complete L", l, cs);
+			CU(cudaEventRecord(n->evLayer[l], cs));
+			n->layerPending[l] = true;
+			launches += 2;
+		}
+	}
+	else
+	{
+		// Error propagation first, down the whole chain: D_{H+1} -> D_H -> ... -> D_1, then the weight gradients,
+		// largest layer first (with the NCCL exchange each one starts its layer's all-reduce, and the largest one
+		// gets the remaining products to hide under; the weights change only after all of them, in launch_update)
+		for (int L = n->H + 1; L >= 2; --L)
+			if (int r = errprop(L)) return r;
+		tr.mark("deltas done", -1, n->stream);
+		int order[GL_MAX_WEIGHT_LAYERS];
+		for (int l = 0; l <= n->H; ++l) order[l] = l;
+		for (int i = 1; i <= n->H; ++i)
+			for (int j = i; j > 0 && (n->woff[order[j] + 1] - n->woff[order[j]]) > (n->woff[order[j - 1] + 1] - n->woff[order[j - 1]]); --j)
+			{
+				const int t = order[j];
+				order[j] = order[j - 1];
+				order[j - 1] = t;
+			}
+		for (int oi = 0; oi <= n->H; ++oi)
+			if (int r = gradient(order[oi], oi == n->H)) return r;
 	}
 	if (n->world > 1 && !push)
 	{
@@ -2374,7 +2412,10 @@ static int dp_push_setup(gl_net* n)
 		off += ((cap + 3) / 4) * 4;
 	}
 	n->dpSlotOff[n->H + 1] = off;
-	const size_t bytes = DP_FLAG_BYTES + (size_t)W * (size_t)off * sizeof(float);
+	// behind the gradient slots: a staging vector for the new weights (the owners write a layer's updated bands there;
+	// every rank copies them into its weights once its own last reader of the old ones has finished)
+	n->dpStageOff = ((DP_FLAG_BYTES + (size_t)W * (size_t)off * sizeof(float)) + 255) & ~(size_t)255;
+	const size_t bytes = n->dpStageOff + ((size_t)n->nw + 4) * sizeof(float);
 	int failed = 0;
 	char why[160] = "";
 	auto local = [&](cudaError_t e, const char* what) {
@@ -2531,6 +2572,7 @@ extern "C" int gl_dp_init(gl_net* n, int32_t rank, int32_t world, const void* id
 		CU(cudaDeviceGetStreamPriorityRange(&lo, &hi));
 		for (int i = 0; i < gl_net::DP_COMM_STREAMS; ++i) CU(cudaStreamCreateWithPriority(&n->layerStream[i], cudaStreamNonBlocking, hi));
 		for (int l = 0; l < GL_MAX_WEIGHT_LAYERS; ++l) CU(cudaEventCreateWithFlags(&n->evLayer[l], cudaEventDisableTiming));
+		for (int l = 0; l < GL_MAX_WEIGHT_LAYERS; ++l) CU(cudaEventCreateWithFlags(&n->evRead[l], cudaEventDisableTiming));
 	}
 	CU(cudaEventCreateWithFlags(&n->evComm, cudaEventDisableTiming));
 	if (const char* e = getenv("GLADES_DP_OVERLAP")) n->dpOverlap = atoi(e) != 0;

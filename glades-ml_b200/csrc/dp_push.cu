@@ -110,15 +110,17 @@ __global__ void __launch_bounds__(256) dp_push_bands_kernel(const float* __restr
 	}
 }
 
-// Owner side: g = sum over sources (rank order) of part[src * src_stride + i]; w = W[wbase + i] - g * inv_mb,
-// written into every rank's weight vector.  Non-finite results raise word `bad_word` in every rank's flags.
+// Owner side: g = sum over sources (rank order) of part[src * src_stride + i]; w = w_own[wbase + i] - g * inv_mb,
+// written at [wbase + i] of every rank's destination vector W.p[r] (the staging vectors: a rank's own weights stay
+// untouched until it commits the layer).  Non-finite results raise word `bad_word` in every rank's flags.
 __global__ void __launch_bounds__(256) dp_reduce_update_kernel(const float* __restrict__ part, long long src_stride, int world,
-                                                                long long count, float inv_mb, long long wbase, DpPeers W,
-                                                                int self, DpPeers flags, int bad_word)
+                                                                long long count, float inv_mb, long long wbase,
+                                                                const float* __restrict__ w_own, DpPeers W, DpPeers flags,
+                                                                int bad_word)
 {
 	const long long stride = (long long)gridDim.x * blockDim.x;
 	const long long i0 = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-	const float* Wown = reinterpret_cast<const float*>(W.p[self]) + wbase;
+	const float* Wown = w_own + wbase;
 	int bad = 0;
 	if (((count | wbase | src_stride) & 3) == 0)
 	{
@@ -256,13 +258,14 @@ cudaError_t launch_dp_push_bands(const float* G, int n_out, int n_in, int band, 
 }
 
 cudaError_t launch_dp_reduce_update(const float* part, long long src_stride, int world, long long count, float inv_mb,
-                                    long long wbase, const DpPeers& W, int self, const DpPeers& flags, int blocks, cudaStream_t s)
+                                    long long wbase, const float* w_own, const DpPeers& W, int self, const DpPeers& flags, int blocks,
+                                    cudaStream_t s)
 {
 	if (count < 1) return cudaSuccess;
 	long long need = (count / 4 + 255) / 256;
 	if (need < 1) need = 1;
 	if (need > blocks) need = blocks;
-	dp_reduce_update_kernel<<<(unsigned)need, 256, 0, s>>>(part, src_stride, world, count, inv_mb, wbase, W, self, flags,
+	dp_reduce_update_kernel<<<(unsigned)need, 256, 0, s>>>(part, src_stride, world, count, inv_mb, wbase, w_own, W, flags,
 	                                                       DP_WORD_BAD + self);
 	return cudaGetLastError();
 }

@@ -552,6 +552,19 @@ __global__ void __launch_bounds__(256) split_lo_kernel(const float4* __restrict_
 	}
 }
 
+// dst = src and lo = the low TF32 parts of src, in one pass (lo may be NULL)
+__global__ void __launch_bounds__(256) copy_split_lo_kernel(const float4* __restrict__ src, float4* __restrict__ dst, float4* __restrict__ lo,
+                                                             long long n4)
+{
+	const long long stride = (long long)gridDim.x * blockDim.x;
+	for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride)
+	{
+		const float4 a = __ldcg(src + i);
+		dst[i] = a;
+		if (lo) lo[i] = make_float4(tf32_lo(a.x), tf32_lo(a.y), tf32_lo(a.z), tf32_lo(a.w));
+	}
+}
+
 __global__ void __launch_bounds__(256) scale_split_lo_kernel(const float* __restrict__ src, const float* __restrict__ rowscale,
                                                               int ld, float* __restrict__ dst, float* __restrict__ lo,
                                                               long long n)
@@ -729,6 +742,18 @@ cudaError_t launch_split_lo(const float* src, float* lo, long long count, cudaSt
 	if (blocks > 148 * 8) blocks = 148 * 8;
 	if (blocks < 1) blocks = 1;
 	split_lo_kernel<<<(unsigned)blocks, 256, 0, s>>>(reinterpret_cast<const float4*>(src), reinterpret_cast<float4*>(lo), n4);
+	return cudaGetLastError();
+}
+
+cudaError_t launch_copy_split_lo(const float* src, float* dst, float* lo, long long count, cudaStream_t s)
+{
+	if (count < 1) return cudaSuccess;
+	if ((count & 3) || (((uintptr_t)src | (uintptr_t)dst | (uintptr_t)lo) & 15)) return cudaErrorInvalidValue;
+	const long long n4 = count >> 2;
+	long long blocks = (n4 + 255) / 256;
+	if (blocks > 148 * 4) blocks = 148 * 4;
+	copy_split_lo_kernel<<<(unsigned)blocks, 256, 0, s>>>(reinterpret_cast<const float4*>(src), reinterpret_cast<float4*>(dst),
+	                                                     reinterpret_cast<float4*>(lo), n4);
 	return cudaGetLastError();
 }
 

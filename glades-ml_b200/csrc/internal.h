@@ -233,8 +233,10 @@ cudaError_t launch_dp_wait(const void* arena, int w0, int groups, int per_group,
 cudaError_t launch_dp_hello_write(const DpPeers& slot_heads, const DpPeers& flags, int world, int self, cudaStream_t s);
 cudaError_t launch_dp_hello_check(const float* slots, long long slot_stride, int world, int* status, int code, cudaStream_t s);
 cudaError_t launch_dp_push_bands(const float* G, int n_out, int n_in, int band, const DpPeers& slot, cudaStream_t s);
+// w_own: this rank's weight vector (read); W.p[r]: rank r's destination vector (the staging vector inside its arena)
 cudaError_t launch_dp_reduce_update(const float* part, long long src_stride, int world, long long count, float inv_mb,
-                                    long long wbase, const DpPeers& W, int self, const DpPeers& flags, int blocks, cudaStream_t s);
+                                    long long wbase, const float* w_own, const DpPeers& W, int self, const DpPeers& flags, int blocks,
+                                    cudaStream_t s);
 cudaError_t launch_dp_small_push(const float* gb, const double* sums2, const DpPeers& flags, int world, int self, int parity,
                                  unsigned value, cudaStream_t s);
 cudaError_t launch_dp_finish(const void* arena, int world, int parity, float* gb_out, double* sums2_out, float* bias,

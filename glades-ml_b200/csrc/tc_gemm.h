@@ -35,6 +35,8 @@ bool tc_make_map2d(void* out128, const float* base, long long rows, long long co
 // lo[i] = tf32_round(src[i] - trunc_tf32(src[i])); with rowscale: first dst_scaled[i] = src[i] *
 // rowscale[i / ld] is formed (and stored), and lo is taken from that.
 cudaError_t launch_split_lo(const float* src, float* lo, long long count, cudaStream_t s);
+// dst = src and (lo != NULL) lo = low TF32 parts of src; count a multiple of 4, pointers 16-byte aligned
+cudaError_t launch_copy_split_lo(const float* src, float* dst, float* lo, long long count, cudaStream_t s);
 cudaError_t launch_scale_split_lo(const float* src, const float* rowscale, int ld, float* dst_scaled, float* lo,
                                   long long count, cudaStream_t s);
 
