@@ -262,6 +262,7 @@ struct gl_net
 	cudaEvent_t evGrad[GL_MAX_WEIGHT_LAYERS + 1] = {};
 	cudaEvent_t evRead[GL_MAX_WEIGHT_LAYERS] = {};  // the window's last product that reads the OLD W_l has finished
 	size_t dpStageOff = 0;  // byte offset of the weight staging vector inside every rank's arena
+	int dpStoreMode = 0;    // how a gradient's bands reach their owners: 0 from the product's epilogue, 1 copy kernel, 2 copy engines
 	cudaEvent_t evComm = nullptr;
 	int dpOverlap = 1;
 	int dpReserveSms = 20;  // upper bound; a product keeps fewer free where that saves it a wave of tiles
@@ -1517,6 +1518,7 @@ static int batched_window(gl_net* n, const float* X, const float* Y, int rows, i
 		const float* Al = (l == 0) ? X : n->dA[l];
 		const Operand opD = op_delta(n, L, rows);
 		const float* colterm = nullptr;
+		bool fused_store = false;
 		if (n->d.wd1[l] != 0.0f || n->d.wd2[l] != 0.0f)
 		{
 			CU(launch_decay_colterm(Al, rows, ni, n->dC[l], n->d.lr[l], n->d.wd1[l], n->d.wd2[l], n->dColterm, n->stream));
@@ -1535,7 +1537,7 @@ static int batched_window(gl_net* n, const float* X, const float* Y, int rows, i
 			g.alpha = n->d.lr[l];
 			g.colterm = colterm;
 			g.sm_reserve = dp_reserve_for(n, no, ni);
-			if (push)
+			if (push && n->dpStoreMode == 0)
 			{
 				// the tensor-core epilogue stores every row band straight into its owner's memory
 				g.peer_maps = static_cast<const char*>(n->dpMaps) + (size_t)l * DP_MAX_WORLD * 128;
@@ -1545,7 +1547,8 @@ static int batched_window(gl_net* n, const float* X, const float* Y, int rows, i
 			}
 			bool gtc = false;
 			if (int r = run_gemm(n, g, opD, op_act(n, l, X, rows), &launches, &gtc)) return r;
-			if (push && !gtc)
+			fused_store = push && n->dpStoreMode == 0;
+			if (fused_store && !gtc)
 			{
 				DpPeers slot;
 				for (int o = 0; o < DP_MAX_WORLD; ++o) slot.p[o] = n->hostBases[l][o];
@@ -1564,10 +1567,42 @@ static int batched_window(gl_net* n, const float* X, const float* Y, int rows, i
 			// layer's exchange stream do this rank's own band (sum the sources in rank order, update, write the
 			// new weights into every replica's STAGING vector) while the compute stream goes on
 			cudaStream_t cs = n->layerStream[l % gl_net::DP_COMM_STREAMS];
-			CU(launch_dp_signal(peerFlags, n->world, DP_WORD_GFLAG + l * DP_MAX_WORLD + n->rank, stepv, n->stream));
-			tr.mark("grad stored L", l, n->stream);
-			CU(cudaEventRecord(n->evGrad[l], n->stream));
-			CU(cudaStreamWaitEvent(cs, n->evGrad[l], 0));
+			if (fused_store)
+			{
+				CU(launch_dp_signal(peerFlags, n->world, DP_WORD_GFLAG + l * DP_MAX_WORLD + n->rank, stepv, n->stream));
+				tr.mark("grad stored L", l, n->stream);
+				CU(cudaEventRecord(n->evGrad[l], n->stream));
+				CU(cudaStreamWaitEvent(cs, n->evGrad[l], 0));
+			}
+			else
+			{
+				// the product wrote the gradient locally; its bands travel to their owners on the layer's exchange
+				// stream, beside the next products: by a copy kernel (mode 1) or by the copy engines (mode 2)
+				CU(cudaEventRecord(n->evGrad[l], n->stream));
+				CU(cudaStreamWaitEvent(cs, n->evGrad[l], 0));
+				if (n->dpStoreMode == 1)
+				{
+					DpPeers slot;
+					for (int o = 0; o < DP_MAX_WORLD; ++o) slot.p[o] = n->hostBases[l][o];
+					CU(launch_dp_push_bands(n->dG + n->woff[l], no, ni, n->dpBand[l], slot, cs));
+					++launches;
+				}
+				else
+				{
+					const int band = n->dpBand[l];
+					for (int k = 0; k < n->world; ++k)
+					{
+						const int o = (n->rank + 1 + k) % n->world;  // every rank starts with another owner
+						int rows_o = no - o * band;
+						rows_o = rows_o < 0 ? 0 : (rows_o > band ? band : rows_o);
+						if (rows_o > 0)
+							CU(cudaMemcpyAsync(n->hostBases[l][o], n->dG + n->woff[l] + (size_t)o * band * ni, (size_t)rows_o * ni * sizeof(float),
+							                   cudaMemcpyDeviceToDevice, cs));
+					}
+				}
+				CU(launch_dp_signal(peerFlags, n->world, DP_WORD_GFLAG + l * DP_MAX_WORLD + n->rank, stepv, cs));
+				tr.mark("grad stored L", l, cs);
+			}
 			CU(launch_dp_wait(n->dpArena, DP_WORD_GFLAG + l * DP_MAX_WORLD, 1, n->world, 0, 0, stepv, n->dFlags + 1, 20 + l, cs));
 			tr.mark("owner has all L", l, cs);
 			const int band = n->dpBand[l];
@@ -2578,6 +2613,7 @@ extern "C" int gl_dp_init(gl_net* n, int32_t rank, int32_t world, const void* id
 	if (const char* e = getenv("GLADES_DP_OVERLAP")) n->dpOverlap = atoi(e) != 0;
 	if (const char* e = getenv("GLADES_DP_RESERVE_SMS")) n->dpReserveSms = atoi(e);
 	if (const char* e = getenv("GLADES_DP_PUSH_BLOCKS")) n->dpPushBlocks = atoi(e) > 0 ? atoi(e) : 296;
+	if (const char* e = getenv("GLADES_DP_STORE")) n->dpStoreMode = (atoi(e) >= 0 && atoi(e) <= 2) ? atoi(e) : 0;
 	// GLADES_DP_PUSH=0: the NCCL all-reduce path; =1: the exchange over peer memory or an error;
 	// unset: the exchange over peer memory when the ranks can map each other's memory, else NCCL
 	const char* e = getenv("GLADES_DP_PUSH");

@@ -269,9 +269,12 @@ __global__ void __launch_bounds__(256) head_kernel(const HeadArgs h)
 		float mx = -INFINITY, inv_den = 1.0f;
 		if (h.softmax)
 		{
+			// (unrolled: the row's loads are independent, and one warp per row leaves few warps to hide their latency)
+#pragma unroll 8
 			for (int o = lane; o < h.n; o += 32) mx = fmaxf(mx, p[o]);
 			mx = warp_max(mx);
 			float den = 0.0f;
+#pragma unroll 8
 			for (int o = lane; o < h.n; o += 32) den += expf(p[o] - mx);
 			den = warp_sum(den);
 			inv_den = 1.0f / den;
@@ -279,6 +282,7 @@ __global__ void __launch_bounds__(256) head_kernel(const HeadArgs h)
 		// running first-maximum argmax of expected and predicted (value, index) per lane
 		float be = 0.0f, bp = 0.0f;
 		int ie = -1, ip = -1;
+#pragma unroll 4
 		for (int o = lane; o < h.n; o += 32)
 		{
 			float pv = p[o];

@@ -8,8 +8,9 @@
 //      FFMA kernel -- then raises a per-layer flag in every rank's arena (dp_signal_kernel);
 //   2. the owner waits for the flags of all sources (dp_wait_kernel, bounded), sums the slots in rank
 //      order, applies the update to its band of the weights and writes the new weights into EVERY
-//      rank's weight vector (dp_reduce_update_kernel), then raises a "weights of layer l from owner
-//      o" flag everywhere;
+//      rank's staging vector (dp_reduce_update_kernel; a rank copies a layer from staging into its
+//      weights once its own readers of the old weights are done), then raises a "weights of layer l
+//      from owner o" flag everywhere;
 //   3. the scalar bias sums and the loss / accuracy sums travel as one 80-byte record per rank
 //      (dp_small_push_kernel), summed in rank order by dp_finish_kernel on every rank.
 // Sums are taken in rank order, so every replica ends a window with bit-identical weights, run to

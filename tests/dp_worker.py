@@ -99,7 +99,8 @@ def main():
             m = net.train_window(0, count, want_metrics=(step == steps - 1))
         wg, bg = net.get_weights()
         dc = [a - c for a, c in zip(g.tc_variant_counts(), before)]
-        if mode == "gpu_tc_wide" and net.dp_mode() == 2 and not (dc[3] >= steps and dc[1] >= steps and dc[2] >= steps):
+        fused_store = os.environ.get("GLADES_DP_STORE", "0") == "0"  # other modes copy the bands after a plain product
+        if mode == "gpu_tc_wide" and net.dp_mode() == 2 and fused_store and not (dc[3] >= steps and dc[1] >= steps and dc[2] >= steps):
             print("the 256-wide persistent peer-store variant did not run: %r" % (dc,))
             ok = False
         tw = torch.from_numpy(wg.copy())
