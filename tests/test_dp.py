@@ -56,6 +56,17 @@ def test_two_gpus_reproduce_one_gpu(g, mode, push):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("store", ["1", "2"])
+def test_two_gpus_other_ways_of_moving_the_gradient_bands(g, store):
+    """GLADES_DP_STORE: the gradient product writes locally and its bands reach their owners by a copy kernel (1)
+    or by the copy engines (2) on the layer's exchange stream, instead of from the product's epilogue."""
+    if g.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    r = _launch("gpu_tc_wide", 2, GLADES_DP_PUSH="1", GLADES_DP_STORE=store)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+
+
+@pytest.mark.gpu
 @pytest.mark.parametrize("ranks", [4, 8])
 def test_more_gpus_reproduce_one_gpu(g, ranks):
     """The exchange over peer memory with 4 and 8 ranks (bands of 4 and 2 row tiles, the rotated walk over the
