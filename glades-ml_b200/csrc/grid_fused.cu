@@ -949,7 +949,7 @@ __global__ void __launch_bounds__(GF_THREADS, 1) grid_fused_kernel(const __grid_
 // (forward) and the weight columns of its nodes (hidden deltas) in shared memory for the whole window -- read
 // from L2 once per window instead of once per sample group -- computes its nodes' activations for the
 // CF_R rows and stores them into the activation buffers of all CF_CS CTAs over distributed shared memory
-// (st.shared::cluster; no multicast loads), one cluster barrier per layer.  The head runs on every CTA's own
+// (st.shared::cluster: plain stores), one cluster barrier per layer.  The head runs on every CTA's own
 // copy (side effects from cluster rank 0 only).  Activations and deltas go to the same window scratch as in
 // grid_fused_kernel, and phase 2 sums the window's rows per weight tile -- here with a 4 x 4 register tile per
 // lane and the 64 rows of a step dealt over the eight warps, whose partial sums are added in warp order.
