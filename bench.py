@@ -859,7 +859,8 @@ def main():
                              % (nwin, nwin * lb * (sizes[0] + sizes[-1]) * 4 / 1e6, (2 * lb * sum(sizes) + net.nw) * 4 / 1e6),
                        "gradient_exchange": {0: None, 1: "NCCL all-reduce per layer, overlapped with the backward pass",
                                              2: "row bands stored into their owner's memory by the gradient product's "
-                                                "epilogue over NVLink; owner sums, updates, writes every replica"}[dp_mode]}),
+                                                "epilogue over NVLink; owner sums, updates, writes every replica's staging "
+                                                "vector; each rank commits a layer after its last reader of the old weights"}[dp_mode]}),
             "e2e": {"value": e2e_value, "unit": "samples/s" if train else "rows/s", "h2d_bytes_per_step": xb + yb,
                     "d2h_bytes_per_step": d2h_bytes, "steps": e2e_steps},
             "gpu_launches": int(launches),
