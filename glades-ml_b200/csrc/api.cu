@@ -194,6 +194,8 @@ struct gl_net
 	float* dD[GL_MAX_WEIGHT_LAYERS + 2] = {};
 	float* dC[GL_MAX_WEIGHT_LAYERS] = {};  // momentum weights per layer (NULL when momentum is 0)
 	float* dColterm = nullptr;
+	double* dSumPart = nullptr;      // scratch of the reproducible bias sums (launch_sum_scaled)
+	unsigned* dSumTicket = nullptr;
 	int cRows = -1, cGlobal = -1, cFirst = -1;
 	int* dArgmax = nullptr;
 	// host-window staging
@@ -414,6 +416,9 @@ extern "C" int gl_create(const gl_net_desc* d, gl_net** out)
 		int maxn = 1;
 		for (int l = 0; l <= H + 1; ++l) maxn = d->sizes[l] > maxn ? d->sizes[l] : maxn;
 		CU(cudaMalloc(&n->dColterm, maxn * sizeof(float)));
+		CU(cudaMalloc(&n->dSumPart, SUM_SCALED_MAX_BLOCKS * sizeof(double)));
+		CU(cudaMalloc(&n->dSumTicket, sizeof(unsigned)));
+		CU(cudaMemset(n->dSumTicket, 0, sizeof(unsigned)));
 	}
 	if (d->gemm < GL_GEMM_AUTO || d->gemm > GL_GEMM_GRID_FUSED || (d->gemm == GL_GEMM_GRID_FUSED && !grid_fused_fits(n)))
 	{
@@ -504,7 +509,7 @@ extern "C" int gl_destroy(gl_net* n)
 	cudaFree(n->dW); cudaFree(n->dBias); cudaFree(n->dG); cudaFree(n->dBscale); cudaFree(n->dFlags);
 	cudaFree(n->dSums); cudaFree(n->dSumsF); cudaFree(n->dConf); cudaFree(n->dHist); cudaFree(n->dHistLen);
 	cudaFree(n->dLastOut);
-	cudaFree(n->dScratch); cudaFree(n->ownX); cudaFree(n->ownY); cudaFree(n->dColterm);
+	cudaFree(n->dScratch); cudaFree(n->ownX); cudaFree(n->ownY); cudaFree(n->dColterm); cudaFree(n->dSumPart); cudaFree(n->dSumTicket);
 	cudaFree(n->dXwin); cudaFree(n->dYwin);
 	if (n->gfTiming)
 	{
@@ -1558,7 +1563,7 @@ static int batched_window(gl_net* n, const float* X, const float* Y, int rows, i
 		}
 		if (l >= 1)
 		{
-			CU(launch_sum_scaled(n->dD[L], (int64_t)rows * no, n->d.lr[l], n->dG + n->nw + l, n->stream));
+			CU(launch_sum_scaled(n->dD[L], (int64_t)rows * no, n->d.lr[l], n->dG + n->nw + l, n->dSumPart, n->dSumTicket, n->stream));
 			++launches;
 		}
 		if (push)

@@ -362,29 +362,64 @@ cudaError_t launch_head(const HeadArgs& h, cudaStream_t s)
 }
 
 // ---------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(256) sum_scaled_kernel(const float* D, long long count, float alpha, float* out)
+// *out += alpha * sum(D[0..count)), reproducibly: every block sums a fixed set of elements in double and leaves its
+// partial in `part`; the block that arrives last (a ticket counter) adds the partials in a fixed order and is the only
+// one to touch *out.  (A float atomic per block would make the scalar bias depend on the order the blocks finish in.)
+// part: gridDim.x doubles; ticket: one word, zero before the launch and zero again after it.
+__global__ void __launch_bounds__(256) sum_scaled_kernel(const float* __restrict__ D, long long count, float alpha, float* out,
+                                                         double* part, unsigned* ticket)
 {
 	double acc = 0.0;
-	for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += (long long)gridDim.x * blockDim.x)
-		acc += (double)D[i];
+	const long long stride = (long long)gridDim.x * blockDim.x;
+	const long long i0 = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+	if ((reinterpret_cast<uintptr_t>(D) & 15) == 0)
+	{
+		const long long n4 = count >> 2;
+		const float4* D4 = reinterpret_cast<const float4*>(D);
+#pragma unroll 4
+		for (long long i = i0; i < n4; i += stride)
+		{
+			const float4 v = D4[i];
+			acc += ((double)v.x + (double)v.y) + ((double)v.z + (double)v.w);
+		}
+		for (long long i = (n4 << 2) + i0; i < count; i += stride) acc += (double)D[i];
+	}
+	else
+		for (long long i = i0; i < count; i += stride) acc += (double)D[i];
 	acc = warp_sum_d(acc);
 	__shared__ double sw[8];
+	__shared__ bool last;
 	if ((threadIdx.x & 31) == 0) sw[threadIdx.x >> 5] = acc;
 	__syncthreads();
 	if (threadIdx.x == 0)
 	{
 		double t = 0.0;
 		for (int w = 0; w < 8; ++w) t += sw[w];
-		atomicAdd(out, (float)(t * (double)alpha));
+		part[blockIdx.x] = t;
+		__threadfence();
+		last = atomicAdd(ticket, 1u) == gridDim.x - 1;
+	}
+	__syncthreads();
+	if (last && threadIdx.x < 32)
+	{
+		__threadfence();
+		double t = 0.0;
+		for (unsigned b = threadIdx.x; b < gridDim.x; b += 32) t += __ldcg(part + b);
+		t = warp_sum_d(t);
+		if (threadIdx.x == 0)
+		{
+			*out += (float)(t * (double)alpha);
+			*ticket = 0u;
+		}
 	}
 }
 
-cudaError_t launch_sum_scaled(const float* D, long long count, float alpha, float* out, cudaStream_t s)
+cudaError_t launch_sum_scaled(const float* D, long long count, float alpha, float* out, double* part, unsigned* ticket, cudaStream_t s)
 {
-	long long blocks = (count + 256 * 8 - 1) / (256 * 8);
-	if (blocks > 148 * 4) blocks = 148 * 4;
+	long long blocks = (count + 256 * 16 - 1) / (256 * 16);
+	if (blocks > SUM_SCALED_MAX_BLOCKS) blocks = SUM_SCALED_MAX_BLOCKS;
 	if (blocks < 1) blocks = 1;
-	sum_scaled_kernel<<<(unsigned)blocks, 256, 0, s>>>(D, count, alpha, out);
+	sum_scaled_kernel<<<(unsigned)blocks, 256, 0, s>>>(D, count, alpha, out, part, ticket);
 	return cudaGetLastError();
 }
 

@@ -133,7 +133,10 @@ struct HeadArgs
 cudaError_t launch_head(const HeadArgs& h, cudaStream_t s);
 
 // sum over all elements of D [rows*n] times alpha, atomically added to *out
-cudaError_t launch_sum_scaled(const float* D, long long count, float alpha, float* out, cudaStream_t s);
+// *out += alpha * sum(D), reproducibly; part: SUM_SCALED_MAX_BLOCKS doubles of scratch, ticket: one zeroed word (both owned
+// by the caller and used by one launch at a time)
+constexpr int SUM_SCALED_MAX_BLOCKS = 148 * 8;
+cudaError_t launch_sum_scaled(const float* D, long long count, float alpha, float* out, double* part, unsigned* ticket, cudaStream_t s);
 // colterm[i] = lr * sum_j c_j * (wd1*|A[j][i]| + wd2*A[j][i])
 cudaError_t launch_decay_colterm(const float* A, int rows, int n, const float* c, float lr, float wd1, float wd2,
                                  float* colterm, cudaStream_t s);
